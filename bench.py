@@ -1,0 +1,318 @@
+#!/usr/bin/env python
+"""Decode-throughput benchmark of the LLaMa token loop on the sm_100a backend.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" = one single-token decode step (one execute() of the graph, batch 1) of a synthetic
+LLaMa2-7B-architecture model with Q4_0 weights (seeded N(0, 0.02), norms = 1, F32 embeddings),
+context 512, after an 8-token seeded prompt. With N > 1 the model is sharded tensor-parallel over
+N GPUs (launched by torchrun, one rank per GPU, NCCL all-reduce after attention-output and FFN-down),
+so scaling is "strong". Rank 0 prints one JSON line.
+
+  value          tokens/s with everything resident in HBM: CUDA-graph replay, greedy argmax and next
+                 embedding on the device, timed with CUDA events on the launching stream.
+  e2e            the same loop through spyb_model_eval: token id from pinned host memory in, the
+                 32000 logits back to the host and the argmax there, every step.
+  roofline       the dominant kernel (FFN up+gate mat-vec, 45 % of the weight bytes) timed alone over
+                 all layers' weights (1.6 GB per sweep, far larger than L2) against the measured HBM peak.
+  cpu_baseline   the reference's own CPU backend (oracle/_ref, compiled from the reference sources)
+                 on the host cores, same GGUF and prompt, a few decode steps.
+
+--impl reference times only that CPU arm and prints the same line with "impl": "reference".
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SEED, PROMPT_SEED, N_PROMPT, N_CTX = 1234, 4321, 8, 512
+WORKLOAD = "llama2-7b-arch Q4_0 bs1 decode, ctx 512, prompt 8 (synthetic GGUF, seed 1234)"
+
+
+def model_path():
+    d = "/dev/shm" if os.path.isdir("/dev/shm") and os.access("/dev/shm", os.W_OK) else "/tmp"
+    return os.path.join(d, f"spyb_llama7b_q4_0_seed{SEED}.gguf")
+
+
+def ensure_model(path, device):
+    from spy_b200 import gguf_io
+    if os.path.exists(path) and os.path.getsize(path) > 4_000_000_000:
+        return
+    cfg = gguf_io.LlamaConfig(**gguf_io.LLAMA2_7B)
+    tmp = path + f".tmp{os.getpid()}"
+    gguf_io.make_llama_gguf_cuda(tmp, cfg, seed=SEED, device=device)
+    os.replace(tmp, path)
+
+
+def prompt_ids(n_vocab=32000):
+    return np.random.default_rng(PROMPT_SEED).integers(3, n_vocab, size=N_PROMPT).astype(np.int32)
+
+
+def physical_cores():
+    try:
+        allowed = os.sched_getaffinity(0)
+        cores, phys, core, cpu = set(), None, None, None
+        for line in open("/proc/cpuinfo"):
+            if line.startswith("processor"):
+                cpu = int(line.split(":")[1])
+            elif line.startswith("physical id"):
+                phys = int(line.split(":")[1])
+            elif line.startswith("core id"):
+                core = int(line.split(":")[1])
+            elif not line.strip():
+                if cpu in allowed and phys is not None and core is not None:
+                    cores.add((phys, core))
+                phys = core = cpu = None
+        n = len(cores) if cores else len(allowed)
+    except Exception:
+        n = os.cpu_count() or 1
+    return max(1, min(n, 64))
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled while the timed region runs (read-only queries)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=3)
+        except Exception:
+            self.proc.kill()
+        sm = [float(r[1]) for r in self.rows if len(r) >= 9 and r[1].replace(".", "").isdigit()]
+        mx = [float(r[2]) for r in self.rows if len(r) >= 9 and r[2].replace(".", "").isdigit()]
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 9:
+                for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                    if v.lower().startswith("active"):
+                        reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def cpu_reference_run(path, steps, warmup, threads):
+    """Reference CPU backend: prefill of the prompt, then warmup + steps single-token decode steps."""
+    from oracle import spy_ref
+    if not spy_ref.available():
+        return None
+    n = 1 + warmup + steps
+    ids, _, ms = spy_ref.generate(path, prompt_ids(), n, n_ctx=N_CTX, threads=threads, warmup=False, want_logits=False)
+    dec = ms[1 + warmup:]
+    return {"tokens_per_s": float(len(dec) / (dec.sum() / 1e3)), "ms_per_step": float(dec.mean()), "ids": ids, "prefill_ms": float(ms[0])}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    path = model_path()
+    if not os.path.exists(path):
+        import torch
+        if not torch.cuda.is_available():
+            print(json.dumps({"impl": "reference", "unavailable": "the synthetic 7B GGUF is generated on the GPU and no CUDA device is visible"}))
+            return
+        ensure_model(path, "cuda:0")
+    threads = physical_cores()
+    steps = max(1, min(args.steps, N_CTX - N_PROMPT - args.warmup - 1))
+    r = cpu_reference_run(path, steps, args.warmup, threads)
+    if r is None:
+        print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libspy_ref.so (the reference's CPU path) was not built"}))
+        return
+    line = {"impl": "reference", "metric": "decode tokens/s", "value": r["tokens_per_s"], "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": args.warmup, "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "int8 block dots, f32 accumulate", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "threads": threads},
+            "cpu_baseline": {"value": r["tokens_per_s"], "unit": "tokens/s", "cores": threads, "kind": "reference",
+                             "sample": f"{steps} decode steps after an 8-token prefill, -t {threads}"},
+            "e2e": {"value": r["tokens_per_s"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    from spy_b200 import backend as B
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs {args.gpus} ranks (launch with torch.distributed.run), got WORLD_SIZE={world}")
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group(backend="gloo", rank=rank, world_size=world)
+    torch.cuda.set_device(local)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    path = model_path()
+    if rank == 0:
+        ensure_model(path, f"cuda:{local}")
+    barrier()
+
+    be = B.B200Backend(local, tp_size=world, tp_rank=rank, use_pdl=not args.no_pdl, use_graph=not args.no_graph)
+    model = B.LlamaModel(be, path, n_ctx=N_CTX)
+    if world > 1:
+        uid = [B.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(uid, src=0)
+        model.init_tp(uid[0])
+    info = model.info
+    prompt = prompt_ids(info.n_vocab)
+
+    steps, warmup = args.steps, max(3, args.warmup)
+    room = N_CTX - N_PROMPT - 1
+    if warmup + steps > room:
+        steps = room - warmup
+
+    # ---- device-resident arm ---------------------------------------------------------------
+    first = model.eval(prompt, 0)
+    tok0 = int(np.argmax(first))
+    model.decode(tok0, N_PROMPT, warmup)                      # warm-up (captures the graph on first use)
+    barrier(); torch.cuda.synchronize(); be.sync()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ids_warm, _ = model.decode(tok0, N_PROMPT, warmup)        # re-run the warm-up region so the timed tokens follow it
+    barrier(); be.sync()
+    last_tok = int(ids_warm[-1])
+    ids, _ = model.decode(last_tok, N_PROMPT + warmup, steps)
+    ms_dev = model.last_ms
+    launches = model.last_launches
+    be.sync(); barrier()
+
+    # ---- end-to-end arm: host token in, host logits out, argmax on the host, every step -----
+    tok = last_tok
+    model.eval(np.array([tok], dtype=np.int32), N_PROMPT + warmup)   # warm
+    barrier(); be.sync()
+    ev_ms = 0.0
+    t0 = time.perf_counter()
+    e2e_ids = []
+    for s in range(steps):
+        logits = model.eval(np.array([tok], dtype=np.int32), N_PROMPT + warmup + s)
+        ev_ms += model.last_ms
+        tok = int(np.argmax(logits))
+        e2e_ids.append(tok)
+    be.sync(); barrier()
+    ms_e2e_wall = (time.perf_counter() - t0) * 1e3
+    clocks = sampler.stop() if rank == 0 else None
+
+    times = torch.tensor([ms_dev, ms_e2e_wall], dtype=torch.float64)
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms_dev, ms_e2e = float(times[0]), float(times[1])
+
+    # ---- dominant kernel alone, over every layer's weights ----------------------------------
+    roof = None
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        kb = bench_kernels(model, be)
+        dom = kb["ffn_up_gate"]
+        roof = {"bound": "hbm", "kernel": "matvec_kernel<Q4_0,1> (FFN up+gate, SiLU-mul epilogue)", "achieved": dom["gbs"], "peak": peak,
+                "peak_kind": f"of {peak_kind} ({'MEASURED_PEAKS.json copy bandwidth' if peak_kind == 'measured' else 'fallback 6650 GB/s'})",
+                "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": None,
+                "bytes_per_launch": dom["bytes"], "us_per_launch": dom["us"], "kernels": kb}
+
+    if rank == 0:
+        weight_b, kv_b = info.weight_bytes, info.kv_bytes_per_token
+        p_avg = N_PROMPT + warmup + (steps - 1) / 2.0
+        bytes_per_token = weight_b + kv_b * p_avg + kv_b           # weights once + KV read + KV written, on this GPU
+        tok_s = steps / (ms_dev / 1e3)
+        peak, peak_kind = measured_peak()
+        line = {"metric": "decode tokens/s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
+                "ms_per_step": ms_dev / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "int8 block dots, f32 accumulate", "data": "synthetic",
+                "config": {"workload": WORKLOAD, "parallelism": f"tp{world}", "l2": "weights 3.7 GB per step, far larger than the 126 MB L2",
+                           "pdl": not args.no_pdl, "cuda_graph": (not args.no_graph) and world == 1},
+                "hbm_gbs_per_gpu": bytes_per_token * tok_s / 1e9, "hbm_frac_of_peak": bytes_per_token * tok_s / 1e9 / peak,
+                "hbm_peak_gbs": peak, "bytes_per_token_per_gpu": bytes_per_token,
+                "e2e": {"value": steps / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": int(info.n_vocab) * 4,
+                        "device_ms_per_step": ev_ms / steps},
+                "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
+                "ids_match_e2e": bool(np.array_equal(ids, np.array(e2e_ids)))}
+        if not args.no_cpu_baseline and world == 1:
+            threads = physical_cores()
+            r = cpu_reference_run(path, 4, 1, threads)
+            if r is not None:
+                n_cmp = min(len(r["ids"]) - 1, warmup + steps)
+                gpu_ids = np.concatenate([[tok0], ids_warm, ids])[: n_cmp + 1]
+                line["cpu_baseline"] = {"value": r["tokens_per_s"], "unit": "tokens/s", "cores": threads, "kind": "reference",
+                                        "sample": f"4 decode steps after the 8-token prefill and 1 warm-up step, -t {threads}",
+                                        "greedy_ids_identical": bool(np.array_equal(r["ids"][: n_cmp + 1], gpu_ids))}
+            else:
+                line["cpu_baseline"] = None
+        print(json.dumps(line))
+    model.close()
+    be.close()
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def bench_kernels(model, be):
+    """Each mat-vec kind launched alone, back to back over all layers (weights come from HBM each time)."""
+    import ctypes as C
+    l = be._l
+    l.spyb_model_bench_kernel.restype = C.c_float
+    l.spyb_model_bench_kernel.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_uint64)]
+    out = {}
+    for kind, name in enumerate(["qkv", "attn_out", "ffn_up_gate", "ffn_down", "head"]):
+        nbytes = C.c_uint64()
+        l.spyb_model_bench_kernel(model.h, kind, 2, C.byref(nbytes))          # warm
+        us = l.spyb_model_bench_kernel(model.h, kind, 10, C.byref(nbytes)) * 1e3
+        if us > 0:
+            out[name] = {"us": us, "bytes": int(nbytes.value), "gbs": nbytes.value / us / 1e3}
+    return out
+
+
+if __name__ == "__main__":
+    main()

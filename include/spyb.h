@@ -1,0 +1,186 @@
+/*
+ * spyb.h - C ABI of the sm_100a backend library (libspyb200.so).
+ *
+ * Every entry point takes plain pointers and sizes; no C++ or framework types cross the
+ * boundary, so the library can be bound from the reference's C++ (a `spy::Backend`
+ * subclass), from C, or from Python ctypes alike.
+ *
+ * Each declaration cites the reference (BL-GS/Spy) interface it stands in for, as a path
+ * inside that project. There is no CPU fallback behind any of these calls: an operator or
+ * number type the GPU path does not implement returns SPYB_UNSUPPORTED.
+ */
+#ifndef SPYB_H_
+#define SPYB_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* OperatorStatus, backend/interface/include/backend/backend.h:22-29 */
+typedef enum { SPYB_SUCCESS = 0, SPYB_FAIL = 1, SPYB_UNSUPPORTED = 2 } spyb_status;
+
+/* NumberType, orchestration/include/number/number_impl/type.h:12-45 (GGML numbering) */
+enum {
+    SPYB_FP32 = 0, SPYB_FP16 = 1, SPYB_Q4_0 = 2, SPYB_Q8_0 = 8, SPYB_Q4_K = 12, SPYB_Q6_K = 14, SPYB_INT32 = 26
+};
+
+/* OperatorType, orchestration/include/operator/type.h:38-52 (order matters) */
+enum {
+    SPYB_OP_INPUT = 0, SPYB_OP_NOP = 1, SPYB_OP_DUP = 2, SPYB_OP_COPY = 3, SPYB_OP_VIEW = 4, SPYB_OP_RESHAPE = 5,
+    SPYB_OP_GETROW = 8, SPYB_OP_TRANSPOSE = 9, SPYB_OP_PERMUTE = 10, SPYB_OP_CONTIGUOUS = 11, SPYB_OP_SILU = 13,
+    SPYB_OP_SOFTMAX = 17, SPYB_OP_ADD = 18, SPYB_OP_MUL = 20, SPYB_OP_MATMUL = 23, SPYB_OP_NORM_RMS = 26,
+    SPYB_OP_ROPE = 27
+};
+
+/* DataNodeType, orchestration/include/graph/data_node.h:12-36 */
+enum { SPYB_NODE_CONSTANT = 0, SPYB_NODE_IO = 1, SPYB_NODE_CACHE = 2, SPYB_NODE_DYNAMIC = 6 };
+
+typedef struct spyb_backend spyb_backend;
+typedef struct spyb_model   spyb_model;
+
+/* Backend configuration; the string keys of the reference's ConfigTable
+ * (util/include/util/wrapper/config_table.h:10-72; GPU key `device_id` at
+ * backend/cuda/include/default_backend.h:38-40) become plain fields. */
+typedef struct {
+    int32_t device_id;     /* CUDA device ordinal */
+    int32_t tp_size;       /* tensor-parallel world size, 1 = single GPU */
+    int32_t tp_rank;       /* this process's rank in [0, tp_size) */
+    int32_t use_pdl;       /* 1 = programmatic dependent launch between the kernels of a step */
+    int32_t use_graph;     /* 1 = replay decode steps from a captured CUDA graph */
+    int32_t reserved;
+    uint64_t arena_bytes;  /* size of the device arena behind spyb_alloc, 0 = default (256 MiB) */
+} spyb_config;
+
+/* Tensor as an operator sees it: Shape + data pointer
+ * (orchestration/include/number/tensor.h:23-263). `bytes` are byte strides; bytes[0] is the
+ * size of one block of `number_type`. `node_type` tells host (IO) from device pointers. */
+typedef struct {
+    int32_t number_type;
+    uint32_t dim;
+    int64_t elements[4];
+    int64_t bytes[4];
+    void   *data;
+    int32_t node_type;
+    int32_t reserved;
+} spyb_tensor;
+
+/* RopeParam, orchestration/include/operator/non-linear.h:191-207 */
+typedef struct {
+    int32_t mode, num_past, num_dim, num_context, num_origin_context;
+    float   freq_base, freq_scale, extend_factor, attention_factor, beta_fast, beta_slow, xpos_base;
+    int32_t xpos_down;
+} spyb_rope_param;
+
+/* One operator node as Backend::submit receives it
+ * (backend/interface/include/backend/backend.h:94; operand contract in
+ * orchestration/include/graph/op_node.h:11-60). */
+typedef struct {
+    int32_t op_type;
+    int32_t num_input;
+    spyb_tensor input[3];
+    spyb_tensor output;
+    float   softmax_scale;     /* SoftmaxParam,  operator/non-linear.h:45 */
+    float   norm_eps;          /* NormRMSParam,  operator/non-linear.h:117 */
+    int64_t view_offset;       /* ViewParam,     operator/view.h:333-336 */
+    spyb_rope_param rope;
+} spyb_op_desc;
+
+/* ---- backend object: BackendFactory::init_backend + Backend ctor/dtor (backend.h:31-40, 109-117) */
+spyb_status spyb_create(const spyb_config *config, spyb_backend **out);
+void        spyb_destroy(spyb_backend *backend);
+/* message of the last failure on this backend ("" if none); replaces the reference's
+ * spy_assert/std::terminate error path (util/include/util/log/logger.h:96-150) */
+const char *spyb_last_error(const spyb_backend *backend);
+
+/* ---- Backend::get_max/avail_memory_capacity (backend.h:46-51) */
+uint64_t spyb_max_memory(const spyb_backend *backend);
+uint64_t spyb_avail_memory(const spyb_backend *backend);
+
+/* ---- Backend::alloc_memory / dealloc_memory (backend.h:59-67): device memory, thread-safe */
+void *spyb_alloc(spyb_backend *backend, uint64_t bytes);
+void  spyb_free(spyb_backend *backend, void *ptr, uint64_t bytes);
+
+/* ---- Backend::is_support (backend.h:87) */
+int32_t spyb_is_support(int32_t op_type);
+
+/* ---- ModelLoader::load for a Constant tensor (storage/include/loader/simple_loader.h:57-70):
+ * copies the tensor's raw blocks to the device once and returns the device pointer that
+ * stands in for the loader's host span. Repeated calls with the same name return the same pointer. */
+void *spyb_upload_constant(spyb_backend *backend, const char *name, const void *host_ptr, uint64_t bytes,
+                           int32_t number_type, const int64_t elements[4]);
+
+/* ---- Backend::submit (backend.h:94): enqueues one operator on the backend's stream.
+ * View-type operators (operator/type.h:115-126) write the aliased pointer to desc->output.data.
+ * `callback(user)` runs on a backend thread once the operator has finished on the device; NULL = none. */
+spyb_status spyb_submit(spyb_backend *backend, spyb_op_desc *desc, void (*callback)(void *), void *user);
+/* waits for everything submitted so far */
+spyb_status spyb_sync(spyb_backend *backend);
+
+/* ---- staging of IO tensors, which the reference keeps in host vectors (model/src/llm/model/llama.cpp:259-263) */
+spyb_status spyb_memcpy_h2d(spyb_backend *backend, void *dst_device, const void *src_host, uint64_t bytes);
+spyb_status spyb_memcpy_d2h(spyb_backend *backend, void *dst_host, const void *src_device, uint64_t bytes);
+
+/* ---- single kernels exposed for parity checks of the arithmetic the reference pins exactly */
+/* Quantizator<FP32,Q8_0>::transform (backend/host/include/simd/vec_convert.h:178-261):
+ * n floats on the device -> n/32 blocks of 34 bytes in the reference layout */
+spyb_status spyb_quantize_q8_0(spyb_backend *backend, const float *x_device, int64_t n, void *blocks_device);
+/* per-block int32 dots of one Q4_0 / Q8_0 weight row against one Q8_0 activation column
+ * (Dot<Q4_0,Q8_0>::exec / Dot<Q8_0,Q8_0>::exec, backend/host/include/simd/vec_dot.h:42-115), all pointers
+ * to raw reference-layout blocks on the device, out: n/32 int32 */
+spyb_status spyb_block_dots(spyb_backend *backend, int32_t weight_type, const void *w_row_device,
+                            const void *x_blocks_device, int64_t n, int32_t *out_device);
+
+/* ---- whole-model path: the graph LLAMAModel::build_graph emits (model/src/llm/model/llama.cpp:86-264)
+ * executed as a fixed plan of fused kernels. */
+typedef struct {
+    int32_t n_layer, d_model, n_head, n_ff, n_vocab, n_ctx, head_dim;
+    int32_t tp_size, tp_rank;
+    float   rms_eps, rope_base;
+    uint64_t weight_bytes;        /* quantized weight bytes resident on this GPU */
+    uint64_t kv_bytes_per_token;  /* KV-cache bytes appended per token on this GPU */
+} spyb_model_info;
+
+/* GGUFAdapter::init_from_file + SimpleModeLoader::preload (storage/src/adapter/gguf_adapter.cpp:90-190,
+ * storage/include/loader/simple_loader.h:36-55) followed by the upload of every tensor's quantized
+ * blocks to device memory; with tp_size > 1 only this rank's shard (heads / FFN columns) is kept. */
+spyb_status spyb_model_load_gguf(spyb_backend *backend, const char *path, int32_t n_ctx, spyb_model **out);
+void        spyb_model_free(spyb_model *model);
+spyb_status spyb_model_info_get(const spyb_model *model, spyb_model_info *info);
+/* attach an NCCL communicator for tensor parallelism: `unique_id` is the 128-byte ncclUniqueId
+ * every rank received from rank 0 (spyb_nccl_unique_id) */
+spyb_status spyb_nccl_unique_id(void *unique_id_128);
+spyb_status spyb_model_init_tp(spyb_model *model, const void *unique_id_128);
+
+/* One distributor->execute() (backend/distributor/include/distributor/simple_distributor.h:47-78)
+ * for `n_tokens` host token ids at positions n_past..n_past+n_tokens-1: host ids in, the last
+ * token's n_vocab logits out to host memory (as model_io.logits, app/cli/include/cli.h:103-105). */
+spyb_status spyb_model_eval(spyb_model *model, const int32_t *tokens_host, int32_t n_tokens, int32_t n_past,
+                            float *logits_host);
+/* The decode loop of AutoModelGenerator::generate (app/cli/include/cli.h:88-128) kept on the device:
+ * `n_steps` single-token steps starting from `first_token` at position n_past, greedy argmax
+ * (SamplerImpl<Greedy>, model/include/llm/sampler/greedy.h:20-25) on the device feeding the next step;
+ * only the token ids come back. logits_host (optional) receives n_steps * n_vocab floats. */
+spyb_status spyb_model_decode(spyb_model *model, int32_t first_token, int32_t n_past, int32_t n_steps,
+                              int32_t *ids_host, float *logits_host);
+/* device time in milliseconds of the most recent spyb_model_decode / spyb_model_eval call,
+ * measured with CUDA events on the backend's stream; number of kernels that call launched */
+float   spyb_model_last_ms(const spyb_model *model);
+int64_t spyb_model_last_launches(const spyb_model *model);
+/* Measurement aid: launches one kind of mat-vec kernel of the plan alone, `sweeps` times over every layer's
+ * weights back to back (kind 0 = Wq|Wk|Wv, 1 = attention output, 2 = FFN up+gate, 3 = FFN down, 4 = output head),
+ * and returns the average device time per launch in milliseconds (CUDA events on the backend's stream);
+ * *bytes_per_launch receives the quantized weight bytes one launch streams. Scratch activations only:
+ * the KV cache below position n_ctx-1 and the residual stream are left untouched. No reference counterpart
+ * (the reference times whole steps only, util/include/util/timer.h:51-80). */
+float spyb_model_bench_kernel(spyb_model *model, int32_t kind, int32_t sweeps, uint64_t *bytes_per_launch);
+/* taps for parity tests: copy the Q8_0 blocks of layer-0's attention-norm output of the last eval
+ * (d_model/32 * 34 bytes, reference layout) to host */
+spyb_status spyb_model_tap_xq(spyb_model *model, void *blocks_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPYB_H_ */

@@ -1,0 +1,479 @@
+// The backend object and the per-operator path of the C ABI: memory, constants, submit.
+// This is the part that stands in for the reference's DefaultGPUBackend
+// (backend/cuda/include/default_backend.h:22-99) behind Backend::{alloc_memory, dealloc_memory, submit}.
+
+#include <cmath>
+#include <cstring>
+
+#include "spyb_common.cuh"
+#include "spyb_internal.h"
+
+namespace spyb {
+
+// ------------------------------------------------------------------------------------------ arena
+bool Arena::init(size_t bytes) {
+    capacity_ = (bytes + ALIGN - 1) / ALIGN * ALIGN;
+    if (cudaMalloc(reinterpret_cast<void **>(&base_), capacity_) != cudaSuccess) { base_ = nullptr; capacity_ = 0; return false; }
+    free_.clear();
+    free_[0] = capacity_;
+    return true;
+}
+
+void Arena::destroy() {
+    for (auto &kv : overflow_) { cudaFree(kv.first); }
+    overflow_.clear();
+    if (base_) { cudaFree(base_); base_ = nullptr; }
+    capacity_ = 0;
+    free_.clear();
+}
+
+void *Arena::alloc(size_t bytes) {
+    if (bytes == 0) { bytes = 1; }
+    const size_t need = (bytes + ALIGN - 1) / ALIGN * ALIGN;
+    std::lock_guard<std::mutex> g(mutex_);
+    for (auto it = free_.begin(); it != free_.end(); ++it) {
+        if (it->second >= need) {
+            const size_t off = it->first, rest = it->second - need;
+            free_.erase(it);
+            if (rest) { free_[off + need] = rest; }
+            return base_ + off;
+        }
+    }
+    void *p = nullptr;   // arena exhausted: fall back to the CUDA allocator rather than fail
+    if (cudaMalloc(&p, need) != cudaSuccess) { return nullptr; }
+    overflow_[p] = need;
+    return p;
+}
+
+void Arena::free(void *ptr, size_t bytes) {
+    if (ptr == nullptr) { return; }
+    std::lock_guard<std::mutex> g(mutex_);
+    auto ov = overflow_.find(ptr);
+    if (ov != overflow_.end()) { cudaFree(ptr); overflow_.erase(ov); return; }
+    if (bytes == 0) { bytes = 1; }
+    size_t off = static_cast<uint8_t *>(ptr) - base_, size = (bytes + ALIGN - 1) / ALIGN * ALIGN;
+    auto next = free_.lower_bound(off);
+    if (next != free_.begin()) {
+        auto prev = std::prev(next);
+        if (prev->first + prev->second == off) { off = prev->first; size += prev->second; free_.erase(prev); }
+    }
+    if (next != free_.end() && off + size == next->first) { size += next->second; free_.erase(next); }
+    free_[off] = size;
+}
+
+size_t Arena::available() {
+    std::lock_guard<std::mutex> g(mutex_);
+    size_t tot = 0;
+    for (auto &kv : free_) { tot += kv.second; }
+    return tot;
+}
+
+// ------------------------------------------------------------------------------------------ matrices
+spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, DevMatrix *out) {
+    if (type != SPYB_Q4_0 && type != SPYB_Q8_0) { be->set_error("weight type %d has no device layout", type); return SPYB_UNSUPPORTED; }
+    DevMatrix m;
+    m.type = type; m.n_rows = n_rows; m.nb = nb; m.k = (int64_t)nb * QK;
+    const size_t nblk = (size_t)n_rows * nb;
+    void *qa = nullptr, *qb = nullptr, *d = nullptr;
+    SPYB_CUDA(be, cudaMalloc(&qa, nblk * 16 + 16));
+    be->owned.push_back(qa);
+    if (type == SPYB_Q8_0) { SPYB_CUDA(be, cudaMalloc(&qb, nblk * 16 + 16)); be->owned.push_back(qb); }
+    SPYB_CUDA(be, cudaMalloc(&d, nblk * 2 + 16));
+    be->owned.push_back(d);
+    m.qa = static_cast<const uint4 *>(qa); m.qb = static_cast<const uint4 *>(qb); m.d = static_cast<const uint16_t *>(d);
+    *out = m;
+    return SPYB_SUCCESS;
+}
+
+spyb_status upload_matrix(spyb_backend *be, int type, const uint8_t *host_rows, int64_t n_rows, int64_t row_stride_bytes,
+                          int64_t blk0, int nb, DevMatrix *out, uint4 *qa_dst, uint4 *qb_dst, uint16_t *d_dst) {
+    if (qa_dst == nullptr) {
+        spyb_status st = alloc_matrix(be, type, n_rows, nb, out);
+        if (st != SPYB_SUCCESS) { return st; }
+        qa_dst = const_cast<uint4 *>(out->qa); qb_dst = const_cast<uint4 *>(out->qb); d_dst = const_cast<uint16_t *>(out->d);
+    }
+    const int     bb = (type == SPYB_Q4_0) ? 18 : 34;
+    const int64_t max_rows = std::max<int64_t>(1, (int64_t)(64u << 20) / row_stride_bytes);   // 64 MiB staging pieces
+    void *stage = nullptr;
+    SPYB_CUDA(be, cudaMalloc(&stage, (size_t)std::min(max_rows, n_rows) * row_stride_bytes + 64));
+    for (int64_t r0 = 0; r0 < n_rows; r0 += max_rows) {
+        const int64_t nr = std::min(max_rows, n_rows - r0);
+        cudaError_t err = cudaMemcpyAsync(stage, host_rows + r0 * row_stride_bytes, (size_t)nr * row_stride_bytes, cudaMemcpyHostToDevice, be->stream);
+        if (err == cudaSuccess) {
+            const uint8_t *raw = static_cast<const uint8_t *>(stage) + blk0 * bb;
+            err = (type == SPYB_Q4_0) ? launch_retile_q4_0(raw, row_stride_bytes, nr, nb, qa_dst + r0 * nb, d_dst + r0 * nb, be->stream)
+                                      : launch_retile_q8_0(raw, row_stride_bytes, nr, nb, qa_dst + r0 * nb, qb_dst + r0 * nb, d_dst + r0 * nb, be->stream);
+        }
+        if (err == cudaSuccess) { err = cudaStreamSynchronize(be->stream); }
+        if (err != cudaSuccess) { cudaFree(stage); be->set_error("weight upload failed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
+    }
+    cudaFree(stage);
+    return SPYB_SUCCESS;
+}
+
+static void callback_worker(spyb_backend *be) {
+    cudaSetDevice(be->config.device_id);
+    for (;;) {
+        PendingCallback cb;
+        {
+            std::unique_lock<std::mutex> g(be->cb_mutex);
+            be->cb_cv.wait(g, [be] { return be->cb_stop || !be->cb_queue.empty(); });
+            if (be->cb_queue.empty()) { return; }
+            cb = be->cb_queue.front();
+            be->cb_queue.pop_front();
+        }
+        cudaEventSynchronize(cb.event);
+        cudaEventDestroy(cb.event);
+        cb.fn(cb.user);
+    }
+}
+
+static int64_t type_block_bytes(int t) {
+    switch (t) { case SPYB_FP32: return 4; case SPYB_FP16: return 2; case SPYB_INT32: return 4; case SPYB_Q4_0: return 18; case SPYB_Q8_0: return 34;
+                 case SPYB_Q4_K: return 144; case SPYB_Q6_K: return 210; default: return -1; }
+}
+static int64_t type_block_elems(int t) {
+    switch (t) { case SPYB_Q4_0: case SPYB_Q8_0: return 32; case SPYB_Q4_K: case SPYB_Q6_K: return 256; default: return 1; }
+}
+static int64_t tensor_elems(const spyb_tensor &t) { return t.elements[0] * t.elements[1] * t.elements[2] * t.elements[3]; }
+// Shape::total_size, orchestration/include/number/tensor.h:137-143
+static int64_t tensor_total_size(const spyb_tensor &t) {
+    int64_t size = t.bytes[0] * t.elements[0] / type_block_elems(t.number_type);
+    for (uint32_t i = 1; i < t.dim && i < 4; ++i) { size += t.bytes[i] * (t.elements[i] - 1); }
+    return size;
+}
+static bool tensor_contiguous(const spyb_tensor &t) {
+    const int64_t bs = type_block_bytes(t.number_type), be = type_block_elems(t.number_type);
+    return t.bytes[0] == bs && t.bytes[1] == bs * t.elements[0] / be && t.bytes[2] == t.bytes[1] * t.elements[1] &&
+           t.bytes[3] == t.bytes[2] * t.elements[2];
+}
+static Strided to_strided(const spyb_tensor &t, void *data) {
+    Strided s; s.data = data;
+    for (int i = 0; i < 4; ++i) { s.ne[i] = t.elements[i]; s.nb[i] = t.bytes[i]; }
+    return s;
+}
+
+}  // namespace spyb
+
+using namespace spyb;
+
+extern "C" {
+
+spyb_status spyb_create(const spyb_config *config, spyb_backend **out) {
+    if (config == nullptr || out == nullptr) { return SPYB_FAIL; }
+    *out = nullptr;
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0) { return SPYB_FAIL; }   // no CPU fallback exists
+    if (config->device_id < 0 || config->device_id >= n_dev) { return SPYB_FAIL; }
+    if (cudaSetDevice(config->device_id) != cudaSuccess) { return SPYB_FAIL; }
+    spyb_backend *be = new spyb_backend();
+    be->config = *config;
+    if (be->config.tp_size < 1) { be->config.tp_size = 1; }
+    cudaDeviceProp prop;
+    if (cudaGetDeviceProperties(&prop, config->device_id) != cudaSuccess) { delete be; return SPYB_FAIL; }
+    be->num_sms = prop.multiProcessorCount;
+    if (cudaStreamCreateWithFlags(&be->stream, cudaStreamNonBlocking) != cudaSuccess) { delete be; return SPYB_FAIL; }
+    const size_t arena = config->arena_bytes ? config->arena_bytes : (size_t)256 << 20;
+    if (!be->arena.init(arena)) { cudaStreamDestroy(be->stream); delete be; return SPYB_FAIL; }
+
+    // fp16-argument tables, built with the host libm exactly as the reference builds them
+    // (orchestration/include/number/lookup_table_impl/non-linear.h:42-47, 134-139); key 0xFFFF stays 0.
+    std::vector<float> silu(65536, 0.f), ex(65536, 0.f);
+    for (uint32_t k = 0; k < 65535; ++k) {
+        _Float16 hv; const uint16_t kk = (uint16_t)k; std::memcpy(&hv, &kk, 2);
+        const float x = (float)hv;
+        silu[k] = x / (1.0f + std::exp(-x));
+        ex[k]   = std::exp(x);
+    }
+    bool ok = cudaMalloc(reinterpret_cast<void **>(&be->d_silu_table), 65536 * 4) == cudaSuccess &&
+              cudaMalloc(reinterpret_cast<void **>(&be->d_exp_table), 65536 * 4) == cudaSuccess &&
+              cudaMemcpy(be->d_silu_table, silu.data(), 65536 * 4, cudaMemcpyHostToDevice) == cudaSuccess &&
+              cudaMemcpy(be->d_exp_table, ex.data(), 65536 * 4, cudaMemcpyHostToDevice) == cudaSuccess;
+    if (!ok) { spyb_destroy(be); return SPYB_FAIL; }
+    be->cb_thread = std::thread(callback_worker, be);
+    *out = be;
+    return SPYB_SUCCESS;
+}
+
+void spyb_destroy(spyb_backend *be) {
+    if (be == nullptr) { return; }
+    cudaSetDevice(be->config.device_id);
+    if (be->stream) { cudaStreamSynchronize(be->stream); }
+    if (be->cb_thread.joinable()) {
+        { std::lock_guard<std::mutex> g(be->cb_mutex); be->cb_stop = true; }
+        be->cb_cv.notify_all();
+        be->cb_thread.join();
+    }
+    for (void *p : be->owned) { cudaFree(p); }
+    if (be->d_silu_table) { cudaFree(be->d_silu_table); }
+    if (be->d_exp_table) { cudaFree(be->d_exp_table); }
+    be->arena.destroy();
+    if (be->stream) { cudaStreamDestroy(be->stream); }
+    delete be;
+}
+
+const char *spyb_last_error(const spyb_backend *be) {
+    if (be == nullptr) { return "no backend (no CUDA device, or creation failed)"; }
+    return be->last_error.c_str();
+}
+
+uint64_t spyb_max_memory(const spyb_backend *be) {
+    size_t free_b = 0, total = 0;
+    cudaSetDevice(be->config.device_id);
+    cudaMemGetInfo(&free_b, &total);
+    return total;
+}
+uint64_t spyb_avail_memory(const spyb_backend *be) {
+    size_t free_b = 0, total = 0;
+    cudaSetDevice(be->config.device_id);
+    cudaMemGetInfo(&free_b, &total);
+    return free_b + const_cast<spyb_backend *>(be)->arena.available();
+}
+
+void *spyb_alloc(spyb_backend *be, uint64_t bytes) {
+    cudaSetDevice(be->config.device_id);
+    void *p = be->arena.alloc(bytes);
+    if (p == nullptr) { be->set_error("out of device memory allocating %llu bytes", (unsigned long long)bytes); }
+    return p;
+}
+void spyb_free(spyb_backend *be, void *ptr, uint64_t bytes) { be->arena.free(ptr, bytes); }
+
+int32_t spyb_is_support(int32_t op) {
+    switch (op) {
+    case SPYB_OP_INPUT: case SPYB_OP_NOP: case SPYB_OP_DUP: case SPYB_OP_COPY: case SPYB_OP_VIEW: case SPYB_OP_RESHAPE:
+    case SPYB_OP_GETROW: case SPYB_OP_TRANSPOSE: case SPYB_OP_PERMUTE: case SPYB_OP_CONTIGUOUS: case SPYB_OP_SILU:
+    case SPYB_OP_SOFTMAX: case SPYB_OP_ADD: case SPYB_OP_MUL: case SPYB_OP_MATMUL: case SPYB_OP_NORM_RMS: case SPYB_OP_ROPE:
+        return 1;
+    default:
+        return 0;
+    }
+}
+
+void *spyb_upload_constant(spyb_backend *be, const char *name, const void *host_ptr, uint64_t bytes, int32_t number_type,
+                           const int64_t elements[4]) {
+    cudaSetDevice(be->config.device_id);
+    std::lock_guard<std::mutex> g(be->const_mutex);
+    auto it = be->constants.find(name);
+    if (it != be->constants.end()) { return it->second; }
+    void *raw = nullptr;
+    if (cudaMalloc(&raw, bytes + 64) != cudaSuccess) { be->set_error("cudaMalloc(%llu) failed for constant %s", (unsigned long long)bytes, name); return nullptr; }
+    be->owned.push_back(raw);
+    if (cudaMemcpy(raw, host_ptr, bytes, cudaMemcpyHostToDevice) != cudaSuccess) { be->set_error("upload of %s failed", name); return nullptr; }
+    if ((number_type == SPYB_Q4_0 || number_type == SPYB_Q8_0) && elements != nullptr) {
+        // matrices also get the plane layout the mat-vec kernels stream; the raw copy stays for GetRow and parity checks
+        const int64_t k = elements[0], rows = elements[1] * elements[2] * elements[3];
+        const int64_t bb = number_type == SPYB_Q4_0 ? 18 : 34;
+        if (k % QK == 0 && rows > 0) {
+            DevMatrix m;
+            if (alloc_matrix(be, number_type, rows, (int)(k / QK), &m) != SPYB_SUCCESS) { return nullptr; }
+            cudaError_t err = number_type == SPYB_Q4_0
+                ? launch_retile_q4_0(static_cast<const uint8_t *>(raw), k / QK * bb, rows, m.nb, const_cast<uint4 *>(m.qa), const_cast<uint16_t *>(m.d), be->stream)
+                : launch_retile_q8_0(static_cast<const uint8_t *>(raw), k / QK * bb, rows, m.nb, const_cast<uint4 *>(m.qa), const_cast<uint4 *>(m.qb), const_cast<uint16_t *>(m.d), be->stream);
+            if (err != cudaSuccess || cudaStreamSynchronize(be->stream) != cudaSuccess) { be->set_error("re-tiling of %s failed", name); return nullptr; }
+            be->retiled[raw] = m;
+        }
+    }
+    be->constants[name] = raw;
+    return raw;
+}
+
+spyb_status spyb_sync(spyb_backend *be) {
+    SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+    return SPYB_SUCCESS;
+}
+
+spyb_status spyb_memcpy_h2d(spyb_backend *be, void *dst, const void *src, uint64_t bytes) {
+    SPYB_CUDA(be, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, be->stream));
+    SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+    return SPYB_SUCCESS;
+}
+spyb_status spyb_memcpy_d2h(spyb_backend *be, void *dst, const void *src, uint64_t bytes) {
+    SPYB_CUDA(be, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, be->stream));
+    SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+    return SPYB_SUCCESS;
+}
+
+spyb_status spyb_quantize_q8_0(spyb_backend *be, const float *x, int64_t n, void *blocks) {
+    if (n % QK != 0) { be->set_error("quantize_q8_0: %lld elements is not a multiple of 32", (long long)n); return SPYB_FAIL; }
+    SPYB_CUDA(be, launch_quantize_q8_0_ref_layout(x, n, static_cast<uint8_t *>(blocks), be->stream));
+    return SPYB_SUCCESS;
+}
+
+spyb_status spyb_block_dots(spyb_backend *be, int32_t wtype, const void *w, const void *xb, int64_t n, int32_t *out) {
+    if (wtype != SPYB_Q4_0 && wtype != SPYB_Q8_0) { be->set_error("block_dots: unsupported weight type %d", wtype); return SPYB_UNSUPPORTED; }
+    SPYB_CUDA(be, launch_block_dots(wtype, static_cast<const uint8_t *>(w), static_cast<const uint8_t *>(xb), n, out, be->stream));
+    return SPYB_SUCCESS;
+}
+
+// ------------------------------------------------------------------------------------------ submit
+namespace {
+
+struct Staged {   // a host (IO) tensor mirrored in device memory for the duration of one operator
+    void   *dev = nullptr;
+    size_t  bytes = 0;
+    bool    temp = false;
+};
+
+spyb_status stage_in(spyb_backend *be, const spyb_tensor &t, Staged *s) {
+    if (t.node_type != SPYB_NODE_IO) { s->dev = t.data; return SPYB_SUCCESS; }
+    s->bytes = (size_t)tensor_total_size(t);
+    s->dev = be->arena.alloc(s->bytes);
+    s->temp = true;
+    if (s->dev == nullptr) { be->set_error("out of device memory staging an IO tensor"); return SPYB_FAIL; }
+    SPYB_CUDA(be, cudaMemcpyAsync(s->dev, t.data, s->bytes, cudaMemcpyHostToDevice, be->stream));
+    return SPYB_SUCCESS;
+}
+
+spyb_status stage_out_begin(spyb_backend *be, const spyb_tensor &t, Staged *s) {
+    if (t.node_type != SPYB_NODE_IO) { s->dev = t.data; return SPYB_SUCCESS; }
+    s->bytes = (size_t)tensor_total_size(t);
+    s->dev = be->arena.alloc(s->bytes);
+    s->temp = true;
+    if (s->dev == nullptr) { be->set_error("out of device memory staging an IO tensor"); return SPYB_FAIL; }
+    return SPYB_SUCCESS;
+}
+
+void stage_release(spyb_backend *be, Staged *s) {
+    if (s->temp && s->dev) { be->arena.free(s->dev, s->bytes); }
+    s->dev = nullptr; s->temp = false;
+}
+
+spyb_status run_matmul(spyb_backend *be, spyb_op_desc *d, void *out_dev) {
+    const spyb_tensor &w = d->input[0], &x = d->input[1];
+    if (x.number_type != SPYB_FP32) { be->set_error("MatMul: activations of type %d", x.number_type); return SPYB_UNSUPPORTED; }
+    if (w.number_type == SPYB_FP16) {
+        SPYB_CUDA(be, launch_matmul_f16(to_strided(w, w.data), to_strided(x, x.data), to_strided(d->output, out_dev), be->stream));
+        return SPYB_SUCCESS;
+    }
+    if (w.number_type != SPYB_Q4_0 && w.number_type != SPYB_Q8_0) {
+        be->set_error("MatMul: weight type %d is not implemented", w.number_type);
+        return SPYB_UNSUPPORTED;
+    }
+    if (!tensor_contiguous(w) || !tensor_contiguous(x) || w.elements[2] != 1 || w.elements[3] != 1) {
+        be->set_error("MatMul: quantized weights need contiguous 2-D operands");
+        return SPYB_UNSUPPORTED;
+    }
+    DevMatrix m;
+    {
+        std::lock_guard<std::mutex> g(be->const_mutex);
+        auto it = be->retiled.find(w.data);
+        if (it == be->retiled.end()) {
+            // a quantized weight that did not come through spyb_upload_constant: re-tile it once and remember it
+            const int64_t bb = w.number_type == SPYB_Q4_0 ? 18 : 34;
+            if (alloc_matrix(be, w.number_type, w.elements[1], (int)(w.elements[0] / QK), &m) != SPYB_SUCCESS) { return SPYB_FAIL; }
+            cudaError_t err = w.number_type == SPYB_Q4_0
+                ? launch_retile_q4_0(static_cast<const uint8_t *>(w.data), w.elements[0] / QK * bb, w.elements[1], m.nb, const_cast<uint4 *>(m.qa), const_cast<uint16_t *>(m.d), be->stream)
+                : launch_retile_q8_0(static_cast<const uint8_t *>(w.data), w.elements[0] / QK * bb, w.elements[1], m.nb, const_cast<uint4 *>(m.qa), const_cast<uint4 *>(m.qb), const_cast<uint16_t *>(m.d), be->stream);
+            if (err != cudaSuccess) { be->set_error("MatMul: re-tiling failed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
+            be->retiled[w.data] = m;
+        } else {
+            m = it->second;
+        }
+    }
+    if (m.k != x.elements[0] || (m.n_rows & 1)) { be->set_error("MatMul: shape mismatch or odd row count"); return SPYB_FAIL; }
+    const int64_t T = x.elements[1] * x.elements[2] * x.elements[3];
+    for (int64_t t0 = 0; t0 < T; t0 += 8) {
+        MatvecParams p;
+        p.A = m; p.T = (int)std::min<int64_t>(8, T - t0);
+        p.pro = PRO_QUANT; p.x = static_cast<const float *>(x.data) + t0 * m.k; p.x_stride = m.k;
+        p.epi = EPI_STORE; p.out = static_cast<float *>(out_dev) + t0 * m.n_rows; p.out_stride = m.n_rows;
+        SPYB_CUDA(be, launch_matvec(p, be->launch_cfg(false)));
+    }
+    return SPYB_SUCCESS;
+}
+
+}  // namespace
+
+spyb_status spyb_submit(spyb_backend *be, spyb_op_desc *d, void (*callback)(void *), void *user) {
+    if (be == nullptr || d == nullptr) { return SPYB_FAIL; }
+    cudaSetDevice(be->config.device_id);
+    spyb_status st = SPYB_SUCCESS;
+    Staged in[3], out;
+    bool   has_out_copy = false;
+
+    switch (d->op_type) {
+    // view-type operators alias their input (backend/host/operator/view.cpp:229-276)
+    case SPYB_OP_INPUT: case SPYB_OP_NOP: break;
+    case SPYB_OP_RESHAPE: case SPYB_OP_TRANSPOSE: case SPYB_OP_PERMUTE: d->output.data = d->input[0].data; break;
+    case SPYB_OP_VIEW: d->output.data = static_cast<uint8_t *>(d->input[0].data) + d->view_offset; break;
+    default: {
+        for (int i = 0; i < d->num_input && i < 3 && st == SPYB_SUCCESS; ++i) { st = stage_in(be, d->input[i], &in[i]); }
+        if (st == SPYB_SUCCESS && d->op_type != SPYB_OP_COPY) { st = stage_out_begin(be, d->output, &out); has_out_copy = out.temp; }
+        if (st != SPYB_SUCCESS) { break; }
+        spyb_op_desc local = *d;
+        for (int i = 0; i < d->num_input && i < 3; ++i) { local.input[i].data = in[i].dev; }
+        const spyb_tensor &a = local.input[0];
+        cudaError_t err = cudaSuccess;
+        switch (d->op_type) {
+        case SPYB_OP_MATMUL: st = run_matmul(be, &local, out.dev); break;
+        case SPYB_OP_ADD: case SPYB_OP_MUL: {
+            const spyb_tensor &b = local.input[1];
+            if (!tensor_contiguous(a) || !tensor_contiguous(b) || a.number_type != SPYB_FP32 || b.number_type != SPYB_FP32 || a.elements[0] != b.elements[0]) {
+                be->set_error("Add/Mul: operands must be contiguous f32 rows of equal length"); st = SPYB_UNSUPPORTED; break;
+            }
+            const int64_t rows = tensor_elems(a) / a.elements[0], brows = tensor_elems(b) / b.elements[0];
+            err = launch_binary_rows(d->op_type == SPYB_OP_ADD ? 0 : 1, static_cast<const float *>(a.data), static_cast<const float *>(b.data),
+                                     static_cast<float *>(out.dev), a.elements[0], rows, brows, be->stream);
+        } break;
+        case SPYB_OP_NORM_RMS:
+            if (!tensor_contiguous(a) || a.number_type != SPYB_FP32) { be->set_error("NormRMS: contiguous f32 expected"); st = SPYB_UNSUPPORTED; break; }
+            err = launch_rmsnorm(static_cast<const float *>(a.data), static_cast<float *>(out.dev), a.elements[0], tensor_elems(a) / a.elements[0], d->norm_eps, be->stream);
+            break;
+        case SPYB_OP_SILU:
+            if (!tensor_contiguous(a) || a.number_type != SPYB_FP32) { be->set_error("Silu: contiguous f32 expected"); st = SPYB_UNSUPPORTED; break; }
+            err = launch_silu(static_cast<const float *>(a.data), static_cast<float *>(out.dev), tensor_elems(a), be->d_silu_table, be->stream);
+            break;
+        case SPYB_OP_SOFTMAX: {
+            if (d->num_input != 2 || !tensor_contiguous(a)) { be->set_error("Softmax: contiguous scores and a mask expected"); st = SPYB_UNSUPPORTED; break; }
+            const spyb_tensor &mk = local.input[1];
+            err = launch_softmax_masked(static_cast<const float *>(a.data), static_cast<const float *>(mk.data), static_cast<float *>(out.dev),
+                                        a.elements[0], a.elements[1], a.elements[2] * a.elements[3], mk.bytes[1] / 4, d->softmax_scale, be->d_exp_table, be->stream);
+        } break;
+        case SPYB_OP_ROPE:
+            if (d->rope.mode != 0 || d->rope.extend_factor != 0.f || d->rope.freq_scale != 1.f || d->rope.attention_factor != 1.f) {
+                be->set_error("Rope: only mode Norm with default scaling is implemented"); st = SPYB_UNSUPPORTED; break;
+            }
+            err = launch_rope(to_strided(a, a.data), static_cast<const int32_t *>(local.input[1].data), to_strided(local.output, out.dev),
+                              d->rope.freq_base, d->rope.num_dim, be->stream);
+            break;
+        case SPYB_OP_COPY: {   // destination = input[1]; the output aliases it (view.cpp:216-227)
+            const spyb_tensor &dst = local.input[1];
+            err = launch_copy_strided(to_strided(a, a.data), a.number_type, to_strided(dst, dst.data), dst.number_type, be->stream);
+            d->output.data = d->input[1].data;
+        } break;
+        case SPYB_OP_DUP: case SPYB_OP_CONTIGUOUS:
+            err = launch_copy_strided(to_strided(a, a.data), a.number_type, to_strided(local.output, out.dev), local.output.number_type, be->stream);
+            break;
+        case SPYB_OP_GETROW: {
+            const spyb_tensor &ids = local.input[1];
+            const int64_t rb = a.bytes[1];
+            err = launch_getrow(static_cast<const uint8_t *>(a.data), a.number_type, rb, a.elements[0], static_cast<const int32_t *>(ids.data),
+                                tensor_elems(ids), static_cast<float *>(out.dev), be->stream);
+            if (err == cudaErrorNotSupported) { be->set_error("GetRow: table type %d", a.number_type); st = SPYB_UNSUPPORTED; err = cudaSuccess; }
+        } break;
+        default:
+            be->set_error("operator type %d is not implemented on this backend", d->op_type);
+            st = SPYB_UNSUPPORTED;
+        }
+        if (st == SPYB_SUCCESS && err != cudaSuccess) { be->set_error("operator %d launch failed: %s", d->op_type, cudaGetErrorString(err)); st = SPYB_FAIL; }
+        if (st == SPYB_SUCCESS && has_out_copy) {
+            cudaError_t e2 = cudaMemcpyAsync(d->output.data, out.dev, out.bytes, cudaMemcpyDeviceToHost, be->stream);
+            if (e2 != cudaSuccess) { be->set_error("copy of an IO result failed: %s", cudaGetErrorString(e2)); st = SPYB_FAIL; }
+        }
+    } break;
+    }
+    for (auto &s : in) { stage_release(be, &s); }
+    stage_release(be, &out);
+    if (st != SPYB_SUCCESS) { return st; }
+
+    if (callback != nullptr) {
+        PendingCallback cb; cb.fn = callback; cb.user = user;
+        SPYB_CUDA(be, cudaEventCreateWithFlags(&cb.event, cudaEventDisableTiming));
+        SPYB_CUDA(be, cudaEventRecord(cb.event, be->stream));
+        { std::lock_guard<std::mutex> g(be->cb_mutex); be->cb_queue.push_back(cb); }
+        be->cb_cv.notify_one();
+    }
+    return SPYB_SUCCESS;
+}
+
+}  // extern "C"

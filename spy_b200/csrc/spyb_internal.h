@@ -1,0 +1,107 @@
+// Internal state of the backend object behind the C ABI.
+#pragma once
+
+#include <condition_variable>
+#include <cstdarg>
+#include <cstdio>
+#include <deque>
+#include <map>
+#include <mutex>
+#include <string>
+#include <thread>
+#include <unordered_map>
+#include <vector>
+
+#include <cuda_runtime.h>
+
+#include "../../include/spyb.h"
+#include "spyb_kernels.h"
+
+namespace spyb {
+
+// First-fit device arena behind spyb_alloc / spyb_free. The reference's scheduler allocates every
+// operator output and frees dead tensors from two threads
+// (backend/distributor/include/scheduler/default_scheduler.h:167-228), so both calls are O(log n)
+// host work under one mutex and never touch the CUDA allocator on the hot path.
+class Arena {
+public:
+    bool     init(size_t bytes);
+    void     destroy();
+    void    *alloc(size_t bytes);
+    void     free(void *ptr, size_t bytes);
+    size_t   capacity() const { return capacity_; }
+    size_t   available();
+    bool     owns(const void *p) const { return p >= base_ && p < base_ + capacity_; }
+
+private:
+    static constexpr size_t ALIGN = 256;
+    uint8_t                 *base_ = nullptr;
+    size_t                   capacity_ = 0;
+    std::map<size_t, size_t> free_;       // offset -> size
+    std::unordered_map<void *, size_t> overflow_;   // allocations that did not fit the arena
+    std::mutex               mutex_;
+};
+
+struct PendingCallback {
+    cudaEvent_t event;
+    void (*fn)(void *);
+    void *user;
+};
+
+}  // namespace spyb
+
+struct spyb_backend {
+    spyb_config  config{};
+    int          num_sms = 148;
+    cudaStream_t stream = nullptr;
+    spyb::Arena  arena;
+    float       *d_silu_table = nullptr;   // 65536 entries: xh / (1 + expf(-xh)) for the fp16 value xh
+    float       *d_exp_table = nullptr;    // 65536 entries: expf(xh)
+
+    std::mutex  err_mutex;
+    std::string last_error;
+
+    // constants uploaded through spyb_upload_constant: name -> raw device copy, and raw pointer -> re-tiled planes
+    std::mutex                               const_mutex;
+    std::unordered_map<std::string, void *>  constants;
+    std::unordered_map<const void *, spyb::DevMatrix> retiled;
+    std::vector<void *>                      owned;   // cudaMalloc'd blocks to release at destroy
+
+    // completion callbacks
+    std::thread                      cb_thread;
+    std::mutex                       cb_mutex;
+    std::condition_variable          cb_cv;
+    std::deque<spyb::PendingCallback> cb_queue;
+    bool                             cb_stop = false;
+
+    void set_error(const char *fmt, ...) {
+        char buf[512];
+        va_list ap; va_start(ap, fmt); vsnprintf(buf, sizeof(buf), fmt, ap); va_end(ap);
+        std::lock_guard<std::mutex> g(err_mutex);
+        last_error = buf;
+    }
+    spyb::LaunchCfg launch_cfg(bool pdl) const {
+        spyb::LaunchCfg c; c.stream = stream; c.pdl = pdl; c.num_sms = num_sms; return c;
+    }
+};
+
+namespace spyb {
+
+#define SPYB_CUDA(backend, expr)                                                                     \
+    do {                                                                                             \
+        cudaError_t err__ = (expr);                                                                  \
+        if (err__ != cudaSuccess) {                                                                  \
+            (backend)->set_error("%s failed: %s (%s:%d)", #expr, cudaGetErrorString(err__), __FILE__, __LINE__); \
+            return SPYB_FAIL;                                                                        \
+        }                                                                                            \
+    } while (0)
+
+// upload raw reference-layout rows [n_rows][row_stride_bytes] (host) and re-tile the block range
+// [blk0, blk0 + nb) of every row into freshly allocated planes; used for row shards (contiguous rows)
+// and K shards (a block sub-range of each row) alike.
+spyb_status upload_matrix(spyb_backend *be, int type, const uint8_t *host_rows, int64_t n_rows, int64_t row_stride_bytes,
+                          int64_t blk0, int nb, DevMatrix *out, uint4 *qa_dst = nullptr, uint4 *qb_dst = nullptr,
+                          uint16_t *d_dst = nullptr);
+spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, DevMatrix *out);
+
+}  // namespace spyb

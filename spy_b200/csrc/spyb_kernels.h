@@ -1,0 +1,110 @@
+// Host-side launch interface of the sm_100a kernels (internal to the library).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace spyb {
+
+// A quantized weight matrix resident in HBM, re-tiled at upload into planes so that every lane's
+// load is one aligned 128-bit word and a warp reads 512 contiguous bytes:
+//   Q4_0: qa[row][block] = the 16 nibble bytes of the block, d[row][block] = fp16 scale
+//   Q8_0: qa[row][block] = int8 values 0..15, qb[row][block] = values 16..31, d = fp16 scale
+// The bytes are those of the reference's block_q4_0_t / block_q8_0_t
+// (orchestration/include/number/number_impl/quant.h:10-33, 124-147), only regrouped.
+struct DevMatrix {
+    int             type = -1;
+    int64_t         n_rows = 0;
+    int64_t         k = 0;
+    int             nb = 0;
+    const uint4    *qa = nullptr;
+    const uint4    *qb = nullptr;
+    const uint16_t *d  = nullptr;
+    size_t bytes() const { return (size_t)n_rows * nb * ((type == 8 ? 32 : 16) + 2); }
+};
+
+enum Prologue { PRO_QUANT = 0, PRO_NORM_QUANT = 1 };
+enum Epilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_SILU_MUL = 2, EPI_QKV_ROPE = 3 };
+
+struct MatvecParams {
+    DevMatrix A;
+    DevMatrix B;               // second matrix when pair_mode == 1 (same shape as A)
+    int       pair_mode = 0;   // 0: a warp owns rows (2u, 2u+1) of A; 1: it owns row u of A and row u of B
+    int       T = 1;           // activation columns (tokens) in this launch, <= 8
+    // prologue
+    int          pro = PRO_QUANT;
+    const float *x = nullptr;  // [T][x_stride] f32
+    int64_t      x_stride = 0;
+    const float *norm_w = nullptr;
+    float        eps = 0.f;
+    // epilogue
+    int          epi = EPI_STORE;
+    float       *out = nullptr;   // [T][out_stride]
+    int64_t      out_stride = 0;
+    const float *resid = nullptr; // [T][out_stride]
+    const float *silu_table = nullptr;
+    // EPI_QKV_ROPE: rows [0,dl) = Q, [dl,2dl) = K, [2dl,3dl) = V
+    const int    *pos_base = nullptr;   // device scalar: position of column 0
+    const float2 *rope_table = nullptr; // [n_ctx][hd/2] (cos, sin)
+    int           hd = 128;
+    int           dl = 0;
+    __half       *q_out = nullptr;      // [T][dl]
+    __half       *k_cache = nullptr;    // [n_ctx][dl]
+    __half       *v_cache = nullptr;    // [n_ctx][dl]
+    // optional tap: reference-layout Q8_0 blocks of column 0 (nb * 34 bytes)
+    uint8_t      *tap_xq = nullptr;
+};
+
+struct AttnParams {
+    const __half *q = nullptr;        // [T][dl], already rounded to fp16
+    const __half *k_cache = nullptr;  // [n_ctx][dl]
+    const __half *v_cache = nullptr;  // [n_ctx][dl]
+    float        *out = nullptr;      // [T][dl]
+    const int    *pos_base = nullptr;
+    const float  *exp_table = nullptr;
+    int   n_head = 0, hd = 128, dl = 0, T = 1, n_ctx = 0;
+    int   n_split = 1;
+    float scale = 0.f;
+    float *scratch = nullptr;         // n_split > 1: [T*n_head][n_split][hd + 2] partials
+    int   *counters = nullptr;        // n_split > 1: [T*n_head], zero before first use; the kernel leaves them zero
+};
+
+struct LaunchCfg {
+    cudaStream_t stream = nullptr;
+    bool         pdl = false;   // launch with the programmatic-stream-serialization attribute
+    int          num_sms = 148;
+};
+
+size_t      matvec_smem_bytes(int nb, int T);
+cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg);
+cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg);
+size_t      attention_scratch_floats(int T, int n_head, int n_split, int hd);
+
+// upload-time re-tiling of raw reference-layout blocks into DevMatrix planes
+cudaError_t launch_retile_q4_0(const uint8_t *raw, int64_t row_stride_bytes, int64_t n_rows, int nb, uint4 *qa, uint16_t *d, cudaStream_t s);
+cudaError_t launch_retile_q8_0(const uint8_t *raw, int64_t row_stride_bytes, int64_t n_rows, int nb, uint4 *qa, uint4 *qb, uint16_t *d, cudaStream_t s);
+
+// stand-alone arithmetic kernels (parity checks and the per-operator path)
+cudaError_t launch_quantize_q8_0_ref_layout(const float *x, int64_t n, uint8_t *blocks, cudaStream_t s);
+cudaError_t launch_block_dots(int wtype, const uint8_t *w_row, const uint8_t *x_blocks, int64_t n, int32_t *out, cudaStream_t s);
+
+struct Strided {   // a tensor as the reference's Shape describes it: elements + byte strides
+    void   *data;
+    int64_t ne[4];
+    int64_t nb[4];
+};
+cudaError_t launch_rmsnorm(const float *x, float *out, int64_t n, int64_t rows, float eps, cudaStream_t s);
+cudaError_t launch_binary_rows(int op /*0 add, 1 mul*/, const float *a, const float *b, float *out, int64_t n, int64_t rows, int64_t b_rows, cudaStream_t s);
+cudaError_t launch_silu(const float *x, float *out, int64_t n, const float *silu_table, cudaStream_t s);
+cudaError_t launch_softmax_masked(const float *scores, const float *mask, float *out, int64_t ne0, int64_t ne1, int64_t ne2,
+                                  int64_t mask_stride, float scale, const float *exp_table, cudaStream_t s);
+cudaError_t launch_rope(const Strided &x, const int32_t *pos, const Strided &out, float freq_base, int n_dim, cudaStream_t s);
+cudaError_t launch_copy_strided(const Strided &src, int src_type, const Strided &dst, int dst_type, cudaStream_t s);
+cudaError_t launch_getrow(const uint8_t *table, int table_type, int64_t row_bytes, int64_t ne0, const int32_t *ids, int64_t n_ids, float *out, cudaStream_t s);
+cudaError_t launch_matmul_f16(const Strided &w /*f16*/, const Strided &x /*f32*/, const Strided &out /*f32*/, cudaStream_t s);
+cudaError_t launch_argmax_embed(const float *logits, int64_t n_vocab, int32_t *token_out, int32_t *history, int *pos_counter,
+                                const uint8_t *embd, int embd_type, int64_t d_model, float *x_out, const LaunchCfg &cfg);
+cudaError_t launch_embed(const int32_t *ids, int n_ids, const uint8_t *embd, int embd_type, int64_t d_model, float *x_out, cudaStream_t s);
+
+}  // namespace spyb

@@ -1,0 +1,596 @@
+// Whole-model path: GGUF -> device-resident quantized planes (optionally one tensor-parallel shard),
+// and the LLaMa step executed as a fixed plan of fused kernels, replayed from a CUDA graph for
+// single-token decode.
+//
+// The plan is the graph LLAMAModel::build_graph emits (model/src/llm/model/llama.cpp:123-222,
+// plugin/attention.cpp:267-302, plugin/ffn.cpp:5-42, plugin/inout.cpp:5-78) with neighbouring
+// operators folded into five kernels per layer:
+//   1  NormRMS + Mul(attn_norm) + Q8_0 quantize -> Wq|Wk|Wv mat-vec -> RoPE(Q,K) + f16 KV append
+//   2  attention (scores, masked softmax, PV)
+//   3  Q8_0 quantize -> Wo mat-vec -> + residual
+//   4  NormRMS + Mul(ffn_norm) + quantize -> Wup & Wgate mat-vec -> up * silu(gate)
+//   5  Q8_0 quantize -> Wdown mat-vec -> + residual
+// then NormRMS + Mul(output_norm) + quantize -> output mat-vec -> logits, and a greedy argmax that
+// also gathers the next token's embedding.
+
+#include <cmath>
+#include <cstring>
+#include <dlfcn.h>
+#include <fcntl.h>
+#include <string>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include "spyb_internal.h"
+
+namespace spyb {
+
+// ------------------------------------------------------------------------------------------ GGUF
+// Same file layout GGUFAdapter::init_from_file reads (storage/src/adapter/gguf_adapter.cpp:90-190).
+struct GgufTensor { int n_dim = 0; int64_t ne[4] = {1, 1, 1, 1}; int type = 0; uint64_t offset = 0; };
+
+struct GgufFile {
+    int      fd = -1;
+    uint8_t *map = nullptr;
+    size_t   size = 0;
+    size_t   data_off = 0;
+    std::map<std::string, GgufTensor> tensors;
+    std::map<std::string, double>     num;    // numeric metadata
+    std::map<std::string, std::string> str;
+    int64_t  n_tokens = 0;
+
+    ~GgufFile() { if (map) { munmap(map, size); } if (fd >= 0) { close(fd); } }
+
+    bool open(const char *path, std::string *err) {
+        fd = ::open(path, O_RDONLY);
+        if (fd < 0) { *err = std::string("cannot open ") + path; return false; }
+        struct stat st;
+        if (fstat(fd, &st) != 0 || st.st_size < 24) { *err = "file too small for a GGUF header"; return false; }
+        size = (size_t)st.st_size;
+        map = static_cast<uint8_t *>(mmap(nullptr, size, PROT_READ, MAP_SHARED, fd, 0));
+        if (map == MAP_FAILED) { map = nullptr; *err = "mmap failed"; return false; }
+        size_t pos = 0;
+        auto need = [&](size_t n) { return pos + n <= size; };
+        auto rd = [&](void *dst, size_t n) { if (!need(n)) { return false; } std::memcpy(dst, map + pos, n); pos += n; return true; };
+        auto rd_str = [&](std::string *s) { uint64_t n; if (!rd(&n, 8) || !need(n)) { return false; } s->assign(reinterpret_cast<char *>(map + pos), n); pos += n; return true; };
+        char magic[4]; uint32_t version; uint64_t n_tensors, n_kv;
+        if (!rd(magic, 4) || std::memcmp(magic, "GGUF", 4) != 0) { *err = "bad GGUF magic"; return false; }
+        if (!rd(&version, 4) || !rd(&n_tensors, 8) || !rd(&n_kv, 8)) { *err = "truncated GGUF header"; return false; }
+        if (version != 3) { *err = "unsupported GGUF version"; return false; }
+        static const int scalar_size[13] = {1, 1, 2, 2, 4, 4, 4, 1, 0, 0, 8, 8, 8};
+        auto rd_scalar = [&](uint32_t type, double *out) {
+            uint8_t buf[8] = {0};
+            if (type > 12 || scalar_size[type] == 0 || !rd(buf, scalar_size[type])) { return false; }
+            switch (type) {
+            case 0: *out = buf[0]; break; case 1: *out = (int8_t)buf[0]; break;
+            case 2: { uint16_t v; std::memcpy(&v, buf, 2); *out = v; } break; case 3: { int16_t v; std::memcpy(&v, buf, 2); *out = v; } break;
+            case 4: { uint32_t v; std::memcpy(&v, buf, 4); *out = v; } break; case 5: { int32_t v; std::memcpy(&v, buf, 4); *out = v; } break;
+            case 6: { float v; std::memcpy(&v, buf, 4); *out = v; } break; case 7: *out = buf[0] != 0; break;
+            case 10: { uint64_t v; std::memcpy(&v, buf, 8); *out = (double)v; } break; case 11: { int64_t v; std::memcpy(&v, buf, 8); *out = (double)v; } break;
+            case 12: { double v; std::memcpy(&v, buf, 8); *out = v; } break;
+            default: return false;
+            }
+            return true;
+        };
+        for (uint64_t i = 0; i < n_kv; ++i) {
+            std::string key; uint32_t type;
+            if (!rd_str(&key) || !rd(&type, 4)) { *err = "truncated GGUF metadata"; return false; }
+            if (type == 8) { std::string v; if (!rd_str(&v)) { *err = "truncated GGUF string"; return false; } str[key] = v; }
+            else if (type == 9) {
+                uint32_t et; uint64_t n;
+                if (!rd(&et, 4) || !rd(&n, 8)) { *err = "truncated GGUF array"; return false; }
+                if (key == "tokenizer.ggml.tokens") { n_tokens = (int64_t)n; }
+                for (uint64_t j = 0; j < n; ++j) {
+                    if (et == 8) { std::string v; if (!rd_str(&v)) { *err = "truncated GGUF array"; return false; } }
+                    else { double v; if (!rd_scalar(et, &v)) { *err = "bad GGUF array element"; return false; } }
+                }
+            } else { double v; if (!rd_scalar(type, &v)) { *err = "bad GGUF value type"; return false; } num[key] = v; }
+        }
+        for (uint64_t i = 0; i < n_tensors; ++i) {
+            std::string name; GgufTensor t; uint32_t nd, ty;
+            if (!rd_str(&name) || !rd(&nd, 4) || nd > 4) { *err = "truncated GGUF tensor info"; return false; }
+            t.n_dim = (int)nd;
+            for (uint32_t k = 0; k < nd; ++k) { uint64_t e; if (!rd(&e, 8)) { *err = "truncated GGUF tensor info"; return false; } t.ne[k] = (int64_t)e; }
+            if (!rd(&ty, 4) || !rd(&t.offset, 8)) { *err = "truncated GGUF tensor info"; return false; }
+            t.type = (int)ty;
+            tensors[name] = t;
+        }
+        const size_t align = num.count("general.alignment") ? (size_t)num["general.alignment"] : 32;
+        data_off = (pos + align - 1) / align * align;
+        return true;
+    }
+
+    static int64_t row_bytes(int type, int64_t k) {
+        switch (type) { case 0: return k * 4; case 1: return k * 2; case 2: return k / 32 * 18; case 8: return k / 32 * 34;
+                        case 12: return k / 256 * 144; case 14: return k / 256 * 210; default: return -1; }
+    }
+    const uint8_t *data(const GgufTensor &t, std::string *err) const {
+        const int64_t rb = row_bytes(t.type, t.ne[0]);
+        if (rb < 0) { *err = "tensor type not supported"; return nullptr; }
+        const size_t bytes = (size_t)rb * t.ne[1] * t.ne[2] * t.ne[3];
+        if (data_off + t.offset + bytes > size) { *err = "tensor data runs past the end of the file"; return nullptr; }
+        return map + data_off + t.offset;
+    }
+};
+
+// ------------------------------------------------------------------------------------------ NCCL (loaded on demand)
+struct NcclApi {
+    struct Uid { char b[128]; };   // ncclUniqueId, passed by value
+    void *lib = nullptr;
+    int (*GetUniqueId)(void *) = nullptr;
+    int (*CommInitRank)(void **, int, Uid, int) = nullptr;
+    int (*AllReduce)(const void *, void *, size_t, int, int, void *, cudaStream_t) = nullptr;
+    int (*CommDestroy)(void *) = nullptr;
+    const char *(*GetErrorString)(int) = nullptr;
+    bool load() {
+        if (lib) { return true; }
+        lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!lib) { return false; }
+        GetUniqueId  = reinterpret_cast<decltype(GetUniqueId)>(dlsym(lib, "ncclGetUniqueId"));
+        CommInitRank = reinterpret_cast<decltype(CommInitRank)>(dlsym(lib, "ncclCommInitRank"));
+        AllReduce    = reinterpret_cast<decltype(AllReduce)>(dlsym(lib, "ncclAllReduce"));
+        CommDestroy  = reinterpret_cast<decltype(CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
+        GetErrorString = reinterpret_cast<decltype(GetErrorString)>(dlsym(lib, "ncclGetErrorString"));
+        return GetUniqueId && CommInitRank && AllReduce && CommDestroy;
+    }
+};
+static NcclApi g_nccl;
+
+struct Layer {
+    DevMatrix wqkv, wo, up, gate, down;
+    float    *attn_norm = nullptr, *ffn_norm = nullptr;
+    __half   *k_cache = nullptr, *v_cache = nullptr;   // [n_ctx][dl] each
+};
+
+}  // namespace spyb
+
+using namespace spyb;
+
+struct spyb_model {
+    spyb_backend   *be = nullptr;
+    spyb_model_info info{};
+    int             dl = 0, fl = 0;          // local (per-rank) attention width and FFN width
+    std::vector<Layer> layers;
+    DevMatrix       head;
+    float          *output_norm = nullptr;
+    uint8_t        *embd = nullptr;
+    int             embd_type = 0;
+    float2         *rope_table = nullptr;
+    // activations for up to 8 tokens per pass
+    float  *x = nullptr, *att = nullptr, *act = nullptr, *partial = nullptr, *logits = nullptr;
+    __half *q = nullptr;
+    int    *d_pos = nullptr;
+    int32_t *d_token = nullptr, *d_tokens_in = nullptr, *d_history = nullptr;
+    uint8_t *d_tap = nullptr;
+    float  *att_scratch = nullptr; int *att_counters = nullptr; int n_split = 1;
+    int    *h_pos_pinned = nullptr; int32_t *h_tok_pinned = nullptr; float *h_logits_pinned = nullptr;
+    void   *nccl_comm = nullptr;
+    cudaGraphExec_t graph_exec = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    float   last_ms = 0.f;
+    int64_t last_launches = 0;
+    std::vector<void *> owned;
+};
+
+namespace {
+
+template <class T>
+spyb_status dev_alloc(spyb_model *m, T **p, size_t count) {
+    void *raw = nullptr;
+    SPYB_CUDA(m->be, cudaMalloc(&raw, count * sizeof(T) + 64));
+    SPYB_CUDA(m->be, cudaMemset(raw, 0, count * sizeof(T) + 64));
+    m->owned.push_back(raw);
+    *p = static_cast<T *>(raw);
+    return SPYB_SUCCESS;
+}
+
+spyb_status allreduce(spyb_model *m, float *buf, size_t count, int64_t *launches) {
+    if (m->info.tp_size == 1) { return SPYB_SUCCESS; }
+    if (m->nccl_comm == nullptr) { m->be->set_error("tensor-parallel model used before spyb_model_init_tp"); return SPYB_FAIL; }
+    const int rc = g_nccl.AllReduce(buf, buf, count, /*ncclFloat32*/ 7, /*ncclSum*/ 0, m->nccl_comm, m->be->stream);
+    if (rc != 0) { m->be->set_error("ncclAllReduce failed: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?"); return SPYB_FAIL; }
+    ++*launches;
+    return SPYB_SUCCESS;
+}
+
+// the five fused kernels of every layer for T tokens whose first position is *d_pos
+spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
+    spyb_backend *be = m->be;
+    const bool pdl = be->config.use_pdl != 0;
+    const LaunchCfg cfg = be->launch_cfg(pdl);
+    const int d = m->info.d_model, tp = m->info.tp_size;
+    for (size_t L = 0; L < m->layers.size(); ++L) {
+        Layer &ly = m->layers[L];
+        {   // 1: norm + quantize -> QKV -> rope + KV append
+            MatvecParams p;
+            p.A = ly.wqkv; p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.attn_norm; p.eps = m->info.rms_eps;
+            p.epi = EPI_QKV_ROPE; p.pos_base = m->d_pos; p.rope_table = m->rope_table; p.hd = m->info.head_dim; p.dl = m->dl;
+            p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache;
+            p.tap_xq = (tap && L == 0) ? m->d_tap : nullptr;
+            SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
+        }
+        {   // 2: attention
+            AttnParams a;
+            a.q = m->q; a.k_cache = ly.k_cache; a.v_cache = ly.v_cache; a.out = m->att; a.pos_base = m->d_pos; a.exp_table = be->d_exp_table;
+            a.n_head = m->dl / m->info.head_dim; a.hd = m->info.head_dim; a.dl = m->dl; a.T = T; a.n_ctx = m->info.n_ctx;
+            a.n_split = m->n_split; a.scale = 1.0f / std::sqrt((float)m->info.head_dim);
+            a.scratch = m->att_scratch; a.counters = m->att_counters;
+            SPYB_CUDA(be, launch_attention(a, cfg)); ++*launches;
+        }
+        {   // 3: quantize -> Wo -> + residual (tensor parallel: partial sums, rank 0 carries the residual)
+            MatvecParams p;
+            p.A = ly.wo; p.T = T; p.pro = PRO_QUANT; p.x = m->att; p.x_stride = m->dl;
+            p.resid = m->x; p.out_stride = d;
+            if (tp == 1) { p.epi = EPI_RESID; p.out = m->x; }
+            else { p.epi = (m->info.tp_rank == 0) ? EPI_RESID : EPI_STORE; p.out = m->partial; }
+            SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
+            if (tp > 1) {
+                if (allreduce(m, m->partial, (size_t)T * d, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
+                std::swap(m->x, m->partial);
+            }
+        }
+        {   // 4: norm + quantize -> up, gate -> up * silu(gate)
+            MatvecParams p;
+            p.A = ly.up; p.B = ly.gate; p.pair_mode = 1; p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
+            p.eps = m->info.rms_eps; p.epi = EPI_SILU_MUL; p.out = m->act; p.out_stride = m->fl; p.silu_table = be->d_silu_table;
+            SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
+        }
+        {   // 5: quantize -> Wdown -> + residual
+            MatvecParams p;
+            p.A = ly.down; p.T = T; p.pro = PRO_QUANT; p.x = m->act; p.x_stride = m->fl;
+            p.resid = m->x; p.out_stride = d;
+            if (tp == 1) { p.epi = EPI_RESID; p.out = m->x; }
+            else { p.epi = (m->info.tp_rank == 0) ? EPI_RESID : EPI_STORE; p.out = m->partial; }
+            SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
+            if (tp > 1) {
+                if (allreduce(m, m->partial, (size_t)T * d, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
+                std::swap(m->x, m->partial);
+            }
+        }
+    }
+    return SPYB_SUCCESS;
+}
+
+// output norm + head on column `col` of x -> logits[n_vocab]
+spyb_status run_head(spyb_model *m, int col, int64_t *launches) {
+    MatvecParams p;
+    p.A = m->head; p.T = 1; p.pro = PRO_NORM_QUANT; p.x = m->x + (int64_t)col * m->info.d_model; p.x_stride = m->info.d_model;
+    p.norm_w = m->output_norm; p.eps = m->info.rms_eps; p.epi = EPI_STORE; p.out = m->logits; p.out_stride = m->info.n_vocab;
+    SPYB_CUDA(m->be, launch_matvec(p, m->be->launch_cfg(m->be->config.use_pdl != 0))); ++*launches;
+    return SPYB_SUCCESS;
+}
+
+spyb_status run_decode_step(spyb_model *m, int64_t *launches) {
+    if (run_layers(m, 1, false, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
+    if (run_head(m, 0, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
+    SPYB_CUDA(m->be, launch_argmax_embed(m->logits, m->info.n_vocab, m->d_token, m->d_history, m->d_pos, m->embd, m->embd_type,
+                                         m->info.d_model, m->x, m->be->launch_cfg(m->be->config.use_pdl != 0)));
+    ++*launches;
+    return SPYB_SUCCESS;
+}
+
+}  // namespace
+
+extern "C" {
+
+spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_ctx, spyb_model **out) {
+    if (be == nullptr || path == nullptr || out == nullptr) { return SPYB_FAIL; }
+    *out = nullptr;
+    cudaSetDevice(be->config.device_id);
+    GgufFile f; std::string err;
+    if (!f.open(path, &err)) { be->set_error("GGUF: %s", err.c_str()); return SPYB_FAIL; }
+    if (f.str["general.architecture"] != "llama") { be->set_error("GGUF: architecture '%s' is not supported", f.str["general.architecture"].c_str()); return SPYB_UNSUPPORTED; }
+    auto num = [&](const char *k, double dflt) { auto it = f.num.find(k); return it == f.num.end() ? dflt : it->second; };
+    spyb_model *m = new spyb_model();
+    m->be = be;
+    spyb_model_info &I = m->info;
+    I.n_layer = (int)num("llama.block_count", 0); I.d_model = (int)num("llama.embedding_length", 0);
+    I.n_head = (int)num("llama.attention.head_count", 0); I.n_ff = (int)num("llama.feed_forward_length", 0);
+    I.n_ctx = n_ctx > 0 ? n_ctx : (int)num("llama.context_length", 512);
+    I.rms_eps = (float)num("llama.attention.layer_norm_rms_epsilon", 1e-5); I.rope_base = (float)num("llama.rope.freq_base", 10000.0);
+    I.tp_size = be->config.tp_size; I.tp_rank = be->config.tp_rank;
+    const int kv_heads = (int)num("llama.attention.head_count_kv", I.n_head);
+    auto fail = [&](spyb_status st) { spyb_model_free(m); return st; };
+    if (I.n_layer <= 0 || I.d_model <= 0 || I.n_head <= 0 || I.n_ff <= 0) { be->set_error("GGUF: missing llama.* hyper-parameters"); return fail(SPYB_FAIL); }
+    if (kv_heads != I.n_head) { be->set_error("grouped-query attention (head_count_kv %d != head_count %d) is not supported", kv_heads, I.n_head); return fail(SPYB_UNSUPPORTED); }
+    I.head_dim = I.d_model / I.n_head;
+    if (I.head_dim != 128) { be->set_error("head_dim %d is not supported (128 only)", I.head_dim); return fail(SPYB_UNSUPPORTED); }
+    const int tp = I.tp_size;
+    if (I.n_head % tp != 0 || (I.n_ff / tp) % 32 != 0 || I.n_ff % tp != 0) { be->set_error("tp_size %d does not divide heads / FFN blocks", tp); return fail(SPYB_FAIL); }
+    m->dl = I.d_model / tp; m->fl = I.n_ff / tp;
+    const int d = I.d_model, dl = m->dl, fl = m->fl, r = I.tp_rank;
+
+    auto tensor = [&](const std::string &name, const GgufTensor **t, const uint8_t **data) {
+        auto it = f.tensors.find(name);
+        if (it == f.tensors.end()) { be->set_error("GGUF: tensor %s is missing", name.c_str()); return false; }
+        *t = &it->second;
+        *data = f.data(it->second, &err);
+        if (*data == nullptr) { be->set_error("GGUF: %s: %s", name.c_str(), err.c_str()); return false; }
+        return true;
+    };
+    auto upload_f32 = [&](const std::string &name, int64_t n, float **dst) {
+        const GgufTensor *t; const uint8_t *data;
+        if (!tensor(name, &t, &data)) { return SPYB_FAIL; }
+        if (t->type != SPYB_FP32 || t->ne[0] != n) { be->set_error("GGUF: %s must be f32[%lld]", name.c_str(), (long long)n); return SPYB_FAIL; }
+        if (dev_alloc(m, dst, (size_t)n) != SPYB_SUCCESS) { return SPYB_FAIL; }
+        SPYB_CUDA(be, cudaMemcpy(*dst, data, (size_t)n * 4, cudaMemcpyHostToDevice));
+        return SPYB_SUCCESS;
+    };
+    // rows [row0, row0 + n_rows) and blocks [blk0, blk0 + nb) of a [k_full, rows_full] matrix -> planes (optionally into `into` at row dst_row)
+    auto upload_w = [&](const std::string &name, int64_t k_full, int64_t rows_full, int64_t row0, int64_t n_rows, int64_t blk0, int nb,
+                        DevMatrix *dst, DevMatrix *into, int64_t dst_row) {
+        const GgufTensor *t; const uint8_t *data;
+        if (!tensor(name, &t, &data)) { return SPYB_FAIL; }
+        if (t->ne[0] != k_full || t->ne[1] != rows_full) { be->set_error("GGUF: %s has shape [%lld, %lld]", name.c_str(), (long long)t->ne[0], (long long)t->ne[1]); return SPYB_FAIL; }
+        if (t->type != SPYB_Q4_0 && t->type != SPYB_Q8_0) { be->set_error("GGUF: %s: weight type %d has no device kernel", name.c_str(), t->type); return SPYB_UNSUPPORTED; }
+        const int64_t rb = GgufFile::row_bytes(t->type, k_full);
+        I.weight_bytes += (uint64_t)n_rows * nb * (t->type == SPYB_Q4_0 ? 18 : 34);
+        if (into != nullptr) {
+            if (into->type != t->type) { be->set_error("GGUF: %s: Wq/Wk/Wv must share one type", name.c_str()); return SPYB_UNSUPPORTED; }
+            return upload_matrix(be, t->type, data + row0 * rb, n_rows, rb, blk0, nb, dst,
+                                 const_cast<uint4 *>(into->qa) + dst_row * nb, into->qb ? const_cast<uint4 *>(into->qb) + dst_row * nb : nullptr,
+                                 const_cast<uint16_t *>(into->d) + dst_row * nb);
+        }
+        return upload_matrix(be, t->type, data + row0 * rb, n_rows, rb, blk0, nb, dst);
+    };
+
+    // embeddings stay in their raw layout (gathered one row at a time); the reference gathers F32 / Q8_0 rows only
+    {
+        const GgufTensor *t; const uint8_t *data;
+        if (!tensor("token_embd.weight", &t, &data)) { return fail(SPYB_FAIL); }
+        I.n_vocab = (int)t->ne[1];
+        m->embd_type = t->type;
+        if (t->type != SPYB_FP32 && t->type != SPYB_FP16 && t->type != SPYB_Q8_0 && t->type != SPYB_Q4_0) { be->set_error("token_embd type %d is not supported", t->type); return fail(SPYB_UNSUPPORTED); }
+        const size_t bytes = (size_t)GgufFile::row_bytes(t->type, d) * t->ne[1];
+        if (dev_alloc(m, &m->embd, bytes) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
+        if (cudaMemcpy(m->embd, data, bytes, cudaMemcpyHostToDevice) != cudaSuccess) { be->set_error("embedding upload failed"); return fail(SPYB_FAIL); }
+    }
+    spyb_status st = upload_f32("output_norm.weight", d, &m->output_norm);
+    if (st != SPYB_SUCCESS) { return fail(st); }
+    {
+        const std::string head_name = f.tensors.count("output.weight") ? "output.weight" : "token_embd.weight";
+        st = upload_w(head_name, d, I.n_vocab, 0, I.n_vocab, 0, d / 32, &m->head, nullptr, 0);   // replicated on every rank
+        if (st != SPYB_SUCCESS) { return fail(st); }
+    }
+    m->layers.resize(I.n_layer);
+    for (int L = 0; L < I.n_layer; ++L) {
+        Layer &ly = m->layers[L];
+        const std::string p = "blk." + std::to_string(L) + ".";
+        if ((st = upload_f32(p + "attn_norm.weight", d, &ly.attn_norm)) != SPYB_SUCCESS) { return fail(st); }
+        if ((st = upload_f32(p + "ffn_norm.weight", d, &ly.ffn_norm)) != SPYB_SUCCESS) { return fail(st); }
+        // heads: rows [r*dl, (r+1)*dl) of Wq, Wk, Wv, stacked into one [3*dl, d] matrix
+        auto itq = f.tensors.find(p + "attn_q.weight");
+        if (itq == f.tensors.end()) { be->set_error("GGUF: %sattn_q.weight is missing", p.c_str()); return fail(SPYB_FAIL); }
+        if ((st = alloc_matrix(be, itq->second.type, 3 * (int64_t)dl, d / 32, &ly.wqkv)) != SPYB_SUCCESS) { return fail(st); }
+        DevMatrix dummy;
+        if ((st = upload_w(p + "attn_q.weight", d, d, (int64_t)r * dl, dl, 0, d / 32, &dummy, &ly.wqkv, 0)) != SPYB_SUCCESS) { return fail(st); }
+        if ((st = upload_w(p + "attn_k.weight", d, d, (int64_t)r * dl, dl, 0, d / 32, &dummy, &ly.wqkv, dl)) != SPYB_SUCCESS) { return fail(st); }
+        if ((st = upload_w(p + "attn_v.weight", d, d, (int64_t)r * dl, dl, 0, d / 32, &dummy, &ly.wqkv, 2 * (int64_t)dl)) != SPYB_SUCCESS) { return fail(st); }
+        // Wo: all d rows, input columns of this rank's heads (a block sub-range of every row)
+        if ((st = upload_w(p + "attn_output.weight", d, d, 0, d, (int64_t)r * dl / 32, dl / 32, &ly.wo, nullptr, 0)) != SPYB_SUCCESS) { return fail(st); }
+        // FFN: rows [r*fl, (r+1)*fl) of up and gate; down keeps all rows and this rank's input columns
+        if ((st = upload_w(p + "ffn_up.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &ly.up, nullptr, 0)) != SPYB_SUCCESS) { return fail(st); }
+        if ((st = upload_w(p + "ffn_gate.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &ly.gate, nullptr, 0)) != SPYB_SUCCESS) { return fail(st); }
+        if ((st = upload_w(p + "ffn_down.weight", I.n_ff, d, 0, d, (int64_t)r * fl / 32, fl / 32, &ly.down, nullptr, 0)) != SPYB_SUCCESS) { return fail(st); }
+        if (ly.up.type != ly.gate.type) { be->set_error("ffn_up and ffn_gate must share one type"); return fail(SPYB_UNSUPPORTED); }
+        if (dev_alloc(m, &ly.k_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS || dev_alloc(m, &ly.v_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
+    }
+    I.weight_bytes += (uint64_t)(2 * I.n_layer + 1) * d * 4;
+    I.kv_bytes_per_token = (uint64_t)2 * I.n_layer * dl * 2;
+
+    // RoPE table with the host libm, theta advanced by repeated f32 multiplication exactly as
+    // OperatorRopeImpl::execute does (backend/host/operator/non-linear.cpp:282, 300-309)
+    {
+        const int hd = I.head_dim;
+        std::vector<float2> tab((size_t)I.n_ctx * (hd / 2));
+        const float theta_scale = std::pow(I.rope_base, -2.0f / (float)hd);
+        for (int pos = 0; pos < I.n_ctx; ++pos) {
+            float theta = (float)pos;
+            for (int i = 0; i < hd / 2; ++i) { tab[(size_t)pos * (hd / 2) + i] = make_float2(std::cos(theta) * 1.0f, std::sin(theta) * 1.0f); theta *= theta_scale; }
+        }
+        if (dev_alloc(m, &m->rope_table, tab.size()) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
+        if (cudaMemcpy(m->rope_table, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice) != cudaSuccess) { be->set_error("rope table upload failed"); return fail(SPYB_FAIL); }
+    }
+    m->n_split = I.n_ctx <= 512 ? 1 : std::min(16, (I.n_ctx + 255) / 256);
+    const int TMAX = 8;
+    bool ok = dev_alloc(m, &m->x, (size_t)TMAX * d) == SPYB_SUCCESS && dev_alloc(m, &m->partial, (size_t)TMAX * d) == SPYB_SUCCESS &&
+              dev_alloc(m, &m->att, (size_t)TMAX * dl) == SPYB_SUCCESS && dev_alloc(m, &m->act, (size_t)TMAX * fl) == SPYB_SUCCESS &&
+              dev_alloc(m, &m->logits, (size_t)I.n_vocab) == SPYB_SUCCESS && dev_alloc(m, &m->q, (size_t)TMAX * dl) == SPYB_SUCCESS &&
+              dev_alloc(m, &m->d_pos, 4) == SPYB_SUCCESS && dev_alloc(m, &m->d_token, 4) == SPYB_SUCCESS &&
+              dev_alloc(m, &m->d_tokens_in, TMAX) == SPYB_SUCCESS && dev_alloc(m, &m->d_history, (size_t)I.n_ctx + 8) == SPYB_SUCCESS &&
+              dev_alloc(m, &m->d_tap, (size_t)d / 32 * 34) == SPYB_SUCCESS &&
+              dev_alloc(m, &m->att_scratch, attention_scratch_floats(TMAX, I.n_head / tp, m->n_split, I.head_dim)) == SPYB_SUCCESS &&
+              dev_alloc(m, &m->att_counters, (size_t)TMAX * I.n_head) == SPYB_SUCCESS;
+    if (!ok) { return fail(SPYB_FAIL); }
+    if (cudaMallocHost(reinterpret_cast<void **>(&m->h_pos_pinned), 64) != cudaSuccess ||
+        cudaMallocHost(reinterpret_cast<void **>(&m->h_tok_pinned), 64) != cudaSuccess ||
+        cudaMallocHost(reinterpret_cast<void **>(&m->h_logits_pinned), (size_t)I.n_vocab * 4) != cudaSuccess) {
+        be->set_error("pinned host allocation failed"); return fail(SPYB_FAIL);
+    }
+    if (cudaEventCreate(&m->ev0) != cudaSuccess || cudaEventCreate(&m->ev1) != cudaSuccess) { be->set_error("event creation failed"); return fail(SPYB_FAIL); }
+    *out = m;
+    return SPYB_SUCCESS;
+}
+
+void spyb_model_free(spyb_model *m) {
+    if (m == nullptr) { return; }
+    cudaSetDevice(m->be->config.device_id);
+    cudaStreamSynchronize(m->be->stream);
+    if (m->graph_exec) { cudaGraphExecDestroy(m->graph_exec); }
+    if (m->nccl_comm && g_nccl.CommDestroy) { g_nccl.CommDestroy(m->nccl_comm); }
+    for (void *p : m->owned) { cudaFree(p); }
+    if (m->h_pos_pinned) { cudaFreeHost(m->h_pos_pinned); }
+    if (m->h_tok_pinned) { cudaFreeHost(m->h_tok_pinned); }
+    if (m->h_logits_pinned) { cudaFreeHost(m->h_logits_pinned); }
+    if (m->ev0) { cudaEventDestroy(m->ev0); }
+    if (m->ev1) { cudaEventDestroy(m->ev1); }
+    delete m;
+}
+
+spyb_status spyb_model_info_get(const spyb_model *m, spyb_model_info *info) {
+    if (m == nullptr || info == nullptr) { return SPYB_FAIL; }
+    *info = m->info;
+    return SPYB_SUCCESS;
+}
+
+spyb_status spyb_nccl_unique_id(void *unique_id_128) {
+    if (!g_nccl.load()) { return SPYB_FAIL; }
+    return g_nccl.GetUniqueId(unique_id_128) == 0 ? SPYB_SUCCESS : SPYB_FAIL;
+}
+
+spyb_status spyb_model_init_tp(spyb_model *m, const void *unique_id_128) {
+    if (m == nullptr) { return SPYB_FAIL; }
+    if (m->info.tp_size == 1) { return SPYB_SUCCESS; }
+    if (!g_nccl.load()) { m->be->set_error("libnccl.so.2 could not be loaded"); return SPYB_FAIL; }
+    cudaSetDevice(m->be->config.device_id);
+    NcclApi::Uid uid; std::memcpy(uid.b, unique_id_128, 128);
+    const int rc = g_nccl.CommInitRank(&m->nccl_comm, m->info.tp_size, uid, m->info.tp_rank);
+    if (rc != 0) { m->be->set_error("ncclCommInitRank failed: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?"); return SPYB_FAIL; }
+    return SPYB_SUCCESS;
+}
+
+spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_tokens, int32_t n_past, float *logits_host) {
+    if (m == nullptr || tokens == nullptr || n_tokens < 1) { return SPYB_FAIL; }
+    spyb_backend *be = m->be;
+    cudaSetDevice(be->config.device_id);
+    if (n_past < 0 || n_past + n_tokens > m->info.n_ctx) { be->set_error("the number of tokens exceeds the context length (%d + %d > %d)", n_past, n_tokens, m->info.n_ctx); return SPYB_FAIL; }
+    for (int i = 0; i < n_tokens; ++i) { if (tokens[i] < 0 || tokens[i] >= m->info.n_vocab) { be->set_error("token id %d out of range", tokens[i]); return SPYB_FAIL; } }
+    int64_t launches = 0;
+    SPYB_CUDA(be, cudaEventRecord(m->ev0, be->stream));
+    for (int t0 = 0; t0 < n_tokens; t0 += 8) {
+        const int T = std::min(8, n_tokens - t0);
+        SPYB_CUDA(be, cudaStreamSynchronize(be->stream));   // pinned staging words are reused per pass
+        *m->h_pos_pinned = n_past + t0;
+        std::memcpy(m->h_tok_pinned, tokens + t0, (size_t)T * 4);
+        SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 4, cudaMemcpyHostToDevice, be->stream));
+        SPYB_CUDA(be, cudaMemcpyAsync(m->d_tokens_in, m->h_tok_pinned, (size_t)T * 4, cudaMemcpyHostToDevice, be->stream));
+        SPYB_CUDA(be, launch_embed(m->d_tokens_in, T, m->embd, m->embd_type, m->info.d_model, m->x, be->stream)); ++launches;
+        if (run_layers(m, T, t0 == 0, &launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
+        if (t0 + T == n_tokens) {
+            if (run_head(m, T - 1, &launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
+            if (logits_host != nullptr) {
+                SPYB_CUDA(be, cudaMemcpyAsync(m->h_logits_pinned, m->logits, (size_t)m->info.n_vocab * 4, cudaMemcpyDeviceToHost, be->stream));
+            }
+        }
+    }
+    SPYB_CUDA(be, cudaEventRecord(m->ev1, be->stream));
+    SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+    if (logits_host != nullptr) { std::memcpy(logits_host, m->h_logits_pinned, (size_t)m->info.n_vocab * 4); }
+    SPYB_CUDA(be, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+    m->last_launches = launches;
+    return SPYB_SUCCESS;
+}
+
+spyb_status spyb_model_decode(spyb_model *m, int32_t first_token, int32_t n_past, int32_t n_steps, int32_t *ids_host, float *logits_host) {
+    if (m == nullptr || n_steps < 1 || ids_host == nullptr) { return SPYB_FAIL; }
+    spyb_backend *be = m->be;
+    cudaSetDevice(be->config.device_id);
+    if (n_past < 0 || n_past + n_steps > m->info.n_ctx) { be->set_error("decode would exceed the context length (%d + %d > %d)", n_past, n_steps, m->info.n_ctx); return SPYB_FAIL; }
+    if (first_token < 0 || first_token >= m->info.n_vocab) { be->set_error("token id %d out of range", first_token); return SPYB_FAIL; }
+    *m->h_pos_pinned = n_past; *m->h_tok_pinned = first_token;
+    SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 4, cudaMemcpyHostToDevice, be->stream));
+    SPYB_CUDA(be, cudaMemcpyAsync(m->d_tokens_in, m->h_tok_pinned, 4, cudaMemcpyHostToDevice, be->stream));
+    SPYB_CUDA(be, launch_embed(m->d_tokens_in, 1, m->embd, m->embd_type, m->info.d_model, m->x, be->stream));
+
+    const bool use_graph = be->config.use_graph != 0 && m->info.tp_size == 1;
+    int64_t per_step = 0;
+    if (use_graph && m->graph_exec == nullptr) {
+        // one decode step captured once; positions and the token live in device memory, so the
+        // same graph replays for every later step
+        cudaGraph_t graph = nullptr;
+        SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+        SPYB_CUDA(be, cudaStreamBeginCapture(be->stream, cudaStreamCaptureModeThreadLocal));
+        int64_t n = 0;
+        const spyb_status st = run_decode_step(m, &n);
+        const cudaError_t ce = cudaStreamEndCapture(be->stream, &graph);
+        if (st != SPYB_SUCCESS || ce != cudaSuccess) {
+            if (graph) { cudaGraphDestroy(graph); }
+            if (st == SPYB_SUCCESS) { be->set_error("CUDA graph capture failed: %s", cudaGetErrorString(ce)); }
+            return SPYB_FAIL;
+        }
+        const cudaError_t ie = cudaGraphInstantiate(&m->graph_exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (ie != cudaSuccess) { m->graph_exec = nullptr; be->set_error("CUDA graph instantiation failed: %s", cudaGetErrorString(ie)); return SPYB_FAIL; }
+    }
+    per_step = (int64_t)m->layers.size() * 5 + 2;
+    SPYB_CUDA(be, cudaEventRecord(m->ev0, be->stream));
+    for (int s = 0; s < n_steps; ++s) {
+        if (use_graph) { SPYB_CUDA(be, cudaGraphLaunch(m->graph_exec, be->stream)); }
+        else { int64_t n = 0; if (run_decode_step(m, &n) != SPYB_SUCCESS) { return SPYB_FAIL; } per_step = n; }
+        if (logits_host != nullptr) {
+            // parity mode: logits of every step come back (argmax_embed does not modify them)
+            SPYB_CUDA(be, cudaMemcpyAsync(logits_host + (size_t)s * m->info.n_vocab, m->logits, (size_t)m->info.n_vocab * 4, cudaMemcpyDeviceToHost, be->stream));
+            SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+        }
+    }
+    SPYB_CUDA(be, cudaEventRecord(m->ev1, be->stream));
+    SPYB_CUDA(be, cudaMemcpyAsync(ids_host, m->d_history + n_past, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, be->stream));
+    SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+    SPYB_CUDA(be, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+    m->last_launches = per_step * n_steps;
+    return SPYB_SUCCESS;
+}
+
+float spyb_model_bench_kernel(spyb_model *m, int32_t kind, int32_t sweeps, uint64_t *bytes_per_launch) {
+    if (m == nullptr || kind < 0 || kind > 4 || sweeps < 1) { return -1.f; }
+    spyb_backend *be = m->be;
+    cudaSetDevice(be->config.device_id);
+    const LaunchCfg cfg = be->launch_cfg(false);
+    const int d = m->info.d_model;
+    *m->h_pos_pinned = m->info.n_ctx - 1;
+    if (cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 4, cudaMemcpyHostToDevice, be->stream) != cudaSuccess) { return -1.f; }
+    auto params = [&](const Layer &ly) {
+        MatvecParams p; p.T = 1;
+        switch (kind) {
+        case 0: p.A = ly.wqkv; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.attn_norm; p.eps = m->info.rms_eps;
+                p.epi = EPI_QKV_ROPE; p.pos_base = m->d_pos; p.rope_table = m->rope_table; p.hd = m->info.head_dim; p.dl = m->dl;
+                p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache; break;
+        case 1: p.A = ly.wo; p.pro = PRO_QUANT; p.x = m->att; p.x_stride = m->dl; p.epi = EPI_STORE; p.out = m->partial; p.out_stride = d; break;
+        case 2: p.A = ly.up; p.B = ly.gate; p.pair_mode = 1; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
+                p.eps = m->info.rms_eps; p.epi = EPI_SILU_MUL; p.out = m->act; p.out_stride = m->fl; p.silu_table = be->d_silu_table; break;
+        case 3: p.A = ly.down; p.pro = PRO_QUANT; p.x = m->act; p.x_stride = m->fl; p.epi = EPI_STORE; p.out = m->partial; p.out_stride = d; break;
+        default: p.A = m->head; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = m->output_norm; p.eps = m->info.rms_eps;
+                p.epi = EPI_STORE; p.out = m->logits; p.out_stride = m->info.n_vocab; break;
+        }
+        return p;
+    };
+    const MatvecParams p0 = params(m->layers[0]);
+    if (bytes_per_launch) { *bytes_per_launch = p0.A.bytes() + (p0.pair_mode ? p0.B.bytes() : 0); }
+    float total_ms = 0.f; int64_t n = 0;
+    if (kind == 4) {
+        // a single 70 MB matrix would stay in the 126 MB L2 between launches: evict it with a 512 MB memset each time
+        void *flush = nullptr;
+        if (cudaMalloc(&flush, (size_t)512 << 20) != cudaSuccess) { return -1.f; }
+        for (int s = 0; s < sweeps * 4; ++s) {
+            cudaMemsetAsync(flush, s, (size_t)512 << 20, be->stream);
+            cudaEventRecord(m->ev0, be->stream);
+            if (launch_matvec(p0, cfg) != cudaSuccess) { cudaFree(flush); return -1.f; }
+            cudaEventRecord(m->ev1, be->stream);
+            cudaStreamSynchronize(be->stream);
+            float ms = 0.f; cudaEventElapsedTime(&ms, m->ev0, m->ev1);
+            total_ms += ms; ++n;
+        }
+        cudaFree(flush);
+    } else {
+        cudaEventRecord(m->ev0, be->stream);
+        for (int s = 0; s < sweeps; ++s) {
+            for (const Layer &ly : m->layers) { if (launch_matvec(params(ly), cfg) != cudaSuccess) { return -1.f; } ++n; }
+        }
+        cudaEventRecord(m->ev1, be->stream);
+        if (cudaStreamSynchronize(be->stream) != cudaSuccess) { return -1.f; }
+        cudaEventElapsedTime(&total_ms, m->ev0, m->ev1);
+    }
+    return n ? total_ms / (float)n : -1.f;
+}
+
+float   spyb_model_last_ms(const spyb_model *m) { return m ? m->last_ms : 0.f; }
+int64_t spyb_model_last_launches(const spyb_model *m) { return m ? m->last_launches : 0; }
+
+spyb_status spyb_model_tap_xq(spyb_model *m, void *blocks_host) {
+    if (m == nullptr || blocks_host == nullptr) { return SPYB_FAIL; }
+    SPYB_CUDA(m->be, cudaMemcpy(blocks_host, m->d_tap, (size_t)m->info.d_model / 32 * 34, cudaMemcpyDeviceToHost));
+    return SPYB_SUCCESS;
+}
+
+}  // extern "C"

@@ -1,0 +1,301 @@
+"""GPU: every kernel of the per-operator path through the C ABI against the CPU oracle.
+Integer and byte results must be identical; f32 results differ only by summation order."""
+import ctypes as C
+import os
+
+import numpy as np
+import pytest
+
+from spy_b200 import backend as B
+from spy_b200 import quants
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.fixture(scope="module")
+def be():
+    b = B.B200Backend(0)
+    yield b
+    b.close()
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+def close(got, want, rel=2e-5):
+    scale = max(1e-6, float(np.abs(want).max()))
+    return float(np.abs(got - want).max()) <= rel * scale
+
+
+def run(be, op, inputs, out_ne, out_type=B.FP32, host_out=False, **params):
+    """inputs: list of (np array, number_type, ne, nb or None, node_type). Returns the f32/u16 output array."""
+    d = B.OpDesc()
+    d.op_type, d.num_input = B.OP[op], len(inputs)
+    dev = []
+    for i, (a, nt, ne, nb, node) in enumerate(inputs):
+        if node == B.NODE_IO:
+            a = np.ascontiguousarray(a)
+            ptr = a.ctypes.data
+            dev.append((None, a))
+        else:
+            ptr = be.upload(a)
+            dev.append((ptr, a))
+        d.input[i] = B.make_tensor(ptr, nt, ne, nb, node)
+    esz = 4 if out_type in (B.FP32, B.INT32) else 2
+    n_out = int(np.prod(out_ne))
+    host_buf = np.zeros(n_out, dtype=np.float32 if esz == 4 else np.uint16)
+    if op == "Copy":
+        d.output = B.make_tensor(None, out_type, out_ne)
+    elif host_out:
+        d.output = B.make_tensor(host_buf.ctypes.data, out_type, out_ne, None, B.NODE_IO)
+    else:
+        po = be.alloc_memory(max(1, n_out * esz))
+        d.output = B.make_tensor(po, out_type, out_ne)
+    d.softmax_scale = params.get("scale", 0.0)
+    d.norm_eps = params.get("eps", 0.0)
+    d.view_offset = params.get("offset", 0)
+    if op == "Rope":
+        r = d.rope
+        r.mode, r.num_dim, r.num_context, r.num_origin_context = 0, params["n_dim"], 512, 4096
+        r.freq_base, r.freq_scale, r.extend_factor, r.attention_factor, r.beta_fast, r.beta_slow = 10000.0, 1.0, 0.0, 1.0, 32.0, 1.0
+    be.submit(d)
+    be.sync()
+    if op == "Copy":
+        return d
+    if host_out:
+        res = host_buf
+    else:
+        res = be.download(d.output.data, (n_out,), np.float32 if esz == 4 else np.uint16)
+        be.dealloc_memory(d.output.data, max(1, n_out * esz))
+    for ptr, a in dev:
+        if ptr:
+            be.dealloc_memory(ptr, max(1, a.nbytes))
+    return res
+
+
+# ----------------------------------------------------------------------------- exact arithmetic
+def test_q8_quantizer_bytes_golden(be):
+    g = np.load(os.path.join(GOLD, "ops_reference.npz"))
+    assert np.array_equal(be.quantize_q8_0(g["q8_x"]), g["q8_blocks"])
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_q8_quantizer_bytes_random(be, oracle, seed):
+    rng = np.random.default_rng(seed)
+    x = (rng.standard_normal(32 * 4096) * rng.choice([1e-6, 1e-2, 1.0, 1e3], size=32 * 4096)).astype(np.float32)
+    x[:64] = 0.0
+    x[64:96] = np.arange(32) * 0.5
+    assert np.array_equal(be.quantize_q8_0(x), oracle.quantize_q8_0(x))
+
+
+def test_q8_quantizer_empty(be):
+    assert be.quantize_q8_0(np.zeros(0, dtype=np.float32)).size == 0
+
+
+@pytest.mark.parametrize("qt", [quants.Q4_0, quants.Q8_0])
+@pytest.mark.parametrize("k", [32, 4096, 11008])
+def test_integer_block_dots_identical(be, oracle, qt, k):
+    rng = np.random.default_rng(k + qt)
+    w = quants.quantize((rng.standard_normal((1, k)) * 0.02).astype(np.float32), qt)[0]
+    xq = oracle.quantize_q8_0(rng.standard_normal(k).astype(np.float32))
+    assert np.array_equal(be.block_dots(qt, w, xq, k), oracle.blockdots(qt, w, xq))
+
+
+def test_block_dots_extreme_values(be, oracle):
+    k = 64
+    w = np.zeros(k // 32 * 18, dtype=np.uint8)
+    w[0:2] = np.frombuffer(np.float16(1.0).tobytes(), dtype=np.uint8)
+    w[2:18] = 0xFF; w[18:20] = w[0:2]; w[20:36] = 0x00          # all nibbles 15, then all 0 (i.e. -8)
+    xq = np.zeros(k // 32 * 34, dtype=np.uint8)
+    xq[0:2] = w[0:2]; xq[2:34] = 127; xq[34:36] = w[0:2]; xq[36:68] = 128   # int8 127 and -128
+    assert np.array_equal(be.block_dots(quants.Q4_0, w, xq, k), oracle.blockdots(quants.Q4_0, w, xq))
+
+
+# ----------------------------------------------------------------------------- MatMul
+SHAPES = [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)]   # (rows N, inner K)
+
+
+@pytest.mark.parametrize("qt", [quants.Q4_0, quants.Q8_0])
+@pytest.mark.parametrize("n,k", [(64, 256), (130, 1024), (2, 32)])
+@pytest.mark.parametrize("t", [1, 3, 8, 11])
+def test_matmul_small_shapes(be, oracle, qt, n, k, t):
+    rng = np.random.default_rng(n * k + t)
+    w = quants.quantize((rng.standard_normal((n, k)) * 0.02).astype(np.float32), qt)
+    x = rng.standard_normal((t, k)).astype(np.float32)
+    got = run(be, "MatMul", [(w, qt, (k, n), None, B.NODE_CONSTANT), (x, B.FP32, (k, t), None, B.NODE_DYNAMIC)], (n, t)).reshape(t, n)
+    want = oracle.matmul(qt, w, k, n, x)
+    assert close(got, want)
+
+
+@pytest.mark.parametrize("qt", [quants.Q4_0, quants.Q8_0])
+@pytest.mark.parametrize("n,k", SHAPES)
+@pytest.mark.parametrize("t", [1, 4, 16])
+def test_matmul_operator_sweep(be, oracle, qt, n, k, t):
+    """BASELINE operator sweep: weights N(0, 0.02), activations N(0, 1); the oracle checks a row sample."""
+    rng = np.random.default_rng(99)
+    w = quants.quantize((rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)), qt)
+    x = rng.standard_normal((t, k)).astype(np.float32)
+    pw = be.upload_constant(f"sweep_{qt}_{n}_{k}", w, qt, (k, n))
+    d = B.OpDesc(); d.op_type, d.num_input = B.OP["MatMul"], 2
+    px = be.upload(x); po = be.alloc_memory(n * t * 4)
+    d.input[0] = B.make_tensor(pw, qt, (k, n), None, B.NODE_CONSTANT)
+    d.input[1] = B.make_tensor(px, B.FP32, (k, t))
+    d.output = B.make_tensor(po, B.FP32, (n, t))
+    be.submit(d); be.sync()
+    got = be.download(po, (t, n), np.float32)
+    be.dealloc_memory(px, x.nbytes); be.dealloc_memory(po, n * t * 4)
+    rows = np.unique(np.concatenate([[0, 1, n - 2, n - 1], rng.integers(0, n, size=60)]))
+    want = oracle.matmul(qt, np.ascontiguousarray(w[rows]), k, len(rows), x)
+    assert close(got[:, rows], want)
+    assert np.isfinite(got).all()
+
+
+def test_matmul_linearity_full_size(be):
+    """Size-independent property at the 7B head shape: W(2x) == 2 W(x) exactly (power-of-two scaling commutes with Q8_0)."""
+    rng = np.random.default_rng(5)
+    n, k = 32000, 4096
+    w = quants.quantize((rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)), quants.Q4_0)
+    pw = be.upload_constant("lin_head", w, quants.Q4_0, (k, n))
+    x = rng.standard_normal((1, k)).astype(np.float32)
+    outs = [_mm(be, pw, quants.Q4_0, n, k, xx) for xx in (x, 2 * x)]
+    assert np.array_equal(bits(outs[1]), bits(2 * outs[0]))
+
+
+def _mm(be, pw, qt, n, k, x):
+    t = x.shape[0]
+    d = B.OpDesc(); d.op_type, d.num_input = B.OP["MatMul"], 2
+    px = be.upload(x); po = be.alloc_memory(n * t * 4)
+    d.input[0] = B.make_tensor(pw, qt, (k, n), None, B.NODE_CONSTANT)
+    d.input[1] = B.make_tensor(px, B.FP32, (k, t))
+    d.output = B.make_tensor(po, B.FP32, (n, t))
+    be.submit(d); be.sync()
+    got = be.download(po, (t, n), np.float32)
+    be.dealloc_memory(px, x.nbytes); be.dealloc_memory(po, n * t * 4)
+    return got
+
+
+def test_matmul_unsupported_weight_type_is_reported(be):
+    d = B.OpDesc(); d.op_type, d.num_input = B.OP["MatMul"], 2
+    p = be.alloc_memory(144 * 4)
+    d.input[0] = B.make_tensor(p, B.Q4_K, (256, 4)); d.input[1] = B.make_tensor(p, B.FP32, (256, 1)); d.output = B.make_tensor(p, B.FP32, (4, 1))
+    with pytest.raises(B.SpybError) as e:
+        be.submit(d)
+    assert e.value.status == B.UNSUPPORTED
+
+
+# ----------------------------------------------------------------------------- the small operators
+def test_rmsnorm_mul_add_silu(be, oracle):
+    rng = np.random.default_rng(3)
+    x = rng.standard_normal((3, 4096)).astype(np.float32)
+    w = rng.standard_normal(4096).astype(np.float32)
+    got = run(be, "NormRMS", [(x, B.FP32, (4096, 3), None, B.NODE_DYNAMIC)], (4096, 3), eps=1e-5).reshape(3, 4096)
+    assert close(got, oracle.rmsnorm(x, 1e-5), rel=5e-6)
+    got = run(be, "Mul", [(x, B.FP32, (4096, 3), None, B.NODE_DYNAMIC), (w, B.FP32, (4096,), None, B.NODE_CONSTANT)], (4096, 3)).reshape(3, 4096)
+    assert np.array_equal(bits(got), bits(oracle.mul_rows(x, w)))
+    y = rng.standard_normal((3, 4096)).astype(np.float32)
+    got = run(be, "Add", [(x, B.FP32, (4096, 3), None, B.NODE_DYNAMIC), (y, B.FP32, (4096, 3), None, B.NODE_DYNAMIC)], (4096, 3)).reshape(3, 4096)
+    assert np.array_equal(bits(got), bits(x + y))
+    g = (rng.standard_normal(11008) * 4).astype(np.float32)
+    got = run(be, "Silu", [(g, B.FP32, (11008,), None, B.NODE_DYNAMIC)], (11008,))
+    assert np.array_equal(bits(got), bits(oracle.silu(g)))   # table built with the same libm: identical bits
+
+
+def test_silu_golden(be):
+    g = np.load(os.path.join(GOLD, "ops_reference.npz"))
+    got = run(be, "Silu", [(g["silu_x"], B.FP32, (2048,), None, B.NODE_DYNAMIC)], (2048,))
+    assert np.array_equal(bits(got), bits(g["silu_out"]))
+
+
+def test_softmax_masked_with_host_mask(be, oracle):
+    rng = np.random.default_rng(4)
+    n_ctx, n_kv, heads = 64, 37, 3
+    sc = (rng.standard_normal((heads, 1, n_kv)) * 3).astype(np.float32)
+    mask = np.full((1, n_ctx), -np.inf, dtype=np.float32); mask[0, : n_kv - 2] = 0
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(128.0)))
+    got = run(be, "Softmax", [(sc, B.FP32, (n_kv, 1, heads), None, B.NODE_DYNAMIC), (mask, B.INT32, (n_ctx, 1), None, B.NODE_IO)],
+              (n_kv, 1, heads), scale=scale).reshape(heads, n_kv)
+    for h in range(heads):
+        want = oracle.softmax_masked(sc[h, 0], mask[0, :n_kv], scale)
+        assert close(got[h], want, rel=2e-6)
+        assert np.all(got[h][n_kv - 2:] == 0)
+
+
+def test_rope_with_host_positions(be, oracle):
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal((3, 4, 128)).astype(np.float32)
+    pos = np.array([0, 17, 511], dtype=np.int32)
+    got = run(be, "Rope", [(x, B.FP32, (128, 4, 3), None, B.NODE_DYNAMIC), (pos, B.INT32, (3,), None, B.NODE_IO)], (128, 4, 3), n_dim=128).reshape(3, 4, 128)
+    assert float(np.abs(got - oracle.rope(x, pos, 10000.0)).max()) <= 2e-5
+
+
+def test_getrow_f32_and_q8_0(be, oracle):
+    rng = np.random.default_rng(7)
+    table = rng.standard_normal((50, 256)).astype(np.float32)
+    ids = np.array([3, 49, 0, 3], dtype=np.int32)
+    got = run(be, "GetRow", [(table, B.FP32, (256, 50), None, B.NODE_CONSTANT), (ids, B.INT32, (4,), None, B.NODE_IO)], (256, 4)).reshape(4, 256)
+    assert np.array_equal(bits(got), bits(table[ids]))
+    tq = quants.quantize(table, quants.Q8_0)
+    got = run(be, "GetRow", [(tq, B.Q8_0, (256, 50), None, B.NODE_CONSTANT), (ids, B.INT32, (4,), None, B.NODE_IO)], (256, 4)).reshape(4, 256)
+    assert np.array_equal(bits(got), bits(quants.dequantize(tq, quants.Q8_0)[ids]))
+
+
+def test_copy_into_strided_f16_cache_and_view(be, oracle):
+    """KV append as the graph does it: View at a byte offset, Copy f32 -> f16 into a transposed destination."""
+    rng = np.random.default_rng(8)
+    n_ctx, d, t, past = 16, 64, 3, 5
+    v = rng.standard_normal((t, d)).astype(np.float32)
+    cache = np.zeros(d * n_ctx, dtype=np.uint16)
+    pc = be.upload(cache)
+    vd = B.OpDesc(); vd.op_type, vd.num_input = B.OP["View"], 1
+    vd.input[0] = B.make_tensor(pc, B.FP16, (d * n_ctx,)); vd.output = B.make_tensor(None, B.FP16, (t, d), (2, 2 * n_ctx)); vd.view_offset = 2 * past
+    be.submit(vd)
+    assert vd.output.data == pc + 2 * past
+    # source = V transposed view of [d, t] f32: elements (t, d), strides (d*4, 4)
+    pv = be.upload(v)
+    cd = B.OpDesc(); cd.op_type, cd.num_input = B.OP["Copy"], 2
+    cd.input[0] = B.make_tensor(pv, B.FP32, (t, d), (4 * d, 4)); cd.input[1] = vd.output; cd.output = B.make_tensor(None, B.FP16, (t, d))
+    be.submit(cd); be.sync()
+    assert cd.output.data == vd.output.data
+    got = be.download(pc, (d, n_ctx), np.uint16)
+    want = np.zeros((d, n_ctx), dtype=np.uint16)
+    want[:, past:past + t] = oracle.quantize_f16(v).reshape(t, d).T
+    assert np.array_equal(got, want)
+
+
+def test_matmul_f16_strided_scores(be, oracle):
+    """attn_score as the graph issues it: K view [hd, n_kv, H] with strides (2, d*2, hd*2) times Q [hd, 1, H] f32."""
+    rng = np.random.default_rng(9)
+    hd, heads, n_kv = 128, 2, 9
+    d = hd * heads
+    kc = oracle.quantize_f16(rng.standard_normal(n_kv * d).astype(np.float32))
+    q = rng.standard_normal((heads, 1, hd)).astype(np.float32)
+    got = run(be, "MatMul", [(kc, B.FP16, (hd, n_kv, heads), (2, d * 2, hd * 2), B.NODE_CACHE), (q, B.FP32, (hd, 1, heads), None, B.NODE_DYNAMIC)],
+              (n_kv, 1, heads)).reshape(heads, n_kv)
+    k2 = kc.reshape(n_kv, heads, hd)
+    for h in range(heads):
+        qh = oracle.quantize_f16(q[h, 0])
+        want = np.array([oracle.dot("f16_f16", np.ascontiguousarray(k2[j, h]), qh, hd) for j in range(n_kv)], dtype=np.float32)
+        assert close(got[h], want, rel=2e-6)
+
+
+def test_alloc_free_reuse_and_callback(be):
+    a = be.alloc_memory(1000); b = be.alloc_memory(5000)
+    assert a % 256 == 0 and b % 256 == 0 and a != b
+    be.dealloc_memory(a, 1000)
+    assert be.alloc_memory(900) == a
+    fired = []
+    x = np.ones(64, dtype=np.float32)
+    d = B.OpDesc(); d.op_type, d.num_input = B.OP["Silu"], 1
+    px = be.upload(x); po = be.alloc_memory(256)
+    d.input[0] = B.make_tensor(px, B.FP32, (64,)); d.output = B.make_tensor(po, B.FP32, (64,))
+    be.submit(d, callback=lambda: fired.append(1))
+    import time
+    for _ in range(200):
+        if fired:
+            break
+        time.sleep(0.01)
+    assert fired == [1]
+    be.sync()
+    assert be.get_max_memory_capacity() > 100 << 30 and be.get_avail_memory_capacity() > 0
