@@ -176,6 +176,11 @@ int64_t spyb_model_last_launches(const spyb_model *model);
  * the KV cache below position n_ctx-1 and the residual stream are left untouched. No reference counterpart
  * (the reference times whole steps only, util/include/util/timer.h:51-80). */
 float spyb_model_bench_kernel(spyb_model *model, int32_t kind, int32_t sweeps, uint64_t *bytes_per_launch);
+/* Parity tap: copies one activation buffer of the last pass (up to 8 token columns) to the host:
+ * which 0 = Q after RoPE as fp16 [T][d_local], 1 = attention output f32 [T][d_local], 2 = residual stream f32 [T][d_model],
+ * 3 = up*silu(gate) f32 [T][ff_local], 4 = logits f32 [n_vocab]; the layer buffers hold the LAST layer's values.
+ * Stands in for reading Dynamic tensors of the reference graph (orchestration/include/graph/data_node.h:38-73). */
+spyb_status spyb_model_read_activation(spyb_model *model, int32_t which, void *host, uint64_t bytes);
 /* taps for parity tests: copy the Q8_0 blocks of layer-0's attention-norm output of the last eval
  * (d_model/32 * 34 bytes, reference layout) to host */
 spyb_status spyb_model_tap_xq(spyb_model *model, void *blocks_host);

@@ -406,6 +406,11 @@ oracle_state *oracle_state_new(const oracle_model *m) {
 }
 void oracle_state_free(oracle_state *s) { if (s) { free(s->k_cache); free(s->v_cache); free(s); } }
 
+/* Optional debugging tap: when set, oracle_eval stores, for layer 0 and the last token of the call,
+ * [q after rope (d) | attention output (d) | x after the attention residual (d) | up*silu(gate) (F) | x after the FFN residual (d)]. */
+static float *g_debug_tap = NULL;
+void oracle_set_debug_tap(float *buf) { g_debug_tap = buf; }
+
 /* One execution of the graph LLAMAModel::build_graph emits (model/src/llm/model/llama.cpp:123-222,
  * plugin/attention.cpp:267-302, plugin/ffn.cpp:5-42, plugin/inout.cpp:5-78) for `t` tokens at
  * positions n_past .. n_past+t-1. logits: [t][n_vocab]. Optional taps (may be NULL):
@@ -452,7 +457,8 @@ int oracle_eval(const oracle_model *m, oracle_state *st, const int32_t *tokens, 
         uint16_t *vc = st->v_cache + (size_t)L * C * d;
         oracle_rmsnorm(x, d, t, m->rms_eps, tmp);
         oracle_mul_rows(tmp, m->attn_norm[L], d, t, xn);
-        rc |= oracle_matmul(m->t_wq[L], m->wq[L], d, d, xn, t, q, (L == 0) ? tap_xq : NULL);
+        if (L == 0 && tap_xq) { oracle_quantize_q8_0(xn, d, tap_xq); }   /* token 0 only */
+        rc |= oracle_matmul(m->t_wq[L], m->wq[L], d, d, xn, t, q, NULL);
         rc |= oracle_matmul(m->t_wk[L], m->wk[L], d, d, xn, t, k, NULL);
         rc |= oracle_matmul(m->t_wv[L], m->wv[L], d, d, xn, t, v, NULL);
         if (rc) { goto done; }
@@ -479,6 +485,11 @@ int oracle_eval(const oracle_model *m, oracle_state *st, const int32_t *tokens, 
         }
         rc |= oracle_matmul(m->t_wo[L], m->wo[L], d, d, att, t, tmp, NULL);
         oracle_add(tmp, x, t * d, x);                       /* ffn_input = attn_out + x, llama.cpp:194-197 */
+        if (g_debug_tap && L == 0) {
+            memcpy(g_debug_tap, q + (t - 1) * d, (size_t)d * 4);
+            memcpy(g_debug_tap + d, att + (t - 1) * d, (size_t)d * 4);
+            memcpy(g_debug_tap + 2 * d, x + (t - 1) * d, (size_t)d * 4);
+        }
         oracle_rmsnorm(x, d, t, m->rms_eps, tmp);
         oracle_mul_rows(tmp, m->ffn_norm[L], d, t, xn);
         rc |= oracle_matmul(m->t_up[L], m->w_up[L], d, F, xn, t, up, NULL);
@@ -486,7 +497,9 @@ int oracle_eval(const oracle_model *m, oracle_state *st, const int32_t *tokens, 
         oracle_silu(gate, t * F, gate);
         oracle_mul(up, gate, t * F, up);                    /* ffn_par = up * silu(gate), ffn.cpp:32-35 */
         rc |= oracle_matmul(m->t_down[L], m->w_down[L], F, d, up, t, tmp, NULL);
+        if (g_debug_tap && L == 0) { memcpy(g_debug_tap + 3 * d, up + (t - 1) * F, (size_t)F * 4); }
         oracle_add(x, tmp, t * d, x);                       /* llama.cpp:206-211 */
+        if (g_debug_tap && L == 0) { memcpy(g_debug_tap + 3 * d + F, x + (t - 1) * d, (size_t)d * 4); }
         if (rc) { goto done; }
     }
     oracle_rmsnorm(x, d, t, m->rms_eps, tmp);

@@ -354,27 +354,39 @@ spyb_status run_matmul(spyb_backend *be, spyb_op_desc *d, void *out_dev) {
         return SPYB_UNSUPPORTED;
     }
     DevMatrix m;
+    bool found = false;
+    void *tmp_qa = nullptr, *tmp_qb = nullptr, *tmp_d = nullptr;
+    const size_t nblk = (size_t)w.elements[1] * (size_t)(w.elements[0] / QK);
     {
         std::lock_guard<std::mutex> g(be->const_mutex);
         auto it = be->retiled.find(w.data);
-        if (it == be->retiled.end()) {
-            // a quantized weight that did not come through spyb_upload_constant: re-tile it once and remember it
-            const int64_t bb = w.number_type == SPYB_Q4_0 ? 18 : 34;
-            if (alloc_matrix(be, w.number_type, w.elements[1], (int)(w.elements[0] / QK), &m) != SPYB_SUCCESS) { return SPYB_FAIL; }
-            cudaError_t err = w.number_type == SPYB_Q4_0
-                ? launch_retile_q4_0(static_cast<const uint8_t *>(w.data), w.elements[0] / QK * bb, w.elements[1], m.nb, const_cast<uint4 *>(m.qa), const_cast<uint16_t *>(m.d), be->stream)
-                : launch_retile_q8_0(static_cast<const uint8_t *>(w.data), w.elements[0] / QK * bb, w.elements[1], m.nb, const_cast<uint4 *>(m.qa), const_cast<uint4 *>(m.qb), const_cast<uint16_t *>(m.d), be->stream);
-            if (err != cudaSuccess) { be->set_error("MatMul: re-tiling failed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
-            be->retiled[w.data] = m;
-        } else {
-            m = it->second;
-        }
+        if (it != be->retiled.end() && w.node_type == SPYB_NODE_CONSTANT) { m = it->second; found = true; }
     }
-    if (m.k != x.elements[0] || (m.n_rows & 1)) { be->set_error("MatMul: shape mismatch or odd row count"); return SPYB_FAIL; }
+    if (!found) {
+        // a quantized operand that did not come through spyb_upload_constant (its address may be reused for other
+        // data later, so nothing is cached): re-tile into planes that live for this operator only
+        const int64_t bb = w.number_type == SPYB_Q4_0 ? 18 : 34;
+        m.type = w.number_type; m.n_rows = w.elements[1]; m.nb = (int)(w.elements[0] / QK); m.k = w.elements[0];
+        tmp_qa = be->arena.alloc(nblk * 16 + 16); tmp_d = be->arena.alloc(nblk * 2 + 16);
+        if (w.number_type == SPYB_Q8_0) { tmp_qb = be->arena.alloc(nblk * 16 + 16); }
+        if (!tmp_qa || !tmp_d || (w.number_type == SPYB_Q8_0 && !tmp_qb)) { be->set_error("MatMul: out of device memory for re-tiled weights"); return SPYB_FAIL; }
+        m.qa = static_cast<const uint4 *>(tmp_qa); m.qb = static_cast<const uint4 *>(tmp_qb); m.d = static_cast<const uint16_t *>(tmp_d);
+        cudaError_t err = w.number_type == SPYB_Q4_0
+            ? launch_retile_q4_0(static_cast<const uint8_t *>(w.data), w.elements[0] / QK * bb, w.elements[1], m.nb, static_cast<uint4 *>(tmp_qa), static_cast<uint16_t *>(tmp_d), be->stream)
+            : launch_retile_q8_0(static_cast<const uint8_t *>(w.data), w.elements[0] / QK * bb, w.elements[1], m.nb, static_cast<uint4 *>(tmp_qa), static_cast<uint4 *>(tmp_qb), static_cast<uint16_t *>(tmp_d), be->stream);
+        if (err != cudaSuccess) { be->set_error("MatMul: re-tiling failed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
+    }
+    struct TmpRelease {   // stream-ordered reuse: safe to hand back as soon as the kernels are enqueued
+        spyb_backend *be; void *a, *b, *c; size_t n;
+        ~TmpRelease() { if (a) { be->arena.free(a, n * 16 + 16); } if (b) { be->arena.free(b, n * 16 + 16); } if (c) { be->arena.free(c, n * 2 + 16); } }
+    } release{be, tmp_qa, tmp_qb, tmp_d, nblk};
+    if (m.k != x.elements[0]) { be->set_error("MatMul: inner dimensions differ"); return SPYB_FAIL; }
+    if (m.n_rows & 3) { be->set_error("MatMul: %lld output rows (quantized weights need a multiple of 4)", (long long)m.n_rows); return SPYB_UNSUPPORTED; }
     const int64_t T = x.elements[1] * x.elements[2] * x.elements[3];
-    for (int64_t t0 = 0; t0 < T; t0 += 8) {
+    const int64_t tmax = matvec_max_columns(m.nb);
+    for (int64_t t0 = 0; t0 < T; t0 += tmax) {
         MatvecParams p;
-        p.A = m; p.T = (int)std::min<int64_t>(8, T - t0);
+        p.A = m; p.T = (int)std::min<int64_t>(tmax, T - t0);
         p.pro = PRO_QUANT; p.x = static_cast<const float *>(x.data) + t0 * m.k; p.x_stride = m.k;
         p.epi = EPI_STORE; p.out = static_cast<float *>(out_dev) + t0 * m.n_rows; p.out_stride = m.n_rows;
         SPYB_CUDA(be, launch_matvec(p, be->launch_cfg(false)));
@@ -433,8 +445,26 @@ spyb_status spyb_submit(spyb_backend *be, spyb_op_desc *d, void (*callback)(void
             if (d->rope.mode != 0 || d->rope.extend_factor != 0.f || d->rope.freq_scale != 1.f || d->rope.attention_factor != 1.f) {
                 be->set_error("Rope: only mode Norm with default scaling is implemented"); st = SPYB_UNSUPPORTED; break;
             }
-            err = launch_rope(to_strided(a, a.data), static_cast<const int32_t *>(local.input[1].data), to_strided(local.output, out.dev),
-                              d->rope.freq_base, d->rope.num_dim, be->stream);
+            {
+                // (cos, sin) per (token, pair) with the host libm and the CPU operator's repeated f32 multiplication of theta
+                // (backend/host/operator/non-linear.cpp:282, 300-309), so the rotation is bit-identical to the CPU's
+                const int64_t n_tok = a.elements[2], npair = a.elements[0] / 2;
+                std::vector<int32_t> pos((size_t)n_tok);
+                if (d->input[1].node_type == SPYB_NODE_IO) { std::memcpy(pos.data(), d->input[1].data, (size_t)n_tok * 4); }
+                else if (cudaMemcpyAsync(pos.data(), d->input[1].data, (size_t)n_tok * 4, cudaMemcpyDeviceToHost, be->stream) != cudaSuccess ||
+                         cudaStreamSynchronize(be->stream) != cudaSuccess) { be->set_error("Rope: reading positions failed"); st = SPYB_FAIL; break; }
+                std::vector<float2> tab((size_t)(n_tok * npair));
+                const float theta_scale = std::pow(d->rope.freq_base, -2.0f / (float)d->rope.num_dim);
+                for (int64_t i = 0; i < n_tok; ++i) {
+                    float theta = (float)pos[(size_t)i];
+                    for (int64_t k = 0; k < npair; ++k) { tab[(size_t)(i * npair + k)] = make_float2(std::cos(theta) * 1.0f, std::sin(theta) * 1.0f); theta *= theta_scale; }
+                }
+                void *dtab = be->arena.alloc(tab.size() * sizeof(float2));
+                if (dtab == nullptr) { be->set_error("Rope: out of device memory"); st = SPYB_FAIL; break; }
+                err = cudaMemcpyAsync(dtab, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice, be->stream);
+                if (err == cudaSuccess) { err = launch_rope(to_strided(a, a.data), static_cast<const float2 *>(dtab), to_strided(local.output, out.dev), be->stream); }
+                be->arena.free(dtab, tab.size() * sizeof(float2));
+            }
             break;
         case SPYB_OP_COPY: {   // destination = input[1]; the output aliases it (view.cpp:216-227)
             const spyb_tensor &dst = local.input[1];

@@ -74,59 +74,92 @@ __device__ __forceinline__ uint32_t quantize_q8_lane4(float4 v, uint16_t &d_half
 // ---------------------------------------------------------------------------------------------
 // Activation columns as the mat-vec kernels keep them in shared memory (structure of arrays, so
 // that every lane's 128-bit read is conflict-free): for column t and block b
-//   lo[t][b] = int8 values 0..15 of the block, hi[t][b] = values 16..31,
-//   d[t][b]  = f32 of the fp16-rounded scale, s[t][b] = integer sum of the 32 values.
-// The values are exactly those of the reference's block_q8_0_t (quant.h:124-147), regrouped.
+//   lo[t][b]  = int8 values 0..15 of the block, hi[t][b] = values 16..31,
+//   blo[t][b] = four words MAGIC_I - 8 * (sum of values 4j..4j+3),        j = 0..3
+//   bhi[t][b] = four words MAGIC_I - 128 * (sum of values 16+4j..16+4j+3), j = 0..3
+//   d[t][b]   = f32 of the fp16-rounded scale.
+// The values are exactly those of the reference's block_q8_0_t (quant.h:124-147), regrouped; the two
+// bias planes are only needed for Q4_0 weights (they fold the "- 8" of every nibble and the
+// int -> float conversion into the accumulator operand of the byte dot product, see lanes_q4_0).
+constexpr float    MAGIC_F = 12582912.0f;     // 1.5 * 2^23: int_as_float(MAGIC_I + p) == MAGIC_F + p exactly for |p| < 2^22
+constexpr uint32_t MAGIC_I = 0x4B400000u;
+
 struct ActView {
     uint4 *lo;
     uint4 *hi;
+    int4  *blo;
+    int4  *bhi;
     float *d;
-    int   *s;
     int    nb;  // blocks per column
 };
 
-__host__ __device__ inline size_t act_bytes(int nb, int t) { return (size_t)t * nb * (16 + 16 + 4 + 4); }
+__host__ __device__ inline size_t act_bytes(int nb, int t) { return (size_t)t * nb * (16 + 16 + 16 + 16 + 4); }
 
 __device__ __forceinline__ ActView act_view(void *base, int nb, int t) {
     ActView v;
-    v.lo = reinterpret_cast<uint4 *>(base);
-    v.hi = v.lo + (size_t)t * nb;
-    v.d  = reinterpret_cast<float *>(v.hi + (size_t)t * nb);
-    v.s  = reinterpret_cast<int *>(v.d + (size_t)t * nb);
-    v.nb = nb;
+    v.lo  = reinterpret_cast<uint4 *>(base);
+    v.hi  = v.lo + (size_t)t * nb;
+    v.blo = reinterpret_cast<int4 *>(v.hi + (size_t)t * nb);
+    v.bhi = v.blo + (size_t)t * nb;
+    v.d   = reinterpret_cast<float *>(v.bhi + (size_t)t * nb);
+    v.nb  = nb;
     return v;
 }
 
-// Integer dot of one Q4_0 block (16 bytes of nibbles) with one Q8_0 activation block:
-// sum_k (nibble_k - 8) * y_k, Dot<Q4_0,Q8_0>::exec (backend/host/include/simd/vec_dot.h:58-75).
-// Low nibbles pair with y[0..15], high nibbles with y[16..31]. Computed as
-// sum nibble*y - 8*sum(y) with four-way byte dot products; exact in int32.
-__device__ __forceinline__ int dot_q4_0_block(const uint4 w, const uint4 ylo, const uint4 yhi, const int ysum) {
-    int acc = 0;
-    acc = __dp4a((int)(w.x & 0x0f0f0f0fu), (int)ylo.x, acc);
-    acc = __dp4a((int)((w.x >> 4) & 0x0f0f0f0fu), (int)yhi.x, acc);
-    acc = __dp4a((int)(w.y & 0x0f0f0f0fu), (int)ylo.y, acc);
-    acc = __dp4a((int)((w.y >> 4) & 0x0f0f0f0fu), (int)yhi.y, acc);
-    acc = __dp4a((int)(w.z & 0x0f0f0f0fu), (int)ylo.z, acc);
-    acc = __dp4a((int)((w.z >> 4) & 0x0f0f0f0fu), (int)yhi.z, acc);
-    acc = __dp4a((int)(w.w & 0x0f0f0f0fu), (int)ylo.w, acc);
-    acc = __dp4a((int)((w.w >> 4) & 0x0f0f0f0fu), (int)yhi.w, acc);
-    return acc - 8 * ysum;
+__device__ __forceinline__ int dp4a_us(uint32_t a_unsigned, uint32_t b_signed, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_unsigned), "r"(b_signed), "r"(c));
+    return d;
 }
 
-// Integer dot of one Q8_0 block (two 16-byte halves) with one Q8_0 activation block,
-// Dot<Q8_0,Q8_0>::exec (vec_dot.h:103-113).
-__device__ __forceinline__ int dot_q8_0_block(const uint4 wa, const uint4 wb, const uint4 ylo, const uint4 yhi) {
-    int acc = 0;
-    acc = __dp4a((int)wa.x, (int)ylo.x, acc);
-    acc = __dp4a((int)wa.y, (int)ylo.y, acc);
-    acc = __dp4a((int)wa.z, (int)ylo.z, acc);
-    acc = __dp4a((int)wa.w, (int)ylo.w, acc);
-    acc = __dp4a((int)wb.x, (int)yhi.x, acc);
-    acc = __dp4a((int)wb.y, (int)yhi.y, acc);
-    acc = __dp4a((int)wb.z, (int)yhi.z, acc);
-    acc = __dp4a((int)wb.w, (int)yhi.w, acc);
-    return acc;
+// The eight integer "lane sums" of one Q4_0 block against one Q8_0 activation block, in the order of
+// the reference's 8-wide accumulator (Dot<Q4_0,Q8_0>::exec, backend/host/include/simd/vec_dot.h:58-75
+// with mul_sum_i8_pairs, vec_util.h:100-110): lanes 0..3 = sum over k = 4j..4j+3 of
+// (high nibble_k - 8) * y[16+k], lanes 4..7 = the same with low nibbles and y[k].
+// Returned already as floats: f[0..3] = 16 * lane sum (the high nibbles are used in place, i.e. scaled
+// by 16; the caller multiplies them by scale/16, which is exact), f[4..7] = lane sum.
+__device__ __forceinline__ void lanes_q4_0(const uint4 w, const uint4 ylo, const uint4 yhi, const int4 blo, const int4 bhi, float f[8]) {
+    f[0] = __int_as_float(dp4a_us(w.x & 0xf0f0f0f0u, yhi.x, bhi.x)) - MAGIC_F;
+    f[1] = __int_as_float(dp4a_us(w.y & 0xf0f0f0f0u, yhi.y, bhi.y)) - MAGIC_F;
+    f[2] = __int_as_float(dp4a_us(w.z & 0xf0f0f0f0u, yhi.z, bhi.z)) - MAGIC_F;
+    f[3] = __int_as_float(dp4a_us(w.w & 0xf0f0f0f0u, yhi.w, bhi.w)) - MAGIC_F;
+    f[4] = __int_as_float(dp4a_us(w.x & 0x0f0f0f0fu, ylo.x, blo.x)) - MAGIC_F;
+    f[5] = __int_as_float(dp4a_us(w.y & 0x0f0f0f0fu, ylo.y, blo.y)) - MAGIC_F;
+    f[6] = __int_as_float(dp4a_us(w.z & 0x0f0f0f0fu, ylo.z, blo.z)) - MAGIC_F;
+    f[7] = __int_as_float(dp4a_us(w.w & 0x0f0f0f0fu, ylo.w, blo.w)) - MAGIC_F;
+}
+
+// Lane sums of one Q8_0 block (two 16-byte halves) against one Q8_0 activation block: lane l = sum of
+// products 4l..4l+3 (mul_sum_i8_pairs_float, vec_util.h:112-132; Dot<Q8_0,Q8_0>::exec, vec_dot.h:103-113).
+__device__ __forceinline__ void lanes_q8_0(const uint4 wa, const uint4 wb, const uint4 ylo, const uint4 yhi, float f[8]) {
+    f[0] = __int_as_float(__dp4a((int)wa.x, (int)ylo.x, (int)MAGIC_I)) - MAGIC_F;
+    f[1] = __int_as_float(__dp4a((int)wa.y, (int)ylo.y, (int)MAGIC_I)) - MAGIC_F;
+    f[2] = __int_as_float(__dp4a((int)wa.z, (int)ylo.z, (int)MAGIC_I)) - MAGIC_F;
+    f[3] = __int_as_float(__dp4a((int)wa.w, (int)ylo.w, (int)MAGIC_I)) - MAGIC_F;
+    f[4] = __int_as_float(__dp4a((int)wb.x, (int)yhi.x, (int)MAGIC_I)) - MAGIC_F;
+    f[5] = __int_as_float(__dp4a((int)wb.y, (int)yhi.y, (int)MAGIC_I)) - MAGIC_F;
+    f[6] = __int_as_float(__dp4a((int)wb.z, (int)yhi.z, (int)MAGIC_I)) - MAGIC_F;
+    f[7] = __int_as_float(__dp4a((int)wb.w, (int)yhi.w, (int)MAGIC_I)) - MAGIC_F;
+}
+
+// hsum_float_8 (vec_util.h:74-81) over the 8 consecutive lanes that hold a0..a7:
+// ((a0+a4) + (a2+a6)) + ((a1+a5) + (a3+a7)). Every lane of the group ends with the same bits.
+__device__ __forceinline__ float hsum8_lanes(float v) {
+    v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+    v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+    v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    return v;
+}
+
+// FP16::block_reduce (vec_util.h:61-71) for the 4 x 8 accumulators of Dot<FP16,FP16> held one per lane
+// (lane = 8 * accumulator + element): (s0+s2) + (s1+s3), then lanes l and l+4, then the two hadd steps.
+__device__ __forceinline__ float reduce_f16dot_lanes(float v) {
+    v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 16));
+    v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 8));
+    v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 4));
+    v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 1));
+    v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, 2));
+    return v;
 }
 
 }  // namespace spyb

@@ -51,7 +51,8 @@ struct MatvecParams {
     int           dl = 0;
     __half       *q_out = nullptr;      // [T][dl]
     __half       *k_cache = nullptr;    // [n_ctx][dl]
-    __half       *v_cache = nullptr;    // [n_ctx][dl]
+    __half       *v_cache = nullptr;    // [dl][n_ctx] (transposed, as the reference keeps it)
+    int           n_ctx = 0;
     // optional tap: reference-layout Q8_0 blocks of column 0 (nb * 34 bytes)
     uint8_t      *tap_xq = nullptr;
 };
@@ -59,15 +60,12 @@ struct MatvecParams {
 struct AttnParams {
     const __half *q = nullptr;        // [T][dl], already rounded to fp16
     const __half *k_cache = nullptr;  // [n_ctx][dl]
-    const __half *v_cache = nullptr;  // [n_ctx][dl]
+    const __half *v_cache = nullptr;  // [dl][n_ctx]
     float        *out = nullptr;      // [T][dl]
     const int    *pos_base = nullptr;
     const float  *exp_table = nullptr;
     int   n_head = 0, hd = 128, dl = 0, T = 1, n_ctx = 0;
-    int   n_split = 1;
     float scale = 0.f;
-    float *scratch = nullptr;         // n_split > 1: [T*n_head][n_split][hd + 2] partials
-    int   *counters = nullptr;        // n_split > 1: [T*n_head], zero before first use; the kernel leaves them zero
 };
 
 struct LaunchCfg {
@@ -77,9 +75,9 @@ struct LaunchCfg {
 };
 
 size_t      matvec_smem_bytes(int nb, int T);
+int         matvec_max_columns(int nb);   // most activation columns one launch can hold in shared memory for rows of nb blocks
 cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg);
 cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg);
-size_t      attention_scratch_floats(int T, int n_head, int n_split, int hd);
 
 // upload-time re-tiling of raw reference-layout blocks into DevMatrix planes
 cudaError_t launch_retile_q4_0(const uint8_t *raw, int64_t row_stride_bytes, int64_t n_rows, int nb, uint4 *qa, uint16_t *d, cudaStream_t s);
@@ -99,7 +97,8 @@ cudaError_t launch_binary_rows(int op /*0 add, 1 mul*/, const float *a, const fl
 cudaError_t launch_silu(const float *x, float *out, int64_t n, const float *silu_table, cudaStream_t s);
 cudaError_t launch_softmax_masked(const float *scores, const float *mask, float *out, int64_t ne0, int64_t ne1, int64_t ne2,
                                   int64_t mask_stride, float scale, const float *exp_table, cudaStream_t s);
-cudaError_t launch_rope(const Strided &x, const int32_t *pos, const Strided &out, float freq_base, int n_dim, cudaStream_t s);
+// cos_sin: device table [ne2 tokens][ne0/2] of (cos, sin) built on the host with the host libm
+cudaError_t launch_rope(const Strided &x, const float2 *cos_sin, const Strided &out, cudaStream_t s);
 cudaError_t launch_copy_strided(const Strided &src, int src_type, const Strided &dst, int dst_type, cudaStream_t s);
 cudaError_t launch_getrow(const uint8_t *table, int table_type, int64_t row_bytes, int64_t ne0, const int32_t *ids, int64_t n_ids, float *out, cudaStream_t s);
 cudaError_t launch_matmul_f16(const Strided &w /*f16*/, const Strided &x /*f32*/, const Strided &out /*f32*/, cudaStream_t s);

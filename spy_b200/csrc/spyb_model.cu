@@ -140,7 +140,7 @@ static NcclApi g_nccl;
 struct Layer {
     DevMatrix wqkv, wo, up, gate, down;
     float    *attn_norm = nullptr, *ffn_norm = nullptr;
-    __half   *k_cache = nullptr, *v_cache = nullptr;   // [n_ctx][dl] each
+    __half   *k_cache = nullptr, *v_cache = nullptr;   // K [n_ctx][dl], V transposed [dl][n_ctx]
 };
 
 }  // namespace spyb
@@ -163,7 +163,6 @@ struct spyb_model {
     int    *d_pos = nullptr;
     int32_t *d_token = nullptr, *d_tokens_in = nullptr, *d_history = nullptr;
     uint8_t *d_tap = nullptr;
-    float  *att_scratch = nullptr; int *att_counters = nullptr; int n_split = 1;
     int    *h_pos_pinned = nullptr; int32_t *h_tok_pinned = nullptr; float *h_logits_pinned = nullptr;
     void   *nccl_comm = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
@@ -206,7 +205,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             MatvecParams p;
             p.A = ly.wqkv; p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.attn_norm; p.eps = m->info.rms_eps;
             p.epi = EPI_QKV_ROPE; p.pos_base = m->d_pos; p.rope_table = m->rope_table; p.hd = m->info.head_dim; p.dl = m->dl;
-            p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache;
+            p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache; p.n_ctx = m->info.n_ctx;
             p.tap_xq = (tap && L == 0) ? m->d_tap : nullptr;
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
         }
@@ -214,8 +213,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             AttnParams a;
             a.q = m->q; a.k_cache = ly.k_cache; a.v_cache = ly.v_cache; a.out = m->att; a.pos_base = m->d_pos; a.exp_table = be->d_exp_table;
             a.n_head = m->dl / m->info.head_dim; a.hd = m->info.head_dim; a.dl = m->dl; a.T = T; a.n_ctx = m->info.n_ctx;
-            a.n_split = m->n_split; a.scale = 1.0f / std::sqrt((float)m->info.head_dim);
-            a.scratch = m->att_scratch; a.counters = m->att_counters;
+            a.scale = 1.0f / std::sqrt((float)m->info.head_dim);
             SPYB_CUDA(be, launch_attention(a, cfg)); ++*launches;
         }
         {   // 3: quantize -> Wo -> + residual (tensor parallel: partial sums, rank 0 carries the residual)
@@ -392,16 +390,13 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         if (dev_alloc(m, &m->rope_table, tab.size()) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
         if (cudaMemcpy(m->rope_table, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice) != cudaSuccess) { be->set_error("rope table upload failed"); return fail(SPYB_FAIL); }
     }
-    m->n_split = I.n_ctx <= 512 ? 1 : std::min(16, (I.n_ctx + 255) / 256);
     const int TMAX = 8;
     bool ok = dev_alloc(m, &m->x, (size_t)TMAX * d) == SPYB_SUCCESS && dev_alloc(m, &m->partial, (size_t)TMAX * d) == SPYB_SUCCESS &&
               dev_alloc(m, &m->att, (size_t)TMAX * dl) == SPYB_SUCCESS && dev_alloc(m, &m->act, (size_t)TMAX * fl) == SPYB_SUCCESS &&
               dev_alloc(m, &m->logits, (size_t)I.n_vocab) == SPYB_SUCCESS && dev_alloc(m, &m->q, (size_t)TMAX * dl) == SPYB_SUCCESS &&
               dev_alloc(m, &m->d_pos, 4) == SPYB_SUCCESS && dev_alloc(m, &m->d_token, 4) == SPYB_SUCCESS &&
               dev_alloc(m, &m->d_tokens_in, TMAX) == SPYB_SUCCESS && dev_alloc(m, &m->d_history, (size_t)I.n_ctx + 8) == SPYB_SUCCESS &&
-              dev_alloc(m, &m->d_tap, (size_t)d / 32 * 34) == SPYB_SUCCESS &&
-              dev_alloc(m, &m->att_scratch, attention_scratch_floats(TMAX, I.n_head / tp, m->n_split, I.head_dim)) == SPYB_SUCCESS &&
-              dev_alloc(m, &m->att_counters, (size_t)TMAX * I.n_head) == SPYB_SUCCESS;
+              dev_alloc(m, &m->d_tap, (size_t)d / 32 * 34) == SPYB_SUCCESS;
     if (!ok) { return fail(SPYB_FAIL); }
     if (cudaMallocHost(reinterpret_cast<void **>(&m->h_pos_pinned), 64) != cudaSuccess ||
         cudaMallocHost(reinterpret_cast<void **>(&m->h_tok_pinned), 64) != cudaSuccess ||
@@ -458,8 +453,9 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
     for (int i = 0; i < n_tokens; ++i) { if (tokens[i] < 0 || tokens[i] >= m->info.n_vocab) { be->set_error("token id %d out of range", tokens[i]); return SPYB_FAIL; } }
     int64_t launches = 0;
     SPYB_CUDA(be, cudaEventRecord(m->ev0, be->stream));
-    for (int t0 = 0; t0 < n_tokens; t0 += 8) {
-        const int T = std::min(8, n_tokens - t0);
+    const int tmax = std::min(8, std::min(matvec_max_columns(m->info.d_model / 32), matvec_max_columns(m->fl / 32)));
+    for (int t0 = 0; t0 < n_tokens; t0 += tmax) {
+        const int T = std::min(tmax, n_tokens - t0);
         SPYB_CUDA(be, cudaStreamSynchronize(be->stream));   // pinned staging words are reused per pass
         *m->h_pos_pinned = n_past + t0;
         std::memcpy(m->h_tok_pinned, tokens + t0, (size_t)T * 4);
@@ -545,7 +541,7 @@ float spyb_model_bench_kernel(spyb_model *m, int32_t kind, int32_t sweeps, uint6
         switch (kind) {
         case 0: p.A = ly.wqkv; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.attn_norm; p.eps = m->info.rms_eps;
                 p.epi = EPI_QKV_ROPE; p.pos_base = m->d_pos; p.rope_table = m->rope_table; p.hd = m->info.head_dim; p.dl = m->dl;
-                p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache; break;
+                p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache; p.n_ctx = m->info.n_ctx; break;
         case 1: p.A = ly.wo; p.pro = PRO_QUANT; p.x = m->att; p.x_stride = m->dl; p.epi = EPI_STORE; p.out = m->partial; p.out_stride = d; break;
         case 2: p.A = ly.up; p.B = ly.gate; p.pair_mode = 1; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
                 p.eps = m->info.rms_eps; p.epi = EPI_SILU_MUL; p.out = m->act; p.out_stride = m->fl; p.silu_table = be->d_silu_table; break;
@@ -586,6 +582,23 @@ float spyb_model_bench_kernel(spyb_model *m, int32_t kind, int32_t sweeps, uint6
 
 float   spyb_model_last_ms(const spyb_model *m) { return m ? m->last_ms : 0.f; }
 int64_t spyb_model_last_launches(const spyb_model *m) { return m ? m->last_launches : 0; }
+
+spyb_status spyb_model_read_activation(spyb_model *m, int32_t which, void *host, uint64_t bytes) {
+    if (m == nullptr || host == nullptr) { return SPYB_FAIL; }
+    const void *src = nullptr; uint64_t avail = 0;
+    switch (which) {
+    case 0: src = m->q;      avail = (uint64_t)8 * m->dl * 2; break;
+    case 1: src = m->att;    avail = (uint64_t)8 * m->dl * 4; break;
+    case 2: src = m->x;      avail = (uint64_t)8 * m->info.d_model * 4; break;
+    case 3: src = m->act;    avail = (uint64_t)8 * m->fl * 4; break;
+    case 4: src = m->logits; avail = (uint64_t)m->info.n_vocab * 4; break;
+    default: m->be->set_error("read_activation: unknown buffer %d", which); return SPYB_FAIL;
+    }
+    if (bytes > avail) { m->be->set_error("read_activation: %llu bytes requested, %llu available", (unsigned long long)bytes, (unsigned long long)avail); return SPYB_FAIL; }
+    SPYB_CUDA(m->be, cudaStreamSynchronize(m->be->stream));
+    SPYB_CUDA(m->be, cudaMemcpy(host, src, bytes, cudaMemcpyDeviceToHost));
+    return SPYB_SUCCESS;
+}
 
 spyb_status spyb_model_tap_xq(spyb_model *m, void *blocks_host) {
     if (m == nullptr || blocks_host == nullptr) { return SPYB_FAIL; }

@@ -1,7 +1,11 @@
-// Attention over the fp16 KV cache (single pass with the reference's exact softmax, or split-K with
-// an online-softmax combine for long contexts), the upload re-tiling kernels, and the small
-// per-operator kernels that let the reference's graph run op by op on the device.
+// Attention over the fp16 KV cache in the reference's exact arithmetic, the upload re-tiling kernels,
+// and the small per-operator kernels that let the reference's graph run op by op on the device.
 // All of these are HBM- or latency-bound byte/float work; none is a dense contraction.
+//
+// Exactness: the reference network quantizes activations at every layer, which amplifies any
+// difference in f32 summation order to percent-level logit differences. Every reduction here therefore
+// follows the CPU's order: the 4 x 8 accumulators and the scalar tail of Dot<FP16,FP16>, the four-wide
+// grouping of std::reduce / std::transform_reduce, and the fixed horizontal-add trees.
 
 #include "spyb_common.cuh"
 #include "spyb_kernels.h"
@@ -12,140 +16,117 @@ namespace spyb {
 
 static inline cudaError_t launch_check() { return cudaGetLastError(); }
 
+// std::reduce over floats as libstdc++ evaluates it for random-access ranges: groups of four combined as
+// (e0 + e1) + (e2 + e3) and added to the running sum one after the other, the remainder one by one.
+// One thread's chain; `v` is in shared memory.
+__device__ __forceinline__ float reduce4_chain(const float *v, int n) {
+    float sum = 0.f;
+    int i = 0;
+    for (; i + 4 <= n; i += 4) { sum = __fadd_rn(sum, __fadd_rn(__fadd_rn(v[i], v[i + 1]), __fadd_rn(v[i + 2], v[i + 3]))); }
+    for (; i < n; ++i) { sum = __fadd_rn(sum, v[i]); }
+    return sum;
+}
+
 // =============================================================================================
-// Attention for one (head, query token, KV split).
+// Attention for one (head, query token): a CTA of 8 warps.
 //   scores = K(f16) . fp16(Q)            MatMul with F16 weights: backend/host/operator/mat.cpp:32-42,
 //                                        Dot<FP16,FP16> backend/host/include/simd/vec_dot.h:117-146
-//   probs  = masked softmax, exp through the table of expf(fp16(s - max))
+//   probs  = masked softmax, exp through the table of expf(fp16(s - max)), std::reduce sum
 //                                        backend/host/operator/non-linear.cpp:129-180
-//   out    = V(f16) . fp16(probs)        same MatMul rule
-// With n_split == 1 the order of operations and every rounding point (fp16 Q, fp16 exp argument,
-// fp16 probabilities) are the reference's; only the f32 summation order differs. With n_split > 1
-// each split keeps its own running maximum and the last split to finish merges the partial sums
-// (online softmax), which also moves the fp16 rounding of the probabilities: tolerance only.
-// Roofline: HBM-bound, 2 * n_kv * head_dim * 2 bytes per head read once.
-constexpr int ATT_THREADS = 128;
+//   out    = V(f16) . fp16(probs)        same MatMul rule; V is kept transposed [d][n_ctx] as the reference
+//                                        graph lays it out (model/src/llm/plugin/attention.cpp:228-262)
+// Dot<FP16,FP16> runs four 8-wide accumulators over 32-element steps while i + 32 < n and leaves the rest
+// (1..32 elements) to a scalar chain added as tail + vector part. Here a warp takes 32 dot products at a
+// time: the vector part of each one cooperatively (lane = accumulator element), then the 32 scalar tails
+// in parallel, one per lane.
+// Roofline: HBM-bound, 2 * n_kv * head_dim * 2 bytes per head read once; latency-bound at short contexts.
+constexpr int ATT_THREADS = 256;
+constexpr int ATT_WARPS   = ATT_THREADS / WARP;
 
 __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams p) {
     extern __shared__ __align__(16) float att_smem[];
-    __shared__ float red[ATT_THREADS / WARP];
-    __shared__ int   is_last;
+    __shared__ float red[ATT_WARPS];
+    __shared__ float bcast;
 
-    const int h = blockIdx.x, t = blockIdx.y, sp = blockIdx.z;
+    const int h = blockIdx.x, t = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    constexpr int NW = ATT_THREADS / WARP;
+    const int hd = p.hd;
 
     pdl_launch_dependents();
     pdl_wait();
 
     const int pos  = *p.pos_base + t;
-    const int n_kv = pos + 1;                               // causal mask: positions 0..pos are visible
-    const int chunk = (n_kv + p.n_split - 1) / p.n_split;
-    const int j0 = min(n_kv, sp * chunk), j1 = min(n_kv, j0 + chunk);
-    const int n  = j1 - j0;
-    float *sc = att_smem;                                   // n floats
+    const int n_kv = pos + 1;                    // causal mask: positions 0..pos are visible
+    float *sc = att_smem;                        // [n_ctx] scores, then probabilities
+    float *qf = att_smem + p.n_ctx;              // [hd] Q as f32 (exact widening of the fp16 values)
 
-    // head_dim == 128: each lane owns 4 consecutive dims
-    const __half2 *q2 = reinterpret_cast<const __half2 *>(p.q + (int64_t)t * p.dl + (int64_t)h * p.hd) + lane * 2;
-    const float2 qa = __half22float2(q2[0]), qb = __half22float2(q2[1]);
+    for (int i = tid; i < hd; i += ATT_THREADS) { qf[i] = __half2float(p.q[(int64_t)t * p.dl + (int64_t)h * hd + i]); }
+    __syncthreads();
 
-    for (int j = j0 + warp; j < j1; j += NW) {
-        const uint2 kv = *reinterpret_cast<const uint2 *>(p.k_cache + (int64_t)j * p.dl + (int64_t)h * p.hd + lane * 4);
-        const float2 ka = __half22float2(*reinterpret_cast<const __half2 *>(&kv.x));
-        const float2 kb = __half22float2(*reinterpret_cast<const __half2 *>(&kv.y));
-        float s = ka.x * qa.x;
-        s = fmaf(ka.y, qa.y, s); s = fmaf(kb.x, qb.x, s); s = fmaf(kb.y, qb.y, s);
-        s = warp_sum(s);
-        if (lane == 0) { sc[j - j0] = __fmul_rn(s, p.scale); }   // (score + 0) * scale
+    // ---- scores
+    const int k_main = ((hd - 1) / 32) * 32;     // elements covered by the vector loop (i + 32 < hd)
+    for (int jb = warp * 32; jb < n_kv; jb += ATT_WARPS * 32) {
+        const int npos = min(32, n_kv - jb);
+        float simd_mine = 0.f;
+        for (int i = 0; i < npos; ++i) {
+            const __half *krow = p.k_cache + (int64_t)(jb + i) * p.dl + (int64_t)h * hd;
+            float acc = 0.f;
+            for (int e = 0; e < k_main; e += 32) { acc = fmaf(__half2float(krow[e + lane]), qf[e + lane], acc); }
+            acc = reduce_f16dot_lanes(acc);
+            if (lane == i) { simd_mine = acc; }
+        }
+        if (lane < npos) {
+            const __half *krow = p.k_cache + (int64_t)(jb + lane) * p.dl + (int64_t)h * hd;
+            float tail = 0.f;
+            for (int e = k_main; e < hd; ++e) { tail = fmaf(__half2float(krow[e]), qf[e], tail); }
+            sc[jb + lane] = __fadd_rn(tail, simd_mine);
+        }
     }
     __syncthreads();
 
+    // ---- masked softmax: (score + mask) * scale, subtract the maximum, table exp, std::reduce, multiply by 1/sum
     float m = -CUDART_INF_F;
-    for (int j = tid; j < n; j += ATT_THREADS) { m = fmaxf(m, sc[j]); }
+    for (int j = tid; j < n_kv; j += ATT_THREADS) {
+        const float v = __fmul_rn(__fadd_rn(sc[j], 0.0f), p.scale);
+        sc[j] = v;
+        m = fmaxf(m, v);
+    }
     m = warp_max(m);
     if (lane == 0) { red[warp] = m; }
     __syncthreads();
     m = red[0];
 #pragma unroll
-    for (int w = 1; w < NW; ++w) { m = fmaxf(m, red[w]); }
+    for (int w = 1; w < ATT_WARPS; ++w) { m = fmaxf(m, red[w]); }
+    for (int j = tid; j < n_kv; j += ATT_THREADS) { sc[j] = p.exp_table[f2h(__fsub_rn(sc[j], m))]; }
+    __syncthreads();
+    if (tid == 0) { bcast = __fdiv_rn(1.0f, reduce4_chain(sc, n_kv)); }
+    __syncthreads();
+    const float inv = bcast;
+    // probabilities, rounded to fp16 as the PV MatMul does with its f32 operand
+    for (int j = tid; j < n_kv; j += ATT_THREADS) { sc[j] = __half2float(__float2half_rn(__fmul_rn(sc[j], inv))); }
     __syncthreads();
 
-    float l = 0.f;
-    for (int j = tid; j < n; j += ATT_THREADS) {
-        const float e = p.exp_table[f2h(__fsub_rn(sc[j], m))];
-        sc[j] = e;
-        l += e;
-    }
-    l = warp_sum(l);
-    if (lane == 0) { red[warp] = l; }
-    __syncthreads();
-    l = 0.f;
-#pragma unroll
-    for (int w = 0; w < NW; ++w) { l += red[w]; }
-
-    if (p.n_split == 1) {
-        const float inv = __fdiv_rn(1.0f, l);
-        for (int j = tid; j < n; j += ATT_THREADS) { sc[j] = h2f(f2h(__fmul_rn(sc[j], inv))); }
-    }
-    __syncthreads();
-
-    // out[e] = sum_j prob_j * V[j][e]; thread e walks the positions with 4 loads in flight
-    const __half *vcol = p.v_cache + (int64_t)h * p.hd + tid;
-    float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-    int j = 0;
-    for (; j + 4 <= n; j += 4) {
-        const float v0 = __half2float(vcol[(int64_t)(j0 + j) * p.dl]);
-        const float v1 = __half2float(vcol[(int64_t)(j0 + j + 1) * p.dl]);
-        const float v2 = __half2float(vcol[(int64_t)(j0 + j + 2) * p.dl]);
-        const float v3 = __half2float(vcol[(int64_t)(j0 + j + 3) * p.dl]);
-        o0 = fmaf(sc[j], v0, o0); o1 = fmaf(sc[j + 1], v1, o1); o2 = fmaf(sc[j + 2], v2, o2); o3 = fmaf(sc[j + 3], v3, o3);
-    }
-    for (; j < n; ++j) { o0 = fmaf(sc[j], __half2float(vcol[(int64_t)(j0 + j) * p.dl]), o0); }
-    const float o = (o0 + o1) + (o2 + o3);
-
-    if (p.n_split == 1) {
-        p.out[(int64_t)t * p.dl + (int64_t)h * p.hd + tid] = o;
-        return;
-    }
-
-    // split-K: publish (max, sum, partial out) and let the last split of this (token, head) merge
-    const int    slot_w = p.hd + 2;
-    const int    th     = t * p.n_head + h;
-    float       *mine   = p.scratch + ((int64_t)th * p.n_split + sp) * slot_w;
-    mine[2 + tid] = o;
-    if (tid == 0) { mine[0] = m; mine[1] = l; }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        const int prev = atomicAdd(p.counters + th, 1);
-        is_last = (prev == p.n_split - 1);
-        if (is_last) { p.counters[th] = 0; }   // ready for the next launch
-    }
-    __syncthreads();
-    if (!is_last) { return; }
-    __threadfence();
-    const float *all = p.scratch + (int64_t)th * p.n_split * slot_w;
-    float gm = -CUDART_INF_F;
-    for (int s = 0; s < p.n_split; ++s) { gm = fmaxf(gm, __ldcg(all + s * slot_w)); }
-    float gl = 0.f, go = 0.f;
-    for (int s = 0; s < p.n_split; ++s) {
-        const float ms = __ldcg(all + s * slot_w), ls = __ldcg(all + s * slot_w + 1);
-        if (ls > 0.f) {
-            const float w = expf(ms - gm);
-            gl = fmaf(ls, w, gl);
-            go = fmaf(__ldcg(all + s * slot_w + 2 + tid), w, go);
+    // ---- out[e] = Dot<FP16,FP16>(V_t[e][0..n_kv), probs)
+    const int n_main = ((n_kv - 1) / 32) * 32;
+    for (int eb = warp * 32; eb < hd; eb += ATT_WARPS * 32) {
+        float simd_mine = 0.f;
+        for (int i = 0; i < 32; ++i) {
+            const __half *vrow = p.v_cache + ((int64_t)h * hd + eb + i) * p.n_ctx;
+            float acc = 0.f;
+            for (int j = 0; j < n_main; j += 32) { acc = fmaf(__half2float(vrow[j + lane]), sc[j + lane], acc); }
+            acc = reduce_f16dot_lanes(acc);
+            if (lane == i) { simd_mine = acc; }
         }
+        const __half *vrow = p.v_cache + ((int64_t)h * hd + eb + lane) * p.n_ctx;
+        float tail = 0.f;
+        for (int j = n_main; j < n_kv; ++j) { tail = fmaf(__half2float(vrow[j]), sc[j], tail); }
+        p.out[(int64_t)t * p.dl + (int64_t)h * hd + eb + lane] = __fadd_rn(tail, simd_mine);
     }
-    p.out[(int64_t)t * p.dl + (int64_t)h * p.hd + tid] = __fdiv_rn(go, gl);
 }
 
-size_t attention_scratch_floats(int T, int n_head, int n_split, int hd) { return (size_t)T * n_head * n_split * (hd + 2); }
-
 cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
-    if (p.hd != 128 || p.n_split < 1 || p.T < 1) { return cudaErrorInvalidValue; }
-    if (p.n_split > 1 && (p.scratch == nullptr || p.counters == nullptr)) { return cudaErrorInvalidValue; }
-    const int    chunk_max = (p.n_ctx + p.n_split - 1) / p.n_split;
-    const size_t smem      = (size_t)chunk_max * sizeof(float) + 16;
+    if (p.hd < 32 || p.hd % 32 != 0 || p.T < 1 || p.n_ctx < 1) { return cudaErrorInvalidValue; }
+    const size_t smem = (size_t)(p.n_ctx + p.hd) * sizeof(float) + 16;
     if (smem > 200 * 1024) { return cudaErrorInvalidValue; }
     static size_t smem_allowed = 40 * 1024;
     if (smem > smem_allowed) {
@@ -154,7 +135,7 @@ cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
         smem_allowed = smem;
     }
     cudaLaunchConfig_t lc = {};
-    lc.gridDim = dim3(p.n_head, p.T, p.n_split); lc.blockDim = dim3(ATT_THREADS); lc.dynamicSmemBytes = smem; lc.stream = cfg.stream;
+    lc.gridDim = dim3(p.n_head, p.T, 1); lc.blockDim = dim3(ATT_THREADS); lc.dynamicSmemBytes = smem; lc.stream = cfg.stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -232,21 +213,30 @@ __global__ void block_dots_kernel(int wtype, const uint8_t *w, const uint8_t *xb
     const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= nblk) { return; }
     const uint8_t *y = xb + b * 34 + 2;
-    uint32_t yw[8]; int ys = 0;
-    for (int k = 0; k < 8; ++k) { yw[k] = y[4 * k] | (y[4 * k + 1] << 8) | (y[4 * k + 2] << 16) | ((uint32_t)y[4 * k + 3] << 24); }
-    for (int k = 0; k < 32; ++k) { ys += (int)(int8_t)y[k]; }
+    uint32_t yw[8]; int gs[8];
+    for (int k = 0; k < 8; ++k) {
+        yw[k] = y[4 * k] | (y[4 * k + 1] << 8) | (y[4 * k + 2] << 16) | ((uint32_t)y[4 * k + 3] << 24);
+        gs[k] = (int)(int8_t)y[4 * k] + (int)(int8_t)y[4 * k + 1] + (int)(int8_t)y[4 * k + 2] + (int)(int8_t)y[4 * k + 3];
+    }
     const uint4 ylo = make_uint4(yw[0], yw[1], yw[2], yw[3]), yhi = make_uint4(yw[4], yw[5], yw[6], yw[7]);
+    float f[8];
+    int   total = 0;
     if (wtype == 2) {
         const uint8_t *q = w + b * 18 + 2;
         uint32_t ww[4];
         for (int k = 0; k < 4; ++k) { ww[k] = q[4 * k] | (q[4 * k + 1] << 8) | (q[4 * k + 2] << 16) | ((uint32_t)q[4 * k + 3] << 24); }
-        out[b] = dot_q4_0_block(make_uint4(ww[0], ww[1], ww[2], ww[3]), ylo, yhi, ys);
+        const int4 blo = make_int4((int)MAGIC_I - 8 * gs[0], (int)MAGIC_I - 8 * gs[1], (int)MAGIC_I - 8 * gs[2], (int)MAGIC_I - 8 * gs[3]);
+        const int4 bhi = make_int4((int)MAGIC_I - 128 * gs[4], (int)MAGIC_I - 128 * gs[5], (int)MAGIC_I - 128 * gs[6], (int)MAGIC_I - 128 * gs[7]);
+        lanes_q4_0(make_uint4(ww[0], ww[1], ww[2], ww[3]), ylo, yhi, blo, bhi, f);
+        for (int l = 0; l < 4; ++l) { total += (int)f[l] / 16 + (int)f[4 + l]; }   // high-nibble lanes come scaled by 16
     } else {
         const uint8_t *q = w + b * 34 + 2;
         uint32_t ww[8];
         for (int k = 0; k < 8; ++k) { ww[k] = q[4 * k] | (q[4 * k + 1] << 8) | (q[4 * k + 2] << 16) | ((uint32_t)q[4 * k + 3] << 24); }
-        out[b] = dot_q8_0_block(make_uint4(ww[0], ww[1], ww[2], ww[3]), make_uint4(ww[4], ww[5], ww[6], ww[7]), ylo, yhi);
+        lanes_q8_0(make_uint4(ww[0], ww[1], ww[2], ww[3]), make_uint4(ww[4], ww[5], ww[6], ww[7]), ylo, yhi, f);
+        for (int l = 0; l < 8; ++l) { total += (int)f[l]; }
     }
+    out[b] = total;
 }
 
 cudaError_t launch_block_dots(int wtype, const uint8_t *w_row, const uint8_t *x_blocks, int64_t n, int32_t *out, cudaStream_t s) {
@@ -260,24 +250,41 @@ cudaError_t launch_block_dots(int wtype, const uint8_t *w_row, const uint8_t *x_
 // =============================================================================================
 // per-operator kernels (each mirrors one OperatorImpl of backend/host/operator/*.cpp)
 
-// OperatorNormRMSImpl::execute, non-linear.cpp:194-223; one CTA per row
+// OperatorNormRMSImpl::execute, non-linear.cpp:194-223; one CTA per row. Sum of squares in the order of
+// std::transform_reduce: (x0^2 + x1^2) + (x2^2 + x3^2) per group of four (first product of each pair fused),
+// groups added to the running sum in order.
 __global__ void rmsnorm_kernel(const float *x, float *out, int64_t n, float eps) {
-    __shared__ float red[8];
+    extern __shared__ __align__(16) float v3[];
+    __shared__ float scale_s;
     const float *xr = x + (int64_t)blockIdx.x * n;
     float       *o  = out + (int64_t)blockIdx.x * n;
-    float ss = 0.f;
-    for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { ss = fmaf(xr[i], xr[i], ss); }
-    ss = warp_sum(ss);
-    if ((threadIdx.x & 31) == 0) { red[threadIdx.x >> 5] = ss; }
+    const int n4 = (int)(n >> 2);
+    for (int g = threadIdx.x; g < n4; g += blockDim.x) {
+        const float4 v = reinterpret_cast<const float4 *>(xr)[g];
+        v3[g] = __fadd_rn(fmaf(v.x, v.x, __fmul_rn(v.y, v.y)), fmaf(v.z, v.z, __fmul_rn(v.w, v.w)));
+    }
     __syncthreads();
-    float tot = 0.f;
-    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) { tot += red[w]; }
-    const float scale = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)n), eps)));
+    if (threadIdx.x == 0) {
+        float sum = 0.f;
+        for (int g = 0; g < n4; ++g) { sum = __fadd_rn(sum, v3[g]); }
+        for (int64_t i = (int64_t)n4 * 4; i < n; ++i) { sum = fmaf(xr[i], xr[i], sum); }
+        scale_s = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(sum, (float)n), eps)));
+    }
+    __syncthreads();
+    const float scale = scale_s;
     for (int64_t i = threadIdx.x; i < n; i += blockDim.x) { o[i] = __fmul_rn(xr[i], scale); }
 }
 cudaError_t launch_rmsnorm(const float *x, float *out, int64_t n, int64_t rows, float eps, cudaStream_t s) {
     if (rows == 0 || n == 0) { return cudaSuccess; }
-    rmsnorm_kernel<<<(unsigned)rows, 256, 0, s>>>(x, out, n, eps);
+    if ((n & 3) != 0 || n > 180 * 1024) { return cudaErrorNotSupported; }   // rows are read as float4 groups
+    const size_t smem = (size_t)n;   // n/4 floats
+    static size_t smem_allowed = 48 * 1024;
+    if (smem > smem_allowed) {
+        cudaError_t err = cudaFuncSetAttribute(rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) { return err; }
+        smem_allowed = smem;
+    }
+    rmsnorm_kernel<<<(unsigned)rows, 256, smem, s>>>(x, out, n, eps);
     return launch_check();
 }
 
@@ -307,10 +314,13 @@ cudaError_t launch_silu(const float *x, float *out, int64_t n, const float *silu
     return launch_check();
 }
 
-// operator_masked_softmax_execute, non-linear.cpp:129-180; one CTA per row (i1, i2), row length ne0
+// operator_masked_softmax_execute, non-linear.cpp:129-180; one CTA per row (i1, i2), row length ne0,
+// the row kept in shared memory; the sum follows std::reduce's order (reduce4_chain).
 __global__ void softmax_masked_kernel(const float *scores, const float *mask, float *out, int64_t ne0, int64_t ne1,
                                       int64_t mask_stride, float scale, const float *exp_table) {
+    extern __shared__ __align__(16) float row_s[];
     __shared__ float red[8];
+    __shared__ float bcast;
     const int64_t row = blockIdx.x;
     const int64_t i1  = row % ne1;
     const float  *src = scores + row * ne0;
@@ -320,7 +330,7 @@ __global__ void softmax_masked_kernel(const float *scores, const float *mask, fl
     float m = -CUDART_INF_F;
     for (int64_t i = threadIdx.x; i < ne0; i += blockDim.x) {
         const float v = __fmul_rn(__fadd_rn(src[i], mk[i]), scale);
-        dst[i] = v;
+        row_s[i] = v;
         m = fmaxf(m, v);
     }
     m = warp_max(m);
@@ -328,25 +338,27 @@ __global__ void softmax_masked_kernel(const float *scores, const float *mask, fl
     __syncthreads();
     m = red[0];
     for (int w = 1; w < nw; ++w) { m = fmaxf(m, red[w]); }
-    __syncthreads();
-    float l = 0.f;
     for (int64_t i = threadIdx.x; i < ne0; i += blockDim.x) {
-        const float e = (mk[i] == -CUDART_INF_F) ? 0.f : exp_table[f2h(__fsub_rn(dst[i], m))];
-        dst[i] = e;
-        l += e;
+        row_s[i] = (mk[i] == -CUDART_INF_F) ? 0.f : exp_table[f2h(__fsub_rn(row_s[i], m))];
     }
-    l = warp_sum(l);
-    if (lane == 0) { red[warp] = l; }
     __syncthreads();
-    l = 0.f;
-    for (int w = 0; w < nw; ++w) { l += red[w]; }
-    const float inv = __fdiv_rn(1.0f, l);
-    for (int64_t i = threadIdx.x; i < ne0; i += blockDim.x) { dst[i] = __fmul_rn(dst[i], inv); }
+    if (threadIdx.x == 0) { bcast = __fdiv_rn(1.0f, reduce4_chain(row_s, (int)ne0)); }
+    __syncthreads();
+    const float inv = bcast;
+    for (int64_t i = threadIdx.x; i < ne0; i += blockDim.x) { dst[i] = __fmul_rn(row_s[i], inv); }
 }
 cudaError_t launch_softmax_masked(const float *scores, const float *mask, float *out, int64_t ne0, int64_t ne1, int64_t ne2,
                                   int64_t mask_stride, float scale, const float *exp_table, cudaStream_t s) {
     if (ne0 == 0 || ne1 * ne2 == 0) { return cudaSuccess; }
-    softmax_masked_kernel<<<(unsigned)(ne1 * ne2), 256, 0, s>>>(scores, mask, out, ne0, ne1, mask_stride, scale, exp_table);
+    const size_t smem = (size_t)ne0 * sizeof(float);
+    if (smem > 200 * 1024) { return cudaErrorNotSupported; }
+    static size_t smem_allowed = 48 * 1024;
+    if (smem > smem_allowed) {
+        cudaError_t err = cudaFuncSetAttribute(softmax_masked_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) { return err; }
+        smem_allowed = smem;
+    }
+    softmax_masked_kernel<<<(unsigned)(ne1 * ne2), 256, smem, s>>>(scores, mask, out, ne0, ne1, mask_stride, scale, exp_table);
     return launch_check();
 }
 
@@ -355,28 +367,25 @@ __device__ __forceinline__ int64_t soff(const Strided &t, int64_t i0, int64_t i1
 }
 
 // OperatorRopeImpl::execute in mode Norm with default YaRN settings, non-linear.cpp:270-371.
-// One thread per (pair, head, token); theta is advanced by repeated f32 multiplication as the CPU does.
-__global__ void rope_kernel(const Strided x, const int32_t *pos, const Strided out, float theta_scale, int n_dim) {
+// One thread per (pair, head, token); the (cos, sin) of every (token, pair) comes from a table the host
+// fills with the same libm calls and the same repeated f32 multiplication of theta as the CPU operator.
+__global__ void rope_kernel(const Strided x, const float2 *cos_sin, const Strided out) {
     const int64_t npair = x.ne[0] >> 1;
     const int64_t i     = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t tot   = npair * x.ne[1] * x.ne[2];
     if (i >= tot) { return; }
     const int64_t k = i % npair, i1 = (i / npair) % x.ne[1], i2 = i / (npair * x.ne[1]);
-    float theta = (float)pos[i2];
-    for (int64_t j = 0; j < k; ++j) { theta = __fmul_rn(theta, theta_scale); }
-    const float c = cosf(theta), s = sinf(theta);
+    const float2 cs = cos_sin[i2 * npair + k];
     const float *src = reinterpret_cast<const float *>(reinterpret_cast<const uint8_t *>(x.data) + soff(x, 2 * k, i1, i2, 0));
     float       *dst = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(out.data) + soff(out, 2 * k, i1, i2, 0));
     const float x0 = src[0], x1 = src[1];
-    dst[0] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
-    dst[1] = __fadd_rn(__fmul_rn(x0, s), __fmul_rn(x1, c));
-    (void)n_dim;
+    dst[0] = __fsub_rn(__fmul_rn(x0, cs.x), __fmul_rn(x1, cs.y));
+    dst[1] = __fadd_rn(__fmul_rn(x0, cs.y), __fmul_rn(x1, cs.x));
 }
-cudaError_t launch_rope(const Strided &x, const int32_t *pos, const Strided &out, float freq_base, int n_dim, cudaStream_t s) {
+cudaError_t launch_rope(const Strided &x, const float2 *cos_sin, const Strided &out, cudaStream_t s) {
     const int64_t tot = (x.ne[0] >> 1) * x.ne[1] * x.ne[2];
     if (tot == 0) { return cudaSuccess; }
-    const float theta_scale = powf(freq_base, -2.0f / (float)n_dim);
-    rope_kernel<<<(unsigned)((tot + 127) / 128), 128, 0, s>>>(x, pos, out, theta_scale, n_dim);
+    rope_kernel<<<(unsigned)((tot + 127) / 128), 128, 0, s>>>(x, cos_sin, out);
     return launch_check();
 }
 
@@ -434,8 +443,9 @@ cudaError_t launch_embed(const int32_t *ids, int n_ids, const uint8_t *embd, int
     return launch_getrow(embd, embd_type, rb, d_model, ids, n_ids, x_out, s);
 }
 
-// MatMul with an F16 weight and f32 activations (the attention products when run op by op):
-// activations are rounded to fp16 first (mat.cpp:32-42), f32 accumulate. One warp per output.
+// MatMul with an F16 weight and f32 activations (the attention products when run op by op): activations
+// are rounded to fp16 first (mat.cpp:32-42), then Dot<FP16,FP16> (vec_dot.h:117-146) in its exact order.
+// One warp per output element; arbitrary byte strides.
 __global__ void matmul_f16_kernel(const Strided w, const Strided x, const Strided out) {
     const int64_t n_out = out.ne[0] * out.ne[1] * out.ne[2];
     const int64_t o     = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
@@ -444,14 +454,24 @@ __global__ void matmul_f16_kernel(const Strided w, const Strided x, const Stride
     const int64_t i01 = o % out.ne[0], i11 = (o / out.ne[0]) % out.ne[1], i02 = o / (out.ne[0] * out.ne[1]);
     const uint8_t *wp = reinterpret_cast<const uint8_t *>(w.data) + soff(w, 0, i01, i02, 0);
     const uint8_t *xp = reinterpret_cast<const uint8_t *>(x.data) + soff(x, 0, i11, i02, 0);
+    const int64_t n = w.ne[0];
+    const int64_t n_main = n > 0 ? ((n - 1) / 32) * 32 : 0;
     float acc = 0.f;
-    for (int64_t k = lane; k < w.ne[0]; k += 32) {
-        const float a = h2f(*reinterpret_cast<const uint16_t *>(wp + k * w.nb[0]));
-        const float b = h2f(f2h(*reinterpret_cast<const float *>(xp + k * x.nb[0])));
+    for (int64_t k = 0; k < n_main; k += 32) {
+        const float a = h2f(*reinterpret_cast<const uint16_t *>(wp + (k + lane) * w.nb[0]));
+        const float b = h2f(f2h(*reinterpret_cast<const float *>(xp + (k + lane) * x.nb[0])));
         acc = fmaf(a, b, acc);
     }
-    acc = warp_sum(acc);
-    if (lane == 0) { *reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(out.data) + soff(out, i01, i11, i02, 0)) = acc; }
+    acc = reduce_f16dot_lanes(acc);
+    if (lane == 0) {
+        float tail = 0.f;
+        for (int64_t k = n_main; k < n; ++k) {
+            const float a = h2f(*reinterpret_cast<const uint16_t *>(wp + k * w.nb[0]));
+            const float b = h2f(f2h(*reinterpret_cast<const float *>(xp + k * x.nb[0])));
+            tail = fmaf(a, b, tail);
+        }
+        *reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(out.data) + soff(out, i01, i11, i02, 0)) = __fadd_rn(tail, acc);
+    }
 }
 cudaError_t launch_matmul_f16(const Strided &w, const Strided &x, const Strided &out, cudaStream_t s) {
     const int64_t n_out = out.ne[0] * out.ne[1] * out.ne[2];

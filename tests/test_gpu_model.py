@@ -19,8 +19,12 @@ ABS_TOL, REL_TOL = 2e-2, 1e-2
 
 
 def logits_ok(got, want):
+    """The stated gate is max-abs 2e-2 / rel 1e-2; the kernels reproduce the CPU's f32 summation order, so the
+    logits are in fact required to be bit-identical (anything less is amplified by the per-layer Q8_0
+    re-quantization to percent-level differences on deep models)."""
     err = np.abs(got - want)
-    return float(err.max()) <= ABS_TOL and float(err.max()) <= REL_TOL * float(np.abs(want).max())
+    within = float(err.max()) <= ABS_TOL and float(err.max()) <= REL_TOL * float(np.abs(want).max())
+    return within and np.array_equal(np.ascontiguousarray(got).view(np.uint32), np.ascontiguousarray(want).view(np.uint32))
 
 
 def top2_gap(logits):
@@ -97,9 +101,8 @@ def test_launch_modes_agree(pdl, graph, oracle, tmp_models):
 
 
 def test_activation_blocks_of_first_layer(be, oracle, tmp_models):
-    """Q8_0 blocks of layer 0's attention-norm output for the first prompt token. The quantizer is
-    bit-exact on equal input (see test_gpu_ops); here its input comes from an RMSNorm whose summation
-    order differs from the CPU's, so a value on a rounding boundary may move by one step."""
+    """Q8_0 blocks of layer 0's attention-norm output for the first prompt token: RMSNorm (in the CPU's
+    summation order), the norm weight and the quantizer together must give the CPU's bytes."""
     cfg = gguf_io.LlamaConfig(weight_std=0.05)
     path = str(tmp_models / "tap.gguf")
     gguf_io.make_llama_gguf(path, cfg, seed=21)
@@ -109,10 +112,7 @@ def test_activation_blocks_of_first_layer(be, oracle, tmp_models):
     m = B.LlamaModel(be, path, n_ctx=32)
     m.eval(prompt, 0)
     got = m.tap_xq()
-    g, w = got.reshape(-1, 34), want.reshape(-1, 34)
-    assert np.array_equal(g[:, :2], w[:, :2])                         # fp16 scales identical
-    dq = np.abs(g[:, 2:].view(np.int8).astype(np.int32) - w[:, 2:].view(np.int8).astype(np.int32))
-    assert dq.max() <= 1 and (dq != 0).mean() <= 0.01
+    assert np.array_equal(got, want)   # byte-identical Q8_0 activation blocks
     m.close()
 
 
@@ -134,8 +134,9 @@ def test_prompt_longer_than_one_pass_and_context_edge(be, oracle, tmp_models):
     m.close()
 
 
-def test_long_context_split_attention(be, oracle, tmp_models):
-    """n_ctx > 512 switches attention to split-K with the online-softmax merge; tolerance only."""
+def test_long_context_attention(be, oracle, tmp_models):
+    """A 600-token prompt in a 1024-token context: many 32-wide accumulator steps and ragged tails in both
+    attention products."""
     cfg = gguf_io.LlamaConfig(n_layer=1, weight_std=0.05)
     path = str(tmp_models / "split.gguf")
     gguf_io.make_llama_gguf(path, cfg, seed=41)
