@@ -291,13 +291,13 @@ int oracle_matmul(int wtype, const uint8_t *w, int64_t k, int64_t n_out, const f
 /* std::reduce / std::transform_reduce on random-access iterators (libstdc++ <numeric>):
  * groups of four are combined as ((v0 + v1) + (v2 + v3)) and added to the running sum, the
  * remainder one by one. With the reference's build flags the compiler contracts
- * x0*x0 + x1*x1 into fma(x0, x0, x1*x1). */
+ * x0*x0 + x1*x1 into fma(x1, x1, x0*x0) (checked on wide-range inputs against that build). */
 static float sum_of_squares(const float *x, int64_t n) {
     float init = 0.0f;
     int64_t i = 0;
     for (; n - i >= 4; i += 4) {
-        const float v1 = fmaf(x[i], x[i], x[i + 1] * x[i + 1]);
-        const float v2 = fmaf(x[i + 2], x[i + 2], x[i + 3] * x[i + 3]);
+        const float v1 = fmaf(x[i + 1], x[i + 1], x[i] * x[i]);
+        const float v2 = fmaf(x[i + 3], x[i + 3], x[i + 2] * x[i + 2]);
         init = init + (v1 + v2);
     }
     for (; i < n; ++i) { init = fmaf(x[i], x[i], init); }
@@ -407,9 +407,14 @@ oracle_state *oracle_state_new(const oracle_model *m) {
 void oracle_state_free(oracle_state *s) { if (s) { free(s->k_cache); free(s->v_cache); free(s); } }
 
 /* Optional debugging tap: when set, oracle_eval stores, for layer 0 and the last token of the call,
- * [q after rope (d) | attention output (d) | x after the attention residual (d) | up*silu(gate) (F) | x after the FFN residual (d)]. */
+ * for the layer chosen with oracle_set_debug_layer: [q after rope (d) | attention output (d) | x after the attention residual (d) | up*silu(gate) (F) | x after the FFN residual (d)]. */
 static float *g_debug_tap = NULL;
+static int g_debug_layer = 0;
 void oracle_set_debug_tap(float *buf) { g_debug_tap = buf; }
+void oracle_set_debug_layer(int layer) { g_debug_layer = layer; }
+/* second tap: residual stream after the chosen layer, then that layer's attention output, then Q after RoPE, for every token of the call ([t][d] each) */
+static float *g_debug_x = NULL;
+void oracle_set_debug_x(float *buf) { g_debug_x = buf; }
 
 /* One execution of the graph LLAMAModel::build_graph emits (model/src/llm/model/llama.cpp:123-222,
  * plugin/attention.cpp:267-302, plugin/ffn.cpp:5-42, plugin/inout.cpp:5-78) for `t` tokens at
@@ -485,7 +490,7 @@ int oracle_eval(const oracle_model *m, oracle_state *st, const int32_t *tokens, 
         }
         rc |= oracle_matmul(m->t_wo[L], m->wo[L], d, d, att, t, tmp, NULL);
         oracle_add(tmp, x, t * d, x);                       /* ffn_input = attn_out + x, llama.cpp:194-197 */
-        if (g_debug_tap && L == 0) {
+        if (g_debug_tap && L == g_debug_layer) {
             memcpy(g_debug_tap, q + (t - 1) * d, (size_t)d * 4);
             memcpy(g_debug_tap + d, att + (t - 1) * d, (size_t)d * 4);
             memcpy(g_debug_tap + 2 * d, x + (t - 1) * d, (size_t)d * 4);
@@ -497,9 +502,10 @@ int oracle_eval(const oracle_model *m, oracle_state *st, const int32_t *tokens, 
         oracle_silu(gate, t * F, gate);
         oracle_mul(up, gate, t * F, up);                    /* ffn_par = up * silu(gate), ffn.cpp:32-35 */
         rc |= oracle_matmul(m->t_down[L], m->w_down[L], F, d, up, t, tmp, NULL);
-        if (g_debug_tap && L == 0) { memcpy(g_debug_tap + 3 * d, up + (t - 1) * F, (size_t)F * 4); }
+        if (g_debug_tap && L == g_debug_layer) { memcpy(g_debug_tap + 3 * d, up + (t - 1) * F, (size_t)F * 4); }
         oracle_add(x, tmp, t * d, x);                       /* llama.cpp:206-211 */
-        if (g_debug_tap && L == 0) { memcpy(g_debug_tap + 3 * d + F, x + (t - 1) * d, (size_t)d * 4); }
+        if (g_debug_tap && L == g_debug_layer) { memcpy(g_debug_tap + 3 * d + F, x + (t - 1) * d, (size_t)d * 4); }
+        if (g_debug_x && L == g_debug_layer) { memcpy(g_debug_x, x, (size_t)t * d * 4); memcpy(g_debug_x + (size_t)t * d, att, (size_t)t * d * 4); memcpy(g_debug_x + (size_t)2 * t * d, q, (size_t)t * d * 4); }
         if (rc) { goto done; }
     }
     oracle_rmsnorm(x, d, t, m->rms_eps, tmp);

@@ -48,7 +48,7 @@ size_t matvec_smem_bytes(int nb, int T) { size_t a, b; return matvec_smem_layout
 // prologue: f32 activations -> Q8_0 columns in shared memory (optionally through RMSNorm * weight)
 //   NormRMS (backend/host/operator/non-linear.cpp:194-223): sum of squares by std::transform_reduce, whose
 //   order for random-access ranges is: groups of four combined as (x0^2 + x1^2) + (x2^2 + x3^2) (the first
-//   product of each pair fused into an FMA by the CPU build) and added to the running sum one group after
+//   product of each pair plain, the second fused into an FMA, as the CPU build evaluates it) and added to the running sum one group after
 //   the other; y = x * (1 / sqrt(sum/n + eps)). The groups are formed in parallel, the running sum is
 //   one thread's chain. Mul (basic.cpp:15-50): y * norm_weight.
 template <int TM>
@@ -62,8 +62,8 @@ __device__ __forceinline__ void matvec_prologue(const MatvecParams &p, ActView a
             const float4 *x4 = reinterpret_cast<const float4 *>(p.x + (int64_t)t * p.x_stride);
             for (int g = tid; g < n4; g += MV_THREADS) {
                 const float4 v = x4[g];
-                const float v1 = fmaf(v.x, v.x, __fmul_rn(v.y, v.y));
-                const float v2 = fmaf(v.z, v.z, __fmul_rn(v.w, v.w));
+                const float v1 = fmaf(v.y, v.y, __fmul_rn(v.x, v.x));
+                const float v2 = fmaf(v.w, v.w, __fmul_rn(v.z, v.z));
                 v3[t * n4 + g] = __fadd_rn(v1, v2);
             }
         }

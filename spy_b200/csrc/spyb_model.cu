@@ -178,7 +178,8 @@ template <class T>
 spyb_status dev_alloc(spyb_model *m, T **p, size_t count) {
     void *raw = nullptr;
     SPYB_CUDA(m->be, cudaMalloc(&raw, count * sizeof(T) + 64));
-    SPYB_CUDA(m->be, cudaMemset(raw, 0, count * sizeof(T) + 64));
+    SPYB_CUDA(m->be, cudaMemsetAsync(raw, 0, count * sizeof(T) + 64, m->be->stream));
+    SPYB_CUDA(m->be, cudaStreamSynchronize(m->be->stream));   // uploads that follow use other streams: order them after the clearing
     m->owned.push_back(raw);
     *p = static_cast<T *>(raw);
     return SPYB_SUCCESS;
@@ -284,6 +285,10 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
     m->be = be;
     spyb_model_info &I = m->info;
     I.n_layer = (int)num("llama.block_count", 0); I.d_model = (int)num("llama.embedding_length", 0);
+    if (const char *cap = std::getenv("SPYB_MAX_LAYERS")) {   // debugging aid: run only the first N blocks of the file
+        const int n = std::atoi(cap);
+        if (n > 0 && n < I.n_layer) { I.n_layer = n; }
+    }
     I.n_head = (int)num("llama.attention.head_count", 0); I.n_ff = (int)num("llama.feed_forward_length", 0);
     I.n_ctx = n_ctx > 0 ? n_ctx : (int)num("llama.context_length", 512);
     I.rms_eps = (float)num("llama.attention.layer_norm_rms_epsilon", 1e-5); I.rope_base = (float)num("llama.rope.freq_base", 10000.0);
@@ -404,6 +409,7 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         be->set_error("pinned host allocation failed"); return fail(SPYB_FAIL);
     }
     if (cudaEventCreate(&m->ev0) != cudaSuccess || cudaEventCreate(&m->ev1) != cudaSuccess) { be->set_error("event creation failed"); return fail(SPYB_FAIL); }
+    if (cudaDeviceSynchronize() != cudaSuccess) { be->set_error("device synchronisation after the upload failed"); return fail(SPYB_FAIL); }
     *out = m;
     return SPYB_SUCCESS;
 }

@@ -251,7 +251,7 @@ cudaError_t launch_block_dots(int wtype, const uint8_t *w_row, const uint8_t *x_
 // per-operator kernels (each mirrors one OperatorImpl of backend/host/operator/*.cpp)
 
 // OperatorNormRMSImpl::execute, non-linear.cpp:194-223; one CTA per row. Sum of squares in the order of
-// std::transform_reduce: (x0^2 + x1^2) + (x2^2 + x3^2) per group of four (first product of each pair fused),
+// std::transform_reduce: (x0^2 + x1^2) + (x2^2 + x3^2) per group of four (second product of each pair fused into the first),
 // groups added to the running sum in order.
 __global__ void rmsnorm_kernel(const float *x, float *out, int64_t n, float eps) {
     extern __shared__ __align__(16) float v3[];
@@ -261,7 +261,7 @@ __global__ void rmsnorm_kernel(const float *x, float *out, int64_t n, float eps)
     const int n4 = (int)(n >> 2);
     for (int g = threadIdx.x; g < n4; g += blockDim.x) {
         const float4 v = reinterpret_cast<const float4 *>(xr)[g];
-        v3[g] = __fadd_rn(fmaf(v.x, v.x, __fmul_rn(v.y, v.y)), fmaf(v.z, v.z, __fmul_rn(v.w, v.w)));
+        v3[g] = __fadd_rn(fmaf(v.y, v.y, __fmul_rn(v.x, v.x)), fmaf(v.w, v.w, __fmul_rn(v.z, v.z)));
     }
     __syncthreads();
     if (threadIdx.x == 0) {

@@ -299,3 +299,37 @@ def test_alloc_free_reuse_and_callback(be):
     assert fired == [1]
     be.sync()
     assert be.get_max_memory_capacity() > 100 << 30 and be.get_avail_memory_capacity() > 0
+
+
+def _attention_oracle(oracle, q16, k16, vt16, pos0, n_head, hd, n_ctx):
+    """The reference attention sub-graph composed from oracle primitives, one (token, head) at a time."""
+    t, d = q16.shape
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(hd)))
+    out = np.zeros((t, d), dtype=np.float32)
+    for i in range(t):
+        n_kv = pos0 + i + 1
+        mask = np.zeros(n_kv, dtype=np.float32)
+        for h in range(n_head):
+            qh = np.ascontiguousarray(q16[i, h * hd:(h + 1) * hd])
+            sc = np.array([oracle.dot("f16_f16", np.ascontiguousarray(k16[j, h * hd:(h + 1) * hd]), qh, hd) for j in range(n_kv)], dtype=np.float32)
+            pr = oracle.quantize_f16(oracle.softmax_masked(sc, mask, scale))
+            for e in range(hd):
+                out[i, h * hd + e] = oracle.dot("f16_f16", np.ascontiguousarray(vt16[h * hd + e, :n_kv]), pr, n_kv)
+    return out
+
+
+@pytest.mark.parametrize("pos0,t", [(0, 1), (0, 4), (4, 4), (6, 1), (30, 3), (31, 2), (63, 2), (100, 1)])
+@pytest.mark.parametrize("spread", [0.5, 4.0, 30.0])
+def test_fused_attention_bits(be, oracle, pos0, t, spread):
+    """Fused scores / softmax / PV against the oracle on wide-range values, across the 32-element boundaries of
+    both dot products (n_kv = 1 .. 101)."""
+    rng = np.random.default_rng(pos0 * 7 + t + int(spread * 10))
+    n_head, hd, n_ctx = 2, 128, 128
+    d = n_head * hd
+    wide = lambda n: (rng.standard_normal(n) * rng.choice([0.05, 1.0, spread], size=n)).astype(np.float32)
+    q16 = oracle.quantize_f16(wide(t * d)).reshape(t, d)
+    k16 = oracle.quantize_f16(wide(n_ctx * d)).reshape(n_ctx, d)
+    vt16 = oracle.quantize_f16(wide(n_ctx * d)).reshape(d, n_ctx)
+    got = be.attention(q16, k16, vt16, pos0, n_head, hd, n_ctx)
+    want = _attention_oracle(oracle, q16, k16, vt16, pos0, n_head, hd, n_ctx)
+    assert np.array_equal(bits(got), bits(want))
