@@ -133,13 +133,19 @@ spyb_status spyb_quantize_q8_0(spyb_backend *backend, const float *x_device, int
 spyb_status spyb_block_dots(spyb_backend *backend, int32_t weight_type, const void *w_row_device,
                             const void *x_blocks_device, int64_t n, int32_t *out_device);
 
+/* Copies of the two 65 536-entry fp16-argument tables the device kernels gather from, silu(xh) and expf(xh)
+ * (FP16LookupTable, orchestration/include/number/lookup_table.h:12-54); either pointer may be NULL. */
+spyb_status spyb_read_tables(spyb_backend *backend, float *silu_host, float *exp_host);
+
 /* The attention sub-graph of one layer for n_tokens query tokens at positions pos0..pos0+n_tokens-1 over caller-provided
  * caches, all on the device: MatMul(K, Q) -> masked Softmax(scale = 1/sqrt(head_dim)) -> MatMul(V, probs)
  * (MultiHeadAttentionBlock::attention_projection, model/src/llm/plugin/attention.cpp:102-132, with the causal mask of
  * model/src/llm/model/llama.cpp:248-257). q: fp16 [n_tokens][n_head*head_dim]; k_cache: fp16 [n_ctx][n_head*head_dim];
- * v_cache_t: fp16 [n_head*head_dim][n_ctx] (transposed, model/src/llm/plugin/attention.cpp:228-262); out: f32 like q. */
+ * v_cache_t: fp16 [n_head*head_dim][n_ctx] (transposed, model/src/llm/plugin/attention.cpp:228-262); out: f32 like q.
+ * n_total = number of positions the step knows (n_past + all tokens of the step, the row length of the reference's score
+ * tensor; 0 = pos0 + n_tokens): masked entries are exact zeros but take part in the grouping of the reference's sums. */
 spyb_status spyb_attention(spyb_backend *backend, const void *q_f16, const void *k_cache_f16, const void *v_cache_t_f16, float *out,
-                           int32_t pos0, int32_t n_tokens, int32_t n_head, int32_t head_dim, int32_t n_ctx);
+                           int32_t pos0, int32_t n_tokens, int32_t n_total, int32_t n_head, int32_t head_dim, int32_t n_ctx);
 
 /* ---- whole-model path: the graph LLAMAModel::build_graph emits (model/src/llm/model/llama.cpp:86-264)
  * executed as a fixed plan of fused kernels. */

@@ -90,7 +90,8 @@ def lib():
         "spyb_memcpy_d2h": (i32, [vp, vp, vp, u64]),
         "spyb_quantize_q8_0": (i32, [vp, vp, i64, vp]),
         "spyb_block_dots": (i32, [vp, i32, vp, vp, i64, vp]),
-        "spyb_attention": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32]),
+        "spyb_read_tables": (i32, [vp, vp, vp]),
+        "spyb_attention": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32]),
         "spyb_model_read_activation": (i32, [vp, i32, vp, u64]),
         "spyb_model_bench_kernel": (C.c_float, [vp, i32, i32, C.POINTER(u64)]),
         "spyb_model_load_gguf": (i32, [vp, C.c_char_p, i32, C.POINTER(vp)]),
@@ -255,14 +256,20 @@ class B200Backend:
             self.dealloc_memory(po, max(4, n // 32 * 4))
 
 
-    def attention(self, q16: np.ndarray, k_cache16: np.ndarray, v_cache_t16: np.ndarray, pos0: int, n_head: int, head_dim: int, n_ctx: int) -> np.ndarray:
+    def read_tables(self):
+        silu = np.empty(65536, dtype=np.float32); ex = np.empty(65536, dtype=np.float32)
+        self._check(self._l.spyb_read_tables(self.h, _np_ptr(silu), _np_ptr(ex)))
+        return silu, ex
+
+    def attention(self, q16: np.ndarray, k_cache16: np.ndarray, v_cache_t16: np.ndarray, pos0: int, n_head: int, head_dim: int, n_ctx: int,
+                  n_total: int = 0) -> np.ndarray:
         """q16: uint16 [T, n_head*head_dim] fp16 bits; k_cache16: [n_ctx, d]; v_cache_t16: [d, n_ctx]. Returns f32 [T, d]."""
         t = q16.shape[0]
         d = n_head * head_dim
         pq, pk, pv = self.upload(q16), self.upload(k_cache16), self.upload(v_cache_t16)
         po = self.alloc_memory(t * d * 4)
         try:
-            self._check(self._l.spyb_attention(self.h, pq, pk, pv, po, pos0, t, n_head, head_dim, n_ctx))
+            self._check(self._l.spyb_attention(self.h, pq, pk, pv, po, pos0, t, n_total, n_head, head_dim, n_ctx))
             return self.download(po, (t, d), np.float32)
         finally:
             self.dealloc_memory(pq, q16.nbytes); self.dealloc_memory(pk, k_cache16.nbytes); self.dealloc_memory(pv, v_cache_t16.nbytes)

@@ -305,19 +305,28 @@ spyb_status spyb_block_dots(spyb_backend *be, int32_t wtype, const void *w, cons
     return SPYB_SUCCESS;
 }
 
+spyb_status spyb_read_tables(spyb_backend *be, float *silu_host, float *exp_host) {
+    SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+    if (silu_host) { SPYB_CUDA(be, cudaMemcpy(silu_host, be->d_silu_table, 65536 * sizeof(float), cudaMemcpyDeviceToHost)); }
+    if (exp_host)  { SPYB_CUDA(be, cudaMemcpy(exp_host, be->d_exp_table, 65536 * sizeof(float), cudaMemcpyDeviceToHost)); }
+    return SPYB_SUCCESS;
+}
+
 spyb_status spyb_attention(spyb_backend *be, const void *q_f16, const void *k_cache_f16, const void *v_cache_t_f16, float *out,
-                           int32_t pos0, int32_t n_tokens, int32_t n_head, int32_t head_dim, int32_t n_ctx) {
-    if (n_tokens < 1 || n_head < 1 || pos0 < 0 || pos0 + n_tokens > n_ctx) { be->set_error("attention: positions %d..%d outside the context %d", pos0, pos0 + n_tokens - 1, n_ctx); return SPYB_FAIL; }
-    int *d_pos = static_cast<int *>(be->arena.alloc(sizeof(int)));
+                           int32_t pos0, int32_t n_tokens, int32_t n_total, int32_t n_head, int32_t head_dim, int32_t n_ctx) {
+    if (n_total == 0) { n_total = pos0 + n_tokens; }
+    if (n_tokens < 1 || n_head < 1 || pos0 < 0 || pos0 + n_tokens > n_total || n_total > n_ctx) { be->set_error("attention: positions %d..%d outside the context %d", pos0, pos0 + n_tokens - 1, n_ctx); return SPYB_FAIL; }
+    int *d_pos = static_cast<int *>(be->arena.alloc(2 * sizeof(int)));
+    const int host_pos[2] = {pos0, n_total};
     if (d_pos == nullptr) { be->set_error("attention: out of device memory"); return SPYB_FAIL; }
     AttnParams a;
     a.q = static_cast<const __half *>(q_f16); a.k_cache = static_cast<const __half *>(k_cache_f16); a.v_cache = static_cast<const __half *>(v_cache_t_f16);
     a.out = out; a.pos_base = d_pos; a.exp_table = be->d_exp_table; a.n_head = n_head; a.hd = head_dim; a.dl = n_head * head_dim; a.T = n_tokens; a.n_ctx = n_ctx;
     a.scale = 1.0f / std::sqrt((float)head_dim);
-    cudaError_t err = cudaMemcpyAsync(d_pos, &pos0, sizeof(int), cudaMemcpyHostToDevice, be->stream);
+    cudaError_t err = cudaMemcpyAsync(d_pos, host_pos, sizeof(host_pos), cudaMemcpyHostToDevice, be->stream);
     if (err == cudaSuccess) { err = launch_attention(a, be->launch_cfg(false)); }
     if (err == cudaSuccess) { err = cudaStreamSynchronize(be->stream); }
-    be->arena.free(d_pos, sizeof(int));
+    be->arena.free(d_pos, 2 * sizeof(int));
     if (err != cudaSuccess) { be->set_error("attention failed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
     return SPYB_SUCCESS;
 }

@@ -463,9 +463,10 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
     for (int t0 = 0; t0 < n_tokens; t0 += tmax) {
         const int T = std::min(tmax, n_tokens - t0);
         SPYB_CUDA(be, cudaStreamSynchronize(be->stream));   // pinned staging words are reused per pass
-        *m->h_pos_pinned = n_past + t0;
+        m->h_pos_pinned[0] = n_past + t0;
+        m->h_pos_pinned[1] = n_past + n_tokens;   // the step's score rows span every position known to the step
         std::memcpy(m->h_tok_pinned, tokens + t0, (size_t)T * 4);
-        SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 4, cudaMemcpyHostToDevice, be->stream));
+        SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 8, cudaMemcpyHostToDevice, be->stream));
         SPYB_CUDA(be, cudaMemcpyAsync(m->d_tokens_in, m->h_tok_pinned, (size_t)T * 4, cudaMemcpyHostToDevice, be->stream));
         SPYB_CUDA(be, launch_embed(m->d_tokens_in, T, m->embd, m->embd_type, m->info.d_model, m->x, be->stream)); ++launches;
         if (run_layers(m, T, t0 == 0, &launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
@@ -490,8 +491,8 @@ spyb_status spyb_model_decode(spyb_model *m, int32_t first_token, int32_t n_past
     cudaSetDevice(be->config.device_id);
     if (n_past < 0 || n_past + n_steps > m->info.n_ctx) { be->set_error("decode would exceed the context length (%d + %d > %d)", n_past, n_steps, m->info.n_ctx); return SPYB_FAIL; }
     if (first_token < 0 || first_token >= m->info.n_vocab) { be->set_error("token id %d out of range", first_token); return SPYB_FAIL; }
-    *m->h_pos_pinned = n_past; *m->h_tok_pinned = first_token;
-    SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 4, cudaMemcpyHostToDevice, be->stream));
+    m->h_pos_pinned[0] = n_past; m->h_pos_pinned[1] = 0; *m->h_tok_pinned = first_token;   // [1] = 0: rows end at the token itself
+    SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 8, cudaMemcpyHostToDevice, be->stream));
     SPYB_CUDA(be, cudaMemcpyAsync(m->d_tokens_in, m->h_tok_pinned, 4, cudaMemcpyHostToDevice, be->stream));
     SPYB_CUDA(be, launch_embed(m->d_tokens_in, 1, m->embd, m->embd_type, m->info.d_model, m->x, be->stream));
 
@@ -540,8 +541,8 @@ float spyb_model_bench_kernel(spyb_model *m, int32_t kind, int32_t sweeps, uint6
     cudaSetDevice(be->config.device_id);
     const LaunchCfg cfg = be->launch_cfg(false);
     const int d = m->info.d_model;
-    *m->h_pos_pinned = m->info.n_ctx - 1;
-    if (cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 4, cudaMemcpyHostToDevice, be->stream) != cudaSuccess) { return -1.f; }
+    m->h_pos_pinned[0] = m->info.n_ctx - 1; m->h_pos_pinned[1] = 0;
+    if (cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 8, cudaMemcpyHostToDevice, be->stream) != cudaSuccess) { return -1.f; }
     auto params = [&](const Layer &ly) {
         MatvecParams p; p.T = 1;
         switch (kind) {

@@ -55,18 +55,23 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
     pdl_launch_dependents();
     pdl_wait();
 
-    const int pos  = *p.pos_base + t;
-    const int n_kv = pos + 1;                    // causal mask: positions 0..pos are visible
+    const int pos   = p.pos_base[0] + t;
+    const int n_vis = pos + 1;                   // causal mask: positions 0..pos are visible
+    // Row length of the score matrix = all positions known to the step (past + every token of the step), as the
+    // reference graph shapes it (K view [hd, n_past + n_token, H], model/src/llm/plugin/attention.cpp:207-223). Entries
+    // beyond the causal limit carry mask -inf: they become exact zeros, but they still decide how std::reduce groups
+    // the sum and where Dot<FP16,FP16> switches from its vector loop to the scalar tail.
+    const int n_tot = (p.pos_base[1] > 0) ? p.pos_base[1] : p.pos_base[0] + p.T;
     float *sc = att_smem;                        // [n_ctx] scores, then probabilities
     float *qf = att_smem + p.n_ctx;              // [hd] Q as f32 (exact widening of the fp16 values)
 
     for (int i = tid; i < hd; i += ATT_THREADS) { qf[i] = __half2float(p.q[(int64_t)t * p.dl + (int64_t)h * hd + i]); }
     __syncthreads();
 
-    // ---- scores
+    // ---- scores of the visible positions
     const int k_main = ((hd - 1) / 32) * 32;     // elements covered by the vector loop (i + 32 < hd)
-    for (int jb = warp * 32; jb < n_kv; jb += ATT_WARPS * 32) {
-        const int npos = min(32, n_kv - jb);
+    for (int jb = warp * 32; jb < n_vis; jb += ATT_WARPS * 32) {
+        const int npos = min(32, n_vis - jb);
         float simd_mine = 0.f;
         for (int i = 0; i < npos; ++i) {
             const __half *krow = p.k_cache + (int64_t)(jb + i) * p.dl + (int64_t)h * hd;
@@ -86,7 +91,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
 
     // ---- masked softmax: (score + mask) * scale, subtract the maximum, table exp, std::reduce, multiply by 1/sum
     float m = -CUDART_INF_F;
-    for (int j = tid; j < n_kv; j += ATT_THREADS) {
+    for (int j = tid; j < n_vis; j += ATT_THREADS) {
         const float v = __fmul_rn(__fadd_rn(sc[j], 0.0f), p.scale);
         sc[j] = v;
         m = fmaxf(m, v);
@@ -97,29 +102,32 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
     m = red[0];
 #pragma unroll
     for (int w = 1; w < ATT_WARPS; ++w) { m = fmaxf(m, red[w]); }
-    for (int j = tid; j < n_kv; j += ATT_THREADS) { sc[j] = p.exp_table[f2h(__fsub_rn(sc[j], m))]; }
+    for (int j = tid; j < n_tot; j += ATT_THREADS) { sc[j] = (j < n_vis) ? p.exp_table[f2h(__fsub_rn(sc[j], m))] : 0.f; }
     __syncthreads();
-    if (tid == 0) { bcast = __fdiv_rn(1.0f, reduce4_chain(sc, n_kv)); }
+    if (tid == 0) { bcast = __fdiv_rn(1.0f, reduce4_chain(sc, n_tot)); }
     __syncthreads();
     const float inv = bcast;
     // probabilities, rounded to fp16 as the PV MatMul does with its f32 operand
-    for (int j = tid; j < n_kv; j += ATT_THREADS) { sc[j] = __half2float(__float2half_rn(__fmul_rn(sc[j], inv))); }
+    for (int j = tid; j < n_vis; j += ATT_THREADS) { sc[j] = __half2float(__float2half_rn(__fmul_rn(sc[j], inv))); }
     __syncthreads();
 
-    // ---- out[e] = Dot<FP16,FP16>(V_t[e][0..n_kv), probs)
-    const int n_main = ((n_kv - 1) / 32) * 32;
+    // ---- out[e] = Dot<FP16,FP16>(V_t[e][0..n_tot), probs); masked positions have probability +0 and leave every
+    // accumulator unchanged, so they are skipped (their cache entries may not be written yet)
+    const int n_main = ((n_tot - 1) / 32) * 32;
     for (int eb = warp * 32; eb < hd; eb += ATT_WARPS * 32) {
         float simd_mine = 0.f;
         for (int i = 0; i < 32; ++i) {
             const __half *vrow = p.v_cache + ((int64_t)h * hd + eb + i) * p.n_ctx;
             float acc = 0.f;
-            for (int j = 0; j < n_main; j += 32) { acc = fmaf(__half2float(vrow[j + lane]), sc[j + lane], acc); }
+            for (int j = 0; j < n_main && j < n_vis; j += 32) {
+                if (j + lane < n_vis) { acc = fmaf(__half2float(vrow[j + lane]), sc[j + lane], acc); }
+            }
             acc = reduce_f16dot_lanes(acc);
             if (lane == i) { simd_mine = acc; }
         }
         const __half *vrow = p.v_cache + ((int64_t)h * hd + eb + lane) * p.n_ctx;
         float tail = 0.f;
-        for (int j = n_main; j < n_kv; ++j) { tail = fmaf(__half2float(vrow[j]), sc[j], tail); }
+        for (int j = n_main; j < n_vis; ++j) { tail = fmaf(__half2float(vrow[j]), sc[j], tail); }
         p.out[(int64_t)t * p.dl + (int64_t)h * hd + eb + lane] = __fadd_rn(tail, simd_mine);
     }
 }

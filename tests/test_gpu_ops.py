@@ -301,14 +301,15 @@ def test_alloc_free_reuse_and_callback(be):
     assert be.get_max_memory_capacity() > 100 << 30 and be.get_avail_memory_capacity() > 0
 
 
-def _attention_oracle(oracle, q16, k16, vt16, pos0, n_head, hd, n_ctx):
-    """The reference attention sub-graph composed from oracle primitives, one (token, head) at a time."""
+def _attention_oracle(oracle, q16, k16, vt16, pos0, n_head, hd, n_ctx, n_total=0):
+    """The reference attention sub-graph composed from oracle primitives, one (token, head) at a time. Every row
+    spans all n_total positions of the step; the causal mask (-inf) zeroes the ones after the token itself."""
     t, d = q16.shape
     scale = float(np.float32(1.0) / np.sqrt(np.float32(hd)))
     out = np.zeros((t, d), dtype=np.float32)
+    n_kv = n_total if n_total else pos0 + t
     for i in range(t):
-        n_kv = pos0 + i + 1
-        mask = np.zeros(n_kv, dtype=np.float32)
+        mask = np.where(np.arange(n_kv) <= pos0 + i, np.float32(0), np.float32(-np.inf)).astype(np.float32)
         for h in range(n_head):
             qh = np.ascontiguousarray(q16[i, h * hd:(h + 1) * hd])
             sc = np.array([oracle.dot("f16_f16", np.ascontiguousarray(k16[j, h * hd:(h + 1) * hd]), qh, hd) for j in range(n_kv)], dtype=np.float32)
@@ -318,9 +319,10 @@ def _attention_oracle(oracle, q16, k16, vt16, pos0, n_head, hd, n_ctx):
     return out
 
 
-@pytest.mark.parametrize("pos0,t", [(0, 1), (0, 4), (4, 4), (6, 1), (30, 3), (31, 2), (63, 2), (100, 1)])
+@pytest.mark.parametrize("pos0,t,n_total", [(0, 1, 0), (0, 4, 0), (4, 4, 0), (6, 1, 0), (30, 3, 0), (31, 2, 0), (63, 2, 0), (100, 1, 0),
+                                            (0, 4, 8), (4, 3, 9), (28, 4, 37), (60, 4, 70), (0, 8, 8)])
 @pytest.mark.parametrize("spread", [0.5, 4.0, 30.0])
-def test_fused_attention_bits(be, oracle, pos0, t, spread):
+def test_fused_attention_bits(be, oracle, pos0, t, n_total, spread):
     """Fused scores / softmax / PV against the oracle on wide-range values, across the 32-element boundaries of
     both dot products (n_kv = 1 .. 101)."""
     rng = np.random.default_rng(pos0 * 7 + t + int(spread * 10))
@@ -330,6 +332,13 @@ def test_fused_attention_bits(be, oracle, pos0, t, spread):
     q16 = oracle.quantize_f16(wide(t * d)).reshape(t, d)
     k16 = oracle.quantize_f16(wide(n_ctx * d)).reshape(n_ctx, d)
     vt16 = oracle.quantize_f16(wide(n_ctx * d)).reshape(d, n_ctx)
-    got = be.attention(q16, k16, vt16, pos0, n_head, hd, n_ctx)
-    want = _attention_oracle(oracle, q16, k16, vt16, pos0, n_head, hd, n_ctx)
+    got = be.attention(q16, k16, vt16, pos0, n_head, hd, n_ctx, n_total)
+    want = _attention_oracle(oracle, q16, k16, vt16, pos0, n_head, hd, n_ctx, n_total)
     assert np.array_equal(bits(got), bits(want))
+
+
+def test_lookup_tables_identical_for_every_key(be, oracle):
+    silu, ex = be.read_tables()
+    want_silu, want_exp = oracle.tables()
+    assert np.array_equal(bits(silu), bits(want_silu))
+    assert np.array_equal(bits(ex), bits(want_exp))
