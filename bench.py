@@ -172,6 +172,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--profile-kernel", type=int, default=-1, metavar="KIND",
+                    help="load the model, run two sweeps of one mat-vec kind over all layers (0 qkv, 1 attn_out, 2 ffn_up_gate, 3 ffn_down, 4 head) and exit: the small case for an ncu capture")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -209,6 +211,13 @@ def main():
         model.init_tp(uid[0])
     info = model.info
     prompt = prompt_ids(info.n_vocab)
+    if args.profile_kernel >= 0:
+        import ctypes as C
+        nbytes = C.c_uint64()
+        ms = be._l.spyb_model_bench_kernel(model.h, args.profile_kernel, 2, C.byref(nbytes))
+        print(json.dumps({"profile_kernel": args.profile_kernel, "us_per_launch": ms * 1e3, "bytes_per_launch": int(nbytes.value)}))
+        model.close(); be.close()
+        return
 
     steps, warmup = args.steps, max(3, args.warmup)
     room = N_CTX - N_PROMPT - 1
@@ -302,8 +311,6 @@ def bench_kernels(model, be):
     """Each mat-vec kind launched alone, back to back over all layers (weights come from HBM each time)."""
     import ctypes as C
     l = be._l
-    l.spyb_model_bench_kernel.restype = C.c_float
-    l.spyb_model_bench_kernel.argtypes = [C.c_void_p, C.c_int32, C.c_int32, C.POINTER(C.c_uint64)]
     out = {}
     for kind, name in enumerate(["qkv", "attn_out", "ffn_up_gate", "ffn_down", "head"]):
         nbytes = C.c_uint64()

@@ -172,6 +172,7 @@ spyb_status spyb_create(const spyb_config *config, spyb_backend **out) {
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, config->device_id) != cudaSuccess) { delete be; return SPYB_FAIL; }
     be->num_sms = prop.multiProcessorCount;
+    if (const char *v = std::getenv("SPYB_MV_CTAS_PER_SM")) { be->mv_ctas_per_sm = std::max(1, std::min(2, std::atoi(v))); }   // tuning knob
     if (cudaStreamCreateWithFlags(&be->stream, cudaStreamNonBlocking) != cudaSuccess) { delete be; return SPYB_FAIL; }
     const size_t arena = config->arena_bytes ? config->arena_bytes : (size_t)256 << 20;
     if (!be->arena.init(arena)) { cudaStreamDestroy(be->stream); delete be; return SPYB_FAIL; }

@@ -53,6 +53,7 @@ struct PendingCallback {
 struct spyb_backend {
     spyb_config  config{};
     int          num_sms = 148;
+    int          mv_ctas_per_sm = 1;
     cudaStream_t stream = nullptr;
     spyb::Arena  arena;
     float       *d_silu_table = nullptr;   // 65536 entries: xh / (1 + expf(-xh)) for the fp16 value xh
@@ -81,7 +82,7 @@ struct spyb_backend {
         last_error = buf;
     }
     spyb::LaunchCfg launch_cfg(bool pdl) const {
-        spyb::LaunchCfg c; c.stream = stream; c.pdl = pdl; c.num_sms = num_sms; return c;
+        spyb::LaunchCfg c; c.stream = stream; c.pdl = pdl; c.num_sms = num_sms; c.mv_ctas_per_sm = mv_ctas_per_sm; return c;
     }
 };
 

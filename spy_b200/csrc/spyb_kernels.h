@@ -30,8 +30,8 @@ enum Epilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_SILU_MUL = 2, EPI_QKV_ROPE = 3
 struct MatvecParams {
     DevMatrix A;
     DevMatrix B;               // second matrix when pair_mode == 1 (same shape as A)
-    int       pair_mode = 0;   // 0: a warp owns rows (2u, 2u+1) of A; 1: it owns row u of A and row u of B
-    int       T = 1;           // activation columns (tokens) in this launch, <= 8
+    int       pair_mode = 0;   // 0: a warp's unit is rows 4u..4u+3 of A; 1: rows 2u, 2u+1 of A interleaved with the same rows of B
+    int       T = 1;           // activation columns (tokens) in this launch, <= matvec_max_columns(nb)
     // prologue
     int          pro = PRO_QUANT;
     const float *x = nullptr;  // [T][x_stride] f32
@@ -72,6 +72,7 @@ struct LaunchCfg {
     cudaStream_t stream = nullptr;
     bool         pdl = false;   // launch with the programmatic-stream-serialization attribute
     int          num_sms = 148;
+    int          mv_ctas_per_sm = 1;   // mat-vec CTAs per SM for single-column launches (their register budget allows 2)
 };
 
 size_t      matvec_smem_bytes(int nb, int T);

@@ -129,12 +129,12 @@ __device__ __forceinline__ void matvec_prologue(const MatvecParams &p, ActView a
 __device__ __forceinline__ void matvec_tap(const MatvecParams &p, ActView act) {
     if (p.tap_xq == nullptr || blockIdx.x != 0) { return; }
     for (int b = threadIdx.x; b < act.nb; b += MV_THREADS) {
-        uint8_t *o = p.tap_xq + (size_t)b * 34;
-        const uint16_t dh = f2h(act.d[b]);
-        o[0] = (uint8_t)(dh & 0xff); o[1] = (uint8_t)(dh >> 8);
+        volatile uint8_t *o = p.tap_xq + (size_t)b * 34;   // 34-byte records: only byte alignment holds
+        const uint32_t dh = f2h(act.d[b]);
         const uint8_t *lo = reinterpret_cast<const uint8_t *>(act.lo + b);
         const uint8_t *hi = reinterpret_cast<const uint8_t *>(act.hi + b);
         for (int i = 0; i < 16; ++i) { o[2 + i] = lo[i]; o[18 + i] = hi[i]; }
+        *reinterpret_cast<volatile uint16_t *>(p.tap_xq + (size_t)b * 34) = (uint16_t)dh;   // records start on even addresses
     }
 }
 
@@ -347,7 +347,7 @@ static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) 
         smem_allowed = smem;
     }
     const int64_t n_units = p.pair_mode ? (p.A.n_rows >> 1) : (p.A.n_rows >> 2);
-    int grid = cfg.num_sms;
+    int grid = cfg.num_sms * ((TM == 1) ? cfg.mv_ctas_per_sm : 1);
     if ((int64_t)grid * MV_WARPS > n_units) { grid = (int)((n_units + MV_WARPS - 1) / MV_WARPS); }
     if (grid < 1) { grid = 1; }
 
