@@ -72,26 +72,28 @@ size_t Arena::available() {
 spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, DevMatrix *out) {
     if (type != SPYB_Q4_0 && type != SPYB_Q8_0) { be->set_error("weight type %d has no device layout", type); return SPYB_UNSUPPORTED; }
     DevMatrix m;
-    m.type = type; m.n_rows = n_rows; m.nb = nb; m.k = (int64_t)nb * QK;
-    const size_t nblk = (size_t)n_rows * nb;
-    void *qa = nullptr, *qb = nullptr, *d = nullptr;
-    SPYB_CUDA(be, cudaMalloc(&qa, nblk * 16 + 16));
-    be->owned.push_back(qa);
-    if (type == SPYB_Q8_0) { SPYB_CUDA(be, cudaMalloc(&qb, nblk * 16 + 16)); be->owned.push_back(qb); }
-    SPYB_CUDA(be, cudaMalloc(&d, nblk * 2 + 16));
+    m.type = type; m.n_rows = n_rows; m.nb = nb; m.nbp = padded_blocks(nb); m.k = (int64_t)nb * QK;
+    void *q = nullptr, *d = nullptr;
+    SPYB_CUDA(be, cudaMalloc(&q, q_plane_bytes(type, n_rows, nb) + 16));
+    be->owned.push_back(q);
+    SPYB_CUDA(be, cudaMalloc(&d, d_plane_bytes(n_rows, nb) + 16));
     be->owned.push_back(d);
-    m.qa = static_cast<const uint4 *>(qa); m.qb = static_cast<const uint4 *>(qb); m.d = static_cast<const uint16_t *>(d);
+    m.q = static_cast<const uint4 *>(q); m.d = static_cast<const uint16_t *>(d);
     *out = m;
     return SPYB_SUCCESS;
 }
 
 spyb_status upload_matrix(spyb_backend *be, int type, const uint8_t *host_rows, int64_t n_rows, int64_t row_stride_bytes,
-                          int64_t blk0, int nb, DevMatrix *out, uint4 *qa_dst, uint4 *qb_dst, uint16_t *d_dst) {
-    if (qa_dst == nullptr) {
+                          int64_t blk0, int nb, DevMatrix *out, const DevMatrix *into, int64_t dst_row) {
+    if (into == nullptr) {
         spyb_status st = alloc_matrix(be, type, n_rows, nb, out);
         if (st != SPYB_SUCCESS) { return st; }
-        qa_dst = const_cast<uint4 *>(out->qa); qb_dst = const_cast<uint4 *>(out->qb); d_dst = const_cast<uint16_t *>(out->d);
+        into = out; dst_row = 0;
+    } else if (into->type != type || into->nb != nb || dst_row + n_rows > into->n_rows) {
+        be->set_error("weight upload: destination rows do not match"); return SPYB_FAIL;
     }
+    uint4    *q_dst = const_cast<uint4 *>(into->q) + (size_t)dst_row * q_row_words(type, nb);
+    uint16_t *d_dst = const_cast<uint16_t *>(into->d) + (size_t)dst_row * into->nbp;
     const int     bb = (type == SPYB_Q4_0) ? 18 : 34;
     const int64_t max_rows = std::max<int64_t>(1, (int64_t)(64u << 20) / row_stride_bytes);   // 64 MiB staging pieces
     void *stage = nullptr;
@@ -101,8 +103,7 @@ spyb_status upload_matrix(spyb_backend *be, int type, const uint8_t *host_rows, 
         cudaError_t err = cudaMemcpyAsync(stage, host_rows + r0 * row_stride_bytes, (size_t)nr * row_stride_bytes, cudaMemcpyHostToDevice, be->stream);
         if (err == cudaSuccess) {
             const uint8_t *raw = static_cast<const uint8_t *>(stage) + blk0 * bb;
-            err = (type == SPYB_Q4_0) ? launch_retile_q4_0(raw, row_stride_bytes, nr, nb, qa_dst + r0 * nb, d_dst + r0 * nb, be->stream)
-                                      : launch_retile_q8_0(raw, row_stride_bytes, nr, nb, qa_dst + r0 * nb, qb_dst + r0 * nb, d_dst + r0 * nb, be->stream);
+            err = launch_retile(type, raw, row_stride_bytes, nr, nb, q_dst + (size_t)r0 * q_row_words(type, nb), d_dst + (size_t)r0 * into->nbp, be->stream);
         }
         if (err == cudaSuccess) { err = cudaStreamSynchronize(be->stream); }
         if (err != cudaSuccess) { cudaFree(stage); be->set_error("weight upload failed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
@@ -172,6 +173,7 @@ spyb_status spyb_create(const spyb_config *config, spyb_backend **out) {
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, config->device_id) != cudaSuccess) { delete be; return SPYB_FAIL; }
     be->num_sms = prop.multiProcessorCount;
+    if (const char *v = std::getenv("SPYB_L2_PREFETCH_MB")) { const int mb = std::atoi(v); be->l2_prefetch_next = mb > 0; be->l2_prefetch_cap = (size_t)std::max(mb, 0) << 20; }   // tuning knob
     if (const char *v = std::getenv("SPYB_MV_CTAS_PER_SM")) { be->mv_ctas_per_sm = std::max(1, std::min(2, std::atoi(v))); }   // tuning knob
     if (cudaStreamCreateWithFlags(&be->stream, cudaStreamNonBlocking) != cudaSuccess) { delete be; return SPYB_FAIL; }
     const size_t arena = config->arena_bytes ? config->arena_bytes : (size_t)256 << 20;
@@ -267,9 +269,7 @@ void *spyb_upload_constant(spyb_backend *be, const char *name, const void *host_
         if (k % QK == 0 && rows > 0) {
             DevMatrix m;
             if (alloc_matrix(be, number_type, rows, (int)(k / QK), &m) != SPYB_SUCCESS) { return nullptr; }
-            cudaError_t err = number_type == SPYB_Q4_0
-                ? launch_retile_q4_0(static_cast<const uint8_t *>(raw), k / QK * bb, rows, m.nb, const_cast<uint4 *>(m.qa), const_cast<uint16_t *>(m.d), be->stream)
-                : launch_retile_q8_0(static_cast<const uint8_t *>(raw), k / QK * bb, rows, m.nb, const_cast<uint4 *>(m.qa), const_cast<uint4 *>(m.qb), const_cast<uint16_t *>(m.d), be->stream);
+            cudaError_t err = launch_retile(number_type, static_cast<const uint8_t *>(raw), k / QK * bb, rows, m.nb, const_cast<uint4 *>(m.q), const_cast<uint16_t *>(m.d), be->stream);
             if (err != cudaSuccess || cudaStreamSynchronize(be->stream) != cudaSuccess) { be->set_error("re-tiling of %s failed", name); return nullptr; }
             be->retiled[raw] = m;
         }
@@ -382,8 +382,9 @@ spyb_status run_matmul(spyb_backend *be, spyb_op_desc *d, void *out_dev) {
     }
     DevMatrix m;
     bool found = false;
-    void *tmp_qa = nullptr, *tmp_qb = nullptr, *tmp_d = nullptr;
-    const size_t nblk = (size_t)w.elements[1] * (size_t)(w.elements[0] / QK);
+    void *tmp_q = nullptr, *tmp_d = nullptr;
+    const int    nb_w = (int)(w.elements[0] / QK);
+    const size_t q_bytes = q_plane_bytes(w.number_type, w.elements[1], nb_w) + 16, d_bytes = d_plane_bytes(w.elements[1], nb_w) + 16;
     {
         std::lock_guard<std::mutex> g(be->const_mutex);
         auto it = be->retiled.find(w.data);
@@ -393,20 +394,18 @@ spyb_status run_matmul(spyb_backend *be, spyb_op_desc *d, void *out_dev) {
         // a quantized operand that did not come through spyb_upload_constant (its address may be reused for other
         // data later, so nothing is cached): re-tile into planes that live for this operator only
         const int64_t bb = w.number_type == SPYB_Q4_0 ? 18 : 34;
-        m.type = w.number_type; m.n_rows = w.elements[1]; m.nb = (int)(w.elements[0] / QK); m.k = w.elements[0];
-        tmp_qa = be->arena.alloc(nblk * 16 + 16); tmp_d = be->arena.alloc(nblk * 2 + 16);
-        if (w.number_type == SPYB_Q8_0) { tmp_qb = be->arena.alloc(nblk * 16 + 16); }
-        if (!tmp_qa || !tmp_d || (w.number_type == SPYB_Q8_0 && !tmp_qb)) { be->set_error("MatMul: out of device memory for re-tiled weights"); return SPYB_FAIL; }
-        m.qa = static_cast<const uint4 *>(tmp_qa); m.qb = static_cast<const uint4 *>(tmp_qb); m.d = static_cast<const uint16_t *>(tmp_d);
-        cudaError_t err = w.number_type == SPYB_Q4_0
-            ? launch_retile_q4_0(static_cast<const uint8_t *>(w.data), w.elements[0] / QK * bb, w.elements[1], m.nb, static_cast<uint4 *>(tmp_qa), static_cast<uint16_t *>(tmp_d), be->stream)
-            : launch_retile_q8_0(static_cast<const uint8_t *>(w.data), w.elements[0] / QK * bb, w.elements[1], m.nb, static_cast<uint4 *>(tmp_qa), static_cast<uint4 *>(tmp_qb), static_cast<uint16_t *>(tmp_d), be->stream);
+        m.type = w.number_type; m.n_rows = w.elements[1]; m.nb = nb_w; m.nbp = padded_blocks(nb_w); m.k = w.elements[0];
+        tmp_q = be->arena.alloc(q_bytes); tmp_d = be->arena.alloc(d_bytes);
+        if (!tmp_q || !tmp_d) { be->set_error("MatMul: out of device memory for re-tiled weights"); return SPYB_FAIL; }
+        m.q = static_cast<const uint4 *>(tmp_q); m.d = static_cast<const uint16_t *>(tmp_d);
+        cudaError_t err = launch_retile(w.number_type, static_cast<const uint8_t *>(w.data), w.elements[0] / QK * bb, w.elements[1], m.nb,
+                                        static_cast<uint4 *>(tmp_q), static_cast<uint16_t *>(tmp_d), be->stream);
         if (err != cudaSuccess) { be->set_error("MatMul: re-tiling failed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
     }
     struct TmpRelease {   // stream-ordered reuse: safe to hand back as soon as the kernels are enqueued
-        spyb_backend *be; void *a, *b, *c; size_t n;
-        ~TmpRelease() { if (a) { be->arena.free(a, n * 16 + 16); } if (b) { be->arena.free(b, n * 16 + 16); } if (c) { be->arena.free(c, n * 2 + 16); } }
-    } release{be, tmp_qa, tmp_qb, tmp_d, nblk};
+        spyb_backend *be; void *a, *b; size_t na, nb;
+        ~TmpRelease() { if (a) { be->arena.free(a, na); } if (b) { be->arena.free(b, nb); } }
+    } release{be, tmp_q, tmp_d, q_bytes, d_bytes};
     if (m.k != x.elements[0]) { be->set_error("MatMul: inner dimensions differ"); return SPYB_FAIL; }
     if (m.n_rows & 3) { be->set_error("MatMul: %lld output rows (quantized weights need a multiple of 4)", (long long)m.n_rows); return SPYB_UNSUPPORTED; }
     const int64_t T = x.elements[1] * x.elements[2] * x.elements[3];

@@ -31,10 +31,22 @@ __device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
-__device__ __forceinline__ uint16_t ldg_stream_u16(const uint16_t *p) {
-    uint16_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+__device__ __forceinline__ uint2 ldg_stream_u2(const uint2 *p) {
+    uint2 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
     return v;
+}
+
+// pull [ptr, ptr + bytes) towards L2; piece `idx` of `n_pieces` equal 16-byte-aligned pieces per call
+__device__ __forceinline__ void l2_prefetch_piece(const void *ptr, size_t bytes, int64_t idx, int64_t n_pieces) {
+    if (ptr == nullptr || bytes == 0) { return; }
+    const uintptr_t lo = reinterpret_cast<uintptr_t>(ptr) & ~(uintptr_t)15;
+    const uintptr_t hi = (reinterpret_cast<uintptr_t>(ptr) + bytes + 15) & ~(uintptr_t)15;
+    const size_t    piece = (((hi - lo) + n_pieces - 1) / n_pieces + 15) & ~(size_t)15;
+    const uintptr_t a = lo + (size_t)idx * piece;
+    if (a >= hi) { return; }
+    const uint32_t n = (uint32_t)min((size_t)(hi - a), piece);
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(__cvta_generic_to_global(reinterpret_cast<const void *>(a))), "r"(n) : "memory");
 }
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -72,39 +84,11 @@ __device__ __forceinline__ uint32_t quantize_q8_lane4(float4 v, uint16_t &d_half
 }
 
 // ---------------------------------------------------------------------------------------------
-// Activation columns as the mat-vec kernels keep them in shared memory (structure of arrays, so
-// that every lane's 128-bit read is conflict-free): for column t and block b
-//   lo[t][b]  = int8 values 0..15 of the block, hi[t][b] = values 16..31,
-//   blo[t][b] = four words MAGIC_I - 8 * (sum of values 4j..4j+3),        j = 0..3
-//   bhi[t][b] = four words MAGIC_I - 128 * (sum of values 16+4j..16+4j+3), j = 0..3
-//   d[t][b]   = f32 of the fp16-rounded scale.
-// The values are exactly those of the reference's block_q8_0_t (quant.h:124-147), regrouped; the two
-// bias planes are only needed for Q4_0 weights (they fold the "- 8" of every nibble and the
-// int -> float conversion into the accumulator operand of the byte dot product, see lanes_q4_0).
+// Integer lane sums are produced directly as floats: the accumulator operand of the byte dot product
+// carries MAGIC_I (plus, for Q4_0 weights, the "- 8 per nibble" correction), so that the result's bit
+// pattern is the float MAGIC_F + lane_sum and one exact subtraction yields (float)lane_sum.
 constexpr float    MAGIC_F = 12582912.0f;     // 1.5 * 2^23: int_as_float(MAGIC_I + p) == MAGIC_F + p exactly for |p| < 2^22
 constexpr uint32_t MAGIC_I = 0x4B400000u;
-
-struct ActView {
-    uint4 *lo;
-    uint4 *hi;
-    int4  *blo;
-    int4  *bhi;
-    float *d;
-    int    nb;  // blocks per column
-};
-
-__host__ __device__ inline size_t act_bytes(int nb, int t) { return (size_t)t * nb * (16 + 16 + 16 + 16 + 4); }
-
-__device__ __forceinline__ ActView act_view(void *base, int nb, int t) {
-    ActView v;
-    v.lo  = reinterpret_cast<uint4 *>(base);
-    v.hi  = v.lo + (size_t)t * nb;
-    v.blo = reinterpret_cast<int4 *>(v.hi + (size_t)t * nb);
-    v.bhi = v.blo + (size_t)t * nb;
-    v.d   = reinterpret_cast<float *>(v.bhi + (size_t)t * nb);
-    v.nb  = nb;
-    return v;
-}
 
 __device__ __forceinline__ int dp4a_us(uint32_t a_unsigned, uint32_t b_signed, int c) {
     int d;
@@ -112,34 +96,18 @@ __device__ __forceinline__ int dp4a_us(uint32_t a_unsigned, uint32_t b_signed, i
     return d;
 }
 
-// The eight integer "lane sums" of one Q4_0 block against one Q8_0 activation block, in the order of
-// the reference's 8-wide accumulator (Dot<Q4_0,Q8_0>::exec, backend/host/include/simd/vec_dot.h:58-75
-// with mul_sum_i8_pairs, vec_util.h:100-110): lanes 0..3 = sum over k = 4j..4j+3 of
-// (high nibble_k - 8) * y[16+k], lanes 4..7 = the same with low nibbles and y[k].
-// Returned already as floats: f[0..3] = 16 * lane sum (the high nibbles are used in place, i.e. scaled
-// by 16; the caller multiplies them by scale/16, which is exact), f[4..7] = lane sum.
-__device__ __forceinline__ void lanes_q4_0(const uint4 w, const uint4 ylo, const uint4 yhi, const int4 blo, const int4 bhi, float f[8]) {
-    f[0] = __int_as_float(dp4a_us(w.x & 0xf0f0f0f0u, yhi.x, bhi.x)) - MAGIC_F;
-    f[1] = __int_as_float(dp4a_us(w.y & 0xf0f0f0f0u, yhi.y, bhi.y)) - MAGIC_F;
-    f[2] = __int_as_float(dp4a_us(w.z & 0xf0f0f0f0u, yhi.z, bhi.z)) - MAGIC_F;
-    f[3] = __int_as_float(dp4a_us(w.w & 0xf0f0f0f0u, yhi.w, bhi.w)) - MAGIC_F;
-    f[4] = __int_as_float(dp4a_us(w.x & 0x0f0f0f0fu, ylo.x, blo.x)) - MAGIC_F;
-    f[5] = __int_as_float(dp4a_us(w.y & 0x0f0f0f0fu, ylo.y, blo.y)) - MAGIC_F;
-    f[6] = __int_as_float(dp4a_us(w.z & 0x0f0f0f0fu, ylo.z, blo.z)) - MAGIC_F;
-    f[7] = __int_as_float(dp4a_us(w.w & 0x0f0f0f0fu, ylo.w, blo.w)) - MAGIC_F;
+// One of the eight integer "lane sums" of a block pair, in the order of the reference's 8-wide accumulator
+// (Dot<Q4_0,Q8_0>::exec, backend/host/include/simd/vec_dot.h:58-75 with mul_sum_i8_pairs, vec_util.h:100-110:
+// lanes 0..3 = sum over k = 4j..4j+3 of (high nibble_k - 8) * y[16+k], lanes 4..7 = the same with low nibbles
+// and y[k]; Dot<Q8_0,Q8_0>::exec, vec_dot.h:103-113: lane l = sum of products 4l..4l+3), returned as a float.
+//   Q4_0: `w_masked` = the weight word with only this lane's nibbles kept (high nibbles stay in place, which
+//   scales the sum by 16; the caller multiplies by scale/16, which is exact), `bias` = MAGIC_I - 8 * (sum of
+//   the four y bytes) for low nibbles, MAGIC_I - 128 * sum for high nibbles.
+__device__ __forceinline__ float lane_sum_q4_0(uint32_t w_masked, uint32_t y, int bias) {
+    return __int_as_float(dp4a_us(w_masked, y, bias)) - MAGIC_F;
 }
-
-// Lane sums of one Q8_0 block (two 16-byte halves) against one Q8_0 activation block: lane l = sum of
-// products 4l..4l+3 (mul_sum_i8_pairs_float, vec_util.h:112-132; Dot<Q8_0,Q8_0>::exec, vec_dot.h:103-113).
-__device__ __forceinline__ void lanes_q8_0(const uint4 wa, const uint4 wb, const uint4 ylo, const uint4 yhi, float f[8]) {
-    f[0] = __int_as_float(__dp4a((int)wa.x, (int)ylo.x, (int)MAGIC_I)) - MAGIC_F;
-    f[1] = __int_as_float(__dp4a((int)wa.y, (int)ylo.y, (int)MAGIC_I)) - MAGIC_F;
-    f[2] = __int_as_float(__dp4a((int)wa.z, (int)ylo.z, (int)MAGIC_I)) - MAGIC_F;
-    f[3] = __int_as_float(__dp4a((int)wa.w, (int)ylo.w, (int)MAGIC_I)) - MAGIC_F;
-    f[4] = __int_as_float(__dp4a((int)wb.x, (int)yhi.x, (int)MAGIC_I)) - MAGIC_F;
-    f[5] = __int_as_float(__dp4a((int)wb.y, (int)yhi.y, (int)MAGIC_I)) - MAGIC_F;
-    f[6] = __int_as_float(__dp4a((int)wb.z, (int)yhi.z, (int)MAGIC_I)) - MAGIC_F;
-    f[7] = __int_as_float(__dp4a((int)wb.w, (int)yhi.w, (int)MAGIC_I)) - MAGIC_F;
+__device__ __forceinline__ float lane_sum_q8_0(uint32_t w, uint32_t y) {
+    return __int_as_float(__dp4a((int)w, (int)y, (int)MAGIC_I)) - MAGIC_F;
 }
 
 // hsum_float_8 (vec_util.h:74-81) over the 8 consecutive lanes that hold a0..a7:

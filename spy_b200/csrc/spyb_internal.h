@@ -53,7 +53,9 @@ struct PendingCallback {
 struct spyb_backend {
     spyb_config  config{};
     int          num_sms = 148;
-    int          mv_ctas_per_sm = 1;
+    int          mv_ctas_per_sm = 2;
+    bool         l2_prefetch_next = true;          // kernels pull the weights of the kernel two places later towards L2
+    size_t       l2_prefetch_cap = (size_t)32 << 20;   // at most this much of one matrix
     cudaStream_t stream = nullptr;
     spyb::Arena  arena;
     float       *d_silu_table = nullptr;   // 65536 entries: xh / (1 + expf(-xh)) for the fp16 value xh
@@ -99,10 +101,9 @@ namespace spyb {
 
 // upload raw reference-layout rows [n_rows][row_stride_bytes] (host) and re-tile the block range
 // [blk0, blk0 + nb) of every row into freshly allocated planes; used for row shards (contiguous rows)
-// and K shards (a block sub-range of each row) alike.
+// and K shards (a block sub-range of each row) alike. With `into`, the rows land at row dst_row of an existing matrix.
 spyb_status upload_matrix(spyb_backend *be, int type, const uint8_t *host_rows, int64_t n_rows, int64_t row_stride_bytes,
-                          int64_t blk0, int nb, DevMatrix *out, uint4 *qa_dst = nullptr, uint4 *qb_dst = nullptr,
-                          uint16_t *d_dst = nullptr);
+                          int64_t blk0, int nb, DevMatrix *out, const DevMatrix *into = nullptr, int64_t dst_row = 0);
 spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, DevMatrix *out);
 
 }  // namespace spyb

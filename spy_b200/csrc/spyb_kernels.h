@@ -7,22 +7,29 @@
 
 namespace spyb {
 
-// A quantized weight matrix resident in HBM, re-tiled at upload into planes so that every lane's
-// load is one aligned 128-bit word and a warp reads 512 contiguous bytes:
-//   Q4_0: qa[row][block] = the 16 nibble bytes of the block, d[row][block] = fp16 scale
-//   Q8_0: qa[row][block] = int8 values 0..15, qb[row][block] = values 16..31, d = fp16 scale
+// A quantized weight matrix resident in HBM, re-tiled at upload. Rows are padded to a multiple of four
+// blocks (nbp; the padding blocks are zeros with a zero scale) and every group of four consecutive
+// blocks of a row is stored word-transposed, so that the lane that owns accumulator l of the CPU's
+// 8-wide dot product loads, with one aligned 128-bit word, exactly its own four bytes of four blocks:
+//   Q4_0: q[row][group][j]  (j = 0..3)  = 32-bit word j of the 16 nibble bytes of blocks 4g..4g+3
+//   Q8_0: q[row][group][l]  (l = 0..7)  = 32-bit word l of the 32 int8 values of blocks 4g..4g+3
+//   d[row][block]                       = fp16 scale
 // The bytes are those of the reference's block_q4_0_t / block_q8_0_t
 // (orchestration/include/number/number_impl/quant.h:10-33, 124-147), only regrouped.
 struct DevMatrix {
     int             type = -1;
     int64_t         n_rows = 0;
     int64_t         k = 0;
-    int             nb = 0;
-    const uint4    *qa = nullptr;
-    const uint4    *qb = nullptr;
-    const uint16_t *d  = nullptr;
-    size_t bytes() const { return (size_t)n_rows * nb * ((type == 8 ? 32 : 16) + 2); }
+    int             nb = 0;    // blocks per row
+    int             nbp = 0;   // blocks per row in memory (nb rounded up to a multiple of 4)
+    const uint4    *q = nullptr;
+    const uint16_t *d = nullptr;
+    size_t bytes() const { return (size_t)n_rows * nb * ((type == 8 ? 32 : 16) + 2); }   // algorithmic bytes (without padding)
 };
+inline int    padded_blocks(int nb) { return (nb + 3) & ~3; }
+inline size_t q_row_words(int type, int nb) { return (size_t)padded_blocks(nb) * (type == 8 ? 2 : 1); }   // uint4 per row of the q plane
+inline size_t q_plane_bytes(int type, int64_t n_rows, int nb) { return (size_t)n_rows * q_row_words(type, nb) * 16; }
+inline size_t d_plane_bytes(int64_t n_rows, int nb) { return (size_t)n_rows * padded_blocks(nb) * 2; }
 
 enum Prologue { PRO_QUANT = 0, PRO_NORM_QUANT = 1 };
 enum Epilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_SILU_MUL = 2, EPI_QKV_ROPE = 3 };
@@ -30,7 +37,7 @@ enum Epilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_SILU_MUL = 2, EPI_QKV_ROPE = 3
 struct MatvecParams {
     DevMatrix A;
     DevMatrix B;               // second matrix when pair_mode == 1 (same shape as A)
-    int       pair_mode = 0;   // 0: a warp's unit is rows 4u..4u+3 of A; 1: rows 2u, 2u+1 of A interleaved with the same rows of B
+    int       pair_mode = 0;   // 1: a warp's tile is rows 4u..4u+3 of A together with the same rows of B (FFN up and gate)
     int       T = 1;           // activation columns (tokens) in this launch, <= matvec_max_columns(nb)
     // prologue
     int          pro = PRO_QUANT;
@@ -55,6 +62,9 @@ struct MatvecParams {
     int           n_ctx = 0;
     // optional tap: reference-layout Q8_0 blocks of column 0 (nb * 34 bytes)
     uint8_t      *tap_xq = nullptr;
+    // weights a later kernel of the step will stream: pulled into L2 once this CTA's own loads are issued
+    const void   *pf_ptr[4] = {nullptr, nullptr, nullptr, nullptr};
+    size_t        pf_bytes[4] = {0, 0, 0, 0};
 };
 
 struct AttnParams {
@@ -66,13 +76,15 @@ struct AttnParams {
     const float  *exp_table = nullptr;
     int   n_head = 0, hd = 128, dl = 0, T = 1, n_ctx = 0;
     float scale = 0.f;
+    const void *pf_ptr[4] = {nullptr, nullptr, nullptr, nullptr};   // as in MatvecParams
+    size_t      pf_bytes[4] = {0, 0, 0, 0};
 };
 
 struct LaunchCfg {
     cudaStream_t stream = nullptr;
     bool         pdl = false;   // launch with the programmatic-stream-serialization attribute
     int          num_sms = 148;
-    int          mv_ctas_per_sm = 1;   // mat-vec CTAs per SM for single-column launches (their register budget allows 2)
+    int          mv_ctas_per_sm = 2;   // mat-vec CTAs per SM for single-column launches (their register budget allows 2)
 };
 
 size_t      matvec_smem_bytes(int nb, int T);
@@ -81,8 +93,8 @@ cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg);
 cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg);
 
 // upload-time re-tiling of raw reference-layout blocks into DevMatrix planes
-cudaError_t launch_retile_q4_0(const uint8_t *raw, int64_t row_stride_bytes, int64_t n_rows, int nb, uint4 *qa, uint16_t *d, cudaStream_t s);
-cudaError_t launch_retile_q8_0(const uint8_t *raw, int64_t row_stride_bytes, int64_t n_rows, int nb, uint4 *qa, uint4 *qb, uint16_t *d, cudaStream_t s);
+// (q_row0, d_row0 point at the first destination row; nb blocks are read per row, the padding is zero-filled)
+cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride_bytes, int64_t n_rows, int nb, uint4 *q_row0, uint16_t *d_row0, cudaStream_t s);
 
 // stand-alone arithmetic kernels (parity checks and the per-operator path)
 cudaError_t launch_quantize_q8_0_ref_layout(const float *x, int64_t n, uint8_t *blocks, cudaStream_t s);

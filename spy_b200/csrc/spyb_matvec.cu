@@ -6,56 +6,67 @@
 // products, each updated block after block with acc = fma(d_w * d_x, (float)lane_sum, acc), and a fixed
 // reduction tree at the end. Because the network re-quantizes its activations at every layer, any
 // difference in f32 summation order is amplified to percent-level logit differences within a few layers,
-// so this kernel reproduces that order exactly:
-//   phase 1 (parallel over the row: lane = block)  weights streamed from HBM with 128-bit loads held in a
-//            register pipeline; per block the eight integer lane sums by byte dot products, converted to
-//            f32 without rounding, and the f32 block scale; both parked in shared memory
-//   phase 2 (sequential along the row: lane = (row, accumulator) for 4 rows x 8 accumulators) the 32
-//            blocks of the chunk are folded into the accumulators in block order with one FMA each
+// so this kernel reproduces that order exactly, by giving every one of the CPU's accumulators to one lane:
+//   lane = (row r of 4, accumulator l of 8); a warp owns a tile of 4*R rows (R rows per lane) and walks
+//   them along K four blocks at a time. Per group of four blocks a lane loads ONE 128-bit word per row
+//   (its own 4 bytes of each of the 4 blocks - the weights are stored word-transposed for this), masks its
+//   nibbles, takes four byte dot products against the Q8_0 activations in shared memory and folds them
+//   into its accumulator with four FMAs in block order. No shared-memory traffic for weights, no
+//   intra-warp synchronisation; the eight lanes of a row meet once per row in the reduction tree.
 // The small neighbouring operators of the LLaMa layer are folded into the prologue (RMSNorm + weight +
 // Q8_0 quantization, in the CPU's summation order) and the epilogue (residual add, SiLU-gate-mul,
 // RoPE + KV append).
 //
 // Roofline: HBM-bound. Algorithmic bytes per launch = rows * K/32 * 18 (Q4_0) or 34 (Q8_0); activations
-// and outputs are a few KB and stay in L2.
+// and outputs are a few KB and stay in L2. Weights are pulled towards L2 ahead of use with bulk
+// prefetches: a CTA's own rows before it waits for the previous kernel, and (optionally) the rows a later
+// kernel of the step will need once its own loads are in flight, so that HBM keeps streaming across
+// kernel boundaries and through the serial prologues.
 
 #include "spyb_common.cuh"
 #include "spyb_kernels.h"
 
 namespace spyb {
 
-constexpr int MV_THREADS = 256;
+constexpr int MV_THREADS = 512;
 constexpr int MV_WARPS   = MV_THREADS / WARP;
-constexpr int P_STRIDE   = 36;                       // floats per (row, accumulator) line: 32 blocks + pad, keeps 128-bit reads conflict-free
-constexpr int P_FLOATS   = 32 * P_STRIDE;            // lane sums: 4 rows x 8 accumulators
-constexpr int S_FLOATS   = 4 * P_STRIDE;             // block scales: 4 rows
-constexpr int WARP_SCRATCH_FLOATS = P_FLOATS + 2 * S_FLOATS;
 
-__host__ __device__ static inline size_t matvec_smem_layout(int nb, int TM, size_t *off_v3, size_t *off_warp) {
-    size_t o = act_bytes(nb, TM);
-    o = (o + 15) / 16 * 16;
-    *off_v3 = o;
-    o += (size_t)TM * (nb * 8) * sizeof(float);      // sum-of-squares partials: K/4 floats per column
-    o = (o + 15) / 16 * 16;
-    *off_warp = o;
-    o += (size_t)MV_WARPS * WARP_SCRATCH_FLOATS * sizeof(float);
-    return o + 16;
+// shared memory: per column t, per group g of four blocks
+//   Y [t][g][w][i]  (w = 0..7, i = 0..3)  word w of the 32 int8 values of block 4g+i (w 0..3 = values 0..15)
+//   Bq[t][g][w][i]  the accumulator operand for Q4_0 weights: MAGIC_I - 8 * (sum of the 4 bytes of that word)
+//                   for w < 4 (paired with low nibbles), MAGIC_I - 128 * sum for w >= 4 (high nibbles in place)
+//   DX[t][b], DX16[t][b]  f32 of the fp16-rounded scale, and the same divided by 16 (exact)
+// The sum-of-squares partials of the RMSNorm prologue alias Y (they are dead before Y is written).
+struct ActPlanes {
+    uint4  *Y;
+    int4   *Bq;
+    float4 *DX;
+    float4 *DX16;
+};
+__host__ __device__ static inline size_t act_plane_bytes(int nbp, int TM) { return (size_t)TM * nbp * (32 + 32 + 4 + 4); }
+__device__ __forceinline__ ActPlanes act_planes(void *base, int nbp, int TM) {
+    ActPlanes a;
+    a.Y    = reinterpret_cast<uint4 *>(base);
+    a.Bq   = reinterpret_cast<int4 *>(a.Y + (size_t)TM * nbp * 2);
+    a.DX   = reinterpret_cast<float4 *>(a.Bq + (size_t)TM * nbp * 2);
+    a.DX16 = a.DX + (size_t)TM * (nbp >> 2);
+    return a;
 }
 
-size_t matvec_smem_bytes(int nb, int T) { size_t a, b; return matvec_smem_layout(nb, T, &a, &b); }
+size_t matvec_smem_bytes(int nb, int T) { return act_plane_bytes(padded_blocks(nb), T) + 16; }
 
 // ---------------------------------------------------------------------------------------------
 // prologue: f32 activations -> Q8_0 columns in shared memory (optionally through RMSNorm * weight)
 //   NormRMS (backend/host/operator/non-linear.cpp:194-223): sum of squares by std::transform_reduce, whose
 //   order for random-access ranges is: groups of four combined as (x0^2 + x1^2) + (x2^2 + x3^2) (the first
-//   product of each pair plain, the second fused into an FMA, as the CPU build evaluates it) and added to the running sum one group after
-//   the other; y = x * (1 / sqrt(sum/n + eps)). The groups are formed in parallel, the running sum is
-//   one thread's chain. Mul (basic.cpp:15-50): y * norm_weight.
+//   product of each pair plain, the second fused into an FMA, as the CPU build evaluates it) and added to
+//   the running sum one group after the other; y = x * (1 / sqrt(sum/n + eps)). The groups are formed in
+//   parallel, the running sum is one thread's chain. Mul (basic.cpp:15-50): y * norm_weight.
 template <int TM>
-__device__ __forceinline__ void matvec_prologue(const MatvecParams &p, ActView act, float *v3, float *scales) {
+__device__ __forceinline__ void matvec_prologue(const MatvecParams &p, ActPlanes act, float *v3, float *scales) {
     const int     tid = threadIdx.x;
     const int64_t K   = p.A.k;
-    const int     nb  = p.A.nb;
+    const int     nb = p.A.nb, nbp = p.A.nbp;
     const int     n4  = (int)(K >> 2);
     if (p.pro == PRO_NORM_QUANT) {
         for (int t = 0; t < p.T; ++t) {
@@ -72,33 +83,32 @@ __device__ __forceinline__ void matvec_prologue(const MatvecParams &p, ActView a
             const float4 *g4 = reinterpret_cast<const float4 *>(v3 + tid * n4);
             float sum = 0.f;
             int g = 0;
-            for (; g + 4 <= n4; g += 4) {
-                const float4 q = g4[g >> 2];
-                sum = __fadd_rn(sum, q.x); sum = __fadd_rn(sum, q.y); sum = __fadd_rn(sum, q.z); sum = __fadd_rn(sum, q.w);
+            for (; g + 16 <= n4; g += 16) {   // four 128-bit reads ahead of their 16 dependent adds
+                const float4 q0 = g4[(g >> 2)], q1 = g4[(g >> 2) + 1], q2 = g4[(g >> 2) + 2], q3 = g4[(g >> 2) + 3];
+                sum = __fadd_rn(sum, q0.x); sum = __fadd_rn(sum, q0.y); sum = __fadd_rn(sum, q0.z); sum = __fadd_rn(sum, q0.w);
+                sum = __fadd_rn(sum, q1.x); sum = __fadd_rn(sum, q1.y); sum = __fadd_rn(sum, q1.z); sum = __fadd_rn(sum, q1.w);
+                sum = __fadd_rn(sum, q2.x); sum = __fadd_rn(sum, q2.y); sum = __fadd_rn(sum, q2.z); sum = __fadd_rn(sum, q2.w);
+                sum = __fadd_rn(sum, q3.x); sum = __fadd_rn(sum, q3.y); sum = __fadd_rn(sum, q3.z); sum = __fadd_rn(sum, q3.w);
             }
             for (; g < n4; ++g) { sum = __fadd_rn(sum, v3[tid * n4 + g]); }
             const float mean = __fdiv_rn(sum, (float)K);
             scales[tid] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
         }
-        __syncthreads();
+        __syncthreads();   // also: the partials (aliasing Y) are dead from here on
     }
+    uint32_t *Yw = reinterpret_cast<uint32_t *>(act.Y);
+    int      *Bw = reinterpret_cast<int *>(act.Bq);
+    float    *DX = reinterpret_cast<float *>(act.DX), *DX16 = reinterpret_cast<float *>(act.DX16);
+    const int n4p = nbp * 8;   // float4 groups including the zero padding up to nbp blocks
 #pragma unroll 1
     for (int t = 0; t < TM; ++t) {
-        if (t >= p.T) {
-            // unused columns: zero scales make every contribution vanish
-            for (int b = tid; b < nb; b += MV_THREADS) {
-                act.d[t * nb + b] = 0.f;
-                act.lo[t * nb + b] = make_uint4(0, 0, 0, 0); act.hi[t * nb + b] = make_uint4(0, 0, 0, 0);
-                act.blo[t * nb + b] = make_int4(MAGIC_I, MAGIC_I, MAGIC_I, MAGIC_I); act.bhi[t * nb + b] = make_int4(MAGIC_I, MAGIC_I, MAGIC_I, MAGIC_I);
-            }
-            continue;
-        }
-        const float4 *x4 = reinterpret_cast<const float4 *>(p.x + (int64_t)t * p.x_stride);
+        const bool    col  = t < p.T;    // unused columns are zeros with zero scales: every contribution vanishes
+        const float4 *x4 = reinterpret_cast<const float4 *>(p.x + (int64_t)(col ? t : 0) * p.x_stride);
         const float4 *w4 = reinterpret_cast<const float4 *>(p.norm_w);
-        const float scale = (p.pro == PRO_NORM_QUANT) ? scales[t] : 1.f;
-        for (int base = 0; base < n4; base += MV_THREADS) {
+        const float scale = (col && p.pro == PRO_NORM_QUANT) ? scales[t] : 1.f;
+        for (int base = 0; base < n4p; base += MV_THREADS) {
             const int  g     = base + tid;
-            const bool valid = g < n4;
+            const bool valid = col && g < n4;
             float4 v = valid ? x4[g] : make_float4(0.f, 0.f, 0.f, 0.f);
             if (p.pro == PRO_NORM_QUANT && valid) {
                 const float4 w = w4[g];
@@ -109,255 +119,257 @@ __device__ __forceinline__ void matvec_prologue(const MatvecParams &p, ActView a
             }
             uint16_t dh; int s;
             const uint32_t q = quantize_q8_lane4(v, dh, s);
-            if (valid) {
-                const int b  = g >> 3;
-                const int li = g & 7;
-                if (li < 4) {
-                    reinterpret_cast<uint32_t *>(act.lo + t * nb + b)[li] = q;
-                    reinterpret_cast<int *>(act.blo + t * nb + b)[li] = (int)MAGIC_I - 8 * s;
-                } else {
-                    reinterpret_cast<uint32_t *>(act.hi + t * nb + b)[li - 4] = q;
-                    reinterpret_cast<int *>(act.bhi + t * nb + b)[li - 4] = (int)MAGIC_I - 128 * s;
+            if (g < n4p) {
+                const int b = g >> 3, w = g & 7;
+                const int idx = ((t * (nbp >> 2) + (b >> 2)) * 8 + w) * 4 + (b & 3);
+                Yw[idx] = q;
+                Bw[idx] = (int)MAGIC_I - ((w < 4) ? 8 : 128) * s;
+                if (w == 0) {
+                    const float d = h2f(dh);
+                    DX[t * nbp + b] = d; DX16[t * nbp + b] = __fmul_rn(d, 0.0625f);
                 }
-                if (li == 0) { act.d[t * nb + b] = h2f(dh); }
             }
         }
     }
+    (void)nb;
 }
 
 // reference-layout copy of column 0 (34-byte blocks) for parity taps
-__device__ __forceinline__ void matvec_tap(const MatvecParams &p, ActView act) {
+__device__ __forceinline__ void matvec_tap(const MatvecParams &p, ActPlanes act) {
     if (p.tap_xq == nullptr || blockIdx.x != 0) { return; }
-    for (int b = threadIdx.x; b < act.nb; b += MV_THREADS) {
-        volatile uint8_t *o = p.tap_xq + (size_t)b * 34;   // 34-byte records: only byte alignment holds
-        const uint32_t dh = f2h(act.d[b]);
-        const uint8_t *lo = reinterpret_cast<const uint8_t *>(act.lo + b);
-        const uint8_t *hi = reinterpret_cast<const uint8_t *>(act.hi + b);
-        for (int i = 0; i < 16; ++i) { o[2 + i] = lo[i]; o[18 + i] = hi[i]; }
-        *reinterpret_cast<volatile uint16_t *>(p.tap_xq + (size_t)b * 34) = (uint16_t)dh;   // records start on even addresses
+    const uint32_t *Yw = reinterpret_cast<const uint32_t *>(act.Y);
+    const float    *DX = reinterpret_cast<const float *>(act.DX);
+    for (int b = threadIdx.x; b < p.A.nb; b += MV_THREADS) {
+        volatile uint8_t *o = p.tap_xq + (size_t)b * 34;   // 34-byte records: only 2-byte alignment holds
+        for (int w = 0; w < 8; ++w) {
+            const uint32_t v = Yw[((b >> 2) * 8 + w) * 4 + (b & 3)];
+            o[2 + 4 * w] = (uint8_t)v; o[3 + 4 * w] = (uint8_t)(v >> 8); o[4 + 4 * w] = (uint8_t)(v >> 16); o[5 + 4 * w] = (uint8_t)(v >> 24);
+        }
+        *reinterpret_cast<volatile uint16_t *>(p.tap_xq + (size_t)b * 34) = f2h(DX[b]);
     }
 }
 
 // ---------------------------------------------------------------------------------------------
-// epilogue for the four finished dot products r[0..3] of unit u, column t
-__device__ __forceinline__ void matvec_epilogue(const MatvecParams &p, int64_t u, int t, const float r[4]) {
+// epilogue for one finished dot product `v` (identical on the 8 lanes of its row) of row `row`, column t.
+// `partner` is the value of the neighbouring row (row ^ 1), needed by RoPE. Called by all lanes; lane l == 0 writes.
+__device__ __forceinline__ void matvec_epilogue(const MatvecParams &p, int64_t row, int t, float v, float partner, bool writer) {
     switch (p.epi) {
-    case EPI_STORE: {
-        float4 *o = reinterpret_cast<float4 *>(p.out + (int64_t)t * p.out_stride + 4 * u);
-        *o = make_float4(r[0], r[1], r[2], r[3]);
-    } break;
-    case EPI_RESID: {   // Add(attn_out, x) / Add(ffn_inp, ffn_out): model/src/llm/model/llama.cpp:194-211
-        const int64_t i = (int64_t)t * p.out_stride + 4 * u;
-        const float4 q = *reinterpret_cast<const float4 *>(p.resid + i);
-        *reinterpret_cast<float4 *>(p.out + i) = make_float4(__fadd_rn(r[0], q.x), __fadd_rn(r[1], q.y), __fadd_rn(r[2], q.z), __fadd_rn(r[3], q.w));
-    } break;
-    case EPI_SILU_MUL: {  // up * silu(gate): model/src/llm/plugin/ffn.cpp:28-35; silu = table on the fp16-rounded argument
-        float2 *o = reinterpret_cast<float2 *>(p.out + (int64_t)t * p.out_stride + 2 * u);
-        *o = make_float2(__fmul_rn(r[0], p.silu_table[f2h(r[1])]), __fmul_rn(r[2], p.silu_table[f2h(r[3])]));
-    } break;
+    case EPI_STORE:
+        if (writer) { p.out[(int64_t)t * p.out_stride + row] = v; }
+        break;
+    case EPI_RESID:   // Add(attn_out, x) / Add(ffn_inp, ffn_out): model/src/llm/model/llama.cpp:194-211
+        if (writer) { const int64_t i = (int64_t)t * p.out_stride + row; p.out[i] = __fadd_rn(v, p.resid[i]); }
+        break;
     case EPI_QKV_ROPE: {
-        const int64_t row = 4 * u;
-        const int     sec = (int)(row / p.dl);
-        const int     e   = (int)(row - (int64_t)sec * p.dl);
-        const int     pos = *p.pos_base + t;
+        if (!writer) { break; }
+        const int sec = (int)(row / p.dl);
+        const int e   = (int)(row - (int64_t)sec * p.dl);
+        const int pos = *p.pos_base + t;
         if (sec == 2) {   // V: f32 -> f16 RNE into the transposed cache [dl][n_ctx] (dup_execute, backend/host/operator/view.cpp:163-191)
-#pragma unroll
-            for (int k = 0; k < 4; ++k) { p.v_cache[(int64_t)(e + k) * p.n_ctx + pos] = __float2half_rn(r[k]); }
-        } else {          // RoPE, mode Norm: backend/host/operator/non-linear.cpp:270-371
-            const int    i0 = (e % p.hd) >> 1;
-            const float2 c0 = p.rope_table[(int64_t)pos * (p.hd >> 1) + i0];
-            const float2 c1 = p.rope_table[(int64_t)pos * (p.hd >> 1) + i0 + 1];
-            const float a0 = __fsub_rn(__fmul_rn(r[0], c0.x), __fmul_rn(r[1], c0.y));
-            const float a1 = __fadd_rn(__fmul_rn(r[0], c0.y), __fmul_rn(r[1], c0.x));
-            const float a2 = __fsub_rn(__fmul_rn(r[2], c1.x), __fmul_rn(r[3], c1.y));
-            const float a3 = __fadd_rn(__fmul_rn(r[2], c1.y), __fmul_rn(r[3], c1.x));
-            __half *base = (sec == 0) ? p.q_out + (int64_t)t * p.dl + e : p.k_cache + (int64_t)pos * p.dl + e;
-            reinterpret_cast<__half2 *>(base)[0] = __halves2half2(__float2half_rn(a0), __float2half_rn(a1));
-            reinterpret_cast<__half2 *>(base)[1] = __halves2half2(__float2half_rn(a2), __float2half_rn(a3));
+            p.v_cache[(int64_t)e * p.n_ctx + pos] = __float2half_rn(v);
+        } else {          // RoPE, mode Norm: backend/host/operator/non-linear.cpp:270-371 (rows 2i, 2i+1 rotate together)
+            const float2 cs = p.rope_table[(int64_t)pos * (p.hd >> 1) + ((e % p.hd) >> 1)];
+            const float x0 = (e & 1) ? partner : v, x1 = (e & 1) ? v : partner;
+            const float a = (e & 1) ? __fadd_rn(__fmul_rn(x0, cs.y), __fmul_rn(x1, cs.x))
+                                    : __fsub_rn(__fmul_rn(x0, cs.x), __fmul_rn(x1, cs.y));
+            __half *dst = (sec == 0) ? p.q_out + (int64_t)t * p.dl + e : p.k_cache + (int64_t)pos * p.dl + e;
+            *dst = __float2half_rn(a);
         }
     } break;
     default: break;
     }
 }
 
-// ---------------------------------------------------------------------------------------------
-// Register pipeline: D work items in flight per lane. One item = one 32-block chunk of a 4-row unit,
-// i.e. per lane one block of each of the four rows: D * 4 * 16 B (Q4_0) of loads per lane outstanding,
-// 256 threads * 256 B = 64 KB per SM, enough to cover HBM latency.
-template <int WT> struct Pipe;
-template <> struct Pipe<2> { static constexpr int D = 4; };   // Q4_0
-template <> struct Pipe<8> { static constexpr int D = 2; };   // Q8_0
+// up * silu(gate): model/src/llm/plugin/ffn.cpp:28-35; silu = table on the fp16-rounded argument
+__device__ __forceinline__ void matvec_epilogue_silu(const MatvecParams &p, int64_t row, int t, float up, float gate, bool writer) {
+    if (writer) { p.out[(int64_t)t * p.out_stride + row] = __fmul_rn(up, p.silu_table[f2h(gate)]); }
+}
 
-template <int WT, int TM>
+// ---------------------------------------------------------------------------------------------
+// Register pipeline: D groups of four blocks in flight per lane and row.
+template <int TM, int R> struct Pipe { static constexpr int D = (TM == 1) ? ((R == 1) ? 4 : 2) : 2; };
+
+template <int WT, int TM, int R>
 __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(const MatvecParams p) {
     extern __shared__ __align__(16) uint8_t smem_raw[];
     __shared__ float norm_scales[8];
-    constexpr int D  = Pipe<WT>::D;
-    constexpr int DB = (WT == 8) ? D : 1;
+    constexpr int D  = Pipe<TM, R>::D;
+    constexpr int QW = (WT == 8) ? 8 : 4;     // 128-bit words per group of four blocks in the q plane
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int nb     = p.A.nb;
-    const int nchunk = (nb + 31) >> 5;
+    const int r = lane >> 3, l = lane & 7;
+    const int nbp = p.A.nbp;
+    const int ng  = nbp >> 2;
 
-    // unit = 4 rows: rows 4u..4u+3 of A, or (pair mode) rows 2u, 2u+1 of A interleaved with the same rows of B
-    const int64_t n_units     = p.pair_mode ? (p.A.n_rows >> 1) : (p.A.n_rows >> 2);
-    const int64_t total_warps = (int64_t)gridDim.x * MV_WARPS;
-    const int64_t gw          = (int64_t)blockIdx.x * MV_WARPS + warp;
-    const int64_t u0          = n_units * gw / total_warps;
-    const int64_t u1          = n_units * (gw + 1) / total_warps;
-    const int64_t n_items     = (u1 - u0) * nchunk;
+    // tiles of this CTA (a contiguous range) and of this warp (every MV_WARPS-th of them)
+    const int64_t n_tiles = p.pair_mode ? (p.A.n_rows >> 2) : (p.A.n_rows / (4 * R));
+    const int64_t tile_lo = n_tiles * blockIdx.x / gridDim.x;
+    const int64_t tile_hi = n_tiles * (blockIdx.x + 1) / gridDim.x;
+    const int64_t my_first = tile_lo + warp;
+    const int64_t my_tiles = (my_first < tile_hi) ? (tile_hi - my_first + MV_WARPS - 1) / MV_WARPS : 0;
+    const int64_t n_items  = my_tiles * ng;
 
-    const int64_t ustride = p.pair_mode ? 2 * (int64_t)nb : 4 * (int64_t)nb;
-    const uint4 *qa_r[4]; const uint4 *qb_r[4]; const uint16_t *d_r[4];
+    // row i of the lane in tile u: rows 4R*u + 4i + r of A, or (pair mode) row 4u + r of A (i = 0) and of B (i = 1)
+    auto row_of = [&](int64_t u, int i) -> int64_t { return p.pair_mode ? 4 * u + r : 4 * R * u + 4 * i + r; };
+    const size_t qrow = (size_t)nbp * ((WT == 8) ? 2 : 1);
+    const int    qoff = (WT == 8) ? l : (l & 3);
+
+    uint4 wq[D][R];
+    uint2 ws[D][R];
+    auto load_item = [&](int j, int64_t u, int g) {
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-        const DevMatrix &M = (p.pair_mode && (r & 1)) ? p.B : p.A;
-        const int64_t ro = p.pair_mode ? (int64_t)(r >> 1) * nb : (int64_t)r * nb;
-        qa_r[r] = M.qa + ro; qb_r[r] = (WT == 8) ? M.qb + ro : nullptr; d_r[r] = M.d + ro;
-    }
-
-    uint4    wa[D][4];
-    uint4    wb[DB][4];
-    uint16_t wd[D][4];
-
-    auto load_item = [&](int j, int64_t u, int c) {
-        const int b = (c << 5) + lane;
-        if (b < nb) {
-            const int64_t off = u * ustride + b;
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                wa[j][r] = ldg_stream(qa_r[r] + off);
-                if (WT == 8) { wb[(WT == 8) ? j : 0][r] = ldg_stream(qb_r[r] + off); }
-                wd[j][r] = ldg_stream_u16(d_r[r] + off);
-            }
-        } else {
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                wa[j][r] = make_uint4(0, 0, 0, 0);
-                if (WT == 8) { wb[(WT == 8) ? j : 0][r] = make_uint4(0, 0, 0, 0); }
-                wd[j][r] = 0;
-            }
+        for (int i = 0; i < R; ++i) {
+            const DevMatrix &M   = (p.pair_mode && i == 1) ? p.B : p.A;
+            const int64_t    row = row_of(u, i);
+            wq[j][i] = ldg_stream(M.q + row * qrow + g * QW + qoff);
+            ws[j][i] = ldg_stream_u2(reinterpret_cast<const uint2 *>(M.d + row * nbp) + g);
         }
     };
 
-    // Let the next kernel of the step begin (its own weight prefetch), then prefetch ours: weights
-    // never change during a step, so these loads may run ahead of the previous kernel's results.
+    // Let the next kernel of the step begin, pull this CTA's rows towards L2 and start the register
+    // pipeline: weights never change during a step, so all of this may run ahead of the previous kernel's results.
     pdl_launch_dependents();
-    int64_t lu = u0; int lc = 0; int64_t issued = 0;
+    {
+        const int64_t rows_lo = p.pair_mode ? 4 * tile_lo : 4 * R * tile_lo, rows_hi = p.pair_mode ? 4 * tile_hi : 4 * R * tile_hi;
+        const size_t  qbytes = (size_t)(rows_hi - rows_lo) * qrow * 16, dbytes = (size_t)(rows_hi - rows_lo) * nbp * 2;
+        const int64_t nq = (int64_t)((qbytes + 4095) / 4096), nd = (int64_t)((dbytes + 4095) / 4096);
+        const int64_t per = nq + nd, total = per * (p.pair_mode ? 2 : 1);
+        for (int64_t i = threadIdx.x; i < total; i += MV_THREADS) {
+            const DevMatrix &M = (i >= per) ? p.B : p.A;
+            const int64_t    k = (i >= per) ? i - per : i;
+            if (k < nq) { l2_prefetch_piece(M.q + rows_lo * qrow, qbytes, k, nq); }
+            else        { l2_prefetch_piece(M.d + rows_lo * nbp, dbytes, k - nq, nd); }
+        }
+    }
+    int64_t lu = my_first; int lg = 0; int64_t issued = 0;
 #pragma unroll
     for (int j = 0; j < D; ++j) {
         if (issued < n_items) {
-            load_item(j, lu, lc);
-            ++issued; if (++lc == nchunk) { lc = 0; ++lu; }
+            load_item(j, lu, lg);
+            ++issued; if (++lg == ng) { lg = 0; lu += MV_WARPS; }
         }
     }
     pdl_wait();
 
-    size_t off_v3, off_warp;
-    matvec_smem_layout(nb, TM, &off_v3, &off_warp);
-    ActView act = act_view(smem_raw, nb, TM);
-    float *v3  = reinterpret_cast<float *>(smem_raw + off_v3);
-    float *P   = reinterpret_cast<float *>(smem_raw + off_warp) + warp * WARP_SCRATCH_FLOATS;
-    float *S   = P + P_FLOATS;            // block scales d_w * d_x per (row, block)
-    float *S16 = S + S_FLOATS;            // the same divided by 16 (Q4_0 high-nibble accumulators)
-    matvec_prologue<TM>(p, act, v3, norm_scales);
+    ActPlanes act = act_planes(smem_raw, nbp, TM);
+    matvec_prologue<TM>(p, act, reinterpret_cast<float *>(smem_raw), norm_scales);
     __syncthreads();
     matvec_tap(p, act);
 
-    float acc[TM];
-#pragma unroll
-    for (int t = 0; t < TM; ++t) { acc[t] = 0.f; }
-    const int    my_row = lane >> 3, my_acc = lane & 7;
-    const float *Pmine  = P + lane * P_STRIDE;
-    const float *Smine  = ((WT == 2 && my_acc < 4) ? S16 : S) + my_row * P_STRIDE;
+    // this lane's operands: activation word (Q8_0 weights: word l; Q4_0: lanes 0..3 hold the high nibbles, which meet
+    // values 16..31 = words 4..7), the matching accumulator operand and the scale plane
+    const int     wsel  = (WT == 8) ? l : (l ^ 4);
+    const uint4  *Ysel  = act.Y + wsel;
+    const int4   *Bsel  = act.Bq + wsel;
+    const float4 *DXsel = (WT == 2 && l < 4) ? act.DX16 : act.DX;
+    const uint32_t mask = (l < 4) ? 0xf0f0f0f0u : 0x0f0f0f0fu;
 
-    int64_t cu = u0; int cc = 0;
+    float acc[TM][R];
+#pragma unroll
+    for (int t = 0; t < TM; ++t) {
+#pragma unroll
+        for (int i = 0; i < R; ++i) { acc[t][i] = 0.f; }
+    }
+
+    int64_t cu = my_first; int cg = 0;
     for (int64_t base = 0; base < n_items; base += D) {
 #pragma unroll
         for (int j = 0; j < D; ++j) {
             if (base + j < n_items) {
-                const int  b     = (cc << 5) + lane;
-                const bool valid = b < nb;
-                const int  bq    = valid ? b : nb - 1;
-                const int  nval  = min(32, nb - (cc << 5));
-                const int  ngrp  = (nval + 3) >> 2;
-                float sw[4];
+                float s[R][4];
+                uint4 wm[R];
 #pragma unroll
-                for (int r = 0; r < 4; ++r) { sw[r] = h2f(wd[j][r]); }
+                for (int i = 0; i < R; ++i) {
+                    const __half2 s01 = *reinterpret_cast<const __half2 *>(&ws[j][i].x), s23 = *reinterpret_cast<const __half2 *>(&ws[j][i].y);
+                    const float2  f01 = __half22float2(s01), f23 = __half22float2(s23);
+                    s[i][0] = f01.x; s[i][1] = f01.y; s[i][2] = f23.x; s[i][3] = f23.y;
+                    wm[i] = wq[j][i];
+                    if (WT == 2) { wm[i].x &= mask; wm[i].y &= mask; wm[i].z &= mask; wm[i].w &= mask; }
+                }
 #pragma unroll
                 for (int t = 0; t < TM; ++t) {
-                    // ---- phase 1: this lane's block of each of the four rows
-                    const uint4 ylo = act.lo[t * nb + bq];
-                    const uint4 yhi = act.hi[t * nb + bq];
-                    const float yd  = valid ? act.d[t * nb + bq] : 0.f;
-                    int4 blo = make_int4(0, 0, 0, 0), bhi = make_int4(0, 0, 0, 0);
-                    if (WT == 2) { blo = act.blo[t * nb + bq]; bhi = act.bhi[t * nb + bq]; }
+                    const uint4  y  = Ysel[(t * ng + cg) * 8];
+                    const float4 dx = DXsel[t * ng + cg];
+                    int4 b = make_int4(0, 0, 0, 0);
+                    if (WT == 2) { b = Bsel[(t * ng + cg) * 8]; }
 #pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        float f[8];
-                        if (WT == 2) { lanes_q4_0(wa[j][r], ylo, yhi, blo, bhi, f); }
-                        else         { lanes_q8_0(wa[j][r], wb[(WT == 8) ? j : 0][r], ylo, yhi, f); }
-#pragma unroll
-                        for (int l = 0; l < 8; ++l) { P[(r * 8 + l) * P_STRIDE + lane] = f[l]; }
-                        const float d = __fmul_rn(sw[r], yd);
-                        S[r * P_STRIDE + lane] = d;
-                        if (WT == 2) { S16[r * P_STRIDE + lane] = __fmul_rn(d, 0.0625f); }
+                    for (int i = 0; i < R; ++i) {
+                        float a = acc[t][i];
+                        if (WT == 2) {
+                            a = fmaf(__fmul_rn(s[i][0], dx.x), lane_sum_q4_0(wm[i].x, y.x, b.x), a);
+                            a = fmaf(__fmul_rn(s[i][1], dx.y), lane_sum_q4_0(wm[i].y, y.y, b.y), a);
+                            a = fmaf(__fmul_rn(s[i][2], dx.z), lane_sum_q4_0(wm[i].z, y.z, b.z), a);
+                            a = fmaf(__fmul_rn(s[i][3], dx.w), lane_sum_q4_0(wm[i].w, y.w, b.w), a);
+                        } else {
+                            a = fmaf(__fmul_rn(s[i][0], dx.x), lane_sum_q8_0(wm[i].x, y.x), a);
+                            a = fmaf(__fmul_rn(s[i][1], dx.y), lane_sum_q8_0(wm[i].y, y.y), a);
+                            a = fmaf(__fmul_rn(s[i][2], dx.z), lane_sum_q8_0(wm[i].z, y.z), a);
+                            a = fmaf(__fmul_rn(s[i][3], dx.w), lane_sum_q8_0(wm[i].w, y.w), a);
+                        }
+                        acc[t][i] = a;
                     }
-                    __syncwarp();
-                    // ---- phase 2: lane (row, accumulator) folds the chunk's blocks in order
-                    float a = acc[t];
-#pragma unroll 2
-                    for (int g = 0; g < ngrp; ++g) {
-                        const float4 pv = *reinterpret_cast<const float4 *>(Pmine + 4 * g);
-                        const float4 sv = *reinterpret_cast<const float4 *>(Smine + 4 * g);
-                        a = fmaf(sv.x, pv.x, a); a = fmaf(sv.y, pv.y, a); a = fmaf(sv.z, pv.z, a); a = fmaf(sv.w, pv.w, a);
-                    }
-                    acc[t] = a;
-                    __syncwarp();
                 }
                 if (issued < n_items) {
-                    load_item(j, lu, lc);
-                    ++issued; if (++lc == nchunk) { lc = 0; ++lu; }
+                    load_item(j, lu, lg);
+                    ++issued; if (++lg == ng) { lg = 0; lu += MV_WARPS; }
                 }
-                if (++cc == nchunk) {   // unit finished: fixed reduction tree over the 8 accumulators of each row, then the epilogue
-                    float r4[4] = {0.f, 0.f, 0.f, 0.f};
+                if (++cg == ng) {   // tile finished: fixed reduction tree over the 8 accumulators of each row, then the epilogue
 #pragma unroll
                     for (int t = 0; t < TM; ++t) {
-                        const float h = hsum8_lanes(acc[t]);
-                        const float r0 = __shfl_sync(0xffffffffu, h, 0), r1 = __shfl_sync(0xffffffffu, h, 8);
-                        const float r2 = __shfl_sync(0xffffffffu, h, 16), r3 = __shfl_sync(0xffffffffu, h, 24);
-                        if (lane == t) { r4[0] = r0; r4[1] = r1; r4[2] = r2; r4[3] = r3; }
-                        acc[t] = 0.f;
+                        float h[R];
+#pragma unroll
+                        for (int i = 0; i < R; ++i) { h[i] = hsum8_lanes(acc[t][i]); acc[t][i] = 0.f; }
+                        const bool writer = (l == 0) && (t < p.T);
+                        if (p.epi == EPI_SILU_MUL) {
+                            if (R == 2) { matvec_epilogue_silu(p, row_of(cu, 0), t, h[0], h[R - 1], writer); }
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < R; ++i) {
+                                const float partner = __shfl_xor_sync(0xffffffffu, h[i], 8);
+                                matvec_epilogue(p, row_of(cu, i), t, h[i], partner, writer);
+                            }
+                        }
                     }
-                    if (lane < p.T) { matvec_epilogue(p, cu, lane, r4); }
-                    cc = 0; ++cu;
+                    cg = 0; cu += MV_WARPS;
                 }
             }
         }
     }
+
+    // weights a later kernel will stream: towards L2 while this kernel drains
+    {
+        const int64_t gw = (int64_t)blockIdx.x * MV_THREADS + threadIdx.x, gn = (int64_t)gridDim.x * MV_THREADS;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int64_t np = (int64_t)((p.pf_bytes[k] + 4095) / 4096);
+            for (int64_t i = gw; i < np; i += gn) { l2_prefetch_piece(p.pf_ptr[k], p.pf_bytes[k], i, np); }
+        }
+    }
 }
 
-template <int WT, int TM>
+template <int WT, int TM, int R>
 static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) {
     const size_t smem = matvec_smem_bytes(p.A.nb, TM);
     static size_t smem_allowed = 48 * 1024;   // one process drives one device, so one high-water mark per kernel suffices
     if (smem > smem_allowed) {
-        cudaError_t err = cudaFuncSetAttribute(matvec_kernel<WT, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t err = cudaFuncSetAttribute(matvec_kernel<WT, TM, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) { return err; }
         smem_allowed = smem;
     }
-    const int64_t n_units = p.pair_mode ? (p.A.n_rows >> 1) : (p.A.n_rows >> 2);
-    int grid = cfg.num_sms * ((TM == 1) ? cfg.mv_ctas_per_sm : 1);
-    if ((int64_t)grid * MV_WARPS > n_units) { grid = (int)((n_units + MV_WARPS - 1) / MV_WARPS); }
+    // every SM gets a CTA even when there are fewer tiles than warps: a tile is a sequential walk along K, so
+    // spreading tiles over all SMs (with some warps idle) beats filling a few CTAs
+    const int64_t n_tiles = p.pair_mode ? (p.A.n_rows >> 2) : (p.A.n_rows / (4 * R));
+    int64_t grid = (int64_t)cfg.num_sms * ((TM == 1) ? cfg.mv_ctas_per_sm : 1);
+    if (grid > n_tiles) { grid = n_tiles; }
     if (grid < 1) { grid = 1; }
 
     cudaLaunchConfig_t lc = {};
-    lc.gridDim = dim3(grid); lc.blockDim = dim3(MV_THREADS); lc.dynamicSmemBytes = smem; lc.stream = cfg.stream;
+    lc.gridDim = dim3((unsigned)grid); lc.blockDim = dim3(MV_THREADS); lc.dynamicSmemBytes = smem; lc.stream = cfg.stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&lc, matvec_kernel<WT, TM>, p);
+    return cudaLaunchKernelEx(&lc, matvec_kernel<WT, TM, R>, p);
 }
 
 int matvec_max_columns(int nb) {
@@ -365,22 +377,29 @@ int matvec_max_columns(int nb) {
     return 1;
 }
 
-template <int WT>
+template <int WT, int R>
 static cudaError_t launch_matvec_w(const MatvecParams &p, const LaunchCfg &cfg) {
-    if (p.T <= 1) { return launch_matvec_t<WT, 1>(p, cfg); }
-    if (p.T <= 2) { return launch_matvec_t<WT, 2>(p, cfg); }
-    if (p.T <= 4) { return launch_matvec_t<WT, 4>(p, cfg); }
-    return launch_matvec_t<WT, 8>(p, cfg);
+    if (p.T <= 1) { return launch_matvec_t<WT, 1, R>(p, cfg); }
+    if (p.T <= 2) { return launch_matvec_t<WT, 2, R>(p, cfg); }
+    if (p.T <= 4) { return launch_matvec_t<WT, 4, R>(p, cfg); }
+    return launch_matvec_t<WT, 8, R>(p, cfg);
 }
 
 cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg) {
     if (p.T < 1 || p.T > matvec_max_columns(p.A.nb)) { return cudaErrorInvalidValue; }
-    if (p.A.k % QK != 0 || p.A.nb < 1) { return cudaErrorInvalidValue; }
-    if (!p.pair_mode && (p.A.n_rows & 3)) { return cudaErrorInvalidValue; }
-    if (p.pair_mode && ((p.A.n_rows & 1) || p.B.type != p.A.type || p.B.n_rows != p.A.n_rows || p.B.k != p.A.k)) { return cudaErrorInvalidValue; }
+    if (p.A.k % QK != 0 || p.A.nb < 1 || p.A.nbp != padded_blocks(p.A.nb)) { return cudaErrorInvalidValue; }
+    if (p.A.n_rows & 3) { return cudaErrorInvalidValue; }
+    if (p.pair_mode && (p.B.type != p.A.type || p.B.n_rows != p.A.n_rows || p.B.k != p.A.k || p.B.nbp != p.A.nbp)) { return cudaErrorInvalidValue; }
+    if ((p.epi == EPI_SILU_MUL) != (p.pair_mode != 0)) { return cudaErrorInvalidValue; }
+    // rows per lane: two when one row per lane would leave tiles waiting for a free warp (single column), or in pair mode
+    bool two = p.pair_mode != 0;
+    if (!two && p.T == 1 && (p.A.n_rows & 7) == 0) {
+        const int64_t slots = (int64_t)cfg.num_sms * cfg.mv_ctas_per_sm * MV_WARPS;
+        two = (p.A.n_rows >> 2) > slots;
+    }
     switch (p.A.type) {
-    case 2: return launch_matvec_w<2>(p, cfg);
-    case 8: return launch_matvec_w<8>(p, cfg);
+    case 2: return two ? launch_matvec_w<2, 2>(p, cfg) : launch_matvec_w<2, 1>(p, cfg);
+    case 8: return two ? launch_matvec_w<8, 2>(p, cfg) : launch_matvec_w<8, 1>(p, cfg);
     default: return cudaErrorNotSupported;
     }
 }

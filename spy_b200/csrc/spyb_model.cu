@@ -194,6 +194,18 @@ spyb_status allreduce(spyb_model *m, float *buf, size_t count, int64_t *launches
     return SPYB_SUCCESS;
 }
 
+// planes of the matrices a later kernel of the step streams (at most two matrices)
+template <class P>
+void prefetch_next(spyb_model *m, P &p, const DevMatrix *a, const DevMatrix *b = nullptr) {
+    if (!m->be->l2_prefetch_next) { return; }
+    int k = 0;
+    for (const DevMatrix *x : {a, b}) {
+        if (x == nullptr || x->q == nullptr) { continue; }
+        p.pf_ptr[k] = x->q; p.pf_bytes[k] = std::min(q_plane_bytes(x->type, x->n_rows, x->nb), m->be->l2_prefetch_cap); ++k;
+        p.pf_ptr[k] = x->d; p.pf_bytes[k] = d_plane_bytes(x->n_rows, x->nb); ++k;
+    }
+}
+
 // the five fused kernels of every layer for T tokens whose first position is *d_pos
 spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
     spyb_backend *be = m->be;
@@ -208,6 +220,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             p.epi = EPI_QKV_ROPE; p.pos_base = m->d_pos; p.rope_table = m->rope_table; p.hd = m->info.head_dim; p.dl = m->dl;
             p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache; p.n_ctx = m->info.n_ctx;
             p.tap_xq = (tap && L == 0) ? m->d_tap : nullptr;
+            prefetch_next(m, p, &ly.wo);
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
         }
         {   // 2: attention
@@ -215,6 +228,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             a.q = m->q; a.k_cache = ly.k_cache; a.v_cache = ly.v_cache; a.out = m->att; a.pos_base = m->d_pos; a.exp_table = be->d_exp_table;
             a.n_head = m->dl / m->info.head_dim; a.hd = m->info.head_dim; a.dl = m->dl; a.T = T; a.n_ctx = m->info.n_ctx;
             a.scale = 1.0f / std::sqrt((float)m->info.head_dim);
+            prefetch_next(m, a, &ly.up, &ly.gate);
             SPYB_CUDA(be, launch_attention(a, cfg)); ++*launches;
         }
         {   // 3: quantize -> Wo -> + residual (tensor parallel: partial sums, rank 0 carries the residual)
@@ -223,6 +237,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             p.resid = m->x; p.out_stride = d;
             if (tp == 1) { p.epi = EPI_RESID; p.out = m->x; }
             else { p.epi = (m->info.tp_rank == 0) ? EPI_RESID : EPI_STORE; p.out = m->partial; }
+            prefetch_next(m, p, &ly.down);
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
             if (tp > 1) {
                 if (allreduce(m, m->partial, (size_t)T * d, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
@@ -233,6 +248,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             MatvecParams p;
             p.A = ly.up; p.B = ly.gate; p.pair_mode = 1; p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
             p.eps = m->info.rms_eps; p.epi = EPI_SILU_MUL; p.out = m->act; p.out_stride = m->fl; p.silu_table = be->d_silu_table;
+            prefetch_next(m, p, L + 1 < m->layers.size() ? &m->layers[L + 1].wqkv : &m->head);
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
         }
         {   // 5: quantize -> Wdown -> + residual
@@ -331,9 +347,7 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         I.weight_bytes += (uint64_t)n_rows * nb * (t->type == SPYB_Q4_0 ? 18 : 34);
         if (into != nullptr) {
             if (into->type != t->type) { be->set_error("GGUF: %s: Wq/Wk/Wv must share one type", name.c_str()); return SPYB_UNSUPPORTED; }
-            return upload_matrix(be, t->type, data + row0 * rb, n_rows, rb, blk0, nb, dst,
-                                 const_cast<uint4 *>(into->qa) + dst_row * nb, into->qb ? const_cast<uint4 *>(into->qb) + dst_row * nb : nullptr,
-                                 const_cast<uint16_t *>(into->d) + dst_row * nb);
+            return upload_matrix(be, t->type, data + row0 * rb, n_rows, rb, blk0, nb, dst, into, dst_row);
         }
         return upload_matrix(be, t->type, data + row0 * rb, n_rows, rb, blk0, nb, dst);
     };

@@ -28,20 +28,29 @@ __device__ __forceinline__ float reduce4_chain(const float *v, int n) {
 }
 
 // =============================================================================================
-// Attention for one (head, query token): a CTA of 8 warps.
+// Attention for one (head, query token): a CTA of 8 warps, head_dim 128.
 //   scores = K(f16) . fp16(Q)            MatMul with F16 weights: backend/host/operator/mat.cpp:32-42,
 //                                        Dot<FP16,FP16> backend/host/include/simd/vec_dot.h:117-146
 //   probs  = masked softmax, exp through the table of expf(fp16(s - max)), std::reduce sum
 //                                        backend/host/operator/non-linear.cpp:129-180
 //   out    = V(f16) . fp16(probs)        same MatMul rule; V is kept transposed [d][n_ctx] as the reference
 //                                        graph lays it out (model/src/llm/plugin/attention.cpp:228-262)
-// Dot<FP16,FP16> runs four 8-wide accumulators over 32-element steps while i + 32 < n and leaves the rest
-// (1..32 elements) to a scalar chain added as tail + vector part. Here a warp takes 32 dot products at a
-// time: the vector part of each one cooperatively (lane = accumulator element), then the 32 scalar tails
-// in parallel, one per lane.
+// Dot<FP16,FP16> runs four 8-wide accumulators over 32-element steps while i + 32 < n, reduces them as
+// (s0 + s2) + (s1 + s3), element l with l + 4, two horizontal adds, and leaves the rest (1..32 elements) to
+// a scalar FMA chain added as tail + vector part. All 32 accumulators of a dot product live in the
+// registers of ONE thread here (scores: one thread per position, the K row read with 128-bit loads) or of a
+// thread pair (PV: elements 0..3 / 4..7 of the four accumulators, the V^T row read with 64-bit loads), so the
+// reduction tree is register arithmetic and the dot products of a head run side by side.
 // Roofline: HBM-bound, 2 * n_kv * head_dim * 2 bytes per head read once; latency-bound at short contexts.
 constexpr int ATT_THREADS = 256;
 constexpr int ATT_WARPS   = ATT_THREADS / WARP;
+constexpr int ATT_HD      = 128;
+
+__device__ __forceinline__ void unpack8(const uint4 v, float f[8]) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&v.x)), b = __half22float2(*reinterpret_cast<const __half2 *>(&v.y));
+    const float2 c = __half22float2(*reinterpret_cast<const __half2 *>(&v.z)), d = __half22float2(*reinterpret_cast<const __half2 *>(&v.w));
+    f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
+}
 
 __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams p) {
     extern __shared__ __align__(16) float att_smem[];
@@ -50,9 +59,16 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
 
     const int h = blockIdx.x, t = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int hd = p.hd;
 
     pdl_launch_dependents();
+    {   // weights of a later kernel of the step: towards L2 while attention occupies only a few SMs
+        const int64_t gw = ((int64_t)blockIdx.y * gridDim.x + blockIdx.x) * ATT_THREADS + tid, gn = (int64_t)gridDim.x * gridDim.y * ATT_THREADS;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const int64_t np = (int64_t)((p.pf_bytes[k] + 4095) / 4096);
+            for (int64_t i = gw; i < np; i += gn) { l2_prefetch_piece(p.pf_ptr[k], p.pf_bytes[k], i, np); }
+        }
+    }
     pdl_wait();
 
     const int pos   = p.pos_base[0] + t;
@@ -62,30 +78,58 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
     // beyond the causal limit carry mask -inf: they become exact zeros, but they still decide how std::reduce groups
     // the sum and where Dot<FP16,FP16> switches from its vector loop to the scalar tail.
     const int n_tot = (p.pos_base[1] > 0) ? p.pos_base[1] : p.pos_base[0] + p.T;
-    float *sc = att_smem;                        // [n_ctx] scores, then probabilities
-    float *qf = att_smem + p.n_ctx;              // [hd] Q as f32 (exact widening of the fp16 values)
+    const int n_pad = (p.n_ctx + 3) & ~3;
+    float *qf = att_smem;                        // [hd] Q as f32 (exact widening of the fp16 values)
+    float *sc = qf + ATT_HD;                     // [n_pad] scores, then probabilities
+    float *gs = sc + n_pad;                      // [n_pad / 4] four-wide partial sums of std::reduce
 
-    for (int i = tid; i < hd; i += ATT_THREADS) { qf[i] = __half2float(p.q[(int64_t)t * p.dl + (int64_t)h * hd + i]); }
+    if (tid < ATT_HD) { qf[tid] = __half2float(p.q[(int64_t)t * p.dl + (int64_t)h * ATT_HD + tid]); }
     __syncthreads();
 
-    // ---- scores of the visible positions
-    const int k_main = ((hd - 1) / 32) * 32;     // elements covered by the vector loop (i + 32 < hd)
-    for (int jb = warp * 32; jb < n_vis; jb += ATT_WARPS * 32) {
-        const int npos = min(32, n_vis - jb);
-        float simd_mine = 0.f;
-        for (int i = 0; i < npos; ++i) {
-            const __half *krow = p.k_cache + (int64_t)(jb + i) * p.dl + (int64_t)h * hd;
-            float acc = 0.f;
-            for (int e = 0; e < k_main; e += 32) { acc = fmaf(__half2float(krow[e + lane]), qf[e + lane], acc); }
-            acc = reduce_f16dot_lanes(acc);
-            if (lane == i) { simd_mine = acc; }
+    // ---- scores of the visible positions: one thread per position
+    for (int j = tid; j < n_vis; j += ATT_THREADS) {
+        const uint4  *krow = reinterpret_cast<const uint4 *>(p.k_cache + (int64_t)j * p.dl + (int64_t)h * ATT_HD);
+        const float4 *q4   = reinterpret_cast<const float4 *>(qf);
+        float acc[4][8];
+        uint4 kv[4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { acc[a][e] = 0.f; }
         }
-        if (lane < npos) {
-            const __half *krow = p.k_cache + (int64_t)(jb + lane) * p.dl + (int64_t)h * hd;
-            float tail = 0.f;
-            for (int e = k_main; e < hd; ++e) { tail = fmaf(__half2float(krow[e]), qf[e], tail); }
-            sc[jb + lane] = __fadd_rn(tail, simd_mine);
+#pragma unroll
+        for (int step = 0; step < 3; ++step) {       // elements 0..95: accumulator a takes elements 32 * step + 8a .. + 7
+#pragma unroll
+            for (int a = 0; a < 4; ++a) { kv[a] = krow[4 * step + a]; }
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                float kf[8]; unpack8(kv[a], kf);
+                const float4 qa = q4[(4 * step + a) * 2], qb = q4[(4 * step + a) * 2 + 1];
+                const float  qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { acc[a][e] = fmaf(kf[e], qv[e], acc[a][e]); }
+            }
         }
+        float u[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float lo = __fadd_rn(__fadd_rn(acc[0][e], acc[2][e]), __fadd_rn(acc[1][e], acc[3][e]));
+            const float hi = __fadd_rn(__fadd_rn(acc[0][e + 4], acc[2][e + 4]), __fadd_rn(acc[1][e + 4], acc[3][e + 4]));
+            u[e] = __fadd_rn(lo, hi);
+        }
+        const float simd = __fadd_rn(__fadd_rn(u[0], u[1]), __fadd_rn(u[2], u[3]));
+        float tail = 0.f;                             // elements 96..127: scalar chain
+#pragma unroll
+        for (int a = 0; a < 4; ++a) { kv[a] = krow[12 + a]; }
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            float kf[8]; unpack8(kv[a], kf);
+            const float4 qa = q4[(12 + a) * 2], qb = q4[(12 + a) * 2 + 1];
+            const float  qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { tail = fmaf(kf[e], qv[e], tail); }
+        }
+        sc[j] = __fadd_rn(tail, simd);
     }
     __syncthreads();
 
@@ -102,39 +146,82 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
     m = red[0];
 #pragma unroll
     for (int w = 1; w < ATT_WARPS; ++w) { m = fmaxf(m, red[w]); }
-    for (int j = tid; j < n_tot; j += ATT_THREADS) { sc[j] = (j < n_vis) ? p.exp_table[f2h(__fsub_rn(sc[j], m))] : 0.f; }
+    const int n_tot4 = (n_tot + 3) & ~3;
+    for (int j = tid; j < n_tot4; j += ATT_THREADS) { sc[j] = (j < n_vis) ? p.exp_table[f2h(__fsub_rn(sc[j], m))] : 0.f; }
     __syncthreads();
-    if (tid == 0) { bcast = __fdiv_rn(1.0f, reduce4_chain(sc, n_tot)); }
+    // std::reduce: groups of four as (e0 + e1) + (e2 + e3), formed in parallel, then one thread's running sum; the
+    // remainder (n_tot % 4 elements) is added one by one
+    for (int g = tid; g < (n_tot >> 2); g += ATT_THREADS) {
+        const float4 v = reinterpret_cast<const float4 *>(sc)[g];
+        gs[g] = __fadd_rn(__fadd_rn(v.x, v.y), __fadd_rn(v.z, v.w));
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float sum = 0.f;
+        const int ng = n_tot >> 2;
+        int g = 0;
+        for (; g + 4 <= ng; g += 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(gs + g);
+            sum = __fadd_rn(sum, v.x); sum = __fadd_rn(sum, v.y); sum = __fadd_rn(sum, v.z); sum = __fadd_rn(sum, v.w);
+        }
+        for (; g < ng; ++g) { sum = __fadd_rn(sum, gs[g]); }
+        for (int j = ng << 2; j < n_tot; ++j) { sum = __fadd_rn(sum, sc[j]); }
+        bcast = __fdiv_rn(1.0f, sum);
+    }
     __syncthreads();
     const float inv = bcast;
     // probabilities, rounded to fp16 as the PV MatMul does with its f32 operand
     for (int j = tid; j < n_vis; j += ATT_THREADS) { sc[j] = __half2float(__float2half_rn(__fmul_rn(sc[j], inv))); }
     __syncthreads();
 
-    // ---- out[e] = Dot<FP16,FP16>(V_t[e][0..n_tot), probs); masked positions have probability +0 and leave every
-    // accumulator unchanged, so they are skipped (their cache entries may not be written yet)
-    const int n_main = ((n_tot - 1) / 32) * 32;
-    for (int eb = warp * 32; eb < hd; eb += ATT_WARPS * 32) {
-        float simd_mine = 0.f;
-        for (int i = 0; i < 32; ++i) {
-            const __half *vrow = p.v_cache + ((int64_t)h * hd + eb + i) * p.n_ctx;
-            float acc = 0.f;
-            for (int j = 0; j < n_main && j < n_vis; j += 32) {
-                if (j + lane < n_vis) { acc = fmaf(__half2float(vrow[j + lane]), sc[j + lane], acc); }
-            }
-            acc = reduce_f16dot_lanes(acc);
-            if (lane == i) { simd_mine = acc; }
+    // ---- out[e] = Dot<FP16,FP16>(V_t[e][0..n_tot), probs): a thread pair per element, thread `half` holding
+    // elements 4 * half .. + 3 of the four accumulators. Masked positions have probability +0 and leave every
+    // accumulator unchanged, so they are skipped (their cache entries may not be written yet).
+    {
+        const int e = tid >> 1, half = tid & 1;
+        const __half *vrow = p.v_cache + ((int64_t)h * ATT_HD + e) * p.n_ctx;
+        const int n_main = ((n_tot - 1) / 32) * 32;
+        float acc[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) { acc[a][k] = 0.f; }
         }
-        const __half *vrow = p.v_cache + ((int64_t)h * hd + eb + lane) * p.n_ctx;
+        for (int j0 = 0; j0 < n_main && j0 < n_vis; j0 += 32) {
+            uint2 vv[4];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const int j = j0 + 8 * a + 4 * half;
+                vv[a] = (j < n_vis) ? *reinterpret_cast<const uint2 *>(vrow + j) : make_uint2(0u, 0u);
+            }
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const int    j  = j0 + 8 * a + 4 * half;
+                const float4 pr = *reinterpret_cast<const float4 *>(sc + j);
+                const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&vv[a].x)), v23 = __half22float2(*reinterpret_cast<const __half2 *>(&vv[a].y));
+                if (j + 0 < n_vis) { acc[a][0] = fmaf(v01.x, pr.x, acc[a][0]); }
+                if (j + 1 < n_vis) { acc[a][1] = fmaf(v01.y, pr.y, acc[a][1]); }
+                if (j + 2 < n_vis) { acc[a][2] = fmaf(v23.x, pr.z, acc[a][2]); }
+                if (j + 3 < n_vis) { acc[a][3] = fmaf(v23.y, pr.w, acc[a][3]); }
+            }
+        }
+        float u[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float mine = __fadd_rn(__fadd_rn(acc[0][k], acc[2][k]), __fadd_rn(acc[1][k], acc[3][k]));
+            u[k] = __fadd_rn(mine, __shfl_xor_sync(0xffffffffu, mine, 1));   // element k of one half with element k + 4 of the other
+        }
+        const float simd = __fadd_rn(__fadd_rn(u[0], u[1]), __fadd_rn(u[2], u[3]));
         float tail = 0.f;
         for (int j = n_main; j < n_vis; ++j) { tail = fmaf(__half2float(vrow[j]), sc[j], tail); }
-        p.out[(int64_t)t * p.dl + (int64_t)h * hd + eb + lane] = __fadd_rn(tail, simd_mine);
+        if (half == 0) { p.out[(int64_t)t * p.dl + (int64_t)h * ATT_HD + e] = __fadd_rn(tail, simd); }
     }
 }
 
 cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
-    if (p.hd < 32 || p.hd % 32 != 0 || p.T < 1 || p.n_ctx < 1) { return cudaErrorInvalidValue; }
-    const size_t smem = (size_t)(p.n_ctx + p.hd) * sizeof(float) + 16;
+    if (p.hd != ATT_HD || p.T < 1 || p.n_ctx < 1 || (p.n_ctx & 3) || (p.dl & 7)) { return cudaErrorInvalidValue; }
+    const size_t n_pad = ((size_t)p.n_ctx + 3) & ~(size_t)3;
+    const size_t smem = (n_pad + n_pad / 4 + ATT_HD) * sizeof(float) + 16;
     if (smem > 200 * 1024) { return cudaErrorInvalidValue; }
     static size_t smem_allowed = 40 * 1024;
     if (smem > smem_allowed) {
@@ -152,42 +239,31 @@ cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
 }
 
 // =============================================================================================
-// upload-time re-tiling: raw 18-byte / 34-byte blocks -> aligned planes (one thread per block)
-__global__ void retile_q4_0_kernel(const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint4 *qa, uint16_t *d) {
+// upload-time re-tiling: raw 18-byte / 34-byte blocks -> word-transposed planes (one thread per padded block;
+// blocks beyond nb are written as zeros with a zero scale)
+template <int WORDS>   // 4: Q4_0 (16 nibble bytes), 8: Q8_0 (32 int8 values)
+__global__ void retile_kernel(const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, int nbp, uint4 *q, uint16_t *d) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_rows * nb) { return; }
-    const int64_t  r = i / nb, b = i - r * nb;
-    const uint8_t *src = raw + r * row_stride + b * 18;
-    d[i] = (uint16_t)(src[0] | (src[1] << 8));
-    uint32_t w[4];
+    if (i >= n_rows * nbp) { return; }
+    const int64_t  r = i / nbp;
+    const int      b = (int)(i - r * nbp);
+    const uint8_t *src = raw + r * row_stride + (int64_t)b * (2 + 4 * WORDS);
+    const bool     real = b < nb;
+    d[i] = real ? (uint16_t)(src[0] | (src[1] << 8)) : (uint16_t)0;
+    uint32_t *dst = reinterpret_cast<uint32_t *>(q + (r * (nbp >> 2) + (b >> 2)) * WORDS) + (b & 3);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) { w[k] = src[2 + 4 * k] | (src[3 + 4 * k] << 8) | (src[4 + 4 * k] << 16) | ((uint32_t)src[5 + 4 * k] << 24); }
-    qa[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    for (int k = 0; k < WORDS; ++k) {
+        dst[4 * k] = real ? (uint32_t)(src[2 + 4 * k] | (src[3 + 4 * k] << 8) | (src[4 + 4 * k] << 16) | ((uint32_t)src[5 + 4 * k] << 24)) : 0u;
+    }
 }
 
-__global__ void retile_q8_0_kernel(const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint4 *qa, uint4 *qb, uint16_t *d) {
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= n_rows * nb) { return; }
-    const int64_t  r = i / nb, b = i - r * nb;
-    const uint8_t *src = raw + r * row_stride + b * 34;
-    d[i] = (uint16_t)(src[0] | (src[1] << 8));
-    uint32_t w[8];
-#pragma unroll
-    for (int k = 0; k < 8; ++k) { w[k] = src[2 + 4 * k] | (src[3 + 4 * k] << 8) | (src[4 + 4 * k] << 16) | ((uint32_t)src[5 + 4 * k] << 24); }
-    qa[i] = make_uint4(w[0], w[1], w[2], w[3]);
-    qb[i] = make_uint4(w[4], w[5], w[6], w[7]);
-}
-
-cudaError_t launch_retile_q4_0(const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint4 *qa, uint16_t *d, cudaStream_t s) {
-    const int64_t n = n_rows * nb;
+cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint4 *q_row0, uint16_t *d_row0, cudaStream_t s) {
+    const int     nbp = padded_blocks(nb);
+    const int64_t n = n_rows * nbp;
     if (n == 0) { return cudaSuccess; }
-    retile_q4_0_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(raw, row_stride, n_rows, nb, qa, d);
-    return launch_check();
-}
-cudaError_t launch_retile_q8_0(const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint4 *qa, uint4 *qb, uint16_t *d, cudaStream_t s) {
-    const int64_t n = n_rows * nb;
-    if (n == 0) { return cudaSuccess; }
-    retile_q8_0_kernel<<<(unsigned)((n + 255) / 256), 256, 0, s>>>(raw, row_stride, n_rows, nb, qa, qb, d);
+    if (type == 2)      { retile_kernel<4><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, q_row0, d_row0); }
+    else if (type == 8) { retile_kernel<8><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, q_row0, d_row0); }
+    else                { return cudaErrorNotSupported; }
     return launch_check();
 }
 
@@ -226,23 +302,21 @@ __global__ void block_dots_kernel(int wtype, const uint8_t *w, const uint8_t *xb
         yw[k] = y[4 * k] | (y[4 * k + 1] << 8) | (y[4 * k + 2] << 16) | ((uint32_t)y[4 * k + 3] << 24);
         gs[k] = (int)(int8_t)y[4 * k] + (int)(int8_t)y[4 * k + 1] + (int)(int8_t)y[4 * k + 2] + (int)(int8_t)y[4 * k + 3];
     }
-    const uint4 ylo = make_uint4(yw[0], yw[1], yw[2], yw[3]), yhi = make_uint4(yw[4], yw[5], yw[6], yw[7]);
-    float f[8];
-    int   total = 0;
+    int total = 0;
     if (wtype == 2) {
         const uint8_t *q = w + b * 18 + 2;
-        uint32_t ww[4];
-        for (int k = 0; k < 4; ++k) { ww[k] = q[4 * k] | (q[4 * k + 1] << 8) | (q[4 * k + 2] << 16) | ((uint32_t)q[4 * k + 3] << 24); }
-        const int4 blo = make_int4((int)MAGIC_I - 8 * gs[0], (int)MAGIC_I - 8 * gs[1], (int)MAGIC_I - 8 * gs[2], (int)MAGIC_I - 8 * gs[3]);
-        const int4 bhi = make_int4((int)MAGIC_I - 128 * gs[4], (int)MAGIC_I - 128 * gs[5], (int)MAGIC_I - 128 * gs[6], (int)MAGIC_I - 128 * gs[7]);
-        lanes_q4_0(make_uint4(ww[0], ww[1], ww[2], ww[3]), ylo, yhi, blo, bhi, f);
-        for (int l = 0; l < 4; ++l) { total += (int)f[l] / 16 + (int)f[4 + l]; }   // high-nibble lanes come scaled by 16
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t ww = q[4 * k] | (q[4 * k + 1] << 8) | (q[4 * k + 2] << 16) | ((uint32_t)q[4 * k + 3] << 24);
+            const float hi = lane_sum_q4_0(ww & 0xf0f0f0f0u, yw[4 + k], (int)MAGIC_I - 128 * gs[4 + k]);   // comes scaled by 16
+            const float lo = lane_sum_q4_0(ww & 0x0f0f0f0fu, yw[k], (int)MAGIC_I - 8 * gs[k]);
+            total += (int)hi / 16 + (int)lo;
+        }
     } else {
         const uint8_t *q = w + b * 34 + 2;
-        uint32_t ww[8];
-        for (int k = 0; k < 8; ++k) { ww[k] = q[4 * k] | (q[4 * k + 1] << 8) | (q[4 * k + 2] << 16) | ((uint32_t)q[4 * k + 3] << 24); }
-        lanes_q8_0(make_uint4(ww[0], ww[1], ww[2], ww[3]), make_uint4(ww[4], ww[5], ww[6], ww[7]), ylo, yhi, f);
-        for (int l = 0; l < 8; ++l) { total += (int)f[l]; }
+        for (int k = 0; k < 8; ++k) {
+            const uint32_t ww = q[4 * k] | (q[4 * k + 1] << 8) | (q[4 * k + 2] << 16) | ((uint32_t)q[4 * k + 3] << 24);
+            total += (int)lane_sum_q8_0(ww, yw[k]);
+        }
     }
     out[b] = total;
 }
