@@ -71,14 +71,13 @@ size_t Arena::available() {
 // ------------------------------------------------------------------------------------------ matrices
 spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, DevMatrix *out) {
     if (type != SPYB_Q4_0 && type != SPYB_Q8_0) { be->set_error("weight type %d has no device layout", type); return SPYB_UNSUPPORTED; }
+    if (n_rows & 3) { be->set_error("quantized matrices need a multiple of 4 rows (got %lld)", (long long)n_rows); return SPYB_UNSUPPORTED; }
     DevMatrix m;
     m.type = type; m.n_rows = n_rows; m.nb = nb; m.nbp = padded_blocks(nb); m.k = (int64_t)nb * QK;
-    void *q = nullptr, *d = nullptr;
-    SPYB_CUDA(be, cudaMalloc(&q, q_plane_bytes(type, n_rows, nb) + 16));
-    be->owned.push_back(q);
-    SPYB_CUDA(be, cudaMalloc(&d, d_plane_bytes(n_rows, nb) + 16));
-    be->owned.push_back(d);
-    m.q = static_cast<const uint4 *>(q); m.d = static_cast<const uint16_t *>(d);
+    void *w = nullptr;
+    SPYB_CUDA(be, cudaMalloc(&w, matrix_bytes(type, n_rows, nb) + 16));
+    be->owned.push_back(w);
+    m.w = static_cast<const uint8_t *>(w);
     *out = m;
     return SPYB_SUCCESS;
 }
@@ -89,13 +88,13 @@ spyb_status upload_matrix(spyb_backend *be, int type, const uint8_t *host_rows, 
         spyb_status st = alloc_matrix(be, type, n_rows, nb, out);
         if (st != SPYB_SUCCESS) { return st; }
         into = out; dst_row = 0;
-    } else if (into->type != type || into->nb != nb || dst_row + n_rows > into->n_rows) {
+    } else if (into->type != type || into->nb != nb || dst_row + n_rows > into->n_rows || ((dst_row | n_rows) & 3)) {
         be->set_error("weight upload: destination rows do not match"); return SPYB_FAIL;
     }
-    uint4    *q_dst = const_cast<uint4 *>(into->q) + (size_t)dst_row * q_row_words(type, nb);
-    uint16_t *d_dst = const_cast<uint16_t *>(into->d) + (size_t)dst_row * into->nbp;
+    const size_t tile_bytes = (size_t)(into->nbp >> 3) * record_bytes(type);
+    uint8_t *dst = const_cast<uint8_t *>(into->w) + (size_t)(dst_row >> 2) * tile_bytes;
     const int     bb = (type == SPYB_Q4_0) ? 18 : 34;
-    const int64_t max_rows = std::max<int64_t>(1, (int64_t)(64u << 20) / row_stride_bytes);   // 64 MiB staging pieces
+    const int64_t max_rows = std::max<int64_t>(4, ((int64_t)(64u << 20) / row_stride_bytes) & ~(int64_t)3);   // 64 MiB staging pieces, whole tiles
     void *stage = nullptr;
     SPYB_CUDA(be, cudaMalloc(&stage, (size_t)std::min(max_rows, n_rows) * row_stride_bytes + 64));
     for (int64_t r0 = 0; r0 < n_rows; r0 += max_rows) {
@@ -103,7 +102,7 @@ spyb_status upload_matrix(spyb_backend *be, int type, const uint8_t *host_rows, 
         cudaError_t err = cudaMemcpyAsync(stage, host_rows + r0 * row_stride_bytes, (size_t)nr * row_stride_bytes, cudaMemcpyHostToDevice, be->stream);
         if (err == cudaSuccess) {
             const uint8_t *raw = static_cast<const uint8_t *>(stage) + blk0 * bb;
-            err = launch_retile(type, raw, row_stride_bytes, nr, nb, q_dst + (size_t)r0 * q_row_words(type, nb), d_dst + (size_t)r0 * into->nbp, be->stream);
+            err = launch_retile(type, raw, row_stride_bytes, nr, nb, dst + (size_t)(r0 >> 2) * tile_bytes, be->stream);
         }
         if (err == cudaSuccess) { err = cudaStreamSynchronize(be->stream); }
         if (err != cudaSuccess) { cudaFree(stage); be->set_error("weight upload failed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
@@ -175,7 +174,13 @@ spyb_status spyb_create(const spyb_config *config, spyb_backend **out) {
     be->num_sms = prop.multiProcessorCount;
     if (const char *v = std::getenv("SPYB_L2_PREFETCH_MB")) { const int mb = std::atoi(v); be->l2_prefetch_next = mb > 0; be->l2_prefetch_cap = (size_t)std::max(mb, 0) << 20; }   // tuning knob
     if (const char *v = std::getenv("SPYB_MV_CTAS_PER_SM")) { be->mv_ctas_per_sm = std::max(1, std::min(2, std::atoi(v))); }   // tuning knob
+    if (const char *v = std::getenv("SPYB_MV_RING_KB")) { be->mv_ring_kb = std::max(8, std::min(96, std::atoi(v))); }   // tuning knob
     if (cudaStreamCreateWithFlags(&be->stream, cudaStreamNonBlocking) != cudaSuccess) { delete be; return SPYB_FAIL; }
+    if (cudaHostAlloc(reinterpret_cast<void **>(&be->h_error_flag), sizeof(int), cudaHostAllocMapped) != cudaSuccess ||
+        cudaHostGetDevicePointer(reinterpret_cast<void **>(&be->d_error_flag), be->h_error_flag, 0) != cudaSuccess) {
+        cudaStreamDestroy(be->stream); delete be; return SPYB_FAIL;
+    }
+    *be->h_error_flag = 0;
     const size_t arena = config->arena_bytes ? config->arena_bytes : (size_t)256 << 20;
     if (!be->arena.init(arena)) { cudaStreamDestroy(be->stream); delete be; return SPYB_FAIL; }
 
@@ -210,6 +215,7 @@ void spyb_destroy(spyb_backend *be) {
     for (void *p : be->owned) { cudaFree(p); }
     if (be->d_silu_table) { cudaFree(be->d_silu_table); }
     if (be->d_exp_table) { cudaFree(be->d_exp_table); }
+    if (be->h_error_flag) { cudaFreeHost(be->h_error_flag); }
     be->arena.destroy();
     if (be->stream) { cudaStreamDestroy(be->stream); }
     delete be;
@@ -266,10 +272,10 @@ void *spyb_upload_constant(spyb_backend *be, const char *name, const void *host_
         // matrices also get the plane layout the mat-vec kernels stream; the raw copy stays for GetRow and parity checks
         const int64_t k = elements[0], rows = elements[1] * elements[2] * elements[3];
         const int64_t bb = number_type == SPYB_Q4_0 ? 18 : 34;
-        if (k % QK == 0 && rows > 0) {
+        if (k % QK == 0 && rows > 0 && (rows & 3) == 0) {
             DevMatrix m;
             if (alloc_matrix(be, number_type, rows, (int)(k / QK), &m) != SPYB_SUCCESS) { return nullptr; }
-            cudaError_t err = launch_retile(number_type, static_cast<const uint8_t *>(raw), k / QK * bb, rows, m.nb, const_cast<uint4 *>(m.q), const_cast<uint16_t *>(m.d), be->stream);
+            cudaError_t err = launch_retile(number_type, static_cast<const uint8_t *>(raw), k / QK * bb, rows, m.nb, const_cast<uint8_t *>(m.w), be->stream);
             if (err != cudaSuccess || cudaStreamSynchronize(be->stream) != cudaSuccess) { be->set_error("re-tiling of %s failed", name); return nullptr; }
             be->retiled[raw] = m;
         }
@@ -280,6 +286,7 @@ void *spyb_upload_constant(spyb_backend *be, const char *name, const void *host_
 
 spyb_status spyb_sync(spyb_backend *be) {
     SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+    if (be->device_error()) { return SPYB_FAIL; }
     return SPYB_SUCCESS;
 }
 
@@ -382,9 +389,10 @@ spyb_status run_matmul(spyb_backend *be, spyb_op_desc *d, void *out_dev) {
     }
     DevMatrix m;
     bool found = false;
-    void *tmp_q = nullptr, *tmp_d = nullptr;
+    void *tmp_w = nullptr;
     const int    nb_w = (int)(w.elements[0] / QK);
-    const size_t q_bytes = q_plane_bytes(w.number_type, w.elements[1], nb_w) + 16, d_bytes = d_plane_bytes(w.elements[1], nb_w) + 16;
+    if (w.elements[1] & 3) { be->set_error("MatMul: %lld output rows (quantized weights need a multiple of 4)", (long long)w.elements[1]); return SPYB_UNSUPPORTED; }
+    const size_t w_bytes = matrix_bytes(w.number_type, w.elements[1], nb_w) + 16;
     {
         std::lock_guard<std::mutex> g(be->const_mutex);
         auto it = be->retiled.find(w.data);
@@ -392,20 +400,20 @@ spyb_status run_matmul(spyb_backend *be, spyb_op_desc *d, void *out_dev) {
     }
     if (!found) {
         // a quantized operand that did not come through spyb_upload_constant (its address may be reused for other
-        // data later, so nothing is cached): re-tile into planes that live for this operator only
+        // data later, so nothing is cached): re-tile into a buffer that lives for this operator only
         const int64_t bb = w.number_type == SPYB_Q4_0 ? 18 : 34;
         m.type = w.number_type; m.n_rows = w.elements[1]; m.nb = nb_w; m.nbp = padded_blocks(nb_w); m.k = w.elements[0];
-        tmp_q = be->arena.alloc(q_bytes); tmp_d = be->arena.alloc(d_bytes);
-        if (!tmp_q || !tmp_d) { be->set_error("MatMul: out of device memory for re-tiled weights"); return SPYB_FAIL; }
-        m.q = static_cast<const uint4 *>(tmp_q); m.d = static_cast<const uint16_t *>(tmp_d);
+        tmp_w = be->arena.alloc(w_bytes);
+        if (!tmp_w) { be->set_error("MatMul: out of device memory for re-tiled weights"); return SPYB_FAIL; }
+        m.w = static_cast<const uint8_t *>(tmp_w);
         cudaError_t err = launch_retile(w.number_type, static_cast<const uint8_t *>(w.data), w.elements[0] / QK * bb, w.elements[1], m.nb,
-                                        static_cast<uint4 *>(tmp_q), static_cast<uint16_t *>(tmp_d), be->stream);
+                                        static_cast<uint8_t *>(tmp_w), be->stream);
         if (err != cudaSuccess) { be->set_error("MatMul: re-tiling failed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
     }
     struct TmpRelease {   // stream-ordered reuse: safe to hand back as soon as the kernels are enqueued
-        spyb_backend *be; void *a, *b; size_t na, nb;
-        ~TmpRelease() { if (a) { be->arena.free(a, na); } if (b) { be->arena.free(b, nb); } }
-    } release{be, tmp_q, tmp_d, q_bytes, d_bytes};
+        spyb_backend *be; void *a; size_t na;
+        ~TmpRelease() { if (a) { be->arena.free(a, na); } }
+    } release{be, tmp_w, w_bytes};
     if (m.k != x.elements[0]) { be->set_error("MatMul: inner dimensions differ"); return SPYB_FAIL; }
     if (m.n_rows & 3) { be->set_error("MatMul: %lld output rows (quantized weights need a multiple of 4)", (long long)m.n_rows); return SPYB_UNSUPPORTED; }
     const int64_t T = x.elements[1] * x.elements[2] * x.elements[3];

@@ -49,6 +49,45 @@ __device__ __forceinline__ void l2_prefetch_piece(const void *ptr, size_t bytes,
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(__cvta_generic_to_global(reinterpret_cast<const void *>(a))), "r"(n) : "memory");
 }
 
+// ---------------------------------------------------------------------------------------------
+// bulk asynchronous copies global -> shared memory, completion counted on an mbarrier (no tensor map: plain
+// contiguous runs; both addresses and the size are multiples of 16 bytes)
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false when the phase did not complete within `limit_ns` of wall-clock time
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint64_t limit_ns) {
+    if (mbar_try_wait(bar, parity)) { return true; }
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        if (mbar_try_wait(bar, parity)) { return true; }
+        if (global_timer_ns() - t0 > limit_ns) { return false; }
+    }
+}
+__device__ __forceinline__ void bulk_copy_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(dst_smem)), "l"(__cvta_generic_to_global(src_gmem)), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) { v += __shfl_xor_sync(0xffffffffu, v, o); }
@@ -85,26 +124,21 @@ __device__ __forceinline__ uint32_t quantize_q8_lane4(float4 v, uint16_t &d_half
 
 // ---------------------------------------------------------------------------------------------
 // Integer lane sums are produced directly as floats: the accumulator operand of the byte dot product
-// carries MAGIC_I (plus, for Q4_0 weights, the "- 8 per nibble" correction), so that the result's bit
+// carries MAGIC_I, so that the result's bit
 // pattern is the float MAGIC_F + lane_sum and one exact subtraction yields (float)lane_sum.
 constexpr float    MAGIC_F = 12582912.0f;     // 1.5 * 2^23: int_as_float(MAGIC_I + p) == MAGIC_F + p exactly for |p| < 2^22
 constexpr uint32_t MAGIC_I = 0x4B400000u;
-
-__device__ __forceinline__ int dp4a_us(uint32_t a_unsigned, uint32_t b_signed, int c) {
-    int d;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a_unsigned), "r"(b_signed), "r"(c));
-    return d;
-}
 
 // One of the eight integer "lane sums" of a block pair, in the order of the reference's 8-wide accumulator
 // (Dot<Q4_0,Q8_0>::exec, backend/host/include/simd/vec_dot.h:58-75 with mul_sum_i8_pairs, vec_util.h:100-110:
 // lanes 0..3 = sum over k = 4j..4j+3 of (high nibble_k - 8) * y[16+k], lanes 4..7 = the same with low nibbles
 // and y[k]; Dot<Q8_0,Q8_0>::exec, vec_dot.h:103-113: lane l = sum of products 4l..4l+3), returned as a float.
-//   Q4_0: `w_masked` = the weight word with only this lane's nibbles kept (high nibbles stay in place, which
-//   scales the sum by 16; the caller multiplies by scale/16, which is exact), `bias` = MAGIC_I - 8 * (sum of
-//   the four y bytes) for low nibbles, MAGIC_I - 128 * sum for high nibbles.
-__device__ __forceinline__ float lane_sum_q4_0(uint32_t w_masked, uint32_t y, int bias) {
-    return __int_as_float(dp4a_us(w_masked, y, bias)) - MAGIC_F;
+//   Q4_0: `w_x88` = the weight word XOR 0x88888888 (every nibble then is value - 8 in two's complement);
+//   `shift` = 0 for the high nibbles, 4 for the low ones: the selected nibble of every byte lands in the high
+//   half of its byte, which as a signed byte is 16 * (value - 8). The result is 16 * lane_sum; the caller
+//   multiplies by scale / 16, which is exact.
+__device__ __forceinline__ float lane_sum16_q4_0(uint32_t w_x88, int shift, uint32_t y) {
+    return __int_as_float(__dp4a((int)((w_x88 << shift) & 0xf0f0f0f0u), (int)y, (int)MAGIC_I)) - MAGIC_F;
 }
 __device__ __forceinline__ float lane_sum_q8_0(uint32_t w, uint32_t y) {
     return __int_as_float(__dp4a((int)w, (int)y, (int)MAGIC_I)) - MAGIC_F;

@@ -54,10 +54,13 @@ struct spyb_backend {
     spyb_config  config{};
     int          num_sms = 148;
     int          mv_ctas_per_sm = 2;
+    int          mv_ring_kb = 80;
     bool         l2_prefetch_next = true;          // kernels pull the weights of the kernel two places later towards L2
     size_t       l2_prefetch_cap = (size_t)32 << 20;   // at most this much of one matrix
     cudaStream_t stream = nullptr;
     spyb::Arena  arena;
+    int         *h_error_flag = nullptr;   // mapped pinned word the kernels set when a bounded wait runs out
+    int         *d_error_flag = nullptr;   // its device address
     float       *d_silu_table = nullptr;   // 65536 entries: xh / (1 + expf(-xh)) for the fp16 value xh
     float       *d_exp_table = nullptr;    // 65536 entries: expf(xh)
 
@@ -83,8 +86,17 @@ struct spyb_backend {
         std::lock_guard<std::mutex> g(err_mutex);
         last_error = buf;
     }
+    // after a stream synchronisation: did a kernel give up on a bounded wait?
+    bool device_error() {
+        if (h_error_flag != nullptr && *reinterpret_cast<volatile int *>(h_error_flag) != 0) {
+            set_error("a kernel gave up waiting for a bulk copy (device error flag %d)", *h_error_flag);
+            return true;
+        }
+        return false;
+    }
     spyb::LaunchCfg launch_cfg(bool pdl) const {
-        spyb::LaunchCfg c; c.stream = stream; c.pdl = pdl; c.num_sms = num_sms; c.mv_ctas_per_sm = mv_ctas_per_sm; return c;
+        spyb::LaunchCfg c; c.stream = stream; c.pdl = pdl; c.num_sms = num_sms; c.mv_ctas_per_sm = mv_ctas_per_sm;
+        c.mv_ring_kb = mv_ring_kb; c.error_flag = d_error_flag; return c;
     }
 };
 

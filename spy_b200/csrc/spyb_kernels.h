@@ -7,29 +7,31 @@
 
 namespace spyb {
 
-// A quantized weight matrix resident in HBM, re-tiled at upload. Rows are padded to a multiple of four
-// blocks (nbp; the padding blocks are zeros with a zero scale) and every group of four consecutive
-// blocks of a row is stored word-transposed, so that the lane that owns accumulator l of the CPU's
-// 8-wide dot product loads, with one aligned 128-bit word, exactly its own four bytes of four blocks:
-//   Q4_0: q[row][group][j]  (j = 0..3)  = 32-bit word j of the 16 nibble bytes of blocks 4g..4g+3
-//   Q8_0: q[row][group][l]  (l = 0..7)  = 32-bit word l of the 32 int8 values of blocks 4g..4g+3
-//   d[row][block]                       = fp16 scale
-// The bytes are those of the reference's block_q4_0_t / block_q8_0_t
+// A quantized weight matrix resident in HBM, re-tiled at upload into the stream a warp consumes:
+//   tile   = 4 consecutive rows; a tile's data is one contiguous run, so a warp walks sequential addresses
+//   record = 8 consecutive blocks ("mini-chunk") of the 4 rows of a tile:
+//              [row 0..3][ q: 2 groups x WORDS x 16 B | d: 8 fp16 scales ]      (WORDS = 4 for Q4_0, 8 for Q8_0)
+//            inside a group of four blocks the quants are word-transposed: 128-bit word j holds 32-bit word j of
+//            each of the four blocks, so the lane that owns accumulator l of the CPU's 8-wide dot product finds
+//            its own four bytes of four blocks in one aligned 128-bit word
+//   Q4_0 quants are stored XOR 0x88: a nibble then reads as (value - 8) in two's complement, and a byte masked
+//   to its high nibble is 16 * (value - 8) as a signed byte - no "- 8" correction term is needed at run time.
+//   Rows are padded to a multiple of 8 blocks (nbp) with zero scales.
+// The information is that of the reference's block_q4_0_t / block_q8_0_t
 // (orchestration/include/number/number_impl/quant.h:10-33, 124-147), only regrouped.
 struct DevMatrix {
-    int             type = -1;
-    int64_t         n_rows = 0;
-    int64_t         k = 0;
-    int             nb = 0;    // blocks per row
-    int             nbp = 0;   // blocks per row in memory (nb rounded up to a multiple of 4)
-    const uint4    *q = nullptr;
-    const uint16_t *d = nullptr;
+    int            type = -1;
+    int64_t        n_rows = 0;   // multiple of 4
+    int64_t        k = 0;
+    int            nb = 0;       // blocks per row
+    int            nbp = 0;      // blocks per row in memory (nb rounded up to a multiple of 8)
+    const uint8_t *w = nullptr;  // [n_rows / 4][nbp / 8] records
     size_t bytes() const { return (size_t)n_rows * nb * ((type == 8 ? 32 : 16) + 2); }   // algorithmic bytes (without padding)
 };
-inline int    padded_blocks(int nb) { return (nb + 3) & ~3; }
-inline size_t q_row_words(int type, int nb) { return (size_t)padded_blocks(nb) * (type == 8 ? 2 : 1); }   // uint4 per row of the q plane
-inline size_t q_plane_bytes(int type, int64_t n_rows, int nb) { return (size_t)n_rows * q_row_words(type, nb) * 16; }
-inline size_t d_plane_bytes(int64_t n_rows, int nb) { return (size_t)n_rows * padded_blocks(nb) * 2; }
+inline int    padded_blocks(int nb) { return (nb + 7) & ~7; }
+inline int    record_row_bytes(int type) { return (type == 8 ? 256 : 128) + 16; }
+inline int    record_bytes(int type) { return 4 * record_row_bytes(type); }            // 576 (Q4_0) or 1088 (Q8_0)
+inline size_t matrix_bytes(int type, int64_t n_rows, int nb) { return (size_t)(n_rows / 4) * (padded_blocks(nb) / 8) * record_bytes(type); }
 
 enum Prologue { PRO_QUANT = 0, PRO_NORM_QUANT = 1 };
 enum Epilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_SILU_MUL = 2, EPI_QKV_ROPE = 3 };
@@ -62,6 +64,7 @@ struct MatvecParams {
     int           n_ctx = 0;
     // optional tap: reference-layout Q8_0 blocks of column 0 (nb * 34 bytes)
     uint8_t      *tap_xq = nullptr;
+    int          *error_flag = nullptr; // set non-zero when a bounded wait on a bulk copy ran out
     // weights a later kernel of the step will stream: pulled into L2 once this CTA's own loads are issued
     const void   *pf_ptr[4] = {nullptr, nullptr, nullptr, nullptr};
     size_t        pf_bytes[4] = {0, 0, 0, 0};
@@ -85,6 +88,8 @@ struct LaunchCfg {
     bool         pdl = false;   // launch with the programmatic-stream-serialization attribute
     int          num_sms = 148;
     int          mv_ctas_per_sm = 2;   // mat-vec CTAs per SM for single-column launches (their register budget allows 2)
+    int          mv_ring_kb = 80;      // shared-memory ring per CTA that bulk copies stream the weights through
+    int         *error_flag = nullptr;
 };
 
 size_t      matvec_smem_bytes(int nb, int T);
@@ -93,8 +98,8 @@ cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg);
 cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg);
 
 // upload-time re-tiling of raw reference-layout blocks into DevMatrix planes
-// (q_row0, d_row0 point at the first destination row; nb blocks are read per row, the padding is zero-filled)
-cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride_bytes, int64_t n_rows, int nb, uint4 *q_row0, uint16_t *d_row0, cudaStream_t s);
+// (dst points at the first destination tile; n_rows is a multiple of 4; nb blocks are read per row, the padding is zero-filled)
+cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride_bytes, int64_t n_rows, int nb, uint8_t *dst, cudaStream_t s);
 
 // stand-alone arithmetic kernels (parity checks and the per-operator path)
 cudaError_t launch_quantize_q8_0_ref_layout(const float *x, int64_t n, uint8_t *blocks, cudaStream_t s);

@@ -7,21 +7,24 @@
 // reduction tree at the end. Because the network re-quantizes its activations at every layer, any
 // difference in f32 summation order is amplified to percent-level logit differences within a few layers,
 // so this kernel reproduces that order exactly, by giving every one of the CPU's accumulators to one lane:
-//   lane = (row r of 4, accumulator l of 8); a warp owns a tile of 4*R rows (R rows per lane) and walks
-//   them along K four blocks at a time. Per group of four blocks a lane loads ONE 128-bit word per row
-//   (its own 4 bytes of each of the 4 blocks - the weights are stored word-transposed for this), masks its
-//   nibbles, takes four byte dot products against the Q8_0 activations in shared memory and folds them
-//   into its accumulator with four FMAs in block order. No shared-memory traffic for weights, no
-//   intra-warp synchronisation; the eight lanes of a row meet once per row in the reduction tree.
+//   lane = (row r of 4, accumulator l of 8); a warp owns R tiles of 4 rows and walks them along K. Per group
+//   of four blocks a lane reads ONE 128-bit word per row (its own 4 bytes of each of the 4 blocks - the
+//   weights are stored word-transposed for this), selects its nibbles, takes four byte dot products against
+//   the Q8_0 activations in shared memory and folds them into its accumulator with four FMAs in block order.
+//   No intra-warp synchronisation in the arithmetic; the eight lanes of a row meet once per row in the
+//   reduction tree.
 // The small neighbouring operators of the LLaMa layer are folded into the prologue (RMSNorm + weight +
 // Q8_0 quantization, in the CPU's summation order) and the epilogue (residual add, SiLU-gate-mul,
 // RoPE + KV append).
 //
 // Roofline: HBM-bound. Algorithmic bytes per launch = rows * K/32 * 18 (Q4_0) or 34 (Q8_0); activations
-// and outputs are a few KB and stay in L2. Weights are pulled towards L2 ahead of use with bulk
-// prefetches: a CTA's own rows before it waits for the previous kernel, and (optionally) the rows a later
-// kernel of the step will need once its own loads are in flight, so that HBM keeps streaming across
-// kernel boundaries and through the serial prologues.
+// and outputs are a few KB and stay in L2. The weights of a tile are one contiguous run in HBM; every warp
+// streams its tiles through a private ring in shared memory with bulk asynchronous copies
+// (cp.async.bulk, completion on mbarriers), issued before the kernel waits for its predecessor: tens of KB
+// per SM are in flight without holding registers, the copies are long sequential runs (DRAM-page friendly),
+// and they keep HBM busy through the serial prologue and across kernel boundaries.
+
+#include <algorithm>
 
 #include "spyb_common.cuh"
 #include "spyb_kernels.h"
@@ -31,29 +34,37 @@ namespace spyb {
 constexpr int MV_THREADS = 512;
 constexpr int MV_WARPS   = MV_THREADS / WARP;
 
+constexpr int MAX_STAGES = 16;              // ring stages per warp (mbarriers per warp)
+constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;   // a bulk copy that has not landed after a second: give up and report
+
 // shared memory: per column t, per group g of four blocks
 //   Y [t][g][w][i]  (w = 0..7, i = 0..3)  word w of the 32 int8 values of block 4g+i (w 0..3 = values 0..15)
-//   Bq[t][g][w][i]  the accumulator operand for Q4_0 weights: MAGIC_I - 8 * (sum of the 4 bytes of that word)
-//                   for w < 4 (paired with low nibbles), MAGIC_I - 128 * sum for w >= 4 (high nibbles in place)
-//   DX[t][b], DX16[t][b]  f32 of the fp16-rounded scale, and the same divided by 16 (exact)
+//   DS[t][b]        f32 of the fp16-rounded scale; divided by 16 (exact) for Q4_0 weights, whose lane sums come
+//                   scaled by 16
 // The sum-of-squares partials of the RMSNorm prologue alias Y (they are dead before Y is written).
 struct ActPlanes {
     uint4  *Y;
-    int4   *Bq;
-    float4 *DX;
-    float4 *DX16;
+    float4 *DS;
 };
-__host__ __device__ static inline size_t act_plane_bytes(int nbp, int TM) { return (size_t)TM * nbp * (32 + 32 + 4 + 4); }
+__host__ __device__ static inline size_t act_plane_bytes(int nbp, int TM) { return (size_t)TM * nbp * (32 + 4); }
 __device__ __forceinline__ ActPlanes act_planes(void *base, int nbp, int TM) {
     ActPlanes a;
-    a.Y    = reinterpret_cast<uint4 *>(base);
-    a.Bq   = reinterpret_cast<int4 *>(a.Y + (size_t)TM * nbp * 2);
-    a.DX   = reinterpret_cast<float4 *>(a.Bq + (size_t)TM * nbp * 2);
-    a.DX16 = a.DX + (size_t)TM * (nbp >> 2);
+    a.Y  = reinterpret_cast<uint4 *>(base);
+    a.DS = reinterpret_cast<float4 *>(a.Y + (size_t)TM * nbp * 2);
     return a;
 }
 
-size_t matvec_smem_bytes(int nb, int T) { return act_plane_bytes(padded_blocks(nb), T) + 16; }
+struct MatvecSmem { size_t act, bars, ring, total; };
+__host__ __device__ static inline MatvecSmem matvec_smem_layout(int nbp, int TM, size_t ring_bytes) {
+    MatvecSmem m;
+    m.act  = 0;
+    m.bars = (act_plane_bytes(nbp, TM) + 15) / 16 * 16;
+    m.ring = (m.bars + (size_t)MV_WARPS * MAX_STAGES * 8 + 127) / 128 * 128;
+    m.total = m.ring + ring_bytes;
+    return m;
+}
+
+size_t matvec_smem_bytes(int nb, int T) { return matvec_smem_layout(padded_blocks(nb), T, 0).total; }
 
 // ---------------------------------------------------------------------------------------------
 // prologue: f32 activations -> Q8_0 columns in shared memory (optionally through RMSNorm * weight)
@@ -97,8 +108,7 @@ __device__ __forceinline__ void matvec_prologue(const MatvecParams &p, ActPlanes
         __syncthreads();   // also: the partials (aliasing Y) are dead from here on
     }
     uint32_t *Yw = reinterpret_cast<uint32_t *>(act.Y);
-    int      *Bw = reinterpret_cast<int *>(act.Bq);
-    float    *DX = reinterpret_cast<float *>(act.DX), *DX16 = reinterpret_cast<float *>(act.DX16);
+    float    *DS = reinterpret_cast<float *>(act.DS);
     const int n4p = nbp * 8;   // float4 groups including the zero padding up to nbp blocks
 #pragma unroll 1
     for (int t = 0; t < TM; ++t) {
@@ -123,11 +133,7 @@ __device__ __forceinline__ void matvec_prologue(const MatvecParams &p, ActPlanes
                 const int b = g >> 3, w = g & 7;
                 const int idx = ((t * (nbp >> 2) + (b >> 2)) * 8 + w) * 4 + (b & 3);
                 Yw[idx] = q;
-                Bw[idx] = (int)MAGIC_I - ((w < 4) ? 8 : 128) * s;
-                if (w == 0) {
-                    const float d = h2f(dh);
-                    DX[t * nbp + b] = d; DX16[t * nbp + b] = __fmul_rn(d, 0.0625f);
-                }
+                if (w == 0) { const float d = h2f(dh); DS[t * nbp + b] = (p.A.type == 2) ? __fmul_rn(d, 0.0625f) : d; }
             }
         }
     }
@@ -138,14 +144,14 @@ __device__ __forceinline__ void matvec_prologue(const MatvecParams &p, ActPlanes
 __device__ __forceinline__ void matvec_tap(const MatvecParams &p, ActPlanes act) {
     if (p.tap_xq == nullptr || blockIdx.x != 0) { return; }
     const uint32_t *Yw = reinterpret_cast<const uint32_t *>(act.Y);
-    const float    *DX = reinterpret_cast<const float *>(act.DX);
+    const float    *DS = reinterpret_cast<const float *>(act.DS);
     for (int b = threadIdx.x; b < p.A.nb; b += MV_THREADS) {
         volatile uint8_t *o = p.tap_xq + (size_t)b * 34;   // 34-byte records: only 2-byte alignment holds
         for (int w = 0; w < 8; ++w) {
             const uint32_t v = Yw[((b >> 2) * 8 + w) * 4 + (b & 3)];
             o[2 + 4 * w] = (uint8_t)v; o[3 + 4 * w] = (uint8_t)(v >> 8); o[4 + 4 * w] = (uint8_t)(v >> 16); o[5 + 4 * w] = (uint8_t)(v >> 24);
         }
-        *reinterpret_cast<volatile uint16_t *>(p.tap_xq + (size_t)b * 34) = f2h(DX[b]);
+        *reinterpret_cast<volatile uint16_t *>(p.tap_xq + (size_t)b * 34) = f2h((p.A.type == 2) ? __fmul_rn(DS[b], 16.0f) : DS[b]);
     }
 }
 
@@ -186,69 +192,65 @@ __device__ __forceinline__ void matvec_epilogue_silu(const MatvecParams &p, int6
 }
 
 // ---------------------------------------------------------------------------------------------
-// Register pipeline: D groups of four blocks in flight per lane and row.
-template <int TM, int R> struct Pipe { static constexpr int D = (TM == 1) ? ((R == 1) ? 4 : 2) : 2; };
-
 template <int WT, int TM, int R>
-__global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(const MatvecParams p) {
-    extern __shared__ __align__(16) uint8_t smem_raw[];
+__global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(const MatvecParams p, const int ring_bytes, const int S) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ float norm_scales[8];
-    constexpr int D  = Pipe<TM, R>::D;
-    constexpr int QW = (WT == 8) ? 8 : 4;     // 128-bit words per group of four blocks in the q plane
+    constexpr int ROWB = ((WT == 8) ? 256 : 128) + 16;   // one row's share of a record: quants of 8 blocks + 8 scales
+    constexpr int RECB = 4 * ROWB;
+    constexpr int GRPB = (WT == 8) ? 128 : 64;           // quants of one group of four blocks
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int r = lane >> 3, l = lane & 7;
-    const int nbp = p.A.nbp;
-    const int ng  = nbp >> 2;
+    const int nbp  = p.A.nbp;
+    const int ng   = nbp >> 2;
+    const int nrec = nbp >> 3;
 
-    // tiles of this CTA (a contiguous range) and of this warp (every MV_WARPS-th of them)
-    const int64_t n_tiles = p.pair_mode ? (p.A.n_rows >> 2) : (p.A.n_rows / (4 * R));
-    const int64_t tile_lo = n_tiles * blockIdx.x / gridDim.x;
-    const int64_t tile_hi = n_tiles * (blockIdx.x + 1) / gridDim.x;
-    const int64_t my_first = tile_lo + warp;
-    const int64_t my_tiles = (my_first < tile_hi) ? (tile_hi - my_first + MV_WARPS - 1) / MV_WARPS : 0;
-    const int64_t n_items  = my_tiles * ng;
+    // units of this CTA (a contiguous range) and of this warp (every MV_WARPS-th of them); a unit is R tiles:
+    // tiles R*u .. R*u + R-1 of A, or (pair mode, R == 2) tile u of A and tile u of B
+    const int64_t n_units  = p.pair_mode ? (p.A.n_rows >> 2) : (p.A.n_rows / (4 * R));
+    const int64_t unit_lo  = n_units * blockIdx.x / gridDim.x;
+    const int64_t unit_hi  = n_units * (blockIdx.x + 1) / gridDim.x;
+    const int64_t my_first = unit_lo + warp;
+    const int64_t my_units = (my_first < unit_hi) ? (unit_hi - my_first + MV_WARPS - 1) / MV_WARPS : 0;
+    const int     n_act    = (int)min((int64_t)MV_WARPS, unit_hi - unit_lo);   // warps of this CTA that have work
+    const int     nch      = (nrec + S - 1) / S;                               // stages per unit
+    const int64_t n_items  = my_units * nch;
+    const int     stage_bytes = R * S * RECB;
+    const int     NS = max(1, min(MAX_STAGES, ring_bytes / (max(n_act, 1) * stage_bytes)));
 
-    // row i of the lane in tile u: rows 4R*u + 4i + r of A, or (pair mode) row 4u + r of A (i = 0) and of B (i = 1)
-    auto row_of = [&](int64_t u, int i) -> int64_t { return p.pair_mode ? 4 * u + r : 4 * R * u + 4 * i + r; };
-    const size_t qrow = (size_t)nbp * ((WT == 8) ? 2 : 1);
-    const int    qoff = (WT == 8) ? l : (l & 3);
+    const MatvecSmem L = matvec_smem_layout(nbp, TM, (size_t)ring_bytes);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw + L.bars) + warp * MAX_STAGES;
+    uint8_t  *ring = smem_raw + L.ring + (size_t)warp * NS * stage_bytes;
 
-    uint4 wq[D][R];
-    uint2 ws[D][R];
-    auto load_item = [&](int j, int64_t u, int g) {
+    auto row_of = [&](int64_t u, int i) -> int64_t { return p.pair_mode ? 4 * u + r : 4 * (R * u + i) + r; };
+
+    // producer side (lane 0 of the warp): stage `slot` <- records [c * S, c * S + cnt) of the unit's R tiles
+    int64_t lu = my_first; int lc = 0, lslot = 0; int64_t issued = 0;
+    auto issue_next = [&]() {
+        const int      rec0  = lc * S;
+        const uint32_t bytes = (uint32_t)min(S, nrec - rec0) * RECB;
+        mbar_expect_tx(&bars[lslot], bytes * R);
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-            const DevMatrix &M   = (p.pair_mode && i == 1) ? p.B : p.A;
-            const int64_t    row = row_of(u, i);
-            wq[j][i] = ldg_stream(M.q + row * qrow + g * QW + qoff);
-            ws[j][i] = ldg_stream_u2(reinterpret_cast<const uint2 *>(M.d + row * nbp) + g);
+            const DevMatrix &M    = (p.pair_mode && i == 1) ? p.B : p.A;
+            const int64_t    tile = p.pair_mode ? lu : R * lu + i;
+            bulk_copy_g2s(ring + (size_t)lslot * stage_bytes + (size_t)i * S * RECB, M.w + ((size_t)tile * nrec + rec0) * RECB, bytes, &bars[lslot]);
         }
+        ++issued;
+        if (++lslot == NS) { lslot = 0; }
+        if (++lc == nch) { lc = 0; lu += MV_WARPS; }
     };
 
-    // Let the next kernel of the step begin, pull this CTA's rows towards L2 and start the register
-    // pipeline: weights never change during a step, so all of this may run ahead of the previous kernel's results.
+    // Let the next kernel of the step begin, and start streaming: weights never change during a step, so the
+    // copies may run ahead of the previous kernel's results.
     pdl_launch_dependents();
-    {
-        const int64_t rows_lo = p.pair_mode ? 4 * tile_lo : 4 * R * tile_lo, rows_hi = p.pair_mode ? 4 * tile_hi : 4 * R * tile_hi;
-        const size_t  qbytes = (size_t)(rows_hi - rows_lo) * qrow * 16, dbytes = (size_t)(rows_hi - rows_lo) * nbp * 2;
-        const int64_t nq = (int64_t)((qbytes + 4095) / 4096), nd = (int64_t)((dbytes + 4095) / 4096);
-        const int64_t per = nq + nd, total = per * (p.pair_mode ? 2 : 1);
-        for (int64_t i = threadIdx.x; i < total; i += MV_THREADS) {
-            const DevMatrix &M = (i >= per) ? p.B : p.A;
-            const int64_t    k = (i >= per) ? i - per : i;
-            if (k < nq) { l2_prefetch_piece(M.q + rows_lo * qrow, qbytes, k, nq); }
-            else        { l2_prefetch_piece(M.d + rows_lo * nbp, dbytes, k - nq, nd); }
-        }
+    if (lane == 0 && n_items > 0) {
+        for (int s = 0; s < NS; ++s) { mbar_init(&bars[s], 1); }
+        mbar_init_fence();
+        for (int s = 0; s < NS && issued < n_items; ++s) { issue_next(); }
     }
-    int64_t lu = my_first; int lg = 0; int64_t issued = 0;
-#pragma unroll
-    for (int j = 0; j < D; ++j) {
-        if (issued < n_items) {
-            load_item(j, lu, lg);
-            ++issued; if (++lg == ng) { lg = 0; lu += MV_WARPS; }
-        }
-    }
+    __syncwarp();
     pdl_wait();
 
     ActPlanes act = act_planes(smem_raw, nbp, TM);
@@ -257,12 +259,10 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
     matvec_tap(p, act);
 
     // this lane's operands: activation word (Q8_0 weights: word l; Q4_0: lanes 0..3 hold the high nibbles, which meet
-    // values 16..31 = words 4..7), the matching accumulator operand and the scale plane
-    const int     wsel  = (WT == 8) ? l : (l ^ 4);
-    const uint4  *Ysel  = act.Y + wsel;
-    const int4   *Bsel  = act.Bq + wsel;
-    const float4 *DXsel = (WT == 2 && l < 4) ? act.DX16 : act.DX;
-    const uint32_t mask = (l < 4) ? 0xf0f0f0f0u : 0x0f0f0f0fu;
+    // values 16..31 = words 4..7) and, for Q4_0, the shift that brings its nibbles into the high half of every byte
+    const uint4 *Ysel  = act.Y + ((WT == 8) ? l : (l ^ 4));
+    const int    shift = (l < 4) ? 0 : 4;
+    const int    qoff  = ((WT == 8) ? l : (l & 3)) * 16;
 
     float acc[TM][R];
 #pragma unroll
@@ -271,68 +271,82 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
         for (int i = 0; i < R; ++i) { acc[t][i] = 0.f; }
     }
 
-    int64_t cu = my_first; int cg = 0;
-    for (int64_t base = 0; base < n_items; base += D) {
+    int64_t  cu = my_first; int cc = 0, slot = 0; uint32_t parity = 0;
+    int64_t  n = 0;
+    bool     ok = true;
+    for (; n < n_items; ++n) {
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bars[slot], parity, WAIT_LIMIT_NS));
+        if (!ok) { break; }
+        const uint8_t *st   = ring + (size_t)slot * stage_bytes + r * ROWB;
+        const int      rec0 = cc * S;
+        const int      cnt  = min(S, nrec - rec0);
+        for (int rc = 0; rc < cnt; ++rc) {
 #pragma unroll
-        for (int j = 0; j < D; ++j) {
-            if (base + j < n_items) {
-                float s[R][4];
-                uint4 wm[R];
+            for (int gg = 0; gg < 2; ++gg) {
+                const int g = (rec0 + rc) * 2 + gg;
+                float    s[R][4];
+                uint4    wq[R];
 #pragma unroll
                 for (int i = 0; i < R; ++i) {
-                    const __half2 s01 = *reinterpret_cast<const __half2 *>(&ws[j][i].x), s23 = *reinterpret_cast<const __half2 *>(&ws[j][i].y);
-                    const float2  f01 = __half22float2(s01), f23 = __half22float2(s23);
+                    const uint8_t *rowp = st + (size_t)i * S * RECB + rc * RECB;
+                    wq[i] = *reinterpret_cast<const uint4 *>(rowp + gg * GRPB + qoff);
+                    const uint2   sc  = *reinterpret_cast<const uint2 *>(rowp + (ROWB - 16) + gg * 8);
+                    const float2  f01 = __half22float2(*reinterpret_cast<const __half2 *>(&sc.x)), f23 = __half22float2(*reinterpret_cast<const __half2 *>(&sc.y));
                     s[i][0] = f01.x; s[i][1] = f01.y; s[i][2] = f23.x; s[i][3] = f23.y;
-                    wm[i] = wq[j][i];
-                    if (WT == 2) { wm[i].x &= mask; wm[i].y &= mask; wm[i].z &= mask; wm[i].w &= mask; }
                 }
 #pragma unroll
                 for (int t = 0; t < TM; ++t) {
-                    const uint4  y  = Ysel[(t * ng + cg) * 8];
-                    const float4 dx = DXsel[t * ng + cg];
-                    int4 b = make_int4(0, 0, 0, 0);
-                    if (WT == 2) { b = Bsel[(t * ng + cg) * 8]; }
+                    const uint4  y  = Ysel[(t * ng + g) * 8];
+                    const float4 ds = act.DS[t * ng + g];
 #pragma unroll
                     for (int i = 0; i < R; ++i) {
                         float a = acc[t][i];
                         if (WT == 2) {
-                            a = fmaf(__fmul_rn(s[i][0], dx.x), lane_sum_q4_0(wm[i].x, y.x, b.x), a);
-                            a = fmaf(__fmul_rn(s[i][1], dx.y), lane_sum_q4_0(wm[i].y, y.y, b.y), a);
-                            a = fmaf(__fmul_rn(s[i][2], dx.z), lane_sum_q4_0(wm[i].z, y.z, b.z), a);
-                            a = fmaf(__fmul_rn(s[i][3], dx.w), lane_sum_q4_0(wm[i].w, y.w, b.w), a);
+                            a = fmaf(__fmul_rn(s[i][0], ds.x), lane_sum16_q4_0(wq[i].x, shift, y.x), a);
+                            a = fmaf(__fmul_rn(s[i][1], ds.y), lane_sum16_q4_0(wq[i].y, shift, y.y), a);
+                            a = fmaf(__fmul_rn(s[i][2], ds.z), lane_sum16_q4_0(wq[i].z, shift, y.z), a);
+                            a = fmaf(__fmul_rn(s[i][3], ds.w), lane_sum16_q4_0(wq[i].w, shift, y.w), a);
                         } else {
-                            a = fmaf(__fmul_rn(s[i][0], dx.x), lane_sum_q8_0(wm[i].x, y.x), a);
-                            a = fmaf(__fmul_rn(s[i][1], dx.y), lane_sum_q8_0(wm[i].y, y.y), a);
-                            a = fmaf(__fmul_rn(s[i][2], dx.z), lane_sum_q8_0(wm[i].z, y.z), a);
-                            a = fmaf(__fmul_rn(s[i][3], dx.w), lane_sum_q8_0(wm[i].w, y.w), a);
+                            a = fmaf(__fmul_rn(s[i][0], ds.x), lane_sum_q8_0(wq[i].x, y.x), a);
+                            a = fmaf(__fmul_rn(s[i][1], ds.y), lane_sum_q8_0(wq[i].y, y.y), a);
+                            a = fmaf(__fmul_rn(s[i][2], ds.z), lane_sum_q8_0(wq[i].z, y.z), a);
+                            a = fmaf(__fmul_rn(s[i][3], ds.w), lane_sum_q8_0(wq[i].w, y.w), a);
                         }
                         acc[t][i] = a;
                     }
                 }
-                if (issued < n_items) {
-                    load_item(j, lu, lg);
-                    ++issued; if (++lg == ng) { lg = 0; lu += MV_WARPS; }
-                }
-                if (++cg == ng) {   // tile finished: fixed reduction tree over the 8 accumulators of each row, then the epilogue
+            }
+        }
+        __syncwarp();   // every lane is done reading the stage: hand it back to the copy engine
+        if (lane == 0 && issued < n_items) { issue_next(); }
+        if (++slot == NS) { slot = 0; parity ^= 1u; }
+        if (++cc == nch) {   // unit finished: fixed reduction tree over the 8 accumulators of each row, then the epilogue
 #pragma unroll
-                    for (int t = 0; t < TM; ++t) {
-                        float h[R];
+            for (int t = 0; t < TM; ++t) {
+                float h[R];
 #pragma unroll
-                        for (int i = 0; i < R; ++i) { h[i] = hsum8_lanes(acc[t][i]); acc[t][i] = 0.f; }
-                        const bool writer = (l == 0) && (t < p.T);
-                        if (p.epi == EPI_SILU_MUL) {
-                            if (R == 2) { matvec_epilogue_silu(p, row_of(cu, 0), t, h[0], h[R - 1], writer); }
-                        } else {
+                for (int i = 0; i < R; ++i) { h[i] = hsum8_lanes(acc[t][i]); acc[t][i] = 0.f; }
+                const bool writer = (l == 0) && (t < p.T);
+                if (p.epi == EPI_SILU_MUL) {
+                    if (R == 2) { matvec_epilogue_silu(p, row_of(cu, 0), t, h[0], h[R - 1], writer); }
+                } else {
 #pragma unroll
-                            for (int i = 0; i < R; ++i) {
-                                const float partner = __shfl_xor_sync(0xffffffffu, h[i], 8);
-                                matvec_epilogue(p, row_of(cu, i), t, h[i], partner, writer);
-                            }
-                        }
+                    for (int i = 0; i < R; ++i) {
+                        const float partner = __shfl_xor_sync(0xffffffffu, h[i], 8);
+                        matvec_epilogue(p, row_of(cu, i), t, h[i], partner, writer);
                     }
-                    cg = 0; cu += MV_WARPS;
                 }
             }
+            cc = 0; cu += MV_WARPS;
+        }
+    }
+    if (!ok) {
+        // a copy did not arrive: report, give the copies still in flight a last bounded chance to land (they
+        // target this CTA's shared memory) and stop; the host sees the flag at its next synchronisation
+        if (lane == 0 && p.error_flag != nullptr) { atomicExch(p.error_flag, 1); }
+        for (int64_t k = n; k < issued; ++k) {
+            mbar_wait_bounded(&bars[slot], parity, 10000000ull);
+            if (++slot == NS) { slot = 0; parity ^= 1u; }
         }
     }
 
@@ -347,21 +361,41 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
     }
 }
 
+int matvec_max_columns(int nb) {
+    for (int t = 8; t > 1; t >>= 1) { if (act_plane_bytes(padded_blocks(nb), t) <= 120 * 1024) { return t; } }
+    return 1;
+}
+
 template <int WT, int TM, int R>
 static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) {
-    const size_t smem = matvec_smem_bytes(p.A.nb, TM);
+    constexpr int RECB = 4 * (((WT == 8) ? 256 : 128) + 16);
+    // every SM gets CTAs even when there are fewer units than warps: a unit is a sequential walk along K, so
+    // spreading units over all SMs (with some warps idle) beats filling a few CTAs
+    const int64_t n_units = p.pair_mode ? (p.A.n_rows >> 2) : (p.A.n_rows / (4 * R));
+    const int     per_sm  = (TM == 1) ? cfg.mv_ctas_per_sm : 1;
+    int64_t grid = (int64_t)cfg.num_sms * per_sm;
+    if (grid > n_units) { grid = n_units; }
+    if (grid < 1) { grid = 1; }
+    const int n_act = (int)std::min<int64_t>(MV_WARPS, (n_units + grid - 1) / grid);
+
+    // ring: what the SM's shared memory leaves after the activation planes (two CTAs per SM for single columns)
+    const MatvecSmem fixed = matvec_smem_layout(p.A.nbp, TM, 0);
+    const size_t budget = (per_sm == 2) ? 112 * 1024 : 224 * 1024;
+    if (fixed.total + (size_t)2 * n_act * R * RECB > budget) { return cudaErrorInvalidValue; }   // rows too long for this kernel
+    size_t ring = std::min<size_t>((size_t)cfg.mv_ring_kb * 1024 * ((TM == 1) ? 1 : 2), budget - fixed.total) / 128 * 128;
+    const int nrec = p.A.nbp >> 3;
+    int S = 4;   // records per stage: as long as the ring still holds four stages per warp
+    while (S > 1 && (S > nrec || ring / ((size_t)n_act * R * S * RECB) < 4)) { S >>= 1; }
+    const size_t smem = fixed.total + ring;
+
     static size_t smem_allowed = 48 * 1024;   // one process drives one device, so one high-water mark per kernel suffices
     if (smem > smem_allowed) {
         cudaError_t err = cudaFuncSetAttribute(matvec_kernel<WT, TM, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) { return err; }
         smem_allowed = smem;
     }
-    // every SM gets a CTA even when there are fewer tiles than warps: a tile is a sequential walk along K, so
-    // spreading tiles over all SMs (with some warps idle) beats filling a few CTAs
-    const int64_t n_tiles = p.pair_mode ? (p.A.n_rows >> 2) : (p.A.n_rows / (4 * R));
-    int64_t grid = (int64_t)cfg.num_sms * ((TM == 1) ? cfg.mv_ctas_per_sm : 1);
-    if (grid > n_tiles) { grid = n_tiles; }
-    if (grid < 1) { grid = 1; }
+    MatvecParams q = p;
+    if (q.error_flag == nullptr) { q.error_flag = cfg.error_flag; }
 
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3((unsigned)grid); lc.blockDim = dim3(MV_THREADS); lc.dynamicSmemBytes = smem; lc.stream = cfg.stream;
@@ -369,12 +403,7 @@ static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&lc, matvec_kernel<WT, TM, R>, p);
-}
-
-int matvec_max_columns(int nb) {
-    for (int t = 8; t > 1; t >>= 1) { if (matvec_smem_bytes(nb, t) <= 200 * 1024) { return t; } }
-    return 1;
+    return cudaLaunchKernelEx(&lc, matvec_kernel<WT, TM, R>, q, (int)ring, S);
 }
 
 template <int WT, int R>
@@ -387,11 +416,11 @@ static cudaError_t launch_matvec_w(const MatvecParams &p, const LaunchCfg &cfg) 
 
 cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg) {
     if (p.T < 1 || p.T > matvec_max_columns(p.A.nb)) { return cudaErrorInvalidValue; }
-    if (p.A.k % QK != 0 || p.A.nb < 1 || p.A.nbp != padded_blocks(p.A.nb)) { return cudaErrorInvalidValue; }
+    if (p.A.k % QK != 0 || p.A.nb < 1 || p.A.nbp != padded_blocks(p.A.nb) || p.A.w == nullptr) { return cudaErrorInvalidValue; }
     if (p.A.n_rows & 3) { return cudaErrorInvalidValue; }
-    if (p.pair_mode && (p.B.type != p.A.type || p.B.n_rows != p.A.n_rows || p.B.k != p.A.k || p.B.nbp != p.A.nbp)) { return cudaErrorInvalidValue; }
+    if (p.pair_mode && (p.B.type != p.A.type || p.B.n_rows != p.A.n_rows || p.B.k != p.A.k || p.B.nbp != p.A.nbp || p.B.w == nullptr)) { return cudaErrorInvalidValue; }
     if ((p.epi == EPI_SILU_MUL) != (p.pair_mode != 0)) { return cudaErrorInvalidValue; }
-    // rows per lane: two when one row per lane would leave tiles waiting for a free warp (single column), or in pair mode
+    // tiles per warp: two when one would leave units waiting for a free warp (single column), or in pair mode
     bool two = p.pair_mode != 0;
     if (!two && p.T == 1 && (p.A.n_rows & 7) == 0) {
         const int64_t slots = (int64_t)cfg.num_sms * cfg.mv_ctas_per_sm * MV_WARPS;

@@ -200,9 +200,8 @@ void prefetch_next(spyb_model *m, P &p, const DevMatrix *a, const DevMatrix *b =
     if (!m->be->l2_prefetch_next) { return; }
     int k = 0;
     for (const DevMatrix *x : {a, b}) {
-        if (x == nullptr || x->q == nullptr) { continue; }
-        p.pf_ptr[k] = x->q; p.pf_bytes[k] = std::min(q_plane_bytes(x->type, x->n_rows, x->nb), m->be->l2_prefetch_cap); ++k;
-        p.pf_ptr[k] = x->d; p.pf_bytes[k] = d_plane_bytes(x->n_rows, x->nb); ++k;
+        if (x == nullptr || x->w == nullptr) { continue; }
+        p.pf_ptr[k] = x->w; p.pf_bytes[k] = std::min(matrix_bytes(x->type, x->n_rows, x->nb), m->be->l2_prefetch_cap); ++k;
     }
 }
 
@@ -493,6 +492,7 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
     }
     SPYB_CUDA(be, cudaEventRecord(m->ev1, be->stream));
     SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+    if (be->device_error()) { return SPYB_FAIL; }
     if (logits_host != nullptr) { std::memcpy(logits_host, m->h_logits_pinned, (size_t)m->info.n_vocab * 4); }
     SPYB_CUDA(be, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
     m->last_launches = launches;
@@ -544,6 +544,7 @@ spyb_status spyb_model_decode(spyb_model *m, int32_t first_token, int32_t n_past
     SPYB_CUDA(be, cudaEventRecord(m->ev1, be->stream));
     SPYB_CUDA(be, cudaMemcpyAsync(ids_host, m->d_history + n_past, (size_t)n_steps * 4, cudaMemcpyDeviceToHost, be->stream));
     SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+    if (be->device_error()) { return SPYB_FAIL; }
     SPYB_CUDA(be, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
     m->last_launches = per_step * n_steps;
     return SPYB_SUCCESS;

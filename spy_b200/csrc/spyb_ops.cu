@@ -239,30 +239,35 @@ cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
 }
 
 // =============================================================================================
-// upload-time re-tiling: raw 18-byte / 34-byte blocks -> word-transposed planes (one thread per padded block;
-// blocks beyond nb are written as zeros with a zero scale)
+// upload-time re-tiling: raw 18-byte / 34-byte blocks -> the record stream described at DevMatrix
+// (one thread per padded block; blocks beyond nb are written as zeros with a zero scale)
 template <int WORDS>   // 4: Q4_0 (16 nibble bytes), 8: Q8_0 (32 int8 values)
-__global__ void retile_kernel(const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, int nbp, uint4 *q, uint16_t *d) {
+__global__ void retile_kernel(const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, int nbp, uint8_t *dst) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_rows * nbp) { return; }
-    const int64_t  r = i / nbp;
-    const int      b = (int)(i - r * nbp);
-    const uint8_t *src = raw + r * row_stride + (int64_t)b * (2 + 4 * WORDS);
+    const int64_t  row = i / nbp;
+    const int      b = (int)(i - row * nbp);
+    const uint8_t *src = raw + row * row_stride + (int64_t)b * (2 + 4 * WORDS);
     const bool     real = b < nb;
-    d[i] = real ? (uint16_t)(src[0] | (src[1] << 8)) : (uint16_t)0;
-    uint32_t *dst = reinterpret_cast<uint32_t *>(q + (r * (nbp >> 2) + (b >> 2)) * WORDS) + (b & 3);
+    constexpr int  ROWB = WORDS * 32 + 16;
+    uint8_t  *rec = dst + ((row >> 2) * (nbp >> 3) + (b >> 3)) * (4 * ROWB) + (row & 3) * ROWB;
+    uint32_t *q   = reinterpret_cast<uint32_t *>(rec + ((b >> 2) & 1) * (WORDS * 16)) + (b & 3);
+    reinterpret_cast<uint16_t *>(rec + WORDS * 32)[b & 7] = real ? (uint16_t)(src[0] | (src[1] << 8)) : (uint16_t)0;
 #pragma unroll
     for (int k = 0; k < WORDS; ++k) {
-        dst[4 * k] = real ? (uint32_t)(src[2 + 4 * k] | (src[3 + 4 * k] << 8) | (src[4 + 4 * k] << 16) | ((uint32_t)src[5 + 4 * k] << 24)) : 0u;
+        uint32_t v = real ? (uint32_t)(src[2 + 4 * k] | (src[3 + 4 * k] << 8) | (src[4 + 4 * k] << 16) | ((uint32_t)src[5 + 4 * k] << 24)) : 0u;
+        if (WORDS == 4) { v ^= 0x88888888u; }
+        q[4 * k] = v;
     }
 }
 
-cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint4 *q_row0, uint16_t *d_row0, cudaStream_t s) {
+cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *dst, cudaStream_t s) {
     const int     nbp = padded_blocks(nb);
     const int64_t n = n_rows * nbp;
     if (n == 0) { return cudaSuccess; }
-    if (type == 2)      { retile_kernel<4><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, q_row0, d_row0); }
-    else if (type == 8) { retile_kernel<8><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, q_row0, d_row0); }
+    if (n_rows & 3) { return cudaErrorInvalidValue; }
+    if (type == 2)      { retile_kernel<4><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, dst); }
+    else if (type == 8) { retile_kernel<8><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, dst); }
     else                { return cudaErrorNotSupported; }
     return launch_check();
 }
@@ -297,19 +302,18 @@ __global__ void block_dots_kernel(int wtype, const uint8_t *w, const uint8_t *xb
     const int64_t b = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= nblk) { return; }
     const uint8_t *y = xb + b * 34 + 2;
-    uint32_t yw[8]; int gs[8];
+    uint32_t yw[8];
     for (int k = 0; k < 8; ++k) {
         yw[k] = y[4 * k] | (y[4 * k + 1] << 8) | (y[4 * k + 2] << 16) | ((uint32_t)y[4 * k + 3] << 24);
-        gs[k] = (int)(int8_t)y[4 * k] + (int)(int8_t)y[4 * k + 1] + (int)(int8_t)y[4 * k + 2] + (int)(int8_t)y[4 * k + 3];
     }
     int total = 0;
     if (wtype == 2) {
         const uint8_t *q = w + b * 18 + 2;
         for (int k = 0; k < 4; ++k) {
             const uint32_t ww = q[4 * k] | (q[4 * k + 1] << 8) | (q[4 * k + 2] << 16) | ((uint32_t)q[4 * k + 3] << 24);
-            const float hi = lane_sum_q4_0(ww & 0xf0f0f0f0u, yw[4 + k], (int)MAGIC_I - 128 * gs[4 + k]);   // comes scaled by 16
-            const float lo = lane_sum_q4_0(ww & 0x0f0f0f0fu, yw[k], (int)MAGIC_I - 8 * gs[k]);
-            total += (int)hi / 16 + (int)lo;
+            const float hi = lane_sum16_q4_0(ww ^ 0x88888888u, 0, yw[4 + k]);   // both come scaled by 16
+            const float lo = lane_sum16_q4_0(ww ^ 0x88888888u, 4, yw[k]);
+            total += (int)hi / 16 + (int)lo / 16;
         }
     } else {
         const uint8_t *q = w + b * 34 + 2;
