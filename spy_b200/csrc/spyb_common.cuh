@@ -53,20 +53,20 @@ __device__ __forceinline__ void l2_prefetch_piece(const void *ptr, size_t bytes,
 // bulk asynchronous copies global -> shared memory, completion counted on an mbarrier (no tensor map: plain
 // contiguous runs; both addresses and the size are multiples of 16 bytes)
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {   // `bar`: shared-space address of the 8-byte barrier
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
 __device__ __forceinline__ void mbar_init_fence() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
 // bounded wait: false when the phase did not complete within `limit_ns` of wall-clock time
@@ -75,7 +75,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, uint64_t limit_ns) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) { return true; }
     const uint64_t t0 = global_timer_ns();
     for (;;) {
@@ -83,9 +83,9 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
         if (global_timer_ns() - t0 > limit_ns) { return false; }
     }
 }
-__device__ __forceinline__ void bulk_copy_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void *src_gmem, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst_smem)), "l"(__cvta_generic_to_global(src_gmem)), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+                 ::"r"(dst_smem), "l"(__cvta_generic_to_global(src_gmem)), "r"(bytes), "r"(bar) : "memory");
 }
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -134,11 +134,11 @@ constexpr uint32_t MAGIC_I = 0x4B400000u;
 // lanes 0..3 = sum over k = 4j..4j+3 of (high nibble_k - 8) * y[16+k], lanes 4..7 = the same with low nibbles
 // and y[k]; Dot<Q8_0,Q8_0>::exec, vec_dot.h:103-113: lane l = sum of products 4l..4l+3), returned as a float.
 //   Q4_0: `w_x88` = the weight word XOR 0x88888888 (every nibble then is value - 8 in two's complement);
-//   `shift` = 0 for the high nibbles, 4 for the low ones: the selected nibble of every byte lands in the high
-//   half of its byte, which as a signed byte is 16 * (value - 8). The result is 16 * lane_sum; the caller
+//   `mult` = 1 for the high nibbles, 16 for the low ones: the selected nibble of every byte lands in the high
+//   half of its byte (a multiply, so that it runs on the FMA pipe beside the integer dot products), which as a signed byte is 16 * (value - 8). The result is 16 * lane_sum; the caller
 //   multiplies by scale / 16, which is exact.
-__device__ __forceinline__ float lane_sum16_q4_0(uint32_t w_x88, int shift, uint32_t y) {
-    return __int_as_float(__dp4a((int)((w_x88 << shift) & 0xf0f0f0f0u), (int)y, (int)MAGIC_I)) - MAGIC_F;
+__device__ __forceinline__ float lane_sum16_q4_0(uint32_t w_x88, uint32_t mult, uint32_t y) {
+    return __int_as_float(__dp4a((int)((w_x88 * mult) & 0xf0f0f0f0u), (int)y, (int)MAGIC_I)) - MAGIC_F;
 }
 __device__ __forceinline__ float lane_sum_q8_0(uint32_t w, uint32_t y) {
     return __int_as_float(__dp4a((int)w, (int)y, (int)MAGIC_I)) - MAGIC_F;

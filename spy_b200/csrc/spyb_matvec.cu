@@ -212,42 +212,48 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
     const int64_t unit_lo  = n_units * blockIdx.x / gridDim.x;
     const int64_t unit_hi  = n_units * (blockIdx.x + 1) / gridDim.x;
     const int64_t my_first = unit_lo + warp;
-    const int64_t my_units = (my_first < unit_hi) ? (unit_hi - my_first + MV_WARPS - 1) / MV_WARPS : 0;
+    const int     my_units = (my_first < unit_hi) ? (int)((unit_hi - my_first + MV_WARPS - 1) / MV_WARPS) : 0;
     const int     n_act    = (int)min((int64_t)MV_WARPS, unit_hi - unit_lo);   // warps of this CTA that have work
     const int     nch      = (nrec + S - 1) / S;                               // stages per unit
-    const int64_t n_items  = my_units * nch;
+    const int     n_items  = my_units * nch;
     const int     stage_bytes = R * S * RECB;
     const int     NS = max(1, min(MAX_STAGES, ring_bytes / (max(n_act, 1) * stage_bytes)));
 
     const MatvecSmem L = matvec_smem_layout(nbp, TM, (size_t)ring_bytes);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem_raw + L.bars) + warp * MAX_STAGES;
-    uint8_t  *ring = smem_raw + L.ring + (size_t)warp * NS * stage_bytes;
+    uint8_t       *ring   = smem_raw + L.ring + (size_t)warp * NS * stage_bytes;
+    const uint32_t ring_s = smem_u32(ring);
+    const uint32_t bar_s  = smem_u32(smem_raw + L.bars) + warp * MAX_STAGES * 8;
+    const size_t   tile_bytes = (size_t)nrec * RECB;
 
-    auto row_of = [&](int64_t u, int i) -> int64_t { return p.pair_mode ? 4 * u + r : 4 * (R * u + i) + r; };
-
-    // producer side (lane 0 of the warp): stage `slot` <- records [c * S, c * S + cnt) of the unit's R tiles
-    int64_t lu = my_first; int lc = 0, lslot = 0; int64_t issued = 0;
-    auto issue_next = [&]() {
-        const int      rec0  = lc * S;
-        const uint32_t bytes = (uint32_t)min(S, nrec - rec0) * RECB;
-        mbar_expect_tx(&bars[lslot], bytes * R);
+    // producer side (lane 0 of the warp): stage `lslot` <- the next <= S records of the unit's R tiles
+    const uint8_t *src[R];
+    int64_t lu = my_first; int lrec = 0, lslot = 0, issued = 0;
+    auto unit_sources = [&](int64_t u) {
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-            const DevMatrix &M    = (p.pair_mode && i == 1) ? p.B : p.A;
-            const int64_t    tile = p.pair_mode ? lu : R * lu + i;
-            bulk_copy_g2s(ring + (size_t)lslot * stage_bytes + (size_t)i * S * RECB, M.w + ((size_t)tile * nrec + rec0) * RECB, bytes, &bars[lslot]);
+            const DevMatrix &M = (p.pair_mode && i == 1) ? p.B : p.A;
+            src[i] = M.w + (size_t)(p.pair_mode ? u : R * u + i) * tile_bytes;
         }
+    };
+    auto issue_next = [&]() {
+        const uint32_t bytes = (uint32_t)min(S, nrec - lrec) * RECB;
+        const uint32_t bar = bar_s + lslot * 8, dst = ring_s + lslot * stage_bytes;
+        mbar_expect_tx(bar, bytes * R);
+#pragma unroll
+        for (int i = 0; i < R; ++i) { bulk_copy_g2s(dst + i * S * RECB, src[i], bytes, bar); src[i] += bytes; }
         ++issued;
         if (++lslot == NS) { lslot = 0; }
-        if (++lc == nch) { lc = 0; lu += MV_WARPS; }
+        lrec += S;
+        if (lrec >= nrec) { lrec = 0; lu += MV_WARPS; unit_sources(lu); }
     };
 
     // Let the next kernel of the step begin, and start streaming: weights never change during a step, so the
     // copies may run ahead of the previous kernel's results.
     pdl_launch_dependents();
     if (lane == 0 && n_items > 0) {
-        for (int s = 0; s < NS; ++s) { mbar_init(&bars[s], 1); }
+        for (int s = 0; s < NS; ++s) { mbar_init(bar_s + s * 8, 1); }
         mbar_init_fence();
+        unit_sources(lu);
         for (int s = 0; s < NS && issued < n_items; ++s) { issue_next(); }
     }
     __syncwarp();
@@ -259,10 +265,11 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
     matvec_tap(p, act);
 
     // this lane's operands: activation word (Q8_0 weights: word l; Q4_0: lanes 0..3 hold the high nibbles, which meet
-    // values 16..31 = words 4..7) and, for Q4_0, the shift that brings its nibbles into the high half of every byte
-    const uint4 *Ysel  = act.Y + ((WT == 8) ? l : (l ^ 4));
-    const int    shift = (l < 4) ? 0 : 4;
-    const int    qoff  = ((WT == 8) ? l : (l & 3)) * 16;
+    // values 16..31 = words 4..7) and, for Q4_0, the factor that brings its nibbles into the high half of every byte
+    const uint4   *Ysel = act.Y + ((WT == 8) ? l : (l ^ 4));
+    const uint32_t mult = (l < 4) ? 1u : 16u;
+    const uint8_t *lane_base = ring + r * ROWB;
+    const int      qoff = ((WT == 8) ? l : (l & 3)) * 16;
 
     float acc[TM][R];
 #pragma unroll
@@ -271,27 +278,32 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
         for (int i = 0; i < R; ++i) { acc[t][i] = 0.f; }
     }
 
-    int64_t  cu = my_first; int cc = 0, slot = 0; uint32_t parity = 0;
-    int64_t  n = 0;
+    int64_t  cu = my_first; int crec = 0, slot = 0; uint32_t parity = 0;
+    int      n = 0;
     bool     ok = true;
     for (; n < n_items; ++n) {
-        ok = __all_sync(0xffffffffu, mbar_wait_bounded(&bars[slot], parity, WAIT_LIMIT_NS));
-        if (!ok) { break; }
-        const uint8_t *st   = ring + (size_t)slot * stage_bytes + r * ROWB;
-        const int      rec0 = cc * S;
-        const int      cnt  = min(S, nrec - rec0);
+        ok = mbar_wait_bounded(bar_s + slot * 8, parity, WAIT_LIMIT_NS);
+        if (__any_sync(0xffffffffu, !ok)) { ok = false; break; }
+        const uint8_t *st  = lane_base + slot * stage_bytes;
+        const int      cnt = min(S, nrec - crec);
+#pragma unroll 1
         for (int rc = 0; rc < cnt; ++rc) {
+            uint4 wq[R][2]; uint4 sc[R];
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+                const uint8_t *rowp = st + i * S * RECB + rc * RECB;
+                wq[i][0] = *reinterpret_cast<const uint4 *>(rowp + qoff);
+                wq[i][1] = *reinterpret_cast<const uint4 *>(rowp + GRPB + qoff);
+                sc[i]    = *reinterpret_cast<const uint4 *>(rowp + (ROWB - 16));
+            }
 #pragma unroll
             for (int gg = 0; gg < 2; ++gg) {
-                const int g = (rec0 + rc) * 2 + gg;
-                float    s[R][4];
-                uint4    wq[R];
+                const int g = (crec + rc) * 2 + gg;
+                float s[R][4];
 #pragma unroll
                 for (int i = 0; i < R; ++i) {
-                    const uint8_t *rowp = st + (size_t)i * S * RECB + rc * RECB;
-                    wq[i] = *reinterpret_cast<const uint4 *>(rowp + gg * GRPB + qoff);
-                    const uint2   sc  = *reinterpret_cast<const uint2 *>(rowp + (ROWB - 16) + gg * 8);
-                    const float2  f01 = __half22float2(*reinterpret_cast<const __half2 *>(&sc.x)), f23 = __half22float2(*reinterpret_cast<const __half2 *>(&sc.y));
+                    const uint32_t s01 = gg ? sc[i].z : sc[i].x, s23 = gg ? sc[i].w : sc[i].y;
+                    const float2   f01 = __half22float2(*reinterpret_cast<const __half2 *>(&s01)), f23 = __half22float2(*reinterpret_cast<const __half2 *>(&s23));
                     s[i][0] = f01.x; s[i][1] = f01.y; s[i][2] = f23.x; s[i][3] = f23.y;
                 }
 #pragma unroll
@@ -300,17 +312,18 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
                     const float4 ds = act.DS[t * ng + g];
 #pragma unroll
                     for (int i = 0; i < R; ++i) {
+                        const uint4 w = wq[i][gg];
                         float a = acc[t][i];
                         if (WT == 2) {
-                            a = fmaf(__fmul_rn(s[i][0], ds.x), lane_sum16_q4_0(wq[i].x, shift, y.x), a);
-                            a = fmaf(__fmul_rn(s[i][1], ds.y), lane_sum16_q4_0(wq[i].y, shift, y.y), a);
-                            a = fmaf(__fmul_rn(s[i][2], ds.z), lane_sum16_q4_0(wq[i].z, shift, y.z), a);
-                            a = fmaf(__fmul_rn(s[i][3], ds.w), lane_sum16_q4_0(wq[i].w, shift, y.w), a);
+                            a = fmaf(__fmul_rn(s[i][0], ds.x), lane_sum16_q4_0(w.x, mult, y.x), a);
+                            a = fmaf(__fmul_rn(s[i][1], ds.y), lane_sum16_q4_0(w.y, mult, y.y), a);
+                            a = fmaf(__fmul_rn(s[i][2], ds.z), lane_sum16_q4_0(w.z, mult, y.z), a);
+                            a = fmaf(__fmul_rn(s[i][3], ds.w), lane_sum16_q4_0(w.w, mult, y.w), a);
                         } else {
-                            a = fmaf(__fmul_rn(s[i][0], ds.x), lane_sum_q8_0(wq[i].x, y.x), a);
-                            a = fmaf(__fmul_rn(s[i][1], ds.y), lane_sum_q8_0(wq[i].y, y.y), a);
-                            a = fmaf(__fmul_rn(s[i][2], ds.z), lane_sum_q8_0(wq[i].z, y.z), a);
-                            a = fmaf(__fmul_rn(s[i][3], ds.w), lane_sum_q8_0(wq[i].w, y.w), a);
+                            a = fmaf(__fmul_rn(s[i][0], ds.x), lane_sum_q8_0(w.x, y.x), a);
+                            a = fmaf(__fmul_rn(s[i][1], ds.y), lane_sum_q8_0(w.y, y.y), a);
+                            a = fmaf(__fmul_rn(s[i][2], ds.z), lane_sum_q8_0(w.z, y.z), a);
+                            a = fmaf(__fmul_rn(s[i][3], ds.w), lane_sum_q8_0(w.w, y.w), a);
                         }
                         acc[t][i] = a;
                     }
@@ -320,32 +333,34 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
         __syncwarp();   // every lane is done reading the stage: hand it back to the copy engine
         if (lane == 0 && issued < n_items) { issue_next(); }
         if (++slot == NS) { slot = 0; parity ^= 1u; }
-        if (++cc == nch) {   // unit finished: fixed reduction tree over the 8 accumulators of each row, then the epilogue
+        crec += S;
+        if (crec >= nrec) {   // unit finished: fixed reduction tree over the 8 accumulators of each row, then the epilogue
 #pragma unroll
             for (int t = 0; t < TM; ++t) {
                 float h[R];
 #pragma unroll
                 for (int i = 0; i < R; ++i) { h[i] = hsum8_lanes(acc[t][i]); acc[t][i] = 0.f; }
-                const bool writer = (l == 0) && (t < p.T);
+                const bool    writer = (l == 0) && (t < p.T);
+                const int64_t row0 = p.pair_mode ? 4 * cu + r : 4 * R * cu + r;
                 if (p.epi == EPI_SILU_MUL) {
-                    if (R == 2) { matvec_epilogue_silu(p, row_of(cu, 0), t, h[0], h[R - 1], writer); }
+                    if (R == 2) { matvec_epilogue_silu(p, row0, t, h[0], h[R - 1], writer); }
                 } else {
 #pragma unroll
                     for (int i = 0; i < R; ++i) {
                         const float partner = __shfl_xor_sync(0xffffffffu, h[i], 8);
-                        matvec_epilogue(p, row_of(cu, i), t, h[i], partner, writer);
+                        matvec_epilogue(p, row0 + 4 * i, t, h[i], partner, writer);
                     }
                 }
             }
-            cc = 0; cu += MV_WARPS;
+            crec = 0; cu += MV_WARPS;
         }
     }
     if (!ok) {
         // a copy did not arrive: report, give the copies still in flight a last bounded chance to land (they
         // target this CTA's shared memory) and stop; the host sees the flag at its next synchronisation
         if (lane == 0 && p.error_flag != nullptr) { atomicExch(p.error_flag, 1); }
-        for (int64_t k = n; k < issued; ++k) {
-            mbar_wait_bounded(&bars[slot], parity, 10000000ull);
+        for (int k = n; k < __shfl_sync(0xffffffffu, issued, 0); ++k) {
+            mbar_wait_bounded(bar_s + slot * 8, parity, 10000000ull);
             if (++slot == NS) { slot = 0; parity ^= 1u; }
         }
     }
@@ -384,8 +399,8 @@ static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) 
     if (fixed.total + (size_t)2 * n_act * R * RECB > budget) { return cudaErrorInvalidValue; }   // rows too long for this kernel
     size_t ring = std::min<size_t>((size_t)cfg.mv_ring_kb * 1024 * ((TM == 1) ? 1 : 2), budget - fixed.total) / 128 * 128;
     const int nrec = p.A.nbp >> 3;
-    int S = 4;   // records per stage: as long as the ring still holds four stages per warp
-    while (S > 1 && (S > nrec || ring / ((size_t)n_act * R * S * RECB) < 4)) { S >>= 1; }
+    int S = 8;   // records per stage: as large as still leaves three stages per warp in the ring
+    while (S > 1 && (S > nrec || ring / ((size_t)n_act * R * S * RECB) < 3)) { S >>= 1; }
     const size_t smem = fixed.total + ring;
 
     static size_t smem_allowed = 48 * 1024;   // one process drives one device, so one high-water mark per kernel suffices

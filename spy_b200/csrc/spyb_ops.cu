@@ -311,8 +311,8 @@ __global__ void block_dots_kernel(int wtype, const uint8_t *w, const uint8_t *xb
         const uint8_t *q = w + b * 18 + 2;
         for (int k = 0; k < 4; ++k) {
             const uint32_t ww = q[4 * k] | (q[4 * k + 1] << 8) | (q[4 * k + 2] << 16) | ((uint32_t)q[4 * k + 3] << 24);
-            const float hi = lane_sum16_q4_0(ww ^ 0x88888888u, 0, yw[4 + k]);   // both come scaled by 16
-            const float lo = lane_sum16_q4_0(ww ^ 0x88888888u, 4, yw[k]);
+            const float hi = lane_sum16_q4_0(ww ^ 0x88888888u, 1u, yw[4 + k]);   // both come scaled by 16
+            const float lo = lane_sum16_q4_0(ww ^ 0x88888888u, 16u, yw[k]);
             total += (int)hi / 16 + (int)lo / 16;
         }
     } else {
