@@ -104,6 +104,7 @@ def lib():
         "spyb_model_last_ms": (C.c_float, [vp]),
         "spyb_model_last_launches": (i64, [vp]),
         "spyb_model_tap_xq": (i32, [vp, vp]),
+        "spyb_model_read_timeline": (i32, [vp, vp, i32]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(l, name)
@@ -341,6 +342,13 @@ class LlamaModel:
     @property
     def last_launches(self) -> int:
         return int(self._l.spyb_model_last_launches(self.h))
+
+    def timeline(self) -> np.ndarray:
+        """[n_kernels, 4] device-clock stamps (ns) of the last step; empty unless loaded with SPYB_TIMELINE=1."""
+        n = 5 * self.info.n_layer + 1
+        out = np.zeros((n, 4), dtype=np.uint64)
+        got = self._l.spyb_model_read_timeline(self.h, _np_ptr(out), n)
+        return out[:got]
 
     def tap_xq(self) -> np.ndarray:
         out = np.empty(self.info.d_model // 32 * 34, dtype=np.uint8)

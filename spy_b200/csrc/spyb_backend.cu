@@ -174,6 +174,8 @@ spyb_status spyb_create(const spyb_config *config, spyb_backend **out) {
     be->num_sms = prop.multiProcessorCount;
     if (const char *v = std::getenv("SPYB_L2_PREFETCH_MB")) { const int mb = std::atoi(v); be->l2_prefetch_next = mb > 0; be->l2_prefetch_cap = (size_t)std::max(mb, 0) << 20; }   // tuning knob
     if (const char *v = std::getenv("SPYB_MV_CTAS_PER_SM")) { be->mv_ctas_per_sm = std::max(1, std::min(2, std::atoi(v))); }   // tuning knob
+    if (const char *v = std::getenv("SPYB_MV_S")) { be->mv_force_s = std::atoi(v); }         // tuning knobs
+    if (const char *v = std::getenv("SPYB_MV_WACT")) { be->mv_force_wact = std::atoi(v); }
     if (const char *v = std::getenv("SPYB_MV_RING_KB")) { be->mv_ring_kb = std::max(8, std::min(96, std::atoi(v))); }   // tuning knob
     if (cudaStreamCreateWithFlags(&be->stream, cudaStreamNonBlocking) != cudaSuccess) { delete be; return SPYB_FAIL; }
     if (cudaHostAlloc(reinterpret_cast<void **>(&be->h_error_flag), sizeof(int), cudaHostAllocMapped) != cudaSuccess ||

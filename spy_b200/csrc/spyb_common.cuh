@@ -75,6 +75,11 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
     return t;
 }
+__device__ __forceinline__ void stamp(unsigned long long *stamps, int slot, bool all_ctas) {
+    if (stamps == nullptr || threadIdx.x != 0) { return; }
+    if (all_ctas) { atomicMax(stamps + slot, (unsigned long long)global_timer_ns()); }
+    else if (blockIdx.x == 0 && blockIdx.y == 0) { stamps[slot] = global_timer_ns(); }
+}
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) { return true; }
     const uint64_t t0 = global_timer_ns();

@@ -65,6 +65,8 @@ struct MatvecParams {
     // optional tap: reference-layout Q8_0 blocks of column 0 (nb * 34 bytes)
     uint8_t      *tap_xq = nullptr;
     int          *error_flag = nullptr; // set non-zero when a bounded wait on a bulk copy ran out
+    // optional profiling aid: four %globaltimer stamps (entry of CTA 0, predecessor finished, prologue done, last CTA done)
+    unsigned long long *stamps = nullptr;
     // weights a later kernel of the step will stream: pulled into L2 once this CTA's own loads are issued
     const void   *pf_ptr[4] = {nullptr, nullptr, nullptr, nullptr};
     size_t        pf_bytes[4] = {0, 0, 0, 0};
@@ -79,6 +81,7 @@ struct AttnParams {
     const float  *exp_table = nullptr;
     int   n_head = 0, hd = 128, dl = 0, T = 1, n_ctx = 0;
     float scale = 0.f;
+    unsigned long long *stamps = nullptr;                           // as in MatvecParams
     const void *pf_ptr[4] = {nullptr, nullptr, nullptr, nullptr};   // as in MatvecParams
     size_t      pf_bytes[4] = {0, 0, 0, 0};
 };
@@ -89,6 +92,7 @@ struct LaunchCfg {
     int          num_sms = 148;
     int          mv_ctas_per_sm = 2;   // mat-vec CTAs per SM for single-column launches (their register budget allows 2)
     int          mv_ring_kb = 80;      // shared-memory ring per CTA that bulk copies stream the weights through
+    int          mv_force_s = 0, mv_force_wact = 0;   // tuning overrides (0 = choose)
     int         *error_flag = nullptr;
 };
 

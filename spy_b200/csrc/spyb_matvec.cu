@@ -73,6 +73,85 @@ size_t matvec_smem_bytes(int nb, int T) { return matvec_smem_layout(padded_block
 //   product of each pair plain, the second fused into an FMA, as the CPU build evaluates it) and added to
 //   the running sum one group after the other; y = x * (1 / sqrt(sum/n + eps)). The groups are formed in
 //   parallel, the running sum is one thread's chain. Mul (basic.cpp:15-50): y * norm_weight.
+// Single column, K <= 12288: every thread keeps its (at most PG) float4 groups of x in registers from the one
+// global read through the sum of squares to the quantizer; same arithmetic as the general prologue below.
+constexpr int PRO_GROUPS = 6;
+template <int PG, bool NORM>
+__device__ __forceinline__ void matvec_prologue_1col(const MatvecParams &p, ActPlanes act, float *v3, float *scales) {
+    const int tid = threadIdx.x;
+    const int nbp = p.A.nbp;
+    const int n4  = (int)(p.A.k >> 2);
+    const int n4p = nbp * 8;                                   // float4 groups including the zero padding up to nbp blocks
+    const int npass = (n4p + MV_THREADS - 1) / MV_THREADS;     // <= PG
+    const float4 *x4 = reinterpret_cast<const float4 *>(p.x);
+    float4 xv[PG];
+#pragma unroll
+    for (int k = 0; k < PG; ++k) {
+        const int g = tid + k * MV_THREADS;
+        xv[k] = (k < npass && g < n4) ? x4[g] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (NORM) {
+        const float4 *w4 = reinterpret_cast<const float4 *>(p.norm_w);
+#pragma unroll
+        for (int k = 0; k < PG; ++k) {
+            const int g = tid + k * MV_THREADS;
+            if (k < npass && g < n4) {
+                const float4 v = xv[k];
+                const float v1 = fmaf(v.y, v.y, __fmul_rn(v.x, v.x));
+                const float v2 = fmaf(v.w, v.w, __fmul_rn(v.z, v.z));
+                v3[g] = __fadd_rn(v1, v2);
+            }
+        }
+        __syncthreads();
+        if (tid == 0) {
+            const float4 *g4 = reinterpret_cast<const float4 *>(v3);
+            float sum = 0.f;
+            int g = 0;
+            for (; g + 16 <= n4; g += 16) {   // four 128-bit reads ahead of their 16 dependent adds
+                const float4 q0 = g4[(g >> 2)], q1 = g4[(g >> 2) + 1], q2 = g4[(g >> 2) + 2], q3 = g4[(g >> 2) + 3];
+                sum = __fadd_rn(sum, q0.x); sum = __fadd_rn(sum, q0.y); sum = __fadd_rn(sum, q0.z); sum = __fadd_rn(sum, q0.w);
+                sum = __fadd_rn(sum, q1.x); sum = __fadd_rn(sum, q1.y); sum = __fadd_rn(sum, q1.z); sum = __fadd_rn(sum, q1.w);
+                sum = __fadd_rn(sum, q2.x); sum = __fadd_rn(sum, q2.y); sum = __fadd_rn(sum, q2.z); sum = __fadd_rn(sum, q2.w);
+                sum = __fadd_rn(sum, q3.x); sum = __fadd_rn(sum, q3.y); sum = __fadd_rn(sum, q3.z); sum = __fadd_rn(sum, q3.w);
+            }
+            for (; g < n4; ++g) { sum = __fadd_rn(sum, v3[g]); }
+            const float mean = __fdiv_rn(sum, (float)p.A.k);
+            scales[0] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
+        }
+        // the norm weights arrive while thread 0 runs its chain
+        float4 wv[PG];
+#pragma unroll
+        for (int k = 0; k < PG; ++k) {
+            const int g = tid + k * MV_THREADS;
+            wv[k] = (k < npass && g < n4) ? w4[g] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        __syncthreads();   // also: the partials (aliasing Y) are dead from here on
+        const float scale = scales[0];
+#pragma unroll
+        for (int k = 0; k < PG; ++k) {
+            xv[k].x = __fmul_rn(__fmul_rn(xv[k].x, scale), wv[k].x);
+            xv[k].y = __fmul_rn(__fmul_rn(xv[k].y, scale), wv[k].y);
+            xv[k].z = __fmul_rn(__fmul_rn(xv[k].z, scale), wv[k].z);
+            xv[k].w = __fmul_rn(__fmul_rn(xv[k].w, scale), wv[k].w);
+        }
+    }
+    uint32_t *Yw = reinterpret_cast<uint32_t *>(act.Y);
+    float    *DS = reinterpret_cast<float *>(act.DS);
+#pragma unroll
+    for (int k = 0; k < PG; ++k) {
+        if (k < npass) {   // uniform over the CTA: the quantizer's shuffles see full warps
+            const int g = tid + k * MV_THREADS;
+            uint16_t dh; int sum;
+            const uint32_t q = quantize_q8_lane4(xv[k], dh, sum);
+            if (g < n4p) {
+                const int b = g >> 3, w = g & 7;
+                Yw[(((b >> 2)) * 8 + w) * 4 + (b & 3)] = q;
+                if (w == 0) { const float d = h2f(dh); DS[b] = (p.A.type == 2) ? __fmul_rn(d, 0.0625f) : d; }
+            }
+        }
+    }
+}
+
 template <int TM>
 __device__ __forceinline__ void matvec_prologue(const MatvecParams &p, ActPlanes act, float *v3, float *scales) {
     const int     tid = threadIdx.x;
@@ -193,7 +272,7 @@ __device__ __forceinline__ void matvec_epilogue_silu(const MatvecParams &p, int6
 
 // ---------------------------------------------------------------------------------------------
 template <int WT, int TM, int R>
-__global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(const MatvecParams p, const int ring_bytes, const int S) {
+__global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(const MatvecParams p, const int ring_bytes, const int S, const int wact) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ float norm_scales[8];
     constexpr int ROWB = ((WT == 8) ? 256 : 128) + 16;   // one row's share of a record: quants of 8 blocks + 8 scales
@@ -206,14 +285,15 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
     const int ng   = nbp >> 2;
     const int nrec = nbp >> 3;
 
-    // units of this CTA (a contiguous range) and of this warp (every MV_WARPS-th of them); a unit is R tiles:
+    // units of this CTA (a contiguous range) and of this warp (every wact-th of them; warps >= wact only help with
+    // the prologue: fewer, longer streams per CTA leave each one a deeper ring and larger copies); a unit is R tiles:
     // tiles R*u .. R*u + R-1 of A, or (pair mode, R == 2) tile u of A and tile u of B
     const int64_t n_units  = p.pair_mode ? (p.A.n_rows >> 2) : (p.A.n_rows / (4 * R));
     const int64_t unit_lo  = n_units * blockIdx.x / gridDim.x;
     const int64_t unit_hi  = n_units * (blockIdx.x + 1) / gridDim.x;
     const int64_t my_first = unit_lo + warp;
-    const int     my_units = (my_first < unit_hi) ? (int)((unit_hi - my_first + MV_WARPS - 1) / MV_WARPS) : 0;
-    const int     n_act    = (int)min((int64_t)MV_WARPS, unit_hi - unit_lo);   // warps of this CTA that have work
+    const int     my_units = (warp < wact && my_first < unit_hi) ? (int)((unit_hi - my_first + wact - 1) / wact) : 0;
+    const int     n_act    = (int)min((int64_t)wact, unit_hi - unit_lo);   // warps of this CTA that have work
     const int     nch      = (nrec + S - 1) / S;                               // stages per unit
     const int     n_items  = my_units * nch;
     const int     stage_bytes = R * S * RECB;
@@ -244,12 +324,13 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
         ++issued;
         if (++lslot == NS) { lslot = 0; }
         lrec += S;
-        if (lrec >= nrec) { lrec = 0; lu += MV_WARPS; unit_sources(lu); }
+        if (lrec >= nrec) { lrec = 0; lu += wact; unit_sources(lu); }
     };
 
     // Let the next kernel of the step begin, and start streaming: weights never change during a step, so the
     // copies may run ahead of the previous kernel's results.
     pdl_launch_dependents();
+    stamp(p.stamps, 0, false);
     if (lane == 0 && n_items > 0) {
         for (int s = 0; s < NS; ++s) { mbar_init(bar_s + s * 8, 1); }
         mbar_init_fence();
@@ -258,10 +339,23 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
     }
     __syncwarp();
     pdl_wait();
+    stamp(p.stamps, 1, false);
 
     ActPlanes act = act_planes(smem_raw, nbp, TM);
-    matvec_prologue<TM>(p, act, reinterpret_cast<float *>(smem_raw), norm_scales);
+    {
+        float *v3 = reinterpret_cast<float *>(smem_raw);
+        const int  n4p  = nbp * 8;
+        const bool norm = p.pro == PRO_NORM_QUANT;
+        if (TM == 1 && n4p <= 2 * MV_THREADS) {
+            if (norm) { matvec_prologue_1col<2, true>(p, act, v3, norm_scales); } else { matvec_prologue_1col<2, false>(p, act, v3, norm_scales); }
+        } else if (TM == 1 && n4p <= PRO_GROUPS * MV_THREADS) {
+            if (norm) { matvec_prologue_1col<PRO_GROUPS, true>(p, act, v3, norm_scales); } else { matvec_prologue_1col<PRO_GROUPS, false>(p, act, v3, norm_scales); }
+        } else {
+            matvec_prologue<TM>(p, act, v3, norm_scales);
+        }
+    }
     __syncthreads();
+    stamp(p.stamps, 2, false);
     matvec_tap(p, act);
 
     // this lane's operands: activation word (Q8_0 weights: word l; Q4_0: lanes 0..3 hold the high nibbles, which meet
@@ -352,7 +446,7 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
                     }
                 }
             }
-            crec = 0; cu += MV_WARPS;
+            crec = 0; cu += wact;
         }
     }
     if (!ok) {
@@ -365,6 +459,7 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
         }
     }
 
+    if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
     // weights a later kernel will stream: towards L2 while this kernel drains
     {
         const int64_t gw = (int64_t)blockIdx.x * MV_THREADS + threadIdx.x, gn = (int64_t)gridDim.x * MV_THREADS;
@@ -391,16 +486,32 @@ static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) 
     int64_t grid = (int64_t)cfg.num_sms * per_sm;
     if (grid > n_units) { grid = n_units; }
     if (grid < 1) { grid = 1; }
-    const int n_act = (int)std::min<int64_t>(MV_WARPS, (n_units + grid - 1) / grid);
+    const int64_t units_per_cta = (n_units + grid - 1) / grid;
 
     // ring: what the SM's shared memory leaves after the activation planes (two CTAs per SM for single columns)
     const MatvecSmem fixed = matvec_smem_layout(p.A.nbp, TM, 0);
     const size_t budget = (per_sm == 2) ? 112 * 1024 : 224 * 1024;
-    if (fixed.total + (size_t)2 * n_act * R * RECB > budget) { return cudaErrorInvalidValue; }   // rows too long for this kernel
+    if (fixed.total + (size_t)2 * R * RECB > budget) { return cudaErrorInvalidValue; }   // rows too long for this kernel
     size_t ring = std::min<size_t>((size_t)cfg.mv_ring_kb * 1024 * ((TM == 1) ? 1 : 2), budget - fixed.total) / 128 * 128;
+    // S records per stage (one bulk copy per tile and stage) and the number of warps that stream: copies of a few KB
+    // and at least three stages per stream; when the ring is too small for that with every warp streaming, fewer
+    // warps take more units each
     const int nrec = p.A.nbp >> 3;
-    int S = 8;   // records per stage: as large as still leaves three stages per warp in the ring
-    while (S > 1 && (S > nrec || ring / ((size_t)n_act * R * S * RECB) < 3)) { S >>= 1; }
+    int wact = (int)std::min<int64_t>(MV_WARPS, units_per_cta);
+    int S = 8;
+    while (S > nrec) { S >>= 1; }
+    if (S < 1) { S = 1; }
+    const int s_small = std::max(1, std::min(S, 4096 / RECB));   // do not go below ~4 KB copies while warps can still be merged
+    while (ring / ((size_t)wact * R * S * RECB) < 3) {
+        if (S > s_small) { S >>= 1; }
+        else if (wact > 4) { wact = (wact + 1) / 2; }
+        else if (S > 1) { S >>= 1; }
+        else if (wact > 1) { wact = (wact + 1) / 2; }
+        else { break; }
+    }
+    if (cfg.mv_force_s > 0) { S = std::min(cfg.mv_force_s, std::max(nrec, 1)); }
+    if (cfg.mv_force_wact > 0) { wact = std::min(cfg.mv_force_wact, MV_WARPS); }
+    if (ring / ((size_t)wact * R * S * RECB) < 1) { return cudaErrorInvalidValue; }
     const size_t smem = fixed.total + ring;
 
     static size_t smem_allowed = 48 * 1024;   // one process drives one device, so one high-water mark per kernel suffices
@@ -418,7 +529,7 @@ static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&lc, matvec_kernel<WT, TM, R>, q, (int)ring, S);
+    return cudaLaunchKernelEx(&lc, matvec_kernel<WT, TM, R>, q, (int)ring, S, wact);
 }
 
 template <int WT, int R>

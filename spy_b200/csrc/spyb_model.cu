@@ -163,6 +163,7 @@ struct spyb_model {
     int    *d_pos = nullptr;
     int32_t *d_token = nullptr, *d_tokens_in = nullptr, *d_history = nullptr;
     uint8_t *d_tap = nullptr;
+    unsigned long long *d_stamps = nullptr;   // profiling aid (SPYB_TIMELINE=1): four time stamps per kernel of a step
     int    *h_pos_pinned = nullptr; int32_t *h_tok_pinned = nullptr; float *h_logits_pinned = nullptr;
     void   *nccl_comm = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
@@ -213,13 +214,14 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
     const int d = m->info.d_model, tp = m->info.tp_size;
     for (size_t L = 0; L < m->layers.size(); ++L) {
         Layer &ly = m->layers[L];
+        auto stamps = [&](int k) { return m->d_stamps ? m->d_stamps + 4 * (5 * L + k) : nullptr; };
         {   // 1: norm + quantize -> QKV -> rope + KV append
             MatvecParams p;
             p.A = ly.wqkv; p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.attn_norm; p.eps = m->info.rms_eps;
             p.epi = EPI_QKV_ROPE; p.pos_base = m->d_pos; p.rope_table = m->rope_table; p.hd = m->info.head_dim; p.dl = m->dl;
             p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache; p.n_ctx = m->info.n_ctx;
             p.tap_xq = (tap && L == 0) ? m->d_tap : nullptr;
-            prefetch_next(m, p, &ly.wo);
+            prefetch_next(m, p, &ly.wo); p.stamps = stamps(0);
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
         }
         {   // 2: attention
@@ -227,7 +229,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             a.q = m->q; a.k_cache = ly.k_cache; a.v_cache = ly.v_cache; a.out = m->att; a.pos_base = m->d_pos; a.exp_table = be->d_exp_table;
             a.n_head = m->dl / m->info.head_dim; a.hd = m->info.head_dim; a.dl = m->dl; a.T = T; a.n_ctx = m->info.n_ctx;
             a.scale = 1.0f / std::sqrt((float)m->info.head_dim);
-            prefetch_next(m, a, &ly.up, &ly.gate);
+            prefetch_next(m, a, &ly.up, &ly.gate); a.stamps = stamps(1);
             SPYB_CUDA(be, launch_attention(a, cfg)); ++*launches;
         }
         {   // 3: quantize -> Wo -> + residual (tensor parallel: partial sums, rank 0 carries the residual)
@@ -236,7 +238,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             p.resid = m->x; p.out_stride = d;
             if (tp == 1) { p.epi = EPI_RESID; p.out = m->x; }
             else { p.epi = (m->info.tp_rank == 0) ? EPI_RESID : EPI_STORE; p.out = m->partial; }
-            prefetch_next(m, p, &ly.down);
+            prefetch_next(m, p, &ly.down); p.stamps = stamps(2);
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
             if (tp > 1) {
                 if (allreduce(m, m->partial, (size_t)T * d, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
@@ -247,13 +249,13 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             MatvecParams p;
             p.A = ly.up; p.B = ly.gate; p.pair_mode = 1; p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
             p.eps = m->info.rms_eps; p.epi = EPI_SILU_MUL; p.out = m->act; p.out_stride = m->fl; p.silu_table = be->d_silu_table;
-            prefetch_next(m, p, L + 1 < m->layers.size() ? &m->layers[L + 1].wqkv : &m->head);
+            prefetch_next(m, p, L + 1 < m->layers.size() ? &m->layers[L + 1].wqkv : &m->head); p.stamps = stamps(3);
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
         }
         {   // 5: quantize -> Wdown -> + residual
             MatvecParams p;
             p.A = ly.down; p.T = T; p.pro = PRO_QUANT; p.x = m->act; p.x_stride = m->fl;
-            p.resid = m->x; p.out_stride = d;
+            p.resid = m->x; p.out_stride = d; p.stamps = stamps(4);
             if (tp == 1) { p.epi = EPI_RESID; p.out = m->x; }
             else { p.epi = (m->info.tp_rank == 0) ? EPI_RESID : EPI_STORE; p.out = m->partial; }
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
@@ -271,6 +273,7 @@ spyb_status run_head(spyb_model *m, int col, int64_t *launches) {
     MatvecParams p;
     p.A = m->head; p.T = 1; p.pro = PRO_NORM_QUANT; p.x = m->x + (int64_t)col * m->info.d_model; p.x_stride = m->info.d_model;
     p.norm_w = m->output_norm; p.eps = m->info.rms_eps; p.epi = EPI_STORE; p.out = m->logits; p.out_stride = m->info.n_vocab;
+    p.stamps = m->d_stamps ? m->d_stamps + 4 * (5 * m->layers.size()) : nullptr;
     SPYB_CUDA(m->be, launch_matvec(p, m->be->launch_cfg(m->be->config.use_pdl != 0))); ++*launches;
     return SPYB_SUCCESS;
 }
@@ -414,7 +417,8 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
               dev_alloc(m, &m->logits, (size_t)I.n_vocab) == SPYB_SUCCESS && dev_alloc(m, &m->q, (size_t)TMAX * dl) == SPYB_SUCCESS &&
               dev_alloc(m, &m->d_pos, 4) == SPYB_SUCCESS && dev_alloc(m, &m->d_token, 4) == SPYB_SUCCESS &&
               dev_alloc(m, &m->d_tokens_in, TMAX) == SPYB_SUCCESS && dev_alloc(m, &m->d_history, (size_t)I.n_ctx + 8) == SPYB_SUCCESS &&
-              dev_alloc(m, &m->d_tap, (size_t)d / 32 * 34) == SPYB_SUCCESS;
+              dev_alloc(m, &m->d_tap, (size_t)d / 32 * 34) == SPYB_SUCCESS &&
+              (std::getenv("SPYB_TIMELINE") == nullptr || dev_alloc(m, &m->d_stamps, (size_t)(5 * I.n_layer + 1) * 4) == SPYB_SUCCESS);
     if (!ok) { return fail(SPYB_FAIL); }
     if (cudaMallocHost(reinterpret_cast<void **>(&m->h_pos_pinned), 64) != cudaSuccess ||
         cudaMallocHost(reinterpret_cast<void **>(&m->h_tok_pinned), 64) != cudaSuccess ||
@@ -620,6 +624,13 @@ spyb_status spyb_model_read_activation(spyb_model *m, int32_t which, void *host,
     SPYB_CUDA(m->be, cudaStreamSynchronize(m->be->stream));
     SPYB_CUDA(m->be, cudaMemcpy(host, src, bytes, cudaMemcpyDeviceToHost));
     return SPYB_SUCCESS;
+}
+
+int32_t spyb_model_read_timeline(spyb_model *m, uint64_t *stamps_host, int32_t max_kernels) {
+    if (m == nullptr || m->d_stamps == nullptr || stamps_host == nullptr) { return 0; }
+    const int n = std::min<int>(max_kernels, 5 * (int)m->layers.size() + 1);
+    if (cudaMemcpy(stamps_host, m->d_stamps, (size_t)n * 4 * sizeof(uint64_t), cudaMemcpyDeviceToHost) != cudaSuccess) { return 0; }
+    return n;
 }
 
 spyb_status spyb_model_tap_xq(spyb_model *m, void *blocks_host) {

@@ -61,6 +61,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     pdl_launch_dependents();
+    stamp(p.stamps, 0, false);
     {   // weights of a later kernel of the step: towards L2 while attention occupies only a few SMs
         const int64_t gw = ((int64_t)blockIdx.y * gridDim.x + blockIdx.x) * ATT_THREADS + tid, gn = (int64_t)gridDim.x * gridDim.y * ATT_THREADS;
 #pragma unroll
@@ -70,6 +71,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
         }
     }
     pdl_wait();
+    stamp(p.stamps, 1, false);
 
     const int pos   = p.pos_base[0] + t;
     const int n_vis = pos + 1;                   // causal mask: positions 0..pos are visible
@@ -91,7 +93,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
         const uint4  *krow = reinterpret_cast<const uint4 *>(p.k_cache + (int64_t)j * p.dl + (int64_t)h * ATT_HD);
         const float4 *q4   = reinterpret_cast<const float4 *>(qf);
         float acc[4][8];
-        uint4 kv[4];
+        uint4 kv[16];                                // the whole K row in flight at once: one memory round trip
+#pragma unroll
+        for (int a = 0; a < 16; ++a) { kv[a] = krow[a]; }
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
 #pragma unroll
@@ -100,10 +104,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
 #pragma unroll
         for (int step = 0; step < 3; ++step) {       // elements 0..95: accumulator a takes elements 32 * step + 8a .. + 7
 #pragma unroll
-            for (int a = 0; a < 4; ++a) { kv[a] = krow[4 * step + a]; }
-#pragma unroll
             for (int a = 0; a < 4; ++a) {
-                float kf[8]; unpack8(kv[a], kf);
+                float kf[8]; unpack8(kv[4 * step + a], kf);
                 const float4 qa = q4[(4 * step + a) * 2], qb = q4[(4 * step + a) * 2 + 1];
                 const float  qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
@@ -120,10 +122,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
         const float simd = __fadd_rn(__fadd_rn(u[0], u[1]), __fadd_rn(u[2], u[3]));
         float tail = 0.f;                             // elements 96..127: scalar chain
 #pragma unroll
-        for (int a = 0; a < 4; ++a) { kv[a] = krow[12 + a]; }
-#pragma unroll
         for (int a = 0; a < 4; ++a) {
-            float kf[8]; unpack8(kv[a], kf);
+            float kf[8]; unpack8(kv[12 + a], kf);
             const float4 qa = q4[(12 + a) * 2], qb = q4[(12 + a) * 2 + 1];
             const float  qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
 #pragma unroll
@@ -212,10 +212,31 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
             u[k] = __fadd_rn(mine, __shfl_xor_sync(0xffffffffu, mine, 1));   // element k of one half with element k + 4 of the other
         }
         const float simd = __fadd_rn(__fadd_rn(u[0], u[1]), __fadd_rn(u[2], u[3]));
+        // scalar tail: positions n_main .. n_tot-1 (at most 32), fetched with eight 64-bit loads before the chain runs
         float tail = 0.f;
-        for (int j = n_main; j < n_vis; ++j) { tail = fmaf(__half2float(vrow[j]), sc[j], tail); }
+        {
+            uint2 tv[8];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int j = n_main + 4 * c;
+                tv[c] = (j < n_vis) ? *reinterpret_cast<const uint2 *>(vrow + j) : make_uint2(0u, 0u);
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                const int j = n_main + 4 * c;
+                if (j < n_vis) {
+                    const float4 pr = *reinterpret_cast<const float4 *>(sc + j);
+                    const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&tv[c].x)), v23 = __half22float2(*reinterpret_cast<const __half2 *>(&tv[c].y));
+                    tail = fmaf(v01.x, pr.x, tail);
+                    if (j + 1 < n_vis) { tail = fmaf(v01.y, pr.y, tail); }
+                    if (j + 2 < n_vis) { tail = fmaf(v23.x, pr.z, tail); }
+                    if (j + 3 < n_vis) { tail = fmaf(v23.y, pr.w, tail); }
+                }
+            }
+        }
         if (half == 0) { p.out[(int64_t)t * p.dl + (int64_t)h * ATT_HD + e] = __fadd_rn(tail, simd); }
     }
+    if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
 }
 
 cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
