@@ -69,11 +69,11 @@ size_t Arena::available() {
 }
 
 // ------------------------------------------------------------------------------------------ matrices
-spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, DevMatrix *out) {
+spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, DevMatrix *out, int tile_rows) {
     if (type != SPYB_Q4_0 && type != SPYB_Q8_0) { be->set_error("weight type %d has no device layout", type); return SPYB_UNSUPPORTED; }
-    if (n_rows & 3) { be->set_error("quantized matrices need a multiple of 4 rows (got %lld)", (long long)n_rows); return SPYB_UNSUPPORTED; }
+    if ((tile_rows != 4 && tile_rows != 32) || n_rows % tile_rows != 0) { be->set_error("quantized matrices need a multiple of %d rows (got %lld)", tile_rows, (long long)n_rows); return SPYB_UNSUPPORTED; }
     DevMatrix m;
-    m.type = type; m.n_rows = n_rows; m.nb = nb; m.nbp = padded_blocks(nb); m.k = (int64_t)nb * QK;
+    m.type = type; m.n_rows = n_rows; m.nb = nb; m.nbp = padded_blocks(nb); m.k = (int64_t)nb * QK; m.tile_rows = tile_rows;
     void *w = nullptr;
     SPYB_CUDA(be, cudaMalloc(&w, matrix_bytes(type, n_rows, nb) + 16));
     be->owned.push_back(w);
@@ -83,18 +83,19 @@ spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, Dev
 }
 
 spyb_status upload_matrix(spyb_backend *be, int type, const uint8_t *host_rows, int64_t n_rows, int64_t row_stride_bytes,
-                          int64_t blk0, int nb, DevMatrix *out, const DevMatrix *into, int64_t dst_row) {
+                          int64_t blk0, int nb, DevMatrix *out, const DevMatrix *into, int64_t dst_row, int sub_rows, int sub_off) {
     if (into == nullptr) {
-        spyb_status st = alloc_matrix(be, type, n_rows, nb, out);
+        spyb_status st = alloc_matrix(be, type, n_rows, nb, out, 4);
         if (st != SPYB_SUCCESS) { return st; }
-        into = out; dst_row = 0;
-    } else if (into->type != type || into->nb != nb || dst_row + n_rows > into->n_rows || ((dst_row | n_rows) & 3)) {
-        be->set_error("weight upload: destination rows do not match"); return SPYB_FAIL;
+        into = out; dst_row = 0; sub_rows = 0; sub_off = 0;
+    } else {
+        const int64_t last = sub_rows > 0 ? dst_row + (n_rows / sub_rows) * into->tile_rows : dst_row + n_rows;
+        if (into->type != type || into->nb != nb || last > into->n_rows || (sub_rows > 0 && (n_rows % sub_rows != 0 || sub_off + sub_rows > into->tile_rows))) {
+            be->set_error("weight upload: destination rows do not match"); return SPYB_FAIL;
+        }
     }
-    const size_t tile_bytes = (size_t)(into->nbp >> 3) * record_bytes(type);
-    uint8_t *dst = const_cast<uint8_t *>(into->w) + (size_t)(dst_row >> 2) * tile_bytes;
     const int     bb = (type == SPYB_Q4_0) ? 18 : 34;
-    const int64_t max_rows = std::max<int64_t>(4, ((int64_t)(64u << 20) / row_stride_bytes) & ~(int64_t)3);   // 64 MiB staging pieces, whole tiles
+    const int64_t max_rows = std::max<int64_t>(1, (int64_t)(64u << 20) / row_stride_bytes);   // 64 MiB staging pieces
     void *stage = nullptr;
     SPYB_CUDA(be, cudaMalloc(&stage, (size_t)std::min(max_rows, n_rows) * row_stride_bytes + 64));
     for (int64_t r0 = 0; r0 < n_rows; r0 += max_rows) {
@@ -102,7 +103,7 @@ spyb_status upload_matrix(spyb_backend *be, int type, const uint8_t *host_rows, 
         cudaError_t err = cudaMemcpyAsync(stage, host_rows + r0 * row_stride_bytes, (size_t)nr * row_stride_bytes, cudaMemcpyHostToDevice, be->stream);
         if (err == cudaSuccess) {
             const uint8_t *raw = static_cast<const uint8_t *>(stage) + blk0 * bb;
-            err = launch_retile(type, raw, row_stride_bytes, nr, nb, dst + (size_t)(r0 >> 2) * tile_bytes, be->stream);
+            err = launch_retile(type, raw, row_stride_bytes, nr, nb, const_cast<uint8_t *>(into->w), into->tile_rows, dst_row, r0, sub_rows, sub_off, be->stream);
         }
         if (err == cudaSuccess) { err = cudaStreamSynchronize(be->stream); }
         if (err != cudaSuccess) { cudaFree(stage); be->set_error("weight upload failed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
@@ -276,8 +277,8 @@ void *spyb_upload_constant(spyb_backend *be, const char *name, const void *host_
         const int64_t bb = number_type == SPYB_Q4_0 ? 18 : 34;
         if (k % QK == 0 && rows > 0 && (rows & 3) == 0) {
             DevMatrix m;
-            if (alloc_matrix(be, number_type, rows, (int)(k / QK), &m) != SPYB_SUCCESS) { return nullptr; }
-            cudaError_t err = launch_retile(number_type, static_cast<const uint8_t *>(raw), k / QK * bb, rows, m.nb, const_cast<uint8_t *>(m.w), be->stream);
+            if (alloc_matrix(be, number_type, rows, (int)(k / QK), &m, 4) != SPYB_SUCCESS) { return nullptr; }
+            cudaError_t err = launch_retile(number_type, static_cast<const uint8_t *>(raw), k / QK * bb, rows, m.nb, const_cast<uint8_t *>(m.w), 4, 0, 0, 0, 0, be->stream);
             if (err != cudaSuccess || cudaStreamSynchronize(be->stream) != cudaSuccess) { be->set_error("re-tiling of %s failed", name); return nullptr; }
             be->retiled[raw] = m;
         }
@@ -409,7 +410,7 @@ spyb_status run_matmul(spyb_backend *be, spyb_op_desc *d, void *out_dev) {
         if (!tmp_w) { be->set_error("MatMul: out of device memory for re-tiled weights"); return SPYB_FAIL; }
         m.w = static_cast<const uint8_t *>(tmp_w);
         cudaError_t err = launch_retile(w.number_type, static_cast<const uint8_t *>(w.data), w.elements[0] / QK * bb, w.elements[1], m.nb,
-                                        static_cast<uint8_t *>(tmp_w), be->stream);
+                                        static_cast<uint8_t *>(tmp_w), 4, 0, 0, 0, 0, be->stream);
         if (err != cudaSuccess) { be->set_error("MatMul: re-tiling failed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
     }
     struct TmpRelease {   // stream-ordered reuse: safe to hand back as soon as the kernels are enqueued

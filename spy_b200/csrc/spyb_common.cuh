@@ -53,6 +53,17 @@ __device__ __forceinline__ void l2_prefetch_piece(const void *ptr, size_t bytes,
 // bulk asynchronous copies global -> shared memory, completion counted on an mbarrier (no tensor map: plain
 // contiguous runs; both addresses and the size are multiples of 16 bytes)
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+// loads through 32-bit shared-space addresses (no generic-pointer arithmetic in the inner loops)
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+    return v;
+}
 __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {   // `bar`: shared-space address of the 8-byte barrier
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
 }
@@ -80,11 +91,19 @@ __device__ __forceinline__ void stamp(unsigned long long *stamps, int slot, bool
     if (all_ctas) { atomicMax(stamps + slot, (unsigned long long)global_timer_ns()); }
     else if (blockIdx.x == 0 && blockIdx.y == 0) { stamps[slot] = global_timer_ns(); }
 }
+// the same with a suspend-time hint: the thread may sleep up to `hint_ns` inside the instruction instead of
+// spinning through the issue slots other warps need
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity), "r"(hint_ns) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
     if (mbar_try_wait(bar, parity)) { return true; }
     const uint64_t t0 = global_timer_ns();
     for (;;) {
-        if (mbar_try_wait(bar, parity)) { return true; }
+        if (mbar_try_wait_sleep(bar, parity, 2000u)) { return true; }
         if (global_timer_ns() - t0 > limit_ns) { return false; }
     }
 }

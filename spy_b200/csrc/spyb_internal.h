@@ -114,9 +114,11 @@ namespace spyb {
 
 // upload raw reference-layout rows [n_rows][row_stride_bytes] (host) and re-tile the block range
 // [blk0, blk0 + nb) of every row into freshly allocated planes; used for row shards (contiguous rows)
-// and K shards (a block sub-range of each row) alike. With `into`, the rows land at row dst_row of an existing matrix.
+// and K shards (a block sub-range of each row) alike. With `into`, the rows land at row dst_row of an existing matrix,
+// or (sub_rows > 0) interleaved tile by tile: source row i at dst_row + (i / sub_rows) * tile_rows + sub_off + i % sub_rows.
 spyb_status upload_matrix(spyb_backend *be, int type, const uint8_t *host_rows, int64_t n_rows, int64_t row_stride_bytes,
-                          int64_t blk0, int nb, DevMatrix *out, const DevMatrix *into = nullptr, int64_t dst_row = 0);
-spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, DevMatrix *out);
+                          int64_t blk0, int nb, DevMatrix *out, const DevMatrix *into = nullptr, int64_t dst_row = 0,
+                          int sub_rows = 0, int sub_off = 0);
+spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, DevMatrix *out, int tile_rows = 4);
 
 }  // namespace spyb

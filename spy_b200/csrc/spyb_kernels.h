@@ -8,9 +8,9 @@
 namespace spyb {
 
 // A quantized weight matrix resident in HBM, re-tiled at upload into the stream a warp consumes:
-//   tile   = 4 consecutive rows; a tile's data is one contiguous run, so a warp walks sequential addresses
-//   record = 8 consecutive blocks ("mini-chunk") of the 4 rows of a tile:
-//              [row 0..3][ q: 2 groups x WORDS x 16 B | d: 8 fp16 scales ]      (WORDS = 4 for Q4_0, 8 for Q8_0)
+//   tile   = 4 (or 32) consecutive rows; a tile's data is one contiguous run, so a warp walks sequential addresses
+//   record = 8 consecutive blocks of the rows of a tile:
+//              [row 0..tile_rows-1][ q: 2 groups x WORDS x 16 B | d: 8 fp16 scales ]      (WORDS = 4 for Q4_0, 8 for Q8_0)
 //            inside a group of four blocks the quants are word-transposed: 128-bit word j holds 32-bit word j of
 //            each of the four blocks, so the lane that owns accumulator l of the CPU's 8-wide dot product finds
 //            its own four bytes of four blocks in one aligned 128-bit word
@@ -25,13 +25,14 @@ struct DevMatrix {
     int64_t        k = 0;
     int            nb = 0;       // blocks per row
     int            nbp = 0;      // blocks per row in memory (nb rounded up to a multiple of 8)
-    const uint8_t *w = nullptr;  // [n_rows / 4][nbp / 8] records
+    int            tile_rows = 4;   // rows per tile: 4 (lane-per-accumulator kernel) or 32 (lane-per-row kernel)
+    int            fused_pair = 0;  // tile_rows == 32 only: rows 0..15 of a tile are FFN-up rows, rows 16..31 the matching FFN-gate rows
+    const uint8_t *w = nullptr;  // [n_rows / tile_rows][nbp / 8] records of tile_rows rows
     size_t bytes() const { return (size_t)n_rows * nb * ((type == 8 ? 32 : 16) + 2); }   // algorithmic bytes (without padding)
 };
 inline int    padded_blocks(int nb) { return (nb + 7) & ~7; }
 inline int    record_row_bytes(int type) { return (type == 8 ? 256 : 128) + 16; }
-inline int    record_bytes(int type) { return 4 * record_row_bytes(type); }            // 576 (Q4_0) or 1088 (Q8_0)
-inline size_t matrix_bytes(int type, int64_t n_rows, int nb) { return (size_t)(n_rows / 4) * (padded_blocks(nb) / 8) * record_bytes(type); }
+inline size_t matrix_bytes(int type, int64_t n_rows, int nb) { return (size_t)n_rows * (padded_blocks(nb) / 8) * record_row_bytes(type); }
 
 enum Prologue { PRO_QUANT = 0, PRO_NORM_QUANT = 1 };
 enum Epilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_SILU_MUL = 2, EPI_QKV_ROPE = 3 };
@@ -102,8 +103,11 @@ cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg);
 cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg);
 
 // upload-time re-tiling of raw reference-layout blocks into DevMatrix planes
-// (dst points at the first destination tile; n_rows is a multiple of 4; nb blocks are read per row, the padding is zero-filled)
-cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride_bytes, int64_t n_rows, int nb, uint8_t *dst, cudaStream_t s);
+// Source row i (i = src_row0 .. src_row0 + n_rows - 1 of the tensor being uploaded; `raw` points at row src_row0) lands
+// at matrix row dst_row0 + i, or, with sub_rows > 0, at dst_row0 + (i / sub_rows) * tile_rows + sub_off + i % sub_rows
+// (interleaving two tensors tile by tile). nb blocks are read per row, the padding up to a multiple of 8 is zero-filled.
+cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride_bytes, int64_t n_rows, int nb, uint8_t *matrix_base, int tile_rows,
+                          int64_t dst_row0, int64_t src_row0, int sub_rows, int sub_off, cudaStream_t s);
 
 // stand-alone arithmetic kernels (parity checks and the per-operator path)
 cudaError_t launch_quantize_q8_0_ref_layout(const float *x, int64_t n, uint8_t *blocks, cudaStream_t s);

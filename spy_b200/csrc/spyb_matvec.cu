@@ -358,12 +358,15 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
     stamp(p.stamps, 2, false);
     matvec_tap(p, act);
 
-    // this lane's operands: activation word (Q8_0 weights: word l; Q4_0: lanes 0..3 hold the high nibbles, which meet
-    // values 16..31 = words 4..7) and, for Q4_0, the factor that brings its nibbles into the high half of every byte
-    const uint4   *Ysel = act.Y + ((WT == 8) ? l : (l ^ 4));
-    const uint32_t mult = (l < 4) ? 1u : 16u;
-    const uint8_t *lane_base = ring + r * ROWB;
-    const int      qoff = ((WT == 8) ? l : (l & 3)) * 16;
+    // this lane's operands, as 32-bit shared-space addresses: activation word (Q8_0 weights: word l; Q4_0: lanes 0..3
+    // hold the high nibbles, which meet values 16..31 = words 4..7), the scales, its row and word in a record; and, for
+    // Q4_0, the factor that brings its nibbles into the high half of every byte
+    const uint32_t y_s   = smem_u32(act.Y) + ((WT == 8) ? l : (l ^ 4)) * 16;
+    const uint32_t ds_s  = smem_u32(act.DS);
+    const uint32_t row_s = ring_s + r * ROWB + ((WT == 8) ? l : (l & 3)) * 16;
+    const uint32_t mult  = (l < 4) ? 1u : 16u;
+    const uint32_t tile_off = (uint32_t)S * RECB;        // second tile of the unit inside a stage
+    const uint32_t col_y = (uint32_t)ng * 128, col_ds = (uint32_t)ng * 16;   // next activation column
 
     float acc[TM][R];
 #pragma unroll
@@ -373,26 +376,26 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
     }
 
     int64_t  cu = my_first; int crec = 0, slot = 0; uint32_t parity = 0;
+    uint32_t ya = y_s, da = ds_s;                        // activations of the unit's current group of four blocks
     int      n = 0;
     bool     ok = true;
     for (; n < n_items; ++n) {
         ok = mbar_wait_bounded(bar_s + slot * 8, parity, WAIT_LIMIT_NS);
         if (__any_sync(0xffffffffu, !ok)) { ok = false; break; }
-        const uint8_t *st  = lane_base + slot * stage_bytes;
-        const int      cnt = min(S, nrec - crec);
+        uint32_t  ra  = row_s + slot * stage_bytes;
+        const int cnt = min(S, nrec - crec);
 #pragma unroll 1
-        for (int rc = 0; rc < cnt; ++rc) {
+        for (int rc = 0; rc < cnt; ++rc, ra += RECB) {
             uint4 wq[R][2]; uint4 sc[R];
 #pragma unroll
             for (int i = 0; i < R; ++i) {
-                const uint8_t *rowp = st + i * S * RECB + rc * RECB;
-                wq[i][0] = *reinterpret_cast<const uint4 *>(rowp + qoff);
-                wq[i][1] = *reinterpret_cast<const uint4 *>(rowp + GRPB + qoff);
-                sc[i]    = *reinterpret_cast<const uint4 *>(rowp + (ROWB - 16));
+                const uint32_t rowa = ra + i * tile_off;
+                wq[i][0] = lds128(rowa);
+                wq[i][1] = lds128(rowa + GRPB);
+                sc[i]    = lds128(rowa - ((WT == 8) ? l : (l & 3)) * 16 + (ROWB - 16));
             }
 #pragma unroll
-            for (int gg = 0; gg < 2; ++gg) {
-                const int g = (crec + rc) * 2 + gg;
+            for (int gg = 0; gg < 2; ++gg, ya += 128, da += 16) {
                 float s[R][4];
 #pragma unroll
                 for (int i = 0; i < R; ++i) {
@@ -402,8 +405,8 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
                 }
 #pragma unroll
                 for (int t = 0; t < TM; ++t) {
-                    const uint4  y  = Ysel[(t * ng + g) * 8];
-                    const float4 ds = act.DS[t * ng + g];
+                    const uint4  y  = lds128(ya + t * col_y);
+                    const float4 ds = lds128f(da + t * col_ds);
 #pragma unroll
                     for (int i = 0; i < R; ++i) {
                         const uint4 w = wq[i][gg];
@@ -446,7 +449,7 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
                     }
                 }
             }
-            crec = 0; cu += wact;
+            crec = 0; cu += wact; ya = y_s; da = ds_s;
         }
     }
     if (!ok) {
@@ -471,8 +474,232 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
     }
 }
 
-int matvec_max_columns(int nb) {
-    for (int t = 8; t > 1; t >>= 1) { if (act_plane_bytes(padded_blocks(nb), t) <= 120 * 1024) { return t; } }
+// ---------------------------------------------------------------------------------------------
+// Variant for matrices stored in 32-row tiles (DevMatrix::tile_rows == 32): lane = row. A lane owns all eight
+// accumulators of its row, so the scale product d_w * d_x and the activation words are fetched once per row and
+// block instead of once per accumulator, and the reduction tree is register arithmetic: about a third fewer
+// instructions per weight byte than the lane-per-accumulator kernel. It needs many rows to fill the machine
+// (a warp walks 32 rows along K), so it is used for the tall matrices (FFN up|gate, the head).
+// A record is [32 rows][2 groups x 64 B (Q4_0) or 128 B (Q8_0) | 8 fp16 scales]: one bulk copy per stage; the
+// 144-byte (272-byte) row pitch makes the per-lane 128-bit reads conflict-free.
+// With fused_pair, rows 0..15 of every tile are FFN-up rows 16u..16u+15 and rows 16..31 the FFN-gate rows.
+template <int WT, int TM>
+__global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const MatvecParams p, const int ring_bytes, const int S, const int wact) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __shared__ float norm_scales[8];
+    constexpr int ROWB = ((WT == 8) ? 256 : 128) + 16;
+    constexpr int RECB = 32 * ROWB;
+    constexpr int GRPB = (WT == 8) ? 128 : 64;
+    constexpr int NW   = (WT == 8) ? 8 : 4;              // 128-bit words of quants per group of four blocks
+
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nbp  = p.A.nbp;
+    const int ng   = nbp >> 2;
+    const int nrec = nbp >> 3;
+
+    const int64_t n_units  = p.A.n_rows >> 5;
+    const int64_t unit_lo  = n_units * blockIdx.x / gridDim.x;
+    const int64_t unit_hi  = n_units * (blockIdx.x + 1) / gridDim.x;
+    const int64_t my_first = unit_lo + warp;
+    const int     my_units = (warp < wact && my_first < unit_hi) ? (int)((unit_hi - my_first + wact - 1) / wact) : 0;
+    const int     n_act    = (int)min((int64_t)wact, unit_hi - unit_lo);
+    const int     nch      = (nrec + S - 1) / S;
+    const int     n_items  = my_units * nch;
+    const int     stage_bytes = S * RECB;
+    const int     NS = max(1, min(MAX_STAGES, ring_bytes / (max(n_act, 1) * stage_bytes)));
+
+    const MatvecSmem L = matvec_smem_layout(nbp, TM, (size_t)ring_bytes);
+    const uint32_t ring_s = smem_u32(smem_raw + L.ring) + (uint32_t)warp * NS * stage_bytes;
+    const uint32_t bar_s  = smem_u32(smem_raw + L.bars) + warp * MAX_STAGES * 8;
+    const size_t   tile_bytes = (size_t)nrec * RECB;
+
+    const uint8_t *src = nullptr;
+    int64_t lu = my_first; int lrec = 0, lslot = 0, issued = 0;
+    auto issue_next = [&]() {
+        const uint32_t bytes = (uint32_t)min(S, nrec - lrec) * RECB;
+        const uint32_t bar = bar_s + lslot * 8;
+        mbar_expect_tx(bar, bytes);
+        bulk_copy_g2s(ring_s + lslot * stage_bytes, src, bytes, bar);
+        src += bytes;
+        ++issued;
+        if (++lslot == NS) { lslot = 0; }
+        lrec += S;
+        if (lrec >= nrec) { lrec = 0; lu += wact; src = p.A.w + (size_t)lu * tile_bytes; }
+    };
+
+    pdl_launch_dependents();
+    stamp(p.stamps, 0, false);
+    if (lane == 0 && n_items > 0) {
+        for (int s = 0; s < NS; ++s) { mbar_init(bar_s + s * 8, 1); }
+        mbar_init_fence();
+        src = p.A.w + (size_t)lu * tile_bytes;
+        for (int s = 0; s < NS && issued < n_items; ++s) { issue_next(); }
+    }
+    __syncwarp();
+    pdl_wait();
+    stamp(p.stamps, 1, false);
+
+    ActPlanes act = act_planes(smem_raw, nbp, TM);
+    {
+        float *v3 = reinterpret_cast<float *>(smem_raw);
+        const int  n4p  = nbp * 8;
+        const bool norm = p.pro == PRO_NORM_QUANT;
+        if (TM == 1 && n4p <= 2 * MV_THREADS) {
+            if (norm) { matvec_prologue_1col<2, true>(p, act, v3, norm_scales); } else { matvec_prologue_1col<2, false>(p, act, v3, norm_scales); }
+        } else if (TM == 1 && n4p <= PRO_GROUPS * MV_THREADS) {
+            if (norm) { matvec_prologue_1col<PRO_GROUPS, true>(p, act, v3, norm_scales); } else { matvec_prologue_1col<PRO_GROUPS, false>(p, act, v3, norm_scales); }
+        } else {
+            matvec_prologue<TM>(p, act, v3, norm_scales);
+        }
+    }
+    __syncthreads();
+    stamp(p.stamps, 2, false);
+    matvec_tap(p, act);
+
+    const uint32_t y_s   = smem_u32(act.Y);
+    const uint32_t ds_s  = smem_u32(act.DS);
+    const uint32_t row_s = ring_s + lane * ROWB;
+    const uint32_t col_y = (uint32_t)ng * 128, col_ds = (uint32_t)ng * 16;
+
+    float acc[TM][8];
+#pragma unroll
+    for (int t = 0; t < TM; ++t) {
+#pragma unroll
+        for (int a = 0; a < 8; ++a) { acc[t][a] = 0.f; }
+    }
+
+    int64_t  cu = my_first; int crec = 0, slot = 0; uint32_t parity = 0;
+    uint32_t ya = y_s, da = ds_s;
+    int      n = 0;
+    bool     ok = true;
+    for (; n < n_items; ++n) {
+        ok = mbar_wait_bounded(bar_s + slot * 8, parity, WAIT_LIMIT_NS);
+        if (__any_sync(0xffffffffu, !ok)) { ok = false; break; }
+        uint32_t  ra  = row_s + slot * stage_bytes;
+        const int cnt = min(S, nrec - crec);
+#pragma unroll 1
+        for (int rc = 0; rc < cnt; ++rc, ra += RECB) {
+            const uint4 sc = lds128(ra + 2 * GRPB);
+#pragma unroll
+            for (int gg = 0; gg < 2; ++gg, ya += 128, da += 16) {
+                const uint32_t s01 = gg ? sc.z : sc.x, s23 = gg ? sc.w : sc.y;
+                const float2   f01 = __half22float2(*reinterpret_cast<const __half2 *>(&s01)), f23 = __half22float2(*reinterpret_cast<const __half2 *>(&s23));
+                uint4 w[NW];
+#pragma unroll
+                for (int j = 0; j < NW; ++j) { w[j] = lds128(ra + gg * GRPB + j * 16); }
+#pragma unroll
+                for (int t = 0; t < TM; ++t) {
+                    const float4 ds = lds128f(da + t * col_ds);
+                    const float  s0 = __fmul_rn(f01.x, ds.x), s1 = __fmul_rn(f01.y, ds.y), s2 = __fmul_rn(f23.x, ds.z), s3 = __fmul_rn(f23.y, ds.w);
+                    if (WT == 2) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {   // word j: high nibbles -> accumulator j (values 16 + 4j.. vs word 4 + j), low -> accumulator 4 + j
+                            const uint4 yh = lds128(ya + t * col_y + (4 + j) * 16), yl = lds128(ya + t * col_y + j * 16);
+                            float ah = acc[t][j], al = acc[t][4 + j];
+                            ah = fmaf(s0, lane_sum16_q4_0(w[j].x, 1u, yh.x), ah);  al = fmaf(s0, lane_sum16_q4_0(w[j].x, 16u, yl.x), al);
+                            ah = fmaf(s1, lane_sum16_q4_0(w[j].y, 1u, yh.y), ah);  al = fmaf(s1, lane_sum16_q4_0(w[j].y, 16u, yl.y), al);
+                            ah = fmaf(s2, lane_sum16_q4_0(w[j].z, 1u, yh.z), ah);  al = fmaf(s2, lane_sum16_q4_0(w[j].z, 16u, yl.z), al);
+                            ah = fmaf(s3, lane_sum16_q4_0(w[j].w, 1u, yh.w), ah);  al = fmaf(s3, lane_sum16_q4_0(w[j].w, 16u, yl.w), al);
+                            acc[t][j] = ah; acc[t][4 + j] = al;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < NW; ++j) {  // word j of every block -> accumulator j
+                            const uint4 y = lds128(ya + t * col_y + j * 16);
+                            float a = acc[t][j];
+                            a = fmaf(s0, lane_sum_q8_0(w[j].x, y.x), a);
+                            a = fmaf(s1, lane_sum_q8_0(w[j].y, y.y), a);
+                            a = fmaf(s2, lane_sum_q8_0(w[j].z, y.z), a);
+                            a = fmaf(s3, lane_sum_q8_0(w[j].w, y.w), a);
+                            acc[t][j] = a;
+                        }
+                    }
+                }
+            }
+        }
+        __syncwarp();
+        if (lane == 0 && issued < n_items) { issue_next(); }
+        if (++slot == NS) { slot = 0; parity ^= 1u; }
+        crec += S;
+        if (crec >= nrec) {   // tile finished: hsum_float_8 tree ((a0+a4)+(a2+a6))+((a1+a5)+(a3+a7)) in registers, then the epilogue
+#pragma unroll
+            for (int t = 0; t < TM; ++t) {
+                const float h = __fadd_rn(__fadd_rn(__fadd_rn(acc[t][0], acc[t][4]), __fadd_rn(acc[t][2], acc[t][6])),
+                                          __fadd_rn(__fadd_rn(acc[t][1], acc[t][5]), __fadd_rn(acc[t][3], acc[t][7])));
+#pragma unroll
+                for (int a = 0; a < 8; ++a) { acc[t][a] = 0.f; }
+                if (p.epi == EPI_SILU_MUL) {
+                    const float gate = __shfl_down_sync(0xffffffffu, h, 16);
+                    matvec_epilogue_silu(p, 16 * cu + lane, t, h, gate, lane < 16 && t < p.T);
+                } else {
+                    const float partner = __shfl_xor_sync(0xffffffffu, h, 1);
+                    matvec_epilogue(p, 32 * cu + lane, t, h, partner, t < p.T);
+                }
+            }
+            crec = 0; cu += wact; ya = y_s; da = ds_s;
+        }
+    }
+    if (!ok) {
+        if (lane == 0 && p.error_flag != nullptr) { atomicExch(p.error_flag, 1); }
+        for (int k = n; k < __shfl_sync(0xffffffffu, issued, 0); ++k) {
+            mbar_wait_bounded(bar_s + slot * 8, parity, 10000000ull);
+            if (++slot == NS) { slot = 0; parity ^= 1u; }
+        }
+    }
+    if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
+}
+
+template <int WT, int TM>
+static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &cfg) {
+    constexpr int RECB = 32 * (((WT == 8) ? 256 : 128) + 16);
+    const int64_t n_units = p.A.n_rows >> 5;
+    int64_t grid = std::min<int64_t>(cfg.num_sms, n_units);
+    if (grid < 1) { grid = 1; }
+    const int64_t units_per_cta = (n_units + grid - 1) / grid;
+    const MatvecSmem fixed = matvec_smem_layout(p.A.nbp, TM, 0);
+    const size_t budget = 224 * 1024;
+    if (fixed.total + (size_t)RECB > budget) { return cudaErrorInvalidValue; }
+    const size_t ring = std::min<size_t>((size_t)cfg.mv_ring_kb * 2 * 1024, budget - fixed.total) / 128 * 128;
+    const int nrec = p.A.nbp >> 3;
+    int wact = (int)std::min<int64_t>(MV_WARPS, units_per_cta);
+    int S = 2;
+    while (S > nrec) { S >>= 1; }
+    if (S < 1) { S = 1; }
+    while (ring / ((size_t)wact * S * RECB) < 3) {
+        if (S > 1) { S >>= 1; }
+        else if (wact > 1) { wact = (wact + 1) / 2; }
+        else { break; }
+    }
+    if (cfg.mv_force_s > 0) { S = std::min(cfg.mv_force_s, std::max(nrec, 1)); }
+    if (cfg.mv_force_wact > 0) { wact = std::min(cfg.mv_force_wact, MV_WARPS); }
+    if (ring / ((size_t)wact * S * RECB) < 1) { return cudaErrorInvalidValue; }
+    const size_t smem = fixed.total + ring;
+    static size_t smem_allowed = 48 * 1024;
+    if (smem > smem_allowed) {
+        cudaError_t err = cudaFuncSetAttribute(matvec_rows_kernel<WT, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) { return err; }
+        smem_allowed = smem;
+    }
+    MatvecParams q = p;
+    if (q.error_flag == nullptr) { q.error_flag = cfg.error_flag; }
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)grid); lc.blockDim = dim3(MV_THREADS); lc.dynamicSmemBytes = smem; lc.stream = cfg.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&lc, matvec_rows_kernel<WT, TM>, q, (int)ring, S, wact);
+}
+
+template <int WT>
+static cudaError_t launch_matvec_rows_w(const MatvecParams &p, const LaunchCfg &cfg) {
+    if (p.T <= 1) { return launch_matvec_rows_t<WT, 1>(p, cfg); }
+    if (p.T <= 2) { return launch_matvec_rows_t<WT, 2>(p, cfg); }
+    return launch_matvec_rows_t<WT, 4>(p, cfg);
+}
+
+int matvec_max_columns(int nb) {   // (the lane-per-row kernel keeps 8 accumulators per column in registers: at most 4 columns)
+    for (int t = 4; t > 1; t >>= 1) { if (act_plane_bytes(padded_blocks(nb), t) <= 120 * 1024) { return t; } }
     return 1;
 }
 
@@ -543,7 +770,15 @@ static cudaError_t launch_matvec_w(const MatvecParams &p, const LaunchCfg &cfg) 
 cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg) {
     if (p.T < 1 || p.T > matvec_max_columns(p.A.nb)) { return cudaErrorInvalidValue; }
     if (p.A.k % QK != 0 || p.A.nb < 1 || p.A.nbp != padded_blocks(p.A.nb) || p.A.w == nullptr) { return cudaErrorInvalidValue; }
-    if (p.A.n_rows & 3) { return cudaErrorInvalidValue; }
+    if (p.A.tile_rows == 32) {
+        if ((p.A.n_rows & 31) || p.pair_mode || (p.epi == EPI_SILU_MUL) != (p.A.fused_pair != 0)) { return cudaErrorInvalidValue; }
+        switch (p.A.type) {
+        case 2: return launch_matvec_rows_w<2>(p, cfg);
+        case 8: return launch_matvec_rows_w<8>(p, cfg);
+        default: return cudaErrorNotSupported;
+        }
+    }
+    if (p.A.tile_rows != 4 || (p.A.n_rows & 3)) { return cudaErrorInvalidValue; }
     if (p.pair_mode && (p.B.type != p.A.type || p.B.n_rows != p.A.n_rows || p.B.k != p.A.k || p.B.nbp != p.A.nbp || p.B.w == nullptr)) { return cudaErrorInvalidValue; }
     if ((p.epi == EPI_SILU_MUL) != (p.pair_mode != 0)) { return cudaErrorInvalidValue; }
     // tiles per warp: two when one would leave units waiting for a free warp (single column), or in pair mode

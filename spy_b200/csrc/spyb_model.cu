@@ -138,6 +138,7 @@ struct NcclApi {
 static NcclApi g_nccl;
 
 struct Layer {
+    DevMatrix upgate;   // FFN up and gate interleaved in 32-row tiles (when the shard's FFN width is a multiple of 16); else up / gate below
     DevMatrix wqkv, wo, up, gate, down;
     float    *attn_norm = nullptr, *ffn_norm = nullptr;
     __half   *k_cache = nullptr, *v_cache = nullptr;   // K [n_ctx][dl], V transposed [dl][n_ctx]
@@ -229,7 +230,8 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             a.q = m->q; a.k_cache = ly.k_cache; a.v_cache = ly.v_cache; a.out = m->att; a.pos_base = m->d_pos; a.exp_table = be->d_exp_table;
             a.n_head = m->dl / m->info.head_dim; a.hd = m->info.head_dim; a.dl = m->dl; a.T = T; a.n_ctx = m->info.n_ctx;
             a.scale = 1.0f / std::sqrt((float)m->info.head_dim);
-            prefetch_next(m, a, &ly.up, &ly.gate); a.stamps = stamps(1);
+            if (ly.upgate.w) { prefetch_next(m, a, &ly.upgate); } else { prefetch_next(m, a, &ly.up, &ly.gate); }
+            a.stamps = stamps(1);
             SPYB_CUDA(be, launch_attention(a, cfg)); ++*launches;
         }
         {   // 3: quantize -> Wo -> + residual (tensor parallel: partial sums, rank 0 carries the residual)
@@ -247,7 +249,8 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
         }
         {   // 4: norm + quantize -> up, gate -> up * silu(gate)
             MatvecParams p;
-            p.A = ly.up; p.B = ly.gate; p.pair_mode = 1; p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
+            if (ly.upgate.w) { p.A = ly.upgate; } else { p.A = ly.up; p.B = ly.gate; p.pair_mode = 1; }
+            p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
             p.eps = m->info.rms_eps; p.epi = EPI_SILU_MUL; p.out = m->act; p.out_stride = m->fl; p.silu_table = be->d_silu_table;
             prefetch_next(m, p, L + 1 < m->layers.size() ? &m->layers[L + 1].wqkv : &m->head); p.stamps = stamps(3);
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
@@ -340,7 +343,7 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
     };
     // rows [row0, row0 + n_rows) and blocks [blk0, blk0 + nb) of a [k_full, rows_full] matrix -> planes (optionally into `into` at row dst_row)
     auto upload_w = [&](const std::string &name, int64_t k_full, int64_t rows_full, int64_t row0, int64_t n_rows, int64_t blk0, int nb,
-                        DevMatrix *dst, DevMatrix *into, int64_t dst_row) {
+                        DevMatrix *dst, DevMatrix *into, int64_t dst_row, int sub_rows = 0, int sub_off = 0) {
         const GgufTensor *t; const uint8_t *data;
         if (!tensor(name, &t, &data)) { return SPYB_FAIL; }
         if (t->ne[0] != k_full || t->ne[1] != rows_full) { be->set_error("GGUF: %s has shape [%lld, %lld]", name.c_str(), (long long)t->ne[0], (long long)t->ne[1]); return SPYB_FAIL; }
@@ -349,7 +352,7 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         I.weight_bytes += (uint64_t)n_rows * nb * (t->type == SPYB_Q4_0 ? 18 : 34);
         if (into != nullptr) {
             if (into->type != t->type) { be->set_error("GGUF: %s: Wq/Wk/Wv must share one type", name.c_str()); return SPYB_UNSUPPORTED; }
-            return upload_matrix(be, t->type, data + row0 * rb, n_rows, rb, blk0, nb, dst, into, dst_row);
+            return upload_matrix(be, t->type, data + row0 * rb, n_rows, rb, blk0, nb, dst, into, dst_row, sub_rows, sub_off);
         }
         return upload_matrix(be, t->type, data + row0 * rb, n_rows, rb, blk0, nb, dst);
     };
@@ -367,9 +370,18 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
     }
     spyb_status st = upload_f32("output_norm.weight", d, &m->output_norm);
     if (st != SPYB_SUCCESS) { return fail(st); }
+    // tall matrices go to 32-row tiles (lane-per-row kernel) when their row count allows; SPYB_NO_ROWS_KERNEL keeps 4-row tiles
+    const bool rows32 = std::getenv("SPYB_NO_ROWS_KERNEL") == nullptr;
     {
         const std::string head_name = f.tensors.count("output.weight") ? "output.weight" : "token_embd.weight";
-        st = upload_w(head_name, d, I.n_vocab, 0, I.n_vocab, 0, d / 32, &m->head, nullptr, 0);   // replicated on every rank
+        auto ith = f.tensors.find(head_name);
+        if (rows32 && ith != f.tensors.end() && I.n_vocab % 32 == 0 && I.n_vocab >= 8192) {
+            DevMatrix dummy;
+            if ((st = alloc_matrix(be, ith->second.type, I.n_vocab, d / 32, &m->head, 32)) != SPYB_SUCCESS) { return fail(st); }
+            st = upload_w(head_name, d, I.n_vocab, 0, I.n_vocab, 0, d / 32, &dummy, &m->head, 0);
+        } else {
+            st = upload_w(head_name, d, I.n_vocab, 0, I.n_vocab, 0, d / 32, &m->head, nullptr, 0);   // replicated on every rank
+        }
         if (st != SPYB_SUCCESS) { return fail(st); }
     }
     m->layers.resize(I.n_layer);
@@ -389,10 +401,18 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         // Wo: all d rows, input columns of this rank's heads (a block sub-range of every row)
         if ((st = upload_w(p + "attn_output.weight", d, d, 0, d, (int64_t)r * dl / 32, dl / 32, &ly.wo, nullptr, 0)) != SPYB_SUCCESS) { return fail(st); }
         // FFN: rows [r*fl, (r+1)*fl) of up and gate; down keeps all rows and this rank's input columns
-        if ((st = upload_w(p + "ffn_up.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &ly.up, nullptr, 0)) != SPYB_SUCCESS) { return fail(st); }
-        if ((st = upload_w(p + "ffn_gate.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &ly.gate, nullptr, 0)) != SPYB_SUCCESS) { return fail(st); }
+        auto itu = f.tensors.find(p + "ffn_up.weight");
+        if (itu != f.tensors.end() && fl % 16 == 0 && rows32) {
+            if ((st = alloc_matrix(be, itu->second.type, 2 * (int64_t)fl, d / 32, &ly.upgate, 32)) != SPYB_SUCCESS) { return fail(st); }
+            ly.upgate.fused_pair = 1;
+            if ((st = upload_w(p + "ffn_up.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &dummy, &ly.upgate, 0, 16, 0)) != SPYB_SUCCESS) { return fail(st); }
+            if ((st = upload_w(p + "ffn_gate.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &dummy, &ly.upgate, 0, 16, 16)) != SPYB_SUCCESS) { return fail(st); }
+        } else {
+            if ((st = upload_w(p + "ffn_up.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &ly.up, nullptr, 0)) != SPYB_SUCCESS) { return fail(st); }
+            if ((st = upload_w(p + "ffn_gate.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &ly.gate, nullptr, 0)) != SPYB_SUCCESS) { return fail(st); }
+            if (ly.up.type != ly.gate.type) { be->set_error("ffn_up and ffn_gate must share one type"); return fail(SPYB_UNSUPPORTED); }
+        }
         if ((st = upload_w(p + "ffn_down.weight", I.n_ff, d, 0, d, (int64_t)r * fl / 32, fl / 32, &ly.down, nullptr, 0)) != SPYB_SUCCESS) { return fail(st); }
-        if (ly.up.type != ly.gate.type) { be->set_error("ffn_up and ffn_gate must share one type"); return fail(SPYB_UNSUPPORTED); }
         if (dev_alloc(m, &ly.k_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS || dev_alloc(m, &ly.v_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
     }
     I.weight_bytes += (uint64_t)(2 * I.n_layer + 1) * d * 4;
@@ -569,7 +589,8 @@ float spyb_model_bench_kernel(spyb_model *m, int32_t kind, int32_t sweeps, uint6
                 p.epi = EPI_QKV_ROPE; p.pos_base = m->d_pos; p.rope_table = m->rope_table; p.hd = m->info.head_dim; p.dl = m->dl;
                 p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache; p.n_ctx = m->info.n_ctx; break;
         case 1: p.A = ly.wo; p.pro = PRO_QUANT; p.x = m->att; p.x_stride = m->dl; p.epi = EPI_STORE; p.out = m->partial; p.out_stride = d; break;
-        case 2: p.A = ly.up; p.B = ly.gate; p.pair_mode = 1; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
+        case 2: if (ly.upgate.w) { p.A = ly.upgate; } else { p.A = ly.up; p.B = ly.gate; p.pair_mode = 1; }
+                p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
                 p.eps = m->info.rms_eps; p.epi = EPI_SILU_MUL; p.out = m->act; p.out_stride = m->fl; p.silu_table = be->d_silu_table; break;
         case 3: p.A = ly.down; p.pro = PRO_QUANT; p.x = m->act; p.x_stride = m->fl; p.epi = EPI_STORE; p.out = m->partial; p.out_stride = d; break;
         default: p.A = m->head; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = m->output_norm; p.eps = m->info.rms_eps;

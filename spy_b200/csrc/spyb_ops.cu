@@ -263,15 +263,18 @@ cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
 // upload-time re-tiling: raw 18-byte / 34-byte blocks -> the record stream described at DevMatrix
 // (one thread per padded block; blocks beyond nb are written as zeros with a zero scale)
 template <int WORDS>   // 4: Q4_0 (16 nibble bytes), 8: Q8_0 (32 int8 values)
-__global__ void retile_kernel(const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, int nbp, uint8_t *dst) {
+__global__ void retile_kernel(const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, int nbp, uint8_t *base, int tile_rows,
+                              int64_t dst_row0, int64_t src_row0, int sub_rows, int sub_off) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_rows * nbp) { return; }
-    const int64_t  row = i / nbp;
-    const int      b = (int)(i - row * nbp);
-    const uint8_t *src = raw + row * row_stride + (int64_t)b * (2 + 4 * WORDS);
+    const int64_t  lrow = i / nbp;
+    const int      b = (int)(i - lrow * nbp);
+    const uint8_t *src = raw + lrow * row_stride + (int64_t)b * (2 + 4 * WORDS);
     const bool     real = b < nb;
     constexpr int  ROWB = WORDS * 32 + 16;
-    uint8_t  *rec = dst + ((row >> 2) * (nbp >> 3) + (b >> 3)) * (4 * ROWB) + (row & 3) * ROWB;
+    const int64_t  srow = src_row0 + lrow;
+    const int64_t  row  = dst_row0 + (sub_rows > 0 ? (srow / sub_rows) * tile_rows + sub_off + srow % sub_rows : srow);
+    uint8_t  *rec = base + ((row / tile_rows) * (nbp >> 3) + (b >> 3)) * ((int64_t)tile_rows * ROWB) + (row % tile_rows) * ROWB;
     uint32_t *q   = reinterpret_cast<uint32_t *>(rec + ((b >> 2) & 1) * (WORDS * 16)) + (b & 3);
     reinterpret_cast<uint16_t *>(rec + WORDS * 32)[b & 7] = real ? (uint16_t)(src[0] | (src[1] << 8)) : (uint16_t)0;
 #pragma unroll
@@ -282,13 +285,15 @@ __global__ void retile_kernel(const uint8_t *raw, int64_t row_stride, int64_t n_
     }
 }
 
-cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *dst, cudaStream_t s) {
+cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *matrix_base, int tile_rows,
+                          int64_t dst_row0, int64_t src_row0, int sub_rows, int sub_off, cudaStream_t s) {
     const int     nbp = padded_blocks(nb);
     const int64_t n = n_rows * nbp;
     if (n == 0) { return cudaSuccess; }
-    if (n_rows & 3) { return cudaErrorInvalidValue; }
-    if (type == 2)      { retile_kernel<4><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, dst); }
-    else if (type == 8) { retile_kernel<8><<<(unsigned)((n + 255) / 256), 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, dst); }
+    if (tile_rows != 4 && tile_rows != 32) { return cudaErrorInvalidValue; }
+    const unsigned grid = (unsigned)((n + 255) / 256);
+    if (type == 2)      { retile_kernel<4><<<grid, 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, matrix_base, tile_rows, dst_row0, src_row0, sub_rows, sub_off); }
+    else if (type == 8) { retile_kernel<8><<<grid, 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, matrix_base, tile_rows, dst_row0, src_row0, sub_rows, sub_off); }
     else                { return cudaErrorNotSupported; }
     return launch_check();
 }
