@@ -177,6 +177,7 @@ spyb_status spyb_create(const spyb_config *config, spyb_backend **out) {
     if (const char *v = std::getenv("SPYB_MV_CTAS_PER_SM")) { be->mv_ctas_per_sm = std::max(1, std::min(2, std::atoi(v))); }   // tuning knob
     if (const char *v = std::getenv("SPYB_MV_S")) { be->mv_force_s = std::atoi(v); }         // tuning knobs
     if (const char *v = std::getenv("SPYB_MV_WACT")) { be->mv_force_wact = std::atoi(v); }
+    if (const char *v = std::getenv("SPYB_MV_ROWS_SPLIT")) { be->mv_rows_split = std::atoi(v); }
     if (const char *v = std::getenv("SPYB_MV_RING_KB")) { be->mv_ring_kb = std::max(8, std::min(96, std::atoi(v))); }   // tuning knob
     if (cudaStreamCreateWithFlags(&be->stream, cudaStreamNonBlocking) != cudaSuccess) { delete be; return SPYB_FAIL; }
     if (cudaHostAlloc(reinterpret_cast<void **>(&be->h_error_flag), sizeof(int), cudaHostAllocMapped) != cudaSuccess ||

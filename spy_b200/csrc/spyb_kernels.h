@@ -94,6 +94,7 @@ struct LaunchCfg {
     int          mv_ctas_per_sm = 2;   // mat-vec CTAs per SM for single-column launches (their register budget allows 2)
     int          mv_ring_kb = 80;      // shared-memory ring per CTA that bulk copies stream the weights through
     int          mv_force_s = 0, mv_force_wact = 0;   // tuning overrides (0 = choose)
+    int          mv_rows_split = 0;                   // lane-per-row kernel: 1 = four warps share a tile when an SM has at most 3 tiles, 2 = whenever groups suffice
     int         *error_flag = nullptr;
 };
 

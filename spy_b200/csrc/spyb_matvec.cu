@@ -54,12 +54,13 @@ __device__ __forceinline__ ActPlanes act_planes(void *base, int nbp, int TM) {
     return a;
 }
 
-struct MatvecSmem { size_t act, bars, ring, total; };
+struct MatvecSmem { size_t act, bars, xch, ring, total; };
 __host__ __device__ static inline MatvecSmem matvec_smem_layout(int nbp, int TM, size_t ring_bytes) {
     MatvecSmem m;
     m.act  = 0;
     m.bars = (act_plane_bytes(nbp, TM) + 15) / 16 * 16;
-    m.ring = (m.bars + (size_t)MV_WARPS * MAX_STAGES * 8 + 127) / 128 * 128;
+    m.xch  = m.bars + (size_t)MV_WARPS * MAX_STAGES * 8;                  // partial-sum exchange of warps that share a tile
+    m.ring = (m.xch + (size_t)(MV_WARPS / 4) * 2 * TM * 4 * 32 * 4 + 127) / 128 * 128;
     m.total = m.ring + ring_bytes;
     return m;
 }
@@ -475,24 +476,32 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
 }
 
 // ---------------------------------------------------------------------------------------------
-// Variant for matrices stored in 32-row tiles (DevMatrix::tile_rows == 32): lane = row. A lane owns all eight
-// accumulators of its row, so the scale product d_w * d_x and the activation words are fetched once per row and
-// block instead of once per accumulator, and the reduction tree is register arithmetic: about a third fewer
-// instructions per weight byte than the lane-per-accumulator kernel. It needs many rows to fill the machine
-// (a warp walks 32 rows along K), so it is used for the tall matrices (FFN up|gate, the head).
-// A record is [32 rows][2 groups x 64 B (Q4_0) or 128 B (Q8_0) | 8 fp16 scales]: one bulk copy per stage; the
-// 144-byte (272-byte) row pitch makes the per-lane 128-bit reads conflict-free.
+// Variant for matrices stored in 32-row tiles (DevMatrix::tile_rows == 32): lane = row. A lane keeps whole
+// accumulators of its row in registers, so the scale product d_w * d_x and the activation words are fetched once
+// per row and block instead of once per accumulator, the results of a tile are 32 consecutive outputs and the
+// reduction tree is register arithmetic: fewer instructions per weight byte than the lane-per-accumulator kernel.
+// It needs many rows to fill the machine (a tile walks along K sequentially), so it serves the tall matrices
+// (FFN up|gate, the head), and NSPLIT warps share a tile to put more warps on every scheduler:
+//   NSPLIT == 1: one warp per tile, all eight accumulators per lane
+//   NSPLIT == 4: warp q of the group takes accumulators q and q + 4 (Q4_0: both nibbles of quant word q; Q8_0:
+//                words q and q + 4) - exactly the pairs hsum_float_8 adds first, ((a0+a4)+(a2+a6))+((a1+a5)+(a3+a7));
+//                the four pair sums meet in shared memory and the group's first warp finishes the tree.
+// The group streams its tiles through one ring: the first warp issues the bulk copies (one per stage), every warp
+// waits on the stage's "full" barrier, and a stage is refilled once all NSPLIT warps have arrived on its "empty" barrier.
+// A record is [32 rows][2 groups x 64 B (Q4_0) or 128 B (Q8_0) | 8 fp16 scales]; the 144-byte (272-byte) row pitch
+// makes the per-lane 128-bit reads conflict-free.
 // With fused_pair, rows 0..15 of every tile are FFN-up rows 16u..16u+15 and rows 16..31 the FFN-gate rows.
-template <int WT, int TM>
+template <int WT, int TM, int NSPLIT>
 __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const MatvecParams p, const int ring_bytes, const int S, const int wact) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ float norm_scales[8];
     constexpr int ROWB = ((WT == 8) ? 256 : 128) + 16;
     constexpr int RECB = 32 * ROWB;
     constexpr int GRPB = (WT == 8) ? 128 : 64;
-    constexpr int NW   = (WT == 8) ? 8 : 4;              // 128-bit words of quants per group of four blocks
+    constexpr int NP   = 4 / NSPLIT;                     // accumulator pairs (j, j + 4) per warp
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int grp = warp / NSPLIT, part = warp % NSPLIT;
     const int nbp  = p.A.nbp;
     const int ng   = nbp >> 2;
     const int nrec = nbp >> 3;
@@ -500,37 +509,47 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
     const int64_t n_units  = p.A.n_rows >> 5;
     const int64_t unit_lo  = n_units * blockIdx.x / gridDim.x;
     const int64_t unit_hi  = n_units * (blockIdx.x + 1) / gridDim.x;
-    const int64_t my_first = unit_lo + warp;
-    const int     my_units = (warp < wact && my_first < unit_hi) ? (int)((unit_hi - my_first + wact - 1) / wact) : 0;
-    const int     n_act    = (int)min((int64_t)wact, unit_hi - unit_lo);
+    const int64_t my_first = unit_lo + grp;
+    const int     my_units = (grp < wact && my_first < unit_hi) ? (int)((unit_hi - my_first + wact - 1) / wact) : 0;
+    const int     n_act    = (int)min((int64_t)wact, unit_hi - unit_lo);   // groups of this CTA that have work
     const int     nch      = (nrec + S - 1) / S;
     const int     n_items  = my_units * nch;
     const int     stage_bytes = S * RECB;
     const int     NS = max(1, min(MAX_STAGES, ring_bytes / (max(n_act, 1) * stage_bytes)));
 
     const MatvecSmem L = matvec_smem_layout(nbp, TM, (size_t)ring_bytes);
-    const uint32_t ring_s = smem_u32(smem_raw + L.ring) + (uint32_t)warp * NS * stage_bytes;
-    const uint32_t bar_s  = smem_u32(smem_raw + L.bars) + warp * MAX_STAGES * 8;
+    const uint32_t ring_s  = smem_u32(smem_raw + L.ring) + (uint32_t)grp * NS * stage_bytes;
+    const uint32_t full_s  = smem_u32(smem_raw + L.bars) + (grp * NSPLIT) * MAX_STAGES * 8;
+    const uint32_t empty_s = full_s + MAX_STAGES * 8;     // (the second warp's barrier slots; used when NSPLIT > 1)
+    const uint32_t xbar_s  = empty_s + MAX_STAGES * 8;    // two "pair sums written" barriers (the third warp's slots)
+    float         *xch     = reinterpret_cast<float *>(smem_raw + L.xch) + (size_t)grp * 2 * TM * 4 * 32;
     const size_t   tile_bytes = (size_t)nrec * RECB;
+    const bool     leader = (part == 0);
 
     const uint8_t *src = nullptr;
-    int64_t lu = my_first; int lrec = 0, lslot = 0, issued = 0;
+    int64_t lu = my_first; int lrec = 0, lslot = 0, issued = 0; uint32_t lparity = 0;
+    bool    ok = true;
+    // leader lane 0: stage lslot <- the next <= S records; a stage that was used before is first waited empty
     auto issue_next = [&]() {
+        if (NSPLIT > 1 && issued >= NS) {
+            if (!mbar_wait_bounded(empty_s + lslot * 8, lparity, WAIT_LIMIT_NS)) { ok = false; return; }
+        }
         const uint32_t bytes = (uint32_t)min(S, nrec - lrec) * RECB;
-        const uint32_t bar = bar_s + lslot * 8;
+        const uint32_t bar = full_s + lslot * 8;
         mbar_expect_tx(bar, bytes);
         bulk_copy_g2s(ring_s + lslot * stage_bytes, src, bytes, bar);
         src += bytes;
         ++issued;
-        if (++lslot == NS) { lslot = 0; }
+        if (++lslot == NS) { lslot = 0; if (issued > NS) { lparity ^= 1u; } }
         lrec += S;
         if (lrec >= nrec) { lrec = 0; lu += wact; src = p.A.w + (size_t)lu * tile_bytes; }
     };
 
     pdl_launch_dependents();
     stamp(p.stamps, 0, false);
-    if (lane == 0 && n_items > 0) {
-        for (int s = 0; s < NS; ++s) { mbar_init(bar_s + s * 8, 1); }
+    if (leader && lane == 0 && n_items > 0) {
+        for (int s = 0; s < NS; ++s) { mbar_init(full_s + s * 8, 1); if (NSPLIT > 1) { mbar_init(empty_s + s * 8, NSPLIT); } }
+        if (NSPLIT > 1) { mbar_init(xbar_s, NSPLIT); mbar_init(xbar_s + 8, NSPLIT); }
         mbar_init_fence();
         src = p.A.w + (size_t)lu * tile_bytes;
         for (int s = 0; s < NS && issued < n_items; ++s) { issue_next(); }
@@ -552,7 +571,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
             matvec_prologue<TM>(p, act, v3, norm_scales);
         }
     }
-    __syncthreads();
+    __syncthreads();   // (also orders the leaders' barrier initialisation before the other warps' first wait)
     stamp(p.stamps, 2, false);
     matvec_tap(p, act);
 
@@ -561,20 +580,19 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
     const uint32_t row_s = ring_s + lane * ROWB;
     const uint32_t col_y = (uint32_t)ng * 128, col_ds = (uint32_t)ng * 16;
 
-    float acc[TM][8];
+    float acc[TM][2 * NP];   // [pair][0] = accumulator j, [pair][1] = accumulator j + 4, j = part * NP + pair
 #pragma unroll
     for (int t = 0; t < TM; ++t) {
 #pragma unroll
-        for (int a = 0; a < 8; ++a) { acc[t][a] = 0.f; }
+        for (int a = 0; a < 2 * NP; ++a) { acc[t][a] = 0.f; }
     }
 
     int64_t  cu = my_first; int crec = 0, slot = 0; uint32_t parity = 0;
     uint32_t ya = y_s, da = ds_s;
-    int      n = 0;
-    bool     ok = true;
+    int      n = 0, tile_no = 0;
     for (; n < n_items; ++n) {
-        ok = mbar_wait_bounded(bar_s + slot * 8, parity, WAIT_LIMIT_NS);
-        if (__any_sync(0xffffffffu, !ok)) { ok = false; break; }
+        bool got = mbar_wait_bounded(full_s + slot * 8, parity, WAIT_LIMIT_NS);
+        if (__any_sync(0xffffffffu, !got || !ok)) { ok = false; break; }
         uint32_t  ra  = row_s + slot * stage_bytes;
         const int cnt = min(S, nrec - crec);
 #pragma unroll 1
@@ -584,74 +602,110 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
             for (int gg = 0; gg < 2; ++gg, ya += 128, da += 16) {
                 const uint32_t s01 = gg ? sc.z : sc.x, s23 = gg ? sc.w : sc.y;
                 const float2   f01 = __half22float2(*reinterpret_cast<const __half2 *>(&s01)), f23 = __half22float2(*reinterpret_cast<const __half2 *>(&s23));
-                uint4 w[NW];
+                uint4 w[(WT == 8) ? 2 * NP : NP];
 #pragma unroll
-                for (int j = 0; j < NW; ++j) { w[j] = lds128(ra + gg * GRPB + j * 16); }
+                for (int k = 0; k < NP; ++k) {
+                    const int j = part * NP + k;
+                    if (WT == 8) { w[2 * k] = lds128(ra + gg * GRPB + j * 16); w[2 * k + 1] = lds128(ra + gg * GRPB + (4 + j) * 16); }
+                    else         { w[k] = lds128(ra + gg * GRPB + j * 16); }
+                }
 #pragma unroll
                 for (int t = 0; t < TM; ++t) {
                     const float4 ds = lds128f(da + t * col_ds);
                     const float  s0 = __fmul_rn(f01.x, ds.x), s1 = __fmul_rn(f01.y, ds.y), s2 = __fmul_rn(f23.x, ds.z), s3 = __fmul_rn(f23.y, ds.w);
-                    if (WT == 2) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {   // word j: high nibbles -> accumulator j (values 16 + 4j.. vs word 4 + j), low -> accumulator 4 + j
-                            const uint4 yh = lds128(ya + t * col_y + (4 + j) * 16), yl = lds128(ya + t * col_y + j * 16);
-                            float ah = acc[t][j], al = acc[t][4 + j];
-                            ah = fmaf(s0, lane_sum16_q4_0(w[j].x, 1u, yh.x), ah);  al = fmaf(s0, lane_sum16_q4_0(w[j].x, 16u, yl.x), al);
-                            ah = fmaf(s1, lane_sum16_q4_0(w[j].y, 1u, yh.y), ah);  al = fmaf(s1, lane_sum16_q4_0(w[j].y, 16u, yl.y), al);
-                            ah = fmaf(s2, lane_sum16_q4_0(w[j].z, 1u, yh.z), ah);  al = fmaf(s2, lane_sum16_q4_0(w[j].z, 16u, yl.z), al);
-                            ah = fmaf(s3, lane_sum16_q4_0(w[j].w, 1u, yh.w), ah);  al = fmaf(s3, lane_sum16_q4_0(w[j].w, 16u, yl.w), al);
-                            acc[t][j] = ah; acc[t][4 + j] = al;
+                    for (int k = 0; k < NP; ++k) {
+                        const int j = part * NP + k;
+                        // accumulator j: Q4_0 high nibbles of word j (values 16 + 4j.. meet activation word 4 + j), Q8_0 word j;
+                        // accumulator 4 + j: Q4_0 low nibbles of word j (activation word j), Q8_0 word 4 + j
+                        const uint4 y0 = lds128(ya + t * col_y + ((WT == 8) ? j : 4 + j) * 16), y1 = lds128(ya + t * col_y + ((WT == 8) ? 4 + j : j) * 16);
+                        float a0 = acc[t][2 * k], a1 = acc[t][2 * k + 1];
+                        if (WT == 2) {
+                            a0 = fmaf(s0, lane_sum16_q4_0(w[k].x, 1u, y0.x), a0);  a1 = fmaf(s0, lane_sum16_q4_0(w[k].x, 16u, y1.x), a1);
+                            a0 = fmaf(s1, lane_sum16_q4_0(w[k].y, 1u, y0.y), a0);  a1 = fmaf(s1, lane_sum16_q4_0(w[k].y, 16u, y1.y), a1);
+                            a0 = fmaf(s2, lane_sum16_q4_0(w[k].z, 1u, y0.z), a0);  a1 = fmaf(s2, lane_sum16_q4_0(w[k].z, 16u, y1.z), a1);
+                            a0 = fmaf(s3, lane_sum16_q4_0(w[k].w, 1u, y0.w), a0);  a1 = fmaf(s3, lane_sum16_q4_0(w[k].w, 16u, y1.w), a1);
+                        } else {
+                            a0 = fmaf(s0, lane_sum_q8_0(w[2 * k].x, y0.x), a0);  a1 = fmaf(s0, lane_sum_q8_0(w[2 * k + 1].x, y1.x), a1);
+                            a0 = fmaf(s1, lane_sum_q8_0(w[2 * k].y, y0.y), a0);  a1 = fmaf(s1, lane_sum_q8_0(w[2 * k + 1].y, y1.y), a1);
+                            a0 = fmaf(s2, lane_sum_q8_0(w[2 * k].z, y0.z), a0);  a1 = fmaf(s2, lane_sum_q8_0(w[2 * k + 1].z, y1.z), a1);
+                            a0 = fmaf(s3, lane_sum_q8_0(w[2 * k].w, y0.w), a0);  a1 = fmaf(s3, lane_sum_q8_0(w[2 * k + 1].w, y1.w), a1);
                         }
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < NW; ++j) {  // word j of every block -> accumulator j
-                            const uint4 y = lds128(ya + t * col_y + j * 16);
-                            float a = acc[t][j];
-                            a = fmaf(s0, lane_sum_q8_0(w[j].x, y.x), a);
-                            a = fmaf(s1, lane_sum_q8_0(w[j].y, y.y), a);
-                            a = fmaf(s2, lane_sum_q8_0(w[j].z, y.z), a);
-                            a = fmaf(s3, lane_sum_q8_0(w[j].w, y.w), a);
-                            acc[t][j] = a;
-                        }
+                        acc[t][2 * k] = a0; acc[t][2 * k + 1] = a1;
                     }
                 }
             }
         }
-        __syncwarp();
-        if (lane == 0 && issued < n_items) { issue_next(); }
+        __syncwarp();   // every lane is done reading the stage
+        if (NSPLIT > 1 && lane == 0) { mbar_arrive(empty_s + slot * 8); }
+        if (leader && lane == 0 && issued < n_items) { issue_next(); }
         if (++slot == NS) { slot = 0; parity ^= 1u; }
         crec += S;
-        if (crec >= nrec) {   // tile finished: hsum_float_8 tree ((a0+a4)+(a2+a6))+((a1+a5)+(a3+a7)) in registers, then the epilogue
+        if (crec >= nrec) {   // tile finished: hsum_float_8 tree ((a0+a4)+(a2+a6))+((a1+a5)+(a3+a7)), then the epilogue
+            float h[TM];
+            if (NSPLIT == 1) {
 #pragma unroll
-            for (int t = 0; t < TM; ++t) {
-                const float h = __fadd_rn(__fadd_rn(__fadd_rn(acc[t][0], acc[t][4]), __fadd_rn(acc[t][2], acc[t][6])),
-                                          __fadd_rn(__fadd_rn(acc[t][1], acc[t][5]), __fadd_rn(acc[t][3], acc[t][7])));
+                for (int t = 0; t < TM; ++t) {
+                    h[t] = __fadd_rn(__fadd_rn(__fadd_rn(acc[t][0], acc[t][1]), __fadd_rn(acc[t][4], acc[t][5])),
+                                     __fadd_rn(__fadd_rn(acc[t][2], acc[t][3]), __fadd_rn(acc[t][6], acc[t][7])));
+                }
+            } else {
+                float *xb = xch + (size_t)(tile_no & 1) * TM * 4 * 32;
 #pragma unroll
-                for (int a = 0; a < 8; ++a) { acc[t][a] = 0.f; }
-                if (p.epi == EPI_SILU_MUL) {
-                    const float gate = __shfl_down_sync(0xffffffffu, h, 16);
-                    matvec_epilogue_silu(p, 16 * cu + lane, t, h, gate, lane < 16 && t < p.T);
-                } else {
-                    const float partner = __shfl_xor_sync(0xffffffffu, h, 1);
-                    matvec_epilogue(p, 32 * cu + lane, t, h, partner, t < p.T);
+                for (int t = 0; t < TM; ++t) {
+#pragma unroll
+                    for (int k = 0; k < NP; ++k) { xb[(t * 4 + part * NP + k) * 32 + lane] = __fadd_rn(acc[t][2 * k], acc[t][2 * k + 1]); }
+                }
+                __syncwarp();
+                if (lane == 0) { mbar_arrive(xbar_s + (tile_no & 1) * 8); }
+                if (leader) {
+                    got = mbar_wait_bounded(xbar_s + (tile_no & 1) * 8, (uint32_t)((tile_no >> 1) & 1), WAIT_LIMIT_NS);
+                    if (__any_sync(0xffffffffu, !got)) { ok = false; break; }
+#pragma unroll
+                    for (int t = 0; t < TM; ++t) {
+                        h[t] = __fadd_rn(__fadd_rn(xb[(t * 4 + 0) * 32 + lane], xb[(t * 4 + 2) * 32 + lane]),
+                                         __fadd_rn(xb[(t * 4 + 1) * 32 + lane], xb[(t * 4 + 3) * 32 + lane]));
+                    }
                 }
             }
-            crec = 0; cu += wact; ya = y_s; da = ds_s;
+#pragma unroll
+            for (int t = 0; t < TM; ++t) {
+#pragma unroll
+                for (int a = 0; a < 2 * NP; ++a) { acc[t][a] = 0.f; }
+            }
+            if (leader) {
+#pragma unroll
+                for (int t = 0; t < TM; ++t) {
+                    if (p.epi == EPI_SILU_MUL) {
+                        const float gate = __shfl_down_sync(0xffffffffu, h[t], 16);
+                        matvec_epilogue_silu(p, 16 * cu + lane, t, h[t], gate, lane < 16 && t < p.T);
+                    } else {
+                        const float partner = __shfl_xor_sync(0xffffffffu, h[t], 1);
+                        matvec_epilogue(p, 32 * cu + lane, t, h[t], partner, t < p.T);
+                    }
+                }
+            }
+            crec = 0; cu += wact; ya = y_s; da = ds_s; ++tile_no;
         }
     }
     if (!ok) {
+        // a copy (or a partner warp) did not arrive: report, give the copies still in flight a last bounded chance to
+        // land (they target this CTA's shared memory) and stop; the host sees the flag at its next synchronisation
         if (lane == 0 && p.error_flag != nullptr) { atomicExch(p.error_flag, 1); }
-        for (int k = n; k < __shfl_sync(0xffffffffu, issued, 0); ++k) {
-            mbar_wait_bounded(bar_s + slot * 8, parity, 10000000ull);
-            if (++slot == NS) { slot = 0; parity ^= 1u; }
+        if (leader) {
+            for (int k = n; k < __shfl_sync(0xffffffffu, issued, 0); ++k) {
+                mbar_wait_bounded(full_s + slot * 8, parity, 10000000ull);
+                if (++slot == NS) { slot = 0; parity ^= 1u; }
+            }
         }
     }
     if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
 }
 
-template <int WT, int TM>
+template <int WT, int TM, int NSPLIT>
 static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &cfg) {
     constexpr int RECB = 32 * (((WT == 8) ? 256 : 128) + 16);
+    constexpr int GROUPS = MV_WARPS / NSPLIT;
     const int64_t n_units = p.A.n_rows >> 5;
     int64_t grid = std::min<int64_t>(cfg.num_sms, n_units);
     if (grid < 1) { grid = 1; }
@@ -661,7 +715,7 @@ static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &
     if (fixed.total + (size_t)RECB > budget) { return cudaErrorInvalidValue; }
     const size_t ring = std::min<size_t>((size_t)cfg.mv_ring_kb * 2 * 1024, budget - fixed.total) / 128 * 128;
     const int nrec = p.A.nbp >> 3;
-    int wact = (int)std::min<int64_t>(MV_WARPS, units_per_cta);
+    int wact = (int)std::min<int64_t>(GROUPS, units_per_cta);
     int S = 2;
     while (S > nrec) { S >>= 1; }
     if (S < 1) { S = 1; }
@@ -671,12 +725,12 @@ static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &
         else { break; }
     }
     if (cfg.mv_force_s > 0) { S = std::min(cfg.mv_force_s, std::max(nrec, 1)); }
-    if (cfg.mv_force_wact > 0) { wact = std::min(cfg.mv_force_wact, MV_WARPS); }
+    if (cfg.mv_force_wact > 0) { wact = std::min(cfg.mv_force_wact, GROUPS); }
     if (ring / ((size_t)wact * S * RECB) < 1) { return cudaErrorInvalidValue; }
     const size_t smem = fixed.total + ring;
     static size_t smem_allowed = 48 * 1024;
     if (smem > smem_allowed) {
-        cudaError_t err = cudaFuncSetAttribute(matvec_rows_kernel<WT, TM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t err = cudaFuncSetAttribute(matvec_rows_kernel<WT, TM, NSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) { return err; }
         smem_allowed = smem;
     }
@@ -688,14 +742,22 @@ static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&lc, matvec_rows_kernel<WT, TM>, q, (int)ring, S, wact);
+    return cudaLaunchKernelEx(&lc, matvec_rows_kernel<WT, TM, NSPLIT>, q, (int)ring, S, wact);
 }
 
 template <int WT>
 static cudaError_t launch_matvec_rows_w(const MatvecParams &p, const LaunchCfg &cfg) {
-    if (p.T <= 1) { return launch_matvec_rows_t<WT, 1>(p, cfg); }
-    if (p.T <= 2) { return launch_matvec_rows_t<WT, 2>(p, cfg); }
-    return launch_matvec_rows_t<WT, 4>(p, cfg);
+    // four warps per tile while that still leaves every SM with fewer tiles than warp groups, else one
+    const int64_t tiles_per_sm = ((p.A.n_rows >> 5) + cfg.num_sms - 1) / cfg.num_sms;
+    const bool split = cfg.mv_rows_split == 1 ? tiles_per_sm <= 3 : (cfg.mv_rows_split == 2 && tiles_per_sm <= MV_WARPS / 4 + 2);
+    if (split) {
+        if (p.T <= 1) { return launch_matvec_rows_t<WT, 1, 4>(p, cfg); }
+        if (p.T <= 2) { return launch_matvec_rows_t<WT, 2, 4>(p, cfg); }
+        return launch_matvec_rows_t<WT, 4, 4>(p, cfg);
+    }
+    if (p.T <= 1) { return launch_matvec_rows_t<WT, 1, 1>(p, cfg); }
+    if (p.T <= 2) { return launch_matvec_rows_t<WT, 2, 1>(p, cfg); }
+    return launch_matvec_rows_t<WT, 4, 1>(p, cfg);
 }
 
 int matvec_max_columns(int nb) {   // (the lane-per-row kernel keeps 8 accumulators per column in registers: at most 4 columns)

@@ -163,3 +163,25 @@ def test_unsupported_models_are_reported(be, tmp_models):
         g.write(f.read(300))
     with pytest.raises(B.SpybError):
         B.LlamaModel(be, bad, n_ctx=32)
+
+
+@pytest.mark.parametrize("env", [{}, {"SPYB_MV_ROWS_SPLIT": "2"}, {"SPYB_QKV_TILE32": "1"}, {"SPYB_QKV_TILE32": "1", "SPYB_MV_ROWS_SPLIT": "2"},
+                                 {"SPYB_NO_ROWS_KERNEL": "1"}, {"SPYB_MV_S": "1", "SPYB_MV_WACT": "2"}])
+@pytest.mark.parametrize("wtype", [quants.Q4_0, quants.Q8_0])
+def test_every_matvec_variant_matches_oracle(env, wtype, oracle, tmp_models, monkeypatch):
+    """The weight layouts (4-row and 32-row tiles, fused up|gate), the lane-per-accumulator and lane-per-row kernels,
+    one or four warps per tile, stage sizes and stream counts are tuning choices: every combination must give the
+    CPU's bits. The vocabulary is large enough for the head to take the lane-per-row path."""
+    cfg = gguf_io.LlamaConfig(n_layer=2, d_model=256, n_head=2, n_ff=512, n_vocab=8192, weight_std=0.05, wtype=wtype)
+    path = str(tmp_models / f"variants_{wtype}.gguf")
+    if not os.path.exists(path):
+        gguf_io.make_llama_gguf(path, cfg, seed=41)
+    prompt = np.random.default_rng(9).integers(3, cfg.n_vocab, size=10)
+    want_ids, want_logits = oracle.OracleLlama(path, n_ctx=32).generate(prompt, 6)
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    b = B.B200Backend(0)
+    m = B.LlamaModel(b, path, n_ctx=32)
+    ids, logits = m.generate(prompt, 6)
+    assert np.array_equal(ids, want_ids) and logits_ok(logits, want_logits)
+    m.close(); b.close()
