@@ -13,8 +13,9 @@ so scaling is "strong". Rank 0 prints one JSON line.
                  embedding on the device, timed with CUDA events on the launching stream.
   e2e            the same loop through spyb_model_eval: token id from pinned host memory in, the
                  32000 logits back to the host and the argmax there, every step.
-  roofline       the dominant kernel (FFN up+gate mat-vec, 45 % of the weight bytes) timed alone over
-                 all layers' weights (1.6 GB per sweep, far larger than L2) against the measured HBM peak.
+  roofline       the dominant kernel (FFN up|gate mat-vec, 45 % of the weight bytes) timed alone over
+                 all layers' weights (1.6 GB per sweep, far larger than L2) against the measured HBM peak;
+                 "kernels" lists the other mat-vec launches of a step the same way.
   cpu_baseline   the reference's own CPU backend (oracle/_ref, compiled from the reference sources)
                  on the host cores, same GGUF and prompt, a few decode steps.
 
@@ -267,9 +268,13 @@ def main():
         peak, peak_kind = measured_peak()
         kb = bench_kernels(model, be)
         dom = kb["ffn_up_gate"]
-        roof = {"bound": "hbm", "kernel": "matvec_kernel<Q4_0,1> (FFN up+gate, SiLU-mul epilogue)", "achieved": dom["gbs"], "peak": peak,
+        # traffic: dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload's FFN
+        # matrices, from the ncu capture summarised in profiles/matvec_rows_q4_0_ffn_up_gate_7b.md
+        roof = {"bound": "hbm", "kernel": "matvec_rows_kernel<Q4_0, 1 column> (fused FFN up|gate, RMSNorm+Q8_0 prologue, SiLU-mul epilogue)",
+                "achieved": dom["gbs"], "peak": peak,
                 "peak_kind": f"of {peak_kind} ({'MEASURED_PEAKS.json copy bandwidth' if peak_kind == 'measured' else 'fallback 6650 GB/s'})",
-                "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": None,
+                "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": 50838016 if dom["bytes"] == 50724864 else None,
+                "timing": "CUDA events on the launching stream around 320 back-to-back launches (10 sweeps over the 32 layers' matrices, 1.6 GB per sweep)",
                 "bytes_per_launch": dom["bytes"], "us_per_launch": dom["us"], "kernels": kb}
 
     if rank == 0:
