@@ -287,7 +287,7 @@ def main():
                 "ms_per_step": ms_dev / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "int8 block dots, f32 accumulate", "data": "synthetic",
                 "config": {"workload": WORKLOAD, "parallelism": f"tp{world}", "l2": "weights 3.7 GB per step, far larger than the 126 MB L2",
-                           "pdl": not args.no_pdl, "cuda_graph": (not args.no_graph) and world == 1},
+                           "pdl": not args.no_pdl, "cuda_graph": not args.no_graph},
                 "hbm_gbs_per_gpu": bytes_per_token * tok_s / 1e9, "hbm_frac_of_peak": bytes_per_token * tok_s / 1e9 / peak,
                 "hbm_peak_gbs": peak, "bytes_per_token_per_gpu": bytes_per_token,
                 "e2e": {"value": steps / (ms_e2e / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": int(info.n_vocab) * 4,

@@ -535,7 +535,7 @@ spyb_status spyb_model_decode(spyb_model *m, int32_t first_token, int32_t n_past
     SPYB_CUDA(be, cudaMemcpyAsync(m->d_tokens_in, m->h_tok_pinned, 4, cudaMemcpyHostToDevice, be->stream));
     SPYB_CUDA(be, launch_embed(m->d_tokens_in, 1, m->embd, m->embd_type, m->info.d_model, m->x, be->stream));
 
-    const bool use_graph = be->config.use_graph != 0 && m->info.tp_size == 1;
+    const bool use_graph = be->config.use_graph != 0 && (m->info.tp_size == 1 || std::getenv("SPYB_TP_NO_GRAPH") == nullptr);   // the all-reduces of the prompt pass have warmed NCCL up before the capture
     int64_t per_step = 0;
     if (use_graph && m->graph_exec == nullptr) {
         // one decode step captured once; positions and the token live in device memory, so the

@@ -1,0 +1,55 @@
+"""Worker of the tensor-parallel GPU check (launched by tests/test_gpu_tp.py through torch.distributed.run):
+every rank holds one shard of a small LLaMa-shaped model, rank 0 also holds the whole model, and the
+tensor-parallel logits are compared with the single-GPU ones. Partial sums are all-reduced, so the f32
+summation order differs from the single-GPU (= CPU) order by construction: the gate is the stated tolerance
+(max-abs 2e-2, rel 1e-2) and identical greedy ids, not identical bits."""
+import os
+import sys
+
+import numpy as np
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    import torch
+    import torch.distributed as dist
+    from spy_b200 import backend as B
+    from spy_b200 import gguf_io
+
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dist.init_process_group(backend="gloo", rank=rank, world_size=world)
+    torch.cuda.set_device(local)
+    path = sys.argv[1]
+    cfg = gguf_io.LlamaConfig(n_layer=3, d_model=512, n_head=4, n_ff=1024, n_vocab=512, weight_std=0.05)
+    if rank == 0:
+        gguf_io.make_llama_gguf(path, cfg, seed=5)
+    dist.barrier()
+    prompt = np.random.default_rng(3).integers(3, cfg.n_vocab, size=9)
+
+    be = B.B200Backend(local, tp_size=world, tp_rank=rank)
+    m = B.LlamaModel(be, path, n_ctx=64)
+    uid = [B.nccl_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(uid, src=0)
+    m.init_tp(uid[0])
+    ids, logits = m.generate(prompt, 12)
+    ok = True
+    if rank == 0:
+        b1 = B.B200Backend(local)
+        m1 = B.LlamaModel(b1, path, n_ctx=64)
+        ids1, logits1 = m1.generate(prompt, 12)
+        err = float(np.abs(logits - logits1).max())
+        rel = err / float(np.abs(logits1).max())
+        ok = bool(np.array_equal(ids, ids1)) and err <= 2e-2 and rel <= 1e-2
+        print(f"TP{world} vs TP1: max|dlogit| = {err:.3e} (rel {rel:.3e}), ids identical = {np.array_equal(ids, ids1)} -> {'OK' if ok else 'FAIL'}", flush=True)
+        m1.close(); b1.close()
+    m.close(); be.close()
+    flag = torch.tensor([0 if ok else 1])
+    dist.all_reduce(flag)
+    dist.destroy_process_group()
+    sys.exit(int(flag.item() != 0))
+
+
+if __name__ == "__main__":
+    main()
