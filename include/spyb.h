@@ -108,7 +108,7 @@ int32_t spyb_is_support(int32_t op_type);
 
 /* ---- ModelLoader::load for a Constant tensor (storage/include/loader/simple_loader.h:57-70):
  * copies the tensor's raw blocks to the device once and returns the device pointer that
- * stands in for the loader's host span. Repeated calls with the same name return the same pointer. */
+ * stands in for the loader's host span. Repeated calls with the same name, host span and size return the same pointer. */
 void *spyb_upload_constant(spyb_backend *backend, const char *name, const void *host_ptr, uint64_t bytes,
                            int32_t number_type, const int64_t elements[4]);
 

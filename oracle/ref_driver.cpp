@@ -44,6 +44,26 @@ std::mutex g_mutex;
 std::map<int, std::unique_ptr<Backend>> g_backends;
 bool g_logger_ready = false;
 
+#ifdef SPY_BACKEND_CUDA
+/// the sm_100a backend behind the reference's own factory hook ("gpu:b200"); a fresh instance per call, so that
+/// the constants of one model file never outlive its mapping
+std::unique_ptr<Backend> g_device_backend;
+Backend *device_backend() {
+	std::lock_guard<std::mutex> guard(g_mutex);
+	if (!g_logger_ready) {
+		LogParam log_param;
+		log_param.log_level = "error";
+		init_logger_format(log_param);
+		g_logger_ready = true;
+	}
+	BackendFactory factory;
+	ConfigTable config;
+	g_device_backend.reset();
+	g_device_backend = factory.init_backend("gpu:b200", config);
+	return g_device_backend.get();
+}
+#endif
+
 Backend *backend_for(int num_thread) {
 	std::lock_guard<std::mutex> guard(g_mutex);
 	if (!g_logger_ready) {
@@ -251,9 +271,17 @@ int spy_ref_run_op(int op_type, int num_in, const spy_ref_tensor *in, spy_ref_te
 ///   out_logits [n_predict * n_vocab]  last-token logits per step (may be null)
 ///   step_ms    [n_predict]            wall time of distributor->execute() per step (may be null)
 /// Returns the vocabulary size, or a negative value on failure.
+/// num_thread < 0 selects the device backend (only in the build with -DSPY_BACKEND_CUDA, which links the adapter
+/// spy_b200/adapter/b200_backend.cpp and libspyb200.so): the reference's graph builder, scheduler, loader and sampler
+/// then run unchanged on top of spy::gpu::B200Backend.
 int spy_ref_generate(const char *gguf_path, const int32_t *prompt, int n_prompt, int n_predict, int num_context,
 		int num_thread, int warmup, int32_t *out_ids, float *out_logits, double *step_ms) {
+#ifdef SPY_BACKEND_CUDA
+	Backend *backend = (num_thread < 0) ? device_backend() : backend_for(num_thread);
+#else
+	if (num_thread < 0) { return -2; }
 	Backend *backend = backend_for(num_thread);
+#endif
 
 	std::unique_ptr<ModelLoader> loader = ModelLoaderFactory::build_model_loader("simple", gguf_path);
 	std::unique_ptr<Model> model = ModelBuilder::build_model(loader->context, default_hyper_param(num_context));

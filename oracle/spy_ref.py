@@ -13,6 +13,9 @@ import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "_ref", "libspy_ref.so")
+# the same reference sources with the sm_100a backend registered through the reference's device-backend hook
+# (adapter spy_b200/adapter/b200_backend.cpp): the reference's graph / scheduler / loader driving libspyb200.so
+LIB_B200_PATH = os.path.join(_HERE, "_ref", "libspy_ref_b200.so")
 
 # OperatorType numbering (orchestration/include/operator/type.h:38-52)
 OP = dict(Input=0, Nop=1, Dup=2, Copy=3, View=4, Reshape=5, MaskedCopy=6, MaskedSelect=7, GetRow=8,
@@ -114,9 +117,27 @@ def run_op(op: str, inputs: list, out_buf: np.ndarray, param: OpParam | None = N
     return out
 
 
+_lib_b200 = None
+
+
+def b200_available() -> bool:
+    return os.path.exists(LIB_B200_PATH)
+
+
+def lib_b200():
+    global _lib_b200
+    if _lib_b200 is None:
+        l = C.CDLL(LIB_B200_PATH)
+        l.spy_ref_generate.argtypes = [C.c_char_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                       C.c_void_p, C.c_void_p, C.c_void_p]
+        _lib_b200 = l
+    return _lib_b200
+
+
 def generate(gguf_path: str, prompt, n_predict: int, n_ctx: int = 512, threads: int = 8, warmup: bool = False,
-             want_logits: bool = True, n_vocab: int | None = None):
-    """Returns (ids [n_predict], logits [n_predict, n_vocab] or None, step_ms [n_predict])."""
+             want_logits: bool = True, n_vocab: int | None = None, device_backend: bool = False):
+    """Returns (ids [n_predict], logits [n_predict, n_vocab] or None, step_ms [n_predict]).
+    device_backend=True runs the reference's token loop on its "gpu:b200" backend (the adapter over libspyb200.so)."""
     prompt = np.ascontiguousarray(prompt, dtype=np.int32)
     ids = np.zeros(n_predict, dtype=np.int32)
     ms = np.zeros(n_predict, dtype=np.float64)
@@ -125,8 +146,9 @@ def generate(gguf_path: str, prompt, n_predict: int, n_ctx: int = 512, threads: 
         if n_vocab is None:
             raise ValueError("n_vocab is required to size the logits buffer")
         logits = np.zeros((n_predict, n_vocab), dtype=np.float32)
-    v = lib().spy_ref_generate(gguf_path.encode(), _ptr(prompt), len(prompt), n_predict, n_ctx, threads, int(warmup),
-                               _ptr(ids), _ptr(logits) if logits is not None else None, _ptr(ms))
+    l = lib_b200() if device_backend else lib()
+    v = l.spy_ref_generate(gguf_path.encode(), _ptr(prompt), len(prompt), n_predict, n_ctx, -1 if device_backend else threads, int(warmup),
+                           _ptr(ids), _ptr(logits) if logits is not None else None, _ptr(ms))
     if v < 0:
         raise RuntimeError("spy_ref_generate failed")
     return ids, logits, ms

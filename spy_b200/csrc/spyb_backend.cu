@@ -266,7 +266,10 @@ void *spyb_upload_constant(spyb_backend *be, const char *name, const void *host_
                            const int64_t elements[4]) {
     cudaSetDevice(be->config.device_id);
     std::lock_guard<std::mutex> g(be->const_mutex);
-    auto it = be->constants.find(name);
+    // a constant is identified by its name together with the host span it came from: another model loaded later under
+    // the same tensor names (a different mapping or size) is uploaded afresh
+    const std::string key = std::string(name) + "@" + std::to_string(reinterpret_cast<uintptr_t>(host_ptr)) + "+" + std::to_string(bytes);
+    auto it = be->constants.find(key);
     if (it != be->constants.end()) { return it->second; }
     void *raw = nullptr;
     if (cudaMalloc(&raw, bytes + 64) != cudaSuccess) { be->set_error("cudaMalloc(%llu) failed for constant %s", (unsigned long long)bytes, name); return nullptr; }
@@ -284,7 +287,7 @@ void *spyb_upload_constant(spyb_backend *be, const char *name, const void *host_
             be->retiled[raw] = m;
         }
     }
-    be->constants[name] = raw;
+    be->constants[key] = raw;
     return raw;
 }
 
