@@ -85,7 +85,31 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
     float *sc = qf + ATT_HD;                     // [n_pad] scores, then probabilities
     float *gs = sc + n_pad;                      // [n_pad / 4] four-wide partial sums of std::reduce
 
-    if (tid < ATT_HD) { qf[tid] = __half2float(p.q[(int64_t)t * p.dl + (int64_t)h * ATT_HD + tid]); }
+    // Everything this thread will need from global memory is requested up front, so that Q, the first K row and
+    // the V^T values of the PV product share one memory round trip instead of three: the PV thread pair of element
+    // e = tid / 2 fetches the first 32-position step and the (at most 32-position) scalar tail of its row now.
+    const int n_main = ((n_tot - 1) / 32) * 32;
+    const int pv_e = tid >> 1, pv_half = tid & 1;
+    const __half *vrow = p.v_cache + ((int64_t)h * ATT_HD + pv_e) * p.n_ctx;
+    uint2 v_first[4], v_tail[8];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        const int j = 8 * a + 4 * pv_half;
+        v_first[a] = (0 < n_main && j < n_vis) ? *reinterpret_cast<const uint2 *>(vrow + j) : make_uint2(0u, 0u);
+    }
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+        const int j = n_main + 4 * c;
+        v_tail[c] = (j < n_vis) ? *reinterpret_cast<const uint2 *>(vrow + j) : make_uint2(0u, 0u);
+    }
+    const __half q_mine = (tid < ATT_HD) ? p.q[(int64_t)t * p.dl + (int64_t)h * ATT_HD + tid] : __float2half(0.f);
+    uint4 kv[16];                                    // a whole K row in flight at once
+    {
+        const uint4 *krow = reinterpret_cast<const uint4 *>(p.k_cache + (int64_t)min(tid, n_vis - 1) * p.dl + (int64_t)h * ATT_HD);
+#pragma unroll
+        for (int a = 0; a < 16; ++a) { kv[a] = krow[a]; }
+    }
+    if (tid < ATT_HD) { qf[tid] = __half2float(q_mine); }
     __syncthreads();
 
     // ---- scores of the visible positions: one thread per position
@@ -93,9 +117,10 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
         const uint4  *krow = reinterpret_cast<const uint4 *>(p.k_cache + (int64_t)j * p.dl + (int64_t)h * ATT_HD);
         const float4 *q4   = reinterpret_cast<const float4 *>(qf);
         float acc[4][8];
-        uint4 kv[16];                                // the whole K row in flight at once: one memory round trip
+        if (j != tid) {
 #pragma unroll
-        for (int a = 0; a < 16; ++a) { kv[a] = krow[a]; }
+            for (int a = 0; a < 16; ++a) { kv[a] = krow[a]; }
+        }
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
 #pragma unroll
@@ -178,9 +203,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
     // elements 4 * half .. + 3 of the four accumulators. Masked positions have probability +0 and leave every
     // accumulator unchanged, so they are skipped (their cache entries may not be written yet).
     {
-        const int e = tid >> 1, half = tid & 1;
-        const __half *vrow = p.v_cache + ((int64_t)h * ATT_HD + e) * p.n_ctx;
-        const int n_main = ((n_tot - 1) / 32) * 32;
+        const int e = pv_e, half = pv_half;
         float acc[4][4];
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
@@ -192,7 +215,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
 #pragma unroll
             for (int a = 0; a < 4; ++a) {
                 const int j = j0 + 8 * a + 4 * half;
-                vv[a] = (j < n_vis) ? *reinterpret_cast<const uint2 *>(vrow + j) : make_uint2(0u, 0u);
+                vv[a] = (j0 == 0) ? v_first[a] : ((j < n_vis) ? *reinterpret_cast<const uint2 *>(vrow + j) : make_uint2(0u, 0u));
             }
 #pragma unroll
             for (int a = 0; a < 4; ++a) {
@@ -212,26 +235,18 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
             u[k] = __fadd_rn(mine, __shfl_xor_sync(0xffffffffu, mine, 1));   // element k of one half with element k + 4 of the other
         }
         const float simd = __fadd_rn(__fadd_rn(u[0], u[1]), __fadd_rn(u[2], u[3]));
-        // scalar tail: positions n_main .. n_tot-1 (at most 32), fetched with eight 64-bit loads before the chain runs
+        // scalar tail: positions n_main .. n_tot-1 (at most 32)
         float tail = 0.f;
-        {
-            uint2 tv[8];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const int j = n_main + 4 * c;
-                tv[c] = (j < n_vis) ? *reinterpret_cast<const uint2 *>(vrow + j) : make_uint2(0u, 0u);
-            }
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                const int j = n_main + 4 * c;
-                if (j < n_vis) {
-                    const float4 pr = *reinterpret_cast<const float4 *>(sc + j);
-                    const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&tv[c].x)), v23 = __half22float2(*reinterpret_cast<const __half2 *>(&tv[c].y));
-                    tail = fmaf(v01.x, pr.x, tail);
-                    if (j + 1 < n_vis) { tail = fmaf(v01.y, pr.y, tail); }
-                    if (j + 2 < n_vis) { tail = fmaf(v23.x, pr.z, tail); }
-                    if (j + 3 < n_vis) { tail = fmaf(v23.y, pr.w, tail); }
-                }
+        for (int c = 0; c < 8; ++c) {
+            const int j = n_main + 4 * c;
+            if (j < n_vis) {
+                const float4 pr = *reinterpret_cast<const float4 *>(sc + j);
+                const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&v_tail[c].x)), v23 = __half22float2(*reinterpret_cast<const __half2 *>(&v_tail[c].y));
+                tail = fmaf(v01.x, pr.x, tail);
+                if (j + 1 < n_vis) { tail = fmaf(v01.y, pr.y, tail); }
+                if (j + 2 < n_vis) { tail = fmaf(v23.x, pr.z, tail); }
+                if (j + 3 < n_vis) { tail = fmaf(v23.y, pr.w, tail); }
             }
         }
         if (half == 0) { p.out[(int64_t)t * p.dl + (int64_t)h * ATT_HD + e] = __fadd_rn(tail, simd); }
