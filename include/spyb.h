@@ -200,9 +200,10 @@ spyb_status spyb_model_read_activation(spyb_model *model, int32_t which, void *h
 spyb_status spyb_model_tap_xq(spyb_model *model, void *blocks_host);
 
 /* Profiling aid without a reference counterpart. When the model was loaded with SPYB_TIMELINE=1 in the
- * environment, every kernel of the step plan records four device-clock stamps (ns): first CTA started,
- * predecessor finished, activations quantized, last CTA finished. Copies up to max_kernels records of
- * four stamps (layer-major: QKV, attention, attention-out, FFN up/gate, FFN down; then the head) and
+ * environment, every kernel of the step plan records eight device-clock stamps (ns): CTA 0 started,
+ * its predecessor finished, its activations quantized, last CTA finished, then the latest CTA's start,
+ * predecessor-finished and activations-quantized times, and one unused word. Copies up to max_kernels records of
+ * eight stamps (layer-major: QKV, attention, attention-out, FFN up/gate, FFN down; then the head) and
  * returns their number (0 when the timeline is off). */
 int32_t spyb_model_read_timeline(spyb_model *model, uint64_t *stamps_host, int32_t max_kernels);
 

@@ -344,9 +344,9 @@ class LlamaModel:
         return int(self._l.spyb_model_last_launches(self.h))
 
     def timeline(self) -> np.ndarray:
-        """[n_kernels, 4] device-clock stamps (ns) of the last step; empty unless loaded with SPYB_TIMELINE=1."""
+        """[n_kernels, 8] device-clock stamps (ns) of the last step; empty unless loaded with SPYB_TIMELINE=1."""
         n = 5 * self.info.n_layer + 1
-        out = np.zeros((n, 4), dtype=np.uint64)
+        out = np.zeros((n, 8), dtype=np.uint64)
         got = self._l.spyb_model_read_timeline(self.h, _np_ptr(out), n)
         return out[:got]
 

@@ -66,7 +66,8 @@ struct MatvecParams {
     // optional tap: reference-layout Q8_0 blocks of column 0 (nb * 34 bytes)
     uint8_t      *tap_xq = nullptr;
     int          *error_flag = nullptr; // set non-zero when a bounded wait on a bulk copy ran out
-    // optional profiling aid: four %globaltimer stamps (entry of CTA 0, predecessor finished, prologue done, last CTA done)
+    // optional profiling aid: eight %globaltimer stamps (CTA 0: entry, predecessor finished, prologue done; last CTA done;
+    // latest CTA: entry, predecessor finished, prologue done; unused)
     unsigned long long *stamps = nullptr;
     // weights a later kernel of the step will stream: pulled into L2 once this CTA's own loads are issued
     const void   *pf_ptr[4] = {nullptr, nullptr, nullptr, nullptr};

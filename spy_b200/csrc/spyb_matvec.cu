@@ -331,7 +331,7 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
     // Let the next kernel of the step begin, and start streaming: weights never change during a step, so the
     // copies may run ahead of the previous kernel's results.
     pdl_launch_dependents();
-    stamp(p.stamps, 0, false);
+    stamp(p.stamps, 0, false); stamp(p.stamps, 4, true);
     if (lane == 0 && n_items > 0) {
         for (int s = 0; s < NS; ++s) { mbar_init(bar_s + s * 8, 1); }
         mbar_init_fence();
@@ -340,7 +340,7 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
     }
     __syncwarp();
     pdl_wait();
-    stamp(p.stamps, 1, false);
+    stamp(p.stamps, 1, false); stamp(p.stamps, 5, true);
 
     ActPlanes act = act_planes(smem_raw, nbp, TM);
     {
@@ -356,7 +356,7 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
         }
     }
     __syncthreads();
-    stamp(p.stamps, 2, false);
+    stamp(p.stamps, 2, false); stamp(p.stamps, 6, true);
     matvec_tap(p, act);
 
     // this lane's operands, as 32-bit shared-space addresses: activation word (Q8_0 weights: word l; Q4_0: lanes 0..3
@@ -546,7 +546,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
     };
 
     pdl_launch_dependents();
-    stamp(p.stamps, 0, false);
+    stamp(p.stamps, 0, false); stamp(p.stamps, 4, true);
     if (leader && lane == 0 && n_items > 0) {
         for (int s = 0; s < NS; ++s) { mbar_init(full_s + s * 8, 1); if (NSPLIT > 1) { mbar_init(empty_s + s * 8, NSPLIT); } }
         if (NSPLIT > 1) { mbar_init(xbar_s, NSPLIT); mbar_init(xbar_s + 8, NSPLIT); }
@@ -556,7 +556,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
     }
     __syncwarp();
     pdl_wait();
-    stamp(p.stamps, 1, false);
+    stamp(p.stamps, 1, false); stamp(p.stamps, 5, true);
 
     ActPlanes act = act_planes(smem_raw, nbp, TM);
     {
@@ -572,7 +572,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
         }
     }
     __syncthreads();   // (also orders the leaders' barrier initialisation before the other warps' first wait)
-    stamp(p.stamps, 2, false);
+    stamp(p.stamps, 2, false); stamp(p.stamps, 6, true);
     matvec_tap(p, act);
 
     const uint32_t y_s   = smem_u32(act.Y);

@@ -164,7 +164,7 @@ struct spyb_model {
     int    *d_pos = nullptr;
     int32_t *d_token = nullptr, *d_tokens_in = nullptr, *d_history = nullptr;
     uint8_t *d_tap = nullptr;
-    unsigned long long *d_stamps = nullptr;   // profiling aid (SPYB_TIMELINE=1): four time stamps per kernel of a step
+    unsigned long long *d_stamps = nullptr;   // profiling aid (SPYB_TIMELINE=1): eight time stamps per kernel of a step
     int    *h_pos_pinned = nullptr; int32_t *h_tok_pinned = nullptr; float *h_logits_pinned = nullptr;
     void   *nccl_comm = nullptr;
     cudaGraphExec_t graph_exec = nullptr;
@@ -215,7 +215,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
     const int d = m->info.d_model, tp = m->info.tp_size;
     for (size_t L = 0; L < m->layers.size(); ++L) {
         Layer &ly = m->layers[L];
-        auto stamps = [&](int k) { return m->d_stamps ? m->d_stamps + 4 * (5 * L + k) : nullptr; };
+        auto stamps = [&](int k) { return m->d_stamps ? m->d_stamps + 8 * (5 * L + k) : nullptr; };
         {   // 1: norm + quantize -> QKV -> rope + KV append
             MatvecParams p;
             p.A = ly.wqkv; p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.attn_norm; p.eps = m->info.rms_eps;
@@ -276,7 +276,7 @@ spyb_status run_head(spyb_model *m, int col, int64_t *launches) {
     MatvecParams p;
     p.A = m->head; p.T = 1; p.pro = PRO_NORM_QUANT; p.x = m->x + (int64_t)col * m->info.d_model; p.x_stride = m->info.d_model;
     p.norm_w = m->output_norm; p.eps = m->info.rms_eps; p.epi = EPI_STORE; p.out = m->logits; p.out_stride = m->info.n_vocab;
-    p.stamps = m->d_stamps ? m->d_stamps + 4 * (5 * m->layers.size()) : nullptr;
+    p.stamps = m->d_stamps ? m->d_stamps + 8 * (5 * m->layers.size()) : nullptr;
     SPYB_CUDA(m->be, launch_matvec(p, m->be->launch_cfg(m->be->config.use_pdl != 0))); ++*launches;
     return SPYB_SUCCESS;
 }
@@ -439,7 +439,7 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
               dev_alloc(m, &m->d_pos, 4) == SPYB_SUCCESS && dev_alloc(m, &m->d_token, 4) == SPYB_SUCCESS &&
               dev_alloc(m, &m->d_tokens_in, TMAX) == SPYB_SUCCESS && dev_alloc(m, &m->d_history, (size_t)I.n_ctx + 8) == SPYB_SUCCESS &&
               dev_alloc(m, &m->d_tap, (size_t)d / 32 * 34) == SPYB_SUCCESS &&
-              (std::getenv("SPYB_TIMELINE") == nullptr || dev_alloc(m, &m->d_stamps, (size_t)(5 * I.n_layer + 1) * 4) == SPYB_SUCCESS);
+              (std::getenv("SPYB_TIMELINE") == nullptr || dev_alloc(m, &m->d_stamps, (size_t)(5 * I.n_layer + 1) * 8) == SPYB_SUCCESS);
     if (!ok) { return fail(SPYB_FAIL); }
     if (cudaMallocHost(reinterpret_cast<void **>(&m->h_pos_pinned), 64) != cudaSuccess ||
         cudaMallocHost(reinterpret_cast<void **>(&m->h_tok_pinned), 64) != cudaSuccess ||
@@ -651,7 +651,7 @@ spyb_status spyb_model_read_activation(spyb_model *m, int32_t which, void *host,
 int32_t spyb_model_read_timeline(spyb_model *m, uint64_t *stamps_host, int32_t max_kernels) {
     if (m == nullptr || m->d_stamps == nullptr || stamps_host == nullptr) { return 0; }
     const int n = std::min<int>(max_kernels, 5 * (int)m->layers.size() + 1);
-    if (cudaMemcpy(stamps_host, m->d_stamps, (size_t)n * 4 * sizeof(uint64_t), cudaMemcpyDeviceToHost) != cudaSuccess) { return 0; }
+    if (cudaMemcpy(stamps_host, m->d_stamps, (size_t)n * 8 * sizeof(uint64_t), cudaMemcpyDeviceToHost) != cudaSuccess) { return 0; }
     return n;
 }
 

@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     pdl_launch_dependents();
-    stamp(p.stamps, 0, false);
+    stamp(p.stamps, 0, false); stamp(p.stamps, 4, true);
     {   // weights of a later kernel of the step: towards L2 while attention occupies only a few SMs
         const int64_t gw = ((int64_t)blockIdx.y * gridDim.x + blockIdx.x) * ATT_THREADS + tid, gn = (int64_t)gridDim.x * gridDim.y * ATT_THREADS;
 #pragma unroll
@@ -71,7 +71,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
         }
     }
     pdl_wait();
-    stamp(p.stamps, 1, false);
+    stamp(p.stamps, 1, false); stamp(p.stamps, 5, true);
 
     const int pos   = p.pos_base[0] + t;
     const int n_vis = pos + 1;                   // causal mask: positions 0..pos are visible
