@@ -386,6 +386,16 @@ spyb_status run_matmul(spyb_backend *be, spyb_op_desc *d, void *out_dev) {
         SPYB_CUDA(be, launch_matmul_f16(to_strided(w, w.data), to_strided(x, x.data), to_strided(d->output, out_dev), be->stream));
         return SPYB_SUCCESS;
     }
+    if (w.number_type == SPYB_Q4_K || w.number_type == SPYB_Q6_K) {
+        // layout-only types in the reference: decoded weights times f32 activations (tolerance-level parity)
+        if (!tensor_contiguous(w) || !tensor_contiguous(x) || w.elements[2] != 1 || w.elements[3] != 1 || w.elements[0] % 256 != 0 || w.elements[0] != x.elements[0]) {
+            be->set_error("MatMul: K-quant weights need contiguous 2-D operands with K a multiple of 256");
+            return SPYB_UNSUPPORTED;
+        }
+        SPYB_CUDA(be, launch_matmul_kquant(w.number_type, static_cast<const uint8_t *>(w.data), w.elements[1], w.elements[0], static_cast<const float *>(x.data),
+                                           x.elements[1] * x.elements[2] * x.elements[3], static_cast<float *>(out_dev), be->stream));
+        return SPYB_SUCCESS;
+    }
     if (w.number_type != SPYB_Q4_0 && w.number_type != SPYB_Q8_0) {
         be->set_error("MatMul: weight type %d is not implemented", w.number_type);
         return SPYB_UNSUPPORTED;

@@ -130,6 +130,8 @@ cudaError_t launch_rope(const Strided &x, const float2 *cos_sin, const Strided &
 cudaError_t launch_copy_strided(const Strided &src, int src_type, const Strided &dst, int dst_type, cudaStream_t s);
 cudaError_t launch_getrow(const uint8_t *table, int table_type, int64_t row_bytes, int64_t ne0, const int32_t *ids, int64_t n_ids, float *out, cudaStream_t s);
 cudaError_t launch_matmul_f16(const Strided &w /*f16*/, const Strided &x /*f32*/, const Strided &out /*f32*/, cudaStream_t s);
+// K-quant weights (raw GGUF rows: Q4_K = 12, Q6_K = 14) times f32 activations [n_cols][k] -> out [n_cols][n_rows]
+cudaError_t launch_matmul_kquant(int type, const uint8_t *w, int64_t n_rows, int64_t k, const float *x, int64_t n_cols, float *out, cudaStream_t s);
 cudaError_t launch_argmax_embed(const float *logits, int64_t n_vocab, int32_t *token_out, int32_t *history, int *pos_counter,
                                 const uint8_t *embd, int embd_type, int64_t d_model, float *x_out, const LaunchCfg &cfg);
 cudaError_t launch_embed(const int32_t *ids, int n_ids, const uint8_t *embd, int embd_type, int64_t d_model, float *x_out, cudaStream_t s);

@@ -7,6 +7,8 @@
 // follows the CPU's order: the 4 x 8 accumulators and the scalar tail of Dot<FP16,FP16>, the four-wide
 // grouping of std::reduce / std::transform_reduce, and the fixed horizontal-add trees.
 
+#include <algorithm>
+
 #include "spyb_common.cuh"
 #include "spyb_kernels.h"
 
@@ -371,6 +373,84 @@ cudaError_t launch_block_dots(int wtype, const uint8_t *w_row, const uint8_t *x_
     const int64_t nblk = n / QK;
     if (nblk == 0) { return cudaSuccess; }
     block_dots_kernel<<<(unsigned)((nblk + 127) / 128), 128, 0, s>>>(wtype, w_row, x_blocks, nblk, out);
+    return launch_check();
+}
+
+// =============================================================================================
+// K-quant weights (Q4_K: 144 B / 256 elements, Q6_K: 210 B / 256 elements; layouts
+// orchestration/include/number/number_impl/k-quant.h:79-117, 162-188). The reference defines only the block layouts
+// and has no compute for them, so there is nothing to be bit-identical to: the kernel multiplies the decoded weights
+// with the f32 activations (the reference's MatMul semantics without an activation quantizer) and is checked against
+// a numpy decode within the stated tolerance. One warp per output row and column; a lane decodes 8 consecutive
+// elements of every 256-element super-block, so a warp reads each 144 / 210-byte block once, contiguously.
+// HBM-bound: rows * K/256 * 144 (210) bytes per launch; activations stay in L2.
+__device__ __forceinline__ void kq_scale_min_k4(const uint8_t *sc12, int j, float &sc, float &mn) {
+    if (j < 4) { sc = (float)(sc12[j] & 63); mn = (float)(sc12[4 + j] & 63); }
+    else { sc = (float)((sc12[4 + j] & 0xF) | ((sc12[j - 4] >> 6) << 4)); mn = (float)((sc12[4 + j] >> 4) | ((sc12[j] >> 6) << 4)); }
+}
+
+template <int TYPE>   // 12: Q4_K, 14: Q6_K
+__global__ void __launch_bounds__(256) matmul_kquant_kernel(const uint8_t *w, int64_t row_bytes, const float *x, float *out, int64_t n_rows,
+                                                            int64_t k, int64_t n_cols) {
+    const int     lane = threadIdx.x & 31;
+    const int64_t gw = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5, nw = ((int64_t)gridDim.x * blockDim.x) >> 5;
+    const int64_t nsb = k >> 8;
+    for (int64_t item = gw; item < n_rows * n_cols; item += nw) {
+        const int64_t  row = item % n_rows, col = item / n_rows;
+        const uint8_t *wr = w + row * row_bytes;
+        const float   *xc = x + col * k;
+        float acc = 0.f;
+        for (int64_t b = 0; b < nsb; ++b) {
+            const float4 x0 = *reinterpret_cast<const float4 *>(xc + b * 256 + lane * 8), x1 = *reinterpret_cast<const float4 *>(xc + b * 256 + lane * 8 + 4);
+            const float  xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            if (TYPE == 12) {
+                const uint8_t *blk = wr + b * 144;
+                const float d = h2f((uint16_t)(blk[0] | (blk[1] << 8))), dmin = h2f((uint16_t)(blk[2] | (blk[3] << 8)));
+                // elements 8*lane .. 8*lane+7 lie in sub-block j = lane / 4; 64-element group g = j / 2 keeps its first 32
+                // elements in the low nibbles and the next 32 in the high nibbles of bytes 32g .. 32g+31
+                const int j = lane >> 2, g = j >> 1, hi = j & 1, off = (lane & 3) * 8;
+                float sc, mn; kq_scale_min_k4(blk + 4, j, sc, mn);
+                const uint2 q = *reinterpret_cast<const uint2 *>(blk + 16 + 32 * g + off);
+                const float dl = __fmul_rn(d, sc), ml = __fmul_rn(dmin, mn);
+                float part = 0.f, xs = 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const uint32_t byte = ((e < 4 ? q.x : q.y) >> (8 * (e & 3))) & 0xff;
+                    part = fmaf((float)(hi ? (byte >> 4) : (byte & 0xF)), xv[e], part);
+                    xs += xv[e];
+                }
+                acc += dl * part - ml * xs;
+            } else {
+                const uint8_t *blk = wr + b * 210;
+                const float d = h2f((uint16_t)(blk[208] | (blk[209] << 8)));
+                // element i = 8*lane + e: half h = i / 128, quarter qq = (i % 128) / 32, l = i % 32; six bits =
+                // nibble of ql[64h + 32(qq & 1) + l] (low for qq < 2, high else) | two bits (2*qq) of qh[32h + l]
+                const int i0 = lane * 8, h = i0 >> 7, qq = (i0 & 127) >> 5, l0 = i0 & 31;
+                const uint8_t *ql = blk + 64 * h + 32 * (qq & 1) + l0;   // 210-byte blocks: only 2-byte alignment holds, byte loads
+                const uint8_t *qh = blk + 128 + 32 * h + l0;
+                const float sc = (float)(int8_t)blk[192 + (i0 >> 4)];
+                float part = 0.f;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const uint32_t byte = ql[e];
+                    const int      six  = (int)((qq < 2 ? (byte & 0xF) : (byte >> 4)) | (((qh[e] >> (2 * qq)) & 3) << 4)) - 32;
+                    part = fmaf((float)six, xv[e], part);
+                }
+                acc += __fmul_rn(d, sc) * part;
+            }
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) { out[col * n_rows + row] = acc; }
+    }
+}
+
+cudaError_t launch_matmul_kquant(int type, const uint8_t *w, int64_t n_rows, int64_t k, const float *x, int64_t n_cols, float *out, cudaStream_t s) {
+    if ((type != 12 && type != 14) || k % 256 != 0) { return cudaErrorInvalidValue; }
+    if (n_rows == 0 || n_cols == 0) { return cudaSuccess; }
+    const int64_t warps = n_rows * n_cols;
+    const unsigned grid = (unsigned)std::min<int64_t>((warps + 7) / 8, 148 * 8);
+    if (type == 12) { matmul_kquant_kernel<12><<<grid, 256, 0, s>>>(w, k / 256 * 144, x, out, n_rows, k, n_cols); }
+    else            { matmul_kquant_kernel<14><<<grid, 256, 0, s>>>(w, k / 256 * 210, x, out, n_rows, k, n_cols); }
     return launch_check();
 }
 

@@ -176,10 +176,25 @@ def _mm(be, pw, qt, n, k, x):
     return got
 
 
+@pytest.mark.parametrize("qt", [quants.Q4_K, quants.Q6_K])
+@pytest.mark.parametrize("n,k,t", [(64, 256, 1), (132, 1024, 3), (4096, 4096, 1), (11008, 4096, 4), (4096, 11008 // 256 * 256, 16)])
+def test_matmul_k_quants_within_tolerance(be, qt, n, k, t):
+    """Q4_K / Q6_K: the reference only defines the block layouts (no compute), so parity is unpinned: the kernel is
+    compared with decoded weights (numpy) times the f32 activations in float64, gate max-abs 2e-2 / rel 1e-2."""
+    rng = np.random.default_rng(n + k + t)
+    w = quants.quantize((rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)), qt)
+    x = rng.standard_normal((t, k)).astype(np.float32)
+    got = _mm(be, be.upload(w), qt, n, k, x)
+    want = x.astype(np.float64) @ quants.dequantize(w, qt).astype(np.float64).T
+    err = float(np.abs(got - want).max())
+    print(f"type {qt} {n}x{k} t={t}: max |d| = {err:.3e}, max |y| = {np.abs(want).max():.3e}")
+    assert err <= 2e-2 and err <= 1e-2 * float(np.abs(want).max())
+
+
 def test_matmul_unsupported_weight_type_is_reported(be):
     d = B.OpDesc(); d.op_type, d.num_input = B.OP["MatMul"], 2
     p = be.alloc_memory(144 * 4)
-    d.input[0] = B.make_tensor(p, B.Q4_K, (256, 4)); d.input[1] = B.make_tensor(p, B.FP32, (256, 1)); d.output = B.make_tensor(p, B.FP32, (4, 1))
+    d.input[0] = B.make_tensor(p, 3, (256, 4), (20, 160, 640, 640)); d.input[1] = B.make_tensor(p, B.FP32, (256, 1)); d.output = B.make_tensor(p, B.FP32, (4, 1))   # type 3 = Q4_1: no kernel
     with pytest.raises(B.SpybError) as e:
         be.submit(d)
     assert e.value.status == B.UNSUPPORTED
