@@ -210,6 +210,10 @@ def main():
         uid = [B.nccl_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(uid, src=0)
         model.init_tp(uid[0])
+        if os.environ.get("SPYB_TP_NCCL_ONLY") is None:   # decode steps exchange through peer memory inside the kernels
+            handles = [None] * world
+            dist.all_gather_object(handles, model.tp_export())
+            model.tp_import(handles)
     info = model.info
     prompt = prompt_ids(info.n_vocab)
     if args.profile_kernel >= 0:
@@ -286,7 +290,7 @@ def main():
         line = {"metric": "decode tokens/s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
                 "ms_per_step": ms_dev / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "int8 block dots, f32 accumulate", "data": "synthetic",
-                "config": {"workload": WORKLOAD, "parallelism": f"tp{world}", "l2": "weights 3.7 GB per step, far larger than the 126 MB L2",
+                "config": {"workload": WORKLOAD, "parallelism": f"tp{world}", "tp_exchange": None if world == 1 else ("nccl" if os.environ.get("SPYB_TP_NCCL_ONLY") else "fused peer-memory (decode), nccl (prompt)"), "l2": "weights 3.7 GB per step, far larger than the 126 MB L2",
                            "pdl": not args.no_pdl, "cuda_graph": not args.no_graph},
                 "hbm_gbs_per_gpu": bytes_per_token * tok_s / 1e9, "hbm_frac_of_peak": bytes_per_token * tok_s / 1e9 / peak,
                 "hbm_peak_gbs": peak, "bytes_per_token_per_gpu": bytes_per_token,

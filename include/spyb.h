@@ -168,6 +168,14 @@ spyb_status spyb_model_info_get(const spyb_model *model, spyb_model_info *info);
 spyb_status spyb_nccl_unique_id(void *unique_id_128);
 spyb_status spyb_model_init_tp(spyb_model *model, const void *unique_id_128);
 
+/* Tensor parallel, optional: exchange of the per-layer partial sums through peer memory inside the mat-vec kernels
+ * (plain peer stores and flag words, bounded waits) instead of an NCCL all-reduce, for single-token steps. No reference
+ * counterpart (the reference has no multi-device path). Every rank calls spyb_model_tp_export (a 64-byte CUDA IPC handle
+ * of its exchange buffer), the handles are gathered over the caller's channel in rank order, and every rank calls
+ * spyb_model_tp_import with the tp_size * 64 bytes. Without these calls the NCCL path is used throughout. */
+spyb_status spyb_model_tp_export(spyb_model *model, void *handle_64);
+spyb_status spyb_model_tp_import(spyb_model *model, const void *handles);
+
 /* One distributor->execute() (backend/distributor/include/distributor/simple_distributor.h:47-78)
  * for `n_tokens` host token ids at positions n_past..n_past+n_tokens-1: host ids in, the last
  * token's n_vocab logits out to host memory (as model_io.logits, app/cli/include/cli.h:103-105). */

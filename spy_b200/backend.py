@@ -104,6 +104,8 @@ def lib():
         "spyb_model_last_ms": (C.c_float, [vp]),
         "spyb_model_last_launches": (i64, [vp]),
         "spyb_model_tap_xq": (i32, [vp, vp]),
+        "spyb_model_tp_export": (i32, [vp, vp]),
+        "spyb_model_tp_import": (i32, [vp, vp]),
         "spyb_model_read_timeline": (i32, [vp, vp, i32]),
     }
     for name, (res, args) in sig.items():
@@ -342,6 +344,17 @@ class LlamaModel:
     @property
     def last_launches(self) -> int:
         return int(self._l.spyb_model_last_launches(self.h))
+
+    def tp_export(self) -> bytes:
+        """64-byte IPC handle of this rank's exchange buffer (fused tensor-parallel exchange)."""
+        buf = C.create_string_buffer(64)
+        self.backend._check(self._l.spyb_model_tp_export(self.h, buf))
+        return buf.raw
+
+    def tp_import(self, handles) -> None:
+        """handles: the tp_export() results of all ranks, in rank order."""
+        blob = b"".join(handles)
+        self.backend._check(self._l.spyb_model_tp_import(self.h, C.c_char_p(blob)))
 
     def timeline(self) -> np.ndarray:
         """[n_kernels, 8] device-clock stamps (ns) of the last step; empty unless loaded with SPYB_TIMELINE=1."""

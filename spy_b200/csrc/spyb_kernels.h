@@ -35,7 +35,8 @@ inline int    record_row_bytes(int type) { return (type == 8 ? 256 : 128) + 16; 
 inline size_t matrix_bytes(int type, int64_t n_rows, int nb) { return (size_t)n_rows * (padded_blocks(nb) / 8) * record_row_bytes(type); }
 
 enum Prologue { PRO_QUANT = 0, PRO_NORM_QUANT = 1 };
-enum Epilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_SILU_MUL = 2, EPI_QKV_ROPE = 3 };
+enum Epilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_SILU_MUL = 2, EPI_QKV_ROPE = 3, EPI_TP_SCATTER = 4 };
+constexpr int TP_MAX = 8;
 
 struct MatvecParams {
     DevMatrix A;
@@ -69,6 +70,19 @@ struct MatvecParams {
     // optional profiling aid: eight %globaltimer stamps (CTA 0: entry, predecessor finished, prologue done; last CTA done;
     // latest CTA: entry, predecessor finished, prologue done; unused)
     unsigned long long *stamps = nullptr;
+    // Tensor-parallel exchange fused into the kernels (single column only), over peer memory mapped from the other ranks:
+    //   EPI_TP_SCATTER: every output (on rank 0 plus the residual) is stored into slot `tp_rank` of EVERY rank's exchange
+    //   buffer (tp_out[r], plain peer stores); the last CTA to finish then publishes *tp_epoch into every rank's flag word.
+    //   A consumer (tp_in != nullptr) waits - bounded - until all tp_n flags of its site show *tp_epoch, reads its
+    //   activations as the sum of the tp_n slots in rank order, and CTA 0 writes that sum to tp_x_out (the residual stream).
+    int             tp_n = 0, tp_rank = 0;
+    float          *tp_out[TP_MAX] = {};          // producer: slot `tp_rank` of the site in each rank's buffer ([k] floats)
+    unsigned       *tp_flag_out[TP_MAX] = {};     // producer: flag word `tp_rank` of the site in each rank's buffer
+    unsigned       *tp_counter = nullptr;         // producer: local CTA counter of the site (self-resetting)
+    const float    *tp_in = nullptr;              // consumer: local slots of the site, [tp_n][k]
+    const unsigned *tp_flag_in = nullptr;         // consumer: local flag words of the site, [tp_n]
+    float          *tp_x_out = nullptr;           // consumer: where CTA 0 leaves the reduced vector
+    const int      *tp_epoch = nullptr;           // device word: the step's exchange epoch
     // weights a later kernel of the step will stream: pulled into L2 once this CTA's own loads are issued
     const void   *pf_ptr[4] = {nullptr, nullptr, nullptr, nullptr};
     size_t        pf_bytes[4] = {0, 0, 0, 0};

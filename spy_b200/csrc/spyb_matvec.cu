@@ -86,10 +86,37 @@ __device__ __forceinline__ void matvec_prologue_1col(const MatvecParams &p, ActP
     const int npass = (n4p + MV_THREADS - 1) / MV_THREADS;     // <= PG
     const float4 *x4 = reinterpret_cast<const float4 *>(p.x);
     float4 xv[PG];
+    if (p.tp_in != nullptr) {
+        // tensor-parallel input: wait (bounded) until every rank has published this step's partial vector, then add the
+        // slots in rank order; CTA 0 also leaves the sum in the residual stream
+        if (tid < p.tp_n) {
+            const unsigned want = (unsigned)*p.tp_epoch;
+            const uint64_t t0 = global_timer_ns();
+            while (ld_acquire_sys(p.tp_flag_in + tid) != want) {
+                if (global_timer_ns() - t0 > WAIT_LIMIT_NS) { if (p.error_flag != nullptr) { atomicExch(p.error_flag, 2); } break; }
+            }
+        }
+        __syncthreads();
 #pragma unroll
-    for (int k = 0; k < PG; ++k) {
-        const int g = tid + k * MV_THREADS;
-        xv[k] = (k < npass && g < n4) ? x4[g] : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < PG; ++k) {
+            const int g = tid + k * MV_THREADS;
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k < npass && g < n4) {
+                a = __ldcg(reinterpret_cast<const float4 *>(p.tp_in) + g);
+                for (int rk = 1; rk < p.tp_n; ++rk) {
+                    const float4 b = __ldcg(reinterpret_cast<const float4 *>(p.tp_in + (size_t)rk * p.A.k) + g);
+                    a.x = __fadd_rn(a.x, b.x); a.y = __fadd_rn(a.y, b.y); a.z = __fadd_rn(a.z, b.z); a.w = __fadd_rn(a.w, b.w);
+                }
+                if (blockIdx.x == 0 && p.tp_x_out != nullptr) { reinterpret_cast<float4 *>(p.tp_x_out)[g] = a; }
+            }
+            xv[k] = a;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < PG; ++k) {
+            const int g = tid + k * MV_THREADS;
+            xv[k] = (k < npass && g < n4) ? x4[g] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
     }
     if (NORM) {
         const float4 *w4 = reinterpret_cast<const float4 *>(p.norm_w);
@@ -245,6 +272,11 @@ __device__ __forceinline__ void matvec_epilogue(const MatvecParams &p, int64_t r
         break;
     case EPI_RESID:   // Add(attn_out, x) / Add(ffn_inp, ffn_out): model/src/llm/model/llama.cpp:194-211
         if (writer) { const int64_t i = (int64_t)t * p.out_stride + row; p.out[i] = __fadd_rn(v, p.resid[i]); }
+        break;
+    case EPI_TP_SCATTER:   // partial sum of a tensor-parallel shard: into this rank's slot on every rank
+        if (writer) {
+            p.tp_out[p.tp_rank][row] = (p.resid != nullptr) ? __fadd_rn(v, p.resid[row]) : v;   // local slot; the last CTA forwards it
+        }
         break;
     case EPI_QKV_ROPE: {
         if (!writer) { break; }
@@ -463,6 +495,32 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
         }
     }
 
+    if (p.tp_counter != nullptr) {
+        // tensor-parallel producer: the CTA that finishes last forwards this rank's partial vector (now complete in the
+        // local slot) to the same slot on every other rank with wide peer stores, then publishes the epoch to every rank
+        __shared__ int tp_last;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            tp_last = (atomicAdd(p.tp_counter, 1u) == gridDim.x - 1) ? 1 : 0;
+            if (tp_last) { *p.tp_counter = 0; __threadfence(); }
+        }
+        __syncthreads();
+        if (tp_last) {
+            const float4 *src = reinterpret_cast<const float4 *>(p.tp_out[p.tp_rank]);
+            const int     n4  = (int)(p.A.n_rows >> 2);
+            for (int i = threadIdx.x; i < n4; i += MV_THREADS) {
+                const float4 v = __ldcg(src + i);
+                for (int rk = 0; rk < p.tp_n; ++rk) { if (rk != p.tp_rank) { reinterpret_cast<float4 *>(p.tp_out[rk])[i] = v; } }
+            }
+            __syncthreads();   // the CTA's peer stores happen-before thread 0's system-scope fence (cumulativity)
+            if (threadIdx.x == 0) {
+                const unsigned epoch = (unsigned)*p.tp_epoch;
+                __threadfence_system();
+                for (int rk = 0; rk < p.tp_n; ++rk) { *reinterpret_cast<volatile unsigned *>(p.tp_flag_out[rk]) = epoch; }
+            }
+        }
+    }
     if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
     // weights a later kernel will stream: towards L2 while this kernel drains
     {
@@ -699,6 +757,32 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
             }
         }
     }
+    if (p.tp_counter != nullptr) {
+        // tensor-parallel producer: the CTA that finishes last forwards this rank's partial vector (now complete in the
+        // local slot) to the same slot on every other rank with wide peer stores, then publishes the epoch to every rank
+        __shared__ int tp_last;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            tp_last = (atomicAdd(p.tp_counter, 1u) == gridDim.x - 1) ? 1 : 0;
+            if (tp_last) { *p.tp_counter = 0; __threadfence(); }
+        }
+        __syncthreads();
+        if (tp_last) {
+            const float4 *src = reinterpret_cast<const float4 *>(p.tp_out[p.tp_rank]);
+            const int     n4  = (int)(p.A.n_rows >> 2);
+            for (int i = threadIdx.x; i < n4; i += MV_THREADS) {
+                const float4 v = __ldcg(src + i);
+                for (int rk = 0; rk < p.tp_n; ++rk) { if (rk != p.tp_rank) { reinterpret_cast<float4 *>(p.tp_out[rk])[i] = v; } }
+            }
+            __syncthreads();   // the CTA's peer stores happen-before thread 0's system-scope fence (cumulativity)
+            if (threadIdx.x == 0) {
+                const unsigned epoch = (unsigned)*p.tp_epoch;
+                __threadfence_system();
+                for (int rk = 0; rk < p.tp_n; ++rk) { *reinterpret_cast<volatile unsigned *>(p.tp_flag_out[rk]) = epoch; }
+            }
+        }
+    }
     if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
 }
 
@@ -831,6 +915,7 @@ static cudaError_t launch_matvec_w(const MatvecParams &p, const LaunchCfg &cfg) 
 
 cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg) {
     if (p.T < 1 || p.T > matvec_max_columns(p.A.nb)) { return cudaErrorInvalidValue; }
+    if ((p.epi == EPI_TP_SCATTER || p.tp_in != nullptr) && (p.T != 1 || p.tp_n < 2 || p.tp_n > TP_MAX || p.tp_epoch == nullptr || p.A.nbp * 8 > PRO_GROUPS * MV_THREADS)) { return cudaErrorInvalidValue; }
     if (p.A.k % QK != 0 || p.A.nb < 1 || p.A.nbp != padded_blocks(p.A.nb) || p.A.w == nullptr) { return cudaErrorInvalidValue; }
     if (p.A.tile_rows == 32) {
         if ((p.A.n_rows & 31) || p.pair_mode || (p.epi == EPI_SILU_MUL) != (p.A.fused_pair != 0)) { return cudaErrorInvalidValue; }

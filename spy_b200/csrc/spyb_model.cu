@@ -167,6 +167,12 @@ struct spyb_model {
     unsigned long long *d_stamps = nullptr;   // profiling aid (SPYB_TIMELINE=1): eight time stamps per kernel of a step
     int    *h_pos_pinned = nullptr; int32_t *h_tok_pinned = nullptr; float *h_logits_pinned = nullptr;
     void   *nccl_comm = nullptr;
+    // fused exchange over peer memory (single-column steps): [2 n_layer sites][tp slots][d] floats, then [sites][tp] flag words,
+    // then [sites] CTA counters; tp_peer[r] = rank r's buffer as mapped into this process (tp_peer[tp_rank] = the local one)
+    uint8_t *tp_local = nullptr;
+    uint8_t *tp_peer[TP_MAX] = {};
+    bool     tp_ready = false;
+    int      epoch = 0;
     cudaGraphExec_t graph_exec = nullptr;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float   last_ms = 0.f;
@@ -196,6 +202,34 @@ spyb_status allreduce(spyb_model *m, float *buf, size_t count, int64_t *launches
     return SPYB_SUCCESS;
 }
 
+size_t tp_buffer_bytes(const spyb_model *m) {
+    const size_t sites = 2 * m->layers.size(), n = m->info.tp_size;
+    return sites * n * m->info.d_model * 4 + sites * n * 4 + sites * 4 + 256;
+}
+float *tp_slot(const spyb_model *m, uint8_t *base, size_t site, int slot) {
+    return reinterpret_cast<float *>(base) + (site * m->info.tp_size + slot) * (size_t)m->info.d_model;
+}
+unsigned *tp_flag(const spyb_model *m, uint8_t *base, size_t site, int slot) {
+    const size_t sites = 2 * m->layers.size(), n = m->info.tp_size;
+    return reinterpret_cast<unsigned *>(base + sites * n * m->info.d_model * 4) + site * n + slot;
+}
+unsigned *tp_counter(const spyb_model *m, size_t site) {
+    const size_t sites = 2 * m->layers.size(), n = m->info.tp_size;
+    return reinterpret_cast<unsigned *>(m->tp_local + sites * n * m->info.d_model * 4) + sites * n + site;
+}
+// producer side of exchange site `site`: scatter into slot tp_rank of every rank, rank 0 adds the residual
+void tp_produce(spyb_model *m, MatvecParams &p, size_t site) {
+    p.epi = EPI_TP_SCATTER; p.tp_n = m->info.tp_size; p.tp_rank = m->info.tp_rank;
+    p.resid = (m->info.tp_rank == 0) ? m->x : nullptr; p.out = nullptr;
+    for (int r = 0; r < m->info.tp_size; ++r) { p.tp_out[r] = tp_slot(m, m->tp_peer[r], site, m->info.tp_rank); p.tp_flag_out[r] = tp_flag(m, m->tp_peer[r], site, m->info.tp_rank); }
+    p.tp_counter = tp_counter(m, site); p.tp_epoch = m->d_pos + 2;
+}
+// consumer side: activations = sum of the site's slots, left in the residual stream by CTA 0
+void tp_consume(spyb_model *m, MatvecParams &p, size_t site) {
+    p.tp_n = m->info.tp_size; p.tp_rank = m->info.tp_rank;
+    p.tp_in = tp_slot(m, m->tp_local, site, 0); p.tp_flag_in = tp_flag(m, m->tp_local, site, 0); p.tp_x_out = m->x; p.tp_epoch = m->d_pos + 2;
+}
+
 // planes of the matrices a later kernel of the step streams (at most two matrices)
 template <class P>
 void prefetch_next(spyb_model *m, P &p, const DevMatrix *a, const DevMatrix *b = nullptr) {
@@ -213,6 +247,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
     const bool pdl = be->config.use_pdl != 0;
     const LaunchCfg cfg = be->launch_cfg(pdl);
     const int d = m->info.d_model, tp = m->info.tp_size;
+    const bool fused = tp > 1 && T == 1 && m->tp_ready;   // single-column steps exchange through peer memory inside the kernels
     for (size_t L = 0; L < m->layers.size(); ++L) {
         Layer &ly = m->layers[L];
         auto stamps = [&](int k) { return m->d_stamps ? m->d_stamps + 8 * (5 * L + k) : nullptr; };
@@ -223,6 +258,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache; p.n_ctx = m->info.n_ctx;
             p.tap_xq = (tap && L == 0) ? m->d_tap : nullptr;
             prefetch_next(m, p, &ly.wo); p.stamps = stamps(0);
+            if (fused && L > 0) { tp_consume(m, p, 2 * (L - 1) + 1); }
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
         }
         {   // 2: attention
@@ -239,10 +275,11 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             p.A = ly.wo; p.T = T; p.pro = PRO_QUANT; p.x = m->att; p.x_stride = m->dl;
             p.resid = m->x; p.out_stride = d;
             if (tp == 1) { p.epi = EPI_RESID; p.out = m->x; }
+            else if (fused) { tp_produce(m, p, 2 * L); }
             else { p.epi = (m->info.tp_rank == 0) ? EPI_RESID : EPI_STORE; p.out = m->partial; }
             prefetch_next(m, p, &ly.down); p.stamps = stamps(2);
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
-            if (tp > 1) {
+            if (tp > 1 && !fused) {
                 if (allreduce(m, m->partial, (size_t)T * d, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
                 std::swap(m->x, m->partial);
             }
@@ -253,6 +290,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
             p.eps = m->info.rms_eps; p.epi = EPI_SILU_MUL; p.out = m->act; p.out_stride = m->fl; p.silu_table = be->d_silu_table;
             prefetch_next(m, p, L + 1 < m->layers.size() ? &m->layers[L + 1].wqkv : &m->head); p.stamps = stamps(3);
+            if (fused) { tp_consume(m, p, 2 * L); }
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
         }
         {   // 5: quantize -> Wdown -> + residual
@@ -260,9 +298,10 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             p.A = ly.down; p.T = T; p.pro = PRO_QUANT; p.x = m->act; p.x_stride = m->fl;
             p.resid = m->x; p.out_stride = d; p.stamps = stamps(4);
             if (tp == 1) { p.epi = EPI_RESID; p.out = m->x; }
+            else if (fused) { tp_produce(m, p, 2 * L + 1); }
             else { p.epi = (m->info.tp_rank == 0) ? EPI_RESID : EPI_STORE; p.out = m->partial; }
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
-            if (tp > 1) {
+            if (tp > 1 && !fused) {
                 if (allreduce(m, m->partial, (size_t)T * d, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
                 std::swap(m->x, m->partial);
             }
@@ -272,18 +311,19 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
 }
 
 // output norm + head on column `col` of x -> logits[n_vocab]
-spyb_status run_head(spyb_model *m, int col, int64_t *launches) {
+spyb_status run_head(spyb_model *m, int col, int64_t *launches, bool fused_input = false) {
     MatvecParams p;
     p.A = m->head; p.T = 1; p.pro = PRO_NORM_QUANT; p.x = m->x + (int64_t)col * m->info.d_model; p.x_stride = m->info.d_model;
     p.norm_w = m->output_norm; p.eps = m->info.rms_eps; p.epi = EPI_STORE; p.out = m->logits; p.out_stride = m->info.n_vocab;
     p.stamps = m->d_stamps ? m->d_stamps + 8 * (5 * m->layers.size()) : nullptr;
+    if (fused_input) { tp_consume(m, p, 2 * m->layers.size() - 1); }
     SPYB_CUDA(m->be, launch_matvec(p, m->be->launch_cfg(m->be->config.use_pdl != 0))); ++*launches;
     return SPYB_SUCCESS;
 }
 
 spyb_status run_decode_step(spyb_model *m, int64_t *launches) {
     if (run_layers(m, 1, false, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
-    if (run_head(m, 0, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
+    if (run_head(m, 0, launches, m->info.tp_size > 1 && m->tp_ready) != SPYB_SUCCESS) { return SPYB_FAIL; }
     SPYB_CUDA(m->be, launch_argmax_embed(m->logits, m->info.n_vocab, m->d_token, m->d_history, m->d_pos, m->embd, m->embd_type,
                                          m->info.d_model, m->x, m->be->launch_cfg(m->be->config.use_pdl != 0)));
     ++*launches;
@@ -489,6 +529,42 @@ spyb_status spyb_model_init_tp(spyb_model *m, const void *unique_id_128) {
     return SPYB_SUCCESS;
 }
 
+spyb_status spyb_model_tp_export(spyb_model *m, void *handle_64) {
+    if (m == nullptr || handle_64 == nullptr) { return SPYB_FAIL; }
+    spyb_backend *be = m->be;
+    if (m->info.tp_size < 2 || m->info.tp_size > TP_MAX) { be->set_error("tp_export: tp_size %d", m->info.tp_size); return SPYB_FAIL; }
+    cudaSetDevice(be->config.device_id);
+    if (m->tp_local == nullptr) {
+        void *raw = nullptr;
+        SPYB_CUDA(be, cudaMalloc(&raw, tp_buffer_bytes(m)));          // plain cudaMalloc: the allocation is exported to the other ranks
+        SPYB_CUDA(be, cudaMemset(raw, 0, tp_buffer_bytes(m)));
+        SPYB_CUDA(be, cudaDeviceSynchronize());
+        m->owned.push_back(raw);
+        m->tp_local = static_cast<uint8_t *>(raw);
+    }
+    cudaIpcMemHandle_t h;
+    SPYB_CUDA(be, cudaIpcGetMemHandle(&h, m->tp_local));
+    static_assert(sizeof(h) == 64, "IPC handle size");
+    std::memcpy(handle_64, &h, 64);
+    return SPYB_SUCCESS;
+}
+
+spyb_status spyb_model_tp_import(spyb_model *m, const void *handles) {
+    if (m == nullptr || handles == nullptr || m->tp_local == nullptr) { return SPYB_FAIL; }
+    spyb_backend *be = m->be;
+    cudaSetDevice(be->config.device_id);
+    for (int r = 0; r < m->info.tp_size; ++r) {
+        if (r == m->info.tp_rank) { m->tp_peer[r] = m->tp_local; continue; }
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, static_cast<const uint8_t *>(handles) + 64 * r, 64);
+        void *ptr = nullptr;
+        SPYB_CUDA(be, cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        m->tp_peer[r] = static_cast<uint8_t *>(ptr);
+    }
+    m->tp_ready = true;
+    return SPYB_SUCCESS;
+}
+
 spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_tokens, int32_t n_past, float *logits_host) {
     if (m == nullptr || tokens == nullptr || n_tokens < 1) { return SPYB_FAIL; }
     spyb_backend *be = m->be;
@@ -503,13 +579,14 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
         SPYB_CUDA(be, cudaStreamSynchronize(be->stream));   // pinned staging words are reused per pass
         m->h_pos_pinned[0] = n_past + t0;
         m->h_pos_pinned[1] = n_past + n_tokens;   // the step's score rows span every position known to the step
+        m->h_pos_pinned[2] = ++m->epoch;          // exchange epoch of this pass (tensor parallel)
         std::memcpy(m->h_tok_pinned, tokens + t0, (size_t)T * 4);
-        SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 8, cudaMemcpyHostToDevice, be->stream));
+        SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 12, cudaMemcpyHostToDevice, be->stream));
         SPYB_CUDA(be, cudaMemcpyAsync(m->d_tokens_in, m->h_tok_pinned, (size_t)T * 4, cudaMemcpyHostToDevice, be->stream));
         SPYB_CUDA(be, launch_embed(m->d_tokens_in, T, m->embd, m->embd_type, m->info.d_model, m->x, be->stream)); ++launches;
         if (run_layers(m, T, t0 == 0, &launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
         if (t0 + T == n_tokens) {
-            if (run_head(m, T - 1, &launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
+            if (run_head(m, T - 1, &launches, m->info.tp_size > 1 && m->tp_ready && T == 1) != SPYB_SUCCESS) { return SPYB_FAIL; }
             if (logits_host != nullptr) {
                 SPYB_CUDA(be, cudaMemcpyAsync(m->h_logits_pinned, m->logits, (size_t)m->info.n_vocab * 4, cudaMemcpyDeviceToHost, be->stream));
             }
@@ -531,7 +608,9 @@ spyb_status spyb_model_decode(spyb_model *m, int32_t first_token, int32_t n_past
     if (n_past < 0 || n_past + n_steps > m->info.n_ctx) { be->set_error("decode would exceed the context length (%d + %d > %d)", n_past, n_steps, m->info.n_ctx); return SPYB_FAIL; }
     if (first_token < 0 || first_token >= m->info.n_vocab) { be->set_error("token id %d out of range", first_token); return SPYB_FAIL; }
     m->h_pos_pinned[0] = n_past; m->h_pos_pinned[1] = 0; *m->h_tok_pinned = first_token;   // [1] = 0: rows end at the token itself
-    SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 8, cudaMemcpyHostToDevice, be->stream));
+    m->h_pos_pinned[2] = ++m->epoch;   // the argmax kernel advances the device copy once per step
+    m->epoch += n_steps - 1;
+    SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 12, cudaMemcpyHostToDevice, be->stream));
     SPYB_CUDA(be, cudaMemcpyAsync(m->d_tokens_in, m->h_tok_pinned, 4, cudaMemcpyHostToDevice, be->stream));
     SPYB_CUDA(be, launch_embed(m->d_tokens_in, 1, m->embd, m->embd_type, m->info.d_model, m->x, be->stream));
 

@@ -726,6 +726,7 @@ __global__ void __launch_bounds__(1024) argmax_embed_kernel(const float *logits,
             const int step_pos = *pos_counter;
             if (history != nullptr) { history[step_pos] = idx; }
             *pos_counter = step_pos + 1;
+            pos_counter[2] += 1;   // exchange epoch of the next step (tensor parallel)
         }
     }
     __syncthreads();

@@ -33,6 +33,10 @@ def main():
     uid = [B.nccl_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(uid, src=0)
     m.init_tp(uid[0])
+    if os.environ.get("SPYB_TP_NCCL_ONLY") is None:   # single-token steps exchange through peer memory inside the kernels
+        handles = [None] * world
+        dist.all_gather_object(handles, m.tp_export())
+        m.tp_import(handles)
     ids, logits = m.generate(prompt, 12)
     ok = True
     if rank == 0:
