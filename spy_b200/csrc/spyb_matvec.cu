@@ -77,7 +77,7 @@ size_t matvec_smem_bytes(int nb, int T) { return matvec_smem_layout(padded_block
 // Single column, K <= 12288: every thread keeps its (at most PG) float4 groups of x in registers from the one
 // global read through the sum of squares to the quantizer; same arithmetic as the general prologue below.
 constexpr int PRO_GROUPS = 6;
-template <int PG, bool NORM>
+template <int PG, bool NORM, bool TPIN>
 __device__ __forceinline__ void matvec_prologue_1col(const MatvecParams &p, ActPlanes act, float *v3, float *scales) {
     const int tid = threadIdx.x;
     const int nbp = p.A.nbp;
@@ -86,7 +86,7 @@ __device__ __forceinline__ void matvec_prologue_1col(const MatvecParams &p, ActP
     const int npass = (n4p + MV_THREADS - 1) / MV_THREADS;     // <= PG
     const float4 *x4 = reinterpret_cast<const float4 *>(p.x);
     float4 xv[PG];
-    if (p.tp_in != nullptr) {
+    if (TPIN) {
         // tensor-parallel input: wait (bounded) until every rank has published this step's partial vector, then add the
         // slots in rank order; CTA 0 also leaves the sum in the residual stream
         if (tid < p.tp_n) {
@@ -304,7 +304,7 @@ __device__ __forceinline__ void matvec_epilogue_silu(const MatvecParams &p, int6
 }
 
 // ---------------------------------------------------------------------------------------------
-template <int WT, int TM, int R>
+template <int WT, int TM, int R, bool TPIN>
 __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(const MatvecParams p, const int ring_bytes, const int S, const int wact) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ float norm_scales[8];
@@ -380,9 +380,9 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
         const int  n4p  = nbp * 8;
         const bool norm = p.pro == PRO_NORM_QUANT;
         if (TM == 1 && n4p <= 2 * MV_THREADS) {
-            if (norm) { matvec_prologue_1col<2, true>(p, act, v3, norm_scales); } else { matvec_prologue_1col<2, false>(p, act, v3, norm_scales); }
+            if (norm) { matvec_prologue_1col<2, true, TPIN>(p, act, v3, norm_scales); } else { matvec_prologue_1col<2, false, TPIN>(p, act, v3, norm_scales); }
         } else if (TM == 1 && n4p <= PRO_GROUPS * MV_THREADS) {
-            if (norm) { matvec_prologue_1col<PRO_GROUPS, true>(p, act, v3, norm_scales); } else { matvec_prologue_1col<PRO_GROUPS, false>(p, act, v3, norm_scales); }
+            if (norm) { matvec_prologue_1col<PRO_GROUPS, true, TPIN>(p, act, v3, norm_scales); } else { matvec_prologue_1col<PRO_GROUPS, false, TPIN>(p, act, v3, norm_scales); }
         } else {
             matvec_prologue<TM>(p, act, v3, norm_scales);
         }
@@ -549,7 +549,7 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
 // A record is [32 rows][2 groups x 64 B (Q4_0) or 128 B (Q8_0) | 8 fp16 scales]; the 144-byte (272-byte) row pitch
 // makes the per-lane 128-bit reads conflict-free.
 // With fused_pair, rows 0..15 of every tile are FFN-up rows 16u..16u+15 and rows 16..31 the FFN-gate rows.
-template <int WT, int TM, int NSPLIT>
+template <int WT, int TM, int NSPLIT, bool TPIN>
 __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const MatvecParams p, const int ring_bytes, const int S, const int wact) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ float norm_scales[8];
@@ -622,9 +622,9 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
         const int  n4p  = nbp * 8;
         const bool norm = p.pro == PRO_NORM_QUANT;
         if (TM == 1 && n4p <= 2 * MV_THREADS) {
-            if (norm) { matvec_prologue_1col<2, true>(p, act, v3, norm_scales); } else { matvec_prologue_1col<2, false>(p, act, v3, norm_scales); }
+            if (norm) { matvec_prologue_1col<2, true, TPIN>(p, act, v3, norm_scales); } else { matvec_prologue_1col<2, false, TPIN>(p, act, v3, norm_scales); }
         } else if (TM == 1 && n4p <= PRO_GROUPS * MV_THREADS) {
-            if (norm) { matvec_prologue_1col<PRO_GROUPS, true>(p, act, v3, norm_scales); } else { matvec_prologue_1col<PRO_GROUPS, false>(p, act, v3, norm_scales); }
+            if (norm) { matvec_prologue_1col<PRO_GROUPS, true, TPIN>(p, act, v3, norm_scales); } else { matvec_prologue_1col<PRO_GROUPS, false, TPIN>(p, act, v3, norm_scales); }
         } else {
             matvec_prologue<TM>(p, act, v3, norm_scales);
         }
@@ -786,7 +786,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
     if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
 }
 
-template <int WT, int TM, int NSPLIT>
+template <int WT, int TM, int NSPLIT, bool TPIN = false>
 static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &cfg) {
     constexpr int RECB = 32 * (((WT == 8) ? 256 : 128) + 16);
     constexpr int GROUPS = MV_WARPS / NSPLIT;
@@ -814,7 +814,7 @@ static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &
     const size_t smem = fixed.total + ring;
     static size_t smem_allowed = 48 * 1024;
     if (smem > smem_allowed) {
-        cudaError_t err = cudaFuncSetAttribute(matvec_rows_kernel<WT, TM, NSPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t err = cudaFuncSetAttribute(matvec_rows_kernel<WT, TM, NSPLIT, TPIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) { return err; }
         smem_allowed = smem;
     }
@@ -826,7 +826,7 @@ static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&lc, matvec_rows_kernel<WT, TM, NSPLIT>, q, (int)ring, S, wact);
+    return cudaLaunchKernelEx(&lc, matvec_rows_kernel<WT, TM, NSPLIT, TPIN>, q, (int)ring, S, wact);
 }
 
 template <int WT>
@@ -835,11 +835,11 @@ static cudaError_t launch_matvec_rows_w(const MatvecParams &p, const LaunchCfg &
     const int64_t tiles_per_sm = ((p.A.n_rows >> 5) + cfg.num_sms - 1) / cfg.num_sms;
     const bool split = cfg.mv_rows_split == 1 ? tiles_per_sm <= 3 : (cfg.mv_rows_split == 2 && tiles_per_sm <= MV_WARPS / 4 + 2);
     if (split) {
-        if (p.T <= 1) { return launch_matvec_rows_t<WT, 1, 4>(p, cfg); }
+        if (p.T <= 1) { return p.tp_in ? launch_matvec_rows_t<WT, 1, 4, true>(p, cfg) : launch_matvec_rows_t<WT, 1, 4>(p, cfg); }
         if (p.T <= 2) { return launch_matvec_rows_t<WT, 2, 4>(p, cfg); }
         return launch_matvec_rows_t<WT, 4, 4>(p, cfg);
     }
-    if (p.T <= 1) { return launch_matvec_rows_t<WT, 1, 1>(p, cfg); }
+    if (p.T <= 1) { return p.tp_in ? launch_matvec_rows_t<WT, 1, 1, true>(p, cfg) : launch_matvec_rows_t<WT, 1, 1>(p, cfg); }
     if (p.T <= 2) { return launch_matvec_rows_t<WT, 2, 1>(p, cfg); }
     return launch_matvec_rows_t<WT, 4, 1>(p, cfg);
 }
@@ -849,7 +849,7 @@ int matvec_max_columns(int nb) {   // (the lane-per-row kernel keeps 8 accumulat
     return 1;
 }
 
-template <int WT, int TM, int R>
+template <int WT, int TM, int R, bool TPIN = false>
 static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) {
     constexpr int RECB = 4 * (((WT == 8) ? 256 : 128) + 16);
     // every SM gets CTAs even when there are fewer units than warps: a unit is a sequential walk along K, so
@@ -889,7 +889,7 @@ static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) 
 
     static size_t smem_allowed = 48 * 1024;   // one process drives one device, so one high-water mark per kernel suffices
     if (smem > smem_allowed) {
-        cudaError_t err = cudaFuncSetAttribute(matvec_kernel<WT, TM, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t err = cudaFuncSetAttribute(matvec_kernel<WT, TM, R, TPIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) { return err; }
         smem_allowed = smem;
     }
@@ -902,12 +902,12 @@ static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&lc, matvec_kernel<WT, TM, R>, q, (int)ring, S, wact);
+    return cudaLaunchKernelEx(&lc, matvec_kernel<WT, TM, R, TPIN>, q, (int)ring, S, wact);
 }
 
 template <int WT, int R>
 static cudaError_t launch_matvec_w(const MatvecParams &p, const LaunchCfg &cfg) {
-    if (p.T <= 1) { return launch_matvec_t<WT, 1, R>(p, cfg); }
+    if (p.T <= 1) { return p.tp_in ? launch_matvec_t<WT, 1, R, true>(p, cfg) : launch_matvec_t<WT, 1, R>(p, cfg); }
     if (p.T <= 2) { return launch_matvec_t<WT, 2, R>(p, cfg); }
     if (p.T <= 4) { return launch_matvec_t<WT, 4, R>(p, cfg); }
     return launch_matvec_t<WT, 8, R>(p, cfg);
