@@ -147,6 +147,33 @@ spyb_status spyb_read_tables(spyb_backend *backend, float *silu_host, float *exp
 spyb_status spyb_attention(spyb_backend *backend, const void *q_f16, const void *k_cache_f16, const void *v_cache_t_f16, float *out,
                            int32_t pos0, int32_t n_tokens, int32_t n_total, int32_t n_head, int32_t head_dim, int32_t n_ctx);
 
+/* MatMul of quantized weights in the reference's row layout (Q4_0 / Q8_0 blocks, [n_rows][k], device memory) with f32
+ * activations x [n_cols][k], out [n_cols][n_rows] - the same arithmetic and bits as a MatMul submitted through spyb_submit -
+ * for callers that may not allocate. No reference counterpart: the reference's CPU MatMul takes its scratch from the
+ * scheduler's allocator.
+ *
+ * Who needs it: a caller that replays its own CUDA graph or runs inside a stream capture (cudaMalloc and cudaFree are
+ * illegal there and would invalidate the capture), or a serving loop that has handed all device memory to its own pool
+ * and must not see the allocator's latency or failure in the token loop. spyb_submit re-tiles weights that were not
+ * registered with spyb_upload_constant into a temporary buffer taken from the backend's arena (which falls back to
+ * cudaMalloc when the arena is full); this entry point re-tiles into a fixed scratch array that is part of the library
+ * image instead and calls no allocating routine at all.
+ *
+ * Limits and rules:
+ *  - the re-tiled matrix (n_rows * ceil8(k/32) * 18 or 34 bytes) must fit SPYB_NOALLOC_SCRATCH_BYTES (32 MiB: every
+ *    matrix of a 7B layer; the 32000 x 4096 head does not fit) - larger requests are rejected with SPYB_UNSUPPORTED;
+ *    n_rows must be a multiple of 4 and k a multiple of 32;
+ *  - the first call on a device looks the scratch array's address up and raises the kernels' shared-memory limit for
+ *    the given shape: make one call per shape before a stream capture begins, later calls only enqueue kernels on the
+ *    backend's stream (they do not synchronise; use spyb_sync);
+ *  - there is ONE scratch array per device and process: calls are safe one after the other on the backend's stream
+ *    (stream order keeps a call's kernels ahead of the next call's re-tiling); two backends on the same device, or any
+ *    other concurrent use, would race on it. Nothing needs clearing between calls: a call writes every byte it later
+ *    reads, padding included. */
+#define SPYB_NOALLOC_SCRATCH_BYTES (32u << 20)
+spyb_status spyb_matmul_noalloc(spyb_backend *backend, int32_t weight_type, const void *w_rows_dev, int64_t n_rows, int64_t k,
+                                const float *x_dev, int64_t n_cols, float *out_dev);
+
 /* ---- whole-model path: the graph LLAMAModel::build_graph emits (model/src/llm/model/llama.cpp:86-264)
  * executed as a fixed plan of fused kernels. */
 typedef struct {

@@ -104,6 +104,7 @@ def lib():
         "spyb_model_last_ms": (C.c_float, [vp]),
         "spyb_model_last_launches": (i64, [vp]),
         "spyb_model_tap_xq": (i32, [vp, vp]),
+        "spyb_matmul_noalloc": (i32, [vp, i32, vp, i64, i64, vp, i64, vp]),
         "spyb_model_tp_export": (i32, [vp, vp]),
         "spyb_model_tp_import": (i32, [vp, vp]),
         "spyb_model_read_timeline": (i32, [vp, vp, i32]),
@@ -263,6 +264,10 @@ class B200Backend:
         silu = np.empty(65536, dtype=np.float32); ex = np.empty(65536, dtype=np.float32)
         self._check(self._l.spyb_read_tables(self.h, _np_ptr(silu), _np_ptr(ex)))
         return silu, ex
+
+    def matmul_noalloc(self, weight_type: int, w_dev: int, n_rows: int, k: int, x_dev: int, n_cols: int, out_dev: int) -> None:
+        """MatMul of raw-layout quantized rows (device pointers throughout) that allocates nothing; enqueues only (use sync())."""
+        self._check(self._l.spyb_matmul_noalloc(self.h, weight_type, w_dev, n_rows, k, x_dev, n_cols, out_dev))
 
     def attention(self, q16: np.ndarray, k_cache16: np.ndarray, v_cache_t16: np.ndarray, pos0: int, n_head: int, head_dim: int, n_ctx: int,
                   n_total: int = 0) -> np.ndarray:

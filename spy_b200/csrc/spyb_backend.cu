@@ -346,6 +346,45 @@ spyb_status spyb_attention(spyb_backend *be, const void *q_f16, const void *k_ca
     return SPYB_SUCCESS;
 }
 
+// ------------------------------------------------------------------------------------------ MatMul without allocation
+// Scratch for the re-tiled weights of spyb_matmul_noalloc: part of the library image, one per device and process.
+static __device__ __align__(256) uint8_t g_noalloc_scratch[SPYB_NOALLOC_SCRATCH_BYTES];
+
+spyb_status spyb_matmul_noalloc(spyb_backend *be, int32_t weight_type, const void *w_rows_dev, int64_t n_rows, int64_t k,
+                                const float *x_dev, int64_t n_cols, float *out_dev) {
+    if (be == nullptr) { return SPYB_FAIL; }
+    if (weight_type != SPYB_Q4_0 && weight_type != SPYB_Q8_0) { be->set_error("matmul_noalloc: weight type %d", weight_type); return SPYB_UNSUPPORTED; }
+    if (w_rows_dev == nullptr || x_dev == nullptr || out_dev == nullptr || n_rows < 4 || (n_rows & 3) || k < QK || k % QK != 0 || n_cols < 1) {
+        be->set_error("matmul_noalloc: needs n_rows a multiple of 4, k a multiple of 32, at least one column"); return SPYB_UNSUPPORTED;
+    }
+    const int nb = (int)(k / QK);
+    if (matrix_bytes(weight_type, n_rows, nb) > SPYB_NOALLOC_SCRATCH_BYTES) {
+        be->set_error("matmul_noalloc: the re-tiled matrix (%llu bytes) exceeds the %u-byte scratch array", (unsigned long long)matrix_bytes(weight_type, n_rows, nb),
+                      (unsigned)SPYB_NOALLOC_SCRATCH_BYTES);
+        return SPYB_UNSUPPORTED;
+    }
+    cudaSetDevice(be->config.device_id);
+    if (be->noalloc_scratch == nullptr) {   // once per device: address of the image's scratch array
+        void *ptr = nullptr;
+        SPYB_CUDA(be, cudaGetSymbolAddress(&ptr, g_noalloc_scratch));
+        if (ptr == nullptr) { be->set_error("matmul_noalloc: no address for the scratch array"); return SPYB_FAIL; }
+        be->noalloc_scratch = static_cast<uint8_t *>(ptr);
+    }
+    DevMatrix m;
+    m.type = weight_type; m.n_rows = n_rows; m.nb = nb; m.nbp = padded_blocks(nb); m.k = k; m.tile_rows = 4; m.w = be->noalloc_scratch;
+    const int64_t bb = weight_type == SPYB_Q4_0 ? 18 : 34;
+    SPYB_CUDA(be, launch_retile(weight_type, static_cast<const uint8_t *>(w_rows_dev), nb * bb, n_rows, nb, be->noalloc_scratch, 4, 0, 0, 0, 0, be->stream));
+    const int64_t tmax = matvec_max_columns(nb);
+    for (int64_t t0 = 0; t0 < n_cols; t0 += tmax) {
+        MatvecParams p;
+        p.A = m; p.T = (int)std::min<int64_t>(tmax, n_cols - t0);
+        p.pro = PRO_QUANT; p.x = x_dev + t0 * k; p.x_stride = k;
+        p.epi = EPI_STORE; p.out = out_dev + t0 * n_rows; p.out_stride = n_rows;
+        SPYB_CUDA(be, launch_matvec(p, be->launch_cfg(false)));
+    }
+    return SPYB_SUCCESS;
+}
+
 // ------------------------------------------------------------------------------------------ submit
 namespace {
 

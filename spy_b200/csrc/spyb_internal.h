@@ -62,6 +62,7 @@ struct spyb_backend {
     spyb::Arena  arena;
     int         *h_error_flag = nullptr;   // mapped pinned word the kernels set when a bounded wait runs out
     int         *d_error_flag = nullptr;   // its device address
+    uint8_t     *noalloc_scratch = nullptr; // device address of the scratch array of spyb_matmul_noalloc (looked up once)
     float       *d_silu_table = nullptr;   // 65536 entries: xh / (1 + expf(-xh)) for the fp16 value xh
     float       *d_exp_table = nullptr;    // 65536 entries: expf(xh)
 
