@@ -135,8 +135,16 @@ __device__ __forceinline__ void matvec_prologue_1col(const MatvecParams &p, ActP
             const float4 *g4 = reinterpret_cast<const float4 *>(v3);
             float sum = 0.f;
             int g = 0;
-            for (; g + 16 <= n4; g += 16) {   // four 128-bit reads ahead of their 16 dependent adds
-                const float4 q0 = g4[(g >> 2)], q1 = g4[(g >> 2) + 1], q2 = g4[(g >> 2) + 2], q3 = g4[(g >> 2) + 3];
+            if (n4 >= 16) {   // the 128-bit reads run one step (16 values) ahead of the dependent adds
+                float4 q0 = g4[0], q1 = g4[1], q2 = g4[2], q3 = g4[3];
+                for (g = 16; g + 16 <= n4; g += 16) {
+                    const float4 n0 = g4[(g >> 2)], n1 = g4[(g >> 2) + 1], n2 = g4[(g >> 2) + 2], n3 = g4[(g >> 2) + 3];
+                    sum = __fadd_rn(sum, q0.x); sum = __fadd_rn(sum, q0.y); sum = __fadd_rn(sum, q0.z); sum = __fadd_rn(sum, q0.w);
+                    sum = __fadd_rn(sum, q1.x); sum = __fadd_rn(sum, q1.y); sum = __fadd_rn(sum, q1.z); sum = __fadd_rn(sum, q1.w);
+                    sum = __fadd_rn(sum, q2.x); sum = __fadd_rn(sum, q2.y); sum = __fadd_rn(sum, q2.z); sum = __fadd_rn(sum, q2.w);
+                    sum = __fadd_rn(sum, q3.x); sum = __fadd_rn(sum, q3.y); sum = __fadd_rn(sum, q3.z); sum = __fadd_rn(sum, q3.w);
+                    q0 = n0; q1 = n1; q2 = n2; q3 = n3;
+                }
                 sum = __fadd_rn(sum, q0.x); sum = __fadd_rn(sum, q0.y); sum = __fadd_rn(sum, q0.z); sum = __fadd_rn(sum, q0.w);
                 sum = __fadd_rn(sum, q1.x); sum = __fadd_rn(sum, q1.y); sum = __fadd_rn(sum, q1.z); sum = __fadd_rn(sum, q1.w);
                 sum = __fadd_rn(sum, q2.x); sum = __fadd_rn(sum, q2.y); sum = __fadd_rn(sum, q2.z); sum = __fadd_rn(sum, q2.w);

@@ -352,6 +352,22 @@ def test_fused_attention_bits(be, oracle, pos0, t, n_total, spread):
     assert np.array_equal(bits(got), bits(want))
 
 
+@pytest.mark.parametrize("pos0,t,n_total,n_ctx", [(255, 1, 0, 512), (256, 2, 0, 512), (300, 1, 0, 512), (511, 1, 0, 512), (700, 2, 703, 1024), (1023, 1, 0, 1024)])
+def test_fused_attention_long_rows(be, oracle, pos0, t, n_total, n_ctx):
+    """Rows longer than the CTA (more than 256 positions: several positions per thread, many 32-position PV steps) up to
+    a full context, against the oracle."""
+    rng = np.random.default_rng(pos0 + n_ctx)
+    n_head, hd = 1, 128
+    d = n_head * hd
+    wide = lambda n: (rng.standard_normal(n) * rng.choice([0.05, 1.0, 4.0], size=n)).astype(np.float32)
+    q16 = oracle.quantize_f16(wide(t * d)).reshape(t, d)
+    k16 = oracle.quantize_f16(wide(n_ctx * d)).reshape(n_ctx, d)
+    vt16 = oracle.quantize_f16(wide(n_ctx * d)).reshape(d, n_ctx)
+    got = be.attention(q16, k16, vt16, pos0, n_head, hd, n_ctx, n_total)
+    want = _attention_oracle(oracle, q16, k16, vt16, pos0, n_head, hd, n_ctx, n_total)
+    assert np.array_equal(bits(got), bits(want))
+
+
 def test_lookup_tables_identical_for_every_key(be, oracle):
     silu, ex = be.read_tables()
     want_silu, want_exp = oracle.tables()
