@@ -174,9 +174,10 @@ struct spyb_model {
     bool     tp_ready = false;
     int      epoch = 0;
     cudaGraphExec_t graph_exec = nullptr;
+    cudaGraphExec_t graph_eval1 = nullptr;   // single-token spyb_model_eval: staging copies, embedding, layers, head, logits copy
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     float   last_ms = 0.f;
-    int64_t last_launches = 0;
+    int64_t last_launches = 0, eval1_launches = 0;
     std::vector<void *> owned;
 };
 
@@ -497,6 +498,7 @@ void spyb_model_free(spyb_model *m) {
     cudaSetDevice(m->be->config.device_id);
     cudaStreamSynchronize(m->be->stream);
     if (m->graph_exec) { cudaGraphExecDestroy(m->graph_exec); }
+    if (m->graph_eval1) { cudaGraphExecDestroy(m->graph_eval1); }
     if (m->nccl_comm && g_nccl.CommDestroy) { g_nccl.CommDestroy(m->nccl_comm); }
     for (void *p : m->owned) { cudaFree(p); }
     if (m->h_pos_pinned) { cudaFreeHost(m->h_pos_pinned); }
@@ -572,6 +574,44 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
     if (n_past < 0 || n_past + n_tokens > m->info.n_ctx) { be->set_error("the number of tokens exceeds the context length (%d + %d > %d)", n_past, n_tokens, m->info.n_ctx); return SPYB_FAIL; }
     for (int i = 0; i < n_tokens; ++i) { if (tokens[i] < 0 || tokens[i] >= m->info.n_vocab) { be->set_error("token id %d out of range", tokens[i]); return SPYB_FAIL; } }
     int64_t launches = 0;
+    if (n_tokens == 1 && be->config.use_graph != 0 && (m->info.tp_size == 1 || std::getenv("SPYB_TP_NO_GRAPH") == nullptr)) {
+        // the host-driven token loop: one captured graph per model (staging words and the logits go through pinned
+        // memory whose addresses are fixed, so the graph replays unchanged for every token)
+        SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+        m->h_pos_pinned[0] = n_past; m->h_pos_pinned[1] = n_past + 1; m->h_pos_pinned[2] = ++m->epoch;
+        m->h_tok_pinned[0] = tokens[0];
+        if (m->graph_eval1 == nullptr) {
+            cudaGraph_t graph = nullptr;
+            SPYB_CUDA(be, cudaStreamBeginCapture(be->stream, cudaStreamCaptureModeThreadLocal));
+            spyb_status st = SPYB_SUCCESS;
+            cudaError_t ce = cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 12, cudaMemcpyHostToDevice, be->stream);
+            if (ce == cudaSuccess) { ce = cudaMemcpyAsync(m->d_tokens_in, m->h_tok_pinned, 4, cudaMemcpyHostToDevice, be->stream); }
+            if (ce == cudaSuccess) { ce = launch_embed(m->d_tokens_in, 1, m->embd, m->embd_type, m->info.d_model, m->x, be->stream); }
+            int64_t n = 1;
+            if (ce == cudaSuccess) { st = run_layers(m, 1, true, &n); }
+            if (ce == cudaSuccess && st == SPYB_SUCCESS) { st = run_head(m, 0, &n, m->info.tp_size > 1 && m->tp_ready); }
+            if (ce == cudaSuccess && st == SPYB_SUCCESS) { ce = cudaMemcpyAsync(m->h_logits_pinned, m->logits, (size_t)m->info.n_vocab * 4, cudaMemcpyDeviceToHost, be->stream); }
+            const cudaError_t ee = cudaStreamEndCapture(be->stream, &graph);
+            if (ce != cudaSuccess || st != SPYB_SUCCESS || ee != cudaSuccess) {
+                if (graph) { cudaGraphDestroy(graph); }
+                if (st == SPYB_SUCCESS) { be->set_error("CUDA graph capture of the single-token step failed: %s", cudaGetErrorString(ce != cudaSuccess ? ce : ee)); }
+                return SPYB_FAIL;
+            }
+            const cudaError_t ie = cudaGraphInstantiate(&m->graph_eval1, graph, 0);
+            cudaGraphDestroy(graph);
+            if (ie != cudaSuccess) { m->graph_eval1 = nullptr; be->set_error("CUDA graph instantiation failed: %s", cudaGetErrorString(ie)); return SPYB_FAIL; }
+            m->eval1_launches = n;
+        }
+        SPYB_CUDA(be, cudaEventRecord(m->ev0, be->stream));
+        SPYB_CUDA(be, cudaGraphLaunch(m->graph_eval1, be->stream));
+        SPYB_CUDA(be, cudaEventRecord(m->ev1, be->stream));
+        SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+        if (be->device_error()) { return SPYB_FAIL; }
+        if (logits_host != nullptr) { std::memcpy(logits_host, m->h_logits_pinned, (size_t)m->info.n_vocab * 4); }
+        SPYB_CUDA(be, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+        m->last_launches = m->eval1_launches;
+        return SPYB_SUCCESS;
+    }
     SPYB_CUDA(be, cudaEventRecord(m->ev0, be->stream));
     const int tmax = std::min(8, std::min(matvec_max_columns(m->info.d_model / 32), matvec_max_columns(m->fl / 32)));
     for (int t0 = 0; t0 < n_tokens; t0 += tmax) {
