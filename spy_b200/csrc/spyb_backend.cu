@@ -71,7 +71,7 @@ size_t Arena::available() {
 // ------------------------------------------------------------------------------------------ matrices
 spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, DevMatrix *out, int tile_rows) {
     if (type != SPYB_Q4_0 && type != SPYB_Q8_0) { be->set_error("weight type %d has no device layout", type); return SPYB_UNSUPPORTED; }
-    if ((tile_rows != 4 && tile_rows != 32) || n_rows % tile_rows != 0) { be->set_error("quantized matrices need a multiple of %d rows (got %lld)", tile_rows, (long long)n_rows); return SPYB_UNSUPPORTED; }
+    if ((tile_rows != 4 && tile_rows != 8 && tile_rows != 16 && tile_rows != 32) || n_rows % tile_rows != 0) { be->set_error("quantized matrices need a multiple of %d rows (got %lld)", tile_rows, (long long)n_rows); return SPYB_UNSUPPORTED; }
     DevMatrix m;
     m.type = type; m.n_rows = n_rows; m.nb = nb; m.nbp = padded_blocks(nb); m.k = (int64_t)nb * QK; m.tile_rows = tile_rows;
     void *w = nullptr;
@@ -177,7 +177,6 @@ spyb_status spyb_create(const spyb_config *config, spyb_backend **out) {
     if (const char *v = std::getenv("SPYB_MV_CTAS_PER_SM")) { be->mv_ctas_per_sm = std::max(1, std::min(2, std::atoi(v))); }   // tuning knob
     if (const char *v = std::getenv("SPYB_MV_S")) { be->mv_force_s = std::atoi(v); }         // tuning knobs
     if (const char *v = std::getenv("SPYB_MV_WACT")) { be->mv_force_wact = std::atoi(v); }
-    if (const char *v = std::getenv("SPYB_MV_ROWS_SPLIT")) { be->mv_rows_split = std::atoi(v); }
     if (const char *v = std::getenv("SPYB_MV_RING_KB")) { be->mv_ring_kb = std::max(8, std::min(96, std::atoi(v))); }   // tuning knob
     if (cudaStreamCreateWithFlags(&be->stream, cudaStreamNonBlocking) != cudaSuccess) { delete be; return SPYB_FAIL; }
     if (cudaHostAlloc(reinterpret_cast<void **>(&be->h_error_flag), sizeof(int), cudaHostAllocMapped) != cudaSuccess ||

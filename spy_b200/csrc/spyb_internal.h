@@ -55,7 +55,7 @@ struct spyb_backend {
     int          num_sms = 148;
     int          mv_ctas_per_sm = 2;
     int          mv_ring_kb = 80;
-    int          mv_force_s = 0, mv_force_wact = 0, mv_rows_split = 0;
+    int          mv_force_s = 0, mv_force_wact = 0;
     bool         l2_prefetch_next = false;         // kernels pull the weights of the kernel two places later towards L2
     size_t       l2_prefetch_cap = (size_t)32 << 20;   // at most this much of one matrix
     cudaStream_t stream = nullptr;
@@ -98,7 +98,7 @@ struct spyb_backend {
     }
     spyb::LaunchCfg launch_cfg(bool pdl) const {
         spyb::LaunchCfg c; c.stream = stream; c.pdl = pdl; c.num_sms = num_sms; c.mv_ctas_per_sm = mv_ctas_per_sm;
-        c.mv_ring_kb = mv_ring_kb; c.mv_force_s = mv_force_s; c.mv_force_wact = mv_force_wact; c.mv_rows_split = mv_rows_split; c.error_flag = d_error_flag; return c;
+        c.mv_ring_kb = mv_ring_kb; c.mv_force_s = mv_force_s; c.mv_force_wact = mv_force_wact; c.error_flag = d_error_flag; return c;
     }
 };
 

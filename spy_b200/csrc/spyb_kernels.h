@@ -25,8 +25,8 @@ struct DevMatrix {
     int64_t        k = 0;
     int            nb = 0;       // blocks per row
     int            nbp = 0;      // blocks per row in memory (nb rounded up to a multiple of 8)
-    int            tile_rows = 4;   // rows per tile: 4 (lane-per-accumulator kernel) or 32 (lane-per-row kernel)
-    int            fused_pair = 0;  // tile_rows == 32 only: rows 0..15 of a tile are FFN-up rows, rows 16..31 the matching FFN-gate rows
+    int            tile_rows = 4;   // rows per tile: 4 (lane-per-accumulator kernel) or 8 / 16 / 32 (lane-per-row kernels)
+    int            fused_pair = 0;  // tile_rows >= 8 only: the first half of a tile's rows are FFN-up rows, the second half the matching FFN-gate rows
     const uint8_t *w = nullptr;  // [n_rows / tile_rows][nbp / 8] records of tile_rows rows
     size_t bytes() const { return (size_t)n_rows * nb * ((type == 8 ? 32 : 16) + 2); }   // algorithmic bytes (without padding)
 };
@@ -109,7 +109,6 @@ struct LaunchCfg {
     int          mv_ctas_per_sm = 2;   // mat-vec CTAs per SM for single-column launches (their register budget allows 2)
     int          mv_ring_kb = 80;      // shared-memory ring per CTA that bulk copies stream the weights through
     int          mv_force_s = 0, mv_force_wact = 0;   // tuning overrides (0 = choose)
-    int          mv_rows_split = 0;                   // lane-per-row kernel: 1 = four warps share a tile when an SM has at most 3 tiles, 2 = whenever groups suffice
     int         *error_flag = nullptr;
 };
 

@@ -54,13 +54,12 @@ __device__ __forceinline__ ActPlanes act_planes(void *base, int nbp, int TM) {
     return a;
 }
 
-struct MatvecSmem { size_t act, bars, xch, ring, total; };
+struct MatvecSmem { size_t act, bars, ring, total; };
 __host__ __device__ static inline MatvecSmem matvec_smem_layout(int nbp, int TM, size_t ring_bytes) {
     MatvecSmem m;
     m.act  = 0;
     m.bars = (act_plane_bytes(nbp, TM) + 15) / 16 * 16;
-    m.xch  = m.bars + (size_t)MV_WARPS * MAX_STAGES * 8;                  // partial-sum exchange of warps that share a tile
-    m.ring = (m.xch + (size_t)(MV_WARPS / 4) * 2 * TM * 4 * 32 * 4 + 127) / 128 * 128;
+    m.ring = (m.bars + (size_t)MV_WARPS * MAX_STAGES * 8 + 127) / 128 * 128;
     m.total = m.ring + ring_bytes;
     return m;
 }
@@ -542,42 +541,43 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
 }
 
 // ---------------------------------------------------------------------------------------------
-// Variant for matrices stored in 32-row tiles (DevMatrix::tile_rows == 32): lane = row. A lane keeps whole
-// accumulators of its row in registers, so the scale product d_w * d_x and the activation words are fetched once
-// per row and block instead of once per accumulator, the results of a tile are 32 consecutive outputs and the
-// reduction tree is register arithmetic: fewer instructions per weight byte than the lane-per-accumulator kernel.
-// It needs many rows to fill the machine (a tile walks along K sequentially), so it serves the tall matrices
-// (FFN up|gate, the head), and NSPLIT warps share a tile to put more warps on every scheduler:
-//   NSPLIT == 1: one warp per tile, all eight accumulators per lane
-//   NSPLIT == 4: warp q of the group takes accumulators q and q + 4 (Q4_0: both nibbles of quant word q; Q8_0:
-//                words q and q + 4) - exactly the pairs hsum_float_8 adds first, ((a0+a4)+(a2+a6))+((a1+a5)+(a3+a7));
-//                the four pair sums meet in shared memory and the group's first warp finishes the tree.
-// The group streams its tiles through one ring: the first warp issues the bulk copies (one per stage), every warp
-// waits on the stage's "full" barrier, and a stage is refilled once all NSPLIT warps have arrived on its "empty" barrier.
-// A record is [32 rows][2 groups x 64 B (Q4_0) or 128 B (Q8_0) | 8 fp16 scales]; the 144-byte (272-byte) row pitch
-// makes the per-lane 128-bit reads conflict-free.
-// With fused_pair, rows 0..15 of every tile are FFN-up rows 16u..16u+15 and rows 16..31 the FFN-gate rows.
-template <int WT, int TM, int NSPLIT, bool TPIN>
+// Variant for matrices stored in tiles of TR = 32, 16 or 8 rows (DevMatrix::tile_rows): a row belongs to LPR = 32 / TR
+// lanes of one warp, lane = (part, row), and a lane keeps 8 / LPR whole accumulators of its row in registers:
+//   LPR == 1: all eight accumulators
+//   LPR == 2: part h takes the accumulator pairs (2h, 2h + 4) and (2h + 1, 2h + 5)
+//   LPR == 4: part q takes the pair (q, q + 4) (Q4_0: both nibbles of quant word q; Q8_0: words q and q + 4)
+// - exactly the pairs hsum_float_8 adds first, ((a0+a4)+(a2+a6))+((a1+a5)+(a3+a7)); the pair sums of a row meet by
+// shuffle. The scale product d_w * d_x and the activation words are fetched once per lane and block instead of once per
+// accumulator, so the kernel issues about half the instructions per weight byte of the lane-per-accumulator kernel.
+// A tile walks along K sequentially on one warp; the tile height is chosen per matrix so that a CTA has about as many
+// tiles as warps (tall matrices: 32 or 16 rows, d_model-sized ones: 8).
+// Every warp streams its tiles through a private ring: lane 0 issues the bulk copies (one per stage), all lanes wait on
+// the stage's mbarrier, and the warp's own __syncwarp hands a stage back for the refill.
+// A record is [TR rows][2 groups x 64 B (Q4_0) or 128 B (Q8_0) | 8 fp16 scales]; the 144-byte (272-byte) row pitch
+// makes the 128-bit reads of eight consecutive rows conflict-free.
+// With fused_pair, rows 0..TR/2-1 of tile u are FFN-up rows (TR/2)u.. and rows TR/2..TR-1 the matching FFN-gate rows.
+template <int WT, int TM, int LPR, bool TPIN>
 __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const MatvecParams p, const int ring_bytes, const int S, const int wact) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ float norm_scales[8];
+    constexpr int TR   = 32 / LPR;                       // rows per tile
     constexpr int ROWB = ((WT == 8) ? 256 : 128) + 16;
-    constexpr int RECB = 32 * ROWB;
+    constexpr int RECB = TR * ROWB;
     constexpr int GRPB = (WT == 8) ? 128 : 64;
-    constexpr int NP   = 4 / NSPLIT;                     // accumulator pairs (j, j + 4) per warp
+    constexpr int NP   = 4 / LPR;                        // accumulator pairs (j, j + 4) per lane
 
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int grp = warp / NSPLIT, part = warp % NSPLIT;
+    const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+    const int part = lane / TR, lrow = lane % TR;
     const int nbp  = p.A.nbp;
     const int ng   = nbp >> 2;
     const int nrec = nbp >> 3;
 
-    const int64_t n_units  = p.A.n_rows >> 5;
+    const int64_t n_units  = p.A.n_rows / TR;
     const int64_t unit_lo  = n_units * blockIdx.x / gridDim.x;
     const int64_t unit_hi  = n_units * (blockIdx.x + 1) / gridDim.x;
     const int64_t my_first = unit_lo + grp;
     const int     my_units = (grp < wact && my_first < unit_hi) ? (int)((unit_hi - my_first + wact - 1) / wact) : 0;
-    const int     n_act    = (int)min((int64_t)wact, unit_hi - unit_lo);   // groups of this CTA that have work
+    const int     n_act    = (int)min((int64_t)wact, unit_hi - unit_lo);   // warps of this CTA that have work
     const int     nch      = (nrec + S - 1) / S;
     const int     n_items  = my_units * nch;
     const int     stage_bytes = S * RECB;
@@ -585,37 +585,29 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
 
     const MatvecSmem L = matvec_smem_layout(nbp, TM, (size_t)ring_bytes);
     const uint32_t ring_s  = smem_u32(smem_raw + L.ring) + (uint32_t)grp * NS * stage_bytes;
-    const uint32_t full_s  = smem_u32(smem_raw + L.bars) + (grp * NSPLIT) * MAX_STAGES * 8;
-    const uint32_t empty_s = full_s + MAX_STAGES * 8;     // (the second warp's barrier slots; used when NSPLIT > 1)
-    const uint32_t xbar_s  = empty_s + MAX_STAGES * 8;    // two "pair sums written" barriers (the third warp's slots)
-    float         *xch     = reinterpret_cast<float *>(smem_raw + L.xch) + (size_t)grp * 2 * TM * 4 * 32;
+    const uint32_t full_s  = smem_u32(smem_raw + L.bars) + grp * MAX_STAGES * 8;
     const size_t   tile_bytes = (size_t)nrec * RECB;
-    const bool     leader = (part == 0);
 
     const uint8_t *src = nullptr;
-    int64_t lu = my_first; int lrec = 0, lslot = 0, issued = 0; uint32_t lparity = 0;
+    int64_t lu = my_first; int lrec = 0, lslot = 0, issued = 0;
     bool    ok = true;
-    // leader lane 0: stage lslot <- the next <= S records; a stage that was used before is first waited empty
+    // lane 0: stage lslot <- the next <= S records (the stage was handed back by this warp's own __syncwarp)
     auto issue_next = [&]() {
-        if (NSPLIT > 1 && issued >= NS) {
-            if (!mbar_wait_bounded(empty_s + lslot * 8, lparity, WAIT_LIMIT_NS)) { ok = false; return; }
-        }
         const uint32_t bytes = (uint32_t)min(S, nrec - lrec) * RECB;
         const uint32_t bar = full_s + lslot * 8;
         mbar_expect_tx(bar, bytes);
         bulk_copy_g2s(ring_s + lslot * stage_bytes, src, bytes, bar);
         src += bytes;
         ++issued;
-        if (++lslot == NS) { lslot = 0; if (issued > NS) { lparity ^= 1u; } }
+        if (++lslot == NS) { lslot = 0; }
         lrec += S;
         if (lrec >= nrec) { lrec = 0; lu += wact; src = p.A.w + (size_t)lu * tile_bytes; }
     };
 
     pdl_launch_dependents();
     stamp(p.stamps, 0, false); stamp(p.stamps, 4, true);
-    if (leader && lane == 0 && n_items > 0) {
-        for (int s = 0; s < NS; ++s) { mbar_init(full_s + s * 8, 1); if (NSPLIT > 1) { mbar_init(empty_s + s * 8, NSPLIT); } }
-        if (NSPLIT > 1) { mbar_init(xbar_s, NSPLIT); mbar_init(xbar_s + 8, NSPLIT); }
+    if (lane == 0 && n_items > 0) {
+        for (int s = 0; s < NS; ++s) { mbar_init(full_s + s * 8, 1); }
         mbar_init_fence();
         src = p.A.w + (size_t)lu * tile_bytes;
         for (int s = 0; s < NS && issued < n_items; ++s) { issue_next(); }
@@ -637,13 +629,13 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
             matvec_prologue<TM>(p, act, v3, norm_scales);
         }
     }
-    __syncthreads();   // (also orders the leaders' barrier initialisation before the other warps' first wait)
+    __syncthreads();
     stamp(p.stamps, 2, false); stamp(p.stamps, 6, true);
     matvec_tap(p, act);
 
     const uint32_t y_s   = smem_u32(act.Y);
     const uint32_t ds_s  = smem_u32(act.DS);
-    const uint32_t row_s = ring_s + lane * ROWB;
+    const uint32_t row_s = ring_s + lrow * ROWB;
     const uint32_t col_y = (uint32_t)ng * 128, col_ds = (uint32_t)ng * 16;
 
     float acc[TM][2 * NP];   // [pair][0] = accumulator j, [pair][1] = accumulator j + 4, j = part * NP + pair
@@ -655,7 +647,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
 
     int64_t  cu = my_first; int crec = 0, slot = 0; uint32_t parity = 0;
     uint32_t ya = y_s, da = ds_s;
-    int      n = 0, tile_no = 0;
+    int      n = 0;
     for (; n < n_items; ++n) {
         bool got = mbar_wait_bounded(full_s + slot * 8, parity, WAIT_LIMIT_NS);
         if (__any_sync(0xffffffffu, !got || !ok)) { ok = false; break; }
@@ -703,66 +695,49 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
             }
         }
         __syncwarp();   // every lane is done reading the stage
-        if (NSPLIT > 1 && lane == 0) { mbar_arrive(empty_s + slot * 8); }
-        if (leader && lane == 0 && issued < n_items) { issue_next(); }
+        if (lane == 0 && issued < n_items) { issue_next(); }
         if (++slot == NS) { slot = 0; parity ^= 1u; }
         crec += S;
         if (crec >= nrec) {   // tile finished: hsum_float_8 tree ((a0+a4)+(a2+a6))+((a1+a5)+(a3+a7)), then the epilogue
+            // pair sums p_j = a_j + a_(j+4); h = (p0 + p2) + (p1 + p3); a row's LPR lanes exchange theirs by shuffle
             float h[TM];
-            if (NSPLIT == 1) {
-#pragma unroll
-                for (int t = 0; t < TM; ++t) {
-                    h[t] = __fadd_rn(__fadd_rn(__fadd_rn(acc[t][0], acc[t][1]), __fadd_rn(acc[t][4], acc[t][5])),
-                                     __fadd_rn(__fadd_rn(acc[t][2], acc[t][3]), __fadd_rn(acc[t][6], acc[t][7])));
-                }
-            } else {
-                float *xb = xch + (size_t)(tile_no & 1) * TM * 4 * 32;
-#pragma unroll
-                for (int t = 0; t < TM; ++t) {
-#pragma unroll
-                    for (int k = 0; k < NP; ++k) { xb[(t * 4 + part * NP + k) * 32 + lane] = __fadd_rn(acc[t][2 * k], acc[t][2 * k + 1]); }
-                }
-                __syncwarp();
-                if (lane == 0) { mbar_arrive(xbar_s + (tile_no & 1) * 8); }
-                if (leader) {
-                    got = mbar_wait_bounded(xbar_s + (tile_no & 1) * 8, (uint32_t)((tile_no >> 1) & 1), WAIT_LIMIT_NS);
-                    if (__any_sync(0xffffffffu, !got)) { ok = false; break; }
-#pragma unroll
-                    for (int t = 0; t < TM; ++t) {
-                        h[t] = __fadd_rn(__fadd_rn(xb[(t * 4 + 0) * 32 + lane], xb[(t * 4 + 2) * 32 + lane]),
-                                         __fadd_rn(xb[(t * 4 + 1) * 32 + lane], xb[(t * 4 + 3) * 32 + lane]));
-                    }
-                }
-            }
 #pragma unroll
             for (int t = 0; t < TM; ++t) {
+                if (LPR == 1) {
+                    h[t] = __fadd_rn(__fadd_rn(__fadd_rn(acc[t][0], acc[t][1]), __fadd_rn(acc[t][4], acc[t][5])),
+                                     __fadd_rn(__fadd_rn(acc[t][2], acc[t][3]), __fadd_rn(acc[t][6], acc[t][7])));
+                } else if (LPR == 2) {   // part 0 holds p0, p1; part 1 holds p2, p3
+                    const float pa = __fadd_rn(acc[t][0], acc[t][1]), pb = __fadd_rn(acc[t][2], acc[t][3]);
+                    const float qa = __fadd_rn(pa, __shfl_xor_sync(0xffffffffu, pa, 16)), qb = __fadd_rn(pb, __shfl_xor_sync(0xffffffffu, pb, 16));
+                    h[t] = __fadd_rn(qa, qb);
+                } else {                 // part q holds p_q
+                    const float pa = __fadd_rn(acc[t][0], acc[t][1]);
+                    const float qa = __fadd_rn(pa, __shfl_xor_sync(0xffffffffu, pa, 16));
+                    h[t] = __fadd_rn(qa, __shfl_xor_sync(0xffffffffu, qa, 8));
+                }
 #pragma unroll
                 for (int a = 0; a < 2 * NP; ++a) { acc[t][a] = 0.f; }
             }
-            if (leader) {
 #pragma unroll
-                for (int t = 0; t < TM; ++t) {
-                    if (p.epi == EPI_SILU_MUL) {
-                        const float gate = __shfl_down_sync(0xffffffffu, h[t], 16);
-                        matvec_epilogue_silu(p, 16 * cu + lane, t, h[t], gate, lane < 16 && t < p.T);
-                    } else {
-                        const float partner = __shfl_xor_sync(0xffffffffu, h[t], 1);
-                        matvec_epilogue(p, 32 * cu + lane, t, h[t], partner, t < p.T);
-                    }
+            for (int t = 0; t < TM; ++t) {
+                if (p.epi == EPI_SILU_MUL) {
+                    const float gate = __shfl_down_sync(0xffffffffu, h[t], TR / 2);
+                    matvec_epilogue_silu(p, (TR / 2) * cu + lane, t, h[t], gate, lane < TR / 2 && t < p.T);
+                } else {
+                    const float partner = __shfl_xor_sync(0xffffffffu, h[t], 1);
+                    matvec_epilogue(p, TR * cu + lane, t, h[t], partner, lane < TR && t < p.T);
                 }
             }
-            crec = 0; cu += wact; ya = y_s; da = ds_s; ++tile_no;
+            crec = 0; cu += wact; ya = y_s; da = ds_s;
         }
     }
     if (!ok) {
         // a copy (or a partner warp) did not arrive: report, give the copies still in flight a last bounded chance to
         // land (they target this CTA's shared memory) and stop; the host sees the flag at its next synchronisation
         if (lane == 0 && p.error_flag != nullptr) { atomicExch(p.error_flag, 1); }
-        if (leader) {
-            for (int k = n; k < __shfl_sync(0xffffffffu, issued, 0); ++k) {
-                mbar_wait_bounded(full_s + slot * 8, parity, 10000000ull);
-                if (++slot == NS) { slot = 0; parity ^= 1u; }
-            }
+        for (int k = n; k < __shfl_sync(0xffffffffu, issued, 0); ++k) {
+            mbar_wait_bounded(full_s + slot * 8, parity, 10000000ull);
+            if (++slot == NS) { slot = 0; parity ^= 1u; }
         }
     }
     if (p.tp_counter != nullptr) {
@@ -794,11 +769,11 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
     if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
 }
 
-template <int WT, int TM, int NSPLIT, bool TPIN = false>
+template <int WT, int TM, int LPR, bool TPIN = false>
 static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &cfg) {
-    constexpr int RECB = 32 * (((WT == 8) ? 256 : 128) + 16);
-    constexpr int GROUPS = MV_WARPS / NSPLIT;
-    const int64_t n_units = p.A.n_rows >> 5;
+    constexpr int TR = 32 / LPR;
+    constexpr int RECB = TR * (((WT == 8) ? 256 : 128) + 16);
+    const int64_t n_units = p.A.n_rows / TR;
     int64_t grid = std::min<int64_t>(cfg.num_sms, n_units);
     if (grid < 1) { grid = 1; }
     const int64_t units_per_cta = (n_units + grid - 1) / grid;
@@ -807,8 +782,8 @@ static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &
     if (fixed.total + (size_t)RECB > budget) { return cudaErrorInvalidValue; }
     const size_t ring = std::min<size_t>((size_t)cfg.mv_ring_kb * 2 * 1024, budget - fixed.total) / 128 * 128;
     const int nrec = p.A.nbp >> 3;
-    int wact = (int)std::min<int64_t>(GROUPS, units_per_cta);
-    int S = 2;
+    int wact = (int)std::min<int64_t>(MV_WARPS, units_per_cta);
+    int S = 2 * LPR;                      // stages of about 9 KB (Q4_0); at least three per warp, else smaller ones
     while (S > nrec) { S >>= 1; }
     if (S < 1) { S = 1; }
     while (ring / ((size_t)wact * S * RECB) < 3) {
@@ -817,12 +792,12 @@ static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &
         else { break; }
     }
     if (cfg.mv_force_s > 0) { S = std::min(cfg.mv_force_s, std::max(nrec, 1)); }
-    if (cfg.mv_force_wact > 0) { wact = std::min(cfg.mv_force_wact, GROUPS); }
+    if (cfg.mv_force_wact > 0) { wact = std::min(cfg.mv_force_wact, MV_WARPS); }
     if (ring / ((size_t)wact * S * RECB) < 1) { return cudaErrorInvalidValue; }
     const size_t smem = fixed.total + ring;
     static size_t smem_allowed = 48 * 1024;
     if (smem > smem_allowed) {
-        cudaError_t err = cudaFuncSetAttribute(matvec_rows_kernel<WT, TM, NSPLIT, TPIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        cudaError_t err = cudaFuncSetAttribute(matvec_rows_kernel<WT, TM, LPR, TPIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) { return err; }
         smem_allowed = smem;
     }
@@ -834,22 +809,14 @@ static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&lc, matvec_rows_kernel<WT, TM, NSPLIT, TPIN>, q, (int)ring, S, wact);
+    return cudaLaunchKernelEx(&lc, matvec_rows_kernel<WT, TM, LPR, TPIN>, q, (int)ring, S, wact);
 }
 
-template <int WT>
+template <int WT, int LPR>
 static cudaError_t launch_matvec_rows_w(const MatvecParams &p, const LaunchCfg &cfg) {
-    // four warps per tile while that still leaves every SM with fewer tiles than warp groups, else one
-    const int64_t tiles_per_sm = ((p.A.n_rows >> 5) + cfg.num_sms - 1) / cfg.num_sms;
-    const bool split = cfg.mv_rows_split == 1 ? tiles_per_sm <= 3 : (cfg.mv_rows_split == 2 && tiles_per_sm <= MV_WARPS / 4 + 2);
-    if (split) {
-        if (p.T <= 1) { return p.tp_in ? launch_matvec_rows_t<WT, 1, 4, true>(p, cfg) : launch_matvec_rows_t<WT, 1, 4>(p, cfg); }
-        if (p.T <= 2) { return launch_matvec_rows_t<WT, 2, 4>(p, cfg); }
-        return launch_matvec_rows_t<WT, 4, 4>(p, cfg);
-    }
-    if (p.T <= 1) { return p.tp_in ? launch_matvec_rows_t<WT, 1, 1, true>(p, cfg) : launch_matvec_rows_t<WT, 1, 1>(p, cfg); }
-    if (p.T <= 2) { return launch_matvec_rows_t<WT, 2, 1>(p, cfg); }
-    return launch_matvec_rows_t<WT, 4, 1>(p, cfg);
+    if (p.T <= 1) { return p.tp_in ? launch_matvec_rows_t<WT, 1, LPR, true>(p, cfg) : launch_matvec_rows_t<WT, 1, LPR>(p, cfg); }
+    if (p.T <= 2) { return launch_matvec_rows_t<WT, 2, LPR>(p, cfg); }
+    return launch_matvec_rows_t<WT, 4, LPR>(p, cfg);
 }
 
 int matvec_max_columns(int nb) {   // (the lane-per-row kernel keeps 8 accumulators per column in registers: at most 4 columns)
@@ -925,11 +892,12 @@ cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg) {
     if (p.T < 1 || p.T > matvec_max_columns(p.A.nb)) { return cudaErrorInvalidValue; }
     if ((p.epi == EPI_TP_SCATTER || p.tp_in != nullptr) && (p.T != 1 || p.tp_n < 2 || p.tp_n > TP_MAX || p.tp_epoch == nullptr || p.A.nbp * 8 > PRO_GROUPS * MV_THREADS)) { return cudaErrorInvalidValue; }
     if (p.A.k % QK != 0 || p.A.nb < 1 || p.A.nbp != padded_blocks(p.A.nb) || p.A.w == nullptr) { return cudaErrorInvalidValue; }
-    if (p.A.tile_rows == 32) {
-        if ((p.A.n_rows & 31) || p.pair_mode || (p.epi == EPI_SILU_MUL) != (p.A.fused_pair != 0)) { return cudaErrorInvalidValue; }
+    if (p.A.tile_rows == 32 || p.A.tile_rows == 16 || p.A.tile_rows == 8) {
+        if ((p.A.n_rows % p.A.tile_rows) || p.pair_mode || (p.epi == EPI_SILU_MUL) != (p.A.fused_pair != 0)) { return cudaErrorInvalidValue; }
+        const int lpr = 32 / p.A.tile_rows;
         switch (p.A.type) {
-        case 2: return launch_matvec_rows_w<2>(p, cfg);
-        case 8: return launch_matvec_rows_w<8>(p, cfg);
+        case 2: return lpr == 1 ? launch_matvec_rows_w<2, 1>(p, cfg) : lpr == 2 ? launch_matvec_rows_w<2, 2>(p, cfg) : launch_matvec_rows_w<2, 4>(p, cfg);
+        case 8: return lpr == 1 ? launch_matvec_rows_w<8, 1>(p, cfg) : lpr == 2 ? launch_matvec_rows_w<8, 2>(p, cfg) : launch_matvec_rows_w<8, 4>(p, cfg);
         default: return cudaErrorNotSupported;
         }
     }

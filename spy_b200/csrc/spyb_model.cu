@@ -411,14 +411,27 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
     }
     spyb_status st = upload_f32("output_norm.weight", d, &m->output_norm);
     if (st != SPYB_SUCCESS) { return fail(st); }
-    // tall matrices go to 32-row tiles (lane-per-row kernel) when their row count allows; SPYB_NO_ROWS_KERNEL keeps 4-row tiles
-    const bool rows32 = std::getenv("SPYB_NO_ROWS_KERNEL") == nullptr;
+    // tile height per matrix (rows per warp-tile of the mat-vec kernels): 4 = lane-per-accumulator kernel, 8 / 16 / 32 =
+    // lane-per-row kernels; the defaults put about one tile on every warp of an SM. SPYB_TILE_<NAME> overrides, and
+    // SPYB_NO_ROWS_KERNEL keeps everything on 4-row tiles.
+    const bool rows_kernel = std::getenv("SPYB_NO_ROWS_KERNEL") == nullptr;
+    auto tile_for = [&](const char *env, int64_t n_rows, int dflt) {
+        int t = dflt;
+        if (const char *v = std::getenv(env)) { t = std::atoi(v); }
+        if (!rows_kernel || (t != 8 && t != 16 && t != 32) || n_rows % t != 0) { t = 4; }
+        return t;
+    };
+    auto auto_tile = [&](int64_t n_rows) {   // the tallest tile that still gives every SM at least 8 tiles
+        const int64_t per_sm = n_rows / std::max(be->num_sms, 1);
+        return per_sm >= 8 * 32 ? 32 : per_sm >= 8 * 16 ? 16 : 8;
+    };
     {
         const std::string head_name = f.tensors.count("output.weight") ? "output.weight" : "token_embd.weight";
         auto ith = f.tensors.find(head_name);
-        if (rows32 && ith != f.tensors.end() && I.n_vocab % 32 == 0 && I.n_vocab >= 8192) {
+        const int head_tile = (I.n_vocab >= 8192) ? tile_for("SPYB_TILE_HEAD", I.n_vocab, auto_tile(I.n_vocab)) : 4;
+        if (ith != f.tensors.end() && head_tile != 4) {
             DevMatrix dummy;
-            if ((st = alloc_matrix(be, ith->second.type, I.n_vocab, d / 32, &m->head, 32)) != SPYB_SUCCESS) { return fail(st); }
+            if ((st = alloc_matrix(be, ith->second.type, I.n_vocab, d / 32, &m->head, head_tile)) != SPYB_SUCCESS) { return fail(st); }
             st = upload_w(head_name, d, I.n_vocab, 0, I.n_vocab, 0, d / 32, &dummy, &m->head, 0);
         } else {
             st = upload_w(head_name, d, I.n_vocab, 0, I.n_vocab, 0, d / 32, &m->head, nullptr, 0);   // replicated on every rank
@@ -434,27 +447,45 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         // heads: rows [r*dl, (r+1)*dl) of Wq, Wk, Wv, stacked into one [3*dl, d] matrix
         auto itq = f.tensors.find(p + "attn_q.weight");
         if (itq == f.tensors.end()) { be->set_error("GGUF: %sattn_q.weight is missing", p.c_str()); return fail(SPYB_FAIL); }
-        const int qkv_tile = (rows32 && dl % 32 == 0 && std::getenv("SPYB_QKV_TILE32") != nullptr) ? 32 : 4;   // measured equal within noise: the 4-row path stays the default
+        const int qkv_tile = tile_for("SPYB_TILE_QKV", dl, auto_tile(3 * (int64_t)dl));
         if ((st = alloc_matrix(be, itq->second.type, 3 * (int64_t)dl, d / 32, &ly.wqkv, qkv_tile)) != SPYB_SUCCESS) { return fail(st); }
         DevMatrix dummy;
         if ((st = upload_w(p + "attn_q.weight", d, d, (int64_t)r * dl, dl, 0, d / 32, &dummy, &ly.wqkv, 0)) != SPYB_SUCCESS) { return fail(st); }
         if ((st = upload_w(p + "attn_k.weight", d, d, (int64_t)r * dl, dl, 0, d / 32, &dummy, &ly.wqkv, dl)) != SPYB_SUCCESS) { return fail(st); }
         if ((st = upload_w(p + "attn_v.weight", d, d, (int64_t)r * dl, dl, 0, d / 32, &dummy, &ly.wqkv, 2 * (int64_t)dl)) != SPYB_SUCCESS) { return fail(st); }
         // Wo: all d rows, input columns of this rank's heads (a block sub-range of every row)
-        if ((st = upload_w(p + "attn_output.weight", d, d, 0, d, (int64_t)r * dl / 32, dl / 32, &ly.wo, nullptr, 0)) != SPYB_SUCCESS) { return fail(st); }
+        auto ito = f.tensors.find(p + "attn_output.weight");
+        const int wo_tile = tile_for("SPYB_TILE_WO", d, auto_tile(d));
+        if (ito != f.tensors.end() && wo_tile != 4) {
+            if ((st = alloc_matrix(be, ito->second.type, d, dl / 32, &ly.wo, wo_tile)) != SPYB_SUCCESS) { return fail(st); }
+            st = upload_w(p + "attn_output.weight", d, d, 0, d, (int64_t)r * dl / 32, dl / 32, &dummy, &ly.wo, 0);
+        } else {
+            st = upload_w(p + "attn_output.weight", d, d, 0, d, (int64_t)r * dl / 32, dl / 32, &ly.wo, nullptr, 0);
+        }
+        if (st != SPYB_SUCCESS) { return fail(st); }
         // FFN: rows [r*fl, (r+1)*fl) of up and gate; down keeps all rows and this rank's input columns
         auto itu = f.tensors.find(p + "ffn_up.weight");
-        if (itu != f.tensors.end() && fl % 16 == 0 && rows32) {
-            if ((st = alloc_matrix(be, itu->second.type, 2 * (int64_t)fl, d / 32, &ly.upgate, 32)) != SPYB_SUCCESS) { return fail(st); }
+        const int ug_tile = tile_for("SPYB_TILE_UPGATE", 2 * (int64_t)fl, auto_tile(2 * (int64_t)fl));
+        if (itu != f.tensors.end() && ug_tile != 4) {
+            const int half = ug_tile / 2;
+            if ((st = alloc_matrix(be, itu->second.type, 2 * (int64_t)fl, d / 32, &ly.upgate, ug_tile)) != SPYB_SUCCESS) { return fail(st); }
             ly.upgate.fused_pair = 1;
-            if ((st = upload_w(p + "ffn_up.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &dummy, &ly.upgate, 0, 16, 0)) != SPYB_SUCCESS) { return fail(st); }
-            if ((st = upload_w(p + "ffn_gate.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &dummy, &ly.upgate, 0, 16, 16)) != SPYB_SUCCESS) { return fail(st); }
+            if ((st = upload_w(p + "ffn_up.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &dummy, &ly.upgate, 0, half, 0)) != SPYB_SUCCESS) { return fail(st); }
+            if ((st = upload_w(p + "ffn_gate.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &dummy, &ly.upgate, 0, half, half)) != SPYB_SUCCESS) { return fail(st); }
         } else {
             if ((st = upload_w(p + "ffn_up.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &ly.up, nullptr, 0)) != SPYB_SUCCESS) { return fail(st); }
             if ((st = upload_w(p + "ffn_gate.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &ly.gate, nullptr, 0)) != SPYB_SUCCESS) { return fail(st); }
             if (ly.up.type != ly.gate.type) { be->set_error("ffn_up and ffn_gate must share one type"); return fail(SPYB_UNSUPPORTED); }
         }
-        if ((st = upload_w(p + "ffn_down.weight", I.n_ff, d, 0, d, (int64_t)r * fl / 32, fl / 32, &ly.down, nullptr, 0)) != SPYB_SUCCESS) { return fail(st); }
+        auto itd = f.tensors.find(p + "ffn_down.weight");
+        const int down_tile = tile_for("SPYB_TILE_DOWN", d, auto_tile(d));
+        if (itd != f.tensors.end() && down_tile != 4) {
+            if ((st = alloc_matrix(be, itd->second.type, d, fl / 32, &ly.down, down_tile)) != SPYB_SUCCESS) { return fail(st); }
+            st = upload_w(p + "ffn_down.weight", I.n_ff, d, 0, d, (int64_t)r * fl / 32, fl / 32, &dummy, &ly.down, 0);
+        } else {
+            st = upload_w(p + "ffn_down.weight", I.n_ff, d, 0, d, (int64_t)r * fl / 32, fl / 32, &ly.down, nullptr, 0);
+        }
+        if (st != SPYB_SUCCESS) { return fail(st); }
         if (dev_alloc(m, &ly.k_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS || dev_alloc(m, &ly.v_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
     }
     I.weight_bytes += (uint64_t)(2 * I.n_layer + 1) * d * 4;
@@ -721,6 +752,7 @@ float spyb_model_bench_kernel(spyb_model *m, int32_t kind, int32_t sweeps, uint6
     const MatvecParams p0 = params(m->layers[0]);
     if (bytes_per_launch) { *bytes_per_launch = p0.A.bytes() + (p0.pair_mode ? p0.B.bytes() : 0); }
     float total_ms = 0.f; int64_t n = 0;
+    const bool hot = std::getenv("SPYB_BENCH_L2_HOT") != nullptr;   // every launch on layer 0's matrix: it stays in L2
     if (kind == 4) {
         // a single 70 MB matrix would stay in the 126 MB L2 between launches: evict it with a 512 MB memset each time
         void *flush = nullptr;
@@ -738,7 +770,7 @@ float spyb_model_bench_kernel(spyb_model *m, int32_t kind, int32_t sweeps, uint6
     } else {
         cudaEventRecord(m->ev0, be->stream);
         for (int s = 0; s < sweeps; ++s) {
-            for (const Layer &ly : m->layers) { if (launch_matvec(params(ly), cfg) != cudaSuccess) { return -1.f; } ++n; }
+            for (const Layer &ly : m->layers) { if (launch_matvec(params(hot ? m->layers[0] : ly), cfg) != cudaSuccess) { return -1.f; } ++n; }
         }
         cudaEventRecord(m->ev1, be->stream);
         if (cudaStreamSynchronize(be->stream) != cudaSuccess) { return -1.f; }

@@ -307,7 +307,7 @@ cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride, int6
     const int     nbp = padded_blocks(nb);
     const int64_t n = n_rows * nbp;
     if (n == 0) { return cudaSuccess; }
-    if (tile_rows != 4 && tile_rows != 32) { return cudaErrorInvalidValue; }
+    if (tile_rows != 4 && tile_rows != 8 && tile_rows != 16 && tile_rows != 32) { return cudaErrorInvalidValue; }
     const unsigned grid = (unsigned)((n + 255) / 256);
     if (type == 2)      { retile_kernel<4><<<grid, 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, matrix_base, tile_rows, dst_row0, src_row0, sub_rows, sub_off); }
     else if (type == 8) { retile_kernel<8><<<grid, 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, matrix_base, tile_rows, dst_row0, src_row0, sub_rows, sub_off); }

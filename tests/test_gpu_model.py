@@ -165,13 +165,18 @@ def test_unsupported_models_are_reported(be, tmp_models):
         B.LlamaModel(be, bad, n_ctx=32)
 
 
-@pytest.mark.parametrize("env", [{}, {"SPYB_MV_ROWS_SPLIT": "2"}, {"SPYB_QKV_TILE32": "1"}, {"SPYB_QKV_TILE32": "1", "SPYB_MV_ROWS_SPLIT": "2"},
-                                 {"SPYB_NO_ROWS_KERNEL": "1"}, {"SPYB_MV_S": "1", "SPYB_MV_WACT": "2"}])
+def _tiles(t):
+    return {f"SPYB_TILE_{n}": str(t) for n in ("QKV", "WO", "UPGATE", "DOWN", "HEAD")}
+
+
+@pytest.mark.parametrize("env", [{}, _tiles(8), _tiles(16), _tiles(32), {"SPYB_TILE_QKV": "4", "SPYB_TILE_DOWN": "4", "SPYB_TILE_UPGATE": "32"},
+                                 {"SPYB_NO_ROWS_KERNEL": "1"}, {"SPYB_MV_S": "1", "SPYB_MV_WACT": "2"},
+                                 dict(_tiles(8), SPYB_MV_S="1", SPYB_MV_WACT="3")])
 @pytest.mark.parametrize("wtype", [quants.Q4_0, quants.Q8_0])
 def test_every_matvec_variant_matches_oracle(env, wtype, oracle, tmp_models, monkeypatch):
-    """The weight layouts (4-row and 32-row tiles, fused up|gate), the lane-per-accumulator and lane-per-row kernels,
-    one or four warps per tile, stage sizes and stream counts are tuning choices: every combination must give the
-    CPU's bits. The vocabulary is large enough for the head to take the lane-per-row path."""
+    """The weight layouts (4-, 8-, 16- and 32-row tiles, fused up|gate), the lane-per-accumulator kernel and the
+    lane-per-row kernels with one, two or four lanes per row, stage sizes and stream counts are tuning choices: every
+    combination must give the CPU's bits. The vocabulary is large enough for the head to take the lane-per-row path."""
     cfg = gguf_io.LlamaConfig(n_layer=2, d_model=256, n_head=2, n_ff=512, n_vocab=8192, weight_std=0.05, wtype=wtype)
     path = str(tmp_models / f"variants_{wtype}.gguf")
     if not os.path.exists(path):
