@@ -75,6 +75,29 @@ size_t matvec_smem_bytes(int nb, int T) { return matvec_smem_layout(padded_block
 //   parallel, the running sum is one thread's chain. Mul (basic.cpp:15-50): y * norm_weight.
 // Single column, K <= 12288: every thread keeps its (at most PG) float4 groups of x in registers from the one
 // global read through the sum of squares to the quantizer; same arithmetic as the general prologue below.
+// the RMSNorm running sum: one thread's chain of dependent f32 additions, in the CPU's order
+__device__ __forceinline__ float running_sum_serial(const float *v3, int n4) {
+    const float4 *g4 = reinterpret_cast<const float4 *>(v3);
+    float sum = 0.f;
+    int g = 0;
+    if (n4 >= 16) {   // the 128-bit reads run one step (16 values) ahead of the dependent adds
+        float4 q0 = g4[0], q1 = g4[1], q2 = g4[2], q3 = g4[3];
+        for (g = 16; g + 16 <= n4; g += 16) {
+            const float4 n0 = g4[(g >> 2)], n1 = g4[(g >> 2) + 1], n2 = g4[(g >> 2) + 2], n3 = g4[(g >> 2) + 3];
+            sum = __fadd_rn(sum, q0.x); sum = __fadd_rn(sum, q0.y); sum = __fadd_rn(sum, q0.z); sum = __fadd_rn(sum, q0.w);
+            sum = __fadd_rn(sum, q1.x); sum = __fadd_rn(sum, q1.y); sum = __fadd_rn(sum, q1.z); sum = __fadd_rn(sum, q1.w);
+            sum = __fadd_rn(sum, q2.x); sum = __fadd_rn(sum, q2.y); sum = __fadd_rn(sum, q2.z); sum = __fadd_rn(sum, q2.w);
+            sum = __fadd_rn(sum, q3.x); sum = __fadd_rn(sum, q3.y); sum = __fadd_rn(sum, q3.z); sum = __fadd_rn(sum, q3.w);
+            q0 = n0; q1 = n1; q2 = n2; q3 = n3;
+        }
+        sum = __fadd_rn(sum, q0.x); sum = __fadd_rn(sum, q0.y); sum = __fadd_rn(sum, q0.z); sum = __fadd_rn(sum, q0.w);
+        sum = __fadd_rn(sum, q1.x); sum = __fadd_rn(sum, q1.y); sum = __fadd_rn(sum, q1.z); sum = __fadd_rn(sum, q1.w);
+        sum = __fadd_rn(sum, q2.x); sum = __fadd_rn(sum, q2.y); sum = __fadd_rn(sum, q2.z); sum = __fadd_rn(sum, q2.w);
+        sum = __fadd_rn(sum, q3.x); sum = __fadd_rn(sum, q3.y); sum = __fadd_rn(sum, q3.z); sum = __fadd_rn(sum, q3.w);
+    }
+    for (; g < n4; ++g) { sum = __fadd_rn(sum, v3[g]); }
+    return sum;
+}
 constexpr int PRO_GROUPS = 6;
 template <int PG, bool NORM, bool TPIN>
 __device__ __forceinline__ void matvec_prologue_1col(const MatvecParams &p, ActPlanes act, float *v3, float *scales) {
@@ -129,36 +152,18 @@ __device__ __forceinline__ void matvec_prologue_1col(const MatvecParams &p, ActP
                 v3[g] = __fadd_rn(v1, v2);
             }
         }
-        __syncthreads();
-        if (tid == 0) {
-            const float4 *g4 = reinterpret_cast<const float4 *>(v3);
-            float sum = 0.f;
-            int g = 0;
-            if (n4 >= 16) {   // the 128-bit reads run one step (16 values) ahead of the dependent adds
-                float4 q0 = g4[0], q1 = g4[1], q2 = g4[2], q3 = g4[3];
-                for (g = 16; g + 16 <= n4; g += 16) {
-                    const float4 n0 = g4[(g >> 2)], n1 = g4[(g >> 2) + 1], n2 = g4[(g >> 2) + 2], n3 = g4[(g >> 2) + 3];
-                    sum = __fadd_rn(sum, q0.x); sum = __fadd_rn(sum, q0.y); sum = __fadd_rn(sum, q0.z); sum = __fadd_rn(sum, q0.w);
-                    sum = __fadd_rn(sum, q1.x); sum = __fadd_rn(sum, q1.y); sum = __fadd_rn(sum, q1.z); sum = __fadd_rn(sum, q1.w);
-                    sum = __fadd_rn(sum, q2.x); sum = __fadd_rn(sum, q2.y); sum = __fadd_rn(sum, q2.z); sum = __fadd_rn(sum, q2.w);
-                    sum = __fadd_rn(sum, q3.x); sum = __fadd_rn(sum, q3.y); sum = __fadd_rn(sum, q3.z); sum = __fadd_rn(sum, q3.w);
-                    q0 = n0; q1 = n1; q2 = n2; q3 = n3;
-                }
-                sum = __fadd_rn(sum, q0.x); sum = __fadd_rn(sum, q0.y); sum = __fadd_rn(sum, q0.z); sum = __fadd_rn(sum, q0.w);
-                sum = __fadd_rn(sum, q1.x); sum = __fadd_rn(sum, q1.y); sum = __fadd_rn(sum, q1.z); sum = __fadd_rn(sum, q1.w);
-                sum = __fadd_rn(sum, q2.x); sum = __fadd_rn(sum, q2.y); sum = __fadd_rn(sum, q2.z); sum = __fadd_rn(sum, q2.w);
-                sum = __fadd_rn(sum, q3.x); sum = __fadd_rn(sum, q3.y); sum = __fadd_rn(sum, q3.z); sum = __fadd_rn(sum, q3.w);
-            }
-            for (; g < n4; ++g) { sum = __fadd_rn(sum, v3[g]); }
-            const float mean = __fdiv_rn(sum, (float)p.A.k);
-            scales[0] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
-        }
-        // the norm weights arrive while thread 0 runs its chain
+        // the norm weights arrive while the sum of squares is formed
         float4 wv[PG];
 #pragma unroll
         for (int k = 0; k < PG; ++k) {
             const int g = tid + k * MV_THREADS;
             wv[k] = (k < npass && g < n4) ? w4[g] : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        __syncthreads();
+        const float sum = (tid == 0) ? running_sum_serial(v3, n4) : 0.f;
+        if (tid == 0) {
+            const float mean = __fdiv_rn(sum, (float)p.A.k);
+            scales[0] = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, p.eps)));
         }
         __syncthreads();   // also: the partials (aliasing Y) are dead from here on
         const float scale = scales[0];
@@ -778,7 +783,7 @@ static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &
     if (grid < 1) { grid = 1; }
     const int64_t units_per_cta = (n_units + grid - 1) / grid;
     const MatvecSmem fixed = matvec_smem_layout(p.A.nbp, TM, 0);
-    const size_t budget = 224 * 1024;
+    const size_t budget = 216 * 1024;   // (the kernels also hold a few KB of static shared memory)
     if (fixed.total + (size_t)RECB > budget) { return cudaErrorInvalidValue; }
     const size_t ring = std::min<size_t>((size_t)cfg.mv_ring_kb * 2 * 1024, budget - fixed.total) / 128 * 128;
     const int nrec = p.A.nbp >> 3;
@@ -838,7 +843,7 @@ static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) 
 
     // ring: what the SM's shared memory leaves after the activation planes (two CTAs per SM for single columns)
     const MatvecSmem fixed = matvec_smem_layout(p.A.nbp, TM, 0);
-    const size_t budget = (per_sm == 2) ? 112 * 1024 : 224 * 1024;
+    const size_t budget = (per_sm == 2) ? 108 * 1024 : 216 * 1024;   // (the kernels also hold a few KB of static shared memory)
     if (fixed.total + (size_t)2 * R * RECB > budget) { return cudaErrorInvalidValue; }   // rows too long for this kernel
     size_t ring = std::min<size_t>((size_t)cfg.mv_ring_kb * 1024 * ((TM == 1) ? 1 : 2), budget - fixed.total) / 128 * 128;
     // S records per stage (one bulk copy per tile and stage) and the number of warps that stream: copies of a few KB

@@ -208,13 +208,17 @@ def llama_tensor_plan(cfg: LlamaConfig) -> list:
     return plan
 
 
-def make_llama_gguf(path: str, cfg: LlamaConfig, seed: int = 1234) -> None:
-    """Seeded synthetic model on the host: matrices N(0, weight_std) quantized to their type, norms = 1."""
+def make_llama_gguf(path: str, cfg: LlamaConfig, seed: int = 1234, embeddings: np.ndarray | None = None) -> None:
+    """Seeded synthetic model on the host: matrices N(0, weight_std) quantized to their type, norms = 1.
+    `embeddings` ([n_vocab, d_model] f32) replaces the random token embeddings (embd_type must be FP32)."""
     rng = np.random.default_rng(seed)
     tensors = []
     for name, ne, number_type, kind in llama_tensor_plan(cfg):
         if kind == "norm":
             raw = np.ones(ne[0], dtype=np.float32).view(np.uint8)
+        elif name == "token_embd.weight" and embeddings is not None:
+            assert number_type == quants.FP32 and embeddings.shape == (ne[1], ne[0])
+            raw = np.ascontiguousarray(embeddings, dtype=np.float32).view(np.uint8).reshape(-1)
         else:
             w = rng.standard_normal((ne[1], ne[0]), dtype=np.float32) * np.float32(cfg.weight_std)
             raw = quants.quantize(w, number_type).reshape(-1)

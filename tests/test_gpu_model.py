@@ -190,3 +190,39 @@ def test_every_matvec_variant_matches_oracle(env, wtype, oracle, tmp_models, mon
     ids, logits = m.generate(prompt, 6)
     assert np.array_equal(ids, want_ids) and logits_ok(logits, want_logits)
     m.close(); b.close()
+
+
+def test_rmsnorm_running_sum_on_hard_inputs(oracle, tmp_models):
+    """The RMSNorm sum of squares is a serial f32 running sum on the CPU; the GPU forms it in parallel from integer
+    increments per binade plus a short serial walk, with a serial fallback. Inputs that stress it - exact ties (ones,
+    powers of two, small dyadic numbers), huge outliers, leading zeros, underflowing squares, all zeros - must still
+    give the CPU's bits. d_model = 4096 exercises the full 1024-group sum."""
+    d, v = 4096, 16
+    rng = np.random.default_rng(77)
+    E = rng.standard_normal((v, d)).astype(np.float32)
+    E[0] = 1.0                                                                  # every group sum is 4: all ties
+    E[1] = np.float32(2.0) ** rng.integers(-3, 4, d) * rng.choice([-1.0, 1.0], d)
+    E[2, rng.integers(0, d, 3)] *= 1000.0                                       # massive outliers
+    E[3] = 0.0; E[3, rng.integers(0, d, 9)] = rng.standard_normal(9)            # mostly zeros
+    E[4] *= 1e-20                                                               # squares underflow to denormals / zero
+    E[5, :2000] = 0.0                                                           # leading zeros
+    E[6] = rng.integers(-8, 9, d) / 8.0                                         # small dyadic numbers: many ties
+    E[7] = 0.0                                                                  # sum == 0
+    E[8] *= 1e4; E[9] *= 1e-4
+    E[10, 0] = 3e4                                                              # the first element dominates
+    cfg = gguf_io.LlamaConfig(n_layer=1, d_model=d, n_head=32, n_ff=256, n_vocab=v, weight_std=0.02)
+    path = str(tmp_models / "hard_norm.gguf")
+    gguf_io.make_llama_gguf(path, cfg, seed=5, embeddings=E)
+    orc = oracle.OracleLlama(path, n_ctx=8)
+    b = B.B200Backend(0)
+    m = B.LlamaModel(b, path, n_ctx=8)
+    bad = []
+    for tok in range(v):
+        orc.n_past = 0                                   # every token starts a fresh sequence (the cache is overwritten)
+        want_ids, want_logits = orc.generate(np.array([tok]), 2)
+        ids, logits = m.generate(np.array([tok]), 2)
+        same = np.array_equal(np.asarray(logits, dtype=np.float32).view(np.uint32), np.asarray(want_logits, dtype=np.float32).view(np.uint32))
+        if not (np.array_equal(ids, want_ids) and same):
+            bad.append((tok, float(np.nanmax(np.abs(np.asarray(logits) - np.asarray(want_logits))))))
+    m.close(); b.close()
+    assert not bad, f"tokens whose logits differ from the CPU's (token, max abs difference): {bad}"
