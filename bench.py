@@ -274,7 +274,7 @@ def main():
         dom = kb["ffn_up_gate"]
         # traffic: dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload's FFN
         # matrices, from the ncu capture summarised in profiles/matvec_rows_q4_0_ffn_up_gate_7b.md
-        roof = {"bound": "hbm", "kernel": "matvec_rows_kernel<Q4_0, 1 column> (fused FFN up|gate, RMSNorm+Q8_0 prologue, SiLU-mul epilogue)",
+        roof = {"bound": "hbm", "kernel": "matvec_rows_kernel<Q4_0, 1 column, 2 lanes per row> (fused FFN up|gate, RMSNorm+Q8_0 prologue, SiLU-mul epilogue)",
                 "achieved": dom["gbs"], "peak": peak,
                 "peak_kind": f"of {peak_kind} ({'MEASURED_PEAKS.json copy bandwidth' if peak_kind == 'measured' else 'fallback 6650 GB/s'})",
                 "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": 50838016 if dom["bytes"] == 50724864 else None,

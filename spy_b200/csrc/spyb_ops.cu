@@ -9,6 +9,8 @@
 
 #include <algorithm>
 
+#include <cstdlib>
+
 #include "spyb_common.cuh"
 #include "spyb_kernels.h"
 
@@ -158,6 +160,19 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
         }
         sc[j] = __fadd_rn(tail, simd);
     }
+    // The V^T values of the next PV steps are requested now (the K row's registers are free), so that they arrive
+    // during the softmax instead of costing one memory round trip per 32 positions afterwards.
+    constexpr int PV_AHEAD = 6;
+    constexpr int n_ahead = PV_AHEAD;
+    uint2 v_ahead[PV_AHEAD][4];
+#pragma unroll
+    for (int s = 0; s < PV_AHEAD; ++s) {
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            const int j0 = 32 * (s + 1), j = j0 + 8 * a + 4 * pv_half;
+            v_ahead[s][a] = (s < n_ahead && j0 < n_main && j < n_vis) ? *reinterpret_cast<const uint2 *>(vrow + j) : make_uint2(0u, 0u);
+        }
+    }
     __syncthreads();
 
     // ---- masked softmax: (score + mask) * scale, subtract the maximum, table exp, std::reduce, multiply by 1/sum
@@ -212,13 +227,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
 #pragma unroll
             for (int k = 0; k < 4; ++k) { acc[a][k] = 0.f; }
         }
-        for (int j0 = 0; j0 < n_main && j0 < n_vis; j0 += 32) {
-            uint2 vv[4];
-#pragma unroll
-            for (int a = 0; a < 4; ++a) {
-                const int j = j0 + 8 * a + 4 * half;
-                vv[a] = (j0 == 0) ? v_first[a] : ((j < n_vis) ? *reinterpret_cast<const uint2 *>(vrow + j) : make_uint2(0u, 0u));
-            }
+        auto pv_step = [&](const uint2 (&vv)[4], int j0) {
 #pragma unroll
             for (int a = 0; a < 4; ++a) {
                 const int    j  = j0 + 8 * a + 4 * half;
@@ -228,6 +237,30 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
                 if (j + 1 < n_vis) { acc[a][1] = fmaf(v01.y, pr.y, acc[a][1]); }
                 if (j + 2 < n_vis) { acc[a][2] = fmaf(v23.x, pr.z, acc[a][2]); }
                 if (j + 3 < n_vis) { acc[a][3] = fmaf(v23.y, pr.w, acc[a][3]); }
+            }
+        };
+        if (0 < n_main) { pv_step(v_first, 0); }
+#pragma unroll
+        for (int s = 0; s < PV_AHEAD; ++s) {
+            const int j0 = 32 * (s + 1);
+            if (s < n_ahead && j0 < n_main && j0 < n_vis) { pv_step(v_ahead[s], j0); }
+        }
+        {   // later steps: loads one step ahead of the arithmetic
+            int j0 = 32 * (n_ahead + 1);
+            uint2 vv[4], vn[4];
+            auto fetch = [&](uint2 (&dst)[4], int jj0) {
+#pragma unroll
+                for (int a = 0; a < 4; ++a) {
+                    const int j = jj0 + 8 * a + 4 * half;
+                    dst[a] = (jj0 < n_main && j < n_vis) ? *reinterpret_cast<const uint2 *>(vrow + j) : make_uint2(0u, 0u);
+                }
+            };
+            fetch(vv, j0);
+            for (; j0 < n_main && j0 < n_vis; j0 += 32) {
+                fetch(vn, j0 + 32);
+                pv_step(vv, j0);
+#pragma unroll
+                for (int a = 0; a < 4; ++a) { vv[a] = vn[a]; }
             }
         }
         float u[4];
