@@ -173,6 +173,11 @@ spyb_status spyb_create(const spyb_config *config, spyb_backend **out) {
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, config->device_id) != cudaSuccess) { delete be; return SPYB_FAIL; }
     be->num_sms = prop.multiProcessorCount;
+    // CTAs of a mat-vec grid: a few SMs fewer than the chip has. The next kernel's CTAs then never have to wait for the
+    // SMs of the previous kernel's last CTAs (they are launched, and have their rings filling, before the previous
+    // kernel ends); measured on B200: 140 of 148 gives 1 % more tokens/s than 148, 132 less again.
+    if (be->num_sms >= 128) { be->num_sms -= 8; }
+    if (const char *v = std::getenv("SPYB_MV_SMS")) { const int n = std::atoi(v); if (n > 0 && n <= prop.multiProcessorCount) { be->num_sms = n; } }
     if (const char *v = std::getenv("SPYB_L2_PREFETCH_MB")) { const int mb = std::atoi(v); be->l2_prefetch_next = mb > 0; be->l2_prefetch_cap = (size_t)std::max(mb, 0) << 20; }   // tuning knob
     if (const char *v = std::getenv("SPYB_MV_CTAS_PER_SM")) { be->mv_ctas_per_sm = std::max(1, std::min(2, std::atoi(v))); }   // tuning knob
     if (const char *v = std::getenv("SPYB_MV_S")) { be->mv_force_s = std::atoi(v); }         // tuning knobs
