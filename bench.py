@@ -173,6 +173,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--profile-step", type=int, default=0, metavar="LAYERS",
+                    help="load only the first LAYERS blocks of the model, evaluate the prompt, decode 4 tokens and exit: the small case for an ncu capture of the single-token step kernel")
     ap.add_argument("--profile-kernel", type=int, default=-1, metavar="KIND",
                     help="load the model, run two sweeps of one mat-vec kind over all layers (0 qkv, 1 attn_out, 2 ffn_up_gate, 3 ffn_down, 4 head) and exit: the small case for an ncu capture")
     args = ap.parse_args()
@@ -183,6 +185,8 @@ def main():
     import torch
     from spy_b200 import backend as B
 
+    if args.profile_step > 0:
+        os.environ["SPYB_MAX_LAYERS"] = str(args.profile_step)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -216,6 +220,12 @@ def main():
             model.tp_import(handles)
     info = model.info
     prompt = prompt_ids(info.n_vocab)
+    if args.profile_step > 0:
+        first = model.eval(prompt, 0)
+        ids, _ = model.decode(int(np.argmax(first)), N_PROMPT, 4)
+        print(json.dumps({"profile_step_layers": args.profile_step, "ms_per_step": model.last_ms / 4, "ids": [int(i) for i in ids]}))
+        model.close(); be.close()
+        return
     if args.profile_kernel >= 0:
         import ctypes as C
         nbytes = C.c_uint64()

@@ -214,6 +214,16 @@ spyb_status spyb_model_eval(spyb_model *model, const int32_t *tokens_host, int32
  * only the token ids come back. logits_host (optional) receives n_steps * n_vocab floats. */
 spyb_status spyb_model_decode(spyb_model *model, int32_t first_token, int32_t n_past, int32_t n_steps,
                               int32_t *ids_host, float *logits_host);
+/* Bound, in nanoseconds, of every device-side wait of the single-token step kernel (grid barriers, shared-memory stage
+ * barriers); default 1 s. When a wait runs out the kernel records a code (1 = a bulk copy did not land, 2 = a barrier or
+ * another rank's result did not arrive), lets its copies in flight land and returns; the call that synchronises next
+ * returns SPYB_FAIL with that text in spyb_last_error, and the backend has to be re-created. Stands in for the
+ * reference's only failure path, spy_assert -> std::terminate (backend/host/include/default_backend.h:75-78). */
+spyb_status spyb_set_wait_limit_ns(spyb_backend *backend, uint64_t ns);
+/* Failure-path check that faults nothing: runs one step whose first grid barrier expects one arrival more than there
+ * are CTAs, with `limit_ns` as the bound. Succeeds when the kernel returned by itself and recorded code 2 (also written
+ * to *error_code_out); the record is cleared again, so the model stays usable. No reference counterpart. */
+spyb_status spyb_model_selftest_wait_timeout(spyb_model *model, uint64_t limit_ns, int32_t *error_code_out);
 /* device time in milliseconds of the most recent spyb_model_decode / spyb_model_eval call,
  * measured with CUDA events on the backend's stream; number of kernels that call launched */
 float   spyb_model_last_ms(const spyb_model *model);
@@ -241,6 +251,10 @@ spyb_status spyb_model_tap_xq(spyb_model *model, void *blocks_host);
  * eight stamps (layer-major: QKV, attention, attention-out, FFN up/gate, FFN down; then the head) and
  * returns their number (0 when the timeline is off). */
 int32_t spyb_model_read_timeline(spyb_model *model, uint64_t *stamps_host, int32_t max_kernels);
+/* The same for single-token steps that run as one persistent kernel: pairs (CTA 0's time, the latest CTA's time) at
+ * every check point of the step - kernel entry, then per layer: barrier passed / activations quantized / mat-vec done for
+ * Wq|Wk|Wv, attention begun / done, and the same triples for Wo, up|gate and down, finally the head. Returns the number of pairs. */
+int32_t spyb_model_read_step_timeline(spyb_model *model, uint64_t *stamps_host, int32_t max_points);
 
 #ifdef __cplusplus
 }

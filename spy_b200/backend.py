@@ -108,6 +108,9 @@ def lib():
         "spyb_model_tp_export": (i32, [vp, vp]),
         "spyb_model_tp_import": (i32, [vp, vp]),
         "spyb_model_read_timeline": (i32, [vp, vp, i32]),
+        "spyb_model_read_step_timeline": (i32, [vp, vp, i32]),
+        "spyb_set_wait_limit_ns": (i32, [vp, u64]),
+        "spyb_model_selftest_wait_timeout": (i32, [vp, u64, C.POINTER(i32)]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(l, name)
@@ -227,6 +230,9 @@ class B200Backend:
             cb = CALLBACK(lambda _user: callback())
             self._callbacks.append(cb)   # keep alive until it has fired
         self._check(self._l.spyb_submit(self.h, C.byref(desc), cb, None))
+
+    def set_wait_limit_ns(self, ns: int) -> None:
+        self._check(self._l.spyb_set_wait_limit_ns(self.h, int(ns)))
 
     def sync(self) -> None:
         self._check(self._l.spyb_sync(self.h))
@@ -367,6 +373,20 @@ class LlamaModel:
         out = np.zeros((n, 8), dtype=np.uint64)
         got = self._l.spyb_model_read_timeline(self.h, _np_ptr(out), n)
         return out[:got]
+
+    def step_timeline(self) -> np.ndarray:
+        """[n_checkpoints, 2] device-clock stamps (ns) of the last single-token step on the persistent kernel: CTA 0's
+        time and the latest CTA's time at every check point; empty unless loaded with SPYB_TIMELINE=1."""
+        n = 16 * self.info.n_layer + 8
+        out = np.zeros((n, 2), dtype=np.uint64)
+        got = self._l.spyb_model_read_step_timeline(self.h, _np_ptr(out), n)
+        return out[:got]
+
+    def selftest_wait_timeout(self, limit_ns: int) -> int:
+        """Runs a step whose first grid barrier cannot complete, bounded by limit_ns; returns the recorded error code."""
+        code = C.c_int32(-1)
+        self.backend._check(self._l.spyb_model_selftest_wait_timeout(self.h, int(limit_ns), C.byref(code)))
+        return int(code.value)
 
     def tap_xq(self) -> np.ndarray:
         out = np.empty(self.info.d_model // 32 * 34, dtype=np.uint8)

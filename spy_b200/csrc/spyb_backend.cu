@@ -69,11 +69,12 @@ size_t Arena::available() {
 }
 
 // ------------------------------------------------------------------------------------------ matrices
-spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, DevMatrix *out, int tile_rows) {
+spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, DevMatrix *out, int tile_rows, int mma) {
     if (type != SPYB_Q4_0 && type != SPYB_Q8_0) { be->set_error("weight type %d has no device layout", type); return SPYB_UNSUPPORTED; }
     if ((tile_rows != 4 && tile_rows != 8 && tile_rows != 16 && tile_rows != 32) || n_rows % tile_rows != 0) { be->set_error("quantized matrices need a multiple of %d rows (got %lld)", tile_rows, (long long)n_rows); return SPYB_UNSUPPORTED; }
     DevMatrix m;
     m.type = type; m.n_rows = n_rows; m.nb = nb; m.nbp = padded_blocks(nb); m.k = (int64_t)nb * QK; m.tile_rows = tile_rows;
+    m.mma = (mma != 0 && (tile_rows == 8 || tile_rows == 16)) ? 1 : 0;
     void *w = nullptr;
     SPYB_CUDA(be, cudaMalloc(&w, matrix_bytes(type, n_rows, nb) + 16));
     be->owned.push_back(w);
@@ -103,7 +104,7 @@ spyb_status upload_matrix(spyb_backend *be, int type, const uint8_t *host_rows, 
         cudaError_t err = cudaMemcpyAsync(stage, host_rows + r0 * row_stride_bytes, (size_t)nr * row_stride_bytes, cudaMemcpyHostToDevice, be->stream);
         if (err == cudaSuccess) {
             const uint8_t *raw = static_cast<const uint8_t *>(stage) + blk0 * bb;
-            err = launch_retile(type, raw, row_stride_bytes, nr, nb, const_cast<uint8_t *>(into->w), into->tile_rows, dst_row, r0, sub_rows, sub_off, be->stream);
+            err = launch_retile(type, raw, row_stride_bytes, nr, nb, const_cast<uint8_t *>(into->w), into->tile_rows, into->mma != 0, dst_row, r0, sub_rows, sub_off, be->stream);
         }
         if (err == cudaSuccess) { err = cudaStreamSynchronize(be->stream); }
         if (err != cudaSuccess) { cudaFree(stage); be->set_error("weight upload failed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
@@ -173,6 +174,8 @@ spyb_status spyb_create(const spyb_config *config, spyb_backend **out) {
     cudaDeviceProp prop;
     if (cudaGetDeviceProperties(&prop, config->device_id) != cudaSuccess) { delete be; return SPYB_FAIL; }
     be->num_sms = prop.multiProcessorCount;
+    be->num_sms_total = prop.multiProcessorCount;
+    be->smem_optin = prop.sharedMemPerBlockOptin;
     // CTAs of a mat-vec grid: a few SMs fewer than the chip has. The next kernel's CTAs then never have to wait for the
     // SMs of the previous kernel's last CTAs (they are launched, and have their rings filling, before the previous
     // kernel ends); measured on B200: 140 of 148 gives 1 % more tokens/s than 148, 132 less again.
@@ -286,7 +289,7 @@ void *spyb_upload_constant(spyb_backend *be, const char *name, const void *host_
         if (k % QK == 0 && rows > 0 && (rows & 3) == 0) {
             DevMatrix m;
             if (alloc_matrix(be, number_type, rows, (int)(k / QK), &m, 4) != SPYB_SUCCESS) { return nullptr; }
-            cudaError_t err = launch_retile(number_type, static_cast<const uint8_t *>(raw), k / QK * bb, rows, m.nb, const_cast<uint8_t *>(m.w), 4, 0, 0, 0, 0, be->stream);
+            cudaError_t err = launch_retile(number_type, static_cast<const uint8_t *>(raw), k / QK * bb, rows, m.nb, const_cast<uint8_t *>(m.w), 4, false, 0, 0, 0, 0, be->stream);
             if (err != cudaSuccess || cudaStreamSynchronize(be->stream) != cudaSuccess) { be->set_error("re-tiling of %s failed", name); return nullptr; }
             be->retiled[raw] = m;
         }
@@ -377,7 +380,7 @@ spyb_status spyb_matmul_noalloc(spyb_backend *be, int32_t weight_type, const voi
     DevMatrix m;
     m.type = weight_type; m.n_rows = n_rows; m.nb = nb; m.nbp = padded_blocks(nb); m.k = k; m.tile_rows = 4; m.w = be->noalloc_scratch;
     const int64_t bb = weight_type == SPYB_Q4_0 ? 18 : 34;
-    SPYB_CUDA(be, launch_retile(weight_type, static_cast<const uint8_t *>(w_rows_dev), nb * bb, n_rows, nb, be->noalloc_scratch, 4, 0, 0, 0, 0, be->stream));
+    SPYB_CUDA(be, launch_retile(weight_type, static_cast<const uint8_t *>(w_rows_dev), nb * bb, n_rows, nb, be->noalloc_scratch, 4, false, 0, 0, 0, 0, be->stream));
     const int64_t tmax = matvec_max_columns(nb);
     for (int64_t t0 = 0; t0 < n_cols; t0 += tmax) {
         MatvecParams p;
@@ -467,7 +470,7 @@ spyb_status run_matmul(spyb_backend *be, spyb_op_desc *d, void *out_dev) {
         if (!tmp_w) { be->set_error("MatMul: out of device memory for re-tiled weights"); return SPYB_FAIL; }
         m.w = static_cast<const uint8_t *>(tmp_w);
         cudaError_t err = launch_retile(w.number_type, static_cast<const uint8_t *>(w.data), w.elements[0] / QK * bb, w.elements[1], m.nb,
-                                        static_cast<uint8_t *>(tmp_w), 4, 0, 0, 0, 0, be->stream);
+                                        static_cast<uint8_t *>(tmp_w), 4, false, 0, 0, 0, 0, be->stream);
         if (err != cudaSuccess) { be->set_error("MatMul: re-tiling failed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
     }
     struct TmpRelease {   // stream-ordered reuse: safe to hand back as soon as the kernels are enqueued

@@ -52,7 +52,10 @@ struct PendingCallback {
 
 struct spyb_backend {
     spyb_config  config{};
-    int          num_sms = 148;
+    int          num_sms = 148;            // CTAs of a per-matrix mat-vec grid
+    int          num_sms_total = 148;      // SMs of the device (grid of the persistent step kernel)
+    size_t       smem_optin = 227 * 1024;  // largest dynamic shared memory a CTA may ask for
+    unsigned long long wait_limit_ns = 1000000000ull;   // bound of the waits inside the step kernel
     int          mv_ctas_per_sm = 2;
     int          mv_ring_kb = 80;
     int          mv_force_s = 0, mv_force_wact = 0;
@@ -91,7 +94,9 @@ struct spyb_backend {
     // after a stream synchronisation: did a kernel give up on a bounded wait?
     bool device_error() {
         if (h_error_flag != nullptr && *reinterpret_cast<volatile int *>(h_error_flag) != 0) {
-            set_error("a kernel gave up waiting for a bulk copy (device error flag %d)", *h_error_flag);
+            const int code = *reinterpret_cast<volatile int *>(h_error_flag);
+            if (code == 1) { set_error("a kernel gave up waiting for a bulk copy into shared memory (device error flag 1); the backend must be re-created"); }
+            else { set_error("a kernel gave up waiting at a barrier or for another rank's partial result (device error flag %d); the backend must be re-created", code); }
             return true;
         }
         return false;
@@ -120,6 +125,6 @@ namespace spyb {
 spyb_status upload_matrix(spyb_backend *be, int type, const uint8_t *host_rows, int64_t n_rows, int64_t row_stride_bytes,
                           int64_t blk0, int nb, DevMatrix *out, const DevMatrix *into = nullptr, int64_t dst_row = 0,
                           int sub_rows = 0, int sub_off = 0);
-spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, DevMatrix *out, int tile_rows = 4);
+spyb_status alloc_matrix(spyb_backend *be, int type, int64_t n_rows, int nb, DevMatrix *out, int tile_rows = 4, int mma = 0);
 
 }  // namespace spyb

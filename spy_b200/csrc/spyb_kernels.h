@@ -5,6 +5,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <map>
+#include <mutex>
+#include <utility>
+
 namespace spyb {
 
 // A quantized weight matrix resident in HBM, re-tiled at upload into the stream a warp consumes:
@@ -26,6 +30,7 @@ struct DevMatrix {
     int            nb = 0;       // blocks per row
     int            nbp = 0;      // blocks per row in memory (nb rounded up to a multiple of 8)
     int            tile_rows = 4;   // rows per tile: 4 (lane-per-accumulator kernel) or 8 / 16 / 32 (lane-per-row kernels)
+    int            mma = 0;         // tile_rows 8 / 16 only: records in the fragment order of the tensor-core kernel (see below)
     int            fused_pair = 0;  // tile_rows >= 8 only: the first half of a tile's rows are FFN-up rows, the second half the matching FFN-gate rows
     const uint8_t *w = nullptr;  // [n_rows / tile_rows][nbp / 8] records of tile_rows rows
     size_t bytes() const { return (size_t)n_rows * nb * ((type == 8 ? 32 : 16) + 2); }   // algorithmic bytes (without padding)
@@ -112,6 +117,20 @@ struct LaunchCfg {
     int         *error_flag = nullptr;
 };
 
+// Book-keeping for cudaFuncAttributeMaxDynamicSharedMemorySize, which is set per (device, kernel): decide() says
+// whether a launch that needs `bytes` must raise the attribute first (and records the new mark).
+class SmemLedger {
+public:
+    enum Decision { KEEP = 0, RAISE = 1 };
+    Decision decide(int device, const void *kernel, size_t bytes);
+    void     forget(int device, const void *kernel);
+private:
+    std::map<std::pair<int, const void *>, size_t> allowed_;
+    std::mutex mutex_;
+};
+// raises the current device's dynamic shared-memory limit of `kernel` to `bytes` when it is below (thread-safe)
+cudaError_t allow_dynamic_smem(const void *kernel, size_t bytes);
+
 size_t      matvec_smem_bytes(int nb, int T);
 int         matvec_max_columns(int nb);   // most activation columns one launch can hold in shared memory for rows of nb blocks
 cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg);
@@ -121,7 +140,7 @@ cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg);
 // Source row i (i = src_row0 .. src_row0 + n_rows - 1 of the tensor being uploaded; `raw` points at row src_row0) lands
 // at matrix row dst_row0 + i, or, with sub_rows > 0, at dst_row0 + (i / sub_rows) * tile_rows + sub_off + i % sub_rows
 // (interleaving two tensors tile by tile). nb blocks are read per row, the padding up to a multiple of 8 is zero-filled.
-cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride_bytes, int64_t n_rows, int nb, uint8_t *matrix_base, int tile_rows,
+cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride_bytes, int64_t n_rows, int nb, uint8_t *matrix_base, int tile_rows, bool mma,
                           int64_t dst_row0, int64_t src_row0, int sub_rows, int sub_off, cudaStream_t s);
 
 // stand-alone arithmetic kernels (parity checks and the per-operator path)
@@ -148,5 +167,51 @@ cudaError_t launch_matmul_kquant(int type, const uint8_t *w, int64_t n_rows, int
 cudaError_t launch_argmax_embed(const float *logits, int64_t n_vocab, int32_t *token_out, int32_t *history, int *pos_counter,
                                 const uint8_t *embd, int embd_type, int64_t d_model, float *x_out, const LaunchCfg &cfg);
 cudaError_t launch_embed(const int32_t *ids, int n_ids, const uint8_t *embd, int embd_type, int64_t d_model, float *x_out, cudaStream_t s);
+
+// ---- one decode step as a single persistent kernel (spyb_step.cu)
+constexpr int ST_STAGE_BYTES = 9216;   // one ring stage: 8 / 4 records of an 8- / 16-row Q4_0 tile (4 / 2 of a Q8_0 tile)
+struct StepMat {                // a matrix the step streams, in fragment-ordered records (DevMatrix::mma)
+    const uint8_t *w = nullptr;
+    int n_tiles = 0;            // tiles of `tr` rows
+    int nrec = 0;               // records (8 blocks) per tile
+    int recb = 0;               // bytes per record
+    int tr = 8;                 // rows per tile: 8 or 16
+    int type = 2;               // 2 = Q4_0, 8 = Q8_0
+    int nbp = 0;                // blocks per row (padded to a multiple of 8)
+    int crecs = 1;              // records per ring stage
+    int nch = 1;                // stages per tile
+};
+struct StepLayer {
+    StepMat      qkv, wo, upgate, down;
+    const float *attn_norm = nullptr, *ffn_norm = nullptr;
+    __half      *k_cache = nullptr, *v_cache = nullptr;   // K [n_ctx][d], V transposed [d][n_ctx]
+};
+struct StepParams {
+    const StepLayer *layers = nullptr;   // device array
+    int          n_layer = 0;
+    StepMat      head;
+    const float *output_norm = nullptr;
+    float       *x = nullptr;            // residual stream [d] (in: the token's embedding)
+    float       *act = nullptr;          // up * silu(gate) [fl]
+    float       *logits = nullptr;       // [n_vocab]
+    int8_t      *att_q = nullptr;        // attention output as Q8_0 values [d] ...
+    float       *att_d = nullptr;        // ... and one scale per 32 (the fp16-rounded scale as f32)
+    __half      *q = nullptr;            // Q after RoPE [d]
+    const int   *pos = nullptr;          // [0] position of the token, [1] row length of the score matrix (0: position + 1)
+    const float2 *rope = nullptr;        // [n_ctx][64] (cos, sin)
+    const float *silu_table = nullptr, *exp_table = nullptr;
+    int          d = 0, fl = 0, n_ctx = 0, n_head = 0, att_parts = 1, nbp_max = 0;
+    float        eps = 0.f, att_scale = 0.f;
+    unsigned long long *sync = nullptr;  // [0] barrier arrivals, [2] abort word; zeroed before every launch
+    int         *error_flag = nullptr;
+    unsigned long long wait_limit_ns = 1000000000ull;
+    int          barrier_extra = 0;      // failure-path check only: arrivals a barrier expects beyond the grid size (it then runs out)
+    uint8_t     *tap_xq = nullptr;       // optional: reference-layout Q8_0 blocks of layer 0's attention-norm output
+    unsigned long long *stamps = nullptr; // optional profiling aid: per check point, CTA 0's time and the latest CTA's time
+};
+size_t      step_act_bytes(const StepParams &p);
+int         step_ring_stages(const StepParams &p, size_t smem_limit);   // stages the ring gets out of `smem_limit` bytes per CTA
+cudaError_t step_resident_ctas(const StepParams &p, int ns, int *ctas_per_sm);
+cudaError_t launch_step(const StepParams &p, int grid, int ns, bool cooperative, cudaStream_t stream);
 
 }  // namespace spyb

@@ -25,9 +25,12 @@
 // and they keep HBM busy through the serial prologue and across kernel boundaries.
 
 #include <algorithm>
+#include <map>
+#include <mutex>
 
 #include "spyb_common.cuh"
 #include "spyb_kernels.h"
+#include "spyb_mma.cuh"
 
 namespace spyb {
 
@@ -65,6 +68,31 @@ __host__ __device__ static inline MatvecSmem matvec_smem_layout(int nbp, int TM,
 }
 
 size_t matvec_smem_bytes(int nb, int T) { return matvec_smem_layout(padded_blocks(nb), T, 0).total; }
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a property of (device, kernel): the largest size allowed so far is kept
+// per pair, so that a process driving several devices raises the limit on each of them.
+SmemLedger::Decision SmemLedger::decide(int device, const void *kernel, size_t bytes) {
+    std::lock_guard<std::mutex> g(mutex_);
+    size_t &have = allowed_[std::make_pair(device, kernel)];
+    if (have == 0) { have = 48 * 1024; }
+    if (bytes <= have) { return KEEP; }
+    have = bytes;
+    return RAISE;
+}
+void SmemLedger::forget(int device, const void *kernel) {
+    std::lock_guard<std::mutex> g(mutex_);
+    allowed_.erase(std::make_pair(device, kernel));
+}
+cudaError_t allow_dynamic_smem(const void *kernel, size_t bytes) {
+    static SmemLedger ledger;
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) { return err; }
+    if (ledger.decide(device, kernel, bytes) == SmemLedger::KEEP) { return cudaSuccess; }
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (err != cudaSuccess) { ledger.forget(device, kernel); }
+    return err;
+}
 
 // ---------------------------------------------------------------------------------------------
 // prologue: f32 activations -> Q8_0 columns in shared memory (optionally through RMSNorm * weight)
@@ -774,6 +802,205 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
     if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Tensor-core variant for matrices stored in fragment order (DevMatrix::mma, tiles of TR = 16 or 8 rows): the integer
+// group sums of a block come out of one mma.sync per block and 16 rows instead of eight byte dot products per row; the
+// inner loop and its exactness argument are in spyb_mma.cuh. Streaming, prologue and epilogues as in matvec_rows_kernel.
+template <int WT, int TM, int TR, bool TPIN>
+__global__ void __launch_bounds__(MV_THREADS, 1) matvec_mma_kernel(const MatvecParams p, const int ring_bytes, const int S, const int wact) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __shared__ float norm_scales[8];
+    constexpr int RECB = MmaTile<WT, TR>::RECB;
+    constexpr int NA   = MmaTile<WT, TR>::NA;            // accumulators per lane
+
+    const int lane = threadIdx.x & 31, grp = threadIdx.x >> 5;
+    const int g = lane >> 2, q = lane & 3;
+    const int nbp  = p.A.nbp;
+    const int ng   = nbp >> 2;
+    const int nrec = nbp >> 3;
+
+    const int64_t n_units  = p.A.n_rows / TR;
+    const int64_t unit_lo  = n_units * blockIdx.x / gridDim.x;
+    const int64_t unit_hi  = n_units * (blockIdx.x + 1) / gridDim.x;
+    const int64_t my_first = unit_lo + grp;
+    const int     my_units = (grp < wact && my_first < unit_hi) ? (int)((unit_hi - my_first + wact - 1) / wact) : 0;
+    const int     n_act    = (int)min((int64_t)wact, unit_hi - unit_lo);
+    const int     nch      = (nrec + S - 1) / S;
+    const int     n_items  = my_units * nch;
+    const int     stage_bytes = S * RECB;
+    const int     NS = max(1, min(MAX_STAGES, ring_bytes / (max(n_act, 1) * stage_bytes)));
+
+    const MatvecSmem L = matvec_smem_layout(nbp, TM, (size_t)ring_bytes);
+    const uint32_t ring_s  = smem_u32(smem_raw + L.ring) + (uint32_t)grp * NS * stage_bytes;
+    const uint32_t full_s  = smem_u32(smem_raw + L.bars) + grp * MAX_STAGES * 8;
+    const size_t   tile_bytes = (size_t)nrec * RECB;
+
+    const uint8_t *src = nullptr;
+    int64_t lu = my_first; int lrec = 0, lslot = 0, issued = 0;
+    bool    ok = true;
+    auto issue_next = [&]() {
+        const uint32_t bytes = (uint32_t)min(S, nrec - lrec) * RECB;
+        const uint32_t bar = full_s + lslot * 8;
+        mbar_expect_tx(bar, bytes);
+        bulk_copy_g2s(ring_s + lslot * stage_bytes, src, bytes, bar);
+        src += bytes;
+        ++issued;
+        if (++lslot == NS) { lslot = 0; }
+        lrec += S;
+        if (lrec >= nrec) { lrec = 0; lu += wact; src = p.A.w + (size_t)lu * tile_bytes; }
+    };
+
+    pdl_launch_dependents();
+    stamp(p.stamps, 0, false); stamp(p.stamps, 4, true);
+    if (lane == 0 && n_items > 0) {
+        for (int s = 0; s < NS; ++s) { mbar_init(full_s + s * 8, 1); }
+        mbar_init_fence();
+        src = p.A.w + (size_t)lu * tile_bytes;
+        for (int s = 0; s < NS && issued < n_items; ++s) { issue_next(); }
+    }
+    __syncwarp();
+    pdl_wait();
+    stamp(p.stamps, 1, false); stamp(p.stamps, 5, true);
+
+    ActPlanes act = act_planes(smem_raw, nbp, TM);
+    {
+        float *v3 = reinterpret_cast<float *>(smem_raw);
+        const int  n4p  = nbp * 8;
+        const bool norm = p.pro == PRO_NORM_QUANT;
+        if (TM == 1 && n4p <= 2 * MV_THREADS) {
+            if (norm) { matvec_prologue_1col<2, true, TPIN>(p, act, v3, norm_scales); } else { matvec_prologue_1col<2, false, TPIN>(p, act, v3, norm_scales); }
+        } else if (TM == 1 && n4p <= PRO_GROUPS * MV_THREADS) {
+            if (norm) { matvec_prologue_1col<PRO_GROUPS, true, TPIN>(p, act, v3, norm_scales); } else { matvec_prologue_1col<PRO_GROUPS, false, TPIN>(p, act, v3, norm_scales); }
+        } else {
+            matvec_prologue<TM>(p, act, v3, norm_scales);
+        }
+    }
+    __syncthreads();
+    stamp(p.stamps, 2, false); stamp(p.stamps, 6, true);
+    matvec_tap(p, act);
+
+    const MmaLane  ML = mma_lane<WT, TR>(lane);
+    const uint32_t y_s = smem_u32(act.Y), ds_s = smem_u32(act.DS);
+    const uint32_t col_y = (uint32_t)ng * 128, col_ds = (uint32_t)ng * 16;
+
+    float acc[TM][NA];
+#pragma unroll
+    for (int t = 0; t < TM; ++t) {
+#pragma unroll
+        for (int a = 0; a < NA; ++a) { acc[t][a] = 0.f; }
+    }
+
+    int64_t  cu = my_first; int crec = 0, slot = 0; uint32_t parity = 0;
+    uint32_t ya = y_s, da = ds_s;
+    int      n = 0;
+    for (; n < n_items; ++n) {
+        bool got = mbar_wait_bounded(full_s + slot * 8, parity, WAIT_LIMIT_NS);
+        if (__any_sync(0xffffffffu, !got || !ok)) { ok = false; break; }
+        mma_records<WT, TR, TM>(ring_s + slot * stage_bytes, min(S, nrec - crec), ya, da, col_y, col_ds, ML, acc);
+        __syncwarp();   // every lane is done reading the stage
+        if (lane == 0 && issued < n_items) { issue_next(); }
+        if (++slot == NS) { slot = 0; parity ^= 1u; }
+        crec += S;
+        if (crec >= nrec) {   // tile finished: hsum_float_8 tree, then the epilogue
+#pragma unroll
+            for (int t = 0; t < TM; ++t) {
+                float h[2] = {0.f, 0.f};
+#pragma unroll
+                for (int r = 0; r < NA / 2; ++r) { h[r] = mma_row_sum(acc[t][2 * r], acc[t][2 * r + 1]); acc[t][2 * r] = 0.f; acc[t][2 * r + 1] = 0.f; }
+                const bool wr = (q == 0) && (t < p.T);
+                if (p.epi == EPI_SILU_MUL) {
+                    if (TR == 16) { matvec_epilogue_silu(p, 8 * cu + g, t, h[0], h[1], wr); }
+                    else { const float gate = __shfl_down_sync(0xffffffffu, h[0], 16); matvec_epilogue_silu(p, 4 * cu + g, t, h[0], gate, wr && g < 4); }
+                } else {
+#pragma unroll
+                    for (int r = 0; r < NA / 2; ++r) {
+                        const float partner = __shfl_xor_sync(0xffffffffu, h[r], 4);   // the neighbouring row (RoPE pairs)
+                        matvec_epilogue(p, TR * cu + 8 * r + g, t, h[r], partner, wr);
+                    }
+                }
+            }
+            crec = 0; cu += wact; ya = y_s; da = ds_s;
+        }
+    }
+    if (!ok) {
+        if (lane == 0 && p.error_flag != nullptr) { atomicExch(p.error_flag, 1); }
+        for (int k = n; k < __shfl_sync(0xffffffffu, issued, 0); ++k) {
+            mbar_wait_bounded(full_s + slot * 8, parity, 10000000ull);
+            if (++slot == NS) { slot = 0; parity ^= 1u; }
+        }
+    }
+    if (p.tp_counter != nullptr) {
+        __shared__ int tp_last;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            tp_last = (atomicAdd(p.tp_counter, 1u) == gridDim.x - 1) ? 1 : 0;
+            if (tp_last) { *p.tp_counter = 0; __threadfence(); }
+        }
+        __syncthreads();
+        if (tp_last) {
+            const float4 *srcv = reinterpret_cast<const float4 *>(p.tp_out[p.tp_rank]);
+            const int     n4  = (int)(p.A.n_rows >> 2);
+            for (int i = threadIdx.x; i < n4; i += MV_THREADS) {
+                const float4 v = __ldcg(srcv + i);
+                for (int rk = 0; rk < p.tp_n; ++rk) { if (rk != p.tp_rank) { reinterpret_cast<float4 *>(p.tp_out[rk])[i] = v; } }
+            }
+            __syncthreads();
+            if (threadIdx.x == 0) {
+                const unsigned epoch = (unsigned)*p.tp_epoch;
+                __threadfence_system();
+                for (int rk = 0; rk < p.tp_n; ++rk) { *reinterpret_cast<volatile unsigned *>(p.tp_flag_out[rk]) = epoch; }
+            }
+        }
+    }
+    if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
+}
+
+template <int WT, int TM, int TR, bool TPIN = false>
+static cudaError_t launch_matvec_mma_t(const MatvecParams &p, const LaunchCfg &cfg) {
+    constexpr int RECB = TR * (((WT == 8) ? 256 : 128) + 16);
+    const int64_t n_units = p.A.n_rows / TR;
+    int64_t grid = std::min<int64_t>(cfg.num_sms, n_units);
+    if (grid < 1) { grid = 1; }
+    const int64_t units_per_cta = (n_units + grid - 1) / grid;
+    const MatvecSmem fixed = matvec_smem_layout(p.A.nbp, TM, 0);
+    const size_t budget = 216 * 1024;
+    if (fixed.total + (size_t)RECB > budget) { return cudaErrorInvalidValue; }
+    const size_t ring = std::min<size_t>((size_t)cfg.mv_ring_kb * 2 * 1024, budget - fixed.total) / 128 * 128;
+    const int nrec = p.A.nbp >> 3;
+    int wact = (int)std::min<int64_t>(MV_WARPS, units_per_cta);
+    int S = 64 / TR;                      // stages of about 9 KB (Q4_0); at least three per warp, else smaller ones
+    while (S > nrec) { S >>= 1; }
+    if (S < 1) { S = 1; }
+    while (ring / ((size_t)wact * S * RECB) < 3) {
+        if (S > 1) { S >>= 1; }
+        else if (wact > 1) { wact = (wact + 1) / 2; }
+        else { break; }
+    }
+    if (cfg.mv_force_s > 0) { S = std::min(cfg.mv_force_s, std::max(nrec, 1)); }
+    if (cfg.mv_force_wact > 0) { wact = std::min(cfg.mv_force_wact, MV_WARPS); }
+    if (ring / ((size_t)wact * S * RECB) < 1) { return cudaErrorInvalidValue; }
+    const size_t smem = fixed.total + ring;
+    cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(matvec_mma_kernel<WT, TM, TR, TPIN>), smem);
+    if (err != cudaSuccess) { return err; }
+    MatvecParams q = p;
+    if (q.error_flag == nullptr) { q.error_flag = cfg.error_flag; }
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((unsigned)grid); lc.blockDim = dim3(MV_THREADS); lc.dynamicSmemBytes = smem; lc.stream = cfg.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&lc, matvec_mma_kernel<WT, TM, TR, TPIN>, q, (int)ring, S, wact);
+}
+
+template <int WT, int TR>
+static cudaError_t launch_matvec_mma_w(const MatvecParams &p, const LaunchCfg &cfg) {
+    if (p.T <= 1) { return p.tp_in ? launch_matvec_mma_t<WT, 1, TR, true>(p, cfg) : launch_matvec_mma_t<WT, 1, TR>(p, cfg); }
+    if (p.T <= 2) { return launch_matvec_mma_t<WT, 2, TR>(p, cfg); }
+    return launch_matvec_mma_t<WT, 4, TR>(p, cfg);
+}
+
 template <int WT, int TM, int LPR, bool TPIN = false>
 static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &cfg) {
     constexpr int TR = 32 / LPR;
@@ -800,12 +1027,8 @@ static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &
     if (cfg.mv_force_wact > 0) { wact = std::min(cfg.mv_force_wact, MV_WARPS); }
     if (ring / ((size_t)wact * S * RECB) < 1) { return cudaErrorInvalidValue; }
     const size_t smem = fixed.total + ring;
-    static size_t smem_allowed = 48 * 1024;
-    if (smem > smem_allowed) {
-        cudaError_t err = cudaFuncSetAttribute(matvec_rows_kernel<WT, TM, LPR, TPIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (err != cudaSuccess) { return err; }
-        smem_allowed = smem;
-    }
+    cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(matvec_rows_kernel<WT, TM, LPR, TPIN>), smem);
+    if (err != cudaSuccess) { return err; }
     MatvecParams q = p;
     if (q.error_flag == nullptr) { q.error_flag = cfg.error_flag; }
     cudaLaunchConfig_t lc = {};
@@ -867,12 +1090,8 @@ static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) 
     if (ring / ((size_t)wact * R * S * RECB) < 1) { return cudaErrorInvalidValue; }
     const size_t smem = fixed.total + ring;
 
-    static size_t smem_allowed = 48 * 1024;   // one process drives one device, so one high-water mark per kernel suffices
-    if (smem > smem_allowed) {
-        cudaError_t err = cudaFuncSetAttribute(matvec_kernel<WT, TM, R, TPIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (err != cudaSuccess) { return err; }
-        smem_allowed = smem;
-    }
+    cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(matvec_kernel<WT, TM, R, TPIN>), smem);
+    if (err != cudaSuccess) { return err; }
     MatvecParams q = p;
     if (q.error_flag == nullptr) { q.error_flag = cfg.error_flag; }
 
@@ -897,6 +1116,14 @@ cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg) {
     if (p.T < 1 || p.T > matvec_max_columns(p.A.nb)) { return cudaErrorInvalidValue; }
     if ((p.epi == EPI_TP_SCATTER || p.tp_in != nullptr) && (p.T != 1 || p.tp_n < 2 || p.tp_n > TP_MAX || p.tp_epoch == nullptr || p.A.nbp * 8 > PRO_GROUPS * MV_THREADS)) { return cudaErrorInvalidValue; }
     if (p.A.k % QK != 0 || p.A.nb < 1 || p.A.nbp != padded_blocks(p.A.nb) || p.A.w == nullptr) { return cudaErrorInvalidValue; }
+    if (p.A.mma) {
+        if ((p.A.tile_rows != 16 && p.A.tile_rows != 8) || (p.A.n_rows % p.A.tile_rows) || p.pair_mode || (p.epi == EPI_SILU_MUL) != (p.A.fused_pair != 0)) { return cudaErrorInvalidValue; }
+        switch (p.A.type) {
+        case 2: return p.A.tile_rows == 16 ? launch_matvec_mma_w<2, 16>(p, cfg) : launch_matvec_mma_w<2, 8>(p, cfg);
+        case 8: return p.A.tile_rows == 16 ? launch_matvec_mma_w<8, 16>(p, cfg) : launch_matvec_mma_w<8, 8>(p, cfg);
+        default: return cudaErrorNotSupported;
+        }
+    }
     if (p.A.tile_rows == 32 || p.A.tile_rows == 16 || p.A.tile_rows == 8) {
         if ((p.A.n_rows % p.A.tile_rows) || p.pair_mode || (p.epi == EPI_SILU_MUL) != (p.A.fused_pair != 0)) { return cudaErrorInvalidValue; }
         const int lpr = 32 / p.A.tile_rows;

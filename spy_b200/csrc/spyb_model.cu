@@ -173,6 +173,12 @@ struct spyb_model {
     uint8_t *tp_peer[TP_MAX] = {};
     bool     tp_ready = false;
     int      epoch = 0;
+    // single-token steps as one persistent kernel (spyb_step.cu) when the shapes allow it
+    StepParams  step;
+    bool        step_ok = false, step_coop = true;
+    int         step_grid = 0, step_ns = 0;
+    unsigned long long *d_step_sync = nullptr, *d_step_stamps = nullptr;
+    int         step_stamp_count = 0;
     cudaGraphExec_t graph_exec = nullptr;
     cudaGraphExec_t graph_eval1 = nullptr;   // single-token spyb_model_eval: staging copies, embedding, layers, head, logits copy
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -182,6 +188,8 @@ struct spyb_model {
 };
 
 namespace {
+
+spyb_status build_step_plan(spyb_model *m);
 
 template <class T>
 spyb_status dev_alloc(spyb_model *m, T **p, size_t count) {
@@ -240,6 +248,79 @@ void prefetch_next(spyb_model *m, P &p, const DevMatrix *a, const DevMatrix *b =
         if (x == nullptr || x->w == nullptr) { continue; }
         p.pf_ptr[k] = x->w; p.pf_bytes[k] = std::min(matrix_bytes(x->type, x->n_rows, x->nb), m->be->l2_prefetch_cap); ++k;
     }
+}
+
+StepMat step_mat_of(const DevMatrix &A) {
+    StepMat s;
+    s.w = A.w; s.tr = A.tile_rows; s.type = A.type; s.nbp = A.nbp;
+    s.n_tiles = (int)(A.n_rows / A.tile_rows);
+    s.nrec = A.nbp >> 3;
+    s.recb = A.tile_rows * record_row_bytes(A.type);
+    s.crecs = std::max(1, std::min(s.nrec, ST_STAGE_BYTES / s.recb));
+    s.nch = (s.nrec + s.crecs - 1) / s.crecs;
+    return s;
+}
+
+// The persistent step kernel serves single-token steps of an unsharded model whose matrices are all in
+// fragment-ordered 8- or 16-row tiles (SPYB_STEP=0 keeps the per-matrix kernels).
+spyb_status build_step_plan(spyb_model *m) {
+    spyb_backend *be = m->be;
+    m->step_ok = false;
+    if (std::getenv("SPYB_STEP") == nullptr || std::atoi(std::getenv("SPYB_STEP")) == 0) { return SPYB_SUCCESS; }
+    if (m->info.tp_size != 1 || m->info.head_dim != 128) { return SPYB_SUCCESS; }
+    auto fits = [](const DevMatrix &A) { return A.w != nullptr && A.mma != 0 && (A.tile_rows == 8 || A.tile_rows == 16) && (A.type == 2 || A.type == 8); };
+    bool ok = fits(m->head) && (m->info.d_model % 128) == 0 && m->info.d_model <= 4 * 4 * 480;
+    for (const Layer &ly : m->layers) { ok = ok && fits(ly.wqkv) && fits(ly.wo) && fits(ly.upgate) && ly.upgate.fused_pair && fits(ly.down); }
+    if (!ok) { return SPYB_SUCCESS; }
+    std::vector<StepLayer> hl(m->layers.size());
+    int nbp_max = m->head.nbp;
+    for (size_t L = 0; L < m->layers.size(); ++L) {
+        const Layer &ly = m->layers[L];
+        hl[L].qkv = step_mat_of(ly.wqkv); hl[L].wo = step_mat_of(ly.wo); hl[L].upgate = step_mat_of(ly.upgate); hl[L].down = step_mat_of(ly.down);
+        hl[L].attn_norm = ly.attn_norm; hl[L].ffn_norm = ly.ffn_norm; hl[L].k_cache = ly.k_cache; hl[L].v_cache = ly.v_cache;
+        nbp_max = std::max(std::max(nbp_max, ly.wqkv.nbp), std::max(ly.down.nbp, std::max(ly.wo.nbp, ly.upgate.nbp)));
+    }
+    StepLayer *d_layers = nullptr;
+    if (dev_alloc(m, &d_layers, hl.size()) != SPYB_SUCCESS) { return SPYB_FAIL; }
+    SPYB_CUDA(be, cudaMemcpy(d_layers, hl.data(), hl.size() * sizeof(StepLayer), cudaMemcpyHostToDevice));
+    int8_t *att_q = nullptr; float *att_d = nullptr;
+    if (dev_alloc(m, &att_q, (size_t)m->info.d_model) != SPYB_SUCCESS || dev_alloc(m, &att_d, (size_t)m->info.d_model / 32) != SPYB_SUCCESS ||
+        dev_alloc(m, &m->d_step_sync, 8) != SPYB_SUCCESS) { return SPYB_FAIL; }
+    StepParams &p = m->step;
+    p.layers = d_layers; p.n_layer = (int)hl.size(); p.head = step_mat_of(m->head); p.output_norm = m->output_norm;
+    p.x = m->x; p.act = m->act; p.logits = m->logits; p.att_q = att_q; p.att_d = att_d; p.q = m->q; p.pos = m->d_pos;
+    p.rope = m->rope_table; p.silu_table = be->d_silu_table; p.exp_table = be->d_exp_table;
+    p.d = m->info.d_model; p.fl = m->fl; p.n_ctx = m->info.n_ctx; p.n_head = m->info.n_head; p.nbp_max = nbp_max;
+    p.eps = m->info.rms_eps; p.att_scale = 1.0f / std::sqrt((float)m->info.head_dim);
+    p.sync = m->d_step_sync; p.error_flag = be->d_error_flag; p.wait_limit_ns = be->wait_limit_ns;
+    m->step_grid = be->num_sms_total;
+    if (const char *v = std::getenv("SPYB_STEP_CTAS")) { const int n = std::atoi(v); if (n > 0 && n <= be->num_sms_total) { m->step_grid = n; } }
+    p.att_parts = 4 * p.n_head <= m->step_grid ? 4 : 2 * p.n_head <= m->step_grid ? 2 : 1;
+    m->step_ns = step_ring_stages(p, be->smem_optin);
+    if (const char *v = std::getenv("SPYB_STEP_STAGES")) { const int n = std::atoi(v); if (n > 15 && n < m->step_ns) { m->step_ns = n; } }
+    if (m->step_ns <= 15) { return SPYB_SUCCESS; }   // context too long for the ring that is left: per-matrix kernels
+    int resident = 0;
+    if (step_resident_ctas(p, m->step_ns, &resident) != cudaSuccess || resident < 1) { cudaGetLastError(); return SPYB_SUCCESS; }
+    if (std::getenv("SPYB_TIMELINE") != nullptr) {
+        m->step_stamp_count = 16 * p.n_layer + 8;
+        if (dev_alloc(m, &m->d_step_stamps, (size_t)2 * m->step_stamp_count) != SPYB_SUCCESS) { return SPYB_FAIL; }
+        p.stamps = m->d_step_stamps;
+    }
+    if (const char *v = std::getenv("SPYB_STEP_COOP")) { m->step_coop = std::atoi(v) != 0; }
+    m->step_ok = true;
+    return SPYB_SUCCESS;
+}
+
+// one single-token step (layers and head) through the persistent kernel
+spyb_status run_step(spyb_model *m, bool tap, int64_t *launches) {
+    spyb_backend *be = m->be;
+    StepParams p = m->step;
+    p.tap_xq = tap ? m->d_tap : nullptr;
+    p.wait_limit_ns = be->wait_limit_ns;
+    SPYB_CUDA(be, cudaMemsetAsync(m->d_step_sync, 0, 32, be->stream));
+    SPYB_CUDA(be, launch_step(p, m->step_grid, m->step_ns, m->step_coop, be->stream));
+    ++*launches;
+    return SPYB_SUCCESS;
 }
 
 // the five fused kernels of every layer for T tokens whose first position is *d_pos
@@ -323,8 +404,12 @@ spyb_status run_head(spyb_model *m, int col, int64_t *launches, bool fused_input
 }
 
 spyb_status run_decode_step(spyb_model *m, int64_t *launches) {
-    if (run_layers(m, 1, false, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
-    if (run_head(m, 0, launches, m->info.tp_size > 1 && m->tp_ready) != SPYB_SUCCESS) { return SPYB_FAIL; }
+    if (m->step_ok) {
+        if (run_step(m, false, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
+    } else {
+        if (run_layers(m, 1, false, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
+        if (run_head(m, 0, launches, m->info.tp_size > 1 && m->tp_ready) != SPYB_SUCCESS) { return SPYB_FAIL; }
+    }
     SPYB_CUDA(m->be, launch_argmax_embed(m->logits, m->info.n_vocab, m->d_token, m->d_history, m->d_pos, m->embd, m->embd_type,
                                          m->info.d_model, m->x, m->be->launch_cfg(m->be->config.use_pdl != 0)));
     ++*launches;
@@ -421,17 +506,23 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         if (!rows_kernel || (t != 8 && t != 16 && t != 32) || n_rows % t != 0) { t = 4; }
         return t;
     };
+    // SPYB_STEP=1: single-token steps as one persistent kernel (needs the fragment-ordered records of the tensor-core
+    // kernels); SPYB_MMA=1: tensor-core kernels, one launch per matrix. Default: the byte-dot-product kernels, which
+    // measure fastest on the 7B workload (1.63 ms per token against 1.83 / 2.2).
+    const bool want_step = std::getenv("SPYB_STEP") != nullptr && std::atoi(std::getenv("SPYB_STEP")) != 0;
+    const int  use_mma = (want_step || (std::getenv("SPYB_MMA") != nullptr && std::atoi(std::getenv("SPYB_MMA")) != 0)) ? 1 : 0;
     auto auto_tile = [&](int64_t n_rows) {   // the tallest tile that still gives every SM at least 8 tiles
         const int64_t per_sm = n_rows / std::max(be->num_sms, 1);
+        if (use_mma) { return per_sm >= 8 * 16 ? 16 : 8; }
         return per_sm >= 8 * 32 ? 32 : per_sm >= 8 * 16 ? 16 : 8;
     };
     {
         const std::string head_name = f.tensors.count("output.weight") ? "output.weight" : "token_embd.weight";
         auto ith = f.tensors.find(head_name);
-        const int head_tile = (I.n_vocab >= 8192) ? tile_for("SPYB_TILE_HEAD", I.n_vocab, auto_tile(I.n_vocab)) : 4;
+        const int head_tile = (I.n_vocab >= 8192 || (use_mma && I.n_vocab % 8 == 0)) ? tile_for("SPYB_TILE_HEAD", I.n_vocab, auto_tile(I.n_vocab)) : 4;
         if (ith != f.tensors.end() && head_tile != 4) {
             DevMatrix dummy;
-            if ((st = alloc_matrix(be, ith->second.type, I.n_vocab, d / 32, &m->head, head_tile)) != SPYB_SUCCESS) { return fail(st); }
+            if ((st = alloc_matrix(be, ith->second.type, I.n_vocab, d / 32, &m->head, head_tile, use_mma)) != SPYB_SUCCESS) { return fail(st); }
             st = upload_w(head_name, d, I.n_vocab, 0, I.n_vocab, 0, d / 32, &dummy, &m->head, 0);
         } else {
             st = upload_w(head_name, d, I.n_vocab, 0, I.n_vocab, 0, d / 32, &m->head, nullptr, 0);   // replicated on every rank
@@ -448,7 +539,7 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         auto itq = f.tensors.find(p + "attn_q.weight");
         if (itq == f.tensors.end()) { be->set_error("GGUF: %sattn_q.weight is missing", p.c_str()); return fail(SPYB_FAIL); }
         const int qkv_tile = tile_for("SPYB_TILE_QKV", dl, auto_tile(3 * (int64_t)dl));
-        if ((st = alloc_matrix(be, itq->second.type, 3 * (int64_t)dl, d / 32, &ly.wqkv, qkv_tile)) != SPYB_SUCCESS) { return fail(st); }
+        if ((st = alloc_matrix(be, itq->second.type, 3 * (int64_t)dl, d / 32, &ly.wqkv, qkv_tile, use_mma)) != SPYB_SUCCESS) { return fail(st); }
         DevMatrix dummy;
         if ((st = upload_w(p + "attn_q.weight", d, d, (int64_t)r * dl, dl, 0, d / 32, &dummy, &ly.wqkv, 0)) != SPYB_SUCCESS) { return fail(st); }
         if ((st = upload_w(p + "attn_k.weight", d, d, (int64_t)r * dl, dl, 0, d / 32, &dummy, &ly.wqkv, dl)) != SPYB_SUCCESS) { return fail(st); }
@@ -457,7 +548,7 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         auto ito = f.tensors.find(p + "attn_output.weight");
         const int wo_tile = tile_for("SPYB_TILE_WO", d, auto_tile(d));
         if (ito != f.tensors.end() && wo_tile != 4) {
-            if ((st = alloc_matrix(be, ito->second.type, d, dl / 32, &ly.wo, wo_tile)) != SPYB_SUCCESS) { return fail(st); }
+            if ((st = alloc_matrix(be, ito->second.type, d, dl / 32, &ly.wo, wo_tile, use_mma)) != SPYB_SUCCESS) { return fail(st); }
             st = upload_w(p + "attn_output.weight", d, d, 0, d, (int64_t)r * dl / 32, dl / 32, &dummy, &ly.wo, 0);
         } else {
             st = upload_w(p + "attn_output.weight", d, d, 0, d, (int64_t)r * dl / 32, dl / 32, &ly.wo, nullptr, 0);
@@ -468,7 +559,7 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         const int ug_tile = tile_for("SPYB_TILE_UPGATE", 2 * (int64_t)fl, auto_tile(2 * (int64_t)fl));
         if (itu != f.tensors.end() && ug_tile != 4) {
             const int half = ug_tile / 2;
-            if ((st = alloc_matrix(be, itu->second.type, 2 * (int64_t)fl, d / 32, &ly.upgate, ug_tile)) != SPYB_SUCCESS) { return fail(st); }
+            if ((st = alloc_matrix(be, itu->second.type, 2 * (int64_t)fl, d / 32, &ly.upgate, ug_tile, use_mma)) != SPYB_SUCCESS) { return fail(st); }
             ly.upgate.fused_pair = 1;
             if ((st = upload_w(p + "ffn_up.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &dummy, &ly.upgate, 0, half, 0)) != SPYB_SUCCESS) { return fail(st); }
             if ((st = upload_w(p + "ffn_gate.weight", d, I.n_ff, (int64_t)r * fl, fl, 0, d / 32, &dummy, &ly.upgate, 0, half, half)) != SPYB_SUCCESS) { return fail(st); }
@@ -480,7 +571,7 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         auto itd = f.tensors.find(p + "ffn_down.weight");
         const int down_tile = tile_for("SPYB_TILE_DOWN", d, auto_tile(d));
         if (itd != f.tensors.end() && down_tile != 4) {
-            if ((st = alloc_matrix(be, itd->second.type, d, fl / 32, &ly.down, down_tile)) != SPYB_SUCCESS) { return fail(st); }
+            if ((st = alloc_matrix(be, itd->second.type, d, fl / 32, &ly.down, down_tile, use_mma)) != SPYB_SUCCESS) { return fail(st); }
             st = upload_w(p + "ffn_down.weight", I.n_ff, d, 0, d, (int64_t)r * fl / 32, fl / 32, &dummy, &ly.down, 0);
         } else {
             st = upload_w(p + "ffn_down.weight", I.n_ff, d, 0, d, (int64_t)r * fl / 32, fl / 32, &ly.down, nullptr, 0);
@@ -520,6 +611,7 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
     }
     if (cudaEventCreate(&m->ev0) != cudaSuccess || cudaEventCreate(&m->ev1) != cudaSuccess) { be->set_error("event creation failed"); return fail(SPYB_FAIL); }
     if (cudaDeviceSynchronize() != cudaSuccess) { be->set_error("device synchronisation after the upload failed"); return fail(SPYB_FAIL); }
+    if (build_step_plan(m) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
     *out = m;
     return SPYB_SUCCESS;
 }
@@ -611,7 +703,7 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
         SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
         m->h_pos_pinned[0] = n_past; m->h_pos_pinned[1] = n_past + 1; m->h_pos_pinned[2] = ++m->epoch;
         m->h_tok_pinned[0] = tokens[0];
-        if (m->graph_eval1 == nullptr) {
+        for (int attempt = 0; m->graph_eval1 == nullptr; ++attempt) {
             cudaGraph_t graph = nullptr;
             SPYB_CUDA(be, cudaStreamBeginCapture(be->stream, cudaStreamCaptureModeThreadLocal));
             spyb_status st = SPYB_SUCCESS;
@@ -619,19 +711,24 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
             if (ce == cudaSuccess) { ce = cudaMemcpyAsync(m->d_tokens_in, m->h_tok_pinned, 4, cudaMemcpyHostToDevice, be->stream); }
             if (ce == cudaSuccess) { ce = launch_embed(m->d_tokens_in, 1, m->embd, m->embd_type, m->info.d_model, m->x, be->stream); }
             int64_t n = 1;
-            if (ce == cudaSuccess) { st = run_layers(m, 1, true, &n); }
-            if (ce == cudaSuccess && st == SPYB_SUCCESS) { st = run_head(m, 0, &n, m->info.tp_size > 1 && m->tp_ready); }
+            if (ce == cudaSuccess && m->step_ok) { st = run_step(m, true, &n); }
+            else {
+                if (ce == cudaSuccess) { st = run_layers(m, 1, true, &n); }
+                if (ce == cudaSuccess && st == SPYB_SUCCESS) { st = run_head(m, 0, &n, m->info.tp_size > 1 && m->tp_ready); }
+            }
             if (ce == cudaSuccess && st == SPYB_SUCCESS) { ce = cudaMemcpyAsync(m->h_logits_pinned, m->logits, (size_t)m->info.n_vocab * 4, cudaMemcpyDeviceToHost, be->stream); }
             const cudaError_t ee = cudaStreamEndCapture(be->stream, &graph);
-            if (ce != cudaSuccess || st != SPYB_SUCCESS || ee != cudaSuccess) {
-                if (graph) { cudaGraphDestroy(graph); }
-                if (st == SPYB_SUCCESS) { be->set_error("CUDA graph capture of the single-token step failed: %s", cudaGetErrorString(ce != cudaSuccess ? ce : ee)); }
-                return SPYB_FAIL;
+            cudaError_t ie = cudaSuccess;
+            if (ce == cudaSuccess && st == SPYB_SUCCESS && ee == cudaSuccess) {
+                ie = cudaGraphInstantiate(&m->graph_eval1, graph, 0);
+                if (ie != cudaSuccess) { m->graph_eval1 = nullptr; }
             }
-            const cudaError_t ie = cudaGraphInstantiate(&m->graph_eval1, graph, 0);
-            cudaGraphDestroy(graph);
-            if (ie != cudaSuccess) { m->graph_eval1 = nullptr; be->set_error("CUDA graph instantiation failed: %s", cudaGetErrorString(ie)); return SPYB_FAIL; }
-            m->eval1_launches = n;
+            if (graph) { cudaGraphDestroy(graph); }
+            if (m->graph_eval1 != nullptr) { m->eval1_launches = n; break; }
+            cudaGetLastError();
+            if (attempt == 0 && m->step_ok && m->step_coop) { m->step_coop = false; continue; }   // a cooperative launch the capture refuses: plain launch of the same grid
+            if (st == SPYB_SUCCESS) { be->set_error("CUDA graph capture of the single-token step failed: %s", cudaGetErrorString(ce != cudaSuccess ? ce : ee != cudaSuccess ? ee : ie)); }
+            return SPYB_FAIL;
         }
         SPYB_CUDA(be, cudaEventRecord(m->ev0, be->stream));
         SPYB_CUDA(be, cudaGraphLaunch(m->graph_eval1, be->stream));
@@ -687,7 +784,7 @@ spyb_status spyb_model_decode(spyb_model *m, int32_t first_token, int32_t n_past
 
     const bool use_graph = be->config.use_graph != 0 && (m->info.tp_size == 1 || std::getenv("SPYB_TP_NO_GRAPH") == nullptr);   // the all-reduces of the prompt pass have warmed NCCL up before the capture
     int64_t per_step = 0;
-    if (use_graph && m->graph_exec == nullptr) {
+    for (int attempt = 0; use_graph && m->graph_exec == nullptr; ++attempt) {
         // one decode step captured once; positions and the token live in device memory, so the
         // same graph replays for every later step
         cudaGraph_t graph = nullptr;
@@ -696,16 +793,19 @@ spyb_status spyb_model_decode(spyb_model *m, int32_t first_token, int32_t n_past
         int64_t n = 0;
         const spyb_status st = run_decode_step(m, &n);
         const cudaError_t ce = cudaStreamEndCapture(be->stream, &graph);
-        if (st != SPYB_SUCCESS || ce != cudaSuccess) {
-            if (graph) { cudaGraphDestroy(graph); }
-            if (st == SPYB_SUCCESS) { be->set_error("CUDA graph capture failed: %s", cudaGetErrorString(ce)); }
-            return SPYB_FAIL;
+        cudaError_t ie = cudaSuccess;
+        if (st == SPYB_SUCCESS && ce == cudaSuccess) {
+            ie = cudaGraphInstantiate(&m->graph_exec, graph, 0);
+            if (ie != cudaSuccess) { m->graph_exec = nullptr; }
         }
-        const cudaError_t ie = cudaGraphInstantiate(&m->graph_exec, graph, 0);
-        cudaGraphDestroy(graph);
-        if (ie != cudaSuccess) { m->graph_exec = nullptr; be->set_error("CUDA graph instantiation failed: %s", cudaGetErrorString(ie)); return SPYB_FAIL; }
+        if (graph) { cudaGraphDestroy(graph); }
+        if (m->graph_exec != nullptr) { break; }
+        cudaGetLastError();
+        if (attempt == 0 && m->step_ok && m->step_coop) { m->step_coop = false; continue; }   // a cooperative launch the capture refuses: plain launch of the same grid
+        if (st == SPYB_SUCCESS) { be->set_error("CUDA graph capture failed: %s", cudaGetErrorString(ce != cudaSuccess ? ce : ie)); }
+        return SPYB_FAIL;
     }
-    per_step = (int64_t)m->layers.size() * 5 + 2;
+    per_step = m->step_ok ? 2 : (int64_t)m->layers.size() * 5 + 2;
     SPYB_CUDA(be, cudaEventRecord(m->ev0, be->stream));
     for (int s = 0; s < n_steps; ++s) {
         if (use_graph) { SPYB_CUDA(be, cudaGraphLaunch(m->graph_exec, be->stream)); }
@@ -779,6 +879,34 @@ float spyb_model_bench_kernel(spyb_model *m, int32_t kind, int32_t sweeps, uint6
     return n ? total_ms / (float)n : -1.f;
 }
 
+spyb_status spyb_set_wait_limit_ns(spyb_backend *be, uint64_t ns) {
+    if (be == nullptr || ns == 0) { return SPYB_FAIL; }
+    be->wait_limit_ns = ns;
+    return SPYB_SUCCESS;
+}
+
+spyb_status spyb_model_selftest_wait_timeout(spyb_model *m, uint64_t limit_ns, int32_t *error_code_out) {
+    if (m == nullptr || limit_ns == 0) { return SPYB_FAIL; }
+    spyb_backend *be = m->be;
+    if (!m->step_ok) { be->set_error("selftest: this model does not run on the step kernel"); return SPYB_UNSUPPORTED; }
+    cudaSetDevice(be->config.device_id);
+    SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+    if (be->device_error()) { return SPYB_FAIL; }
+    m->h_pos_pinned[0] = m->info.n_ctx - 1; m->h_pos_pinned[1] = 0;
+    SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 8, cudaMemcpyHostToDevice, be->stream));
+    StepParams p = m->step;
+    p.wait_limit_ns = limit_ns;
+    p.barrier_extra = 1;   // every barrier expects one arrival more than there are CTAs: the first one runs out
+    SPYB_CUDA(be, cudaMemsetAsync(m->d_step_sync, 0, 32, be->stream));
+    SPYB_CUDA(be, launch_step(p, m->step_grid, m->step_ns, m->step_coop, be->stream));
+    SPYB_CUDA(be, cudaStreamSynchronize(be->stream));   // returns: the kernel ended by itself
+    const int code = *reinterpret_cast<volatile int *>(be->h_error_flag);
+    if (error_code_out != nullptr) { *error_code_out = code; }
+    *reinterpret_cast<volatile int *>(be->h_error_flag) = 0;   // the check leaves the backend usable
+    if (code != 2) { be->set_error("selftest: expected the barrier wait to give up with code 2, got %d", code); return SPYB_FAIL; }
+    return SPYB_SUCCESS;
+}
+
 float   spyb_model_last_ms(const spyb_model *m) { return m ? m->last_ms : 0.f; }
 int64_t spyb_model_last_launches(const spyb_model *m) { return m ? m->last_launches : 0; }
 
@@ -803,6 +931,13 @@ int32_t spyb_model_read_timeline(spyb_model *m, uint64_t *stamps_host, int32_t m
     if (m == nullptr || m->d_stamps == nullptr || stamps_host == nullptr) { return 0; }
     const int n = std::min<int>(max_kernels, 5 * (int)m->layers.size() + 1);
     if (cudaMemcpy(stamps_host, m->d_stamps, (size_t)n * 8 * sizeof(uint64_t), cudaMemcpyDeviceToHost) != cudaSuccess) { return 0; }
+    return n;
+}
+
+int32_t spyb_model_read_step_timeline(spyb_model *m, uint64_t *stamps_host, int32_t max_points) {
+    if (m == nullptr || m->d_step_stamps == nullptr || stamps_host == nullptr) { return 0; }
+    const int n = std::min<int>(max_points, m->step_stamp_count);
+    if (cudaMemcpy(stamps_host, m->d_step_stamps, (size_t)n * 2 * sizeof(uint64_t), cudaMemcpyDeviceToHost) != cudaSuccess) { return 0; }
     return n;
 }
 

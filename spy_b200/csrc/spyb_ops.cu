@@ -294,12 +294,8 @@ cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
     const size_t n_pad = ((size_t)p.n_ctx + 3) & ~(size_t)3;
     const size_t smem = (n_pad + n_pad / 4 + ATT_HD) * sizeof(float) + 16;
     if (smem > 200 * 1024) { return cudaErrorInvalidValue; }
-    static size_t smem_allowed = 40 * 1024;
-    if (smem > smem_allowed) {
-        cudaError_t err = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (err != cudaSuccess) { return err; }
-        smem_allowed = smem;
-    }
+    cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(attention_kernel), smem);
+    if (err != cudaSuccess) { return err; }
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(p.n_head, p.T, 1); lc.blockDim = dim3(ATT_THREADS); lc.dynamicSmemBytes = smem; lc.stream = cfg.stream;
     cudaLaunchAttribute attr[1];
@@ -312,7 +308,7 @@ cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
 // =============================================================================================
 // upload-time re-tiling: raw 18-byte / 34-byte blocks -> the record stream described at DevMatrix
 // (one thread per padded block; blocks beyond nb are written as zeros with a zero scale)
-template <int WORDS>   // 4: Q4_0 (16 nibble bytes), 8: Q8_0 (32 int8 values)
+template <int WORDS, bool MMA>   // WORDS 4: Q4_0 (16 nibble bytes), 8: Q8_0 (32 int8 values); MMA: the fragment-ordered record of DevMatrix::mma
 __global__ void retile_kernel(const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, int nbp, uint8_t *base, int tile_rows,
                               int64_t dst_row0, int64_t src_row0, int sub_rows, int sub_off) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -324,27 +320,39 @@ __global__ void retile_kernel(const uint8_t *raw, int64_t row_stride, int64_t n_
     constexpr int  ROWB = WORDS * 32 + 16;
     const int64_t  srow = src_row0 + lrow;
     const int64_t  row  = dst_row0 + (sub_rows > 0 ? (srow / sub_rows) * tile_rows + sub_off + srow % sub_rows : srow);
-    uint8_t  *rec = base + ((row / tile_rows) * (nbp >> 3) + (b >> 3)) * ((int64_t)tile_rows * ROWB) + (row % tile_rows) * ROWB;
-    uint32_t *q   = reinterpret_cast<uint32_t *>(rec + ((b >> 2) & 1) * (WORDS * 16)) + (b & 3);
-    reinterpret_cast<uint16_t *>(rec + WORDS * 32)[b & 7] = real ? (uint16_t)(src[0] | (src[1] << 8)) : (uint16_t)0;
+    const int      r    = (int)(row % tile_rows);
+    uint8_t  *rec = base + ((row / tile_rows) * (nbp >> 3) + (b >> 3)) * ((int64_t)tile_rows * ROWB);
+    const uint16_t d = real ? (uint16_t)(src[0] | (src[1] << 8)) : (uint16_t)0;
+    const int      grp_bytes = tile_rows * WORDS * 16;   // MMA: quants of one group of four blocks, all rows of the tile
+    if (MMA) { reinterpret_cast<uint16_t *>(rec + 2 * grp_bytes + r * 16)[b & 7] = d; }
+    else     { reinterpret_cast<uint16_t *>(rec + r * ROWB + WORDS * 32)[b & 7] = d; }
 #pragma unroll
     for (int k = 0; k < WORDS; ++k) {
         uint32_t v = real ? (uint32_t)(src[2 + 4 * k] | (src[3 + 4 * k] << 8) | (src[4 + 4 * k] << 16) | ((uint32_t)src[5 + 4 * k] << 24)) : 0u;
         if (WORDS == 4) { v ^= 0x88888888u; }
-        q[4 * k] = v;
+        if (MMA) {   // [group][half of the block][row][word of the half] x 16 B, the four blocks of the group side by side
+            reinterpret_cast<uint32_t *>(rec + ((b >> 2) & 1) * grp_bytes + (((k >> 2) * tile_rows + r) * 4 + (k & 3)) * 16)[b & 3] = v;
+        } else {
+            reinterpret_cast<uint32_t *>(rec + r * ROWB + ((b >> 2) & 1) * (WORDS * 16))[(b & 3) + 4 * k] = v;
+        }
     }
 }
 
-cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *matrix_base, int tile_rows,
+cudaError_t launch_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *matrix_base, int tile_rows, bool mma,
                           int64_t dst_row0, int64_t src_row0, int sub_rows, int sub_off, cudaStream_t s) {
     const int     nbp = padded_blocks(nb);
     const int64_t n = n_rows * nbp;
     if (n == 0) { return cudaSuccess; }
     if (tile_rows != 4 && tile_rows != 8 && tile_rows != 16 && tile_rows != 32) { return cudaErrorInvalidValue; }
+    if (mma && tile_rows != 8 && tile_rows != 16) { return cudaErrorInvalidValue; }
     const unsigned grid = (unsigned)((n + 255) / 256);
-    if (type == 2)      { retile_kernel<4><<<grid, 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, matrix_base, tile_rows, dst_row0, src_row0, sub_rows, sub_off); }
-    else if (type == 8) { retile_kernel<8><<<grid, 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, matrix_base, tile_rows, dst_row0, src_row0, sub_rows, sub_off); }
-    else                { return cudaErrorNotSupported; }
+    if (type == 2) {
+        if (mma) { retile_kernel<4, true><<<grid, 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, matrix_base, tile_rows, dst_row0, src_row0, sub_rows, sub_off); }
+        else     { retile_kernel<4, false><<<grid, 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, matrix_base, tile_rows, dst_row0, src_row0, sub_rows, sub_off); }
+    } else if (type == 8) {
+        if (mma) { retile_kernel<8, true><<<grid, 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, matrix_base, tile_rows, dst_row0, src_row0, sub_rows, sub_off); }
+        else     { retile_kernel<8, false><<<grid, 256, 0, s>>>(raw, row_stride, n_rows, nb, nbp, matrix_base, tile_rows, dst_row0, src_row0, sub_rows, sub_off); }
+    } else { return cudaErrorNotSupported; }
     return launch_check();
 }
 
