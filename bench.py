@@ -35,6 +35,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 SEED, PROMPT_SEED, N_PROMPT, N_CTX = 1234, 4321, 8, 512
+REPS = 5         # repetitions of the timed region; the median is reported
 WORKLOAD = "llama2-7b-arch Q4_0 bs1 decode, ctx 512, prompt 8 (synthetic GGUF, seed 1234)"
 
 
@@ -125,15 +126,35 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
-def cpu_reference_run(path, steps, warmup, threads):
+N_PARITY = 32   # generated tokens of the parity record: the 8-token prompt, then 32 greedy tokens
+
+
+def cpu_reference_run(path, steps, warmup, threads, want_logits=False, n_vocab=None):
     """Reference CPU backend: prefill of the prompt, then warmup + steps single-token decode steps."""
     from oracle import spy_ref
     if not spy_ref.available():
         return None
     n = 1 + warmup + steps
-    ids, _, ms = spy_ref.generate(path, prompt_ids(), n, n_ctx=N_CTX, threads=threads, warmup=False, want_logits=False)
+    ids, logits, ms = spy_ref.generate(path, prompt_ids(), n, n_ctx=N_CTX, threads=threads, warmup=False, want_logits=want_logits, n_vocab=n_vocab)
     dec = ms[1 + warmup:]
-    return {"tokens_per_s": float(len(dec) / (dec.sum() / 1e3)), "ms_per_step": float(dec.mean()), "ids": ids, "prefill_ms": float(ms[0])}
+    return {"tokens_per_s": float(len(dec) / (dec.sum() / 1e3)), "ms_per_step": float(dec.mean()), "ids": ids, "logits": logits,
+            "prefill_ms": float(ms[0])}
+
+
+def parity_record(ids, logits, want_ids, want_logits):
+    """The stated gates: greedy ids identical; per-step logits within max-abs 2e-2 and rel 1e-2 (relative to the step's
+    largest |logit|); plus the smallest gap between the two largest logits of a step (what a flipped id would need)."""
+    ids, want_ids = np.asarray(ids), np.asarray(want_ids)
+    logits, want_logits = np.asarray(logits, dtype=np.float32), np.asarray(want_logits, dtype=np.float32)
+    n = min(len(ids), len(want_ids))
+    d = np.abs(logits[:n] - want_logits[:n]).max(axis=1)
+    scale = np.abs(want_logits[:n]).max(axis=1)
+    top2 = np.sort(want_logits[:n], axis=1)[:, -2:]
+    rec = {"n_ids": int(n), "ids_identical": bool(np.array_equal(ids[:n], want_ids[:n])), "max_abs_dlogit": float(d.max()),
+           "max_rel_dlogit": float((d / np.maximum(scale, 1e-30)).max()), "min_top2_gap": float((top2[:, 1] - top2[:, 0]).min()),
+           "bits_identical": bool(np.array_equal(logits[:n].view(np.uint32), want_logits[:n].view(np.uint32)))}
+    rec["within_tolerance"] = bool(rec["ids_identical"] and rec["max_abs_dlogit"] <= 2e-2 and rec["max_rel_dlogit"] <= 1e-2)
+    return rec
 
 
 def run_reference_arm(args):
@@ -234,6 +255,7 @@ def main():
         model.close(); be.close()
         return
 
+    closed = False
     steps, warmup = args.steps, max(3, args.warmup)
     room = N_CTX - N_PROMPT - 1
     if warmup + steps > room:
@@ -250,8 +272,15 @@ def main():
     ids_warm, _ = model.decode(tok0, N_PROMPT, warmup)        # re-run the warm-up region so the timed tokens follow it
     barrier(); be.sync()
     last_tok = int(ids_warm[-1])
-    ids, _ = model.decode(last_tok, N_PROMPT + warmup, steps)
-    ms_dev = model.last_ms
+    reps_ms = []
+    for _ in range(REPS):                                     # the same `steps` positions every time: identical work per repetition
+        barrier()
+        ids, _ = model.decode(last_tok, N_PROMPT + warmup, steps)
+        t = torch.tensor([model.last_ms], dtype=torch.float64)
+        if dist is not None:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)          # device time of the slowest rank
+        reps_ms.append(float(t[0]))
+    ms_dev = float(np.median(reps_ms))
     launches = model.last_launches
     be.sync(); barrier()
 
@@ -271,10 +300,26 @@ def main():
     ms_e2e_wall = (time.perf_counter() - t0) * 1e3
     clocks = sampler.stop() if rank == 0 else None
 
-    times = torch.tensor([ms_dev, ms_e2e_wall], dtype=torch.float64)
+    times = torch.tensor([ms_e2e_wall], dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms_dev, ms_e2e = float(times[0]), float(times[1])
+    ms_e2e = float(times[0])
+
+    # ---- parity of the tensor-parallel run against the unsharded model, on the benchmarked model (rank 0 loads both)
+    parity_tp = None
+    if world > 1:
+        ids_tp, logits_tp = model.decode(last_tok, N_PROMPT + warmup, min(steps, N_PARITY), want_logits=True)
+        if rank == 0:
+            be1 = B.B200Backend(local, tp_size=1, tp_rank=0, use_pdl=not args.no_pdl, use_graph=not args.no_graph)
+            m1 = B.LlamaModel(be1, path, n_ctx=N_CTX)
+            f1 = m1.eval(prompt, 0)
+            w1, _ = m1.decode(int(np.argmax(f1)), N_PROMPT, warmup)
+            ids_1, logits_1 = m1.decode(int(w1[-1]), N_PROMPT + warmup, min(steps, N_PARITY), want_logits=True)
+            parity_tp = parity_record(ids_tp, logits_tp, ids_1, logits_1)
+            parity_tp["against"] = "the same model unsharded on one GPU, same prompt and positions"
+            parity_tp["warmup_ids_identical"] = bool(np.array_equal(w1, ids_warm) and int(np.argmax(f1)) == tok0)
+            m1.close(); be1.close()
+        barrier()
 
     # ---- dominant kernel alone, over every layer's weights ----------------------------------
     roof = None
@@ -283,11 +328,12 @@ def main():
         kb = bench_kernels(model, be)
         dom = kb["ffn_up_gate"]
         # traffic: dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this workload's FFN
-        # matrices, from the ncu capture summarised in profiles/matvec_rows_q4_0_ffn_up_gate_7b.md
+        # matrices, taken from an earlier ncu capture (the line says so in traffic_source)
         roof = {"bound": "hbm", "kernel": "matvec_rows_kernel<Q4_0, 1 column, 2 lanes per row> (fused FFN up|gate, RMSNorm+Q8_0 prologue, SiLU-mul epilogue)",
                 "achieved": dom["gbs"], "peak": peak,
                 "peak_kind": f"of {peak_kind} ({'MEASURED_PEAKS.json copy bandwidth' if peak_kind == 'measured' else 'fallback 6650 GB/s'})",
                 "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": 50838016 if dom["bytes"] == 50724864 else None,
+                "traffic_source": "ncu capture of this kernel on this matrix, summarised in profiles/matvec_rows_q4_0_ffn_up_gate_7b.md (not re-measured by this run)" if dom["bytes"] == 50724864 else None,
                 "timing": "CUDA events on the launching stream around 320 back-to-back launches (10 sweeps over the 32 layers' matrices, 1.6 GB per sweep)",
                 "bytes_per_launch": dom["bytes"], "us_per_launch": dom["us"], "kernels": kb}
 
@@ -298,7 +344,8 @@ def main():
         tok_s = steps / (ms_dev / 1e3)
         peak, peak_kind = measured_peak()
         line = {"metric": "decode tokens/s", "value": tok_s, "unit": "tokens/s", "n_gpus": world, "steps": steps, "warmup": warmup,
-                "ms_per_step": ms_dev / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "ms_per_step": ms_dev / steps, "ms_per_step_reps": {"min": min(reps_ms) / steps, "median": ms_dev / steps, "max": max(reps_ms) / steps, "n": REPS},
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "int8 block dots, f32 accumulate", "data": "synthetic",
                 "config": {"workload": WORKLOAD, "parallelism": f"tp{world}", "tp_exchange": None if world == 1 else ("nccl" if os.environ.get("SPYB_TP_NCCL_ONLY") else "fused peer-memory (decode), nccl (prompt)"), "l2": "weights 3.7 GB per step, far larger than the 126 MB L2",
                            "pdl": not args.no_pdl, "cuda_graph": not args.no_graph},
@@ -308,20 +355,42 @@ def main():
                         "device_ms_per_step": ev_ms / steps},
                 "gpu_launches": int(launches), "clocks": clocks, "roofline": roof,
                 "ids_match_e2e": bool(np.array_equal(ids, np.array(e2e_ids)))}
+        if parity_tp is not None:
+            line["parity_tp"] = parity_tp
         if not args.no_cpu_baseline and world == 1:
+            # the reference's CPU backend on the whole parity sequence (8-token prompt, 32 greedy tokens, logits of every
+            # step): its decode steps are the timed CPU baseline, its ids and logits the parity record
             threads = physical_cores()
-            r = cpu_reference_run(path, 4, 1, threads)
+            r = cpu_reference_run(path, N_PARITY - 2, 1, threads, want_logits=True, n_vocab=int(info.n_vocab))
             if r is not None:
-                n_cmp = min(len(r["ids"]) - 1, warmup + steps)
-                gpu_ids = np.concatenate([[tok0], ids_warm, ids])[: n_cmp + 1]
+                g_first = model.eval(prompt, 0)
+                g_ids, g_logits = model.decode(int(np.argmax(g_first)), N_PROMPT, N_PARITY - 1, want_logits=True)
+                g_ids = np.concatenate([[int(np.argmax(g_first))], g_ids])
+                g_logits = np.concatenate([g_first[None, :], g_logits])
+                line["parity"] = parity_record(g_ids, g_logits, r["ids"], r["logits"])
+                line["parity"]["against"] = f"the reference's CPU backend (-t {threads}) on the same GGUF and prompt: prompt step + {N_PARITY - 1} decode steps"
                 line["cpu_baseline"] = {"value": r["tokens_per_s"], "unit": "tokens/s", "cores": threads, "kind": "reference",
-                                        "sample": f"4 decode steps after the 8-token prefill and 1 warm-up step, -t {threads}",
-                                        "greedy_ids_identical": bool(np.array_equal(r["ids"][: n_cmp + 1], gpu_ids))}
+                                        "sample": f"{N_PARITY - 2} decode steps after the 8-token prefill and 1 warm-up step, -t {threads}",
+                                        "prefill_ms": r["prefill_ms"], "greedy_ids_identical": line["parity"]["ids_identical"]}
+                line["vs_cpu_reference"] = {"value": tok_s / r["tokens_per_s"], "e2e": line["e2e"]["value"] / r["tokens_per_s"],
+                                            "note": f"tokens/s over the reference's CPU backend at -t {threads} (physical cores of this box) in the same job"}
             else:
                 line["cpu_baseline"] = None
+            # the reference's own token loop (scheduler, graph, sampler) on this library through the spy::Backend adapter
+            try:
+                from oracle import spy_ref
+                if spy_ref.b200_available():
+                    model.close(); be.close(); closed = True   # the adapter creates its own backend and uploads the weights itself
+                    a_ids, _, a_ms = spy_ref.generate(path, prompt, 12, n_ctx=N_CTX, want_logits=False, device_backend=True)
+                    line["adapter_e2e"] = {"value": float(10 / (a_ms[2:].sum() / 1e3)), "unit": "tokens/s",
+                                           "sample": "10 decode steps of the reference's generate loop on backend gpu:b200 (operator-by-operator submit)",
+                                           "ids_identical_to_cpu": bool(r is not None and np.array_equal(a_ids, r["ids"][:12]))}
+            except Exception as e:   # the adapter build is optional
+                line["adapter_e2e"] = {"unavailable": str(e)[:200]}
         print(json.dumps(line))
-    model.close()
-    be.close()
+    if not closed:
+        model.close()
+        be.close()
     if dist is not None:
         dist.destroy_process_group()
 
