@@ -6,7 +6,8 @@
 One "step" = one single-token decode step (one execute() of the graph, batch 1) of a synthetic
 LLaMa2-7B-architecture model with Q4_0 weights (seeded N(0, 0.02), norms = 1, F32 embeddings),
 context 512, after an 8-token seeded prompt. With N > 1 the model is sharded tensor-parallel over
-N GPUs (launched by torchrun, one rank per GPU, NCCL all-reduce after attention-output and FFN-down),
+N GPUs (launched by torchrun, one rank per GPU: heads and FFN columns per rank, the attention output and the
+FFN activation all-gathered over NVLink, Wo and W_down replicated - the results are the single-GPU bits),
 so scaling is "strong". Rank 0 prints one JSON line.
 
   value          tokens/s with everything resident in HBM: CUDA-graph replay, greedy argmax and next
@@ -347,7 +348,7 @@ def main():
                 "ms_per_step": ms_dev / steps, "ms_per_step_reps": {"min": min(reps_ms) / steps, "median": ms_dev / steps, "max": max(reps_ms) / steps, "n": REPS},
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "int8 block dots, f32 accumulate", "data": "synthetic",
-                "config": {"workload": WORKLOAD, "parallelism": f"tp{world}", "tp_exchange": None if world == 1 else ("nccl" if os.environ.get("SPYB_TP_NCCL_ONLY") else "fused peer-memory (decode), nccl (prompt)"), "l2": "weights 3.7 GB per step, far larger than the 126 MB L2",
+                "config": {"workload": WORKLOAD, "parallelism": f"tp{world}", "tp_exchange": None if world == 1 else ("all-gather by NCCL" if os.environ.get("SPYB_TP_NCCL_ONLY") else "all-gather fused into the kernels over peer memory"), "l2": "weights 3.7 GB per step, far larger than the 126 MB L2",
                            "pdl": not args.no_pdl, "cuda_graph": not args.no_graph},
                 "hbm_gbs_per_gpu": bytes_per_token * tok_s / 1e9, "hbm_frac_of_peak": bytes_per_token * tok_s / 1e9 / peak,
                 "hbm_peak_gbs": peak, "bytes_per_token_per_gpu": bytes_per_token,

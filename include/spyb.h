@@ -95,6 +95,10 @@ void        spyb_destroy(spyb_backend *backend);
  * spy_assert/std::terminate error path (util/include/util/log/logger.h:96-150) */
 const char *spyb_last_error(const spyb_backend *backend);
 
+/* Host-only self-check of the library's book-keeping (per-device shared-memory limits of the kernels); needs no GPU.
+ * 0 = passed. No reference counterpart. */
+int32_t spyb_selftest_host(void);
+
 /* ---- Backend::get_max/avail_memory_capacity (backend.h:46-51) */
 uint64_t spyb_max_memory(const spyb_backend *backend);
 uint64_t spyb_avail_memory(const spyb_backend *backend);
@@ -162,7 +166,9 @@ spyb_status spyb_attention(spyb_backend *backend, const void *q_f16, const void 
  * Limits and rules:
  *  - the re-tiled matrix (n_rows * ceil8(k/32) * 18 or 34 bytes) must fit SPYB_NOALLOC_SCRATCH_BYTES (32 MiB: every
  *    matrix of a 7B layer; the 32000 x 4096 head does not fit) - larger requests are rejected with SPYB_UNSUPPORTED;
- *    n_rows must be a multiple of 4 and k a multiple of 32;
+ *    n_rows must be a multiple of 4 and k a multiple of 32; x_dev must be 16-byte aligned (the kernels read it with
+ *    128-bit loads), out_dev 4-byte and w_rows_dev 2-byte aligned - anything else is rejected with SPYB_UNSUPPORTED
+ *    before a kernel is launched (the same rule holds for MatMul operands passed to spyb_submit);
  *  - the first call on a device looks the scratch array's address up and raises the kernels' shared-memory limit for
  *    the given shape: make one call per shape before a stream capture begins, later calls only enqueue kernels on the
  *    backend's stream (they do not synchronise; use spyb_sync);
@@ -195,10 +201,18 @@ spyb_status spyb_model_info_get(const spyb_model *model, spyb_model_info *info);
 spyb_status spyb_nccl_unique_id(void *unique_id_128);
 spyb_status spyb_model_init_tp(spyb_model *model, const void *unique_id_128);
 
-/* Tensor parallel, optional: exchange of the per-layer partial sums through peer memory inside the mat-vec kernels
- * (plain peer stores and flag words, bounded waits) instead of an NCCL all-reduce, for single-token steps. No reference
- * counterpart (the reference has no multi-device path). Every rank calls spyb_model_tp_export (a 64-byte CUDA IPC handle
- * of its exchange buffer), the handles are gathered over the caller's channel in rank order, and every rank calls
+/* The tensor-parallel partition of a layer, as spyb_model_load_gguf cuts it (host arithmetic only, no GPU needed):
+ * out[0], out[1] = first row and number of rows of Wq, Wk and Wv this rank holds (whole heads; also its share of the
+ * gathered attention output), out[2], out[3] = the same for W_up and W_gate (its share of the gathered FFN activation).
+ * Wo and W_down are replicated: they consume the gathered vectors, so no f32 sum is split across ranks and the
+ * tensor-parallel results are the single-GPU bits. SPYB_FAIL when tp_size does not divide the heads or the FFN width
+ * into whole 32-element blocks. No reference counterpart (backend/distributor's graph divider is empty). */
+spyb_status spyb_tp_layer_shard(int32_t d_model, int32_t n_head, int32_t n_ff, int32_t tp_size, int32_t tp_rank, int64_t out[4]);
+
+/* Tensor parallel, optional: the all-gather of the attention output and the FFN activation through peer memory inside
+ * the kernels (plain peer stores and flag words, bounded waits) instead of NCCL all-gathers. No reference counterpart
+ * (the reference has no multi-device path). Every rank calls spyb_model_tp_export (a 64-byte CUDA IPC handle of its
+ * exchange buffer), the handles are gathered over the caller's channel in rank order, and every rank calls
  * spyb_model_tp_import with the tp_size * 64 bytes. Without these calls the NCCL path is used throughout. */
 spyb_status spyb_model_tp_export(spyb_model *model, void *handle_64);
 spyb_status spyb_model_tp_import(spyb_model *model, const void *handles);

@@ -110,6 +110,8 @@ def lib():
         "spyb_model_read_timeline": (i32, [vp, vp, i32]),
         "spyb_model_read_step_timeline": (i32, [vp, vp, i32]),
         "spyb_set_wait_limit_ns": (i32, [vp, u64]),
+        "spyb_selftest_host": (i32, []),
+        "spyb_tp_layer_shard": (i32, [i32, i32, i32, i32, i32, C.POINTER(i64)]),
         "spyb_model_selftest_wait_timeout": (i32, [vp, u64, C.POINTER(i32)]),
     }
     for name, (res, args) in sig.items():

@@ -161,6 +161,8 @@ using namespace spyb;
 
 extern "C" {
 
+int32_t spyb_selftest_host(void) { return smem_ledger_selftest(); }
+
 spyb_status spyb_create(const spyb_config *config, spyb_backend **out) {
     if (config == nullptr || out == nullptr) { return SPYB_FAIL; }
     *out = nullptr;
@@ -181,7 +183,6 @@ spyb_status spyb_create(const spyb_config *config, spyb_backend **out) {
     // kernel ends); measured on B200: 140 of 148 gives 1 % more tokens/s than 148, 132 less again.
     if (be->num_sms >= 128) { be->num_sms -= 8; }
     if (const char *v = std::getenv("SPYB_MV_SMS")) { const int n = std::atoi(v); if (n > 0 && n <= prop.multiProcessorCount) { be->num_sms = n; } }
-    if (const char *v = std::getenv("SPYB_L2_PREFETCH_MB")) { const int mb = std::atoi(v); be->l2_prefetch_next = mb > 0; be->l2_prefetch_cap = (size_t)std::max(mb, 0) << 20; }   // tuning knob
     if (const char *v = std::getenv("SPYB_MV_CTAS_PER_SM")) { be->mv_ctas_per_sm = std::max(1, std::min(2, std::atoi(v))); }   // tuning knob
     if (const char *v = std::getenv("SPYB_MV_S")) { be->mv_force_s = std::atoi(v); }         // tuning knobs
     if (const char *v = std::getenv("SPYB_MV_WACT")) { be->mv_force_wact = std::atoi(v); }
@@ -364,6 +365,11 @@ spyb_status spyb_matmul_noalloc(spyb_backend *be, int32_t weight_type, const voi
     if (w_rows_dev == nullptr || x_dev == nullptr || out_dev == nullptr || n_rows < 4 || (n_rows & 3) || k < QK || k % QK != 0 || n_cols < 1) {
         be->set_error("matmul_noalloc: needs n_rows a multiple of 4, k a multiple of 32, at least one column"); return SPYB_UNSUPPORTED;
     }
+    // the kernels read the activations with 128-bit loads and the raw blocks with 16-bit ones: a misaligned pointer would
+    // raise a device fault (and lose the context), so it is refused here
+    if ((reinterpret_cast<uintptr_t>(x_dev) & 15) || (reinterpret_cast<uintptr_t>(out_dev) & 3) || (reinterpret_cast<uintptr_t>(w_rows_dev) & 1)) {
+        be->set_error("matmul_noalloc: x must be 16-byte aligned, out 4-byte aligned, the weight blocks 2-byte aligned"); return SPYB_UNSUPPORTED;
+    }
     const int nb = (int)(k / QK);
     if (matrix_bytes(weight_type, n_rows, nb) > SPYB_NOALLOC_SCRATCH_BYTES) {
         be->set_error("matmul_noalloc: the re-tiled matrix (%llu bytes) exceeds the %u-byte scratch array", (unsigned long long)matrix_bytes(weight_type, n_rows, nb),
@@ -445,6 +451,10 @@ spyb_status run_matmul(spyb_backend *be, spyb_op_desc *d, void *out_dev) {
     if (w.number_type != SPYB_Q4_0 && w.number_type != SPYB_Q8_0) {
         be->set_error("MatMul: weight type %d is not implemented", w.number_type);
         return SPYB_UNSUPPORTED;
+    }
+    if ((reinterpret_cast<uintptr_t>(x.data) & 15) || (reinterpret_cast<uintptr_t>(out_dev) & 3) || (reinterpret_cast<uintptr_t>(w.data) & 1)) {
+        be->set_error("MatMul: activations must be 16-byte aligned, the output 4-byte aligned, quantized blocks 2-byte aligned");
+        return SPYB_UNSUPPORTED;   // (the kernels use 128-bit loads: a misaligned view would fault on the device)
     }
     if (!tensor_contiguous(w) || !tensor_contiguous(x) || w.elements[2] != 1 || w.elements[3] != 1) {
         be->set_error("MatMul: quantized weights need contiguous 2-D operands");

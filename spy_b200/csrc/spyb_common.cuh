@@ -11,6 +11,7 @@ namespace spyb {
 
 constexpr int WARP = 32;
 constexpr int QK = 32;  // elements per Q4_0 / Q8_0 block (orchestration/include/number/number_impl/quant.h:10-33,124-147)
+constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;   // a bulk copy or a peer's flag that has not arrived after a second: give up and report
 
 // ---------------------------------------------------------------------------------------------
 // fp16 <-> fp32. The reference converts fp16 -> fp32 through an exact table
@@ -24,30 +25,6 @@ __device__ __forceinline__ uint16_t f2h(float f) { return __half_as_ushort(__flo
 // this one is still running, and wait for the previous kernel's results before touching them.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-
-// 128-bit streaming load of weights: read-only path, no L1 allocation (each weight byte is used once).
-__device__ __forceinline__ uint4 ldg_stream(const uint4 *p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-__device__ __forceinline__ uint2 ldg_stream_u2(const uint2 *p) {
-    uint2 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-    return v;
-}
-
-// pull [ptr, ptr + bytes) towards L2; piece `idx` of `n_pieces` equal 16-byte-aligned pieces per call
-__device__ __forceinline__ void l2_prefetch_piece(const void *ptr, size_t bytes, int64_t idx, int64_t n_pieces) {
-    if (ptr == nullptr || bytes == 0) { return; }
-    const uintptr_t lo = reinterpret_cast<uintptr_t>(ptr) & ~(uintptr_t)15;
-    const uintptr_t hi = (reinterpret_cast<uintptr_t>(ptr) + bytes + 15) & ~(uintptr_t)15;
-    const size_t    piece = (((hi - lo) + n_pieces - 1) / n_pieces + 15) & ~(size_t)15;
-    const uintptr_t a = lo + (size_t)idx * piece;
-    if (a >= hi) { return; }
-    const uint32_t n = (uint32_t)min((size_t)(hi - a), piece);
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(__cvta_generic_to_global(reinterpret_cast<const void *>(a))), "r"(n) : "memory");
-}
 
 // ---------------------------------------------------------------------------------------------
 // bulk asynchronous copies global -> shared memory, completion counted on an mbarrier (no tensor map: plain
@@ -73,9 +50,6 @@ __device__ __forceinline__ void mbar_init_fence() {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
@@ -120,9 +94,6 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
     unsigned v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
-}
-__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

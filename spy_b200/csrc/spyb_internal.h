@@ -59,8 +59,6 @@ struct spyb_backend {
     int          mv_ctas_per_sm = 2;
     int          mv_ring_kb = 80;
     int          mv_force_s = 0, mv_force_wact = 0;
-    bool         l2_prefetch_next = false;         // kernels pull the weights of the kernel two places later towards L2
-    size_t       l2_prefetch_cap = (size_t)32 << 20;   // at most this much of one matrix
     cudaStream_t stream = nullptr;
     spyb::Arena  arena;
     int         *h_error_flag = nullptr;   // mapped pinned word the kernels set when a bounded wait runs out

@@ -40,8 +40,23 @@ inline int    record_row_bytes(int type) { return (type == 8 ? 256 : 128) + 16; 
 inline size_t matrix_bytes(int type, int64_t n_rows, int nb) { return (size_t)n_rows * (padded_blocks(nb) / 8) * record_row_bytes(type); }
 
 enum Prologue { PRO_QUANT = 0, PRO_NORM_QUANT = 1 };
-enum Epilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_SILU_MUL = 2, EPI_QKV_ROPE = 3, EPI_TP_SCATTER = 4 };
+enum Epilogue { EPI_STORE = 0, EPI_RESID = 1, EPI_SILU_MUL = 2, EPI_QKV_ROPE = 3 };
 constexpr int TP_MAX = 8;
+
+// One exchange site of the tensor-parallel all-gather over peer memory (memory of the other ranks mapped into this
+// process). A producing kernel writes its share of the gathered vector [T][stride] - elements [off, off + len) of every
+// column - into its own copy; its last CTA copies the share into every other rank's copy and then writes *epoch into
+// every rank's flag word `rank` of the site. A consuming kernel waits (bounded) until all n flag words of the site in its
+// own memory show *epoch.
+struct TpLink {
+    int             n = 0, rank = 0;
+    float          *gather[TP_MAX] = {};      // producer: the gathered vector in each rank's memory (gather[rank] = the local copy)
+    int64_t         stride = 0, off = 0, len = 0;
+    unsigned       *flag_out[TP_MAX] = {};    // producer: flag word `rank` of the site in each rank's memory
+    unsigned       *counter = nullptr;        // producer: local CTA counter of the site (self-resetting); nullptr = not a producer
+    const unsigned *flag_in = nullptr;        // consumer: the site's n flag words in local memory; nullptr = not a consumer
+    const int      *epoch = nullptr;          // device word: the step's exchange epoch
+};
 
 struct MatvecParams {
     DevMatrix A;
@@ -75,36 +90,22 @@ struct MatvecParams {
     // optional profiling aid: eight %globaltimer stamps (CTA 0: entry, predecessor finished, prologue done; last CTA done;
     // latest CTA: entry, predecessor finished, prologue done; unused)
     unsigned long long *stamps = nullptr;
-    // Tensor-parallel exchange fused into the kernels (single column only), over peer memory mapped from the other ranks:
-    //   EPI_TP_SCATTER: every output (on rank 0 plus the residual) is stored into slot `tp_rank` of EVERY rank's exchange
-    //   buffer (tp_out[r], plain peer stores); the last CTA to finish then publishes *tp_epoch into every rank's flag word.
-    //   A consumer (tp_in != nullptr) waits - bounded - until all tp_n flags of its site show *tp_epoch, reads its
-    //   activations as the sum of the tp_n slots in rank order, and CTA 0 writes that sum to tp_x_out (the residual stream).
-    int             tp_n = 0, tp_rank = 0;
-    float          *tp_out[TP_MAX] = {};          // producer: slot `tp_rank` of the site in each rank's buffer ([k] floats)
-    unsigned       *tp_flag_out[TP_MAX] = {};     // producer: flag word `tp_rank` of the site in each rank's buffer
-    unsigned       *tp_counter = nullptr;         // producer: local CTA counter of the site (self-resetting)
-    const float    *tp_in = nullptr;              // consumer: local slots of the site, [tp_n][k]
-    const unsigned *tp_flag_in = nullptr;         // consumer: local flag words of the site, [tp_n]
-    float          *tp_x_out = nullptr;           // consumer: where CTA 0 leaves the reduced vector
-    const int      *tp_epoch = nullptr;           // device word: the step's exchange epoch
-    // weights a later kernel of the step will stream: pulled into L2 once this CTA's own loads are issued
-    const void   *pf_ptr[4] = {nullptr, nullptr, nullptr, nullptr};
-    size_t        pf_bytes[4] = {0, 0, 0, 0};
+    TpLink tp;                          // tensor-parallel all-gather fused into the kernel (producer and / or consumer side)
 };
 
 struct AttnParams {
     const __half *q = nullptr;        // [T][dl], already rounded to fp16
     const __half *k_cache = nullptr;  // [n_ctx][dl]
     const __half *v_cache = nullptr;  // [dl][n_ctx]
-    float        *out = nullptr;      // [T][dl]
+    float        *out = nullptr;      // [T][out_stride]
+    int64_t       out_stride = 0;     // 0 = dl
     const int    *pos_base = nullptr;
     const float  *exp_table = nullptr;
     int   n_head = 0, hd = 128, dl = 0, T = 1, n_ctx = 0;
     float scale = 0.f;
     unsigned long long *stamps = nullptr;                           // as in MatvecParams
-    const void *pf_ptr[4] = {nullptr, nullptr, nullptr, nullptr};   // as in MatvecParams
-    size_t      pf_bytes[4] = {0, 0, 0, 0};
+    TpLink tp;                                                      // producer side of the all-gather of the attention output
+    int   *error_flag = nullptr;
 };
 
 struct LaunchCfg {
@@ -130,6 +131,7 @@ private:
 };
 // raises the current device's dynamic shared-memory limit of `kernel` to `bytes` when it is below (thread-safe)
 cudaError_t allow_dynamic_smem(const void *kernel, size_t bytes);
+int         smem_ledger_selftest();   // host-only check of SmemLedger, 0 = passed
 
 size_t      matvec_smem_bytes(int nb, int T);
 int         matvec_max_columns(int nb);   // most activation columns one launch can hold in shared memory for rows of nb blocks

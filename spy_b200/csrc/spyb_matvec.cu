@@ -31,6 +31,7 @@
 #include "spyb_common.cuh"
 #include "spyb_kernels.h"
 #include "spyb_mma.cuh"
+#include "spyb_tp.cuh"
 
 namespace spyb {
 
@@ -38,7 +39,6 @@ constexpr int MV_THREADS = 512;
 constexpr int MV_WARPS   = MV_THREADS / WARP;
 
 constexpr int MAX_STAGES = 16;              // ring stages per warp (mbarriers per warp)
-constexpr uint64_t WAIT_LIMIT_NS = 1000000000ull;   // a bulk copy that has not landed after a second: give up and report
 
 // shared memory: per column t, per group g of four blocks
 //   Y [t][g][w][i]  (w = 0..7, i = 0..3)  word w of the 32 int8 values of block 4g+i (w 0..3 = values 0..15)
@@ -83,6 +83,21 @@ void SmemLedger::forget(int device, const void *kernel) {
     std::lock_guard<std::mutex> g(mutex_);
     allowed_.erase(std::make_pair(device, kernel));
 }
+// host-only check of the ledger's rules (no device needed): 0 when they hold
+int smem_ledger_selftest() {
+    SmemLedger l;
+    const int k1 = 1, k2 = 2;
+    if (l.decide(0, &k1, 40 * 1024) != SmemLedger::KEEP) { return 1; }       // below the default limit: nothing to do
+    if (l.decide(0, &k1, 100 * 1024) != SmemLedger::RAISE) { return 2; }     // first large launch on device 0
+    if (l.decide(0, &k1, 90 * 1024) != SmemLedger::KEEP) { return 3; }       // already allowed
+    if (l.decide(1, &k1, 100 * 1024) != SmemLedger::RAISE) { return 4; }     // the same kernel on another device: its own mark
+    if (l.decide(0, &k2, 100 * 1024) != SmemLedger::RAISE) { return 5; }     // another kernel on device 0: its own mark
+    if (l.decide(0, &k1, 160 * 1024) != SmemLedger::RAISE) { return 6; }
+    l.forget(0, &k1);                                                        // a failed cudaFuncSetAttribute: back to the default
+    if (l.decide(0, &k1, 100 * 1024) != SmemLedger::RAISE) { return 7; }
+    return 0;
+}
+
 cudaError_t allow_dynamic_smem(const void *kernel, size_t bytes) {
     static SmemLedger ledger;
     int device = 0;
@@ -127,7 +142,7 @@ __device__ __forceinline__ float running_sum_serial(const float *v3, int n4) {
     return sum;
 }
 constexpr int PRO_GROUPS = 6;
-template <int PG, bool NORM, bool TPIN>
+template <int PG, bool NORM>
 __device__ __forceinline__ void matvec_prologue_1col(const MatvecParams &p, ActPlanes act, float *v3, float *scales) {
     const int tid = threadIdx.x;
     const int nbp = p.A.nbp;
@@ -136,37 +151,11 @@ __device__ __forceinline__ void matvec_prologue_1col(const MatvecParams &p, ActP
     const int npass = (n4p + MV_THREADS - 1) / MV_THREADS;     // <= PG
     const float4 *x4 = reinterpret_cast<const float4 *>(p.x);
     float4 xv[PG];
-    if (TPIN) {
-        // tensor-parallel input: wait (bounded) until every rank has published this step's partial vector, then add the
-        // slots in rank order; CTA 0 also leaves the sum in the residual stream
-        if (tid < p.tp_n) {
-            const unsigned want = (unsigned)*p.tp_epoch;
-            const uint64_t t0 = global_timer_ns();
-            while (ld_acquire_sys(p.tp_flag_in + tid) != want) {
-                if (global_timer_ns() - t0 > WAIT_LIMIT_NS) { if (p.error_flag != nullptr) { atomicExch(p.error_flag, 2); } break; }
-            }
-        }
-        __syncthreads();
+    // (activations are read past L1: under tensor parallelism other GPUs wrote part of them)
 #pragma unroll
-        for (int k = 0; k < PG; ++k) {
-            const int g = tid + k * MV_THREADS;
-            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (k < npass && g < n4) {
-                a = __ldcg(reinterpret_cast<const float4 *>(p.tp_in) + g);
-                for (int rk = 1; rk < p.tp_n; ++rk) {
-                    const float4 b = __ldcg(reinterpret_cast<const float4 *>(p.tp_in + (size_t)rk * p.A.k) + g);
-                    a.x = __fadd_rn(a.x, b.x); a.y = __fadd_rn(a.y, b.y); a.z = __fadd_rn(a.z, b.z); a.w = __fadd_rn(a.w, b.w);
-                }
-                if (blockIdx.x == 0 && p.tp_x_out != nullptr) { reinterpret_cast<float4 *>(p.tp_x_out)[g] = a; }
-            }
-            xv[k] = a;
-        }
-    } else {
-#pragma unroll
-        for (int k = 0; k < PG; ++k) {
-            const int g = tid + k * MV_THREADS;
-            xv[k] = (k < npass && g < n4) ? x4[g] : make_float4(0.f, 0.f, 0.f, 0.f);
-        }
+    for (int k = 0; k < PG; ++k) {
+        const int g = tid + k * MV_THREADS;
+        xv[k] = (k < npass && g < n4) ? __ldcg(x4 + g) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     if (NORM) {
         const float4 *w4 = reinterpret_cast<const float4 *>(p.norm_w);
@@ -230,7 +219,7 @@ __device__ __forceinline__ void matvec_prologue(const MatvecParams &p, ActPlanes
         for (int t = 0; t < p.T; ++t) {
             const float4 *x4 = reinterpret_cast<const float4 *>(p.x + (int64_t)t * p.x_stride);
             for (int g = tid; g < n4; g += MV_THREADS) {
-                const float4 v = x4[g];
+                const float4 v = __ldcg(x4 + g);
                 const float v1 = fmaf(v.y, v.y, __fmul_rn(v.x, v.x));
                 const float v2 = fmaf(v.w, v.w, __fmul_rn(v.z, v.z));
                 v3[t * n4 + g] = __fadd_rn(v1, v2);
@@ -266,7 +255,7 @@ __device__ __forceinline__ void matvec_prologue(const MatvecParams &p, ActPlanes
         for (int base = 0; base < n4p; base += MV_THREADS) {
             const int  g     = base + tid;
             const bool valid = col && g < n4;
-            float4 v = valid ? x4[g] : make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 v = valid ? __ldcg(x4 + g) : make_float4(0.f, 0.f, 0.f, 0.f);
             if (p.pro == PRO_NORM_QUANT && valid) {
                 const float4 w = w4[g];
                 v.x = __fmul_rn(__fmul_rn(v.x, scale), w.x);
@@ -313,11 +302,6 @@ __device__ __forceinline__ void matvec_epilogue(const MatvecParams &p, int64_t r
     case EPI_RESID:   // Add(attn_out, x) / Add(ffn_inp, ffn_out): model/src/llm/model/llama.cpp:194-211
         if (writer) { const int64_t i = (int64_t)t * p.out_stride + row; p.out[i] = __fadd_rn(v, p.resid[i]); }
         break;
-    case EPI_TP_SCATTER:   // partial sum of a tensor-parallel shard: into this rank's slot on every rank
-        if (writer) {
-            p.tp_out[p.tp_rank][row] = (p.resid != nullptr) ? __fadd_rn(v, p.resid[row]) : v;   // local slot; the last CTA forwards it
-        }
-        break;
     case EPI_QKV_ROPE: {
         if (!writer) { break; }
         const int sec = (int)(row / p.dl);
@@ -344,7 +328,7 @@ __device__ __forceinline__ void matvec_epilogue_silu(const MatvecParams &p, int6
 }
 
 // ---------------------------------------------------------------------------------------------
-template <int WT, int TM, int R, bool TPIN>
+template <int WT, int TM, int R>
 __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(const MatvecParams p, const int ring_bytes, const int S, const int wact) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ float norm_scales[8];
@@ -413,6 +397,7 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
     __syncwarp();
     pdl_wait();
     stamp(p.stamps, 1, false); stamp(p.stamps, 5, true);
+    tp_wait(p.tp, p.error_flag);
 
     ActPlanes act = act_planes(smem_raw, nbp, TM);
     {
@@ -420,9 +405,9 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
         const int  n4p  = nbp * 8;
         const bool norm = p.pro == PRO_NORM_QUANT;
         if (TM == 1 && n4p <= 2 * MV_THREADS) {
-            if (norm) { matvec_prologue_1col<2, true, TPIN>(p, act, v3, norm_scales); } else { matvec_prologue_1col<2, false, TPIN>(p, act, v3, norm_scales); }
+            if (norm) { matvec_prologue_1col<2, true>(p, act, v3, norm_scales); } else { matvec_prologue_1col<2, false>(p, act, v3, norm_scales); }
         } else if (TM == 1 && n4p <= PRO_GROUPS * MV_THREADS) {
-            if (norm) { matvec_prologue_1col<PRO_GROUPS, true, TPIN>(p, act, v3, norm_scales); } else { matvec_prologue_1col<PRO_GROUPS, false, TPIN>(p, act, v3, norm_scales); }
+            if (norm) { matvec_prologue_1col<PRO_GROUPS, true>(p, act, v3, norm_scales); } else { matvec_prologue_1col<PRO_GROUPS, false>(p, act, v3, norm_scales); }
         } else {
             matvec_prologue<TM>(p, act, v3, norm_scales);
         }
@@ -535,42 +520,8 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
         }
     }
 
-    if (p.tp_counter != nullptr) {
-        // tensor-parallel producer: the CTA that finishes last forwards this rank's partial vector (now complete in the
-        // local slot) to the same slot on every other rank with wide peer stores, then publishes the epoch to every rank
-        __shared__ int tp_last;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            __threadfence();
-            tp_last = (atomicAdd(p.tp_counter, 1u) == gridDim.x - 1) ? 1 : 0;
-            if (tp_last) { *p.tp_counter = 0; __threadfence(); }
-        }
-        __syncthreads();
-        if (tp_last) {
-            const float4 *src = reinterpret_cast<const float4 *>(p.tp_out[p.tp_rank]);
-            const int     n4  = (int)(p.A.n_rows >> 2);
-            for (int i = threadIdx.x; i < n4; i += MV_THREADS) {
-                const float4 v = __ldcg(src + i);
-                for (int rk = 0; rk < p.tp_n; ++rk) { if (rk != p.tp_rank) { reinterpret_cast<float4 *>(p.tp_out[rk])[i] = v; } }
-            }
-            __syncthreads();   // the CTA's peer stores happen-before thread 0's system-scope fence (cumulativity)
-            if (threadIdx.x == 0) {
-                const unsigned epoch = (unsigned)*p.tp_epoch;
-                __threadfence_system();
-                for (int rk = 0; rk < p.tp_n; ++rk) { *reinterpret_cast<volatile unsigned *>(p.tp_flag_out[rk]) = epoch; }
-            }
-        }
-    }
+    tp_publish(p.tp, p.T);
     if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
-    // weights a later kernel will stream: towards L2 while this kernel drains
-    {
-        const int64_t gw = (int64_t)blockIdx.x * MV_THREADS + threadIdx.x, gn = (int64_t)gridDim.x * MV_THREADS;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int64_t np = (int64_t)((p.pf_bytes[k] + 4095) / 4096);
-            for (int64_t i = gw; i < np; i += gn) { l2_prefetch_piece(p.pf_ptr[k], p.pf_bytes[k], i, np); }
-        }
-    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -589,7 +540,7 @@ __global__ void __launch_bounds__(MV_THREADS, (TM == 1) ? 2 : 1) matvec_kernel(c
 // A record is [TR rows][2 groups x 64 B (Q4_0) or 128 B (Q8_0) | 8 fp16 scales]; the 144-byte (272-byte) row pitch
 // makes the 128-bit reads of eight consecutive rows conflict-free.
 // With fused_pair, rows 0..TR/2-1 of tile u are FFN-up rows (TR/2)u.. and rows TR/2..TR-1 the matching FFN-gate rows.
-template <int WT, int TM, int LPR, bool TPIN>
+template <int WT, int TM, int LPR>
 __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const MatvecParams p, const int ring_bytes, const int S, const int wact) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ float norm_scales[8];
@@ -648,6 +599,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
     __syncwarp();
     pdl_wait();
     stamp(p.stamps, 1, false); stamp(p.stamps, 5, true);
+    tp_wait(p.tp, p.error_flag);
 
     ActPlanes act = act_planes(smem_raw, nbp, TM);
     {
@@ -655,9 +607,9 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
         const int  n4p  = nbp * 8;
         const bool norm = p.pro == PRO_NORM_QUANT;
         if (TM == 1 && n4p <= 2 * MV_THREADS) {
-            if (norm) { matvec_prologue_1col<2, true, TPIN>(p, act, v3, norm_scales); } else { matvec_prologue_1col<2, false, TPIN>(p, act, v3, norm_scales); }
+            if (norm) { matvec_prologue_1col<2, true>(p, act, v3, norm_scales); } else { matvec_prologue_1col<2, false>(p, act, v3, norm_scales); }
         } else if (TM == 1 && n4p <= PRO_GROUPS * MV_THREADS) {
-            if (norm) { matvec_prologue_1col<PRO_GROUPS, true, TPIN>(p, act, v3, norm_scales); } else { matvec_prologue_1col<PRO_GROUPS, false, TPIN>(p, act, v3, norm_scales); }
+            if (norm) { matvec_prologue_1col<PRO_GROUPS, true>(p, act, v3, norm_scales); } else { matvec_prologue_1col<PRO_GROUPS, false>(p, act, v3, norm_scales); }
         } else {
             matvec_prologue<TM>(p, act, v3, norm_scales);
         }
@@ -773,32 +725,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
             if (++slot == NS) { slot = 0; parity ^= 1u; }
         }
     }
-    if (p.tp_counter != nullptr) {
-        // tensor-parallel producer: the CTA that finishes last forwards this rank's partial vector (now complete in the
-        // local slot) to the same slot on every other rank with wide peer stores, then publishes the epoch to every rank
-        __shared__ int tp_last;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            __threadfence();
-            tp_last = (atomicAdd(p.tp_counter, 1u) == gridDim.x - 1) ? 1 : 0;
-            if (tp_last) { *p.tp_counter = 0; __threadfence(); }
-        }
-        __syncthreads();
-        if (tp_last) {
-            const float4 *src = reinterpret_cast<const float4 *>(p.tp_out[p.tp_rank]);
-            const int     n4  = (int)(p.A.n_rows >> 2);
-            for (int i = threadIdx.x; i < n4; i += MV_THREADS) {
-                const float4 v = __ldcg(src + i);
-                for (int rk = 0; rk < p.tp_n; ++rk) { if (rk != p.tp_rank) { reinterpret_cast<float4 *>(p.tp_out[rk])[i] = v; } }
-            }
-            __syncthreads();   // the CTA's peer stores happen-before thread 0's system-scope fence (cumulativity)
-            if (threadIdx.x == 0) {
-                const unsigned epoch = (unsigned)*p.tp_epoch;
-                __threadfence_system();
-                for (int rk = 0; rk < p.tp_n; ++rk) { *reinterpret_cast<volatile unsigned *>(p.tp_flag_out[rk]) = epoch; }
-            }
-        }
-    }
+    tp_publish(p.tp, p.T);
     if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
 }
 
@@ -806,7 +733,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
 // Tensor-core variant for matrices stored in fragment order (DevMatrix::mma, tiles of TR = 16 or 8 rows): the integer
 // group sums of a block come out of one mma.sync per block and 16 rows instead of eight byte dot products per row; the
 // inner loop and its exactness argument are in spyb_mma.cuh. Streaming, prologue and epilogues as in matvec_rows_kernel.
-template <int WT, int TM, int TR, bool TPIN>
+template <int WT, int TM, int TR>
 __global__ void __launch_bounds__(MV_THREADS, 1) matvec_mma_kernel(const MatvecParams p, const int ring_bytes, const int S, const int wact) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ float norm_scales[8];
@@ -861,6 +788,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_mma_kernel(const MatvecP
     __syncwarp();
     pdl_wait();
     stamp(p.stamps, 1, false); stamp(p.stamps, 5, true);
+    tp_wait(p.tp, p.error_flag);
 
     ActPlanes act = act_planes(smem_raw, nbp, TM);
     {
@@ -868,9 +796,9 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_mma_kernel(const MatvecP
         const int  n4p  = nbp * 8;
         const bool norm = p.pro == PRO_NORM_QUANT;
         if (TM == 1 && n4p <= 2 * MV_THREADS) {
-            if (norm) { matvec_prologue_1col<2, true, TPIN>(p, act, v3, norm_scales); } else { matvec_prologue_1col<2, false, TPIN>(p, act, v3, norm_scales); }
+            if (norm) { matvec_prologue_1col<2, true>(p, act, v3, norm_scales); } else { matvec_prologue_1col<2, false>(p, act, v3, norm_scales); }
         } else if (TM == 1 && n4p <= PRO_GROUPS * MV_THREADS) {
-            if (norm) { matvec_prologue_1col<PRO_GROUPS, true, TPIN>(p, act, v3, norm_scales); } else { matvec_prologue_1col<PRO_GROUPS, false, TPIN>(p, act, v3, norm_scales); }
+            if (norm) { matvec_prologue_1col<PRO_GROUPS, true>(p, act, v3, norm_scales); } else { matvec_prologue_1col<PRO_GROUPS, false>(p, act, v3, norm_scales); }
         } else {
             matvec_prologue<TM>(p, act, v3, norm_scales);
         }
@@ -929,34 +857,11 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_mma_kernel(const MatvecP
             if (++slot == NS) { slot = 0; parity ^= 1u; }
         }
     }
-    if (p.tp_counter != nullptr) {
-        __shared__ int tp_last;
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            __threadfence();
-            tp_last = (atomicAdd(p.tp_counter, 1u) == gridDim.x - 1) ? 1 : 0;
-            if (tp_last) { *p.tp_counter = 0; __threadfence(); }
-        }
-        __syncthreads();
-        if (tp_last) {
-            const float4 *srcv = reinterpret_cast<const float4 *>(p.tp_out[p.tp_rank]);
-            const int     n4  = (int)(p.A.n_rows >> 2);
-            for (int i = threadIdx.x; i < n4; i += MV_THREADS) {
-                const float4 v = __ldcg(srcv + i);
-                for (int rk = 0; rk < p.tp_n; ++rk) { if (rk != p.tp_rank) { reinterpret_cast<float4 *>(p.tp_out[rk])[i] = v; } }
-            }
-            __syncthreads();
-            if (threadIdx.x == 0) {
-                const unsigned epoch = (unsigned)*p.tp_epoch;
-                __threadfence_system();
-                for (int rk = 0; rk < p.tp_n; ++rk) { *reinterpret_cast<volatile unsigned *>(p.tp_flag_out[rk]) = epoch; }
-            }
-        }
-    }
+    tp_publish(p.tp, p.T);
     if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
 }
 
-template <int WT, int TM, int TR, bool TPIN = false>
+template <int WT, int TM, int TR>
 static cudaError_t launch_matvec_mma_t(const MatvecParams &p, const LaunchCfg &cfg) {
     constexpr int RECB = TR * (((WT == 8) ? 256 : 128) + 16);
     const int64_t n_units = p.A.n_rows / TR;
@@ -981,7 +886,7 @@ static cudaError_t launch_matvec_mma_t(const MatvecParams &p, const LaunchCfg &c
     if (cfg.mv_force_wact > 0) { wact = std::min(cfg.mv_force_wact, MV_WARPS); }
     if (ring / ((size_t)wact * S * RECB) < 1) { return cudaErrorInvalidValue; }
     const size_t smem = fixed.total + ring;
-    cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(matvec_mma_kernel<WT, TM, TR, TPIN>), smem);
+    cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(matvec_mma_kernel<WT, TM, TR>), smem);
     if (err != cudaSuccess) { return err; }
     MatvecParams q = p;
     if (q.error_flag == nullptr) { q.error_flag = cfg.error_flag; }
@@ -991,17 +896,17 @@ static cudaError_t launch_matvec_mma_t(const MatvecParams &p, const LaunchCfg &c
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&lc, matvec_mma_kernel<WT, TM, TR, TPIN>, q, (int)ring, S, wact);
+    return cudaLaunchKernelEx(&lc, matvec_mma_kernel<WT, TM, TR>, q, (int)ring, S, wact);
 }
 
 template <int WT, int TR>
 static cudaError_t launch_matvec_mma_w(const MatvecParams &p, const LaunchCfg &cfg) {
-    if (p.T <= 1) { return p.tp_in ? launch_matvec_mma_t<WT, 1, TR, true>(p, cfg) : launch_matvec_mma_t<WT, 1, TR>(p, cfg); }
+    if (p.T <= 1) { return launch_matvec_mma_t<WT, 1, TR>(p, cfg); }
     if (p.T <= 2) { return launch_matvec_mma_t<WT, 2, TR>(p, cfg); }
     return launch_matvec_mma_t<WT, 4, TR>(p, cfg);
 }
 
-template <int WT, int TM, int LPR, bool TPIN = false>
+template <int WT, int TM, int LPR>
 static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &cfg) {
     constexpr int TR = 32 / LPR;
     constexpr int RECB = TR * (((WT == 8) ? 256 : 128) + 16);
@@ -1027,7 +932,7 @@ static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &
     if (cfg.mv_force_wact > 0) { wact = std::min(cfg.mv_force_wact, MV_WARPS); }
     if (ring / ((size_t)wact * S * RECB) < 1) { return cudaErrorInvalidValue; }
     const size_t smem = fixed.total + ring;
-    cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(matvec_rows_kernel<WT, TM, LPR, TPIN>), smem);
+    cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(matvec_rows_kernel<WT, TM, LPR>), smem);
     if (err != cudaSuccess) { return err; }
     MatvecParams q = p;
     if (q.error_flag == nullptr) { q.error_flag = cfg.error_flag; }
@@ -1037,12 +942,12 @@ static cudaError_t launch_matvec_rows_t(const MatvecParams &p, const LaunchCfg &
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&lc, matvec_rows_kernel<WT, TM, LPR, TPIN>, q, (int)ring, S, wact);
+    return cudaLaunchKernelEx(&lc, matvec_rows_kernel<WT, TM, LPR>, q, (int)ring, S, wact);
 }
 
 template <int WT, int LPR>
 static cudaError_t launch_matvec_rows_w(const MatvecParams &p, const LaunchCfg &cfg) {
-    if (p.T <= 1) { return p.tp_in ? launch_matvec_rows_t<WT, 1, LPR, true>(p, cfg) : launch_matvec_rows_t<WT, 1, LPR>(p, cfg); }
+    if (p.T <= 1) { return launch_matvec_rows_t<WT, 1, LPR>(p, cfg); }
     if (p.T <= 2) { return launch_matvec_rows_t<WT, 2, LPR>(p, cfg); }
     return launch_matvec_rows_t<WT, 4, LPR>(p, cfg);
 }
@@ -1052,7 +957,7 @@ int matvec_max_columns(int nb) {   // (the lane-per-row kernel keeps 8 accumulat
     return 1;
 }
 
-template <int WT, int TM, int R, bool TPIN = false>
+template <int WT, int TM, int R>
 static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) {
     constexpr int RECB = 4 * (((WT == 8) ? 256 : 128) + 16);
     // every SM gets CTAs even when there are fewer units than warps: a unit is a sequential walk along K, so
@@ -1090,7 +995,7 @@ static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) 
     if (ring / ((size_t)wact * R * S * RECB) < 1) { return cudaErrorInvalidValue; }
     const size_t smem = fixed.total + ring;
 
-    cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(matvec_kernel<WT, TM, R, TPIN>), smem);
+    cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(matvec_kernel<WT, TM, R>), smem);
     if (err != cudaSuccess) { return err; }
     MatvecParams q = p;
     if (q.error_flag == nullptr) { q.error_flag = cfg.error_flag; }
@@ -1101,12 +1006,12 @@ static cudaError_t launch_matvec_t(const MatvecParams &p, const LaunchCfg &cfg) 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&lc, matvec_kernel<WT, TM, R, TPIN>, q, (int)ring, S, wact);
+    return cudaLaunchKernelEx(&lc, matvec_kernel<WT, TM, R>, q, (int)ring, S, wact);
 }
 
 template <int WT, int R>
 static cudaError_t launch_matvec_w(const MatvecParams &p, const LaunchCfg &cfg) {
-    if (p.T <= 1) { return p.tp_in ? launch_matvec_t<WT, 1, R, true>(p, cfg) : launch_matvec_t<WT, 1, R>(p, cfg); }
+    if (p.T <= 1) { return launch_matvec_t<WT, 1, R>(p, cfg); }
     if (p.T <= 2) { return launch_matvec_t<WT, 2, R>(p, cfg); }
     if (p.T <= 4) { return launch_matvec_t<WT, 4, R>(p, cfg); }
     return launch_matvec_t<WT, 8, R>(p, cfg);
@@ -1114,7 +1019,8 @@ static cudaError_t launch_matvec_w(const MatvecParams &p, const LaunchCfg &cfg) 
 
 cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg) {
     if (p.T < 1 || p.T > matvec_max_columns(p.A.nb)) { return cudaErrorInvalidValue; }
-    if ((p.epi == EPI_TP_SCATTER || p.tp_in != nullptr) && (p.T != 1 || p.tp_n < 2 || p.tp_n > TP_MAX || p.tp_epoch == nullptr || p.A.nbp * 8 > PRO_GROUPS * MV_THREADS)) { return cudaErrorInvalidValue; }
+    if ((p.tp.counter != nullptr || p.tp.flag_in != nullptr) && (p.tp.n < 2 || p.tp.n > TP_MAX || p.tp.epoch == nullptr)) { return cudaErrorInvalidValue; }
+    if (p.tp.counter != nullptr && ((p.tp.len & 3) || (p.tp.off & 3) || (p.tp.stride & 3))) { return cudaErrorInvalidValue; }
     if (p.A.k % QK != 0 || p.A.nb < 1 || p.A.nbp != padded_blocks(p.A.nb) || p.A.w == nullptr) { return cudaErrorInvalidValue; }
     if (p.A.mma) {
         if ((p.A.tile_rows != 16 && p.A.tile_rows != 8) || (p.A.n_rows % p.A.tile_rows) || p.pair_mode || (p.epi == EPI_SILU_MUL) != (p.A.fused_pair != 0)) { return cudaErrorInvalidValue; }

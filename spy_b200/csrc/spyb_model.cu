@@ -120,7 +120,7 @@ struct NcclApi {
     void *lib = nullptr;
     int (*GetUniqueId)(void *) = nullptr;
     int (*CommInitRank)(void **, int, Uid, int) = nullptr;
-    int (*AllReduce)(const void *, void *, size_t, int, int, void *, cudaStream_t) = nullptr;
+    int (*AllGather)(const void *, void *, size_t, int, void *, cudaStream_t) = nullptr;
     int (*CommDestroy)(void *) = nullptr;
     const char *(*GetErrorString)(int) = nullptr;
     bool load() {
@@ -129,10 +129,10 @@ struct NcclApi {
         if (!lib) { return false; }
         GetUniqueId  = reinterpret_cast<decltype(GetUniqueId)>(dlsym(lib, "ncclGetUniqueId"));
         CommInitRank = reinterpret_cast<decltype(CommInitRank)>(dlsym(lib, "ncclCommInitRank"));
-        AllReduce    = reinterpret_cast<decltype(AllReduce)>(dlsym(lib, "ncclAllReduce"));
+        AllGather    = reinterpret_cast<decltype(AllGather)>(dlsym(lib, "ncclAllGather"));
         CommDestroy  = reinterpret_cast<decltype(CommDestroy)>(dlsym(lib, "ncclCommDestroy"));
         GetErrorString = reinterpret_cast<decltype(GetErrorString)>(dlsym(lib, "ncclGetErrorString"));
-        return GetUniqueId && CommInitRank && AllReduce && CommDestroy;
+        return GetUniqueId && CommInitRank && AllGather && CommDestroy;
     }
 };
 static NcclApi g_nccl;
@@ -159,7 +159,7 @@ struct spyb_model {
     int             embd_type = 0;
     float2         *rope_table = nullptr;
     // activations for up to 8 tokens per pass
-    float  *x = nullptr, *att = nullptr, *act = nullptr, *partial = nullptr, *logits = nullptr;
+    float  *x = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr, *scratch = nullptr;   // att [T][d_model] and act [T][n_ff] are the gathered vectors (inside tp_local)
     __half *q = nullptr;
     int    *d_pos = nullptr;
     int32_t *d_token = nullptr, *d_tokens_in = nullptr, *d_history = nullptr;
@@ -167,8 +167,9 @@ struct spyb_model {
     unsigned long long *d_stamps = nullptr;   // profiling aid (SPYB_TIMELINE=1): eight time stamps per kernel of a step
     int    *h_pos_pinned = nullptr; int32_t *h_tok_pinned = nullptr; float *h_logits_pinned = nullptr;
     void   *nccl_comm = nullptr;
-    // fused exchange over peer memory (single-column steps): [2 n_layer sites][tp slots][d] floats, then [sites][tp] flag words,
-    // then [sites] CTA counters; tp_peer[r] = rank r's buffer as mapped into this process (tp_peer[tp_rank] = the local one)
+    // exchange buffer (exported to the other ranks for the fused all-gather): the gathered attention output [8][d_model] and
+    // FFN activation [8][n_ff] as floats, then [2 n_layer sites][tp] flag words, then [sites] CTA counters;
+    // tp_peer[r] = rank r's buffer as mapped into this process (tp_peer[tp_rank] = the local one)
     uint8_t *tp_local = nullptr;
     uint8_t *tp_peer[TP_MAX] = {};
     bool     tp_ready = false;
@@ -202,52 +203,48 @@ spyb_status dev_alloc(spyb_model *m, T **p, size_t count) {
     return SPYB_SUCCESS;
 }
 
-spyb_status allreduce(spyb_model *m, float *buf, size_t count, int64_t *launches) {
+constexpr int TMAX = 8;   // activation columns the buffers hold
+
+// NCCL form of the exchange (used until the peer buffers are imported): every rank's share [off, off + len) of every
+// column is gathered in place into buf [T][stride]; len * tp_size == stride
+spyb_status allgather(spyb_model *m, float *buf, int T, int64_t stride, int64_t len, int64_t *launches) {
     if (m->info.tp_size == 1) { return SPYB_SUCCESS; }
     if (m->nccl_comm == nullptr) { m->be->set_error("tensor-parallel model used before spyb_model_init_tp"); return SPYB_FAIL; }
-    const int rc = g_nccl.AllReduce(buf, buf, count, /*ncclFloat32*/ 7, /*ncclSum*/ 0, m->nccl_comm, m->be->stream);
-    if (rc != 0) { m->be->set_error("ncclAllReduce failed: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?"); return SPYB_FAIL; }
-    ++*launches;
+    for (int t = 0; t < T; ++t) {
+        float *col = buf + (int64_t)t * stride;
+        const int rc = g_nccl.AllGather(col + (int64_t)m->info.tp_rank * len, col, (size_t)len, /*ncclFloat32*/ 7, m->nccl_comm, m->be->stream);
+        if (rc != 0) { m->be->set_error("ncclAllGather failed: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?"); return SPYB_FAIL; }
+        ++*launches;
+    }
     return SPYB_SUCCESS;
 }
 
+size_t tp_float_count(const spyb_model *m) { return (size_t)TMAX * ((size_t)m->info.d_model + (size_t)m->info.n_ff); }
 size_t tp_buffer_bytes(const spyb_model *m) {
-    const size_t sites = 2 * m->layers.size(), n = m->info.tp_size;
-    return sites * n * m->info.d_model * 4 + sites * n * 4 + sites * 4 + 256;
+    const size_t sites = 2 * (size_t)m->info.n_layer, n = m->info.tp_size;
+    return tp_float_count(m) * 4 + sites * n * 4 + sites * 4 + 256;
 }
-float *tp_slot(const spyb_model *m, uint8_t *base, size_t site, int slot) {
-    return reinterpret_cast<float *>(base) + (site * m->info.tp_size + slot) * (size_t)m->info.d_model;
-}
-unsigned *tp_flag(const spyb_model *m, uint8_t *base, size_t site, int slot) {
-    const size_t sites = 2 * m->layers.size(), n = m->info.tp_size;
-    return reinterpret_cast<unsigned *>(base + sites * n * m->info.d_model * 4) + site * n + slot;
+float *tp_att(const spyb_model *m, uint8_t *base) { return reinterpret_cast<float *>(base); }
+float *tp_act(const spyb_model *m, uint8_t *base) { return reinterpret_cast<float *>(base) + (size_t)TMAX * m->info.d_model; }
+unsigned *tp_flag(const spyb_model *m, uint8_t *base, size_t site, int rank) {
+    return reinterpret_cast<unsigned *>(base + tp_float_count(m) * 4) + site * m->info.tp_size + rank;
 }
 unsigned *tp_counter(const spyb_model *m, size_t site) {
-    const size_t sites = 2 * m->layers.size(), n = m->info.tp_size;
-    return reinterpret_cast<unsigned *>(m->tp_local + sites * n * m->info.d_model * 4) + sites * n + site;
+    const size_t sites = 2 * (size_t)m->info.n_layer, n = m->info.tp_size;
+    return reinterpret_cast<unsigned *>(m->tp_local + tp_float_count(m) * 4) + sites * n + site;
 }
-// producer side of exchange site `site`: scatter into slot tp_rank of every rank, rank 0 adds the residual
-void tp_produce(spyb_model *m, MatvecParams &p, size_t site) {
-    p.epi = EPI_TP_SCATTER; p.tp_n = m->info.tp_size; p.tp_rank = m->info.tp_rank;
-    p.resid = (m->info.tp_rank == 0) ? m->x : nullptr; p.out = nullptr;
-    for (int r = 0; r < m->info.tp_size; ++r) { p.tp_out[r] = tp_slot(m, m->tp_peer[r], site, m->info.tp_rank); p.tp_flag_out[r] = tp_flag(m, m->tp_peer[r], site, m->info.tp_rank); }
-    p.tp_counter = tp_counter(m, site); p.tp_epoch = m->d_pos + 2;
+// producer side of exchange site `site`: this rank's share of the gathered attention output (is_att) or FFN activation
+void tp_produce(spyb_model *m, TpLink &l, size_t site, bool is_att) {
+    l.n = m->info.tp_size; l.rank = m->info.tp_rank;
+    l.stride = is_att ? m->info.d_model : m->info.n_ff;
+    l.len = is_att ? m->dl : m->fl; l.off = (int64_t)l.rank * l.len;
+    for (int r = 0; r < l.n; ++r) { l.gather[r] = is_att ? tp_att(m, m->tp_peer[r]) : tp_act(m, m->tp_peer[r]); l.flag_out[r] = tp_flag(m, m->tp_peer[r], site, l.rank); }
+    l.counter = tp_counter(m, site); l.epoch = m->d_pos + 2;
 }
-// consumer side: activations = sum of the site's slots, left in the residual stream by CTA 0
-void tp_consume(spyb_model *m, MatvecParams &p, size_t site) {
-    p.tp_n = m->info.tp_size; p.tp_rank = m->info.tp_rank;
-    p.tp_in = tp_slot(m, m->tp_local, site, 0); p.tp_flag_in = tp_flag(m, m->tp_local, site, 0); p.tp_x_out = m->x; p.tp_epoch = m->d_pos + 2;
-}
-
-// planes of the matrices a later kernel of the step streams (at most two matrices)
-template <class P>
-void prefetch_next(spyb_model *m, P &p, const DevMatrix *a, const DevMatrix *b = nullptr) {
-    if (!m->be->l2_prefetch_next) { return; }
-    int k = 0;
-    for (const DevMatrix *x : {a, b}) {
-        if (x == nullptr || x->w == nullptr) { continue; }
-        p.pf_ptr[k] = x->w; p.pf_bytes[k] = std::min(matrix_bytes(x->type, x->n_rows, x->nb), m->be->l2_prefetch_cap); ++k;
-    }
+// consumer side: wait until every rank has published its share for this step
+void tp_consume(spyb_model *m, TpLink &l, size_t site) {
+    l.n = m->info.tp_size; l.rank = m->info.tp_rank;
+    l.flag_in = tp_flag(m, m->tp_local, site, 0); l.epoch = m->d_pos + 2;
 }
 
 StepMat step_mat_of(const DevMatrix &A) {
@@ -323,13 +320,16 @@ spyb_status run_step(spyb_model *m, bool tap, int64_t *launches) {
     return SPYB_SUCCESS;
 }
 
-// the five fused kernels of every layer for T tokens whose first position is *d_pos
+// the five fused kernels of every layer for T tokens whose first position is *d_pos.
+// Tensor parallel: Wq|Wk|Wv, attention and FFN up|gate work on this rank's heads / FFN columns; their outputs are
+// all-gathered (inside the kernels over peer memory, or by NCCL) and Wo / FFN down run replicated on the complete
+// vectors, so no f32 sum is ever split across ranks and every rank holds the single-GPU bits of the residual stream.
 spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
     spyb_backend *be = m->be;
     const bool pdl = be->config.use_pdl != 0;
     const LaunchCfg cfg = be->launch_cfg(pdl);
-    const int d = m->info.d_model, tp = m->info.tp_size;
-    const bool fused = tp > 1 && T == 1 && m->tp_ready;   // single-column steps exchange through peer memory inside the kernels
+    const int d = m->info.d_model, ff = m->info.n_ff, tp = m->info.tp_size, rank = m->info.tp_rank;
+    const bool fused = tp > 1 && m->tp_ready;   // exchange through peer memory inside the kernels
     for (size_t L = 0; L < m->layers.size(); ++L) {
         Layer &ly = m->layers[L];
         auto stamps = [&](int k) { return m->d_stamps ? m->d_stamps + 8 * (5 * L + k) : nullptr; };
@@ -339,66 +339,54 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             p.epi = EPI_QKV_ROPE; p.pos_base = m->d_pos; p.rope_table = m->rope_table; p.hd = m->info.head_dim; p.dl = m->dl;
             p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache; p.n_ctx = m->info.n_ctx;
             p.tap_xq = (tap && L == 0) ? m->d_tap : nullptr;
-            prefetch_next(m, p, &ly.wo); p.stamps = stamps(0);
-            if (fused && L > 0) { tp_consume(m, p, 2 * (L - 1) + 1); }
+            p.stamps = stamps(0);
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
         }
-        {   // 2: attention
+        {   // 2: attention of this rank's heads -> its share of the gathered output
             AttnParams a;
-            a.q = m->q; a.k_cache = ly.k_cache; a.v_cache = ly.v_cache; a.out = m->att; a.pos_base = m->d_pos; a.exp_table = be->d_exp_table;
+            a.q = m->q; a.k_cache = ly.k_cache; a.v_cache = ly.v_cache; a.out = m->att + (int64_t)rank * m->dl; a.out_stride = d;
+            a.pos_base = m->d_pos; a.exp_table = be->d_exp_table;
             a.n_head = m->dl / m->info.head_dim; a.hd = m->info.head_dim; a.dl = m->dl; a.T = T; a.n_ctx = m->info.n_ctx;
             a.scale = 1.0f / std::sqrt((float)m->info.head_dim);
-            if (ly.upgate.w) { prefetch_next(m, a, &ly.upgate); } else { prefetch_next(m, a, &ly.up, &ly.gate); }
-            a.stamps = stamps(1);
+            a.stamps = stamps(1); a.error_flag = be->d_error_flag;
+            if (fused) { tp_produce(m, a.tp, 2 * L, true); }
             SPYB_CUDA(be, launch_attention(a, cfg)); ++*launches;
+            if (tp > 1 && !fused && allgather(m, m->att, T, d, m->dl, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
         }
-        {   // 3: quantize -> Wo -> + residual (tensor parallel: partial sums, rank 0 carries the residual)
+        {   // 3: quantize -> Wo -> + residual (replicated)
             MatvecParams p;
-            p.A = ly.wo; p.T = T; p.pro = PRO_QUANT; p.x = m->att; p.x_stride = m->dl;
-            p.resid = m->x; p.out_stride = d;
-            if (tp == 1) { p.epi = EPI_RESID; p.out = m->x; }
-            else if (fused) { tp_produce(m, p, 2 * L); }
-            else { p.epi = (m->info.tp_rank == 0) ? EPI_RESID : EPI_STORE; p.out = m->partial; }
-            prefetch_next(m, p, &ly.down); p.stamps = stamps(2);
+            p.A = ly.wo; p.T = T; p.pro = PRO_QUANT; p.x = m->att; p.x_stride = d;
+            p.epi = EPI_RESID; p.resid = m->x; p.out = m->x; p.out_stride = d; p.stamps = stamps(2);
+            if (fused) { tp_consume(m, p.tp, 2 * L); }
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
-            if (tp > 1 && !fused) {
-                if (allreduce(m, m->partial, (size_t)T * d, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
-                std::swap(m->x, m->partial);
-            }
         }
-        {   // 4: norm + quantize -> up, gate -> up * silu(gate)
+        {   // 4: norm + quantize -> up, gate (this rank's FFN columns) -> up * silu(gate) into its share of the gathered activation
             MatvecParams p;
             if (ly.upgate.w) { p.A = ly.upgate; } else { p.A = ly.up; p.B = ly.gate; p.pair_mode = 1; }
             p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
-            p.eps = m->info.rms_eps; p.epi = EPI_SILU_MUL; p.out = m->act; p.out_stride = m->fl; p.silu_table = be->d_silu_table;
-            prefetch_next(m, p, L + 1 < m->layers.size() ? &m->layers[L + 1].wqkv : &m->head); p.stamps = stamps(3);
-            if (fused) { tp_consume(m, p, 2 * L); }
+            p.eps = m->info.rms_eps; p.epi = EPI_SILU_MUL; p.out = m->act + (int64_t)rank * m->fl; p.out_stride = ff; p.silu_table = be->d_silu_table;
+            p.stamps = stamps(3);
+            if (fused) { tp_produce(m, p.tp, 2 * L + 1, false); }
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
+            if (tp > 1 && !fused && allgather(m, m->act, T, ff, m->fl, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
         }
-        {   // 5: quantize -> Wdown -> + residual
+        {   // 5: quantize -> Wdown -> + residual (replicated)
             MatvecParams p;
-            p.A = ly.down; p.T = T; p.pro = PRO_QUANT; p.x = m->act; p.x_stride = m->fl;
-            p.resid = m->x; p.out_stride = d; p.stamps = stamps(4);
-            if (tp == 1) { p.epi = EPI_RESID; p.out = m->x; }
-            else if (fused) { tp_produce(m, p, 2 * L + 1); }
-            else { p.epi = (m->info.tp_rank == 0) ? EPI_RESID : EPI_STORE; p.out = m->partial; }
+            p.A = ly.down; p.T = T; p.pro = PRO_QUANT; p.x = m->act; p.x_stride = ff;
+            p.epi = EPI_RESID; p.resid = m->x; p.out = m->x; p.out_stride = d; p.stamps = stamps(4);
+            if (fused) { tp_consume(m, p.tp, 2 * L + 1); }
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
-            if (tp > 1 && !fused) {
-                if (allreduce(m, m->partial, (size_t)T * d, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
-                std::swap(m->x, m->partial);
-            }
         }
     }
     return SPYB_SUCCESS;
 }
 
 // output norm + head on column `col` of x -> logits[n_vocab]
-spyb_status run_head(spyb_model *m, int col, int64_t *launches, bool fused_input = false) {
+spyb_status run_head(spyb_model *m, int col, int64_t *launches) {
     MatvecParams p;
     p.A = m->head; p.T = 1; p.pro = PRO_NORM_QUANT; p.x = m->x + (int64_t)col * m->info.d_model; p.x_stride = m->info.d_model;
     p.norm_w = m->output_norm; p.eps = m->info.rms_eps; p.epi = EPI_STORE; p.out = m->logits; p.out_stride = m->info.n_vocab;
     p.stamps = m->d_stamps ? m->d_stamps + 8 * (5 * m->layers.size()) : nullptr;
-    if (fused_input) { tp_consume(m, p, 2 * m->layers.size() - 1); }
     SPYB_CUDA(m->be, launch_matvec(p, m->be->launch_cfg(m->be->config.use_pdl != 0))); ++*launches;
     return SPYB_SUCCESS;
 }
@@ -408,7 +396,7 @@ spyb_status run_decode_step(spyb_model *m, int64_t *launches) {
         if (run_step(m, false, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
     } else {
         if (run_layers(m, 1, false, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
-        if (run_head(m, 0, launches, m->info.tp_size > 1 && m->tp_ready) != SPYB_SUCCESS) { return SPYB_FAIL; }
+        if (run_head(m, 0, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
     }
     SPYB_CUDA(m->be, launch_argmax_embed(m->logits, m->info.n_vocab, m->d_token, m->d_history, m->d_pos, m->embd, m->embd_type,
                                          m->info.d_model, m->x, m->be->launch_cfg(m->be->config.use_pdl != 0)));
@@ -447,9 +435,10 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
     I.head_dim = I.d_model / I.n_head;
     if (I.head_dim != 128) { be->set_error("head_dim %d is not supported (128 only)", I.head_dim); return fail(SPYB_UNSUPPORTED); }
     const int tp = I.tp_size;
-    if (I.n_head % tp != 0 || (I.n_ff / tp) % 32 != 0 || I.n_ff % tp != 0) { be->set_error("tp_size %d does not divide heads / FFN blocks", tp); return fail(SPYB_FAIL); }
-    m->dl = I.d_model / tp; m->fl = I.n_ff / tp;
-    const int d = I.d_model, dl = m->dl, fl = m->fl, r = I.tp_rank;
+    int64_t shard[4];
+    if (spyb_tp_layer_shard(I.d_model, I.n_head, I.n_ff, tp, I.tp_rank, shard) != SPYB_SUCCESS) { be->set_error("tp_size %d does not divide heads / FFN blocks", tp); return fail(SPYB_FAIL); }
+    m->dl = (int)shard[1]; m->fl = (int)shard[3];
+    const int d = I.d_model, dl = m->dl, fl = m->fl, r = I.tp_rank;   // (shard[0] == r * dl, shard[2] == r * fl)
 
     auto tensor = [&](const std::string &name, const GgufTensor **t, const uint8_t **data) {
         auto it = f.tensors.find(name);
@@ -544,17 +533,17 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         if ((st = upload_w(p + "attn_q.weight", d, d, (int64_t)r * dl, dl, 0, d / 32, &dummy, &ly.wqkv, 0)) != SPYB_SUCCESS) { return fail(st); }
         if ((st = upload_w(p + "attn_k.weight", d, d, (int64_t)r * dl, dl, 0, d / 32, &dummy, &ly.wqkv, dl)) != SPYB_SUCCESS) { return fail(st); }
         if ((st = upload_w(p + "attn_v.weight", d, d, (int64_t)r * dl, dl, 0, d / 32, &dummy, &ly.wqkv, 2 * (int64_t)dl)) != SPYB_SUCCESS) { return fail(st); }
-        // Wo: all d rows, input columns of this rank's heads (a block sub-range of every row)
+        // Wo: replicated (all d rows, all d input columns): it consumes the gathered attention output
         auto ito = f.tensors.find(p + "attn_output.weight");
         const int wo_tile = tile_for("SPYB_TILE_WO", d, auto_tile(d));
         if (ito != f.tensors.end() && wo_tile != 4) {
-            if ((st = alloc_matrix(be, ito->second.type, d, dl / 32, &ly.wo, wo_tile, use_mma)) != SPYB_SUCCESS) { return fail(st); }
-            st = upload_w(p + "attn_output.weight", d, d, 0, d, (int64_t)r * dl / 32, dl / 32, &dummy, &ly.wo, 0);
+            if ((st = alloc_matrix(be, ito->second.type, d, d / 32, &ly.wo, wo_tile, use_mma)) != SPYB_SUCCESS) { return fail(st); }
+            st = upload_w(p + "attn_output.weight", d, d, 0, d, 0, d / 32, &dummy, &ly.wo, 0);
         } else {
-            st = upload_w(p + "attn_output.weight", d, d, 0, d, (int64_t)r * dl / 32, dl / 32, &ly.wo, nullptr, 0);
+            st = upload_w(p + "attn_output.weight", d, d, 0, d, 0, d / 32, &ly.wo, nullptr, 0);
         }
         if (st != SPYB_SUCCESS) { return fail(st); }
-        // FFN: rows [r*fl, (r+1)*fl) of up and gate; down keeps all rows and this rank's input columns
+        // FFN: rows [r*fl, (r+1)*fl) of up and gate; down is replicated and consumes the gathered activation
         auto itu = f.tensors.find(p + "ffn_up.weight");
         const int ug_tile = tile_for("SPYB_TILE_UPGATE", 2 * (int64_t)fl, auto_tile(2 * (int64_t)fl));
         if (itu != f.tensors.end() && ug_tile != 4) {
@@ -571,10 +560,10 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         auto itd = f.tensors.find(p + "ffn_down.weight");
         const int down_tile = tile_for("SPYB_TILE_DOWN", d, auto_tile(d));
         if (itd != f.tensors.end() && down_tile != 4) {
-            if ((st = alloc_matrix(be, itd->second.type, d, fl / 32, &ly.down, down_tile, use_mma)) != SPYB_SUCCESS) { return fail(st); }
-            st = upload_w(p + "ffn_down.weight", I.n_ff, d, 0, d, (int64_t)r * fl / 32, fl / 32, &dummy, &ly.down, 0);
+            if ((st = alloc_matrix(be, itd->second.type, d, I.n_ff / 32, &ly.down, down_tile, use_mma)) != SPYB_SUCCESS) { return fail(st); }
+            st = upload_w(p + "ffn_down.weight", I.n_ff, d, 0, d, 0, I.n_ff / 32, &dummy, &ly.down, 0);
         } else {
-            st = upload_w(p + "ffn_down.weight", I.n_ff, d, 0, d, (int64_t)r * fl / 32, fl / 32, &ly.down, nullptr, 0);
+            st = upload_w(p + "ffn_down.weight", I.n_ff, d, 0, d, 0, I.n_ff / 32, &ly.down, nullptr, 0);
         }
         if (st != SPYB_SUCCESS) { return fail(st); }
         if (dev_alloc(m, &ly.k_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS || dev_alloc(m, &ly.v_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
@@ -595,9 +584,15 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         if (dev_alloc(m, &m->rope_table, tab.size()) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
         if (cudaMemcpy(m->rope_table, tab.data(), tab.size() * sizeof(float2), cudaMemcpyHostToDevice) != cudaSuccess) { be->set_error("rope table upload failed"); return fail(SPYB_FAIL); }
     }
-    const int TMAX = 8;
-    bool ok = dev_alloc(m, &m->x, (size_t)TMAX * d) == SPYB_SUCCESS && dev_alloc(m, &m->partial, (size_t)TMAX * d) == SPYB_SUCCESS &&
-              dev_alloc(m, &m->att, (size_t)TMAX * dl) == SPYB_SUCCESS && dev_alloc(m, &m->act, (size_t)TMAX * fl) == SPYB_SUCCESS &&
+    {   // the exchange buffer: gathered attention output and FFN activation, flag words, counters (one plain cudaMalloc: it is exported)
+        void *raw = nullptr;
+        if (cudaMalloc(&raw, tp_buffer_bytes(m)) != cudaSuccess || cudaMemset(raw, 0, tp_buffer_bytes(m)) != cudaSuccess) { be->set_error("exchange buffer allocation failed"); return fail(SPYB_FAIL); }
+        m->owned.push_back(raw);
+        m->tp_local = static_cast<uint8_t *>(raw);
+        m->tp_peer[I.tp_rank] = m->tp_local;
+        m->att = tp_att(m, m->tp_local); m->act = tp_act(m, m->tp_local);
+    }
+    bool ok = dev_alloc(m, &m->x, (size_t)TMAX * d) == SPYB_SUCCESS && dev_alloc(m, &m->scratch, (size_t)TMAX * d) == SPYB_SUCCESS &&
               dev_alloc(m, &m->logits, (size_t)I.n_vocab) == SPYB_SUCCESS && dev_alloc(m, &m->q, (size_t)TMAX * dl) == SPYB_SUCCESS &&
               dev_alloc(m, &m->d_pos, 4) == SPYB_SUCCESS && dev_alloc(m, &m->d_token, 4) == SPYB_SUCCESS &&
               dev_alloc(m, &m->d_tokens_in, TMAX) == SPYB_SUCCESS && dev_alloc(m, &m->d_history, (size_t)I.n_ctx + 8) == SPYB_SUCCESS &&
@@ -659,14 +654,6 @@ spyb_status spyb_model_tp_export(spyb_model *m, void *handle_64) {
     spyb_backend *be = m->be;
     if (m->info.tp_size < 2 || m->info.tp_size > TP_MAX) { be->set_error("tp_export: tp_size %d", m->info.tp_size); return SPYB_FAIL; }
     cudaSetDevice(be->config.device_id);
-    if (m->tp_local == nullptr) {
-        void *raw = nullptr;
-        SPYB_CUDA(be, cudaMalloc(&raw, tp_buffer_bytes(m)));          // plain cudaMalloc: the allocation is exported to the other ranks
-        SPYB_CUDA(be, cudaMemset(raw, 0, tp_buffer_bytes(m)));
-        SPYB_CUDA(be, cudaDeviceSynchronize());
-        m->owned.push_back(raw);
-        m->tp_local = static_cast<uint8_t *>(raw);
-    }
     cudaIpcMemHandle_t h;
     SPYB_CUDA(be, cudaIpcGetMemHandle(&h, m->tp_local));
     static_assert(sizeof(h) == 64, "IPC handle size");
@@ -714,7 +701,7 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
             if (ce == cudaSuccess && m->step_ok) { st = run_step(m, true, &n); }
             else {
                 if (ce == cudaSuccess) { st = run_layers(m, 1, true, &n); }
-                if (ce == cudaSuccess && st == SPYB_SUCCESS) { st = run_head(m, 0, &n, m->info.tp_size > 1 && m->tp_ready); }
+                if (ce == cudaSuccess && st == SPYB_SUCCESS) { st = run_head(m, 0, &n); }
             }
             if (ce == cudaSuccess && st == SPYB_SUCCESS) { ce = cudaMemcpyAsync(m->h_logits_pinned, m->logits, (size_t)m->info.n_vocab * 4, cudaMemcpyDeviceToHost, be->stream); }
             const cudaError_t ee = cudaStreamEndCapture(be->stream, &graph);
@@ -741,7 +728,7 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
         return SPYB_SUCCESS;
     }
     SPYB_CUDA(be, cudaEventRecord(m->ev0, be->stream));
-    const int tmax = std::min(8, std::min(matvec_max_columns(m->info.d_model / 32), matvec_max_columns(m->fl / 32)));
+    const int tmax = std::min(8, std::min(matvec_max_columns(m->info.d_model / 32), matvec_max_columns(m->info.n_ff / 32)));
     for (int t0 = 0; t0 < n_tokens; t0 += tmax) {
         const int T = std::min(tmax, n_tokens - t0);
         SPYB_CUDA(be, cudaStreamSynchronize(be->stream));   // pinned staging words are reused per pass
@@ -754,7 +741,7 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
         SPYB_CUDA(be, launch_embed(m->d_tokens_in, T, m->embd, m->embd_type, m->info.d_model, m->x, be->stream)); ++launches;
         if (run_layers(m, T, t0 == 0, &launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
         if (t0 + T == n_tokens) {
-            if (run_head(m, T - 1, &launches, m->info.tp_size > 1 && m->tp_ready && T == 1) != SPYB_SUCCESS) { return SPYB_FAIL; }
+            if (run_head(m, T - 1, &launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
             if (logits_host != nullptr) {
                 SPYB_CUDA(be, cudaMemcpyAsync(m->h_logits_pinned, m->logits, (size_t)m->info.n_vocab * 4, cudaMemcpyDeviceToHost, be->stream));
             }
@@ -839,11 +826,11 @@ float spyb_model_bench_kernel(spyb_model *m, int32_t kind, int32_t sweeps, uint6
         case 0: p.A = ly.wqkv; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.attn_norm; p.eps = m->info.rms_eps;
                 p.epi = EPI_QKV_ROPE; p.pos_base = m->d_pos; p.rope_table = m->rope_table; p.hd = m->info.head_dim; p.dl = m->dl;
                 p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache; p.n_ctx = m->info.n_ctx; break;
-        case 1: p.A = ly.wo; p.pro = PRO_QUANT; p.x = m->att; p.x_stride = m->dl; p.epi = EPI_STORE; p.out = m->partial; p.out_stride = d; break;
+        case 1: p.A = ly.wo; p.pro = PRO_QUANT; p.x = m->att; p.x_stride = d; p.epi = EPI_STORE; p.out = m->scratch; p.out_stride = d; break;
         case 2: if (ly.upgate.w) { p.A = ly.upgate; } else { p.A = ly.up; p.B = ly.gate; p.pair_mode = 1; }
                 p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
-                p.eps = m->info.rms_eps; p.epi = EPI_SILU_MUL; p.out = m->act; p.out_stride = m->fl; p.silu_table = be->d_silu_table; break;
-        case 3: p.A = ly.down; p.pro = PRO_QUANT; p.x = m->act; p.x_stride = m->fl; p.epi = EPI_STORE; p.out = m->partial; p.out_stride = d; break;
+                p.eps = m->info.rms_eps; p.epi = EPI_SILU_MUL; p.out = m->act + (int64_t)m->info.tp_rank * m->fl; p.out_stride = m->info.n_ff; p.silu_table = be->d_silu_table; break;
+        case 3: p.A = ly.down; p.pro = PRO_QUANT; p.x = m->act; p.x_stride = m->info.n_ff; p.epi = EPI_STORE; p.out = m->scratch; p.out_stride = d; break;
         default: p.A = m->head; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = m->output_norm; p.eps = m->info.rms_eps;
                 p.epi = EPI_STORE; p.out = m->logits; p.out_stride = m->info.n_vocab; break;
         }
@@ -854,19 +841,20 @@ float spyb_model_bench_kernel(spyb_model *m, int32_t kind, int32_t sweeps, uint6
     float total_ms = 0.f; int64_t n = 0;
     const bool hot = std::getenv("SPYB_BENCH_L2_HOT") != nullptr;   // every launch on layer 0's matrix: it stays in L2
     if (kind == 4) {
-        // a single 70 MB matrix would stay in the 126 MB L2 between launches: evict it with a 512 MB memset each time
-        void *flush = nullptr;
-        if (cudaMalloc(&flush, (size_t)512 << 20) != cudaSuccess) { return -1.f; }
+        // a single 70 MB matrix would stay in the 126 MB L2 between launches: every timed launch follows a sweep of the
+        // FFN down kernel over the layers' matrices (hundreds of MB), which evicts it
+        const int saved_kind = kind;
         for (int s = 0; s < sweeps * 4; ++s) {
-            cudaMemsetAsync(flush, s, (size_t)512 << 20, be->stream);
+            kind = 3;
+            for (const Layer &ly : m->layers) { if (launch_matvec(params(ly), cfg) != cudaSuccess) { return -1.f; } }
+            kind = saved_kind;
             cudaEventRecord(m->ev0, be->stream);
-            if (launch_matvec(p0, cfg) != cudaSuccess) { cudaFree(flush); return -1.f; }
+            if (launch_matvec(p0, cfg) != cudaSuccess) { return -1.f; }
             cudaEventRecord(m->ev1, be->stream);
             cudaStreamSynchronize(be->stream);
             float ms = 0.f; cudaEventElapsedTime(&ms, m->ev0, m->ev1);
             total_ms += ms; ++n;
         }
-        cudaFree(flush);
     } else {
         cudaEventRecord(m->ev0, be->stream);
         for (int s = 0; s < sweeps; ++s) {
@@ -877,6 +865,15 @@ float spyb_model_bench_kernel(spyb_model *m, int32_t kind, int32_t sweeps, uint6
         cudaEventElapsedTime(&total_ms, m->ev0, m->ev1);
     }
     return n ? total_ms / (float)n : -1.f;
+}
+
+spyb_status spyb_tp_layer_shard(int32_t d_model, int32_t n_head, int32_t n_ff, int32_t tp_size, int32_t tp_rank, int64_t out[4]) {
+    if (out == nullptr || tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size || d_model <= 0 || n_head <= 0 || n_ff <= 0 || d_model % n_head != 0) { return SPYB_FAIL; }
+    if (n_head % tp_size != 0 || n_ff % tp_size != 0 || (n_ff / tp_size) % 32 != 0 || (d_model / n_head) % 32 != 0) { return SPYB_FAIL; }
+    const int64_t dl = d_model / tp_size, fl = n_ff / tp_size;
+    out[0] = (int64_t)tp_rank * dl; out[1] = dl;   // rows of Wq, Wk, Wv = elements of the gathered attention output
+    out[2] = (int64_t)tp_rank * fl; out[3] = fl;   // rows of W_up, W_gate = elements of the gathered FFN activation
+    return SPYB_SUCCESS;
 }
 
 spyb_status spyb_set_wait_limit_ns(spyb_backend *be, uint64_t ns) {
@@ -915,9 +912,9 @@ spyb_status spyb_model_read_activation(spyb_model *m, int32_t which, void *host,
     const void *src = nullptr; uint64_t avail = 0;
     switch (which) {
     case 0: src = m->q;      avail = (uint64_t)8 * m->dl * 2; break;
-    case 1: src = m->att;    avail = (uint64_t)8 * m->dl * 4; break;
+    case 1: src = m->att;    avail = (uint64_t)8 * m->info.d_model * 4; break;
     case 2: src = m->x;      avail = (uint64_t)8 * m->info.d_model * 4; break;
-    case 3: src = m->act;    avail = (uint64_t)8 * m->fl * 4; break;
+    case 3: src = m->act;    avail = (uint64_t)8 * m->info.n_ff * 4; break;
     case 4: src = m->logits; avail = (uint64_t)m->info.n_vocab * 4; break;
     default: m->be->set_error("read_activation: unknown buffer %d", which); return SPYB_FAIL;
     }

@@ -13,6 +13,7 @@
 
 #include "spyb_common.cuh"
 #include "spyb_kernels.h"
+#include "spyb_tp.cuh"
 
 #include <math_constants.h>
 
@@ -66,14 +67,6 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
 
     pdl_launch_dependents();
     stamp(p.stamps, 0, false); stamp(p.stamps, 4, true);
-    {   // weights of a later kernel of the step: towards L2 while attention occupies only a few SMs
-        const int64_t gw = ((int64_t)blockIdx.y * gridDim.x + blockIdx.x) * ATT_THREADS + tid, gn = (int64_t)gridDim.x * gridDim.y * ATT_THREADS;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-            const int64_t np = (int64_t)((p.pf_bytes[k] + 4095) / 4096);
-            for (int64_t i = gw; i < np; i += gn) { l2_prefetch_piece(p.pf_ptr[k], p.pf_bytes[k], i, np); }
-        }
-    }
     pdl_wait();
     stamp(p.stamps, 1, false); stamp(p.stamps, 5, true);
 
@@ -284,8 +277,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
                 if (j + 3 < n_vis) { tail = fmaf(v23.y, pr.w, tail); }
             }
         }
-        if (half == 0) { p.out[(int64_t)t * p.dl + (int64_t)h * ATT_HD + e] = __fadd_rn(tail, simd); }
+        if (half == 0) { p.out[(int64_t)t * (p.out_stride ? p.out_stride : p.dl) + (int64_t)h * ATT_HD + e] = __fadd_rn(tail, simd); }
     }
+    tp_publish(p.tp, p.T);
     if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
 }
 

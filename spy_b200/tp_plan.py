@@ -1,37 +1,26 @@
-"""Tensor-parallel partition of one LLaMa layer, as `spyb_model_load_gguf` cuts it at upload
-(spy_b200/csrc/spyb_model.cu): rank r of N owns the heads [r*H/N, (r+1)*H/N) - i.e. those rows of Wq, Wk, Wv
-and the matching input columns of Wo (whole 32-element blocks: head_dim is a multiple of 32) - and the FFN
-columns [r*F/N, (r+1)*F/N): those rows of W_up / W_gate and the matching input columns of W_down.
-Norms, the residual stream, embeddings and the head are replicated; the two partial [d] vectors of a layer
-are summed over ranks (all-reduce), rank 0 carrying the residual.
+"""Tensor-parallel partition of one LLaMa layer. The arithmetic is the library's own (spyb_tp_layer_shard, the function
+spyb_model_load_gguf cuts its shards with), bound here so that it can be checked without a GPU: rank r of N owns the heads
+[r*H/N, (r+1)*H/N) - those rows of Wq, Wk, Wv, their KV cache and attention - and the FFN columns [r*F/N, (r+1)*F/N) - those
+rows of W_up / W_gate. The attention output and the FFN activation are all-gathered; Wo, W_down, the norms, the residual
+stream, the embeddings and the head are replicated, so no floating-point sum is ever split across ranks.
 
-The reference has no tensor parallelism (backend/distributor: graph_divider is empty); this plan is the
-contract between the loader and the model step plan, kept here so that it can be checked without a GPU."""
+The reference has no tensor parallelism (backend/distributor: graph_divider is empty)."""
+import ctypes as C
 from dataclasses import dataclass
+
+from . import backend
 
 
 @dataclass(frozen=True)
 class LayerShard:
     rank: int
     tp: int
-    qkv_rows: range        # rows of each of Wq, Wk, Wv (and columns of Wo) held by this rank
-    wo_blocks: range       # 32-element blocks of every Wo row
-    ffn_rows: range        # rows of W_up and W_gate
-    down_blocks: range     # 32-element blocks of every W_down row
-    carries_residual: bool
-
-
-def check_divisible(d_model: int, n_head: int, n_ff: int, tp: int) -> None:
-    if tp < 1 or n_head % tp or n_ff % tp or (n_ff // tp) % 32 or d_model % n_head:
-        raise ValueError(f"tp_size {tp} does not divide heads / FFN blocks")
-    if (d_model // n_head) % 32:
-        raise ValueError("head_dim must be a multiple of the 32-element quantization block")
+    qkv_rows: range        # rows of each of Wq, Wk, Wv held by this rank = its elements of the gathered attention output
+    ffn_rows: range        # rows of W_up and W_gate = its elements of the gathered FFN activation
 
 
 def layer_shard(d_model: int, n_head: int, n_ff: int, tp: int, rank: int) -> LayerShard:
-    check_divisible(d_model, n_head, n_ff, tp)
-    if not 0 <= rank < tp:
-        raise ValueError("rank out of range")
-    dl, fl = d_model // tp, n_ff // tp
-    return LayerShard(rank, tp, range(rank * dl, (rank + 1) * dl), range(rank * dl // 32, (rank + 1) * dl // 32),
-                      range(rank * fl, (rank + 1) * fl), range(rank * fl // 32, (rank + 1) * fl // 32), rank == 0)
+    out = (C.c_int64 * 4)()
+    if backend.lib().spyb_tp_layer_shard(d_model, n_head, n_ff, tp, rank, out) != backend.SUCCESS:
+        raise ValueError(f"tp_size {tp} / rank {rank} does not give whole heads and whole 32-element FFN blocks")
+    return LayerShard(rank, tp, range(out[0], out[0] + out[1]), range(out[2], out[2] + out[3]))

@@ -32,3 +32,9 @@ def test_create_fails_loudly_without_a_gpu():
         pytest.skip("a GPU is present")
     with pytest.raises(backend.SpybError):
         backend.B200Backend(0)
+
+
+def test_shared_memory_ledger_is_kept_per_device_and_kernel():
+    """cudaFuncAttributeMaxDynamicSharedMemorySize belongs to a (device, kernel) pair: the library's record of what it
+    has already raised must be kept per pair, or the second device of a process never gets the attribute set."""
+    assert backend.lib().spyb_selftest_host() == 0

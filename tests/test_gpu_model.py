@@ -217,10 +217,10 @@ def test_step_kernel_wait_runs_out_and_is_reported(oracle, tmp_models, monkeypat
 
 
 def test_rmsnorm_running_sum_on_hard_inputs(oracle, tmp_models):
-    """The RMSNorm sum of squares is a serial f32 running sum on the CPU; the GPU forms it in parallel from integer
-    increments per binade plus a short serial walk, with a serial fallback. Inputs that stress it - exact ties (ones,
-    powers of two, small dyadic numbers), huge outliers, leading zeros, underflowing squares, all zeros - must still
-    give the CPU's bits. d_model = 4096 exercises the full 1024-group sum."""
+    """The RMSNorm sum of squares is a serial f32 running sum on the CPU (groups of four squares added to one
+    accumulator in order); the GPU forms the groups in parallel and runs the same chain on one thread. Inputs that
+    stress the order of the additions - exact ties (ones, powers of two, small dyadic numbers), huge outliers, leading
+    zeros, underflowing squares, all zeros - must give the CPU's bits. d_model = 4096 exercises the full 1024-group sum."""
     d, v = 4096, 16
     rng = np.random.default_rng(77)
     E = rng.standard_normal((v, d)).astype(np.float32)
