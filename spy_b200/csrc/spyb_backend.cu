@@ -346,10 +346,16 @@ spyb_status spyb_attention(spyb_backend *be, const void *q_f16, const void *k_ca
     a.q = static_cast<const __half *>(q_f16); a.k_cache = static_cast<const __half *>(k_cache_f16); a.v_cache = static_cast<const __half *>(v_cache_t_f16);
     a.out = out; a.pos_base = d_pos; a.exp_table = be->d_exp_table; a.n_head = n_head; a.hd = head_dim; a.dl = n_head * head_dim; a.T = n_tokens; a.n_ctx = n_ctx;
     a.scale = 1.0f / std::sqrt((float)head_dim);
+    const size_t scratch_bytes = attention_scratch_floats(n_ctx, n_head, n_tokens) * sizeof(float);
+    if (scratch_bytes > 0) {
+        a.scratch = static_cast<float *>(be->arena.alloc(scratch_bytes));
+        if (a.scratch == nullptr) { be->arena.free(d_pos, 2 * sizeof(int)); be->set_error("attention: out of device memory"); return SPYB_FAIL; }
+    }
     cudaError_t err = cudaMemcpyAsync(d_pos, host_pos, sizeof(host_pos), cudaMemcpyHostToDevice, be->stream);
     if (err == cudaSuccess) { err = launch_attention(a, be->launch_cfg(false)); }
     if (err == cudaSuccess) { err = cudaStreamSynchronize(be->stream); }
     be->arena.free(d_pos, 2 * sizeof(int));
+    if (a.scratch != nullptr) { be->arena.free(a.scratch, scratch_bytes); }
     if (err != cudaSuccess) { be->set_error("attention failed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
     return SPYB_SUCCESS;
 }

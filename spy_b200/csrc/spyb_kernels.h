@@ -101,6 +101,7 @@ struct AttnParams {
     int64_t       out_stride = 0;     // 0 = dl
     const int    *pos_base = nullptr;
     const float  *exp_table = nullptr;
+    float        *scratch = nullptr;  // [T][n_head][n_ctx] floats; needed when attention_scratch_floats() > 0 (long contexts)
     int   n_head = 0, hd = 128, dl = 0, T = 1, n_ctx = 0;
     float scale = 0.f;
     unsigned long long *stamps = nullptr;                           // as in MatvecParams
@@ -137,6 +138,7 @@ size_t      matvec_smem_bytes(int nb, int T);
 int         matvec_max_columns(int nb);   // most activation columns one launch can hold in shared memory for rows of nb blocks
 cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg);
 cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg);
+size_t      attention_scratch_floats(int n_ctx, int n_head, int T);
 
 // upload-time re-tiling of raw reference-layout blocks into DevMatrix planes
 // Source row i (i = src_row0 .. src_row0 + n_rows - 1 of the tensor being uploaded; `raw` points at row src_row0) lands

@@ -159,7 +159,7 @@ struct spyb_model {
     int             embd_type = 0;
     float2         *rope_table = nullptr;
     // activations for up to 8 tokens per pass
-    float  *x = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr, *scratch = nullptr;   // att [T][d_model] and act [T][n_ff] are the gathered vectors (inside tp_local)
+    float  *x = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr, *scratch = nullptr, *att_scratch = nullptr;   // att [T][d_model] and act [T][n_ff] are the gathered vectors (inside tp_local)
     __half *q = nullptr;
     int    *d_pos = nullptr;
     int32_t *d_token = nullptr, *d_tokens_in = nullptr, *d_history = nullptr;
@@ -348,7 +348,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             a.pos_base = m->d_pos; a.exp_table = be->d_exp_table;
             a.n_head = m->dl / m->info.head_dim; a.hd = m->info.head_dim; a.dl = m->dl; a.T = T; a.n_ctx = m->info.n_ctx;
             a.scale = 1.0f / std::sqrt((float)m->info.head_dim);
-            a.stamps = stamps(1); a.error_flag = be->d_error_flag;
+            a.stamps = stamps(1); a.error_flag = be->d_error_flag; a.scratch = m->att_scratch;
             if (fused) { tp_produce(m, a.tp, 2 * L, true); }
             SPYB_CUDA(be, launch_attention(a, cfg)); ++*launches;
             if (tp > 1 && !fused && allgather(m, m->att, T, d, m->dl, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
@@ -592,7 +592,9 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         m->tp_peer[I.tp_rank] = m->tp_local;
         m->att = tp_att(m, m->tp_local); m->act = tp_act(m, m->tp_local);
     }
+    const size_t att_scratch = attention_scratch_floats(I.n_ctx, dl / I.head_dim, TMAX);
     bool ok = dev_alloc(m, &m->x, (size_t)TMAX * d) == SPYB_SUCCESS && dev_alloc(m, &m->scratch, (size_t)TMAX * d) == SPYB_SUCCESS &&
+              (att_scratch == 0 || dev_alloc(m, &m->att_scratch, att_scratch) == SPYB_SUCCESS) &&
               dev_alloc(m, &m->logits, (size_t)I.n_vocab) == SPYB_SUCCESS && dev_alloc(m, &m->q, (size_t)TMAX * dl) == SPYB_SUCCESS &&
               dev_alloc(m, &m->d_pos, 4) == SPYB_SUCCESS && dev_alloc(m, &m->d_token, 4) == SPYB_SUCCESS &&
               dev_alloc(m, &m->d_tokens_in, TMAX) == SPYB_SUCCESS && dev_alloc(m, &m->d_history, (size_t)I.n_ctx + 8) == SPYB_SUCCESS &&

@@ -283,20 +283,207 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
     if (p.stamps != nullptr) { __syncthreads(); stamp(p.stamps, 3, true); }
 }
 
-cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
-    if (p.hd != ATT_HD || p.T < 1 || p.n_ctx < 1 || (p.n_ctx & 3) || (p.dl & 7)) { return cudaErrorInvalidValue; }
-    const size_t n_pad = ((size_t)p.n_ctx + 3) & ~(size_t)3;
-    const size_t smem = (n_pad + n_pad / 4 + ATT_HD) * sizeof(float) + 16;
-    if (smem > 200 * 1024) { return cudaErrorInvalidValue; }
-    cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(attention_kernel), smem);
-    if (err != cudaSuccess) { return err; }
+// ---------------------------------------------------------------------------------------------
+// Long contexts (n_ctx > ATT_LONG_MIN): the same arithmetic as attention_kernel, spread over the chip in three kernels
+// that meet in a scratch buffer [T][n_head][n_ctx] of floats (scores, then probabilities):
+//   attn_scores_kernel   one thread per (position, head, token): Dot<FP16,FP16>(K row, Q), all 32 accumulators in registers
+//   attn_softmax_kernel  one CTA per (head, token): scale, maximum, table exp, std::reduce's grouped running sum, 1/sum,
+//                        probabilities rounded to fp16
+//   attn_pv_kernel       one warp per output element, lane = 8 * accumulator + element of the CPU's 4 x 8 accumulators
+//                        (position j of a 32-step goes to lane j % 32), sixteen elements per CTA
+// HBM-bound: the K rows and the V^T rows of the visible positions are read once (2 * n_kv * 128 * 2 bytes per head).
+constexpr int ATT_LONG_MIN = 1024;
+
+__global__ void __launch_bounds__(256) attn_scores_kernel(const AttnParams p) {
+    __shared__ __align__(16) float qf[ATT_HD];
+    const int h = blockIdx.y, t = blockIdx.z, tid = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n_vis = p.pos_base[0] + t + 1;
+    if ((int)blockIdx.x * 256 >= n_vis) { return; }
+    const int n_pad = (p.n_ctx + 3) & ~3;
+    if (tid < ATT_HD) { qf[tid] = __half2float(p.q[(int64_t)t * p.dl + (int64_t)h * ATT_HD + tid]); }
+    __syncthreads();
+    const int j = blockIdx.x * 256 + tid;
+    if (j >= n_vis) { return; }
+    uint4 kv[16];
+    {
+        const uint4 *krow = reinterpret_cast<const uint4 *>(p.k_cache + (int64_t)j * p.dl + (int64_t)h * ATT_HD);
+#pragma unroll
+        for (int a = 0; a < 16; ++a) { kv[a] = krow[a]; }
+    }
+    const float4 *q4 = reinterpret_cast<const float4 *>(qf);
+    float acc[4][8];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { acc[a][e] = 0.f; }
+    }
+#pragma unroll
+    for (int step = 0; step < 3; ++step) {       // elements 0..95: accumulator a takes elements 32 * step + 8a .. + 7
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+            float kf[8]; unpack8(kv[4 * step + a], kf);
+            const float4 qa = q4[(4 * step + a) * 2], qb = q4[(4 * step + a) * 2 + 1];
+            const float  qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { acc[a][e] = fmaf(kf[e], qv[e], acc[a][e]); }
+        }
+    }
+    float u[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float lo = __fadd_rn(__fadd_rn(acc[0][e], acc[2][e]), __fadd_rn(acc[1][e], acc[3][e]));
+        const float hi = __fadd_rn(__fadd_rn(acc[0][e + 4], acc[2][e + 4]), __fadd_rn(acc[1][e + 4], acc[3][e + 4]));
+        u[e] = __fadd_rn(lo, hi);
+    }
+    const float simd = __fadd_rn(__fadd_rn(u[0], u[1]), __fadd_rn(u[2], u[3]));
+    float tail = 0.f;                             // elements 96..127: scalar chain
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+        float kf[8]; unpack8(kv[12 + a], kf);
+        const float4 qa = q4[(12 + a) * 2], qb = q4[(12 + a) * 2 + 1];
+        const float  qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { tail = fmaf(kf[e], qv[e], tail); }
+    }
+    p.scratch[((int64_t)t * p.n_head + h) * n_pad + j] = __fadd_rn(tail, simd);
+}
+
+constexpr int ATT_SM_THREADS = 1024;
+__global__ void __launch_bounds__(ATT_SM_THREADS) attn_softmax_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) float att_smem[];
+    __shared__ float red[ATT_SM_THREADS / WARP];
+    __shared__ float bcast;
+    const int h = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n_vis = p.pos_base[0] + t + 1;
+    const int n_tot = (p.pos_base[1] > 0) ? p.pos_base[1] : p.pos_base[0] + p.T;
+    const int n_pad = (p.n_ctx + 3) & ~3;
+    float *sc = att_smem, *gs = sc + n_pad;
+    float *row = p.scratch + ((int64_t)t * p.n_head + h) * n_pad;
+    // masked softmax: (score + mask) * scale, subtract the maximum, table exp, std::reduce, multiply by 1/sum
+    float m = -CUDART_INF_F;
+    for (int j = tid; j < n_vis; j += ATT_SM_THREADS) {
+        const float v = __fmul_rn(__fadd_rn(row[j], 0.0f), p.scale);
+        sc[j] = v;
+        m = fmaxf(m, v);
+    }
+    m = warp_max(m);
+    if (lane == 0) { red[warp] = m; }
+    __syncthreads();
+    m = red[0];
+#pragma unroll
+    for (int w = 1; w < ATT_SM_THREADS / WARP; ++w) { m = fmaxf(m, red[w]); }
+    const int n_tot4 = (n_tot + 3) & ~3;
+    for (int j = tid; j < n_tot4; j += ATT_SM_THREADS) { sc[j] = (j < n_vis) ? p.exp_table[f2h(__fsub_rn(sc[j], m))] : 0.f; }
+    __syncthreads();
+    for (int g = tid; g < (n_tot >> 2); g += ATT_SM_THREADS) {
+        const float4 v = reinterpret_cast<const float4 *>(sc)[g];
+        gs[g] = __fadd_rn(__fadd_rn(v.x, v.y), __fadd_rn(v.z, v.w));
+    }
+    __syncthreads();
+    if (tid == 0) {
+        float sum = 0.f;
+        const int ng = n_tot >> 2;
+        int g = 0;
+        for (; g + 4 <= ng; g += 4) {
+            const float4 v = *reinterpret_cast<const float4 *>(gs + g);
+            sum = __fadd_rn(sum, v.x); sum = __fadd_rn(sum, v.y); sum = __fadd_rn(sum, v.z); sum = __fadd_rn(sum, v.w);
+        }
+        for (; g < ng; ++g) { sum = __fadd_rn(sum, gs[g]); }
+        for (int j = ng << 2; j < n_tot; ++j) { sum = __fadd_rn(sum, sc[j]); }
+        bcast = __fdiv_rn(1.0f, sum);
+    }
+    __syncthreads();
+    const float inv = bcast;
+    // probabilities, rounded to fp16 as the PV MatMul does with its f32 operand
+    for (int j = tid; j < n_vis; j += ATT_SM_THREADS) { row[j] = __half2float(__float2half_rn(__fmul_rn(sc[j], inv))); }
+}
+
+constexpr int ATT_PV_WARPS = 16;
+__global__ void __launch_bounds__(ATT_PV_WARPS * WARP) attn_pv_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) float att_smem[];
+    const int per_head = ATT_HD / ATT_PV_WARPS;
+    const int h = blockIdx.x / per_head, e = (blockIdx.x % per_head) * ATT_PV_WARPS + (threadIdx.x >> 5), t = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n_vis = p.pos_base[0] + t + 1;
+    const int n_tot = (p.pos_base[1] > 0) ? p.pos_base[1] : p.pos_base[0] + p.T;
+    const int n_pad = (p.n_ctx + 3) & ~3;
+    const int n_main = ((n_tot - 1) / 32) * 32;
+    float *pr = att_smem;
+    const float *row = p.scratch + ((int64_t)t * p.n_head + h) * n_pad;
+    for (int j = tid; j < n_vis; j += ATT_PV_WARPS * WARP) { pr[j] = row[j]; }
+    __syncthreads();
+    // out[e] = Dot<FP16,FP16>(V_t[e][0..n_tot), probs); masked positions have probability +0 and leave every accumulator
+    // unchanged, so they are skipped (their cache entries may not be written yet)
+    const __half *vrow = p.v_cache + ((int64_t)h * ATT_HD + e) * p.n_ctx;
+    float acc = 0.f;
+    int j0 = 0;
+    for (; j0 + 8 * 32 <= n_main && j0 + 8 * 32 <= n_vis; j0 += 8 * 32) {   // eight steps' loads in flight
+        float v[8];
+#pragma unroll
+        for (int s = 0; s < 8; ++s) { v[s] = __half2float(vrow[j0 + 32 * s + lane]); }
+#pragma unroll
+        for (int s = 0; s < 8; ++s) { acc = fmaf(v[s], pr[j0 + 32 * s + lane], acc); }
+    }
+    for (; j0 < n_main; j0 += 32) {
+        const int j = j0 + lane;
+        if (j < n_vis) { acc = fmaf(__half2float(vrow[j]), pr[j], acc); }
+    }
+    acc = reduce_f16dot_lanes(acc);
+    const float vt = (n_main + lane < n_vis) ? __half2float(vrow[n_main + lane]) : 0.f;
+    float tail = 0.f;                         // positions n_main .. n_tot-1 (at most 32): scalar chain
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+        const float v = __shfl_sync(0xffffffffu, vt, i);
+        if (n_main + i < n_vis) { tail = fmaf(v, pr[n_main + i], tail); }
+    }
+    if (lane == 0) { p.out[(int64_t)t * (p.out_stride ? p.out_stride : p.dl) + (int64_t)h * ATT_HD + e] = __fadd_rn(tail, acc); }
+    tp_publish(p.tp, p.T);
+}
+
+static cudaError_t launch_with_pdl(const void *kernel, dim3 grid, dim3 block, size_t smem, const AttnParams &p, const LaunchCfg &cfg) {
     cudaLaunchConfig_t lc = {};
-    lc.gridDim = dim3(p.n_head, p.T, 1); lc.blockDim = dim3(ATT_THREADS); lc.dynamicSmemBytes = smem; lc.stream = cfg.stream;
+    lc.gridDim = grid; lc.blockDim = block; lc.dynamicSmemBytes = smem; lc.stream = cfg.stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&lc, attention_kernel, p);
+    void *args[] = {const_cast<AttnParams *>(&p)};
+    return cudaLaunchKernelExC(&lc, kernel, args);
+}
+
+size_t attention_scratch_floats(int n_ctx, int n_head, int T) {   // 0: the single-kernel path serves this context length
+    if (n_ctx <= ATT_LONG_MIN) { return 0; }
+    return (size_t)T * n_head * (((size_t)n_ctx + 3) & ~(size_t)3);
+}
+
+cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
+    if (p.hd != ATT_HD || p.T < 1 || p.n_ctx < 1 || (p.n_ctx & 3) || (p.dl & 7)) { return cudaErrorInvalidValue; }
+    const size_t n_pad = ((size_t)p.n_ctx + 3) & ~(size_t)3;
+    if (p.n_ctx > ATT_LONG_MIN && p.scratch != nullptr) {
+        cudaError_t err = launch_with_pdl(reinterpret_cast<const void *>(attn_scores_kernel), dim3((unsigned)((p.n_ctx + 255) / 256), p.n_head, p.T), dim3(256), 0, p, cfg);
+        if (err != cudaSuccess) { return err; }
+        const size_t sm_smem = (n_pad + n_pad / 4) * sizeof(float) + 16;
+        if (sm_smem > 200 * 1024) { return cudaErrorInvalidValue; }
+        err = allow_dynamic_smem(reinterpret_cast<const void *>(attn_softmax_kernel), sm_smem);
+        if (err != cudaSuccess) { return err; }
+        err = launch_with_pdl(reinterpret_cast<const void *>(attn_softmax_kernel), dim3(p.n_head, p.T), dim3(ATT_SM_THREADS), sm_smem, p, cfg);
+        if (err != cudaSuccess) { return err; }
+        const size_t pv_smem = n_pad * sizeof(float) + 16;
+        err = allow_dynamic_smem(reinterpret_cast<const void *>(attn_pv_kernel), pv_smem);
+        if (err != cudaSuccess) { return err; }
+        return launch_with_pdl(reinterpret_cast<const void *>(attn_pv_kernel), dim3(p.n_head * (ATT_HD / ATT_PV_WARPS), p.T), dim3(ATT_PV_WARPS * WARP), pv_smem, p, cfg);
+    }
+    const size_t smem = (n_pad + n_pad / 4 + ATT_HD) * sizeof(float) + 16;
+    if (smem > 200 * 1024) { return cudaErrorInvalidValue; }
+    cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(attention_kernel), smem);
+    if (err != cudaSuccess) { return err; }
+    return launch_with_pdl(reinterpret_cast<const void *>(attention_kernel), dim3(p.n_head, p.T, 1), dim3(ATT_THREADS), smem, p, cfg);
 }
 
 // =============================================================================================

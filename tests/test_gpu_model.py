@@ -216,6 +216,25 @@ def test_step_kernel_wait_runs_out_and_is_reported(oracle, tmp_models, monkeypat
     m.close(); b.close()
 
 
+@pytest.mark.parametrize("env", [{}, {"SPYB_STEP": "1"}])
+def test_long_context_attention_path_in_the_model(env, oracle, tmp_models, monkeypatch):
+    """A context above 1024 positions switches attention to the three-kernel path (scores / softmax / PV spread over the
+    chip); prompt passes of several tokens and single-token steps through it must give the CPU's bits."""
+    cfg = gguf_io.LlamaConfig(n_layer=2, d_model=256, n_head=2, n_ff=512, n_vocab=512, weight_std=0.05)
+    path = str(tmp_models / "longctx.gguf")
+    if not os.path.exists(path):
+        gguf_io.make_llama_gguf(path, cfg, seed=47)
+    prompt = np.random.default_rng(12).integers(3, cfg.n_vocab, size=70)
+    want_ids, want_logits = oracle.OracleLlama(path, n_ctx=2048).generate(prompt, 6)
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    b = B.B200Backend(0)
+    m = B.LlamaModel(b, path, n_ctx=2048)
+    ids, logits = m.generate(prompt, 6)
+    assert np.array_equal(ids, want_ids) and logits_ok(logits, want_logits)
+    m.close(); b.close()
+
+
 def test_rmsnorm_running_sum_on_hard_inputs(oracle, tmp_models):
     """The RMSNorm sum of squares is a serial f32 running sum on the CPU (groups of four squares added to one
     accumulator in order); the GPU forms the groups in parallel and runs the same chain on one thread. Inputs that

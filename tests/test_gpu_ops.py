@@ -352,10 +352,12 @@ def test_fused_attention_bits(be, oracle, pos0, t, n_total, spread):
     assert np.array_equal(bits(got), bits(want))
 
 
-@pytest.mark.parametrize("pos0,t,n_total,n_ctx", [(255, 1, 0, 512), (256, 2, 0, 512), (300, 1, 0, 512), (511, 1, 0, 512), (700, 2, 703, 1024), (1023, 1, 0, 1024)])
+@pytest.mark.parametrize("pos0,t,n_total,n_ctx", [(255, 1, 0, 512), (256, 2, 0, 512), (300, 1, 0, 512), (511, 1, 0, 512), (700, 2, 703, 1024), (1023, 1, 0, 1024),
+                                                  (0, 1, 0, 2048), (5, 3, 0, 2048), (1500, 2, 0, 2048), (3000, 3, 3010, 4096), (4094, 2, 0, 4096), (4095, 1, 0, 4096)])
 def test_fused_attention_long_rows(be, oracle, pos0, t, n_total, n_ctx):
     """Rows longer than the CTA (more than 256 positions: several positions per thread, many 32-position PV steps) up to
-    a full context, against the oracle."""
+    a full context, against the oracle. Contexts above 1024 positions take the three-kernel path (scores, softmax and PV
+    spread over the chip), at short and at full rows."""
     rng = np.random.default_rng(pos0 + n_ctx)
     n_head, hd = 1, 128
     d = n_head * hd
