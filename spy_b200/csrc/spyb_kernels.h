@@ -58,6 +58,15 @@ struct TpLink {
     const int      *epoch = nullptr;          // device word: the step's exchange epoch
 };
 
+// K-quant weights stay in their GGUF row layout (Q4_K) or a 16-byte-aligned re-layout of it (Q6_K, see spyb_kquant.cu):
+// up to three row ranges form one virtual matrix (Wq | Wk | Wv), or, in pair mode, two matrices whose rows i meet (up, gate)
+struct KqSeg {
+    const uint8_t *w = nullptr;
+    int     type = 0;          // 12 = Q4_K, 14 = Q6_K
+    int64_t n_rows = 0;
+    int64_t row_bytes = 0;
+};
+
 struct MatvecParams {
     DevMatrix A;
     DevMatrix B;               // second matrix when pair_mode == 1 (same shape as A)
@@ -91,6 +100,8 @@ struct MatvecParams {
     // latest CTA: entry, predecessor finished, prologue done; unused)
     unsigned long long *stamps = nullptr;
     TpLink tp;                          // tensor-parallel all-gather fused into the kernel (producer and / or consumer side)
+    KqSeg  kq[3];                       // K-quant weights: kq_n > 0 selects the K-quant kernel (A then only carries k, nb and n_rows)
+    int    kq_n = 0;
 };
 
 struct AttnParams {
@@ -137,6 +148,9 @@ int         smem_ledger_selftest();   // host-only check of SmemLedger, 0 = pass
 size_t      matvec_smem_bytes(int nb, int T);
 int         matvec_max_columns(int nb);   // most activation columns one launch can hold in shared memory for rows of nb blocks
 cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg);
+cudaError_t launch_matvec_kq(const MatvecParams &p, const LaunchCfg &cfg);   // (launch_matvec forwards to it when p.kq_n > 0)
+int64_t     kq_row_bytes(int type, int64_t k);                             // bytes of one K-quant row in device memory
+cudaError_t launch_kq_relayout_q6k(const uint8_t *raw, int64_t n_rows, int64_t k, uint8_t *dst, cudaStream_t s);
 cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg);
 size_t      attention_scratch_floats(int n_ctx, int n_head, int T);
 

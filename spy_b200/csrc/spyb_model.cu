@@ -140,6 +140,7 @@ static NcclApi g_nccl;
 struct Layer {
     DevMatrix upgate;   // FFN up and gate interleaved in 32-row tiles (when the shard's FFN width is a multiple of 16); else up / gate below
     DevMatrix wqkv, wo, up, gate, down;
+    KqSeg     kq_q, kq_k, kq_v, kq_o, kq_up, kq_gate, kq_down;   // K-quant models (Q4_K / Q6_K): the matrices as row ranges in GGUF order
     float    *attn_norm = nullptr, *ffn_norm = nullptr;
     __half   *k_cache = nullptr, *v_cache = nullptr;   // K [n_ctx][dl], V transposed [dl][n_ctx]
 };
@@ -154,6 +155,8 @@ struct spyb_model {
     int             dl = 0, fl = 0;          // local (per-rank) attention width and FFN width
     std::vector<Layer> layers;
     DevMatrix       head;
+    KqSeg           kq_head;
+    bool            kq = false;              // every matrix is a K-quant: the step plan runs on the K-quant mat-vec kernel
     float          *output_norm = nullptr;
     uint8_t        *embd = nullptr;
     int             embd_type = 0;
@@ -320,6 +323,39 @@ spyb_status run_step(spyb_model *m, bool tap, int64_t *launches) {
     return SPYB_SUCCESS;
 }
 
+// the weights of one mat-vec of the step plan: kind 0 = Wq|Wk|Wv, 1 = Wo, 2 = up|gate, 3 = down, 4 = output head
+void set_weights(const spyb_model *m, const Layer *ly, int kind, MatvecParams &p) {
+    const int d = m->info.d_model;
+    if (m->kq) {
+        DevMatrix A;   // only the shape is used
+        A.type = SPYB_Q4_K; A.k = (kind == 3) ? m->info.n_ff : d; A.nb = (int)(A.k / 32); A.nbp = A.nb;
+        switch (kind) {
+        case 0: p.kq[0] = ly->kq_q; p.kq[1] = ly->kq_k; p.kq[2] = ly->kq_v; p.kq_n = 3; A.n_rows = 3 * (int64_t)m->dl; break;
+        case 1: p.kq[0] = ly->kq_o; p.kq_n = 1; A.n_rows = d; break;
+        case 2: p.kq[0] = ly->kq_up; p.kq[1] = ly->kq_gate; p.kq_n = 2; p.pair_mode = 1; A.n_rows = m->fl; break;
+        case 3: p.kq[0] = ly->kq_down; p.kq_n = 1; A.n_rows = d; break;
+        default: p.kq[0] = m->kq_head; p.kq_n = 1; A.n_rows = m->info.n_vocab; break;
+        }
+        p.A = A;
+        return;
+    }
+    switch (kind) {
+    case 0: p.A = ly->wqkv; break;
+    case 1: p.A = ly->wo; break;
+    case 2: if (ly->upgate.w) { p.A = ly->upgate; } else { p.A = ly->up; p.B = ly->gate; p.pair_mode = 1; } break;
+    case 3: p.A = ly->down; break;
+    default: p.A = m->head; break;
+    }
+}
+uint64_t weights_bytes(const MatvecParams &p) {
+    if (p.kq_n > 0) {
+        uint64_t b = 0;
+        for (int i = 0; i < p.kq_n; ++i) { b += (uint64_t)p.kq[i].n_rows * (p.A.k / 256) * (p.kq[i].type == SPYB_Q4_K ? 144 : 210); }
+        return b;
+    }
+    return p.A.bytes() + (p.pair_mode ? p.B.bytes() : 0);
+}
+
 // the five fused kernels of every layer for T tokens whose first position is *d_pos.
 // Tensor parallel: Wq|Wk|Wv, attention and FFN up|gate work on this rank's heads / FFN columns; their outputs are
 // all-gathered (inside the kernels over peer memory, or by NCCL) and Wo / FFN down run replicated on the complete
@@ -335,7 +371,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
         auto stamps = [&](int k) { return m->d_stamps ? m->d_stamps + 8 * (5 * L + k) : nullptr; };
         {   // 1: norm + quantize -> QKV -> rope + KV append
             MatvecParams p;
-            p.A = ly.wqkv; p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.attn_norm; p.eps = m->info.rms_eps;
+            set_weights(m, &ly, 0, p); p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.attn_norm; p.eps = m->info.rms_eps;
             p.epi = EPI_QKV_ROPE; p.pos_base = m->d_pos; p.rope_table = m->rope_table; p.hd = m->info.head_dim; p.dl = m->dl;
             p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache; p.n_ctx = m->info.n_ctx;
             p.tap_xq = (tap && L == 0) ? m->d_tap : nullptr;
@@ -355,14 +391,14 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
         }
         {   // 3: quantize -> Wo -> + residual (replicated)
             MatvecParams p;
-            p.A = ly.wo; p.T = T; p.pro = PRO_QUANT; p.x = m->att; p.x_stride = d;
+            set_weights(m, &ly, 1, p); p.T = T; p.pro = PRO_QUANT; p.x = m->att; p.x_stride = d;
             p.epi = EPI_RESID; p.resid = m->x; p.out = m->x; p.out_stride = d; p.stamps = stamps(2);
             if (fused) { tp_consume(m, p.tp, 2 * L); }
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
         }
         {   // 4: norm + quantize -> up, gate (this rank's FFN columns) -> up * silu(gate) into its share of the gathered activation
             MatvecParams p;
-            if (ly.upgate.w) { p.A = ly.upgate; } else { p.A = ly.up; p.B = ly.gate; p.pair_mode = 1; }
+            set_weights(m, &ly, 2, p);
             p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
             p.eps = m->info.rms_eps; p.epi = EPI_SILU_MUL; p.out = m->act + (int64_t)rank * m->fl; p.out_stride = ff; p.silu_table = be->d_silu_table;
             p.stamps = stamps(3);
@@ -372,7 +408,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
         }
         {   // 5: quantize -> Wdown -> + residual (replicated)
             MatvecParams p;
-            p.A = ly.down; p.T = T; p.pro = PRO_QUANT; p.x = m->act; p.x_stride = ff;
+            set_weights(m, &ly, 3, p); p.T = T; p.pro = PRO_QUANT; p.x = m->act; p.x_stride = ff;
             p.epi = EPI_RESID; p.resid = m->x; p.out = m->x; p.out_stride = d; p.stamps = stamps(4);
             if (fused) { tp_consume(m, p.tp, 2 * L + 1); }
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
@@ -384,7 +420,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
 // output norm + head on column `col` of x -> logits[n_vocab]
 spyb_status run_head(spyb_model *m, int col, int64_t *launches) {
     MatvecParams p;
-    p.A = m->head; p.T = 1; p.pro = PRO_NORM_QUANT; p.x = m->x + (int64_t)col * m->info.d_model; p.x_stride = m->info.d_model;
+    set_weights(m, nullptr, 4, p); p.T = 1; p.pro = PRO_NORM_QUANT; p.x = m->x + (int64_t)col * m->info.d_model; p.x_stride = m->info.d_model;
     p.norm_w = m->output_norm; p.eps = m->info.rms_eps; p.epi = EPI_STORE; p.out = m->logits; p.out_stride = m->info.n_vocab;
     p.stamps = m->d_stamps ? m->d_stamps + 8 * (5 * m->layers.size()) : nullptr;
     SPYB_CUDA(m->be, launch_matvec(p, m->be->launch_cfg(m->be->config.use_pdl != 0))); ++*launches;
@@ -472,6 +508,38 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         return upload_matrix(be, t->type, data + row0 * rb, n_rows, rb, blk0, nb, dst);
     };
 
+    // K-quant matrix: rows [row0, row0 + n_rows) of a [k_full, rows_full] Q4_K / Q6_K tensor, kept in GGUF row order
+    auto upload_kq = [&](const std::string &name, int64_t k_full, int64_t rows_full, int64_t row0, int64_t n_rows, KqSeg *dst) {
+        const GgufTensor *t; const uint8_t *data;
+        if (!tensor(name, &t, &data)) { return SPYB_FAIL; }
+        if (t->ne[0] != k_full || t->ne[1] != rows_full) { be->set_error("GGUF: %s has shape [%lld, %lld]", name.c_str(), (long long)t->ne[0], (long long)t->ne[1]); return SPYB_FAIL; }
+        if (t->type != SPYB_Q4_K && t->type != SPYB_Q6_K) { be->set_error("GGUF: %s: type %d in a K-quant model (every matrix must be Q4_K or Q6_K)", name.c_str(), t->type); return SPYB_UNSUPPORTED; }
+        if (k_full % 256 != 0 || (n_rows & 1)) { be->set_error("GGUF: %s: K-quant rows need K a multiple of 256 and an even row count", name.c_str()); return SPYB_UNSUPPORTED; }
+        const int64_t rb_file = GgufFile::row_bytes(t->type, k_full), rb_dev = kq_row_bytes(t->type, k_full);
+        uint8_t *dev = nullptr;
+        if (dev_alloc(m, &dev, (size_t)n_rows * rb_dev) != SPYB_SUCCESS) { return SPYB_FAIL; }
+        if (t->type == SPYB_Q4_K) {
+            SPYB_CUDA(be, cudaMemcpy(dev, data + row0 * rb_file, (size_t)n_rows * rb_file, cudaMemcpyHostToDevice));
+        } else {   // Q6_K: 210-byte super-blocks -> 16-byte-aligned pieces
+            void *stage = nullptr;
+            SPYB_CUDA(be, cudaMalloc(&stage, (size_t)n_rows * rb_file + 64));
+            // (on the backend's stream, like the kernel that reads it: a plain cudaMemcpy from pageable memory is not
+            // ordered with a non-blocking stream)
+            cudaError_t err = cudaMemcpyAsync(stage, data + row0 * rb_file, (size_t)n_rows * rb_file, cudaMemcpyHostToDevice, be->stream);
+            if (err == cudaSuccess) { err = launch_kq_relayout_q6k(static_cast<const uint8_t *>(stage), n_rows, k_full, dev, be->stream); }
+            if (err == cudaSuccess) { err = cudaStreamSynchronize(be->stream); }
+            cudaFree(stage);
+            if (err != cudaSuccess) { be->set_error("GGUF: %s: upload failed: %s", name.c_str(), cudaGetErrorString(err)); return SPYB_FAIL; }
+        }
+        dst->w = dev; dst->type = t->type; dst->n_rows = n_rows; dst->row_bytes = rb_dev;
+        I.weight_bytes += (uint64_t)n_rows * rb_file;
+        return SPYB_SUCCESS;
+    };
+    {   // a model whose attention query weights are K-quants runs on the K-quant kernel throughout
+        auto it = f.tensors.find("blk.0.attn_q.weight");
+        m->kq = it != f.tensors.end() && (it->second.type == SPYB_Q4_K || it->second.type == SPYB_Q6_K);
+    }
+
     // embeddings stay in their raw layout (gathered one row at a time); the reference gathers F32 / Q8_0 rows only
     {
         const GgufTensor *t; const uint8_t *data;
@@ -505,7 +573,9 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         if (use_mma) { return per_sm >= 8 * 16 ? 16 : 8; }
         return per_sm >= 8 * 32 ? 32 : per_sm >= 8 * 16 ? 16 : 8;
     };
-    {
+    if (m->kq) {
+        if ((st = upload_kq("output.weight", d, I.n_vocab, 0, I.n_vocab, &m->kq_head)) != SPYB_SUCCESS) { return fail(st); }
+    } else {
         const std::string head_name = f.tensors.count("output.weight") ? "output.weight" : "token_embd.weight";
         auto ith = f.tensors.find(head_name);
         const int head_tile = (I.n_vocab >= 8192 || (use_mma && I.n_vocab % 8 == 0)) ? tile_for("SPYB_TILE_HEAD", I.n_vocab, auto_tile(I.n_vocab)) : 4;
@@ -524,6 +594,14 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         const std::string p = "blk." + std::to_string(L) + ".";
         if ((st = upload_f32(p + "attn_norm.weight", d, &ly.attn_norm)) != SPYB_SUCCESS) { return fail(st); }
         if ((st = upload_f32(p + "ffn_norm.weight", d, &ly.ffn_norm)) != SPYB_SUCCESS) { return fail(st); }
+        if (m->kq) {   // K-quants: heads / FFN columns of this rank as row ranges; Wo and W_down whole
+            if ((st = upload_kq(p + "attn_q.weight", d, d, (int64_t)r * dl, dl, &ly.kq_q)) != SPYB_SUCCESS || (st = upload_kq(p + "attn_k.weight", d, d, (int64_t)r * dl, dl, &ly.kq_k)) != SPYB_SUCCESS ||
+                (st = upload_kq(p + "attn_v.weight", d, d, (int64_t)r * dl, dl, &ly.kq_v)) != SPYB_SUCCESS || (st = upload_kq(p + "attn_output.weight", d, d, 0, d, &ly.kq_o)) != SPYB_SUCCESS ||
+                (st = upload_kq(p + "ffn_up.weight", d, I.n_ff, (int64_t)r * fl, fl, &ly.kq_up)) != SPYB_SUCCESS || (st = upload_kq(p + "ffn_gate.weight", d, I.n_ff, (int64_t)r * fl, fl, &ly.kq_gate)) != SPYB_SUCCESS ||
+                (st = upload_kq(p + "ffn_down.weight", I.n_ff, d, 0, d, &ly.kq_down)) != SPYB_SUCCESS) { return fail(st); }
+            if (dev_alloc(m, &ly.k_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS || dev_alloc(m, &ly.v_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
+            continue;
+        }
         // heads: rows [r*dl, (r+1)*dl) of Wq, Wk, Wv, stacked into one [3*dl, d] matrix
         auto itq = f.tensors.find(p + "attn_q.weight");
         if (itq == f.tensors.end()) { be->set_error("GGUF: %sattn_q.weight is missing", p.c_str()); return fail(SPYB_FAIL); }
@@ -730,7 +808,7 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
         return SPYB_SUCCESS;
     }
     SPYB_CUDA(be, cudaEventRecord(m->ev0, be->stream));
-    const int tmax = std::min(8, std::min(matvec_max_columns(m->info.d_model / 32), matvec_max_columns(m->info.n_ff / 32)));
+    const int tmax = m->kq ? 1 : std::min(8, std::min(matvec_max_columns(m->info.d_model / 32), matvec_max_columns(m->info.n_ff / 32)));   // (the K-quant kernel takes one column)
     for (int t0 = 0; t0 < n_tokens; t0 += tmax) {
         const int T = std::min(tmax, n_tokens - t0);
         SPYB_CUDA(be, cudaStreamSynchronize(be->stream));   // pinned staging words are reused per pass
@@ -824,22 +902,22 @@ float spyb_model_bench_kernel(spyb_model *m, int32_t kind, int32_t sweeps, uint6
     if (cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 8, cudaMemcpyHostToDevice, be->stream) != cudaSuccess) { return -1.f; }
     auto params = [&](const Layer &ly) {
         MatvecParams p; p.T = 1;
+        set_weights(m, &ly, kind, p);
         switch (kind) {
-        case 0: p.A = ly.wqkv; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.attn_norm; p.eps = m->info.rms_eps;
+        case 0: p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.attn_norm; p.eps = m->info.rms_eps;
                 p.epi = EPI_QKV_ROPE; p.pos_base = m->d_pos; p.rope_table = m->rope_table; p.hd = m->info.head_dim; p.dl = m->dl;
                 p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache; p.n_ctx = m->info.n_ctx; break;
-        case 1: p.A = ly.wo; p.pro = PRO_QUANT; p.x = m->att; p.x_stride = d; p.epi = EPI_STORE; p.out = m->scratch; p.out_stride = d; break;
-        case 2: if (ly.upgate.w) { p.A = ly.upgate; } else { p.A = ly.up; p.B = ly.gate; p.pair_mode = 1; }
-                p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
+        case 1: p.pro = PRO_QUANT; p.x = m->att; p.x_stride = d; p.epi = EPI_STORE; p.out = m->scratch; p.out_stride = d; break;
+        case 2: p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.ffn_norm;
                 p.eps = m->info.rms_eps; p.epi = EPI_SILU_MUL; p.out = m->act + (int64_t)m->info.tp_rank * m->fl; p.out_stride = m->info.n_ff; p.silu_table = be->d_silu_table; break;
-        case 3: p.A = ly.down; p.pro = PRO_QUANT; p.x = m->act; p.x_stride = m->info.n_ff; p.epi = EPI_STORE; p.out = m->scratch; p.out_stride = d; break;
-        default: p.A = m->head; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = m->output_norm; p.eps = m->info.rms_eps;
+        case 3: p.pro = PRO_QUANT; p.x = m->act; p.x_stride = m->info.n_ff; p.epi = EPI_STORE; p.out = m->scratch; p.out_stride = d; break;
+        default: p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = m->output_norm; p.eps = m->info.rms_eps;
                 p.epi = EPI_STORE; p.out = m->logits; p.out_stride = m->info.n_vocab; break;
         }
         return p;
     };
     const MatvecParams p0 = params(m->layers[0]);
-    if (bytes_per_launch) { *bytes_per_launch = p0.A.bytes() + (p0.pair_mode ? p0.B.bytes() : 0); }
+    if (bytes_per_launch) { *bytes_per_launch = weights_bytes(p0); }
     float total_ms = 0.f; int64_t n = 0;
     const bool hot = std::getenv("SPYB_BENCH_L2_HOT") != nullptr;   // every launch on layer 0's matrix: it stays in L2
     if (kind == 4) {

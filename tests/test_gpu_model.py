@@ -150,9 +150,34 @@ def test_long_context_attention(be, oracle, tmp_models):
     m.close()
 
 
+@pytest.mark.parametrize("name,cfg", [
+    ("q4k", dict(wtype=quants.Q4_K)),
+    ("q4k_m", dict(wtype=quants.Q4_K, overrides={"attn_v": quants.Q6_K, "ffn_down": quants.Q6_K, "output": quants.Q6_K})),
+    ("q6k_long_rows", dict(wtype=quants.Q6_K, n_ff=4608, overrides={"ffn_gate": quants.Q4_K, "ffn_down": quants.Q4_K})),   # 18 super-blocks per W_down row
+])
+def test_k_quant_models_match_the_restatement(name, cfg, oracle, tmp_models):
+    """Q4_K / Q6_K weights through the step plan (the Q4_K_M-style mix: Q6_K for attn_v, ffn_down and the output head).
+    The reference has block layouts but no arithmetic for these types, so parity is unpinned: the checker is the CPU
+    restatement (activations quantized to Q8_0, integer sub-block sums, one f32 chain per super-block), whose order the
+    kernel follows - the gate is the stated tolerance and identical ids, and the bits are expected to agree as well."""
+    c = gguf_io.LlamaConfig(**dict(dict(n_layer=2, d_model=256, n_head=2, n_ff=512, n_vocab=512, weight_std=0.05), **cfg))
+    path = str(tmp_models / f"{name}.gguf")
+    gguf_io.make_llama_gguf(path, c, seed=51)
+    prompt = np.random.default_rng(13).integers(3, c.n_vocab, size=7)
+    want_ids, want_logits = oracle.OracleLlama(path, n_ctx=32).generate(prompt, 6)
+    b = B.B200Backend(0)
+    m = B.LlamaModel(b, path, n_ctx=32)
+    ids, logits = m.generate(prompt, 6)
+    assert np.array_equal(ids, want_ids) and logits_ok(logits, want_logits)
+    assert np.array_equal(np.asarray(logits, dtype=np.float32).view(np.uint32), np.asarray(want_logits, dtype=np.float32).view(np.uint32))
+    ids_dev, _ = m.decode(int(ids[0]), len(prompt), 5)          # and the device-side decode loop (graph replay)
+    assert np.array_equal(ids_dev, want_ids[1:])
+    m.close(); b.close()
+
+
 def test_unsupported_models_are_reported(be, tmp_models):
-    path = str(tmp_models / "q4k.gguf")
-    gguf_io.make_llama_gguf(path, gguf_io.LlamaConfig(wtype=quants.Q4_K), seed=1)
+    path = str(tmp_models / "mixed.gguf")      # K-quants beside Q4_0 matrices: no kernel mixes the two activation layouts
+    gguf_io.make_llama_gguf(path, gguf_io.LlamaConfig(wtype=quants.Q4_K, overrides={"attn_q": quants.Q4_0}), seed=1)
     with pytest.raises(B.SpybError) as e:
         B.LlamaModel(be, path, n_ctx=32)
     assert e.value.status == B.UNSUPPORTED
