@@ -48,7 +48,9 @@ bool g_logger_ready = false;
 /// the sm_100a backend behind the reference's own factory hook ("gpu:b200"); a fresh instance per call, so that
 /// the constants of one model file never outlive its mapping
 std::unique_ptr<Backend> g_device_backend;
-Backend *device_backend() {
+/// plan_model: path of the GGUF file for the adapter's plan mode (steps served from the fused step plan), or null for
+/// operator-by-operator submission
+Backend *device_backend(const char *plan_model, int num_context) {
 	std::lock_guard<std::mutex> guard(g_mutex);
 	if (!g_logger_ready) {
 		LogParam log_param;
@@ -58,6 +60,7 @@ Backend *device_backend() {
 	}
 	BackendFactory factory;
 	ConfigTable config;
+	if (plan_model != nullptr) { config.add("model", plan_model); config.add("num_context", std::to_string(num_context)); }
 	g_device_backend.reset();
 	g_device_backend = factory.init_backend("gpu:b200", config);
 	return g_device_backend.get();
@@ -277,7 +280,8 @@ int spy_ref_run_op(int op_type, int num_in, const spy_ref_tensor *in, spy_ref_te
 int spy_ref_generate(const char *gguf_path, const int32_t *prompt, int n_prompt, int n_predict, int num_context,
 		int num_thread, int warmup, int32_t *out_ids, float *out_logits, double *step_ms) {
 #ifdef SPY_BACKEND_CUDA
-	Backend *backend = (num_thread < 0) ? device_backend() : backend_for(num_thread);
+	// num_thread -1: operator by operator; num_thread -2: the adapter's plan mode
+	Backend *backend = (num_thread < 0) ? device_backend(num_thread == -2 ? gguf_path : nullptr, num_context) : backend_for(num_thread);
 #else
 	if (num_thread < 0) { return -2; }
 	Backend *backend = backend_for(num_thread);

@@ -135,9 +135,10 @@ def lib_b200():
 
 
 def generate(gguf_path: str, prompt, n_predict: int, n_ctx: int = 512, threads: int = 8, warmup: bool = False,
-             want_logits: bool = True, n_vocab: int | None = None, device_backend: bool = False):
+             want_logits: bool = True, n_vocab: int | None = None, device_backend: bool = False, plan: bool = False):
     """Returns (ids [n_predict], logits [n_predict, n_vocab] or None, step_ms [n_predict]).
-    device_backend=True runs the reference's token loop on its "gpu:b200" backend (the adapter over libspyb200.so)."""
+    device_backend=True runs the reference's token loop on its "gpu:b200" backend (the adapter over libspyb200.so),
+    operator by operator or, with plan=True, with the steps served from the library's fused step plan."""
     prompt = np.ascontiguousarray(prompt, dtype=np.int32)
     ids = np.zeros(n_predict, dtype=np.int32)
     ms = np.zeros(n_predict, dtype=np.float64)
@@ -147,7 +148,7 @@ def generate(gguf_path: str, prompt, n_predict: int, n_ctx: int = 512, threads: 
             raise ValueError("n_vocab is required to size the logits buffer")
         logits = np.zeros((n_predict, n_vocab), dtype=np.float32)
     l = lib_b200() if device_backend else lib()
-    v = l.spy_ref_generate(gguf_path.encode(), _ptr(prompt), len(prompt), n_predict, n_ctx, -1 if device_backend else threads, int(warmup),
+    v = l.spy_ref_generate(gguf_path.encode(), _ptr(prompt), len(prompt), n_predict, n_ctx, (-2 if plan else -1) if device_backend else threads, int(warmup),
                            _ptr(ids), _ptr(logits) if logits is not None else None, _ptr(ms))
     if v < 0:
         raise RuntimeError("spy_ref_generate failed")

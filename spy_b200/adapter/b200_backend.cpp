@@ -24,9 +24,62 @@ namespace spy::gpu {
 		pod.arena_bytes = config.parse_or<uint64_t>("arena_bytes", 0);
 		const spyb_status status = spyb_create(&pod, &handle_);
 		spy_assert(status == SPYB_SUCCESS && handle_ != nullptr, "Failed to create the B200 backend on device {}: no CPU fallback exists", device_id_);
+		plan_path_    = config.get_or("model", "");
+		plan_context_ = config.parse_or("num_context", 512);
+		plan_enabled_ = !plan_path_.empty() && config.parse_or("plan", 1) != 0;
 	}
 
-	B200Backend::~B200Backend() noexcept { spyb_destroy(handle_); }
+	B200Backend::~B200Backend() noexcept {
+		if (plan_model_ != nullptr) { spyb_model_free(plan_model_); }
+		spyb_destroy(handle_);
+	}
+
+	/*!
+	 * @brief Plan mode: serve the node from the fused step plan. Returns false when the node has to take the
+	 * operator-by-operator path (plan mode off, or the model is one the step plan does not cover).
+	 * @note The step's graph is the one LLAMAModel::build_graph emits (model/src/llm/model/llama.cpp:123-222): the token
+	 * ids enter through GetRow on the embedding table (plugin/inout.cpp:5-30), the position through the Rope parameters
+	 * (plugin/attention.cpp:64-97), and the only node whose output lives in host memory is the logits MatMul
+	 * (plugin/inout.cpp:61-75). Its output tensor holds one column of logits per token of the step; like the reference's
+	 * generate loop (app/cli/include/cli.h:103-105) only the last column is filled.
+	 */
+	bool B200Backend::submit_planned(OperatorNode *op_node_ptr) {
+		if (!plan_enabled_) { return false; }
+		if (!plan_tried_) {
+			plan_tried_ = true;
+			if (spyb_model_load_gguf(handle_, plan_path_.c_str(), plan_context_, &plan_model_) != SPYB_SUCCESS) { plan_model_ = nullptr; }
+		}
+		if (plan_model_ == nullptr) { return false; }
+
+		DataNode *output_node = (op_node_ptr->num_output() > 0) ? op_node_ptr->output_data(0) : nullptr;
+		const OperatorType op_type = op_node_ptr->op_type;
+		if (op_type == OperatorType::GetRow && op_node_ptr->num_input() >= 2 && op_node_ptr->input_data(1)->node_prop.node_type == DataNodeType::IO) {
+			const Tensor &ids = op_node_ptr->input_data(1)->tensor;
+			plan_ids_       = static_cast<const int32_t *>(ids.get());
+			plan_num_token_ = static_cast<int>(ids.get_shape().total_element());
+			plan_num_past_  = -1;
+		} else if (op_type == OperatorType::Rope && plan_num_past_ < 0) {
+			plan_num_past_ = static_cast<OperatorDefinition<OperatorType::Rope> *>(op_node_ptr)->params.get_val().num_past;
+		} else if (output_node != nullptr && is_view(op_type)) {
+			// the scheduler leaves the output pointer of view-type operators to the backend (backend/host/operator/view.cpp:224-276)
+			if (op_type == OperatorType::Copy) { output_node->tensor.set_data_ptr(op_node_ptr->input_data(1)->tensor.get()); }
+			else {
+				uint8_t *base = static_cast<uint8_t *>(op_node_ptr->input_data(0)->tensor.get());
+				const int64_t offset = (op_type == OperatorType::View) ? static_cast<OperatorDefinition<OperatorType::View> *>(op_node_ptr)->params.get_val().offset : 0;
+				output_node->tensor.set_data_ptr(base + offset);
+			}
+		}
+		if (output_node != nullptr && output_node->node_prop.node_type == DataNodeType::IO) {   // the logits: run the step
+			spy_assert(plan_ids_ != nullptr && plan_num_token_ > 0 && plan_num_past_ >= 0, "B200 backend: the step plan saw no token ids / position before the logits node");
+			spyb_model_info info{};
+			spyb_model_info_get(plan_model_, &info);
+			float *logits = static_cast<float *>(output_node->tensor.get()) + static_cast<size_t>(plan_num_token_ - 1) * info.n_vocab;
+			const spyb_status status = spyb_model_eval(plan_model_, plan_ids_, plan_num_token_, plan_num_past_, logits);
+			spy_assert(status == SPYB_SUCCESS, "B200 backend (step plan): {}", spyb_last_error(handle_));
+			plan_ids_ = nullptr; plan_num_token_ = 0; plan_num_past_ = -1;
+		}
+		return true;
+	}
 
 	void *B200Backend::alloc_memory(size_t size) {
 		void *ptr = spyb_alloc(handle_, size);
@@ -43,6 +96,10 @@ namespace spy::gpu {
 	 * host memory (IO nodes such as the logits) are waited for first.
 	 */
 	void B200Backend::submit(OperatorNode *op_node_ptr, std::function<void()> &&callback) {
+		if (submit_planned(op_node_ptr)) {
+			if (callback) { callback(); }
+			return;
+		}
 		spyb_op_desc desc{};
 		desc.op_type   = static_cast<int32_t>(op_node_ptr->op_type);
 		desc.num_input = static_cast<int32_t>(std::min<size_t>(op_node_ptr->num_input(), 3));

@@ -26,6 +26,18 @@ namespace spy::gpu {
 		spyb_backend *handle_ = nullptr;
 		int           device_id_ = 0;
 
+		// Plan mode (configuration key "model" = path of the GGUF file the graph was built from): the steps of the LLaMa
+		// graph are served from the library's fused step plan instead of operator by operator. The scheduler still walks
+		// its graph and submits every node; the adapter only notes the step's inputs (token ids from the embedding
+		// GetRow, the position from the first Rope), keeps the pointer aliasing of view-type operators alive, and runs
+		// the whole step when the node that produces the logits arrives.
+		std::string     plan_path_;
+		int             plan_context_ = 512;
+		bool            plan_enabled_ = false, plan_tried_ = false;
+		spyb_model     *plan_model_ = nullptr;
+		const int32_t  *plan_ids_ = nullptr;
+		int             plan_num_token_ = 0, plan_num_past_ = -1;
+
 	public:
 		explicit B200Backend(const BackendFactory::BackendConfiguration &config);
 
@@ -47,6 +59,10 @@ namespace spy::gpu {
 
 	public:
 		spyb_backend *handle() const { return handle_; }
+		bool plan_active() const { return plan_model_ != nullptr; }
+
+	private:
+		bool submit_planned(OperatorNode *op_node_ptr);
 	};
 
 	void init_backend(BackendFactory &factory);

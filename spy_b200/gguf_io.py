@@ -227,7 +227,7 @@ def make_llama_gguf(path: str, cfg: LlamaConfig, seed: int = 1234, embeddings: n
 
 
 def make_llama_gguf_cuda(path: str, cfg: LlamaConfig, seed: int = 1234, device: str = "cuda:0") -> None:
-    """Same model family generated with torch on a GPU (Q4_0 / Q8_0 / F32 / F16 only), for
+    """Same model family generated with torch on a GPU (Q4_0 / Q8_0 / Q4_K / Q6_K / F32 / F16), for
     full-size models where host generation would take minutes. The file is the ground truth
     shared by the GPU arm and the CPU baseline; it is not bit-identical to make_llama_gguf."""
     import torch
@@ -256,7 +256,54 @@ def make_llama_gguf_cuda(path: str, cfg: LlamaConfig, seed: int = 1234, device: 
         out[:, 2:] = q.view(torch.uint8)
         return out
 
-    enc = {quants.Q4_0: q4_0, quants.Q8_0: q8_0,
+    def pack_scale_min(sc, mn):
+        out = torch.zeros((sc.shape[0], 12), dtype=torch.uint8, device=sc.device)
+        out[:, 0:4] = (sc[:, :4] & 63) | ((sc[:, 4:] >> 4) << 6)
+        out[:, 4:8] = (mn[:, :4] & 63) | ((mn[:, 4:] >> 4) << 6)
+        out[:, 8:12] = (sc[:, 4:] & 0xF) | ((mn[:, 4:] & 0xF) << 4)
+        return out
+
+    def q4_k(w):   # the plain min/max encoder of quants.quantize_q4_k
+        b = w.reshape(-1, 8, 32)
+        lo = torch.clamp(b.amin(dim=2), max=0.0)
+        hi = torch.clamp(b.amax(dim=2), min=0.0)
+        scale, minv = (hi - lo) / 15.0, -lo
+        d = (scale.amax(dim=1) / 63.0).to(torch.float16)
+        dmin = (minv.amax(dim=1) / 63.0).to(torch.float16)
+        d32, dmin32 = d.float()[:, None], dmin.float()[:, None]
+        sc = torch.where(d32 > 0, torch.round(scale / d32), torch.zeros_like(scale)).clamp(0, 63).to(torch.uint8)
+        mn = torch.where(dmin32 > 0, torch.round(minv / dmin32), torch.zeros_like(minv)).clamp(0, 63).to(torch.uint8)
+        eff, off = (d32 * sc.float())[:, :, None], (dmin32 * mn.float())[:, :, None]
+        q = torch.where(eff > 0, torch.round((b + off) / eff), torch.zeros_like(b)).clamp(0, 15).to(torch.uint8)
+        out = torch.empty((b.shape[0], 144), dtype=torch.uint8, device=w.device)
+        out[:, 0:2] = d.view(torch.uint8).reshape(-1, 2)
+        out[:, 2:4] = dmin.view(torch.uint8).reshape(-1, 2)
+        out[:, 4:16] = pack_scale_min(sc, mn)
+        q = q.reshape(-1, 4, 2, 32)
+        out[:, 16:] = (q[:, :, 0, :] | (q[:, :, 1, :] << 4)).reshape(-1, 128)
+        return out
+
+    def q6_k(w):   # the encoder of quants.quantize_q6_k
+        b = w.reshape(-1, 16, 16)
+        scale = b.abs().amax(dim=2) / 31.0
+        d = (scale.amax(dim=1) / 127.0).to(torch.float16)
+        d32 = d.float()[:, None]
+        sc = torch.where(d32 > 0, torch.round(scale / d32), torch.zeros_like(scale)).clamp(0, 127).to(torch.int8)
+        eff = (d32 * sc.float())[:, :, None]
+        q = torch.where(eff > 0, torch.round(b / eff), torch.zeros_like(b)).clamp(-32, 31).to(torch.int16)
+        u = (q.reshape(-1, 256) + 32).to(torch.uint8).reshape(-1, 2, 4, 32)
+        ql = torch.empty((u.shape[0], 2, 64), dtype=torch.uint8, device=w.device)
+        ql[:, :, :32] = (u[:, :, 0, :] & 0xF) | ((u[:, :, 2, :] & 0xF) << 4)
+        ql[:, :, 32:] = (u[:, :, 1, :] & 0xF) | ((u[:, :, 3, :] & 0xF) << 4)
+        qh = (u[:, :, 0, :] >> 4) | ((u[:, :, 1, :] >> 4) << 2) | ((u[:, :, 2, :] >> 4) << 4) | ((u[:, :, 3, :] >> 4) << 6)
+        out = torch.empty((u.shape[0], 210), dtype=torch.uint8, device=w.device)
+        out[:, 0:128] = ql.reshape(-1, 128)
+        out[:, 128:192] = qh.reshape(-1, 64)
+        out[:, 192:208] = sc.view(torch.uint8)
+        out[:, 208:210] = d.view(torch.uint8).reshape(-1, 2)
+        return out
+
+    enc = {quants.Q4_0: q4_0, quants.Q8_0: q8_0, quants.Q4_K: q4_k, quants.Q6_K: q6_k,
            quants.FP32: lambda w: w.contiguous().view(torch.uint8),
            quants.FP16: lambda w: w.to(torch.float16).contiguous().view(torch.uint8)}
     tensors = []

@@ -256,6 +256,21 @@ def test_getrow_f32_and_q8_0(be, oracle):
     assert np.array_equal(bits(got), bits(quants.dequantize(tq, quants.Q8_0)[ids]))
 
 
+def test_getrow_q4_0_and_f16_tables(be):
+    """Embedding tables the CPU backend cannot gather (it aborts on Q4_0 rows, backend/host/operator/view.cpp:65-77):
+    rows decode to value = (nibble - 8) * d in the element order of the dot product (low nibbles = elements 0..15), F16
+    rows widen exactly. A model with such a table runs end to end as well."""
+    rng = np.random.default_rng(17)
+    table = (rng.standard_normal((40, 256)) * 0.1).astype(np.float32)
+    ids = np.array([39, 0, 7, 7, 12], dtype=np.int32)
+    tq = quants.quantize(table, quants.Q4_0)
+    got = run(be, "GetRow", [(tq, B.Q4_0, (256, 40), None, B.NODE_CONSTANT), (ids, B.INT32, (5,), None, B.NODE_IO)], (256, 5)).reshape(5, 256)
+    assert np.array_equal(bits(got), bits(quants.dequantize(tq, quants.Q4_0).reshape(40, 256)[ids]))
+    th = table.astype(np.float16)
+    got = run(be, "GetRow", [(th.view(np.uint16), B.FP16, (256, 40), None, B.NODE_CONSTANT), (ids, B.INT32, (5,), None, B.NODE_IO)], (256, 5)).reshape(5, 256)
+    assert np.array_equal(bits(got), bits(th.astype(np.float32)[ids]))
+
+
 def test_copy_into_strided_f16_cache_and_view(be, oracle):
     """KV append as the graph does it: View at a byte offset, Copy f32 -> f16 into a transposed destination."""
     rng = np.random.default_rng(8)
