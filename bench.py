@@ -296,13 +296,14 @@ def main():
     pre_ids = np.random.default_rng(PROMPT_SEED + 1).integers(3, info.n_vocab, size=n_pre).astype(np.int32)
     model.eval(pre_ids[:8], 0)                                # warm
     barrier(); be.sync()
-    model.eval(pre_ids, 0)
+    pre_logits = model.eval(pre_ids, 0).copy()
     t_pre = torch.tensor([model.last_ms], dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t_pre, op=dist.ReduceOp.MAX)
     prefill = {"tokens": int(n_pre), "ms": float(t_pre[0]), "tokens_per_s": float(n_pre / (float(t_pre[0]) / 1e3)),
                "launches": int(model.last_launches),
-               "note": "one spyb_model_eval over the prompt (device time, CUDA events); passes of up to 4 token columns through the mat-vec kernels, the weights streamed once per pass"}
+               "note": "one spyb_model_eval over the prompt (device time, CUDA events): chunks of up to 512 tokens through the tcgen05 GEMM kernel when the "
+                       "model is unsharded Q4_0 / Q8_0 (otherwise passes of up to 8 token columns through the mat-vec kernels)"}
     barrier()
 
     # ---- device-resident arm ---------------------------------------------------------------
@@ -418,6 +419,14 @@ def main():
                                         "prefill_ms": r["prefill_ms"], "greedy_ids_identical": line["parity"]["ids_identical"]}
                 line["vs_cpu_reference"] = {"value": tok_s / r["tokens_per_s"], "e2e": line["e2e"]["value"] / r["tokens_per_s"],
                                             "note": f"tokens/s over the reference's CPU backend at -t {threads} (physical cores of this box) in the same job"}
+                # the prompt path: the reference CPU backend evaluates the same long prompt once (its logits after the prompt)
+                try:
+                    from oracle import spy_ref
+                    p_ids, p_logits, p_ms = spy_ref.generate(path, pre_ids, 1, n_ctx=N_CTX, threads=threads, warmup=False, want_logits=True, n_vocab=int(info.n_vocab))
+                    line["prefill"]["parity"] = parity_record([int(np.argmax(pre_logits))], pre_logits[None, :], p_ids[:1], np.asarray(p_logits)[:1])
+                    line["prefill"]["cpu_reference_tokens_per_s"] = float(n_pre / (float(p_ms[0]) / 1e3))
+                except Exception as e:  # noqa: BLE001
+                    line["prefill"]["parity"] = {"error": str(e)[:200]}
             else:
                 line["cpu_baseline"] = None
             # the reference's own token loop (scheduler, graph, sampler) on this library through the spy::Backend adapter

@@ -180,6 +180,22 @@ spyb_status spyb_attention(spyb_backend *backend, const void *q_f16, const void 
 spyb_status spyb_matmul_noalloc(spyb_backend *backend, int32_t weight_type, const void *w_rows_dev, int64_t n_rows, int64_t k,
                                 const float *x_dev, int64_t n_cols, float *out_dev);
 
+/* MatMul(W[Q4_0 | Q8_0], x) for a prompt of n_cols tokens on the tensor cores - the operator the reference evaluates as
+ * n_cols x n_rows independent dot products (OperatorMatMul, backend/host/operator/mat.cpp:95-128, Dot<Q4_0,Q8_0> /
+ * Dot<Q8_0,Q8_0>, backend/host/include/simd/vec_dot.h:42-115), with the same f32 arithmetic and order, so the result is
+ * bit-identical to spyb_submit(MatMul) and to the CPU backend. The integer lane sums of a block come from one
+ * tcgen05 MMA per tile of 128 rows x 16 tokens; the f32 chains follow in block order.
+ *   w_rows_host : n_rows rows of k / 32 blocks in GGUF order (18 or 34 bytes per block), host memory
+ *   x_host      : [n_cols][k] f32; norm_w_host (optional, [k]): RMSNorm(x) * norm_w is applied first, as in front of
+ *                 the QKV and FFN MatMuls of the graph (eps as in NormRMS)
+ *   out_host    : [n_cols][n_rows] f32
+ * Needs n_rows a multiple of 128, k a multiple of 32 (<= 14336), 1..4096 columns; anything else is SPYB_UNSUPPORTED.
+ * Stages everything inside the call (it allocates and synchronises): the entry point of the parity tests, while
+ * spyb_model_eval runs the same kernels on resident buffers for prompts of SPYB_PREFILL_MIN_TOKENS tokens and more. */
+#define SPYB_PREFILL_MIN_TOKENS 16
+spyb_status spyb_prefill_matmul(spyb_backend *backend, int32_t weight_type, const void *w_rows_host, int64_t n_rows, int64_t k,
+                                const float *x_host, int64_t n_cols, const float *norm_w_host, float eps, float *out_host);
+
 /* ---- whole-model path: the graph LLAMAModel::build_graph emits (model/src/llm/model/llama.cpp:86-264)
  * executed as a fixed plan of fused kernels. */
 typedef struct {

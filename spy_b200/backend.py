@@ -105,6 +105,7 @@ def lib():
         "spyb_model_last_launches": (i64, [vp]),
         "spyb_model_tap_xq": (i32, [vp, vp]),
         "spyb_matmul_noalloc": (i32, [vp, i32, vp, i64, i64, vp, i64, vp]),
+        "spyb_prefill_matmul": (i32, [vp, i32, vp, i64, i64, vp, i64, vp, C.c_float, vp]),
         "spyb_model_tp_export": (i32, [vp, vp]),
         "spyb_model_tp_import": (i32, [vp, vp]),
         "spyb_model_read_timeline": (i32, [vp, vp, i32]),
@@ -276,6 +277,17 @@ class B200Backend:
     def matmul_noalloc(self, weight_type: int, w_dev: int, n_rows: int, k: int, x_dev: int, n_cols: int, out_dev: int) -> None:
         """MatMul of raw-layout quantized rows (device pointers throughout) that allocates nothing; enqueues only (use sync())."""
         self._check(self._l.spyb_matmul_noalloc(self.h, weight_type, w_dev, n_rows, k, x_dev, n_cols, out_dev))
+
+    def prefill_matmul(self, weight_type: int, w_rows: np.ndarray, n_rows: int, k: int, x: np.ndarray, norm_w=None, eps: float = 0.0) -> np.ndarray:
+        """MatMul of raw-layout quantized rows (host bytes) with the columns x [T, k] on the tensor-core prompt kernel; returns f32 [T, n_rows]."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        w_rows = np.ascontiguousarray(w_rows)
+        t = x.shape[0]
+        out = np.empty((t, n_rows), dtype=np.float32)
+        nw = None if norm_w is None else np.ascontiguousarray(norm_w, dtype=np.float32)
+        self._check(self._l.spyb_prefill_matmul(self.h, weight_type, _np_ptr(w_rows), n_rows, k, _np_ptr(x), t, None if nw is None else _np_ptr(nw),
+                                                C.c_float(eps), _np_ptr(out)))
+        return out
 
     def attention(self, q16: np.ndarray, k_cache16: np.ndarray, v_cache_t16: np.ndarray, pos0: int, n_head: int, head_dim: int, n_ctx: int,
                   n_total: int = 0) -> np.ndarray:

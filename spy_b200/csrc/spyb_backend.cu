@@ -404,6 +404,50 @@ spyb_status spyb_matmul_noalloc(spyb_backend *be, int32_t weight_type, const voi
     return SPYB_SUCCESS;
 }
 
+// ------------------------------------------------------------------------------------------ MatMul of a prompt on the tensor cores
+// OperatorMatMul (backend/host/operator/mat.cpp:95-128) for n_cols activation columns through the tcgen05 prompt kernel:
+// host pointers in and out, everything staged inside the call. The entry point the parity tests drive; the model path
+// uses the same kernels on resident buffers.
+spyb_status spyb_prefill_matmul(spyb_backend *be, int32_t weight_type, const void *w_rows_host, int64_t n_rows, int64_t k, const float *x_host,
+                                int64_t n_cols, const float *norm_w_host, float eps, float *out_host) {
+    if (be == nullptr) { return SPYB_FAIL; }
+    if (weight_type != SPYB_Q4_0 && weight_type != SPYB_Q8_0) { be->set_error("prefill_matmul: weight type %d", weight_type); return SPYB_UNSUPPORTED; }
+    if (w_rows_host == nullptr || x_host == nullptr || out_host == nullptr || n_rows < PF_ROWS || n_rows % PF_ROWS != 0 || k < QK || k % QK != 0 || k > PF_MAX_K ||
+        n_cols < 1 || n_cols > 4096) {
+        be->set_error("prefill_matmul: needs n_rows a multiple of %d, k a multiple of 32 up to %d, 1..4096 columns", PF_ROWS, PF_MAX_K); return SPYB_UNSUPPORTED;
+    }
+    cudaSetDevice(be->config.device_id);
+    const int nb = (int)(k / QK), T = (int)n_cols;
+    const int64_t rb = (int64_t)nb * (weight_type == SPYB_Q4_0 ? 18 : 34);
+    const size_t wbytes = prefill_weight_bytes(weight_type, n_rows, nb), ybytes = prefill_act_bytes(T, nb);
+    uint8_t *raw = nullptr, *w = nullptr, *yq = nullptr; float *x = nullptr, *nw = nullptr, *out = nullptr;
+    auto release = [&]() { cudaFree(raw); cudaFree(w); cudaFree(yq); cudaFree(x); cudaFree(nw); cudaFree(out); };
+    cudaError_t err = cudaMalloc(&raw, (size_t)n_rows * rb + 64);
+    if (err == cudaSuccess) { err = cudaMalloc(&w, wbytes); }
+    if (err == cudaSuccess) { err = cudaMalloc(&yq, ybytes); }
+    if (err == cudaSuccess) { err = cudaMalloc(&x, (size_t)T * k * 4); }
+    if (err == cudaSuccess) { err = cudaMalloc(&out, (size_t)T * n_rows * 4); }
+    if (err == cudaSuccess && norm_w_host != nullptr) { err = cudaMalloc(&nw, (size_t)k * 4); }
+    if (err == cudaSuccess) { err = cudaMemsetAsync(yq, 0, ybytes, be->stream); }
+    if (err == cudaSuccess) { err = cudaMemcpyAsync(raw, w_rows_host, (size_t)n_rows * rb, cudaMemcpyHostToDevice, be->stream); }
+    if (err == cudaSuccess) { err = cudaMemcpyAsync(x, x_host, (size_t)T * k * 4, cudaMemcpyHostToDevice, be->stream); }
+    if (err == cudaSuccess && nw != nullptr) { err = cudaMemcpyAsync(nw, norm_w_host, (size_t)k * 4, cudaMemcpyHostToDevice, be->stream); }
+    if (err == cudaSuccess) { err = launch_prefill_retile(weight_type, raw, rb, n_rows, nb, w, 0, be->stream); }
+    if (err == cudaSuccess) { err = launch_prefill_quant(x, k, T, (int)k, nw, eps, yq, be->stream); }
+    if (err == cudaSuccess) {
+        PrefillGemm g;
+        g.w = w; g.type = weight_type; g.n_rows = n_rows; g.nb = nb; g.yq = yq; g.T = T; g.out = out; g.out_stride = n_rows;
+        g.error_flag = be->d_error_flag; g.wait_limit_ns = be->wait_limit_ns;
+        err = launch_prefill_gemm(g, be->stream);
+    }
+    if (err == cudaSuccess) { err = cudaMemcpyAsync(out_host, out, (size_t)T * n_rows * 4, cudaMemcpyDeviceToHost, be->stream); }
+    if (err == cudaSuccess) { err = cudaStreamSynchronize(be->stream); }
+    release();
+    if (err != cudaSuccess) { be->set_error("prefill_matmul: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
+    if (be->device_error()) { return SPYB_FAIL; }
+    return SPYB_SUCCESS;
+}
+
 // ------------------------------------------------------------------------------------------ submit
 namespace {
 

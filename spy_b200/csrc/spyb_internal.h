@@ -94,6 +94,7 @@ struct spyb_backend {
         if (h_error_flag != nullptr && *reinterpret_cast<volatile int *>(h_error_flag) != 0) {
             const int code = *reinterpret_cast<volatile int *>(h_error_flag);
             if (code == 1) { set_error("a kernel gave up waiting for a bulk copy into shared memory (device error flag 1); the backend must be re-created"); }
+            else if (code >= 4 && code <= 6) { set_error("the prompt GEMM gave up waiting for %s (device error flag %d); the backend must be re-created", code == 4 ? "a shared-memory stage" : code == 5 ? "its operands or a free accumulator buffer" : "a tensor-core result", code); }
             else { set_error("a kernel gave up waiting at a barrier or for another rank's partial result (device error flag %d); the backend must be re-created", code); }
             return true;
         }

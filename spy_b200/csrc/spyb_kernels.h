@@ -104,6 +104,34 @@ struct MatvecParams {
     int    kq_n = 0;
 };
 
+// Prompt evaluation as a GEMM on the tcgen05 tensor cores (spyb_prefill.cu). Weights in tiles of PF_ROWS rows x 1 block,
+// activations as compact Q8_0 blocks grouped by (tile of PF_TOK tokens, block).
+constexpr int PF_ROWS = 128, PF_TOK = 16;
+constexpr int PF_YQ_BYTES = PF_TOK * 32 + PF_TOK * 4;
+constexpr int PF_MAX_K = 14336;   // widest activation row the quantizer kernel holds in registers
+struct PrefillGemm {
+    const uint8_t *w = nullptr;       // [n_rows / PF_ROWS][nb] weight tiles (launch_prefill_retile)
+    int            type = 0;          // 2 = Q4_0, 8 = Q8_0
+    int64_t        n_rows = 0;        // multiple of PF_ROWS
+    int            nb = 0;            // blocks per row
+    const uint8_t *yq = nullptr;      // [ceil(T / PF_TOK)][nb][PF_YQ_BYTES] (launch_prefill_quant)
+    int            T = 0;
+    float         *out = nullptr;     // [T][out_stride]
+    int64_t        out_stride = 0;
+    const float   *resid = nullptr;   // optional [T][out_stride]: out = W x + resid (may alias out)
+    int           *error_flag = nullptr;
+    uint64_t       wait_limit_ns = 1000000000ull;
+    int            stages = 0;        // shared-memory stages (0 = default)
+};
+size_t      prefill_weight_bytes(int type, int64_t n_rows, int nb);
+size_t      prefill_act_bytes(int T, int nb);
+cudaError_t launch_prefill_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0, cudaStream_t stream);
+cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K, const float *norm_w, float eps, uint8_t *yq, cudaStream_t stream);
+cudaError_t launch_prefill_gemm(const PrefillGemm &g, cudaStream_t stream);
+cudaError_t launch_prefill_qkv_post(const float *qkv, int T, int dl, int hd, const int *pos_base, const float2 *rope, __half *q_out, __half *k_cache,
+                                    __half *v_cache, int n_ctx, cudaStream_t stream);
+cudaError_t launch_prefill_silu_mul(const float *upgate, int T, int F, const float *silu_table, float *act, cudaStream_t stream);
+
 struct AttnParams {
     const __half *q = nullptr;        // [T][dl], already rounded to fp16
     const __half *k_cache = nullptr;  // [n_ctx][dl]

@@ -137,12 +137,16 @@ struct NcclApi {
 };
 static NcclApi g_nccl;
 
+struct PfMat { uint8_t *w = nullptr; int type = 0; int64_t n_rows = 0; int nb = 0; };
+
 struct Layer {
     DevMatrix upgate;   // FFN up and gate interleaved in 32-row tiles (when the shard's FFN width is a multiple of 16); else up / gate below
     DevMatrix wqkv, wo, up, gate, down;
     KqSeg     kq_q, kq_k, kq_v, kq_o, kq_up, kq_gate, kq_down;   // K-quant models (Q4_K / Q6_K): the matrices as row ranges in GGUF order
     float    *attn_norm = nullptr, *ffn_norm = nullptr;
     __half   *k_cache = nullptr, *v_cache = nullptr;   // K [n_ctx][dl], V transposed [dl][n_ctx]
+    // the same weights in the tile layout of the tensor-core prompt kernel (spyb_prefill.cu): Wq|Wk|Wv stacked, up|gate stacked
+    PfMat     pf_qkv, pf_wo, pf_ug, pf_down;
 };
 
 }  // namespace spyb
@@ -183,6 +187,14 @@ struct spyb_model {
     int         step_grid = 0, step_ns = 0;
     unsigned long long *d_step_sync = nullptr, *d_step_stamps = nullptr;
     int         step_stamp_count = 0;
+    // prompts of SPYB_PREFILL_MIN_TOKENS tokens and more: GEMMs on the tensor cores over chunks of pf_chunk tokens
+    bool     pf_ok = false, pf_buffers = false;
+    int      pf_chunk = 512;
+    float   *pf_x = nullptr, *pf_qkv = nullptr, *pf_att = nullptr, *pf_ug = nullptr, *pf_act = nullptr;
+    __half  *pf_q = nullptr;
+    uint8_t *pf_yq = nullptr;
+    int32_t *pf_tokens = nullptr, *h_pf_tokens = nullptr;
+    int     *pf_pos = nullptr, *h_pf_pos = nullptr;      // (first position, positions known to the step) per group of 8 tokens
     cudaGraphExec_t graph_exec = nullptr;
     cudaGraphExec_t graph_eval1 = nullptr;   // single-token spyb_model_eval: staging copies, embedding, layers, head, logits copy
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -418,12 +430,74 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
 }
 
 // output norm + head on column `col` of x -> logits[n_vocab]
-spyb_status run_head(spyb_model *m, int col, int64_t *launches) {
+spyb_status run_head(spyb_model *m, int col, int64_t *launches, const float *x_row = nullptr) {
     MatvecParams p;
-    set_weights(m, nullptr, 4, p); p.T = 1; p.pro = PRO_NORM_QUANT; p.x = m->x + (int64_t)col * m->info.d_model; p.x_stride = m->info.d_model;
+    set_weights(m, nullptr, 4, p); p.T = 1; p.pro = PRO_NORM_QUANT; p.x = x_row != nullptr ? x_row : m->x + (int64_t)col * m->info.d_model; p.x_stride = m->info.d_model;
     p.norm_w = m->output_norm; p.eps = m->info.rms_eps; p.epi = EPI_STORE; p.out = m->logits; p.out_stride = m->info.n_vocab;
     p.stamps = m->d_stamps ? m->d_stamps + 8 * (5 * m->layers.size()) : nullptr;
     SPYB_CUDA(m->be, launch_matvec(p, m->be->launch_cfg(m->be->config.use_pdl != 0))); ++*launches;
+    return SPYB_SUCCESS;
+}
+
+// buffers of the tensor-core prompt path, allocated at the first long prompt
+spyb_status ensure_prefill_buffers(spyb_model *m) {
+    if (m->pf_buffers) { return SPYB_SUCCESS; }
+    spyb_backend *be = m->be;
+    const size_t C = (size_t)m->pf_chunk, d = m->info.d_model, ff = m->info.n_ff, dl = m->dl;
+    const int nb_max = (int)(std::max(d, ff) / 32);
+    bool ok = dev_alloc(m, &m->pf_x, C * d) == SPYB_SUCCESS && dev_alloc(m, &m->pf_qkv, C * 3 * dl) == SPYB_SUCCESS && dev_alloc(m, &m->pf_att, C * d) == SPYB_SUCCESS &&
+              dev_alloc(m, &m->pf_ug, C * 2 * ff) == SPYB_SUCCESS && dev_alloc(m, &m->pf_act, C * ff) == SPYB_SUCCESS && dev_alloc(m, &m->pf_q, C * dl) == SPYB_SUCCESS &&
+              dev_alloc(m, &m->pf_yq, prefill_act_bytes((int)C, nb_max)) == SPYB_SUCCESS && dev_alloc(m, &m->pf_tokens, C) == SPYB_SUCCESS &&
+              dev_alloc(m, &m->pf_pos, 2 * (C / TMAX + 1)) == SPYB_SUCCESS;
+    if (!ok) { return SPYB_FAIL; }
+    if (cudaMallocHost(reinterpret_cast<void **>(&m->h_pf_tokens), C * 4) != cudaSuccess ||
+        cudaMallocHost(reinterpret_cast<void **>(&m->h_pf_pos), 2 * (C / TMAX + 1) * 4) != cudaSuccess) { be->set_error("pinned host allocation failed"); return SPYB_FAIL; }
+    m->pf_buffers = true;
+    return SPYB_SUCCESS;
+}
+
+// all layers for the T tokens in pf_x (first position d_pos[0], d_pos[1] positions known to the step): per layer
+//   norm + quantize -> QKV GEMM -> RoPE / KV append -> attention -> quantize -> Wo GEMM + residual
+//   -> norm + quantize -> up|gate GEMM -> up * silu(gate) -> quantize -> down GEMM + residual
+// with the arithmetic of the five fused kernels of run_layers, so that a prompt gives the same bits on either path.
+spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches) {
+    spyb_backend *be = m->be;
+    cudaStream_t s = be->stream;
+    const LaunchCfg cfg = be->launch_cfg(false);
+    const int d = m->info.d_model, ff = m->info.n_ff, dl = m->dl, hd = m->info.head_dim;
+    auto gemm = [&](const PfMat &W, int K, float *out, int64_t out_stride, const float *resid) {
+        PrefillGemm g;
+        g.w = W.w; g.type = W.type; g.n_rows = W.n_rows; g.nb = K / 32; g.yq = m->pf_yq; g.T = T; g.out = out; g.out_stride = out_stride; g.resid = resid;
+        g.error_flag = be->d_error_flag; g.wait_limit_ns = be->wait_limit_ns;
+        return launch_prefill_gemm(g, s);
+    };
+    for (Layer &ly : m->layers) {
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, d, T, d, ly.attn_norm, m->info.rms_eps, m->pf_yq, s));
+        SPYB_CUDA(be, gemm(ly.pf_qkv, d, m->pf_qkv, 3 * (int64_t)dl, nullptr));
+        SPYB_CUDA(be, launch_prefill_qkv_post(m->pf_qkv, T, dl, hd, m->d_pos, m->rope_table, m->pf_q, ly.k_cache, ly.v_cache, m->info.n_ctx, s));
+        *launches += 3;
+        AttnParams a;
+        a.k_cache = ly.k_cache; a.v_cache = ly.v_cache; a.out_stride = d; a.exp_table = be->d_exp_table;
+        a.n_head = dl / hd; a.hd = hd; a.dl = dl; a.n_ctx = m->info.n_ctx; a.scale = 1.0f / std::sqrt((float)hd); a.error_flag = be->d_error_flag;
+        if (m->att_scratch == nullptr) {   // short contexts: one CTA per (head, token)
+            a.q = m->pf_q; a.out = m->pf_att; a.pos_base = m->d_pos; a.T = T;
+            SPYB_CUDA(be, launch_attention(a, cfg)); ++*launches;
+        } else {                           // long contexts: the chip-wide kernels on groups of tokens that fit the score scratch
+            a.scratch = m->att_scratch;
+            for (int t0 = 0; t0 < T; t0 += TMAX) {
+                a.q = m->pf_q + (int64_t)t0 * dl; a.out = m->pf_att + (int64_t)t0 * d; a.pos_base = m->pf_pos + 2 * (t0 / TMAX); a.T = std::min(TMAX, T - t0);
+                SPYB_CUDA(be, launch_attention(a, cfg)); *launches += 3;
+            }
+        }
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_att, d, T, d, nullptr, 0.f, m->pf_yq, s));
+        SPYB_CUDA(be, gemm(ly.pf_wo, d, m->pf_x, d, m->pf_x));
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, d, T, d, ly.ffn_norm, m->info.rms_eps, m->pf_yq, s));
+        SPYB_CUDA(be, gemm(ly.pf_ug, d, m->pf_ug, 2 * (int64_t)ff, nullptr));
+        SPYB_CUDA(be, launch_prefill_silu_mul(m->pf_ug, T, ff, be->d_silu_table, m->pf_act, s));
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_act, ff, T, ff, nullptr, 0.f, m->pf_yq, s));
+        SPYB_CUDA(be, gemm(ly.pf_down, ff, m->pf_x, d, m->pf_x));
+        *launches += 7;
+    }
     return SPYB_SUCCESS;
 }
 
@@ -535,6 +609,30 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         I.weight_bytes += (uint64_t)n_rows * rb_file;
         return SPYB_SUCCESS;
     };
+    // the tile layout of the tensor-core prompt kernel: rows [0, rows_full) of a tensor into rows [dst_row, ...) of a matrix of total_rows rows
+    auto upload_pf = [&](const std::string &name, int64_t k_full, int64_t rows_full, PfMat *into, int64_t dst_row, int64_t total_rows) {
+        const GgufTensor *t; const uint8_t *data;
+        if (!tensor(name, &t, &data)) { return SPYB_FAIL; }
+        if (t->ne[0] != k_full || t->ne[1] != rows_full || (t->type != SPYB_Q4_0 && t->type != SPYB_Q8_0)) { return SPYB_UNSUPPORTED; }
+        const int nb = (int)(k_full / 32);
+        if (into->w == nullptr) {
+            if (dev_alloc(m, &into->w, prefill_weight_bytes(t->type, total_rows, nb)) != SPYB_SUCCESS) { return SPYB_FAIL; }
+            into->type = t->type; into->n_rows = total_rows; into->nb = nb;
+        } else if (into->type != t->type) { return SPYB_UNSUPPORTED; }
+        const int64_t rb = GgufFile::row_bytes(t->type, k_full);
+        const int64_t max_rows = std::max<int64_t>(1, (int64_t)(64u << 20) / rb);   // 64 MiB staging pieces
+        void *stage = nullptr;
+        SPYB_CUDA(be, cudaMalloc(&stage, (size_t)std::min(max_rows, rows_full) * rb + 64));
+        for (int64_t r0 = 0; r0 < rows_full; r0 += max_rows) {
+            const int64_t nr = std::min(max_rows, rows_full - r0);
+            cudaError_t e = cudaMemcpyAsync(stage, data + r0 * rb, (size_t)nr * rb, cudaMemcpyHostToDevice, be->stream);
+            if (e == cudaSuccess) { e = launch_prefill_retile(t->type, static_cast<const uint8_t *>(stage), rb, nr, nb, into->w, dst_row + r0, be->stream); }
+            if (e == cudaSuccess) { e = cudaStreamSynchronize(be->stream); }
+            if (e != cudaSuccess) { cudaFree(stage); be->set_error("GGUF: %s: upload failed: %s", name.c_str(), cudaGetErrorString(e)); return SPYB_FAIL; }
+        }
+        cudaFree(stage);
+        return SPYB_SUCCESS;
+    };
     {   // a model whose attention query weights are K-quants runs on the K-quant kernel throughout
         auto it = f.tensors.find("blk.0.attn_q.weight");
         m->kq = it != f.tensors.end() && (it->second.type == SPYB_Q4_K || it->second.type == SPYB_Q6_K);
@@ -588,6 +686,11 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         }
         if (st != SPYB_SUCCESS) { return fail(st); }
     }
+    // prompts run as GEMMs on the tensor cores when the model is unsharded, Q4_0 / Q8_0 throughout and its widths are
+    // multiples of the kernel's 128-row tile (SPYB_PREFILL=0 keeps the mat-vec passes; the extra copy of the layer weights is then not made)
+    m->pf_ok = tp == 1 && !m->kq && (std::getenv("SPYB_PREFILL") == nullptr || std::atoi(std::getenv("SPYB_PREFILL")) != 0) &&
+               d % PF_ROWS == 0 && I.n_ff % PF_ROWS == 0 && d <= PF_MAX_K && I.n_ff <= PF_MAX_K;
+    if (const char *v = std::getenv("SPYB_PREFILL_CHUNK")) { const int n = std::atoi(v); if (n >= PF_TOK && n <= 4096) { m->pf_chunk = (n + TMAX - 1) / TMAX * TMAX; } }
     m->layers.resize(I.n_layer);
     for (int L = 0; L < I.n_layer; ++L) {
         Layer &ly = m->layers[L];
@@ -645,6 +748,17 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         }
         if (st != SPYB_SUCCESS) { return fail(st); }
         if (dev_alloc(m, &ly.k_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS || dev_alloc(m, &ly.v_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
+        if (m->pf_ok) {
+            spyb_status ps = upload_pf(p + "attn_q.weight", d, d, &ly.pf_qkv, 0, 3 * (int64_t)d);
+            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_k.weight", d, d, &ly.pf_qkv, d, 3 * (int64_t)d); }
+            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_v.weight", d, d, &ly.pf_qkv, 2 * (int64_t)d, 3 * (int64_t)d); }
+            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_output.weight", d, d, &ly.pf_wo, 0, d); }
+            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_up.weight", d, I.n_ff, &ly.pf_ug, 0, 2 * (int64_t)I.n_ff); }
+            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_gate.weight", d, I.n_ff, &ly.pf_ug, I.n_ff, 2 * (int64_t)I.n_ff); }
+            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_down.weight", I.n_ff, d, &ly.pf_down, 0, d); }
+            if (ps == SPYB_FAIL) { return fail(ps); }
+            if (ps != SPYB_SUCCESS) { m->pf_ok = false; }   // a mix of types inside one stacked matrix: prompts stay on the mat-vec passes
+        }
     }
     I.weight_bytes += (uint64_t)(2 * I.n_layer + 1) * d * 4;
     I.kv_bytes_per_token = (uint64_t)2 * I.n_layer * dl * 2;
@@ -702,6 +816,8 @@ void spyb_model_free(spyb_model *m) {
     if (m->h_pos_pinned) { cudaFreeHost(m->h_pos_pinned); }
     if (m->h_tok_pinned) { cudaFreeHost(m->h_tok_pinned); }
     if (m->h_logits_pinned) { cudaFreeHost(m->h_logits_pinned); }
+    if (m->h_pf_tokens) { cudaFreeHost(m->h_pf_tokens); }
+    if (m->h_pf_pos) { cudaFreeHost(m->h_pf_pos); }
     if (m->ev0) { cudaEventDestroy(m->ev0); }
     if (m->ev1) { cudaEventDestroy(m->ev1); }
     delete m;
@@ -805,6 +921,38 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
         if (logits_host != nullptr) { std::memcpy(logits_host, m->h_logits_pinned, (size_t)m->info.n_vocab * 4); }
         SPYB_CUDA(be, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
         m->last_launches = m->eval1_launches;
+        return SPYB_SUCCESS;
+    }
+    if (m->pf_ok && n_tokens >= SPYB_PREFILL_MIN_TOKENS) {
+        // a prompt: chunks of pf_chunk tokens through the tensor-core GEMMs; the score rows of every chunk span all
+        // positions known to the step, as in the passes below
+        if (ensure_prefill_buffers(m) != SPYB_SUCCESS) { return SPYB_FAIL; }
+        SPYB_CUDA(be, cudaEventRecord(m->ev0, be->stream));
+        for (int t0 = 0; t0 < n_tokens; t0 += m->pf_chunk) {
+            const int T = std::min(m->pf_chunk, n_tokens - t0);
+            SPYB_CUDA(be, cudaStreamSynchronize(be->stream));   // pinned staging words are reused per chunk
+            m->h_pos_pinned[0] = n_past + t0; m->h_pos_pinned[1] = n_past + n_tokens; m->h_pos_pinned[2] = ++m->epoch;
+            std::memcpy(m->h_pf_tokens, tokens + t0, (size_t)T * 4);
+            const int groups = (T + TMAX - 1) / TMAX;
+            for (int gi = 0; gi < groups; ++gi) { m->h_pf_pos[2 * gi] = n_past + t0 + gi * TMAX; m->h_pf_pos[2 * gi + 1] = n_past + n_tokens; }
+            SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 12, cudaMemcpyHostToDevice, be->stream));
+            SPYB_CUDA(be, cudaMemcpyAsync(m->pf_pos, m->h_pf_pos, (size_t)groups * 8, cudaMemcpyHostToDevice, be->stream));
+            SPYB_CUDA(be, cudaMemcpyAsync(m->pf_tokens, m->h_pf_tokens, (size_t)T * 4, cudaMemcpyHostToDevice, be->stream));
+            SPYB_CUDA(be, launch_embed(m->pf_tokens, T, m->embd, m->embd_type, m->info.d_model, m->pf_x, be->stream)); ++launches;
+            if (run_prefill_layers(m, T, &launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
+            if (t0 + T == n_tokens) {
+                if (run_head(m, 0, &launches, m->pf_x + (int64_t)(T - 1) * m->info.d_model) != SPYB_SUCCESS) { return SPYB_FAIL; }
+                if (logits_host != nullptr) {
+                    SPYB_CUDA(be, cudaMemcpyAsync(m->h_logits_pinned, m->logits, (size_t)m->info.n_vocab * 4, cudaMemcpyDeviceToHost, be->stream));
+                }
+            }
+        }
+        SPYB_CUDA(be, cudaEventRecord(m->ev1, be->stream));
+        SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+        if (be->device_error()) { return SPYB_FAIL; }
+        if (logits_host != nullptr) { std::memcpy(logits_host, m->h_logits_pinned, (size_t)m->info.n_vocab * 4); }
+        SPYB_CUDA(be, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+        m->last_launches = launches;
         return SPYB_SUCCESS;
     }
     SPYB_CUDA(be, cudaEventRecord(m->ev0, be->stream));

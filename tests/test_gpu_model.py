@@ -134,6 +134,45 @@ def test_prompt_longer_than_one_pass_and_context_edge(be, oracle, tmp_models):
     m.close()
 
 
+@pytest.mark.parametrize("wtype", [quants.Q4_0, quants.Q8_0])
+@pytest.mark.parametrize("env", [{}, {"SPYB_PREFILL_CHUNK": "32"}, {"SPYB_PREFILL": "0"}])
+def test_prompt_on_the_tensor_cores(env, wtype, oracle, tmp_models, monkeypatch):
+    """An 83-token prompt: as one GEMM chunk (default), as chunks of 32 + 32 + 19 tokens, and as mat-vec passes
+    (SPYB_PREFILL=0): the same bits as the CPU restatement each time, for the prompt's logits and for the tokens
+    decoded afterwards from the KV cache the prompt left behind."""
+    cfg = gguf_io.LlamaConfig(n_layer=3, d_model=384, n_head=3, n_ff=640, n_vocab=500, wtype=wtype, weight_std=0.05)
+    path = str(tmp_models / f"tc_prompt_{wtype}.gguf")
+    if not os.path.exists(path):
+        gguf_io.make_llama_gguf(path, cfg, seed=53)
+    prompt = np.random.default_rng(8).integers(3, cfg.n_vocab, size=83)
+    want_ids, want_logits = oracle.OracleLlama(path, n_ctx=96).generate(prompt, 8)
+    for k, v in env.items():
+        monkeypatch.setenv(k, v)
+    b = B.B200Backend(0)
+    m = B.LlamaModel(b, path, n_ctx=96)
+    ids, logits = m.generate(prompt, 8)
+    assert np.array_equal(ids, want_ids) and logits_ok(logits, want_logits)
+    # a second prompt appended behind the first one's context (n_past > 0), again through the GEMM path
+    m2 = B.LlamaModel(b, path, n_ctx=96)
+    m2.eval(prompt[:40], 0)
+    again = m2.eval(prompt[40:], 40)
+    assert np.array_equal(again.view(np.uint32), want_logits[0].view(np.uint32))
+    m.close(); m2.close(); b.close()
+
+
+def test_prompt_widths_the_gemm_tile_does_not_divide(be, oracle, tmp_models):
+    """n_ff = 448 is no multiple of the 128-row GEMM tile: the prompt stays on the mat-vec passes and is still exact."""
+    cfg = gguf_io.LlamaConfig(n_layer=2, d_model=256, n_head=2, n_ff=448, n_vocab=300, weight_std=0.05)
+    path = str(tmp_models / "odd_ff.gguf")
+    gguf_io.make_llama_gguf(path, cfg, seed=59)
+    prompt = np.random.default_rng(9).integers(3, cfg.n_vocab, size=20)
+    want_ids, want_logits = oracle.OracleLlama(path, n_ctx=32).generate(prompt, 4)
+    m = B.LlamaModel(be, path, n_ctx=32)
+    ids, logits = m.generate(prompt, 4)
+    assert np.array_equal(ids, want_ids) and logits_ok(logits, want_logits)
+    m.close()
+
+
 def test_long_context_attention(be, oracle, tmp_models):
     """A 600-token prompt in a 1024-token context: many 32-wide accumulator steps and ragged tails in both
     attention products."""

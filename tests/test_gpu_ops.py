@@ -129,6 +129,49 @@ def test_matmul_small_shapes(be, oracle, qt, n, k, t):
     assert close(got, want)
 
 
+# MatMul of a prompt on the tensor cores (tcgen05): the same operator, the same bits
+@pytest.mark.parametrize("qt", [quants.Q4_0, quants.Q8_0])
+@pytest.mark.parametrize("n,k,t,norm", [(128, 32, 1, False), (128, 256, 16, False), (256, 1024, 37, True), (384, 96, 5, False), (128, 4096, 64, True),
+                                        (1024, 11008, 19, False)])
+def test_prefill_matmul_matches_oracle(be, oracle, qt, n, k, t, norm):
+    """Block counts below, at and above the pipeline depths (1, 3, 8, 32, 128, 344 blocks), ragged token tiles, with and
+    without the RMSNorm in front; activations with a few outliers so that block scales differ widely."""
+    rng = np.random.default_rng(n + k + t + qt)
+    w = quants.quantize((rng.standard_normal((n, k)) * 0.02).astype(np.float32), qt)
+    x = rng.standard_normal((t, k)).astype(np.float32)
+    x[rng.integers(0, t, 8), rng.integers(0, k, 8)] *= 40.0
+    nw = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32) if norm else None
+    got = be.prefill_matmul(qt, w, n, k, x, nw, 1e-5)
+    xin = oracle.mul_rows(oracle.rmsnorm(x, 1e-5), nw) if norm else x
+    want = oracle.matmul(qt, w, k, n, xin)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_prefill_matmul_full_size_rows_sample(be, oracle):
+    """The 7B FFN-down shape with a 512-token prompt: a row and token sample against the oracle, bit for bit."""
+    n, k, t = 4096, 11008, 512
+    rng = np.random.default_rng(5)
+    w = quants.quantize((rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)), quants.Q4_0)
+    x = rng.standard_normal((t, k)).astype(np.float32)
+    got = be.prefill_matmul(quants.Q4_0, w, n, k, x)
+    rows = np.unique(np.concatenate([[0, 127, 128, n - 1], rng.integers(0, n, size=28)]))
+    cols = np.unique(np.concatenate([[0, 15, 16, t - 1], rng.integers(0, t, size=12)]))
+    want = oracle.matmul(quants.Q4_0, np.ascontiguousarray(w[rows]), k, len(rows), x[cols])
+    assert np.array_equal(got[np.ix_(cols, rows)].view(np.uint32), want.view(np.uint32))
+    assert np.isfinite(got).all()
+
+
+def test_prefill_matmul_rejects_what_does_not_fit(be):
+    w = np.zeros(100 * 18, dtype=np.uint8)
+    x = np.zeros((2, 32), dtype=np.float32)
+    with pytest.raises(B.SpybError) as e:
+        be.prefill_matmul(quants.Q4_0, w, 100, 32, x)          # rows not a multiple of 128
+    assert e.value.status == B.UNSUPPORTED
+    with pytest.raises(B.SpybError) as e:
+        be.prefill_matmul(quants.Q4_K, w, 128, 256, np.zeros((2, 256), dtype=np.float32))
+    assert e.value.status == B.UNSUPPORTED
+
+
 @pytest.mark.parametrize("qt", [quants.Q4_0, quants.Q8_0])
 @pytest.mark.parametrize("n,k", SHAPES)
 @pytest.mark.parametrize("t", [1, 4, 16])
