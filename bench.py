@@ -223,6 +223,8 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--profile-step", type=int, default=0, metavar="LAYERS",
                     help="load only the first LAYERS blocks of the model, evaluate the prompt, decode 4 tokens and exit: the small case for an ncu capture of the single-token step kernel")
+    ap.add_argument("--profile-prefill", type=int, default=0, metavar="LAYERS",
+                    help="load only the first LAYERS blocks of the model, evaluate a 448-token prompt twice and exit: the small case for an ncu capture of the prompt kernels")
     ap.add_argument("--profile-kernel", type=int, default=-1, metavar="KIND",
                     help="load the model, run two sweeps of one mat-vec kind over all layers (0 qkv, 1 attn_out, 2 ffn_up_gate, 3 ffn_down, 4 head) and exit: the small case for an ncu capture")
     args = ap.parse_args()
@@ -236,8 +238,8 @@ def main():
     import torch
     from spy_b200 import backend as B
 
-    if args.profile_step > 0:
-        os.environ["SPYB_MAX_LAYERS"] = str(args.profile_step)
+    if args.profile_step > 0 or args.profile_prefill > 0:
+        os.environ["SPYB_MAX_LAYERS"] = str(max(args.profile_step, args.profile_prefill))
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -275,6 +277,14 @@ def main():
         first = model.eval(prompt, 0)
         ids, _ = model.decode(int(np.argmax(first)), N_PROMPT, 4)
         print(json.dumps({"profile_step_layers": args.profile_step, "ms_per_step": model.last_ms / 4, "ids": [int(i) for i in ids]}))
+        model.close(); be.close()
+        return
+    if args.profile_prefill > 0:
+        n_pre = max(N_PROMPT, min(512, N_CTX - 64))
+        pre_ids = np.random.default_rng(PROMPT_SEED + 1).integers(3, info.n_vocab, size=n_pre).astype(np.int32)
+        model.eval(pre_ids, 0)
+        model.eval(pre_ids, 0)
+        print(json.dumps({"profile_prefill_layers": args.profile_prefill, "tokens": int(n_pre), "ms": model.last_ms, "launches": int(model.last_launches)}))
         model.close(); be.close()
         return
     if args.profile_kernel >= 0:

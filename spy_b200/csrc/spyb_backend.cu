@@ -438,7 +438,21 @@ spyb_status spyb_prefill_matmul(spyb_backend *be, int32_t weight_type, const voi
         PrefillGemm g;
         g.w = w; g.type = weight_type; g.n_rows = n_rows; g.nb = nb; g.yq = yq; g.T = T; g.out = out; g.out_stride = n_rows;
         g.error_flag = be->d_error_flag; g.wait_limit_ns = be->wait_limit_ns;
+        // profiling aid (SPYB_PF_STAMPS=<file>): clock stamps of the roles of one CTA of a second, warm launch
+        long long *stamps = nullptr;
+        const char *dump = std::getenv("SPYB_PF_STAMPS");
+        const size_t stamp_bytes = 8 * 512 * 4 * sizeof(long long);
         err = launch_prefill_gemm(g, be->stream);
+        if (err == cudaSuccess && dump != nullptr && cudaMalloc(&stamps, stamp_bytes) == cudaSuccess) {
+            cudaMemsetAsync(stamps, 0, stamp_bytes, be->stream);
+            g.stamps = stamps;
+            err = launch_prefill_gemm(g, be->stream);
+            std::vector<long long> h(stamp_bytes / sizeof(long long));
+            cudaStreamSynchronize(be->stream);
+            cudaMemcpy(h.data(), stamps, stamp_bytes, cudaMemcpyDeviceToHost);
+            if (FILE *f = std::fopen(dump, "wb")) { std::fwrite(h.data(), 8, h.size(), f); std::fclose(f); }
+            cudaFree(stamps);
+        }
     }
     if (err == cudaSuccess) { err = cudaMemcpyAsync(out_host, out, (size_t)T * n_rows * 4, cudaMemcpyDeviceToHost, be->stream); }
     if (err == cudaSuccess) { err = cudaStreamSynchronize(be->stream); }

@@ -84,6 +84,15 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
         if (global_timer_ns() - t0 > limit_ns) { return false; }
     }
 }
+// the same for waits that normally end within a microsecond (pipeline hand-offs inside a CTA): the plain form of
+// try_wait wakes as soon as the phase completes, the suspend-hint form is only the fallback of a wait that drags on
+__device__ __forceinline__ bool mbar_wait_prompt(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
+#pragma unroll 1
+    for (int i = 0; i < 2048; ++i) {
+        if (mbar_try_wait(bar, parity)) { return true; }
+    }
+    return mbar_wait_bounded(bar, parity, limit_ns);
+}
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void *src_gmem, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(dst_smem), "l"(__cvta_generic_to_global(src_gmem)), "r"(bytes), "r"(bar) : "memory");

@@ -121,7 +121,7 @@ struct PrefillGemm {
     const float   *resid = nullptr;   // optional [T][out_stride]: out = W x + resid (may alias out)
     int           *error_flag = nullptr;
     uint64_t       wait_limit_ns = 1000000000ull;
-    int            stages = 0;        // shared-memory stages (0 = default)
+    long long     *stamps = nullptr;  // profiling aid: clock stamps of CTA (0, 0), [8 roles][512 blocks][4]
 };
 size_t      prefill_weight_bytes(int type, int64_t n_rows, int nb);
 size_t      prefill_act_bytes(int T, int nb);

@@ -28,23 +28,17 @@ namespace {
 
 constexpr int PF_M           = PF_ROWS;            // weight rows per CTA = M of the MMA
 constexpr int PF_N           = 8 * PF_TOK;         // 8 accumulator columns per token
-constexpr int PF_EPI_THREADS = 256;                // 8 epilogue warps: (row quadrant 0..3) x (token half 0..1)
-constexpr int PF_THREADS     = PF_EPI_THREADS + 64;   // + one copy warp + one MMA warp
 constexpr int PF_TILE        = PF_M * 32;          // bytes of one s8 operand tile
+constexpr int PF_EPI_WARPS   = 16;                 // epilogue warps: (row quadrant 0..3) x (4 tokens of the 16)
+constexpr int PF_BATCH       = 4;                  // blocks per batch: the unit of the copies, of the expansion and of stage reuse
+constexpr int PF_RING        = 4;                  // batches in the shared-memory rings
+constexpr int PF_STAGES      = PF_RING * PF_BATCH; // blocks in the rings
+constexpr int PF_WTILE       = PF_TILE + 256;      // a weight tile in HBM: the s8 A operand of 128 rows x 32, then 128 fp16 block scales
+constexpr int PF_MMA_WARPS   = 2;                  // warps whose first thread issues the MMAs of every PF_MMA_WARPS-th block
+constexpr int PF_THREADS     = (PF_EPI_WARPS + 2 + PF_MMA_WARPS) * 32;   // + the copy warp and the expander warp
 constexpr int PF_DBUF        = 4;                  // accumulator buffers in tensor memory, PF_N columns each (512 columns = all of it)
-constexpr int PF_AHEAD       = 3;                  // blocks whose operands are expanded before their lane sums are read back
 constexpr int PF_QUANT_THREADS = 512;
 constexpr int PF_QUANT_GROUPS  = PF_MAX_K / (4 * PF_QUANT_THREADS);   // float4 groups per thread
-
-// shared-memory stage of one block step
-template <int WT> struct PfStage {
-    static constexpr int RAW    = WT == 2 ? 2304 : 4352;           // the weight tile as it lies in HBM (Q8_0: already the A operand)
-    static constexpr int SC_OFF = WT == 2 ? 2048 : 4096;           // its 128 fp16 scales
-    static constexpr int YQ_OFF = RAW;                             // 16 tokens x 32 s8, then 16 f32 scales
-    static constexpr int A_OFF  = WT == 2 ? RAW + PF_YQ_BYTES : 0;
-    static constexpr int B_OFF  = WT == 2 ? A_OFF + PF_TILE : RAW + PF_YQ_BYTES;
-    static constexpr int BYTES  = B_OFF + PF_TILE;
-};
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -76,10 +70,10 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
 constexpr uint32_t PF_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PF_N >> 3) << 17) | ((uint32_t)(PF_M >> 4) << 24);
 
 __device__ __forceinline__ void mma_s8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc) {
-    const uint32_t zero = 0;
+    const uint32_t zero = 0, accumulate = 1;   // D += A B^T: D holds the offset pattern
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
                  "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(PF_IDESC), "r"(zero), "r"(zero) : "memory");
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(PF_IDESC), "r"(accumulate), "r"(zero) : "memory");
 }
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -93,43 +87,85 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
                    "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *r) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// the same 32-bit word into 32 consecutive columns of this thread's lane
+__device__ __forceinline__ void tmem_st32_same(uint32_t taddr, uint32_t v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(taddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// feeder roles (copy, expansion, MMA issue) run ahead of the epilogue: their waits back off instead of competing with the
+// epilogue warps for issue slots
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
+    if (mbar_try_wait(bar, parity)) { return true; }
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        __nanosleep(100);
+        if (mbar_try_wait(bar, parity)) { return true; }
+        if (global_timer_ns() - t0 > limit_ns) { return false; }
+    }
+}
+// profiling aid: clock stamps of CTA (0, 0) into g.stamps [8 roles][512 blocks][4] (nullptr: off)
+#define PF_STAMP(role, b, i) do { if (g.stamps != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (b) < 512) { g.stamps[((role) * 512 + (b)) * 4 + (i)] = clock64(); } } while (0)
 __device__ __forceinline__ void pf_report(int *error_flag, int code) {
     if (error_flag != nullptr) { atomicExch(error_flag, code); }
 }
 
 // ---------------------------------------------------------------------------------------------
-// the GEMM. grid = (row tiles, token tiles); one CTA per SM (it takes all 512 tensor-memory columns).
+// the GEMM. grid = (token tiles, row tiles); one CTA per SM (it takes all 512 tensor-memory columns).
+//
+// Warps 0-15  epilogue: row = 32 (warp % 4) + lane, tokens 4 (warp / 4) .. + 3 of the tile; four warps per scheduler and loads
+//             requested a half block ahead hide the latency of tensor memory behind the f32 chains
+// warp 16     one thread streams batches of PF_BATCH blocks with cp.async.bulk: two copies per batch (the weight tiles, which
+//             arrive as A operands, and the compact activations) - issuing a bulk copy costs its thread hundreds of cycles
+// warp 17     expands the compact activations of a batch into the B operands
+// warps 18-19 one thread each issues the MMAs of alternate blocks (an MMA and its commit hold the issuing thread for
+//             ~450 cycles; threads of different warps issue in parallel)
+//
+// The accumulator buffers hold the s32 pattern of 1.5 * 2^23 in every element and the MMA accumulates onto it, so what
+// the epilogue reads back is the bit pattern of the float 1.5 * 2^23 + lane_sum: one exact subtraction gives
+// (float)lane_sum without an integer conversion (|lane_sum| < 2^22). The epilogue writes the pattern back after reading.
+//
+// Shared memory: rings of PF_STAGES blocks (PF_RING batches), one ring per kind so that a batch is one contiguous run:
+//   A ring  [PF_STAGES][4352]   weight tiles (s8 operand + 128 fp16 scales), written by cp.async.bulk
+//   Y ring  [PF_STAGES][576]    compact activations (16 tokens x 32 s8, 16 f32 scales), written by cp.async.bulk
+//   B ring  [PF_STAGES][4096]   expanded activations, written by the expander warp
 template <int WT>
-__global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm g, int NS) {
-    using S = PfStage<WT>;
+__global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm g) {
+    constexpr int NS = PF_STAGES, NQ = PF_RING;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t bars  = sbase + (uint32_t)NS * S::BYTES;
-    auto stage    = [&](int s) { return sbase + (uint32_t)s * S::BYTES; };
-    auto raw_full = [&](int s) { return bars + 8u * s; };                        // weights and activations of the stage have landed
-    auto ops_full = [&](int s) { return bars + 8u * (NS + s); };                 // both operand tiles are written (256 arrivals)
-    auto st_free  = [&](int s) { return bars + 8u * (2 * NS + s); };             // the stage may be refilled (256 arrivals)
-    auto d_full   = [&](int i) { return bars + 8u * (3 * NS + i); };             // the MMA into buffer i has completed
-    auto d_free   = [&](int i) { return bars + 8u * (3 * NS + PF_DBUF + i); };   // buffer i has been read back (256 arrivals)
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (size_t)NS * S::BYTES + 8 * (3 * NS + 2 * PF_DBUF));
+    const uint32_t a_ring = sbase, y_ring = a_ring + NS * PF_WTILE, b_ring = y_ring + NS * PF_YQ_BYTES;
+    const uint32_t bars  = b_ring + NS * PF_TILE;
+    auto raw_full = [&](int q) { return bars + 8u * q; };                        // the batch's weights and activations have landed
+    auto ops_full = [&](int q) { return bars + 8u * (NQ + q); };                 // the batch's B operands are written and fenced
+    auto st_free  = [&](int q) { return bars + 8u * (2 * NQ + q); };             // the batch's stages may be refilled (one arrival per epilogue warp)
+    auto d_full   = [&](int i) { return bars + 8u * (3 * NQ + i); };             // the MMA into buffer i has completed
+    auto d_free   = [&](int i) { return bars + 8u * (3 * NQ + PF_DBUF + i); };   // buffer i holds the offset pattern again (one arrival per epilogue warp)
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (size_t)NS * (PF_WTILE + PF_YQ_BYTES + PF_TILE) + 8 * (3 * NQ + 2 * PF_DBUF));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nb = g.nb;
+    const int nb = g.nb, n_batch = (nb + PF_BATCH - 1) / PF_BATCH;
     const uint64_t limit = g.wait_limit_ns;
-    const uint8_t *wsrc = g.w + ((int64_t)blockIdx.x * nb) * S::RAW;
-    const uint8_t *ysrc = g.yq + ((int64_t)blockIdx.y * nb) * PF_YQ_BYTES;
+    const int row_tile = blockIdx.y, tok_tile = blockIdx.x;   // CTAs that run together share a weight tile: it crosses HBM once
+    const uint8_t *wsrc = g.w + ((int64_t)row_tile * nb) * PF_WTILE;
+    const uint8_t *ysrc = g.yq + ((int64_t)tok_tile * nb) * PF_YQ_BYTES;
 
     if (tid == 0) {
-        for (int s = 0; s < NS; ++s) { mbar_init(raw_full(s), 1); mbar_init(ops_full(s), PF_EPI_THREADS); mbar_init(st_free(s), PF_EPI_THREADS); }
-        for (int i = 0; i < PF_DBUF; ++i) { mbar_init(d_full(i), 1); mbar_init(d_free(i), PF_EPI_THREADS); }
+        for (int q = 0; q < NQ; ++q) { mbar_init(raw_full(q), 1); mbar_init(ops_full(q), 1); mbar_init(st_free(q), PF_EPI_WARPS); }
+        for (int i = 0; i < PF_DBUF; ++i) { mbar_init(d_full(i), 1); mbar_init(d_free(i), PF_EPI_WARPS); }
         mbar_init_fence();
     }
     // the B tiles are zero except where the expansion writes, and it writes the same places for every block
-    for (int i = tid; i < NS * (PF_TILE / 16); i += PF_THREADS) {
-        sts128(stage(i / (PF_TILE / 16)) + S::B_OFF + (uint32_t)(i % (PF_TILE / 16)) * 16u, make_uint4(0u, 0u, 0u, 0u));
-    }
+    for (int i = tid; i < NS * (PF_TILE / 16); i += PF_THREADS) { sts128(b_ring + (uint32_t)i * 16u, make_uint4(0u, 0u, 0u, 0u)); }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(PF_DBUF * PF_N) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -140,116 +176,138 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp == PF_EPI_THREADS / 32) {
-        // ---- copy warp: one thread streams the stages
+    if (warp >= PF_EPI_WARPS + 2) {
+        // ---- MMA warps: the first thread of warp m issues the 128 x 128 x 32 MMA of blocks m, m + PF_MMA_WARPS, ... onto a buffer
+        // that holds the offset pattern; MMAs into different buffers do not depend on one another
         if (lane == 0) {
-            int issued = 0;
-            for (int b = 0; b < nb; ++b) {
-                const int s = b % NS;
-                if (b >= NS && !mbar_wait_bounded(st_free(s), (uint32_t)((b / NS) - 1) & 1u, limit)) { pf_report(g.error_flag, 4); break; }
-                mbar_expect_tx(raw_full(s), (uint32_t)(S::RAW + PF_YQ_BYTES));
-                bulk_copy_g2s(stage(s), wsrc + (int64_t)b * S::RAW, (uint32_t)S::RAW, raw_full(s));
-                bulk_copy_g2s(stage(s) + S::YQ_OFF, ysrc + (int64_t)b * PF_YQ_BYTES, (uint32_t)PF_YQ_BYTES, raw_full(s));
-                issued = b + 1;
-            }
-            // no copy of this CTA is in flight when it leaves
-            for (int b = max(0, issued - NS); b < issued; ++b) {
-                if (!mbar_wait_bounded(raw_full(b % NS), (uint32_t)(b / NS) & 1u, limit)) { pf_report(g.error_flag, 4); break; }
-            }
-        }
-    } else if (warp == PF_EPI_THREADS / 32 + 1) {
-        // ---- MMA warp: one thread issues one 128 x 128 x 32 MMA per block
-        if (lane == 0) {
-            int issued = 0;
-            for (int b = 0; b < nb; ++b) {
-                const int s = b % NS, buf = b % PF_DBUF;
-                if (!mbar_wait_bounded(ops_full(s), (uint32_t)(b / NS) & 1u, limit)) { pf_report(g.error_flag, 5); break; }
-                if (b >= PF_DBUF && !mbar_wait_bounded(d_free(buf), (uint32_t)((b / PF_DBUF) - 1) & 1u, limit)) { pf_report(g.error_flag, 5); break; }
+            int last = -1;
+            for (int b = warp - (PF_EPI_WARPS + 2); b < nb; b += PF_MMA_WARPS) {
+                const int s = b % NS, q = b / PF_BATCH, buf = b % PF_DBUF;
+                PF_STAMP(2, b, 0);
+                if (!mbar_wait_relaxed(ops_full(q % NQ), (uint32_t)(q / NQ) & 1u, limit)) { pf_report(g.error_flag, 5); break; }
+                PF_STAMP(2, b, 1);
+                if (!mbar_wait_relaxed(d_free(buf), (uint32_t)(b / PF_DBUF) & 1u, limit)) { pf_report(g.error_flag, 5); break; }
+                PF_STAMP(2, b, 2);
                 tc_fence_after();
-                mma_s8_ss(tmem + (uint32_t)(buf * PF_N), operand_desc(stage(s) + S::A_OFF), operand_desc(stage(s) + S::B_OFF));
+                mma_s8_ss(tmem + (uint32_t)(buf * PF_N), operand_desc(a_ring + (uint32_t)s * PF_WTILE), operand_desc(b_ring + (uint32_t)s * PF_TILE));
                 mma_commit(d_full(buf));
-                issued = b + 1;
+                PF_STAMP(2, b, 3);
+                last = b;
             }
             // every MMA has completed (it reads shared memory and writes tensor memory) before the CTA leaves
-            if (issued > 0) {
-                const int b = issued - 1;
-                if (!mbar_wait_bounded(d_full(b % PF_DBUF), (uint32_t)(b / PF_DBUF) & 1u, limit)) { pf_report(g.error_flag, 5); }
+            if (last >= 0 && !mbar_wait_relaxed(d_full(last % PF_DBUF), (uint32_t)(last / PF_DBUF) & 1u, limit)) { pf_report(g.error_flag, 5); }
+        }
+    } else if (warp == PF_EPI_WARPS) {
+        // ---- copy warp: one thread requests batch after batch
+        if (lane == 0) {
+            int issued = 0;
+            for (int q = 0; q < n_batch; ++q) {
+                if (q >= NQ && !mbar_wait_relaxed(st_free(q % NQ), (uint32_t)((q / NQ) - 1) & 1u, limit)) { pf_report(g.error_flag, 4); break; }
+                const int b0 = q * PF_BATCH, n = min(PF_BATCH, nb - b0), s0 = b0 % NS;
+                PF_STAMP(0, b0, 0);
+                mbar_expect_tx(raw_full(q % NQ), (uint32_t)(n * (PF_WTILE + PF_YQ_BYTES)));
+                bulk_copy_g2s(a_ring + (uint32_t)s0 * PF_WTILE, wsrc + (int64_t)b0 * PF_WTILE, (uint32_t)(n * PF_WTILE), raw_full(q % NQ));
+                bulk_copy_g2s(y_ring + (uint32_t)s0 * PF_YQ_BYTES, ysrc + (int64_t)b0 * PF_YQ_BYTES, (uint32_t)(n * PF_YQ_BYTES), raw_full(q % NQ));
+                issued = q + 1;
+            }
+            // no copy of this CTA is in flight when it leaves
+            for (int q = max(0, issued - NQ); q < issued; ++q) {
+                if (!mbar_wait_relaxed(raw_full(q % NQ), (uint32_t)(q / NQ) & 1u, limit)) { pf_report(g.error_flag, 4); break; }
             }
         }
-    } else {
-        // ---- epilogue warps: expand operands ahead, read the lane sums back, run the f32 chains
-        const int quad = warp & 3, half = warp >> 2;
-        const int row = 32 * quad + lane;
-        float acc[8][8];
+    } else if (warp == PF_EPI_WARPS + 1) {
+        // ---- expander warp: word w of token tt of the compact activations -> row 8 tt + w of B, at its own place in the
+        // block (the rest of B stays zero); one proxy fence per batch makes the writes visible to the tensor core
+        for (int q = 0; q < n_batch; ++q) {
+            bool ok = mbar_wait_relaxed(raw_full(q % NQ), (uint32_t)(q / NQ) & 1u, limit);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { if (lane == 0) { pf_report(g.error_flag, 4); } break; }
+            const int b0 = q * PF_BATCH, n = min(PF_BATCH, nb - b0), s0 = b0 % NS;
+            if (lane == 0) { PF_STAMP(1, b0, 0); }
+            for (int j = 0; j < n; ++j) {
+                const uint32_t ysrc_s = y_ring + (uint32_t)(s0 + j) * PF_YQ_BYTES, bdst = b_ring + (uint32_t)(s0 + j) * PF_TILE;
 #pragma unroll
-        for (int t = 0; t < 8; ++t) {
+                for (int k = 0; k < PF_TOK * 8 / 32; ++k) {
+                    const int i = lane + 32 * k, tt = i >> 3, w = i & 7;
+                    sts32(bdst + (uint32_t)tt * 256u + (uint32_t)(w >> 2) * 128u + (uint32_t)w * 16u + (uint32_t)(w & 3) * 4u, lds32(ysrc_s + (uint32_t)i * 4u));
+                }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(ops_full(q % NQ)); PF_STAMP(1, b0, 1); }
+        }
+    } else {
+        // ---- epilogue warps: row = 32 (warp % 4) + lane, tokens 4 (warp / 4) .. + 3 of the tile = 32 columns of D, read back as two
+        // halves of 16 columns (two tokens): a half of the next block is requested as soon as its registers are free, so the
+        // tensor-memory loads overlap the f32 chains of the other half
+        const int quad = warp & 3, part = warp >> 2;
+        const int row = 32 * quad + lane;
+        const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(32 * part);
+        const uint32_t dw_addr = a_ring + PF_TILE + 2u * (uint32_t)row, dx_addr = y_ring + PF_TOK * 32 + 16u * (uint32_t)part;
+        float acc[4][8];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
 #pragma unroll
             for (int n = 0; n < 8; ++n) { acc[t][n] = 0.f; }
         }
-        auto expand = [&](int b) -> bool {
-            const int s = b % NS;
-            bool ok = mbar_wait_bounded(raw_full(s), (uint32_t)(b / NS) & 1u, limit);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) { return false; }
-            const uint32_t st = stage(s);
-            if (WT == 2) {   // nibbles (stored XOR 8) -> 16 * (value - 8) as s8: low nibbles are elements 0..15, high nibbles 16..31
-                const uint4 w = lds128(st + (uint32_t)row * 16u);
-                uint4 o;
-                if (half == 0) { o.x = (w.x << 4) & 0xf0f0f0f0u; o.y = (w.y << 4) & 0xf0f0f0f0u; o.z = (w.z << 4) & 0xf0f0f0f0u; o.w = (w.w << 4) & 0xf0f0f0f0u; }
-                else           { o.x = w.x & 0xf0f0f0f0u; o.y = w.y & 0xf0f0f0f0u; o.z = w.z & 0xf0f0f0f0u; o.w = w.w & 0xf0f0f0f0u; }
-                sts128(st + S::A_OFF + (uint32_t)(row >> 3) * 256u + (uint32_t)half * 128u + (uint32_t)(row & 7) * 16u, o);
-            }
-            if (tid < PF_TOK * 8) {   // word w of token tt -> row 8 tt + w of B, at its own place in the block
-                const int tt = tid >> 3, w = tid & 7;
-                const uint32_t v = lds32(st + S::YQ_OFF + (uint32_t)tt * 32u + (uint32_t)w * 4u);
-                sts32(st + S::B_OFF + (uint32_t)tt * 256u + (uint32_t)(w >> 2) * 128u + (uint32_t)w * 16u + (uint32_t)(w & 3) * 4u, v);
-            }
-            fence_async_smem();
-            mbar_arrive(ops_full(s));
-            return true;
-        };
-        bool ok = true;
-        for (int b = 0; b < PF_AHEAD && b < nb && ok; ++b) { ok = expand(b); }
+        for (int i = 0; i < PF_DBUF; ++i) { tmem_st32_same(tbase + (uint32_t)(i * PF_N), MAGIC_I); }   // the offset pattern into this thread's part of every buffer
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) { for (int i = 0; i < PF_DBUF; ++i) { mbar_arrive(d_free(i)); } }
+
+        uint32_t ra[16], rb[16];
+        bool ok = mbar_wait_bounded(d_full(0), 0u, limit);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) { tc_fence_after(); tmem_ld16(tbase, ra); tmem_ld16(tbase + 16u, rb); }
         for (int b = 0; b < nb && ok; ++b) {
-            if (b + PF_AHEAD < nb) { ok = expand(b + PF_AHEAD); if (!ok) { break; } }
             const int s = b % NS, buf = b % PF_DBUF;
-            ok = mbar_wait_bounded(d_full(buf), (uint32_t)(b / PF_DBUF) & 1u, limit);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) { break; }
-            tc_fence_after();
-            uint32_t r[64];
-            const uint32_t taddr = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(buf * PF_N + 64 * half);
-            tmem_ld32(taddr, r);
-            tmem_ld32(taddr + 32u, r + 32);
-            tmem_ld_wait();
-            tc_fence_before();
-            mbar_arrive(d_free(buf));
-            const uint32_t st = stage(s);
-            float dw = h2f((uint16_t)lds16(st + S::SC_OFF + 2u * (uint32_t)row));
+            const uint32_t taddr = tbase + (uint32_t)(buf * PF_N);
+            float dw = h2f((uint16_t)lds16(dw_addr + (uint32_t)s * PF_WTILE));
             if (WT == 2) { dw = __fmul_rn(dw, 0.0625f); }   // exact: undoes the factor 16 of the nibble trick
-            const float4 dxa = lds128f(st + S::YQ_OFF + PF_TOK * 32 + 32u * (uint32_t)half);
-            const float4 dxb = lds128f(st + S::YQ_OFF + PF_TOK * 32 + 32u * (uint32_t)half + 16u);
-            const float dx[8] = {dxa.x, dxa.y, dxa.z, dxa.w, dxb.x, dxb.y, dxb.z, dxb.w};
+            const float4 dx = lds128f(dx_addr + (uint32_t)s * PF_YQ_BYTES);
+            const float sc[4] = {__fmul_rn(dw, dx.x), __fmul_rn(dw, dx.y), __fmul_rn(dw, dx.z), __fmul_rn(dw, dx.w)};
+            tmem_ld_wait();                       // both halves of block b are in registers
+            tmem_st32_same(taddr, MAGIC_I);       // the buffer's columns have been read: put the offset pattern back
 #pragma unroll
-            for (int t = 0; t < 8; ++t) {
-                const float sc = __fmul_rn(dw, dx[t]);
+            for (int t = 0; t < 2; ++t) {
 #pragma unroll
-                for (int n = 0; n < 8; ++n) { acc[t][n] = fmaf(sc, __int2float_rn((int)r[8 * t + n]), acc[t][n]); }
+                for (int n = 0; n < 8; ++n) { acc[t][n] = fmaf(sc[t], __fsub_rn(__uint_as_float(ra[8 * t + n]), MAGIC_F), acc[t][n]); }
             }
-            mbar_arrive(st_free(s));
+            const bool more = b + 1 < nb;
+            const uint32_t tnext = tbase + (uint32_t)(((b + 1) % PF_DBUF) * PF_N);
+            if (more) {                           // the first half of the next block arrives while the second half of this one is folded
+                ok = mbar_wait_bounded(d_full((b + 1) % PF_DBUF), (uint32_t)((b + 1) / PF_DBUF) & 1u, limit);
+                ok = __all_sync(0xffffffffu, ok);
+                if (ok) { tc_fence_after(); tmem_ld16(tnext, ra); }
+            }
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+#pragma unroll
+                for (int n = 0; n < 8; ++n) { acc[2 + t][n] = fmaf(sc[2 + t], __fsub_rn(__uint_as_float(rb[8 * t + n]), MAGIC_F), acc[2 + t][n]); }
+            }
+            if (more && ok) { tmem_ld16(tnext + 16u, rb); }   // and its second half while the hand-offs below are made
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(d_free(buf));
+                if ((b % PF_BATCH) == PF_BATCH - 1 || b == nb - 1) { mbar_arrive(st_free((b / PF_BATCH) % NQ)); }   // the batch's scales have been read
+            }
         }
-        if (!ok) { pf_report(g.error_flag, 6); }
+        tmem_ld_wait();
+        if (!ok) { if (lane == 0) { pf_report(g.error_flag, 6); } }
         else {
             // hsum_float_8 (vec_util.h:74-81): column n < 4 is accumulator 4 + n for Q4_0 (low nibbles) and accumulator n for Q8_0;
             // either way the tree is (c0 + c4) + (c2 + c6) and (c1 + c5) + (c3 + c7)
 #pragma unroll
-            for (int t = 0; t < 8; ++t) {
-                const int token = blockIdx.y * PF_TOK + 8 * half + t;
+            for (int t = 0; t < 4; ++t) {
+                const int token = tok_tile * PF_TOK + 4 * part + t;
                 if (token < g.T) {
                     const float r0 = __fadd_rn(acc[t][0], acc[t][4]), r1 = __fadd_rn(acc[t][1], acc[t][5]);
                     const float r2 = __fadd_rn(acc[t][2], acc[t][6]), r3 = __fadd_rn(acc[t][3], acc[t][7]);
                     const float v = __fadd_rn(__fadd_rn(r0, r2), __fadd_rn(r1, r3));
-                    const int64_t i = (int64_t)token * g.out_stride + (int64_t)blockIdx.x * PF_M + row;
+                    const int64_t i = (int64_t)token * g.out_stride + (int64_t)row_tile * PF_M + row;
                     g.out[i] = g.resid != nullptr ? __fadd_rn(v, g.resid[i]) : v;
                 }
             }
@@ -333,12 +391,11 @@ __global__ void __launch_bounds__(PF_QUANT_THREADS) prefill_quant_kernel(const f
     }
 }
 
-// upload-time re-layout: raw 18-byte / 34-byte blocks of rows [0, n_rows) -> tiles of 128 rows x 1 block
-//   Q4_0: [128 rows][16 nibble bytes XOR 0x88] then [128] fp16 scales              (2304 bytes)
-//   Q8_0: the s8 operand tile itself (core matrices of 8 rows x 16 bytes) then the scales   (4352 bytes)
+// upload-time re-layout: raw 18-byte / 34-byte blocks of rows [0, n_rows) -> tiles of 128 rows x 1 block: the s8 A operand
+// (core matrices of 8 rows x 16 bytes; Q4_0: element k < 16 is 16 * (low nibble of byte k - 8), element 16 + k the same of
+// the high nibble - the factor 16 is undone in the scale, exactly) followed by the 128 fp16 block scales
 template <int WT>
 __global__ void prefill_retile_kernel(const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0) {
-    using S = PfStage<WT>;
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_rows * nb) { return; }
     const int64_t lrow = i / nb;
@@ -346,14 +403,19 @@ __global__ void prefill_retile_kernel(const uint8_t *raw, int64_t row_stride, in
     const uint8_t *src = raw + lrow * row_stride + (int64_t)b * (WT == 2 ? 18 : 34);
     const int64_t row = dst_row0 + lrow;
     const int     r = (int)(row % PF_M);
-    uint8_t *tile = base + ((row / PF_M) * nb + b) * (int64_t)S::RAW;
-    reinterpret_cast<uint16_t *>(tile + S::SC_OFF)[r] = (uint16_t)(src[0] | (src[1] << 8));
-    constexpr int WORDS = WT == 2 ? 4 : 8;
+    uint8_t *tile = base + ((row / PF_M) * nb + b) * (int64_t)PF_WTILE;
+    reinterpret_cast<uint16_t *>(tile + PF_TILE)[r] = (uint16_t)(src[0] | (src[1] << 8));
+    uint32_t *lo = reinterpret_cast<uint32_t *>(tile + (r >> 3) * 256 + (r & 7) * 16), *hi = lo + 32;   // elements 0..15 and 16..31
 #pragma unroll
-    for (int k = 0; k < WORDS; ++k) {
-        uint32_t v = (uint32_t)(src[2 + 4 * k] | (src[3 + 4 * k] << 8) | (src[4 + 4 * k] << 16) | ((uint32_t)src[5 + 4 * k] << 24));
-        if (WT == 2) { reinterpret_cast<uint32_t *>(tile + r * 16)[k] = v ^ 0x88888888u; }
-        else         { reinterpret_cast<uint32_t *>(tile + (r >> 3) * 256 + (k >> 2) * 128 + (r & 7) * 16)[k & 3] = v; }
+    for (int k = 0; k < 4; ++k) {
+        if (WT == 2) {
+            const uint32_t v = (uint32_t)(src[2 + 4 * k] | (src[3 + 4 * k] << 8) | (src[4 + 4 * k] << 16) | ((uint32_t)src[5 + 4 * k] << 24)) ^ 0x88888888u;
+            lo[k] = (v << 4) & 0xf0f0f0f0u;
+            hi[k] = v & 0xf0f0f0f0u;
+        } else {
+            lo[k] = (uint32_t)(src[2 + 4 * k] | (src[3 + 4 * k] << 8) | (src[4 + 4 * k] << 16) | ((uint32_t)src[5 + 4 * k] << 24));
+            hi[k] = (uint32_t)(src[18 + 4 * k] | (src[19 + 4 * k] << 8) | (src[20 + 4 * k] << 16) | ((uint32_t)src[21 + 4 * k] << 24));
+        }
     }
 }
 
@@ -391,23 +453,21 @@ __global__ void prefill_silu_mul_kernel(const float *upgate, int T, int F, const
     act[i] = __fmul_rn(up, silu_table[f2h(gate)]);
 }
 
-template <int WT> size_t pf_smem_bytes(int NS) { return (size_t)NS * PfStage<WT>::BYTES + 8 * (3 * NS + 2 * PF_DBUF) + 16; }
+constexpr size_t PF_SMEM_BYTES = (size_t)PF_STAGES * (PF_WTILE + PF_YQ_BYTES + PF_TILE) + 8 * (3 * PF_RING + 2 * PF_DBUF) + 16;
 
 template <int WT>
 cudaError_t launch_gemm_t(const PrefillGemm &g, cudaStream_t stream) {
-    int NS = 12;
-    if (g.stages > PF_AHEAD + 1 && g.stages <= 16) { NS = g.stages; }
-    const size_t smem = pf_smem_bytes<WT>(NS);
+    const size_t smem = PF_SMEM_BYTES;
     cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(prefill_gemm_kernel<WT>), smem);
     if (err != cudaSuccess) { return err; }
-    const dim3 grid((unsigned)(g.n_rows / PF_M), (unsigned)((g.T + PF_TOK - 1) / PF_TOK));
-    prefill_gemm_kernel<WT><<<grid, PF_THREADS, smem, stream>>>(g, NS);
+    const dim3 grid((unsigned)((g.T + PF_TOK - 1) / PF_TOK), (unsigned)(g.n_rows / PF_M));
+    prefill_gemm_kernel<WT><<<grid, PF_THREADS, smem, stream>>>(g);
     return cudaGetLastError();
 }
 
 }  // namespace
 
-size_t prefill_weight_bytes(int type, int64_t n_rows, int nb) { return (size_t)(n_rows / PF_ROWS) * nb * (type == 2 ? PfStage<2>::RAW : PfStage<8>::RAW); }
+size_t prefill_weight_bytes(int type, int64_t n_rows, int nb) { (void)type; return (size_t)(n_rows / PF_ROWS) * nb * PF_WTILE; }
 size_t prefill_act_bytes(int T, int nb) { return (size_t)((T + PF_TOK - 1) / PF_TOK) * nb * PF_YQ_BYTES; }
 
 cudaError_t launch_prefill_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0, cudaStream_t stream) {
