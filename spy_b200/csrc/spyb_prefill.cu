@@ -260,39 +260,48 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
         bool ok = mbar_wait_bounded(d_full(0), 0u, limit);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) { tc_fence_after(); tmem_ld16(tbase, ra); tmem_ld16(tbase + 16u, rb); }
-        for (int b = 0; b < nb && ok; ++b) {
-            const int s = b % NS, buf = b % PF_DBUF;
-            const uint32_t taddr = tbase + (uint32_t)(buf * PF_N);
-            float dw = h2f((uint16_t)lds16(dw_addr + (uint32_t)s * PF_WTILE));
-            if (WT == 2) { dw = __fmul_rn(dw, 0.0625f); }   // exact: undoes the factor 16 of the nibble trick
-            const float4 dx = lds128f(dx_addr + (uint32_t)s * PF_YQ_BYTES);
-            const float sc[4] = {__fmul_rn(dw, dx.x), __fmul_rn(dw, dx.y), __fmul_rn(dw, dx.z), __fmul_rn(dw, dx.w)};
-            tmem_ld_wait();                       // both halves of block b are in registers
-            tmem_st32_same(taddr, MAGIC_I);       // the buffer's columns have been read: put the offset pattern back
+        // a batch per outer iteration: block j of a batch uses accumulator buffer j and stage 4 (q % PF_RING) + j, so that inside the
+        // unrolled body every address is a constant offset and every phase parity a bit of q
+        static_assert(PF_BATCH == PF_DBUF, "the unrolled epilogue pairs block j of a batch with accumulator buffer j");
+        for (int q = 0; q < n_batch && ok; ++q) {
+            const uint32_t ring_q = (uint32_t)(q % NQ) * PF_BATCH;
+            const uint32_t dw_q = dw_addr + ring_q * PF_WTILE, dx_q = dx_addr + ring_q * PF_YQ_BYTES;
 #pragma unroll
-            for (int t = 0; t < 2; ++t) {
+            for (int j = 0; j < PF_BATCH; ++j) {
+                const int b = q * PF_BATCH + j;
+                if (b >= nb || !ok) { break; }
+                const uint32_t taddr = tbase + (uint32_t)(j * PF_N);
+                float dw = h2f((uint16_t)lds16(dw_q + (uint32_t)j * PF_WTILE));
+                if (WT == 2) { dw = __fmul_rn(dw, 0.0625f); }   // exact: undoes the factor 16 of the nibble trick
+                const float4 dx = lds128f(dx_q + (uint32_t)j * PF_YQ_BYTES);
+                const float sc[4] = {__fmul_rn(dw, dx.x), __fmul_rn(dw, dx.y), __fmul_rn(dw, dx.z), __fmul_rn(dw, dx.w)};
+                tmem_ld_wait();                       // both halves of block b are in registers
+                tmem_st32_same(taddr, MAGIC_I);       // the buffer's columns have been read: put the offset pattern back
 #pragma unroll
-                for (int n = 0; n < 8; ++n) { acc[t][n] = fmaf(sc[t], __fsub_rn(__uint_as_float(ra[8 * t + n]), MAGIC_F), acc[t][n]); }
-            }
-            const bool more = b + 1 < nb;
-            const uint32_t tnext = tbase + (uint32_t)(((b + 1) % PF_DBUF) * PF_N);
-            if (more) {                           // the first half of the next block arrives while the second half of this one is folded
-                ok = mbar_wait_bounded(d_full((b + 1) % PF_DBUF), (uint32_t)((b + 1) / PF_DBUF) & 1u, limit);
-                ok = __all_sync(0xffffffffu, ok);
-                if (ok) { tc_fence_after(); tmem_ld16(tnext, ra); }
-            }
+                for (int t = 0; t < 2; ++t) {
 #pragma unroll
-            for (int t = 0; t < 2; ++t) {
+                    for (int n = 0; n < 8; ++n) { acc[t][n] = fmaf(sc[t], __fsub_rn(__uint_as_float(ra[8 * t + n]), MAGIC_F), acc[t][n]); }
+                }
+                const bool more = b + 1 < nb;
+                const uint32_t tnext = tbase + (uint32_t)(((j + 1) % PF_DBUF) * PF_N);
+                if (more) {                           // the first half of the next block arrives while the second half of this one is folded
+                    ok = mbar_wait_bounded(d_full((j + 1) % PF_DBUF), (uint32_t)(q + (j + 1) / PF_DBUF) & 1u, limit);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (ok) { tc_fence_after(); tmem_ld16(tnext, ra); }
+                }
 #pragma unroll
-                for (int n = 0; n < 8; ++n) { acc[2 + t][n] = fmaf(sc[2 + t], __fsub_rn(__uint_as_float(rb[8 * t + n]), MAGIC_F), acc[2 + t][n]); }
-            }
-            if (more && ok) { tmem_ld16(tnext + 16u, rb); }   // and its second half while the hand-offs below are made
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(d_free(buf));
-                if ((b % PF_BATCH) == PF_BATCH - 1 || b == nb - 1) { mbar_arrive(st_free((b / PF_BATCH) % NQ)); }   // the batch's scales have been read
+                for (int t = 0; t < 2; ++t) {
+#pragma unroll
+                    for (int n = 0; n < 8; ++n) { acc[2 + t][n] = fmaf(sc[2 + t], __fsub_rn(__uint_as_float(rb[8 * t + n]), MAGIC_F), acc[2 + t][n]); }
+                }
+                if (more && ok) { tmem_ld16(tnext + 16u, rb); }   // and its second half while the hand-offs below are made
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(d_free(j));
+                    if (j == PF_BATCH - 1 || b == nb - 1) { mbar_arrive(st_free(q % NQ)); }   // the batch's scales have been read
+                }
             }
         }
         tmem_ld_wait();
