@@ -29,7 +29,7 @@ namespace {
 constexpr int PF_M           = PF_ROWS;            // weight rows per CTA = M of the MMA
 constexpr int PF_N           = 8 * PF_TOK;         // 8 accumulator columns per token
 constexpr int PF_TILE        = PF_M * 32;          // bytes of one s8 operand tile
-constexpr int PF_EPI_WARPS   = 16;                 // epilogue warps: (row quadrant 0..3) x (4 tokens of the 16)
+constexpr int PF_EPI_WARPS   = 8;                  // epilogue warps: (row quadrant 0..3) x (8 tokens of the 16); 12 warps in all leave them 168 registers
 constexpr int PF_BATCH       = 4;                  // blocks per batch: the unit of the copies, of the expansion and of stage reuse
 constexpr int PF_RING        = 4;                  // batches in the shared-memory rings
 constexpr int PF_STAGES      = PF_RING * PF_BATCH; // blocks in the rings
@@ -237,26 +237,36 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
             if (lane == 0) { mbar_arrive(ops_full(q % NQ)); PF_STAMP(1, b0, 1); }
         }
     } else {
-        // ---- epilogue warps: row = 32 (warp % 4) + lane, tokens 4 (warp / 4) .. + 3 of the tile = 32 columns of D, read back as two
-        // halves of 16 columns (two tokens): a half of the next block is requested as soon as its registers are free, so the
-        // tensor-memory loads overlap the f32 chains of the other half
-        const int quad = warp & 3, part = warp >> 2;
+        // ---- epilogue warps: row = 32 (warp % 4) + lane, tokens 8 (warp / 4) .. + 7 of the tile = 64 columns of D, read back 16
+        // columns (two tokens) at a time into two alternating register sets: a set is requested again as soon as its values
+        // have been folded, so that the tensor-memory loads overlap the f32 chains of the other set
+        const int quad = warp & 3, half = warp >> 2;
         const int row = 32 * quad + lane;
-        const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(32 * part);
-        const uint32_t dw_addr = a_ring + PF_TILE + 2u * (uint32_t)row, dx_addr = y_ring + PF_TOK * 32 + 16u * (uint32_t)part;
-        float acc[4][8];
+        const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(64 * half);
+        const uint32_t dw_addr = a_ring + PF_TILE + 2u * (uint32_t)row, dx_addr = y_ring + PF_TOK * 32 + 32u * (uint32_t)half;
+        float acc[8][8];
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
+        for (int t = 0; t < 8; ++t) {
 #pragma unroll
             for (int n = 0; n < 8; ++n) { acc[t][n] = 0.f; }
         }
-        for (int i = 0; i < PF_DBUF; ++i) { tmem_st32_same(tbase + (uint32_t)(i * PF_N), MAGIC_I); }   // the offset pattern into this thread's part of every buffer
+        for (int i = 0; i < PF_DBUF; ++i) {   // the offset pattern into this thread's part of every buffer
+            tmem_st32_same(tbase + (uint32_t)(i * PF_N), MAGIC_I);
+            tmem_st32_same(tbase + (uint32_t)(i * PF_N) + 32u, MAGIC_I);
+        }
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) { for (int i = 0; i < PF_DBUF; ++i) { mbar_arrive(d_free(i)); } }
 
         uint32_t ra[16], rb[16];
+        auto fold2 = [&](const uint32_t *r, int t0, const float *sc) {   // two tokens: columns 8 t0 .. 8 t0 + 15
+#pragma unroll
+            for (int t = 0; t < 2; ++t) {
+#pragma unroll
+                for (int n = 0; n < 8; ++n) { acc[t0 + t][n] = fmaf(sc[t0 + t], __fsub_rn(__uint_as_float(r[8 * t + n]), MAGIC_F), acc[t0 + t][n]); }
+            }
+        };
         bool ok = mbar_wait_bounded(d_full(0), 0u, limit);
         ok = __all_sync(0xffffffffu, ok);
         if (ok) { tc_fence_after(); tmem_ld16(tbase, ra); tmem_ld16(tbase + 16u, rb); }
@@ -273,28 +283,27 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
                 const uint32_t taddr = tbase + (uint32_t)(j * PF_N);
                 float dw = h2f((uint16_t)lds16(dw_q + (uint32_t)j * PF_WTILE));
                 if (WT == 2) { dw = __fmul_rn(dw, 0.0625f); }   // exact: undoes the factor 16 of the nibble trick
-                const float4 dx = lds128f(dx_q + (uint32_t)j * PF_YQ_BYTES);
-                const float sc[4] = {__fmul_rn(dw, dx.x), __fmul_rn(dw, dx.y), __fmul_rn(dw, dx.z), __fmul_rn(dw, dx.w)};
-                tmem_ld_wait();                       // both halves of block b are in registers
-                tmem_st32_same(taddr, MAGIC_I);       // the buffer's columns have been read: put the offset pattern back
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
-#pragma unroll
-                    for (int n = 0; n < 8; ++n) { acc[t][n] = fmaf(sc[t], __fsub_rn(__uint_as_float(ra[8 * t + n]), MAGIC_F), acc[t][n]); }
-                }
+                const float4 dxa = lds128f(dx_q + (uint32_t)j * PF_YQ_BYTES), dxb = lds128f(dx_q + (uint32_t)j * PF_YQ_BYTES + 16u);
+                const float sc[8] = {__fmul_rn(dw, dxa.x), __fmul_rn(dw, dxa.y), __fmul_rn(dw, dxa.z), __fmul_rn(dw, dxa.w),
+                                     __fmul_rn(dw, dxb.x), __fmul_rn(dw, dxb.y), __fmul_rn(dw, dxb.z), __fmul_rn(dw, dxb.w)};
+                tmem_ld_wait();                       // columns 0..31 of block b are in registers
+                fold2(ra, 0, sc);
+                tmem_ld16(taddr + 32u, ra);
+                fold2(rb, 2, sc);
+                tmem_ld16(taddr + 48u, rb);
+                tmem_ld_wait();                       // columns 32..63 too: the buffer has been read, put the offset pattern back
+                tmem_st32_same(taddr, MAGIC_I);
+                tmem_st32_same(taddr + 32u, MAGIC_I);
+                fold2(ra, 4, sc);
                 const bool more = b + 1 < nb;
                 const uint32_t tnext = tbase + (uint32_t)(((j + 1) % PF_DBUF) * PF_N);
-                if (more) {                           // the first half of the next block arrives while the second half of this one is folded
+                if (more) {                           // the next block's first columns arrive while the last two tokens are folded
                     ok = mbar_wait_bounded(d_full((j + 1) % PF_DBUF), (uint32_t)(q + (j + 1) / PF_DBUF) & 1u, limit);
                     ok = __all_sync(0xffffffffu, ok);
                     if (ok) { tc_fence_after(); tmem_ld16(tnext, ra); }
                 }
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
-#pragma unroll
-                    for (int n = 0; n < 8; ++n) { acc[2 + t][n] = fmaf(sc[2 + t], __fsub_rn(__uint_as_float(rb[8 * t + n]), MAGIC_F), acc[2 + t][n]); }
-                }
-                if (more && ok) { tmem_ld16(tnext + 16u, rb); }   // and its second half while the hand-offs below are made
+                fold2(rb, 6, sc);
+                if (more && ok) { tmem_ld16(tnext + 16u, rb); }
                 tmem_st_wait();
                 tc_fence_before();
                 __syncwarp();
@@ -310,8 +319,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
             // hsum_float_8 (vec_util.h:74-81): column n < 4 is accumulator 4 + n for Q4_0 (low nibbles) and accumulator n for Q8_0;
             // either way the tree is (c0 + c4) + (c2 + c6) and (c1 + c5) + (c3 + c7)
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
-                const int token = tok_tile * PF_TOK + 4 * part + t;
+            for (int t = 0; t < 8; ++t) {
+                const int token = tok_tile * PF_TOK + 8 * half + t;
                 if (token < g.T) {
                     const float r0 = __fadd_rn(acc[t][0], acc[t][4]), r1 = __fadd_rn(acc[t][1], acc[t][5]);
                     const float r2 = __fadd_rn(acc[t][2], acc[t][6]), r3 = __fadd_rn(acc[t][3], acc[t][7]);
