@@ -100,6 +100,13 @@ __device__ __forceinline__ void tmem_st32_same(uint32_t taddr, uint32_t v) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                  "{%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(taddr), "r"(v) : "memory");
 }
+// 16 consecutive columns of this thread's lane from 16 registers (callers keep a register set that holds the offset
+// pattern alive across the loop, so that no copies are made per store)
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+                   "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // feeder roles (copy, expansion, MMA issue) run ahead of the epilogue: their waits back off instead of competing with the
@@ -259,7 +266,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
         __syncwarp();
         if (lane == 0) { for (int i = 0; i < PF_DBUF; ++i) { mbar_arrive(d_free(i)); } }
 
-        uint32_t ra[16], rb[16];
+        uint32_t ra[16], rb[16], pattern[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) { asm volatile("mov.b32 %0, %1;" : "=r"(pattern[i]) : "r"(MAGIC_I)); }   // (opaque to the compiler: 16 live registers)
         auto fold2 = [&](const uint32_t *r, int t0, const float *sc) {   // two tokens: columns 8 t0 .. 8 t0 + 15
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
@@ -292,8 +301,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
                 fold2(rb, 2, sc);
                 tmem_ld16(taddr + 48u, rb);
                 tmem_ld_wait();                       // columns 32..63 too: the buffer has been read, put the offset pattern back
-                tmem_st32_same(taddr, MAGIC_I);
-                tmem_st32_same(taddr + 32u, MAGIC_I);
+                tmem_st16(taddr, pattern); tmem_st16(taddr + 16u, pattern); tmem_st16(taddr + 32u, pattern); tmem_st16(taddr + 48u, pattern);
                 fold2(ra, 4, sc);
                 const bool more = b + 1 < nb;
                 const uint32_t tnext = tbase + (uint32_t)(((j + 1) % PF_DBUF) * PF_N);
