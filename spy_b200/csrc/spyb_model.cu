@@ -137,6 +137,9 @@ struct NcclApi {
 };
 static NcclApi g_nccl;
 
+constexpr int TMAX_COLUMNS = 8;        // activation columns the mat-vec passes hold
+constexpr int PF_ATT_GROUP = 64;       // tokens per long-context attention launch of the prompt path
+
 struct PfMat { uint8_t *w = nullptr; int type = 0; int64_t n_rows = 0; int nb = 0; };
 
 struct Layer {
@@ -190,6 +193,7 @@ struct spyb_model {
     // prompts of SPYB_PREFILL_MIN_TOKENS tokens and more: GEMMs on the tensor cores over chunks of pf_chunk tokens
     bool     pf_ok = false, pf_buffers = false;
     int      pf_chunk = 512;
+    int      att_group = TMAX_COLUMNS;   // tokens per attention launch on the long-context path (as many as the score scratch holds)
     float   *pf_x = nullptr, *pf_qkv = nullptr, *pf_att = nullptr, *pf_ug = nullptr, *pf_act = nullptr;
     __half  *pf_q = nullptr;
     uint8_t *pf_yq = nullptr;
@@ -218,7 +222,7 @@ spyb_status dev_alloc(spyb_model *m, T **p, size_t count) {
     return SPYB_SUCCESS;
 }
 
-constexpr int TMAX = 8;   // activation columns the buffers hold
+constexpr int TMAX = TMAX_COLUMNS;   // activation columns the buffers hold
 
 // NCCL form of the exchange (used until the peer buffers are imported): every rank's share [off, off + len) of every
 // column is gathered in place into buf [T][stride]; len * tp_size == stride
@@ -448,7 +452,7 @@ spyb_status ensure_prefill_buffers(spyb_model *m) {
     bool ok = dev_alloc(m, &m->pf_x, C * d) == SPYB_SUCCESS && dev_alloc(m, &m->pf_qkv, C * 3 * dl) == SPYB_SUCCESS && dev_alloc(m, &m->pf_att, C * d) == SPYB_SUCCESS &&
               dev_alloc(m, &m->pf_ug, C * 2 * ff) == SPYB_SUCCESS && dev_alloc(m, &m->pf_act, C * ff) == SPYB_SUCCESS && dev_alloc(m, &m->pf_q, C * dl) == SPYB_SUCCESS &&
               dev_alloc(m, &m->pf_yq, prefill_act_bytes((int)C, nb_max)) == SPYB_SUCCESS && dev_alloc(m, &m->pf_tokens, C) == SPYB_SUCCESS &&
-              dev_alloc(m, &m->pf_pos, 2 * (C / TMAX + 1)) == SPYB_SUCCESS;
+              dev_alloc(m, &m->pf_pos, 2 * (C / TMAX + 1)) == SPYB_SUCCESS;   // (sized for the smallest group)
     if (!ok) { return SPYB_FAIL; }
     if (cudaMallocHost(reinterpret_cast<void **>(&m->h_pf_tokens), C * 4) != cudaSuccess ||
         cudaMallocHost(reinterpret_cast<void **>(&m->h_pf_pos), 2 * (C / TMAX + 1) * 4) != cudaSuccess) { be->set_error("pinned host allocation failed"); return SPYB_FAIL; }
@@ -484,8 +488,8 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches) {
             SPYB_CUDA(be, launch_attention(a, cfg)); ++*launches;
         } else {                           // long contexts: the chip-wide kernels on groups of tokens that fit the score scratch
             a.scratch = m->att_scratch;
-            for (int t0 = 0; t0 < T; t0 += TMAX) {
-                a.q = m->pf_q + (int64_t)t0 * dl; a.out = m->pf_att + (int64_t)t0 * d; a.pos_base = m->pf_pos + 2 * (t0 / TMAX); a.T = std::min(TMAX, T - t0);
+            for (int t0 = 0; t0 < T; t0 += m->att_group) {
+                a.q = m->pf_q + (int64_t)t0 * dl; a.out = m->pf_att + (int64_t)t0 * d; a.pos_base = m->pf_pos + 2 * (t0 / m->att_group); a.T = std::min(m->att_group, T - t0);
                 SPYB_CUDA(be, launch_attention(a, cfg)); *launches += 3;
             }
         }
@@ -784,7 +788,8 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         m->tp_peer[I.tp_rank] = m->tp_local;
         m->att = tp_att(m, m->tp_local); m->act = tp_act(m, m->tp_local);
     }
-    const size_t att_scratch = attention_scratch_floats(I.n_ctx, dl / I.head_dim, TMAX);
+    m->att_group = m->pf_ok ? PF_ATT_GROUP : TMAX;
+    const size_t att_scratch = attention_scratch_floats(I.n_ctx, dl / I.head_dim, m->att_group);
     bool ok = dev_alloc(m, &m->x, (size_t)TMAX * d) == SPYB_SUCCESS && dev_alloc(m, &m->scratch, (size_t)TMAX * d) == SPYB_SUCCESS &&
               (att_scratch == 0 || dev_alloc(m, &m->att_scratch, att_scratch) == SPYB_SUCCESS) &&
               dev_alloc(m, &m->logits, (size_t)I.n_vocab) == SPYB_SUCCESS && dev_alloc(m, &m->q, (size_t)TMAX * dl) == SPYB_SUCCESS &&
@@ -933,8 +938,8 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
             SPYB_CUDA(be, cudaStreamSynchronize(be->stream));   // pinned staging words are reused per chunk
             m->h_pos_pinned[0] = n_past + t0; m->h_pos_pinned[1] = n_past + n_tokens; m->h_pos_pinned[2] = ++m->epoch;
             std::memcpy(m->h_pf_tokens, tokens + t0, (size_t)T * 4);
-            const int groups = (T + TMAX - 1) / TMAX;
-            for (int gi = 0; gi < groups; ++gi) { m->h_pf_pos[2 * gi] = n_past + t0 + gi * TMAX; m->h_pf_pos[2 * gi + 1] = n_past + n_tokens; }
+            const int groups = (T + m->att_group - 1) / m->att_group;
+            for (int gi = 0; gi < groups; ++gi) { m->h_pf_pos[2 * gi] = n_past + t0 + gi * m->att_group; m->h_pf_pos[2 * gi + 1] = n_past + n_tokens; }
             SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 12, cudaMemcpyHostToDevice, be->stream));
             SPYB_CUDA(be, cudaMemcpyAsync(m->pf_pos, m->h_pf_pos, (size_t)groups * 8, cudaMemcpyHostToDevice, be->stream));
             SPYB_CUDA(be, cudaMemcpyAsync(m->pf_tokens, m->h_pf_tokens, (size_t)T * 4, cudaMemcpyHostToDevice, be->stream));
