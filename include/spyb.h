@@ -196,6 +196,12 @@ spyb_status spyb_matmul_noalloc(spyb_backend *backend, int32_t weight_type, cons
 spyb_status spyb_prefill_matmul(spyb_backend *backend, int32_t weight_type, const void *w_rows_host, int64_t n_rows, int64_t k,
                                 const float *x_host, int64_t n_cols, const float *norm_w_host, float eps, float *out_host);
 
+/* Failure-path check of the prompt kernel that faults nothing: a small launch whose second batch of blocks is never
+ * copied, with `limit_ns` as the bound of every wait. Succeeds when the kernel returned by itself and recorded one of
+ * its codes (4 = a shared-memory stage, 5 = operands or a free accumulator buffer, 6 = a tensor-core result; also
+ * written to *error_code_out); the record is cleared again, so the backend stays usable. No reference counterpart. */
+spyb_status spyb_prefill_selftest_wait_timeout(spyb_backend *backend, uint64_t limit_ns, int32_t *error_code_out);
+
 /* ---- whole-model path: the graph LLAMAModel::build_graph emits (model/src/llm/model/llama.cpp:86-264)
  * executed as a fixed plan of fused kernels. */
 typedef struct {

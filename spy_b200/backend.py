@@ -106,6 +106,7 @@ def lib():
         "spyb_model_tap_xq": (i32, [vp, vp]),
         "spyb_matmul_noalloc": (i32, [vp, i32, vp, i64, i64, vp, i64, vp]),
         "spyb_prefill_matmul": (i32, [vp, i32, vp, i64, i64, vp, i64, vp, C.c_float, vp]),
+        "spyb_prefill_selftest_wait_timeout": (i32, [vp, u64, C.POINTER(i32)]),
         "spyb_model_tp_export": (i32, [vp, vp]),
         "spyb_model_tp_import": (i32, [vp, vp]),
         "spyb_model_read_timeline": (i32, [vp, vp, i32]),
@@ -288,6 +289,12 @@ class B200Backend:
         self._check(self._l.spyb_prefill_matmul(self.h, weight_type, _np_ptr(w_rows), n_rows, k, _np_ptr(x), t, None if nw is None else _np_ptr(nw),
                                                 C.c_float(eps), _np_ptr(out)))
         return out
+
+    def prefill_selftest_wait_timeout(self, limit_ns: int) -> int:
+        """Runs the prompt kernel with one batch withheld; returns the code of the wait that gave up (4, 5 or 6)."""
+        code = C.c_int32(0)
+        self._check(self._l.spyb_prefill_selftest_wait_timeout(self.h, limit_ns, C.byref(code)))
+        return int(code.value)
 
     def attention(self, q16: np.ndarray, k_cache16: np.ndarray, v_cache_t16: np.ndarray, pos0: int, n_head: int, head_dim: int, n_ctx: int,
                   n_total: int = 0) -> np.ndarray:

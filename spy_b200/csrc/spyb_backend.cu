@@ -462,6 +462,39 @@ spyb_status spyb_prefill_matmul(spyb_backend *be, int32_t weight_type, const voi
     return SPYB_SUCCESS;
 }
 
+// Failure-path check of the prompt GEMM that faults nothing: one small launch whose copy thread leaves the second batch of
+// blocks out, with `limit_ns` as the bound of every wait. The roles that wait for that batch give up one after the other,
+// the kernel frees its tensor memory and returns, and the error word holds a code of the prompt kernel (4, 5 or 6).
+spyb_status spyb_prefill_selftest_wait_timeout(spyb_backend *be, uint64_t limit_ns, int32_t *error_code_out) {
+    if (be == nullptr || limit_ns == 0) { return SPYB_FAIL; }
+    cudaSetDevice(be->config.device_id);
+    SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+    if (be->device_error()) { return SPYB_FAIL; }
+    const int nb = 12, T = PF_TOK;
+    const size_t wbytes = prefill_weight_bytes(SPYB_Q8_0, PF_ROWS, nb), ybytes = prefill_act_bytes(T, nb);
+    uint8_t *w = nullptr, *yq = nullptr; float *out = nullptr;
+    auto release = [&]() { cudaFree(w); cudaFree(yq); cudaFree(out); };
+    cudaError_t err = cudaMalloc(&w, wbytes);
+    if (err == cudaSuccess) { err = cudaMalloc(&yq, ybytes); }
+    if (err == cudaSuccess) { err = cudaMalloc(&out, (size_t)T * PF_ROWS * 4); }
+    if (err == cudaSuccess) { err = cudaMemsetAsync(w, 0, wbytes, be->stream); }
+    if (err == cudaSuccess) { err = cudaMemsetAsync(yq, 0, ybytes, be->stream); }
+    if (err == cudaSuccess) {
+        PrefillGemm g;
+        g.w = w; g.type = SPYB_Q8_0; g.n_rows = PF_ROWS; g.nb = nb; g.yq = yq; g.T = T; g.out = out; g.out_stride = PF_ROWS;
+        g.error_flag = be->d_error_flag; g.wait_limit_ns = limit_ns; g.selftest_skip_batch = 1;
+        err = launch_prefill_gemm(g, be->stream);
+    }
+    if (err == cudaSuccess) { err = cudaStreamSynchronize(be->stream); }   // returns: the kernel ended by itself
+    release();
+    if (err != cudaSuccess) { be->set_error("prefill selftest: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
+    const int code = *reinterpret_cast<volatile int *>(be->h_error_flag);
+    if (error_code_out != nullptr) { *error_code_out = code; }
+    *reinterpret_cast<volatile int *>(be->h_error_flag) = 0;   // the check leaves the backend usable
+    if (code < 4 || code > 6) { be->set_error("prefill selftest: expected a wait of the prompt kernel to give up (codes 4-6), got %d", code); return SPYB_FAIL; }
+    return SPYB_SUCCESS;
+}
+
 // ------------------------------------------------------------------------------------------ submit
 namespace {
 

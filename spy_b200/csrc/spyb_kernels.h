@@ -122,6 +122,7 @@ struct PrefillGemm {
     int           *error_flag = nullptr;
     uint64_t       wait_limit_ns = 1000000000ull;
     long long     *stamps = nullptr;  // profiling aid: clock stamps of CTA (0, 0), [8 roles][512 blocks][4]
+    int            selftest_skip_batch = -1;   // failure-path check: the copy thread leaves this batch out, so the waits for it run out
 };
 size_t      prefill_weight_bytes(int type, int64_t n_rows, int nb);
 size_t      prefill_act_bytes(int T, int nb);

@@ -200,6 +200,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
         if (lane == 0) {
             int issued = 0;
             for (int q = 0; q < n_batch; ++q) {
+                if (q == g.selftest_skip_batch) { issued = q + 1; continue; }   // (failure-path check: this batch never arrives)
                 if (q >= NQ && !mbar_wait_relaxed(st_free(q % NQ), (uint32_t)((q / NQ) - 1) & 1u, limit)) { pf_report(g.error_flag, 4); break; }
                 const int b0 = q * PF_BATCH, n = min(PF_BATCH, nb - b0), s0 = b0 % NS;
                 PF_STAMP(0, b0, 0);

@@ -161,6 +161,18 @@ def test_prefill_matmul_full_size_rows_sample(be, oracle):
     assert np.isfinite(got).all()
 
 
+def test_prefill_kernel_wait_runs_out_and_is_reported():
+    """A batch of blocks that is never copied: every role of the prompt kernel that waits for it gives up after the 2 ms
+    bound, the kernel returns by itself, the status names the wait, and the backend computes correctly afterwards."""
+    b = B.B200Backend(0)
+    assert b.prefill_selftest_wait_timeout(2_000_000) in (4, 5, 6)
+    w = quants.quantize((np.random.default_rng(1).standard_normal((128, 64)) * 0.02).astype(np.float32), quants.Q8_0)
+    x = np.random.default_rng(2).standard_normal((3, 64)).astype(np.float32)
+    got = b.prefill_matmul(quants.Q8_0, w, 128, 64, x)
+    assert np.isfinite(got).all() and np.abs(got).max() > 0
+    b.close()
+
+
 def test_prefill_matmul_rejects_what_does_not_fit(be):
     w = np.zeros(100 * 18, dtype=np.uint8)
     x = np.zeros((2, 32), dtype=np.float32)
