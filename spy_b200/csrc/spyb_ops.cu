@@ -294,25 +294,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
 // HBM-bound: the K rows and the V^T rows of the visible positions are read once (2 * n_kv * 128 * 2 bytes per head).
 constexpr int ATT_LONG_MIN = 1024;
 
-__global__ void __launch_bounds__(256) attn_scores_kernel(const AttnParams p) {
-    __shared__ __align__(16) float qf[ATT_HD];
-    const int h = blockIdx.y, t = blockIdx.z, tid = threadIdx.x;
-    pdl_launch_dependents();
-    pdl_wait();
-    const int n_vis = p.pos_base[0] + t + 1;
-    if ((int)blockIdx.x * 256 >= n_vis) { return; }
-    const int n_pad = (p.n_ctx + 3) & ~3;
-    if (tid < ATT_HD) { qf[tid] = __half2float(p.q[(int64_t)t * p.dl + (int64_t)h * ATT_HD + tid]); }
-    __syncthreads();
-    const int j = blockIdx.x * 256 + tid;
-    if (j >= n_vis) { return; }
-    uint4 kv[16];
-    {
-        const uint4 *krow = reinterpret_cast<const uint4 *>(p.k_cache + (int64_t)j * p.dl + (int64_t)h * ATT_HD);
-#pragma unroll
-        for (int a = 0; a < 16; ++a) { kv[a] = krow[a]; }
-    }
-    const float4 *q4 = reinterpret_cast<const float4 *>(qf);
+// Dot<FP16,FP16>(K row, Q) with the K row in registers (16 x 8 fp16) and Q as 128 floats in shared memory: 4 x 8
+// accumulators over elements 0..95, the reduction tree, the scalar chain over elements 96..127, tail + simd
+__device__ __forceinline__ float score_dot(const uint4 (&kv)[16], const float4 *q4) {
     float acc[4][8];
 #pragma unroll
     for (int a = 0; a < 4; ++a) {
@@ -347,7 +331,55 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnParams p) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) { tail = fmaf(kf[e], qv[e], tail); }
     }
-    p.scratch[((int64_t)t * p.n_head + h) * n_pad + j] = __fadd_rn(tail, simd);
+    return __fadd_rn(tail, simd);
+}
+
+__global__ void __launch_bounds__(256) attn_scores_kernel(const AttnParams p) {
+    __shared__ __align__(16) float qf[ATT_HD];
+    const int h = blockIdx.y, t = blockIdx.z, tid = threadIdx.x;
+    pdl_launch_dependents();
+    pdl_wait();
+    const int n_vis = p.pos_base[0] + t + 1;
+    if ((int)blockIdx.x * 256 >= n_vis) { return; }
+    const int n_pad = (p.n_ctx + 3) & ~3;
+    if (tid < ATT_HD) { qf[tid] = __half2float(p.q[(int64_t)t * p.dl + (int64_t)h * ATT_HD + tid]); }
+    __syncthreads();
+    const int j = blockIdx.x * 256 + tid;
+    if (j >= n_vis) { return; }
+    uint4 kv[16];
+    {
+        const uint4 *krow = reinterpret_cast<const uint4 *>(p.k_cache + (int64_t)j * p.dl + (int64_t)h * ATT_HD);
+#pragma unroll
+        for (int a = 0; a < 16; ++a) { kv[a] = krow[a]; }
+    }
+    p.scratch[((int64_t)t * p.n_head + h) * n_pad + j] = score_dot(kv, reinterpret_cast<const float4 *>(qf));
+}
+
+// The same for a prompt: ATT_TT consecutive tokens per CTA share the K rows, which stay in the threads' registers while
+// the tokens are walked (the K cache is then read once per ATT_TT tokens instead of once per token)
+constexpr int ATT_TT = 8;
+__global__ void __launch_bounds__(256) attn_scores_tiled_kernel(const AttnParams p) {
+    __shared__ __align__(16) float qf[ATT_TT][ATT_HD];
+    const int h = blockIdx.y, t0 = blockIdx.z * ATT_TT, tid = threadIdx.x;
+    const int nt = min(ATT_TT, p.T - t0);
+    const int n_vis_last = p.pos_base[0] + t0 + nt;          // positions the last token of the tile sees
+    if ((int)blockIdx.x * 256 >= n_vis_last) { return; }
+    const int n_pad = (p.n_ctx + 3) & ~3;
+    for (int i = tid; i < nt * ATT_HD; i += 256) { qf[i / ATT_HD][i % ATT_HD] = __half2float(p.q[(int64_t)(t0 + i / ATT_HD) * p.dl + (int64_t)h * ATT_HD + i % ATT_HD]); }
+    __syncthreads();
+    const int j = blockIdx.x * 256 + tid;
+    if (j >= n_vis_last) { return; }
+    uint4 kv[16];
+    {
+        const uint4 *krow = reinterpret_cast<const uint4 *>(p.k_cache + (int64_t)j * p.dl + (int64_t)h * ATT_HD);
+#pragma unroll
+        for (int a = 0; a < 16; ++a) { kv[a] = krow[a]; }
+    }
+#pragma unroll 1
+    for (int tt = 0; tt < nt; ++tt) {
+        if (j > p.pos_base[0] + t0 + tt) { continue; }       // masked for this token
+        p.scratch[((int64_t)(t0 + tt) * p.n_head + h) * n_pad + j] = score_dot(kv, reinterpret_cast<const float4 *>(qf[tt]));
+    }
 }
 
 constexpr int ATT_SM_THREADS = 1024;
@@ -446,6 +478,93 @@ __global__ void __launch_bounds__(ATT_PV_WARPS * WARP) attn_pv_kernel(const Attn
     tp_publish(p.tp, p.T);
 }
 
+// PV for a prompt: ATT_TT consecutive tokens per CTA share the V^T rows, and a warp takes ATT_EE output elements, so that a
+// probability read from shared memory serves ATT_EE products. Every token's product is the untiled kernel's (same lanes,
+// same steps, same tail); only the loads are shared.
+constexpr int ATT_EE = 4;
+__global__ void __launch_bounds__(ATT_PV_WARPS * WARP) attn_pv_tiled_kernel(const AttnParams p) {
+    extern __shared__ __align__(16) float att_smem[];
+    constexpr int PER_CTA = ATT_PV_WARPS * ATT_EE;            // output elements per CTA
+    const int per_head = ATT_HD / PER_CTA;
+    const int h = blockIdx.x / per_head, e0 = (blockIdx.x % per_head) * PER_CTA + (threadIdx.x >> 5) * ATT_EE, t0 = blockIdx.y * ATT_TT;
+    const int tid = threadIdx.x, lane = tid & 31;
+    const int nt = min(ATT_TT, p.T - t0);
+    const int n_tot = (p.pos_base[1] > 0) ? p.pos_base[1] : p.pos_base[0] + p.T;
+    const int n_pad = (p.n_ctx + 3) & ~3;
+    const int n_main = ((n_tot - 1) / 32) * 32;
+    const int vis0 = p.pos_base[0] + t0 + 1;                  // positions token t0 + tt sees: vis0 + tt
+    const int vis_last = vis0 + nt - 1;
+    // probabilities of the tile's tokens; positions a token does not see read as +0 (they leave its accumulators unchanged)
+    for (int tt = 0; tt < nt; ++tt) {
+        const float *row = p.scratch + ((int64_t)(t0 + tt) * p.n_head + h) * n_pad;
+        float *pr = att_smem + (size_t)tt * n_pad;
+        for (int j = tid; j < vis_last; j += ATT_PV_WARPS * WARP) { pr[j] = (j < vis0 + tt) ? row[j] : 0.f; }
+    }
+    __syncthreads();
+    const __half *vrow = p.v_cache + ((int64_t)h * ATT_HD + e0) * p.n_ctx;   // row e0 + ee starts ee * n_ctx further
+    float acc[ATT_TT][ATT_EE];
+#pragma unroll
+    for (int tt = 0; tt < ATT_TT; ++tt) {
+#pragma unroll
+        for (int ee = 0; ee < ATT_EE; ++ee) { acc[tt][ee] = 0.f; }
+    }
+    int j0 = 0;
+    for (; j0 + 2 * 32 <= n_main && j0 + 2 * 32 <= vis_last; j0 += 2 * 32) {   // two steps' loads in flight per element
+        float v[2][ATT_EE];
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+#pragma unroll
+            for (int ee = 0; ee < ATT_EE; ++ee) { v[s][ee] = __half2float(vrow[(int64_t)ee * p.n_ctx + j0 + 32 * s + lane]); }
+        }
+#pragma unroll
+        for (int tt = 0; tt < ATT_TT; ++tt) {
+            if (tt < nt) {
+                const float *pr = att_smem + (size_t)tt * n_pad;
+#pragma unroll
+                for (int s = 0; s < 2; ++s) {
+                    if (j0 + 32 * s < vis0 + tt) {   // (a step wholly behind the token's last position adds nothing: skipped as in the untiled kernel)
+                        const float pv = pr[j0 + 32 * s + lane];
+#pragma unroll
+                        for (int ee = 0; ee < ATT_EE; ++ee) { acc[tt][ee] = fmaf(v[s][ee], pv, acc[tt][ee]); }
+                    }
+                }
+            }
+        }
+    }
+    for (; j0 < n_main; j0 += 32) {
+        const int j = j0 + lane;
+        float v[ATT_EE];
+#pragma unroll
+        for (int ee = 0; ee < ATT_EE; ++ee) { v[ee] = (j < vis_last) ? __half2float(vrow[(int64_t)ee * p.n_ctx + j]) : 0.f; }
+#pragma unroll
+        for (int tt = 0; tt < ATT_TT; ++tt) {
+            if (tt < nt && j < vis0 + tt) {
+                const float pv = att_smem[(size_t)tt * n_pad + j];
+#pragma unroll
+                for (int ee = 0; ee < ATT_EE; ++ee) { acc[tt][ee] = fmaf(v[ee], pv, acc[tt][ee]); }
+            }
+        }
+    }
+    float vt[ATT_EE];
+#pragma unroll
+    for (int ee = 0; ee < ATT_EE; ++ee) { vt[ee] = (n_main + lane < vis_last) ? __half2float(vrow[(int64_t)ee * p.n_ctx + n_main + lane]) : 0.f; }
+#pragma unroll
+    for (int tt = 0; tt < ATT_TT; ++tt) {
+        if (tt >= nt) { break; }
+#pragma unroll
+        for (int ee = 0; ee < ATT_EE; ++ee) {
+            const float a = reduce_f16dot_lanes(acc[tt][ee]);
+            float tail = 0.f;                         // positions n_main .. n_tot-1 (at most 32): scalar chain
+#pragma unroll 1
+            for (int i = 0; i < 32; ++i) {
+                const float v = __shfl_sync(0xffffffffu, vt[ee], i);
+                if (n_main + i < vis0 + tt) { tail = fmaf(v, att_smem[(size_t)tt * n_pad + n_main + i], tail); }
+            }
+            if (lane == 0) { p.out[(int64_t)(t0 + tt) * (p.out_stride ? p.out_stride : p.dl) + (int64_t)h * ATT_HD + e0 + ee] = __fadd_rn(tail, a); }
+        }
+    }
+}
+
 static cudaError_t launch_with_pdl(const void *kernel, dim3 grid, dim3 block, size_t smem, const AttnParams &p, const LaunchCfg &cfg) {
     cudaLaunchConfig_t lc = {};
     lc.gridDim = grid; lc.blockDim = block; lc.dynamicSmemBytes = smem; lc.stream = cfg.stream;
@@ -466,7 +585,10 @@ cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
     if (p.hd != ATT_HD || p.T < 1 || p.n_ctx < 1 || (p.n_ctx & 3) || (p.dl & 7)) { return cudaErrorInvalidValue; }
     const size_t n_pad = ((size_t)p.n_ctx + 3) & ~(size_t)3;
     if (p.n_ctx > ATT_LONG_MIN && p.scratch != nullptr) {
-        cudaError_t err = launch_with_pdl(reinterpret_cast<const void *>(attn_scores_kernel), dim3((unsigned)((p.n_ctx + 255) / 256), p.n_head, p.T), dim3(256), 0, p, cfg);
+        const bool tiled = p.T >= ATT_TT && p.tp.counter == nullptr && !cfg.pdl;   // a prompt: tokens share the K rows and the V^T rows
+        cudaError_t err = tiled
+            ? launch_with_pdl(reinterpret_cast<const void *>(attn_scores_tiled_kernel), dim3((unsigned)((p.n_ctx + 255) / 256), p.n_head, (unsigned)((p.T + ATT_TT - 1) / ATT_TT)), dim3(256), 0, p, cfg)
+            : launch_with_pdl(reinterpret_cast<const void *>(attn_scores_kernel), dim3((unsigned)((p.n_ctx + 255) / 256), p.n_head, p.T), dim3(256), 0, p, cfg);
         if (err != cudaSuccess) { return err; }
         const size_t sm_smem = (n_pad + n_pad / 4) * sizeof(float) + 16;
         if (sm_smem > 200 * 1024) { return cudaErrorInvalidValue; }
@@ -474,6 +596,13 @@ cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
         if (err != cudaSuccess) { return err; }
         err = launch_with_pdl(reinterpret_cast<const void *>(attn_softmax_kernel), dim3(p.n_head, p.T), dim3(ATT_SM_THREADS), sm_smem, p, cfg);
         if (err != cudaSuccess) { return err; }
+        if (tiled && (size_t)ATT_TT * n_pad * sizeof(float) + 16 <= 200 * 1024) {
+            const size_t tsm = (size_t)ATT_TT * n_pad * sizeof(float) + 16;
+            err = allow_dynamic_smem(reinterpret_cast<const void *>(attn_pv_tiled_kernel), tsm);
+            if (err != cudaSuccess) { return err; }
+            return launch_with_pdl(reinterpret_cast<const void *>(attn_pv_tiled_kernel), dim3(p.n_head * (ATT_HD / (ATT_PV_WARPS * ATT_EE)), (unsigned)((p.T + ATT_TT - 1) / ATT_TT)),
+                                   dim3(ATT_PV_WARPS * WARP), tsm, p, cfg);
+        }
         const size_t pv_smem = n_pad * sizeof(float) + 16;
         err = allow_dynamic_smem(reinterpret_cast<const void *>(attn_pv_kernel), pv_smem);
         if (err != cudaSuccess) { return err; }

@@ -440,6 +440,23 @@ def test_fused_attention_long_rows(be, oracle, pos0, t, n_total, n_ctx):
     assert np.array_equal(bits(got), bits(want))
 
 
+@pytest.mark.parametrize("pos0,t,n_total", [(0, 11, 0), (250, 16, 0), (1200, 9, 1215), (31, 8, 40), (2030, 18, 2048)])
+def test_attention_of_a_prompt_shares_k_and_v_rows(be, oracle, pos0, t, n_total):
+    """Eight and more tokens above 1024 positions of context: tiles of eight tokens share the K rows (scores) and the V^T rows
+    (PV); every token's result must still be the oracle's bits - ragged last tiles, tiles that straddle 32- and 256-position
+    boundaries, rows that end at the context's end."""
+    rng = np.random.default_rng(pos0 + t)
+    n_head, hd, n_ctx = 2, 128, 2048
+    d = n_head * hd
+    wide = lambda n: (rng.standard_normal(n) * rng.choice([0.05, 1.0, 4.0], size=n)).astype(np.float32)
+    q16 = oracle.quantize_f16(wide(t * d)).reshape(t, d)
+    k16 = oracle.quantize_f16(wide(n_ctx * d)).reshape(n_ctx, d)
+    vt16 = oracle.quantize_f16(wide(n_ctx * d)).reshape(d, n_ctx)
+    got = be.attention(q16, k16, vt16, pos0, n_head, hd, n_ctx, n_total)
+    want = _attention_oracle(oracle, q16, k16, vt16, pos0, n_head, hd, n_ctx, n_total)
+    assert np.array_equal(bits(got), bits(want))
+
+
 def test_lookup_tables_identical_for_every_key(be, oracle):
     silu, ex = be.read_tables()
     want_silu, want_exp = oracle.tables()
