@@ -260,6 +260,18 @@ spyb_status spyb_set_wait_limit_ns(spyb_backend *backend, uint64_t ns);
  * are CTAs, with `limit_ns` as the bound. Succeeds when the kernel returned by itself and recorded code 2 (also written
  * to *error_code_out); the record is cleared again, so the model stays usable. No reference counterpart. */
 spyb_status spyb_model_selftest_wait_timeout(spyb_model *model, uint64_t limit_ns, int32_t *error_code_out);
+/* ---- batches of independent sequences (no reference counterpart: the reference decodes one sequence; the batch > 1
+ * configurations are replicas of it that share the weights, so every sequence must give the bits of a run on its own).
+ * spyb_model_set_sequences gives the model n_seq KV caches (1..64; unsharded Q4_0 / Q8_0 models); spyb_model_select_sequence
+ * makes spyb_model_eval / spyb_model_decode act on one of them (e.g. to evaluate each sequence's prompt);
+ * spyb_model_decode_batch then decodes sequences 0 .. n_seq-1 greedily in lockstep from the common position n_past
+ * (all prompts must have that length): per step the layer weights are streamed once per group of activation columns
+ * instead of once per sequence. ids_host receives [n_steps][n_seq] token ids, logits_host (optional)
+ * [n_steps][n_seq][n_vocab] floats. */
+spyb_status spyb_model_set_sequences(spyb_model *model, int32_t n_seq);
+spyb_status spyb_model_select_sequence(spyb_model *model, int32_t seq);
+spyb_status spyb_model_decode_batch(spyb_model *model, const int32_t *first_tokens, int32_t n_seq, int32_t n_past, int32_t n_steps,
+                                    int32_t *ids_host, float *logits_host);
 /* device time in milliseconds of the most recent spyb_model_decode / spyb_model_eval call,
  * measured with CUDA events on the backend's stream; number of kernels that call launched */
 float   spyb_model_last_ms(const spyb_model *model);

@@ -101,6 +101,9 @@ def lib():
         "spyb_model_init_tp": (i32, [vp, vp]),
         "spyb_model_eval": (i32, [vp, vp, i32, i32, vp]),
         "spyb_model_decode": (i32, [vp, i32, i32, i32, vp, vp]),
+        "spyb_model_set_sequences": (i32, [vp, i32]),
+        "spyb_model_select_sequence": (i32, [vp, i32]),
+        "spyb_model_decode_batch": (i32, [vp, vp, i32, i32, i32, vp, vp]),
         "spyb_model_last_ms": (C.c_float, [vp]),
         "spyb_model_last_launches": (i64, [vp]),
         "spyb_model_tap_xq": (i32, [vp, vp]),
@@ -353,6 +356,24 @@ class LlamaModel:
         logits = np.empty((n_steps, self.info.n_vocab), dtype=np.float32) if want_logits else None
         self.backend._check(self._l.spyb_model_decode(self.h, int(first_token), n_past, n_steps, _np_ptr(ids),
                                                       _np_ptr(logits) if want_logits else None))
+        return ids, logits
+
+    def set_sequences(self, n_seq: int) -> None:
+        """n_seq independent KV caches (sequences that share the weights); select_sequence picks the one eval / decode act on."""
+        self.backend._check(self._l.spyb_model_set_sequences(self.h, n_seq))
+
+    def select_sequence(self, seq: int) -> None:
+        self.backend._check(self._l.spyb_model_select_sequence(self.h, seq))
+
+    def decode_batch(self, first_tokens, n_past: int, n_steps: int, want_logits: bool = False):
+        """Greedy decoding of len(first_tokens) sequences in lockstep from the common position n_past; returns
+        (ids [n_steps, n_seq], logits [n_steps, n_seq, n_vocab] or None)."""
+        first = np.ascontiguousarray(first_tokens, dtype=np.int32)
+        n_seq = len(first)
+        ids = np.zeros((n_steps, n_seq), dtype=np.int32)
+        logits = np.empty((n_steps, n_seq, self.info.n_vocab), dtype=np.float32) if want_logits else None
+        self.backend._check(self._l.spyb_model_decode_batch(self.h, _np_ptr(first), n_seq, n_past, n_steps, _np_ptr(ids),
+                                                            _np_ptr(logits) if want_logits else None))
         return ids, logits
 
     def generate(self, prompt, n_predict: int, want_logits: bool = True):

@@ -93,6 +93,9 @@ struct MatvecParams {
     __half       *k_cache = nullptr;    // [n_ctx][dl]
     __half       *v_cache = nullptr;    // [dl][n_ctx] (transposed, as the reference keeps it)
     int           n_ctx = 0;
+    // batch of independent sequences in lockstep (seq_stride > 0): column t is sequence t - its position is *pos_base for every
+    // column, and its K / V cache lies t * seq_stride elements behind k_cache / v_cache
+    int64_t       seq_stride = 0;
     // optional tap: reference-layout Q8_0 blocks of column 0 (nb * 34 bytes)
     uint8_t      *tap_xq = nullptr;
     int          *error_flag = nullptr; // set non-zero when a bounded wait on a bulk copy ran out
@@ -130,7 +133,7 @@ cudaError_t launch_prefill_retile(int type, const uint8_t *raw, int64_t row_stri
 cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K, const float *norm_w, float eps, uint8_t *yq, cudaStream_t stream);
 cudaError_t launch_prefill_gemm(const PrefillGemm &g, cudaStream_t stream);
 cudaError_t launch_prefill_qkv_post(const float *qkv, int T, int dl, int hd, const int *pos_base, const float2 *rope, __half *q_out, __half *k_cache,
-                                    __half *v_cache, int n_ctx, cudaStream_t stream);
+                                    __half *v_cache, int n_ctx, int64_t seq_stride, cudaStream_t stream);
 cudaError_t launch_prefill_silu_mul(const float *upgate, int T, int F, const float *silu_table, float *act, cudaStream_t stream);
 
 struct AttnParams {
@@ -144,6 +147,7 @@ struct AttnParams {
     float        *scratch = nullptr;  // [T][n_head][n_ctx] floats; needed when attention_scratch_floats() > 0 (long contexts)
     int   n_head = 0, hd = 128, dl = 0, T = 1, n_ctx = 0;
     float scale = 0.f;
+    int64_t seq_stride = 0;           // > 0: token t is sequence t of a batch in lockstep (position pos_base[0], cache t * seq_stride elements further, no other token visible)
     unsigned long long *stamps = nullptr;                           // as in MatvecParams
     TpLink tp;                                                      // producer side of the all-gather of the attention output
     int   *error_flag = nullptr;
@@ -211,6 +215,8 @@ cudaError_t launch_getrow(const uint8_t *table, int table_type, int64_t row_byte
 cudaError_t launch_matmul_f16(const Strided &w /*f16*/, const Strided &x /*f32*/, const Strided &out /*f32*/, cudaStream_t s);
 // K-quant weights (raw GGUF rows: Q4_K = 12, Q6_K = 14) times f32 activations [n_cols][k] -> out [n_cols][n_rows]
 cudaError_t launch_matmul_kquant(int type, const uint8_t *w, int64_t n_rows, int64_t k, const float *x, int64_t n_cols, float *out, cudaStream_t s);
+cudaError_t launch_argmax_embed_batch(const float *logits, int64_t n_vocab, int n_seq, int32_t *tokens, int32_t *ids_out, const uint8_t *embd, int embd_type,
+                                      int64_t d_model, float *x_out, int64_t x_stride, int *pos_counter, cudaStream_t s);
 cudaError_t launch_argmax_embed(const float *logits, int64_t n_vocab, int32_t *token_out, int32_t *history, int *pos_counter,
                                 const uint8_t *embd, int embd_type, int64_t d_model, float *x_out, const LaunchCfg &cfg);
 cudaError_t launch_embed(const int32_t *ids, int n_ids, const uint8_t *embd, int embd_type, int64_t d_model, float *x_out, cudaStream_t s);

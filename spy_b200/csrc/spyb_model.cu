@@ -147,7 +147,8 @@ struct Layer {
     DevMatrix wqkv, wo, up, gate, down;
     KqSeg     kq_q, kq_k, kq_v, kq_o, kq_up, kq_gate, kq_down;   // K-quant models (Q4_K / Q6_K): the matrices as row ranges in GGUF order
     float    *attn_norm = nullptr, *ffn_norm = nullptr;
-    __half   *k_cache = nullptr, *v_cache = nullptr;   // K [n_ctx][dl], V transposed [dl][n_ctx]
+    __half   *k_cache = nullptr, *v_cache = nullptr;   // K [n_ctx][dl], V transposed [dl][n_ctx] of the selected sequence
+    __half   *k_base = nullptr, *v_base = nullptr;     // the caches of all sequences, seq_stride elements apart (spyb_model_set_sequences)
     // the same weights in the tile layout of the tensor-core prompt kernel (spyb_prefill.cu): Wq|Wk|Wv stacked, up|gate stacked
     PfMat     pf_qkv, pf_wo, pf_ug, pf_down;
 };
@@ -199,6 +200,12 @@ struct spyb_model {
     uint8_t *pf_yq = nullptr;
     int32_t *pf_tokens = nullptr, *h_pf_tokens = nullptr;
     int     *pf_pos = nullptr, *h_pf_pos = nullptr;      // (first position, positions known to the step) per group of 8 tokens
+    // batches of independent sequences in lockstep (spyb_model_set_sequences / spyb_model_decode_batch)
+    int      n_seq = 1, cur_seq = 0;
+    int64_t  seq_stride = 0;
+    float   *logits_batch = nullptr;
+    int32_t *batch_tokens = nullptr, *batch_ids = nullptr;
+    int64_t  batch_ids_cap = 0;
     cudaGraphExec_t graph_exec = nullptr;
     cudaGraphExec_t graph_eval1 = nullptr;   // single-token spyb_model_eval: staging copies, embedding, layers, head, logits copy
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -376,7 +383,8 @@ uint64_t weights_bytes(const MatvecParams &p) {
 // Tensor parallel: Wq|Wk|Wv, attention and FFN up|gate work on this rank's heads / FFN columns; their outputs are
 // all-gathered (inside the kernels over peer memory, or by NCCL) and Wo / FFN down run replicated on the complete
 // vectors, so no f32 sum is ever split across ranks and every rank holds the single-GPU bits of the residual stream.
-spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
+// (seq0 >= 0: the T columns are sequences seq0 .. seq0 + T - 1 of a batch in lockstep, each with its own cache)
+spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches, int seq0 = -1) {
     spyb_backend *be = m->be;
     const bool pdl = be->config.use_pdl != 0;
     const LaunchCfg cfg = be->launch_cfg(pdl);
@@ -390,6 +398,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             set_weights(m, &ly, 0, p); p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = d; p.norm_w = ly.attn_norm; p.eps = m->info.rms_eps;
             p.epi = EPI_QKV_ROPE; p.pos_base = m->d_pos; p.rope_table = m->rope_table; p.hd = m->info.head_dim; p.dl = m->dl;
             p.q_out = m->q; p.k_cache = ly.k_cache; p.v_cache = ly.v_cache; p.n_ctx = m->info.n_ctx;
+            if (seq0 >= 0) { p.seq_stride = m->seq_stride; p.k_cache = ly.k_base + (int64_t)seq0 * m->seq_stride; p.v_cache = ly.v_base + (int64_t)seq0 * m->seq_stride; }
             p.tap_xq = (tap && L == 0) ? m->d_tap : nullptr;
             p.stamps = stamps(0);
             SPYB_CUDA(be, launch_matvec(p, cfg)); ++*launches;
@@ -401,6 +410,7 @@ spyb_status run_layers(spyb_model *m, int T, bool tap, int64_t *launches) {
             a.n_head = m->dl / m->info.head_dim; a.hd = m->info.head_dim; a.dl = m->dl; a.T = T; a.n_ctx = m->info.n_ctx;
             a.scale = 1.0f / std::sqrt((float)m->info.head_dim);
             a.stamps = stamps(1); a.error_flag = be->d_error_flag; a.scratch = m->att_scratch;
+            if (seq0 >= 0) { a.seq_stride = m->seq_stride; a.k_cache = ly.k_base + (int64_t)seq0 * m->seq_stride; a.v_cache = ly.v_base + (int64_t)seq0 * m->seq_stride; }
             if (fused) { tp_produce(m, a.tp, 2 * L, true); }
             SPYB_CUDA(be, launch_attention(a, cfg)); ++*launches;
             if (tp > 1 && !fused && allgather(m, m->att, T, d, m->dl, launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
@@ -464,7 +474,8 @@ spyb_status ensure_prefill_buffers(spyb_model *m) {
 //   norm + quantize -> QKV GEMM -> RoPE / KV append -> attention -> quantize -> Wo GEMM + residual
 //   -> norm + quantize -> up|gate GEMM -> up * silu(gate) -> quantize -> down GEMM + residual
 // with the arithmetic of the five fused kernels of run_layers, so that a prompt gives the same bits on either path.
-spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches) {
+// (batch: the T tokens are sequences 0 .. T-1 of a batch in lockstep, each with its own cache, all at position d_pos[0])
+spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool batch = false) {
     spyb_backend *be = m->be;
     cudaStream_t s = be->stream;
     const LaunchCfg cfg = be->launch_cfg(false);
@@ -478,10 +489,11 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches) {
     for (Layer &ly : m->layers) {
         SPYB_CUDA(be, launch_prefill_quant(m->pf_x, d, T, d, ly.attn_norm, m->info.rms_eps, m->pf_yq, s));
         SPYB_CUDA(be, gemm(ly.pf_qkv, d, m->pf_qkv, 3 * (int64_t)dl, nullptr));
-        SPYB_CUDA(be, launch_prefill_qkv_post(m->pf_qkv, T, dl, hd, m->d_pos, m->rope_table, m->pf_q, ly.k_cache, ly.v_cache, m->info.n_ctx, s));
+        __half *kc = batch ? ly.k_base : ly.k_cache, *vc = batch ? ly.v_base : ly.v_cache;
+        SPYB_CUDA(be, launch_prefill_qkv_post(m->pf_qkv, T, dl, hd, m->d_pos, m->rope_table, m->pf_q, kc, vc, m->info.n_ctx, batch ? m->seq_stride : 0, s));
         *launches += 3;
         AttnParams a;
-        a.k_cache = ly.k_cache; a.v_cache = ly.v_cache; a.out_stride = d; a.exp_table = be->d_exp_table;
+        a.k_cache = kc; a.v_cache = vc; a.out_stride = d; a.exp_table = be->d_exp_table; a.seq_stride = batch ? m->seq_stride : 0;
         a.n_head = dl / hd; a.hd = hd; a.dl = dl; a.n_ctx = m->info.n_ctx; a.scale = 1.0f / std::sqrt((float)hd); a.error_flag = be->d_error_flag;
         if (m->att_scratch == nullptr) {   // short contexts: one CTA per (head, token)
             a.q = m->pf_q; a.out = m->pf_att; a.pos_base = m->d_pos; a.T = T;
@@ -489,7 +501,8 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches) {
         } else {                           // long contexts: the chip-wide kernels on groups of tokens that fit the score scratch
             a.scratch = m->att_scratch;
             for (int t0 = 0; t0 < T; t0 += m->att_group) {
-                a.q = m->pf_q + (int64_t)t0 * dl; a.out = m->pf_att + (int64_t)t0 * d; a.pos_base = m->pf_pos + 2 * (t0 / m->att_group); a.T = std::min(m->att_group, T - t0);
+                a.q = m->pf_q + (int64_t)t0 * dl; a.out = m->pf_att + (int64_t)t0 * d; a.pos_base = batch ? m->d_pos : m->pf_pos + 2 * (t0 / m->att_group); a.T = std::min(m->att_group, T - t0);
+                if (batch) { a.k_cache = kc + (int64_t)t0 * m->seq_stride; a.v_cache = vc + (int64_t)t0 * m->seq_stride; }
                 SPYB_CUDA(be, launch_attention(a, cfg)); *launches += 3;
             }
         }
@@ -502,6 +515,15 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches) {
         SPYB_CUDA(be, gemm(ly.pf_down, ff, m->pf_x, d, m->pf_x));
         *launches += 7;
     }
+    return SPYB_SUCCESS;
+}
+
+// output norm + head on the first T columns of x -> out [T][n_vocab]
+spyb_status run_head_columns(spyb_model *m, int T, float *out, int64_t *launches) {
+    MatvecParams p;
+    set_weights(m, nullptr, 4, p); p.T = T; p.pro = PRO_NORM_QUANT; p.x = m->x; p.x_stride = m->info.d_model;
+    p.norm_w = m->output_norm; p.eps = m->info.rms_eps; p.epi = EPI_STORE; p.out = out; p.out_stride = m->info.n_vocab;
+    SPYB_CUDA(m->be, launch_matvec(p, m->be->launch_cfg(m->be->config.use_pdl != 0))); ++*launches;
     return SPYB_SUCCESS;
 }
 
@@ -752,6 +774,7 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         }
         if (st != SPYB_SUCCESS) { return fail(st); }
         if (dev_alloc(m, &ly.k_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS || dev_alloc(m, &ly.v_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
+        ly.k_base = ly.k_cache; ly.v_base = ly.v_cache;
         if (m->pf_ok) {
             spyb_status ps = upload_pf(p + "attn_q.weight", d, d, &ly.pf_qkv, 0, 3 * (int64_t)d);
             if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_k.weight", d, d, &ly.pf_qkv, d, 3 * (int64_t)d); }
@@ -766,6 +789,7 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
     }
     I.weight_bytes += (uint64_t)(2 * I.n_layer + 1) * d * 4;
     I.kv_bytes_per_token = (uint64_t)2 * I.n_layer * dl * 2;
+    m->seq_stride = (int64_t)I.n_ctx * dl;
 
     // RoPE table with the host libm, theta advanced by repeated f32 multiplication exactly as
     // OperatorRopeImpl::execute does (backend/host/operator/non-linear.cpp:282, 300-309)
@@ -1134,6 +1158,99 @@ spyb_status spyb_model_selftest_wait_timeout(spyb_model *m, uint64_t limit_ns, i
     if (error_code_out != nullptr) { *error_code_out = code; }
     *reinterpret_cast<volatile int *>(be->h_error_flag) = 0;   // the check leaves the backend usable
     if (code != 2) { be->set_error("selftest: expected the barrier wait to give up with code 2, got %d", code); return SPYB_FAIL; }
+    return SPYB_SUCCESS;
+}
+
+// ---- batches of independent sequences that share the weights (every step reads them once for all sequences)
+static void drop_graphs(spyb_model *m) {
+    if (m->graph_exec) { cudaGraphExecDestroy(m->graph_exec); m->graph_exec = nullptr; }
+    if (m->graph_eval1) { cudaGraphExecDestroy(m->graph_eval1); m->graph_eval1 = nullptr; }
+}
+
+spyb_status spyb_model_set_sequences(spyb_model *m, int32_t n_seq) {
+    if (m == nullptr) { return SPYB_FAIL; }
+    spyb_backend *be = m->be;
+    if (n_seq < 1 || n_seq > 64) { be->set_error("set_sequences: 1 to 64 sequences, got %d", n_seq); return SPYB_UNSUPPORTED; }
+    if (m->kq || m->info.tp_size != 1 || m->step_ok) { be->set_error("set_sequences: batches need an unsharded Q4_0 / Q8_0 model on the per-matrix kernels"); return SPYB_UNSUPPORTED; }
+    cudaSetDevice(be->config.device_id);
+    SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+    drop_graphs(m);
+    for (Layer &ly : m->layers) {   // fresh caches for all sequences (the previous ones stay allocated until the model is freed)
+        if (dev_alloc(m, &ly.k_base, (size_t)n_seq * m->seq_stride) != SPYB_SUCCESS || dev_alloc(m, &ly.v_base, (size_t)n_seq * m->seq_stride) != SPYB_SUCCESS) { return SPYB_FAIL; }
+        ly.k_cache = ly.k_base; ly.v_cache = ly.v_base;
+    }
+    m->n_seq = n_seq; m->cur_seq = 0;
+    if (m->logits_batch == nullptr || n_seq > 1) {
+        if (dev_alloc(m, &m->logits_batch, (size_t)n_seq * m->info.n_vocab) != SPYB_SUCCESS || dev_alloc(m, &m->batch_tokens, (size_t)n_seq) != SPYB_SUCCESS) { return SPYB_FAIL; }
+    }
+    return SPYB_SUCCESS;
+}
+
+spyb_status spyb_model_select_sequence(spyb_model *m, int32_t seq) {
+    if (m == nullptr) { return SPYB_FAIL; }
+    if (seq < 0 || seq >= m->n_seq) { m->be->set_error("select_sequence: %d of %d", seq, m->n_seq); return SPYB_FAIL; }
+    if (seq == m->cur_seq) { return SPYB_SUCCESS; }
+    cudaSetDevice(m->be->config.device_id);
+    SPYB_CUDA(m->be, cudaStreamSynchronize(m->be->stream));
+    drop_graphs(m);   // the captured steps hold the cache addresses of the sequence they were captured for
+    for (Layer &ly : m->layers) { ly.k_cache = ly.k_base + (int64_t)seq * m->seq_stride; ly.v_cache = ly.v_base + (int64_t)seq * m->seq_stride; }
+    m->cur_seq = seq;
+    return SPYB_SUCCESS;
+}
+
+spyb_status spyb_model_decode_batch(spyb_model *m, const int32_t *first_tokens, int32_t n_seq, int32_t n_past, int32_t n_steps, int32_t *ids_host,
+                                    float *logits_host) {
+    if (m == nullptr || first_tokens == nullptr || ids_host == nullptr || n_steps < 1) { return SPYB_FAIL; }
+    spyb_backend *be = m->be;
+    cudaSetDevice(be->config.device_id);
+    if (n_seq < 1 || n_seq > m->n_seq || m->logits_batch == nullptr) { be->set_error("decode_batch: %d sequences, %d prepared by spyb_model_set_sequences", n_seq, m->n_seq); return SPYB_FAIL; }
+    if (n_past < 0 || n_past + n_steps > m->info.n_ctx) { be->set_error("decode would exceed the context length (%d + %d > %d)", n_past, n_steps, m->info.n_ctx); return SPYB_FAIL; }
+    for (int c = 0; c < n_seq; ++c) { if (first_tokens[c] < 0 || first_tokens[c] >= m->info.n_vocab) { be->set_error("token id %d out of range", first_tokens[c]); return SPYB_FAIL; } }
+    const int64_t need = (int64_t)n_steps * n_seq;
+    if (need > m->batch_ids_cap) {
+        if (dev_alloc(m, &m->batch_ids, (size_t)need) != SPYB_SUCCESS) { return SPYB_FAIL; }
+        m->batch_ids_cap = need;
+    }
+    const int V = m->info.n_vocab, d = m->info.d_model;
+    const int group = std::min(TMAX, std::min(matvec_max_columns(d / 32), matvec_max_columns(m->info.n_ff / 32)));   // columns per pass through the layers
+    SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+    m->h_pos_pinned[0] = n_past; m->h_pos_pinned[1] = 0; m->h_pos_pinned[2] = ++m->epoch;
+    m->epoch += n_steps - 1;
+    SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 12, cudaMemcpyHostToDevice, be->stream));
+    SPYB_CUDA(be, cudaMemcpyAsync(m->batch_tokens, first_tokens, (size_t)n_seq * 4, cudaMemcpyHostToDevice, be->stream));
+    SPYB_CUDA(be, cudaStreamSynchronize(be->stream));   // (first_tokens may be pageable: it is consumed here)
+    int64_t launches = 0;
+    SPYB_CUDA(be, cudaEventRecord(m->ev0, be->stream));
+    const bool gemm = m->pf_ok && n_seq >= SPYB_PREFILL_MIN_TOKENS && n_seq <= m->pf_chunk;   // enough sequences to fill the tensor-core tiles
+    if (gemm && ensure_prefill_buffers(m) != SPYB_SUCCESS) { return SPYB_FAIL; }
+    for (int step = 0; step < n_steps; ++step) {
+        if (gemm) {   // the sequences of a step are the "tokens" of one GEMM pass; the head runs on groups of columns
+            SPYB_CUDA(be, launch_embed(m->batch_tokens, n_seq, m->embd, m->embd_type, d, m->pf_x, be->stream)); ++launches;
+            if (run_prefill_layers(m, n_seq, &launches, true) != SPYB_SUCCESS) { return SPYB_FAIL; }
+            for (int g0 = 0; g0 < n_seq; g0 += group) {
+                const int T = std::min(group, n_seq - g0);
+                SPYB_CUDA(be, cudaMemcpyAsync(m->x, m->pf_x + (int64_t)g0 * d, (size_t)T * d * 4, cudaMemcpyDeviceToDevice, be->stream));
+                if (run_head_columns(m, T, m->logits_batch + (int64_t)g0 * V, &launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
+            }
+        }
+        for (int g0 = 0; !gemm && g0 < n_seq; g0 += group) {
+            const int T = std::min(group, n_seq - g0);
+            SPYB_CUDA(be, launch_embed(m->batch_tokens + g0, T, m->embd, m->embd_type, d, m->x, be->stream)); ++launches;
+            if (run_layers(m, T, false, &launches, g0) != SPYB_SUCCESS) { return SPYB_FAIL; }
+            if (run_head_columns(m, T, m->logits_batch + (int64_t)g0 * V, &launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
+        }
+        SPYB_CUDA(be, launch_argmax_embed_batch(m->logits_batch, V, n_seq, m->batch_tokens, m->batch_ids + (int64_t)step * n_seq, nullptr, 0, d, nullptr, 0, m->d_pos, be->stream));
+        launches += 2;
+        if (logits_host != nullptr) {
+            SPYB_CUDA(be, cudaMemcpyAsync(logits_host + (int64_t)step * n_seq * V, m->logits_batch, (size_t)n_seq * V * 4, cudaMemcpyDeviceToHost, be->stream));
+        }
+    }
+    SPYB_CUDA(be, cudaEventRecord(m->ev1, be->stream));
+    SPYB_CUDA(be, cudaMemcpyAsync(ids_host, m->batch_ids, (size_t)need * 4, cudaMemcpyDeviceToHost, be->stream));
+    SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
+    if (be->device_error()) { return SPYB_FAIL; }
+    SPYB_CUDA(be, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+    m->last_launches = launches;
     return SPYB_SUCCESS;
 }
 

@@ -44,15 +44,16 @@ __device__ __forceinline__ void matvec_epilogue(const MatvecParams &p, int64_t r
         if (!writer) { break; }
         const int sec = (int)(row / p.dl);
         const int e   = (int)(row - (int64_t)sec * p.dl);
-        const int pos = *p.pos_base + t;
+        const int pos = *p.pos_base + (p.seq_stride ? 0 : t);          // a batch in lockstep: every column at the same position,
+        const int64_t seq_off = p.seq_stride ? (int64_t)t * p.seq_stride : 0;   // each in its own cache
         if (sec == 2) {   // V: f32 -> f16 RNE into the transposed cache [dl][n_ctx] (dup_execute, backend/host/operator/view.cpp:163-191)
-            p.v_cache[(int64_t)e * p.n_ctx + pos] = __float2half_rn(v);
+            p.v_cache[seq_off + (int64_t)e * p.n_ctx + pos] = __float2half_rn(v);
         } else {          // RoPE, mode Norm: backend/host/operator/non-linear.cpp:270-371 (rows 2i, 2i+1 rotate together)
             const float2 cs = p.rope_table[(int64_t)pos * (p.hd >> 1) + ((e % p.hd) >> 1)];
             const float x0 = (e & 1) ? partner : v, x1 = (e & 1) ? v : partner;
             const float a = (e & 1) ? __fadd_rn(__fmul_rn(x0, cs.y), __fmul_rn(x1, cs.x))
                                     : __fsub_rn(__fmul_rn(x0, cs.x), __fmul_rn(x1, cs.y));
-            __half *dst = (sec == 0) ? p.q_out + (int64_t)t * p.dl + e : p.k_cache + (int64_t)pos * p.dl + e;
+            __half *dst = (sec == 0) ? p.q_out + (int64_t)t * p.dl + e : p.k_cache + seq_off + (int64_t)pos * p.dl + e;
             *dst = __float2half_rn(a);
         }
     } break;

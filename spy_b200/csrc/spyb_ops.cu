@@ -70,13 +70,15 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
     pdl_wait();
     stamp(p.stamps, 1, false); stamp(p.stamps, 5, true);
 
-    const int pos   = p.pos_base[0] + t;
+    const bool batch = p.seq_stride != 0;        // token t = sequence t of a batch in lockstep: own cache, same position, nothing else visible
+    const __half *k_cache = p.k_cache + (batch ? (int64_t)t * p.seq_stride : 0), *v_cache = p.v_cache + (batch ? (int64_t)t * p.seq_stride : 0);
+    const int pos   = p.pos_base[0] + (batch ? 0 : t);
     const int n_vis = pos + 1;                   // causal mask: positions 0..pos are visible
     // Row length of the score matrix = all positions known to the step (past + every token of the step), as the
     // reference graph shapes it (K view [hd, n_past + n_token, H], model/src/llm/plugin/attention.cpp:207-223). Entries
     // beyond the causal limit carry mask -inf: they become exact zeros, but they still decide how std::reduce groups
     // the sum and where Dot<FP16,FP16> switches from its vector loop to the scalar tail.
-    const int n_tot = (p.pos_base[1] > 0) ? p.pos_base[1] : p.pos_base[0] + p.T;
+    const int n_tot = batch ? n_vis : (p.pos_base[1] > 0) ? p.pos_base[1] : p.pos_base[0] + p.T;
     const int n_pad = (p.n_ctx + 3) & ~3;
     float *qf = att_smem;                        // [hd] Q as f32 (exact widening of the fp16 values)
     float *sc = qf + ATT_HD;                     // [n_pad] scores, then probabilities
@@ -87,7 +89,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
     // e = tid / 2 fetches the first 32-position step and the (at most 32-position) scalar tail of its row now.
     const int n_main = ((n_tot - 1) / 32) * 32;
     const int pv_e = tid >> 1, pv_half = tid & 1;
-    const __half *vrow = p.v_cache + ((int64_t)h * ATT_HD + pv_e) * p.n_ctx;
+    const __half *vrow = v_cache + ((int64_t)h * ATT_HD + pv_e) * p.n_ctx;
     uint2 v_first[4], v_tail[8];
 #pragma unroll
     for (int a = 0; a < 4; ++a) {
@@ -102,7 +104,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
     const __half q_mine = (tid < ATT_HD) ? p.q[(int64_t)t * p.dl + (int64_t)h * ATT_HD + tid] : __float2half(0.f);
     uint4 kv[16];                                    // a whole K row in flight at once
     {
-        const uint4 *krow = reinterpret_cast<const uint4 *>(p.k_cache + (int64_t)min(tid, n_vis - 1) * p.dl + (int64_t)h * ATT_HD);
+        const uint4 *krow = reinterpret_cast<const uint4 *>(k_cache + (int64_t)min(tid, n_vis - 1) * p.dl + (int64_t)h * ATT_HD);
 #pragma unroll
         for (int a = 0; a < 16; ++a) { kv[a] = krow[a]; }
     }
@@ -111,7 +113,7 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_kernel(const AttnParams
 
     // ---- scores of the visible positions: one thread per position
     for (int j = tid; j < n_vis; j += ATT_THREADS) {
-        const uint4  *krow = reinterpret_cast<const uint4 *>(p.k_cache + (int64_t)j * p.dl + (int64_t)h * ATT_HD);
+        const uint4  *krow = reinterpret_cast<const uint4 *>(k_cache + (int64_t)j * p.dl + (int64_t)h * ATT_HD);
         const float4 *q4   = reinterpret_cast<const float4 *>(qf);
         float acc[4][8];
         if (j != tid) {
@@ -339,7 +341,8 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnParams p) {
     const int h = blockIdx.y, t = blockIdx.z, tid = threadIdx.x;
     pdl_launch_dependents();
     pdl_wait();
-    const int n_vis = p.pos_base[0] + t + 1;
+    const bool batch = p.seq_stride != 0;
+    const int n_vis = p.pos_base[0] + (batch ? 0 : t) + 1;
     if ((int)blockIdx.x * 256 >= n_vis) { return; }
     const int n_pad = (p.n_ctx + 3) & ~3;
     if (tid < ATT_HD) { qf[tid] = __half2float(p.q[(int64_t)t * p.dl + (int64_t)h * ATT_HD + tid]); }
@@ -348,7 +351,7 @@ __global__ void __launch_bounds__(256) attn_scores_kernel(const AttnParams p) {
     if (j >= n_vis) { return; }
     uint4 kv[16];
     {
-        const uint4 *krow = reinterpret_cast<const uint4 *>(p.k_cache + (int64_t)j * p.dl + (int64_t)h * ATT_HD);
+        const uint4 *krow = reinterpret_cast<const uint4 *>(p.k_cache + (batch ? (int64_t)t * p.seq_stride : 0) + (int64_t)j * p.dl + (int64_t)h * ATT_HD);
 #pragma unroll
         for (int a = 0; a < 16; ++a) { kv[a] = krow[a]; }
     }
@@ -390,8 +393,9 @@ __global__ void __launch_bounds__(ATT_SM_THREADS) attn_softmax_kernel(const Attn
     const int h = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     pdl_launch_dependents();
     pdl_wait();
-    const int n_vis = p.pos_base[0] + t + 1;
-    const int n_tot = (p.pos_base[1] > 0) ? p.pos_base[1] : p.pos_base[0] + p.T;
+    const bool batch = p.seq_stride != 0;
+    const int n_vis = p.pos_base[0] + (batch ? 0 : t) + 1;
+    const int n_tot = batch ? n_vis : (p.pos_base[1] > 0) ? p.pos_base[1] : p.pos_base[0] + p.T;
     const int n_pad = (p.n_ctx + 3) & ~3;
     float *sc = att_smem, *gs = sc + n_pad;
     float *row = p.scratch + ((int64_t)t * p.n_head + h) * n_pad;
@@ -442,8 +446,9 @@ __global__ void __launch_bounds__(ATT_PV_WARPS * WARP) attn_pv_kernel(const Attn
     const int tid = threadIdx.x, lane = tid & 31;
     pdl_launch_dependents();
     pdl_wait();
-    const int n_vis = p.pos_base[0] + t + 1;
-    const int n_tot = (p.pos_base[1] > 0) ? p.pos_base[1] : p.pos_base[0] + p.T;
+    const bool batch = p.seq_stride != 0;
+    const int n_vis = p.pos_base[0] + (batch ? 0 : t) + 1;
+    const int n_tot = batch ? n_vis : (p.pos_base[1] > 0) ? p.pos_base[1] : p.pos_base[0] + p.T;
     const int n_pad = (p.n_ctx + 3) & ~3;
     const int n_main = ((n_tot - 1) / 32) * 32;
     float *pr = att_smem;
@@ -452,7 +457,7 @@ __global__ void __launch_bounds__(ATT_PV_WARPS * WARP) attn_pv_kernel(const Attn
     __syncthreads();
     // out[e] = Dot<FP16,FP16>(V_t[e][0..n_tot), probs); masked positions have probability +0 and leave every accumulator
     // unchanged, so they are skipped (their cache entries may not be written yet)
-    const __half *vrow = p.v_cache + ((int64_t)h * ATT_HD + e) * p.n_ctx;
+    const __half *vrow = p.v_cache + (batch ? (int64_t)t * p.seq_stride : 0) + ((int64_t)h * ATT_HD + e) * p.n_ctx;
     float acc = 0.f;
     int j0 = 0;
     for (; j0 + 8 * 32 <= n_main && j0 + 8 * 32 <= n_vis; j0 += 8 * 32) {   // eight steps' loads in flight
@@ -585,7 +590,7 @@ cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
     if (p.hd != ATT_HD || p.T < 1 || p.n_ctx < 1 || (p.n_ctx & 3) || (p.dl & 7)) { return cudaErrorInvalidValue; }
     const size_t n_pad = ((size_t)p.n_ctx + 3) & ~(size_t)3;
     if (p.n_ctx > ATT_LONG_MIN && p.scratch != nullptr) {
-        const bool tiled = p.T >= ATT_TT && p.tp.counter == nullptr && !cfg.pdl;   // a prompt: tokens share the K rows and the V^T rows
+        const bool tiled = p.T >= ATT_TT && p.tp.counter == nullptr && !cfg.pdl && p.seq_stride == 0;   // a prompt: tokens share the K rows and the V^T rows
         cudaError_t err = tiled
             ? launch_with_pdl(reinterpret_cast<const void *>(attn_scores_tiled_kernel), dim3((unsigned)((p.n_ctx + 255) / 256), p.n_head, (unsigned)((p.T + ATT_TT - 1) / ATT_TT)), dim3(256), 0, p, cfg)
             : launch_with_pdl(reinterpret_cast<const void *>(attn_scores_kernel), dim3((unsigned)((p.n_ctx + 255) / 256), p.n_head, p.T), dim3(256), 0, p, cfg);
@@ -1096,6 +1101,63 @@ cudaError_t launch_argmax_embed(const float *logits, int64_t n_vocab, int32_t *t
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
     return cudaLaunchKernelEx(&lc, argmax_embed_kernel, logits, n_vocab, token_out, history, pos_counter, embd, embd_type, d_model, x_out);
+}
+
+// Greedy sampling for a batch of sequences in lockstep: block c takes the logits of sequence c, writes its token (for the next
+// step's embedding gather and into ids_out[step][c]) and gathers the embedding into column c of x. The position is advanced
+// by advance_pos_kernel afterwards (one word for the whole batch).
+__global__ void __launch_bounds__(1024) argmax_embed_batch_kernel(const float *logits, int64_t n_vocab, int32_t *tokens, int32_t *ids_out,
+                                                                 const uint8_t *embd, int embd_type, int64_t d_model, float *x_out, int64_t x_stride) {
+    __shared__ float bv[32];
+    __shared__ int   bi[32];
+    __shared__ int   winner;
+    const int c = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float *row_logits = logits + (int64_t)c * n_vocab;
+    float best = -CUDART_INF_F; int idx = 0x7fffffff;
+    for (int64_t i = tid; i < n_vocab; i += blockDim.x) {
+        const float v = row_logits[i];
+        if (v > best || (v == best && (int)i < idx)) { best = v; idx = (int)i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int   oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+    }
+    if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        best = (lane < (int)(blockDim.x >> 5)) ? bv[lane] : -CUDART_INF_F;
+        idx  = (lane < (int)(blockDim.x >> 5)) ? bi[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int   oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+        }
+        if (lane == 0) {
+            if (idx == 0x7fffffff) { idx = 0; }   // all-NaN row: the CPU's max_element returns the first element
+            winner = idx;
+            tokens[c] = idx;
+            ids_out[c] = idx;
+        }
+    }
+    __syncthreads();
+    if (embd != nullptr && x_out != nullptr) {
+        const int64_t rb = embd_type == 0 ? d_model * 4 : embd_type == 1 ? d_model * 2 : embd_type == 8 ? d_model / 32 * 34 : d_model / 32 * 18;
+        const uint8_t *row = embd + (int64_t)winner * rb;
+        for (int64_t i = tid; i < d_model; i += blockDim.x) { x_out[(int64_t)c * x_stride + i] = embd_value(row, embd_type, i); }
+    }
+}
+__global__ void advance_pos_kernel(int *pos_counter) { pos_counter[0] += 1; pos_counter[2] += 1; }
+
+cudaError_t launch_argmax_embed_batch(const float *logits, int64_t n_vocab, int n_seq, int32_t *tokens, int32_t *ids_out, const uint8_t *embd, int embd_type,
+                                      int64_t d_model, float *x_out, int64_t x_stride, int *pos_counter, cudaStream_t s) {
+    argmax_embed_batch_kernel<<<n_seq, 1024, 0, s>>>(logits, n_vocab, tokens, ids_out, embd, embd_type, d_model, x_out, x_stride);
+    cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) { return err; }
+    advance_pos_kernel<<<1, 1, 0, s>>>(pos_counter);
+    return cudaGetLastError();
 }
 
 }  // namespace spyb

@@ -440,14 +440,15 @@ __global__ void prefill_retile_kernel(const uint8_t *raw, int64_t row_stride, in
 // RoPE(Q, K) + fp16 stores of Q / K / V after the QKV GEMM (the arithmetic of the mat-vec epilogue EPI_QKV_ROPE:
 // backend/host/operator/non-linear.cpp:270-371, view.cpp:163-191). One thread per pair of neighbouring elements.
 __global__ void prefill_qkv_post_kernel(const float *qkv, int T, int dl, int hd, const int *pos_base, const float2 *rope, __half *q_out, __half *k_cache,
-                                        __half *v_cache, int n_ctx) {
+                                        __half *v_cache, int n_ctx, int64_t seq_stride) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int64_t per_token = 3 * (int64_t)dl / 2;
     if (i >= per_token * T) { return; }
     const int t = (int)(i / per_token);
     const int64_t col = 2 * (i - (int64_t)t * per_token);
     const int sec = (int)(col / dl), e = (int)(col - (int64_t)sec * dl);
-    const int pos = *pos_base + t;
+    const int pos = *pos_base + (seq_stride ? 0 : t);   // (seq_stride > 0: token t is sequence t of a batch in lockstep, with its own cache)
+    k_cache += seq_stride ? (int64_t)t * seq_stride : 0; v_cache += seq_stride ? (int64_t)t * seq_stride : 0;
     const float2 x = *reinterpret_cast<const float2 *>(qkv + (int64_t)t * 3 * dl + col);
     if (sec == 2) {
         v_cache[(int64_t)e * n_ctx + pos] = __float2half_rn(x.x);
@@ -513,9 +514,9 @@ cudaError_t launch_prefill_gemm(const PrefillGemm &g, cudaStream_t stream) {
 }
 
 cudaError_t launch_prefill_qkv_post(const float *qkv, int T, int dl, int hd, const int *pos_base, const float2 *rope, __half *q_out, __half *k_cache,
-                                    __half *v_cache, int n_ctx, cudaStream_t stream) {
+                                    __half *v_cache, int n_ctx, int64_t seq_stride, cudaStream_t stream) {
     const int64_t n = 3 * (int64_t)dl / 2 * T;
-    prefill_qkv_post_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(qkv, T, dl, hd, pos_base, rope, q_out, k_cache, v_cache, n_ctx);
+    prefill_qkv_post_kernel<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(qkv, T, dl, hd, pos_base, rope, q_out, k_cache, v_cache, n_ctx, seq_stride);
     return cudaGetLastError();
 }
 

@@ -173,6 +173,41 @@ def test_prompt_widths_the_gemm_tile_does_not_divide(be, oracle, tmp_models):
     m.close()
 
 
+@pytest.mark.parametrize("n_seq,n_ctx", [(3, 64), (8, 64), (6, 1100), (20, 64), (17, 1100)])
+def test_batch_of_sequences_equals_single_sequence_runs(n_seq, n_ctx, oracle, tmp_models):
+    """Independent sequences that share the weights and advance in lockstep: every sequence must give the ids and the
+    logits of a run on its own (the batch > 1 configurations are replicas of the single-sequence reference). Prompts of
+    one length, different contents; 3 sequences = one group of activation columns, 8 and 6 = two groups; 16 and more go
+    through the tensor-core GEMM kernels as the tokens of one pass; a context above 1024 positions takes the three-kernel
+    attention."""
+    cfg = gguf_io.LlamaConfig(n_layer=2, d_model=256, n_head=2, n_ff=512, n_vocab=400, weight_std=0.06)
+    path = str(tmp_models / "batch.gguf")
+    if not os.path.exists(path):
+        gguf_io.make_llama_gguf(path, cfg, seed=61)
+    rng = np.random.default_rng(n_seq)
+    n_prompt, n_steps = 19, 9
+    prompts = [rng.integers(3, cfg.n_vocab, size=n_prompt) for _ in range(n_seq)]
+    want = [oracle.OracleLlama(path, n_ctx=n_ctx).generate(p, n_steps + 1) for p in prompts]
+    b = B.B200Backend(0)
+    m = B.LlamaModel(b, path, n_ctx=n_ctx)
+    m.set_sequences(n_seq)
+    first = []
+    for c, p in enumerate(prompts):
+        m.select_sequence(c)
+        lg = m.eval(p, 0)
+        assert np.array_equal(lg.view(np.uint32), want[c][1][0].view(np.uint32))
+        first.append(int(np.argmax(lg)))
+    ids, logits = m.decode_batch(first, n_prompt, n_steps, want_logits=True)
+    for c in range(n_seq):
+        assert first[c] == want[c][0][0] and np.array_equal(ids[:, c], want[c][0][1:]), c
+        assert np.array_equal(np.ascontiguousarray(logits[:, c]).view(np.uint32), want[c][1][1:].view(np.uint32)), c
+    # a single sequence continues from the batch's caches with the single-sequence entry point
+    m.select_sequence(n_seq - 1)
+    nxt = m.eval(np.array([ids[-1, n_seq - 1]], dtype=np.int32), n_prompt + n_steps)
+    assert np.isfinite(nxt).all()
+    m.close(); b.close()
+
+
 def test_long_context_attention(be, oracle, tmp_models):
     """A 600-token prompt in a 1024-token context: many 32-wide accumulator steps and ragged tails in both
     attention products."""
