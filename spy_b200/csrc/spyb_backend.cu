@@ -411,14 +411,16 @@ spyb_status spyb_matmul_noalloc(spyb_backend *be, int32_t weight_type, const voi
 spyb_status spyb_prefill_matmul(spyb_backend *be, int32_t weight_type, const void *w_rows_host, int64_t n_rows, int64_t k, const float *x_host,
                                 int64_t n_cols, const float *norm_w_host, float eps, float *out_host) {
     if (be == nullptr) { return SPYB_FAIL; }
-    if (weight_type != SPYB_Q4_0 && weight_type != SPYB_Q8_0) { be->set_error("prefill_matmul: weight type %d", weight_type); return SPYB_UNSUPPORTED; }
+    const bool kq = weight_type == SPYB_Q4_K || weight_type == SPYB_Q6_K;
+    if (weight_type != SPYB_Q4_0 && weight_type != SPYB_Q8_0 && !kq) { be->set_error("prefill_matmul: weight type %d", weight_type); return SPYB_UNSUPPORTED; }
+    if (kq && k % 256 != 0) { be->set_error("prefill_matmul: K-quant rows need k a multiple of 256"); return SPYB_UNSUPPORTED; }
     if (w_rows_host == nullptr || x_host == nullptr || out_host == nullptr || n_rows < PF_ROWS || n_rows % PF_ROWS != 0 || k < QK || k % QK != 0 || k > PF_MAX_K ||
         n_cols < 1 || n_cols > 4096) {
         be->set_error("prefill_matmul: needs n_rows a multiple of %d, k a multiple of 32 up to %d, 1..4096 columns", PF_ROWS, PF_MAX_K); return SPYB_UNSUPPORTED;
     }
     cudaSetDevice(be->config.device_id);
     const int nb = (int)(k / QK), T = (int)n_cols;
-    const int64_t rb = (int64_t)nb * (weight_type == SPYB_Q4_0 ? 18 : 34);
+    const int64_t rb = kq ? (k / 256) * (weight_type == SPYB_Q4_K ? 144 : 210) : (int64_t)nb * (weight_type == SPYB_Q4_0 ? 18 : 34);
     const size_t wbytes = prefill_weight_bytes(weight_type, n_rows, nb), ybytes = prefill_act_bytes(T, nb);
     uint8_t *raw = nullptr, *w = nullptr, *yq = nullptr; float *x = nullptr, *nw = nullptr, *out = nullptr;
     auto release = [&]() { cudaFree(raw); cudaFree(w); cudaFree(yq); cudaFree(x); cudaFree(nw); cudaFree(out); };
@@ -433,7 +435,7 @@ spyb_status spyb_prefill_matmul(spyb_backend *be, int32_t weight_type, const voi
     if (err == cudaSuccess) { err = cudaMemcpyAsync(x, x_host, (size_t)T * k * 4, cudaMemcpyHostToDevice, be->stream); }
     if (err == cudaSuccess && nw != nullptr) { err = cudaMemcpyAsync(nw, norm_w_host, (size_t)k * 4, cudaMemcpyHostToDevice, be->stream); }
     if (err == cudaSuccess) { err = launch_prefill_retile(weight_type, raw, rb, n_rows, nb, w, 0, be->stream); }
-    if (err == cudaSuccess) { err = launch_prefill_quant(x, k, T, (int)k, nw, eps, yq, be->stream); }
+    if (err == cudaSuccess) { err = launch_prefill_quant(x, k, T, (int)k, nw, eps, yq, be->stream, kq); }
     if (err == cudaSuccess) {
         PrefillGemm g;
         g.w = w; g.type = weight_type; g.n_rows = n_rows; g.nb = nb; g.yq = yq; g.T = T; g.out = out; g.out_stride = n_rows;

@@ -111,10 +111,13 @@ struct MatvecParams {
 // activations as compact Q8_0 blocks grouped by (tile of PF_TOK tokens, block).
 constexpr int PF_ROWS = 128, PF_TOK = 16;
 constexpr int PF_YQ_BYTES = PF_TOK * 32 + PF_TOK * 4;
+constexpr int PF_KQ_TOK = 64;                                   // K-quant kernels: 64 tokens per tile, two columns of D per token
+constexpr int PF_KQ_YQ_BYTES = PF_KQ_TOK * 32 + PF_KQ_TOK * 8;   // 64 x 32 s8, 64 f32 scales, 64 f32 block sums
+constexpr int PF_KQ_WTILE = 128 * 32 + 128 * 8;                 // the s8 A operand of a 32-element block, then two f32 scale products per row
 constexpr int PF_MAX_K = 14336;   // widest activation row the quantizer kernel holds in registers
 struct PrefillGemm {
     const uint8_t *w = nullptr;       // [n_rows / PF_ROWS][nb] weight tiles (launch_prefill_retile)
-    int            type = 0;          // 2 = Q4_0, 8 = Q8_0
+    int            type = 0;          // 2 = Q4_0, 8 = Q8_0, 12 = Q4_K, 14 = Q6_K
     int64_t        n_rows = 0;        // multiple of PF_ROWS
     int            nb = 0;            // blocks per row
     const uint8_t *yq = nullptr;      // [ceil(T / PF_TOK)][nb][PF_YQ_BYTES] (launch_prefill_quant)
@@ -130,7 +133,9 @@ struct PrefillGemm {
 size_t      prefill_weight_bytes(int type, int64_t n_rows, int nb);
 size_t      prefill_act_bytes(int T, int nb);
 cudaError_t launch_prefill_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0, cudaStream_t stream);
-cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K, const float *norm_w, float eps, uint8_t *yq, cudaStream_t stream);
+cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K, const float *norm_w, float eps, uint8_t *yq, cudaStream_t stream, bool kq_layout = false);
+cudaError_t launch_prefill_gemm_kq(const PrefillGemm &g, cudaStream_t stream);   // type 12 = Q4_K, 14 = Q6_K (spyb_prefill_kq.cu)
+cudaError_t launch_prefill_retile_kq(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0, cudaStream_t stream);
 cudaError_t launch_prefill_gemm(const PrefillGemm &g, cudaStream_t stream);
 cudaError_t launch_prefill_qkv_post(const float *qkv, int T, int dl, int hd, const int *pos_base, const float2 *rope, __half *q_out, __half *k_cache,
                                     __half *v_cache, int n_ctx, int64_t seq_stride, cudaStream_t stream);

@@ -17,8 +17,7 @@
 // accumulators per thread. Operands reach shared memory by cp.async.bulk (weights in a 128-row x 1-block tile layout
 // made at upload, activations as compact Q8_0 blocks); the epilogue warps also expand them into the canonical K-major
 // no-swizzle operand layout (core matrices of 8 rows x 16 bytes) ahead of the MMA. Every wait is bounded.
-#include "spyb_common.cuh"
-#include "spyb_kernels.h"
+#include "spyb_tc.cuh"
 
 #include <algorithm>
 
@@ -26,96 +25,11 @@ namespace spyb {
 
 namespace {
 
-constexpr int PF_M           = PF_ROWS;            // weight rows per CTA = M of the MMA
 constexpr int PF_N           = 8 * PF_TOK;         // 8 accumulator columns per token
-constexpr int PF_TILE        = PF_M * 32;          // bytes of one s8 operand tile
-constexpr int PF_EPI_WARPS   = 8;                  // epilogue warps: (row quadrant 0..3) x (8 tokens of the 16); 12 warps in all leave them 168 registers
-constexpr int PF_BATCH       = 4;                  // blocks per batch: the unit of the copies, of the expansion and of stage reuse
-constexpr int PF_RING        = 4;                  // batches in the shared-memory rings
-constexpr int PF_STAGES      = PF_RING * PF_BATCH; // blocks in the rings
+static_assert(PF_N == PF_NCOL, "16 tokens x 8 accumulators fill the MMA's columns");
 constexpr int PF_WTILE       = PF_TILE + 256;      // a weight tile in HBM: the s8 A operand of 128 rows x 32, then 128 fp16 block scales
-constexpr int PF_MMA_WARPS   = 2;                  // warps whose first thread issues the MMAs of every PF_MMA_WARPS-th block
-constexpr int PF_THREADS     = (PF_EPI_WARPS + 2 + PF_MMA_WARPS) * 32;   // + the copy warp and the expander warp
-constexpr int PF_DBUF        = 4;                  // accumulator buffers in tensor memory, PF_N columns each (512 columns = all of it)
 constexpr int PF_QUANT_THREADS = 512;
 constexpr int PF_QUANT_GROUPS  = PF_MAX_K / (4 * PF_QUANT_THREADS);   // float4 groups per thread
-
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void sts128(uint32_t addr, uint4 v) {
-    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-__device__ __forceinline__ void sts32(uint32_t addr, uint32_t v) { asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory"); }
-__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
-    uint32_t v;
-    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
-    uint16_t v;
-    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// shared-memory operand descriptor: K-major, no swizzle; element (row r, byte k) of the tile lies at
-// (r / 8) * 256 + (k / 16) * 128 + (r % 8) * 16 + k % 16: leading (K-chunk) offset 128, stride (8-row group) offset 256
-__device__ __forceinline__ uint64_t operand_desc(uint32_t smem_addr) {
-    return (uint64_t)((smem_addr & 0x3FFFFu) >> 4) | ((uint64_t)(128u >> 4) << 16) | ((uint64_t)(256u >> 4) << 32) | (1ull << 46);
-}
-// instruction descriptor: D s32, A and B s8 K-major, N = 128, M = 128
-constexpr uint32_t PF_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(PF_N >> 3) << 17) | ((uint32_t)(PF_M >> 4) << 24);
-
-__device__ __forceinline__ void mma_s8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc) {
-    const uint32_t zero = 0, accumulate = 1;   // D += A B^T: D holds the offset pattern
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(PF_IDESC), "r"(accumulate), "r"(zero) : "memory");
-}
-__device__ __forceinline__ void mma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t *r) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
-                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// the same 32-bit word into 32 consecutive columns of this thread's lane
-__device__ __forceinline__ void tmem_st32_same(uint32_t taddr, uint32_t v) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-                 "{%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(taddr), "r"(v) : "memory");
-}
-// 16 consecutive columns of this thread's lane from 16 registers (callers keep a register set that holds the offset
-// pattern alive across the loop, so that no copies are made per store)
-__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *v) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
-                   "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// feeder roles (copy, expansion, MMA issue) run ahead of the epilogue: their waits back off instead of competing with the
-// epilogue warps for issue slots
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, uint64_t limit_ns) {
-    if (mbar_try_wait(bar, parity)) { return true; }
-    const uint64_t t0 = global_timer_ns();
-    for (;;) {
-        __nanosleep(100);
-        if (mbar_try_wait(bar, parity)) { return true; }
-        if (global_timer_ns() - t0 > limit_ns) { return false; }
-    }
-}
-// profiling aid: clock stamps of CTA (0, 0) into g.stamps [8 roles][512 blocks][4] (nullptr: off)
-#define PF_STAMP(role, b, i) do { if (g.stamps != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && (b) < 512) { g.stamps[((role) * 512 + (b)) * 4 + (i)] = clock64(); } } while (0)
-__device__ __forceinline__ void pf_report(int *error_flag, int code) {
-    if (error_flag != nullptr) { atomicExch(error_flag, code); }
-}
 
 // ---------------------------------------------------------------------------------------------
 // the GEMM. grid = (token tiles, row tiles); one CTA per SM (it takes all 512 tensor-memory columns).
@@ -343,8 +257,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
 // activations of T tokens -> compact Q8_0 blocks grouped by (token tile, block): [T/16][nb][16 x 32 s8 | 16 f32 scales].
 // One CTA per token; RMSNorm and the quantizer as in the mat-vec prologue (NormRMS, backend/host/operator/non-linear.cpp:194-223:
 // groups of four squares formed in parallel, the running sum on one thread; Quantizator<FP32,Q8_0>, simd/vec_convert.h:178-261).
-template <bool NORM>
+// TOKT tokens per tile; YSUM: the blocks' integer sums follow the scales as floats (the K-quant kernels need them)
+template <bool NORM, int TOKT, bool YSUM>
 __global__ void __launch_bounds__(PF_QUANT_THREADS) prefill_quant_kernel(const float *x, int64_t x_stride, int K, const float *norm_w, float eps, uint8_t *yq) {
+    constexpr int YQB = TOKT * 32 + TOKT * 4 * (YSUM ? 2 : 1);
     extern __shared__ __align__(16) float v3[];
     __shared__ float scale_s;
     const int tid = threadIdx.x, token = blockIdx.x;
@@ -391,19 +307,25 @@ __global__ void __launch_bounds__(PF_QUANT_THREADS) prefill_quant_kernel(const f
             xv[k].w = __fmul_rn(__fmul_rn(xv[k].w, scale), wv[k].w);
         }
     }
-    uint8_t *tile = yq + ((int64_t)(token / PF_TOK) * nb) * PF_YQ_BYTES;
-    const int tt = token % PF_TOK;
+    uint8_t *tile = yq + ((int64_t)(token / TOKT) * nb) * YQB;
+    const int tt = token % TOKT;
 #pragma unroll
     for (int k = 0; k < PF_QUANT_GROUPS; ++k) {
         if (k < npass) {   // uniform over the CTA: the quantizer's shuffles see full warps
             const int gi = tid + k * PF_QUANT_THREADS;
             uint16_t dh; int sum;
             const uint32_t q = quantize_q8_lane4(xv[k], dh, sum);
+            if (YSUM) {   // the block's sum over its eight lanes
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1); sum += __shfl_xor_sync(0xffffffffu, sum, 2); sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+            }
             if (gi < n4) {
                 const int b = gi >> 3, w = gi & 7;
-                uint8_t *blk = tile + (int64_t)b * PF_YQ_BYTES;
+                uint8_t *blk = tile + (int64_t)b * YQB;
                 reinterpret_cast<uint32_t *>(blk + tt * 32)[w] = q;
-                if (w == 0) { reinterpret_cast<float *>(blk + PF_TOK * 32)[tt] = h2f(dh); }
+                if (w == 0) {
+                    reinterpret_cast<float *>(blk + TOKT * 32)[tt] = h2f(dh);
+                    if (YSUM) { reinterpret_cast<float *>(blk + TOKT * 32 + TOKT * 4)[tt] = (float)sum; }
+                }
             }
         }
     }
@@ -486,10 +408,11 @@ cudaError_t launch_gemm_t(const PrefillGemm &g, cudaStream_t stream) {
 
 }  // namespace
 
-size_t prefill_weight_bytes(int type, int64_t n_rows, int nb) { (void)type; return (size_t)(n_rows / PF_ROWS) * nb * PF_WTILE; }
-size_t prefill_act_bytes(int T, int nb) { return (size_t)((T + PF_TOK - 1) / PF_TOK) * nb * PF_YQ_BYTES; }
+size_t prefill_weight_bytes(int type, int64_t n_rows, int nb) { return (size_t)(n_rows / PF_ROWS) * nb * ((type == 12 || type == 14) ? PF_KQ_WTILE : PF_WTILE); }
+size_t prefill_act_bytes(int T, int nb) { return std::max((size_t)((T + PF_TOK - 1) / PF_TOK) * nb * PF_YQ_BYTES, (size_t)((T + PF_KQ_TOK - 1) / PF_KQ_TOK) * nb * PF_KQ_YQ_BYTES); }
 
 cudaError_t launch_prefill_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0, cudaStream_t stream) {
+    if (type == 12 || type == 14) { return launch_prefill_retile_kq(type, raw, row_stride, n_rows, nb, base, dst_row0, stream); }
     if ((type != 2 && type != 8) || n_rows < 1 || nb < 1) { return cudaErrorInvalidValue; }
     const int64_t n = n_rows * nb;
     const unsigned blocks = (unsigned)((n + 255) / 256);
@@ -498,15 +421,21 @@ cudaError_t launch_prefill_retile(int type, const uint8_t *raw, int64_t row_stri
     return cudaGetLastError();
 }
 
-cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K, const float *norm_w, float eps, uint8_t *yq, cudaStream_t stream) {
+cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K, const float *norm_w, float eps, uint8_t *yq, cudaStream_t stream, bool kq_layout) {
     if (T < 1 || K < 32 || (K & 31) || K > PF_MAX_K || (x_stride & 3) || ((uintptr_t)x & 15)) { return cudaErrorInvalidValue; }
     const size_t smem = norm_w != nullptr ? (size_t)K : 0;   // K / 4 floats
-    if (norm_w != nullptr) { prefill_quant_kernel<true><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq); }
-    else                   { prefill_quant_kernel<false><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq); }
+    if (kq_layout) {
+        if (norm_w != nullptr) { prefill_quant_kernel<true, PF_KQ_TOK, true><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq); }
+        else                   { prefill_quant_kernel<false, PF_KQ_TOK, true><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq); }
+    } else {
+        if (norm_w != nullptr) { prefill_quant_kernel<true, PF_TOK, false><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq); }
+        else                   { prefill_quant_kernel<false, PF_TOK, false><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq); }
+    }
     return cudaGetLastError();
 }
 
 cudaError_t launch_prefill_gemm(const PrefillGemm &g, cudaStream_t stream) {
+    if (g.type == 12 || g.type == 14) { return launch_prefill_gemm_kq(g, stream); }
     if (g.w == nullptr || g.yq == nullptr || g.out == nullptr || g.T < 1 || g.nb < 1 || g.n_rows < PF_ROWS || g.n_rows % PF_ROWS != 0) { return cudaErrorInvalidValue; }
     if (g.type == 2) { return launch_gemm_t<2>(g, stream); }
     if (g.type == 8) { return launch_gemm_t<8>(g, stream); }

@@ -147,6 +147,22 @@ def test_prefill_matmul_matches_oracle(be, oracle, qt, n, k, t, norm):
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("qt", [quants.Q4_K, quants.Q6_K])
+@pytest.mark.parametrize("n,k,t,norm", [(128, 256, 1, False), (256, 1024, 70, True), (128, 2048, 64, False), (384, 4096, 129, True), (256, 11008 - 11008 % 256, 33, False)])
+def test_prefill_matmul_k_quants_match_the_restatement(be, oracle, qt, n, k, t, norm):
+    """K-quant weights through the tensor-core prompt kernel: 1 to 43 super-blocks, ragged tiles of 64 tokens, with and without
+    the RMSNorm in front; bit-identical to the CPU restatement (the reference has no arithmetic for these types)."""
+    rng = np.random.default_rng(n + k + t + qt)
+    w = quants.quantize((rng.standard_normal((n, k)) * 0.02).astype(np.float32), qt)
+    x = rng.standard_normal((t, k)).astype(np.float32)
+    x[rng.integers(0, t, 8), rng.integers(0, k, 8)] *= 40.0
+    nw = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32) if norm else None
+    got = be.prefill_matmul(qt, w, n, k, x, nw, 1e-5)
+    xin = oracle.mul_rows(oracle.rmsnorm(x, 1e-5), nw) if norm else x
+    want = oracle.matmul(qt, w, k, n, xin)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
 def test_prefill_matmul_full_size_rows_sample(be, oracle):
     """The 7B FFN-down shape with a 512-token prompt: a row and token sample against the oracle, bit for bit."""
     n, k, t = 4096, 11008, 512
@@ -180,7 +196,7 @@ def test_prefill_matmul_rejects_what_does_not_fit(be):
         be.prefill_matmul(quants.Q4_0, w, 100, 32, x)          # rows not a multiple of 128
     assert e.value.status == B.UNSUPPORTED
     with pytest.raises(B.SpybError) as e:
-        be.prefill_matmul(quants.Q4_K, w, 128, 256, np.zeros((2, 256), dtype=np.float32))
+        be.prefill_matmul(quants.Q4_K, w, 128, 128, np.zeros((2, 128), dtype=np.float32))   # K-quant rows: k a multiple of 256
     assert e.value.status == B.UNSUPPORTED
 
 
