@@ -151,6 +151,7 @@ struct Layer {
     __half   *k_base = nullptr, *v_base = nullptr;     // the caches of all sequences, seq_stride elements apart (spyb_model_set_sequences)
     // the same weights in the tile layout of the tensor-core prompt kernel (spyb_prefill.cu): Wq|Wk|Wv stacked, up|gate stacked
     PfMat     pf_qkv, pf_wo, pf_ug, pf_down;
+    PfMat     pf_k, pf_v, pf_gate;   // K-quant models: one matrix per tensor (types differ per tensor); pf_qkv then holds Wq, pf_ug holds W_up
 };
 
 }  // namespace spyb
@@ -487,8 +488,13 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool bat
         return launch_prefill_gemm(g, s);
     };
     for (Layer &ly : m->layers) {
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, d, T, d, ly.attn_norm, m->info.rms_eps, m->pf_yq, s));
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, d, T, d, ly.attn_norm, m->info.rms_eps, m->pf_yq, s, m->kq));
         SPYB_CUDA(be, gemm(ly.pf_qkv, d, m->pf_qkv, 3 * (int64_t)dl, nullptr));
+        if (m->kq) {   // one matrix per tensor: Wk and Wv fill the other two thirds of the QKV rows
+            SPYB_CUDA(be, gemm(ly.pf_k, d, m->pf_qkv + dl, 3 * (int64_t)dl, nullptr));
+            SPYB_CUDA(be, gemm(ly.pf_v, d, m->pf_qkv + 2 * dl, 3 * (int64_t)dl, nullptr));
+            *launches += 2;
+        }
         __half *kc = batch ? ly.k_base : ly.k_cache, *vc = batch ? ly.v_base : ly.v_cache;
         SPYB_CUDA(be, launch_prefill_qkv_post(m->pf_qkv, T, dl, hd, m->d_pos, m->rope_table, m->pf_q, kc, vc, m->info.n_ctx, batch ? m->seq_stride : 0, s));
         *launches += 3;
@@ -506,12 +512,13 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool bat
                 SPYB_CUDA(be, launch_attention(a, cfg)); *launches += 3;
             }
         }
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_att, d, T, d, nullptr, 0.f, m->pf_yq, s));
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_att, d, T, d, nullptr, 0.f, m->pf_yq, s, m->kq));
         SPYB_CUDA(be, gemm(ly.pf_wo, d, m->pf_x, d, m->pf_x));
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, d, T, d, ly.ffn_norm, m->info.rms_eps, m->pf_yq, s));
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, d, T, d, ly.ffn_norm, m->info.rms_eps, m->pf_yq, s, m->kq));
         SPYB_CUDA(be, gemm(ly.pf_ug, d, m->pf_ug, 2 * (int64_t)ff, nullptr));
+        if (m->kq) { SPYB_CUDA(be, gemm(ly.pf_gate, d, m->pf_ug + ff, 2 * (int64_t)ff, nullptr)); ++*launches; }
         SPYB_CUDA(be, launch_prefill_silu_mul(m->pf_ug, T, ff, be->d_silu_table, m->pf_act, s));
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_act, ff, T, ff, nullptr, 0.f, m->pf_yq, s));
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_act, ff, T, ff, nullptr, 0.f, m->pf_yq, s, m->kq));
         SPYB_CUDA(be, gemm(ly.pf_down, ff, m->pf_x, d, m->pf_x));
         *launches += 7;
     }
@@ -639,7 +646,7 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
     auto upload_pf = [&](const std::string &name, int64_t k_full, int64_t rows_full, PfMat *into, int64_t dst_row, int64_t total_rows) {
         const GgufTensor *t; const uint8_t *data;
         if (!tensor(name, &t, &data)) { return SPYB_FAIL; }
-        if (t->ne[0] != k_full || t->ne[1] != rows_full || (t->type != SPYB_Q4_0 && t->type != SPYB_Q8_0)) { return SPYB_UNSUPPORTED; }
+        if (t->ne[0] != k_full || t->ne[1] != rows_full || (t->type != SPYB_Q4_0 && t->type != SPYB_Q8_0 && t->type != SPYB_Q4_K && t->type != SPYB_Q6_K)) { return SPYB_UNSUPPORTED; }
         const int nb = (int)(k_full / 32);
         if (into->w == nullptr) {
             if (dev_alloc(m, &into->w, prefill_weight_bytes(t->type, total_rows, nb)) != SPYB_SUCCESS) { return SPYB_FAIL; }
@@ -714,8 +721,8 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
     }
     // prompts run as GEMMs on the tensor cores when the model is unsharded, Q4_0 / Q8_0 throughout and its widths are
     // multiples of the kernel's 128-row tile (SPYB_PREFILL=0 keeps the mat-vec passes; the extra copy of the layer weights is then not made)
-    m->pf_ok = tp == 1 && !m->kq && (std::getenv("SPYB_PREFILL") == nullptr || std::atoi(std::getenv("SPYB_PREFILL")) != 0) &&
-               d % PF_ROWS == 0 && I.n_ff % PF_ROWS == 0 && d <= PF_MAX_K && I.n_ff <= PF_MAX_K;
+    m->pf_ok = tp == 1 && (std::getenv("SPYB_PREFILL") == nullptr || std::atoi(std::getenv("SPYB_PREFILL")) != 0) &&
+               d % PF_ROWS == 0 && I.n_ff % PF_ROWS == 0 && d <= PF_MAX_K && I.n_ff <= PF_MAX_K && (!m->kq || (d % 256 == 0 && I.n_ff % 256 == 0));
     if (const char *v = std::getenv("SPYB_PREFILL_CHUNK")) { const int n = std::atoi(v); if (n >= PF_TOK && n <= 4096) { m->pf_chunk = (n + TMAX - 1) / TMAX * TMAX; } }
     m->layers.resize(I.n_layer);
     for (int L = 0; L < I.n_layer; ++L) {
@@ -729,6 +736,18 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
                 (st = upload_kq(p + "ffn_up.weight", d, I.n_ff, (int64_t)r * fl, fl, &ly.kq_up)) != SPYB_SUCCESS || (st = upload_kq(p + "ffn_gate.weight", d, I.n_ff, (int64_t)r * fl, fl, &ly.kq_gate)) != SPYB_SUCCESS ||
                 (st = upload_kq(p + "ffn_down.weight", I.n_ff, d, 0, d, &ly.kq_down)) != SPYB_SUCCESS) { return fail(st); }
             if (dev_alloc(m, &ly.k_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS || dev_alloc(m, &ly.v_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
+            ly.k_base = ly.k_cache; ly.v_base = ly.v_cache;
+            if (m->pf_ok) {   // the same tensors in the tile layout of the tensor-core prompt kernel, one matrix per tensor
+                spyb_status ps = upload_pf(p + "attn_q.weight", d, d, &ly.pf_qkv, 0, d);
+                if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_k.weight", d, d, &ly.pf_k, 0, d); }
+                if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_v.weight", d, d, &ly.pf_v, 0, d); }
+                if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_output.weight", d, d, &ly.pf_wo, 0, d); }
+                if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_up.weight", d, I.n_ff, &ly.pf_ug, 0, I.n_ff); }
+                if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_gate.weight", d, I.n_ff, &ly.pf_gate, 0, I.n_ff); }
+                if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_down.weight", I.n_ff, d, &ly.pf_down, 0, d); }
+                if (ps == SPYB_FAIL) { return fail(ps); }
+                if (ps != SPYB_SUCCESS) { m->pf_ok = false; }
+            }
             continue;
         }
         // heads: rows [r*dl, (r+1)*dl) of Wq, Wk, Wv, stacked into one [3*dl, d] matrix

@@ -246,7 +246,15 @@ def test_k_quant_models_match_the_restatement(name, cfg, oracle, tmp_models):
     assert np.array_equal(np.asarray(logits, dtype=np.float32).view(np.uint32), np.asarray(want_logits, dtype=np.float32).view(np.uint32))
     ids_dev, _ = m.decode(int(ids[0]), len(prompt), 5)          # and the device-side decode loop (graph replay)
     assert np.array_equal(ids_dev, want_ids[1:])
-    m.close(); b.close()
+    m.close()
+    # a prompt long enough for the tensor-core GEMM kernels (two tiles of 64 tokens, the second ragged), then decode
+    long_prompt = np.random.default_rng(14).integers(3, c.n_vocab, size=75)
+    want_ids2, want_logits2 = oracle.OracleLlama(path, n_ctx=96).generate(long_prompt, 4)
+    m2 = B.LlamaModel(b, path, n_ctx=96)
+    ids2, logits2 = m2.generate(long_prompt, 4)
+    assert np.array_equal(ids2, want_ids2)
+    assert np.array_equal(np.asarray(logits2, dtype=np.float32).view(np.uint32), np.asarray(want_logits2, dtype=np.float32).view(np.uint32))
+    m2.close(); b.close()
 
 
 def test_unsupported_models_are_reported(be, tmp_models):
