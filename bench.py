@@ -305,7 +305,8 @@ def main():
     # ---- prompt evaluation (prefill): one eval call over a 512-token prompt (or the configuration's own, if longer) ----
     n_pre = max(N_PROMPT, min(512, N_CTX - 64))
     pre_ids = np.random.default_rng(PROMPT_SEED + 1).integers(3, info.n_vocab, size=n_pre).astype(np.int32)
-    model.eval(pre_ids[:8], 0)                                # warm
+    model.eval(pre_ids[:8], 0)                                # warm: the short-prompt path ...
+    model.eval(pre_ids, 0)                                    # ... and the long-prompt path (first use of its kernels, buffers and, sharded, NCCL connections)
     barrier(); be.sync()
     pre_logits = model.eval(pre_ids, 0).copy()
     t_pre = torch.tensor([model.last_ms], dtype=torch.float64)
@@ -314,7 +315,7 @@ def main():
     prefill = {"tokens": int(n_pre), "ms": float(t_pre[0]), "tokens_per_s": float(n_pre / (float(t_pre[0]) / 1e3)),
                "launches": int(model.last_launches),
                "note": "one spyb_model_eval over the prompt (device time, CUDA events): chunks of up to 512 tokens through the tcgen05 GEMM kernel when the "
-                       "model is unsharded Q4_0 / Q8_0 (otherwise passes of up to 8 token columns through the mat-vec kernels)"}
+                       "widths fit its tiles (sharded models: each rank its heads and FFN rows, one NCCL all-gather of the attention output and of the FFN activation per layer)"}
     barrier()
 
     # ---- device-resident arm ---------------------------------------------------------------

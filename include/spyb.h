@@ -189,7 +189,7 @@ spyb_status spyb_matmul_noalloc(spyb_backend *backend, int32_t weight_type, cons
  *   x_host      : [n_cols][k] f32; norm_w_host (optional, [k]): RMSNorm(x) * norm_w is applied first, as in front of
  *                 the QKV and FFN MatMuls of the graph (eps as in NormRMS)
  *   out_host    : [n_cols][n_rows] f32
- * Needs n_rows a multiple of 128, k a multiple of 32 (<= 14336), 1..4096 columns; anything else is SPYB_UNSUPPORTED.
+ * Needs k a multiple of 32 (256 for Q4_K / Q6_K; <= 14336) and 1..4096 columns; anything else is SPYB_UNSUPPORTED.
  * Stages everything inside the call (it allocates and synchronises): the entry point of the parity tests, while
  * spyb_model_eval runs the same kernels on resident buffers for prompts of SPYB_PREFILL_MIN_TOKENS tokens and more. */
 #define SPYB_PREFILL_MIN_TOKENS 16

@@ -414,9 +414,9 @@ spyb_status spyb_prefill_matmul(spyb_backend *be, int32_t weight_type, const voi
     const bool kq = weight_type == SPYB_Q4_K || weight_type == SPYB_Q6_K;
     if (weight_type != SPYB_Q4_0 && weight_type != SPYB_Q8_0 && !kq) { be->set_error("prefill_matmul: weight type %d", weight_type); return SPYB_UNSUPPORTED; }
     if (kq && k % 256 != 0) { be->set_error("prefill_matmul: K-quant rows need k a multiple of 256"); return SPYB_UNSUPPORTED; }
-    if (w_rows_host == nullptr || x_host == nullptr || out_host == nullptr || n_rows < PF_ROWS || n_rows % PF_ROWS != 0 || k < QK || k % QK != 0 || k > PF_MAX_K ||
+    if (w_rows_host == nullptr || x_host == nullptr || out_host == nullptr || n_rows < 1 || k < QK || k % QK != 0 || k > PF_MAX_K ||
         n_cols < 1 || n_cols > 4096) {
-        be->set_error("prefill_matmul: needs n_rows a multiple of %d, k a multiple of 32 up to %d, 1..4096 columns", PF_ROWS, PF_MAX_K); return SPYB_UNSUPPORTED;
+        be->set_error("prefill_matmul: needs k a multiple of 32 up to %d, 1..4096 columns", PF_MAX_K); return SPYB_UNSUPPORTED;
     }
     cudaSetDevice(be->config.device_id);
     const int nb = (int)(k / QK), T = (int)n_cols;
@@ -426,6 +426,7 @@ spyb_status spyb_prefill_matmul(spyb_backend *be, int32_t weight_type, const voi
     auto release = [&]() { cudaFree(raw); cudaFree(w); cudaFree(yq); cudaFree(x); cudaFree(nw); cudaFree(out); };
     cudaError_t err = cudaMalloc(&raw, (size_t)n_rows * rb + 64);
     if (err == cudaSuccess) { err = cudaMalloc(&w, wbytes); }
+    if (err == cudaSuccess) { err = cudaMemsetAsync(w, 0, wbytes, be->stream); }   // (rows that pad the last tile stay zero)
     if (err == cudaSuccess) { err = cudaMalloc(&yq, ybytes); }
     if (err == cudaSuccess) { err = cudaMalloc(&x, (size_t)T * k * 4); }
     if (err == cudaSuccess) { err = cudaMalloc(&out, (size_t)T * n_rows * 4); }

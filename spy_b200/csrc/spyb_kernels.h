@@ -118,7 +118,7 @@ constexpr int PF_MAX_K = 14336;   // widest activation row the quantizer kernel 
 struct PrefillGemm {
     const uint8_t *w = nullptr;       // [n_rows / PF_ROWS][nb] weight tiles (launch_prefill_retile)
     int            type = 0;          // 2 = Q4_0, 8 = Q8_0, 12 = Q4_K, 14 = Q6_K
-    int64_t        n_rows = 0;        // multiple of PF_ROWS
+    int64_t        n_rows = 0;        // (the last tile of PF_ROWS rows may be partly padding: zero weights, rows not stored)
     int            nb = 0;            // blocks per row
     const uint8_t *yq = nullptr;      // [ceil(T / PF_TOK)][nb][PF_YQ_BYTES] (launch_prefill_quant)
     int            T = 0;
@@ -133,7 +133,8 @@ struct PrefillGemm {
 size_t      prefill_weight_bytes(int type, int64_t n_rows, int nb);
 size_t      prefill_act_bytes(int T, int nb);
 cudaError_t launch_prefill_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0, cudaStream_t stream);
-cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K, const float *norm_w, float eps, uint8_t *yq, cudaStream_t stream, bool kq_layout = false);
+cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K, const float *norm_w, float eps, uint8_t *yq, cudaStream_t stream, bool kq_layout = false,
+                                 int part_len = 0, int64_t part_stride = 0);   // part_len > 0: a row lies in K / part_len parts, part_stride floats apart
 cudaError_t launch_prefill_gemm_kq(const PrefillGemm &g, cudaStream_t stream);   // type 12 = Q4_K, 14 = Q6_K (spyb_prefill_kq.cu)
 cudaError_t launch_prefill_retile_kq(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0, cudaStream_t stream);
 cudaError_t launch_prefill_gemm(const PrefillGemm &g, cudaStream_t stream);

@@ -480,13 +480,28 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool bat
     spyb_backend *be = m->be;
     cudaStream_t s = be->stream;
     const LaunchCfg cfg = be->launch_cfg(false);
-    const int d = m->info.d_model, ff = m->info.n_ff, dl = m->dl, hd = m->info.head_dim;
+    const int d = m->info.d_model, ff = m->info.n_ff, dl = m->dl, fl = m->fl, hd = m->info.head_dim;
+    const int tp = m->info.tp_size, rank = m->info.tp_rank;
     auto gemm = [&](const PfMat &W, int K, float *out, int64_t out_stride, const float *resid) {
         PrefillGemm g;
         g.w = W.w; g.type = W.type; g.n_rows = W.n_rows; g.nb = K / 32; g.yq = m->pf_yq; g.T = T; g.out = out; g.out_stride = out_stride; g.resid = resid;
         g.error_flag = be->d_error_flag; g.wait_limit_ns = be->wait_limit_ns;
         return launch_prefill_gemm(g, s);
     };
+    // Tensor parallel: this rank's heads and FFN rows produce their slices of the attention output and of the FFN activation
+    // for all T tokens as one contiguous part [T][dl] / [T][fl]; one NCCL all-gather per vector puts the ranks' parts side
+    // by side ([tp][T][len]), and the quantizer in front of the replicated W_o / W_down reads a token's row across the parts.
+    // No f32 sum is split across ranks, as on the single-token path.
+    auto gather = [&](float *parts, int64_t len) -> spyb_status {
+        if (tp == 1) { return SPYB_SUCCESS; }
+        if (m->nccl_comm == nullptr) { be->set_error("tensor-parallel model used before spyb_model_init_tp"); return SPYB_FAIL; }
+        const size_t count = (size_t)T * len;
+        const int rc = g_nccl.AllGather(parts + (size_t)rank * count, parts, count, /*ncclFloat32*/ 7, m->nccl_comm, s);
+        if (rc != 0) { be->set_error("ncclAllGather failed: %s", g_nccl.GetErrorString ? g_nccl.GetErrorString(rc) : "?"); return SPYB_FAIL; }
+        ++*launches;
+        return SPYB_SUCCESS;
+    };
+    float *att_part = m->pf_att + (size_t)rank * T * dl, *act_part = m->pf_act + (size_t)rank * T * fl;   // (tp == 1: the whole buffers)
     for (Layer &ly : m->layers) {
         SPYB_CUDA(be, launch_prefill_quant(m->pf_x, d, T, d, ly.attn_norm, m->info.rms_eps, m->pf_yq, s, m->kq));
         SPYB_CUDA(be, gemm(ly.pf_qkv, d, m->pf_qkv, 3 * (int64_t)dl, nullptr));
@@ -499,26 +514,28 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool bat
         SPYB_CUDA(be, launch_prefill_qkv_post(m->pf_qkv, T, dl, hd, m->d_pos, m->rope_table, m->pf_q, kc, vc, m->info.n_ctx, batch ? m->seq_stride : 0, s));
         *launches += 3;
         AttnParams a;
-        a.k_cache = kc; a.v_cache = vc; a.out_stride = d; a.exp_table = be->d_exp_table; a.seq_stride = batch ? m->seq_stride : 0;
+        a.k_cache = kc; a.v_cache = vc; a.out_stride = dl; a.exp_table = be->d_exp_table; a.seq_stride = batch ? m->seq_stride : 0;
         a.n_head = dl / hd; a.hd = hd; a.dl = dl; a.n_ctx = m->info.n_ctx; a.scale = 1.0f / std::sqrt((float)hd); a.error_flag = be->d_error_flag;
         if (m->att_scratch == nullptr) {   // short contexts: one CTA per (head, token)
-            a.q = m->pf_q; a.out = m->pf_att; a.pos_base = m->d_pos; a.T = T;
+            a.q = m->pf_q; a.out = att_part; a.pos_base = m->d_pos; a.T = T;
             SPYB_CUDA(be, launch_attention(a, cfg)); ++*launches;
         } else {                           // long contexts: the chip-wide kernels on groups of tokens that fit the score scratch
             a.scratch = m->att_scratch;
             for (int t0 = 0; t0 < T; t0 += m->att_group) {
-                a.q = m->pf_q + (int64_t)t0 * dl; a.out = m->pf_att + (int64_t)t0 * d; a.pos_base = batch ? m->d_pos : m->pf_pos + 2 * (t0 / m->att_group); a.T = std::min(m->att_group, T - t0);
+                a.q = m->pf_q + (int64_t)t0 * dl; a.out = att_part + (int64_t)t0 * dl; a.pos_base = batch ? m->d_pos : m->pf_pos + 2 * (t0 / m->att_group); a.T = std::min(m->att_group, T - t0);
                 if (batch) { a.k_cache = kc + (int64_t)t0 * m->seq_stride; a.v_cache = vc + (int64_t)t0 * m->seq_stride; }
                 SPYB_CUDA(be, launch_attention(a, cfg)); *launches += 3;
             }
         }
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_att, d, T, d, nullptr, 0.f, m->pf_yq, s, m->kq));
+        if (gather(m->pf_att, dl) != SPYB_SUCCESS) { return SPYB_FAIL; }
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_att, dl, T, d, nullptr, 0.f, m->pf_yq, s, m->kq, dl, (int64_t)T * dl));
         SPYB_CUDA(be, gemm(ly.pf_wo, d, m->pf_x, d, m->pf_x));
         SPYB_CUDA(be, launch_prefill_quant(m->pf_x, d, T, d, ly.ffn_norm, m->info.rms_eps, m->pf_yq, s, m->kq));
-        SPYB_CUDA(be, gemm(ly.pf_ug, d, m->pf_ug, 2 * (int64_t)ff, nullptr));
-        if (m->kq) { SPYB_CUDA(be, gemm(ly.pf_gate, d, m->pf_ug + ff, 2 * (int64_t)ff, nullptr)); ++*launches; }
-        SPYB_CUDA(be, launch_prefill_silu_mul(m->pf_ug, T, ff, be->d_silu_table, m->pf_act, s));
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_act, ff, T, ff, nullptr, 0.f, m->pf_yq, s, m->kq));
+        SPYB_CUDA(be, gemm(ly.pf_ug, d, m->pf_ug, 2 * (int64_t)fl, nullptr));
+        if (m->kq) { SPYB_CUDA(be, gemm(ly.pf_gate, d, m->pf_ug + fl, 2 * (int64_t)fl, nullptr)); ++*launches; }
+        SPYB_CUDA(be, launch_prefill_silu_mul(m->pf_ug, T, fl, be->d_silu_table, act_part, s));
+        if (gather(m->pf_act, fl) != SPYB_SUCCESS) { return SPYB_FAIL; }
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_act, fl, T, ff, nullptr, 0.f, m->pf_yq, s, m->kq, fl, (int64_t)T * fl));
         SPYB_CUDA(be, gemm(ly.pf_down, ff, m->pf_x, d, m->pf_x));
         *launches += 7;
     }
@@ -643,7 +660,9 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         return SPYB_SUCCESS;
     };
     // the tile layout of the tensor-core prompt kernel: rows [0, rows_full) of a tensor into rows [dst_row, ...) of a matrix of total_rows rows
-    auto upload_pf = [&](const std::string &name, int64_t k_full, int64_t rows_full, PfMat *into, int64_t dst_row, int64_t total_rows) {
+    // (rows [row0, row0 + n_rows) of the tensor; n_rows < 0: all of them)
+    auto upload_pf = [&](const std::string &name, int64_t k_full, int64_t rows_full, PfMat *into, int64_t dst_row, int64_t total_rows, int64_t row0 = 0, int64_t n_rows = -1) {
+        if (n_rows < 0) { n_rows = rows_full; }
         const GgufTensor *t; const uint8_t *data;
         if (!tensor(name, &t, &data)) { return SPYB_FAIL; }
         if (t->ne[0] != k_full || t->ne[1] != rows_full || (t->type != SPYB_Q4_0 && t->type != SPYB_Q8_0 && t->type != SPYB_Q4_K && t->type != SPYB_Q6_K)) { return SPYB_UNSUPPORTED; }
@@ -655,10 +674,10 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         const int64_t rb = GgufFile::row_bytes(t->type, k_full);
         const int64_t max_rows = std::max<int64_t>(1, (int64_t)(64u << 20) / rb);   // 64 MiB staging pieces
         void *stage = nullptr;
-        SPYB_CUDA(be, cudaMalloc(&stage, (size_t)std::min(max_rows, rows_full) * rb + 64));
-        for (int64_t r0 = 0; r0 < rows_full; r0 += max_rows) {
-            const int64_t nr = std::min(max_rows, rows_full - r0);
-            cudaError_t e = cudaMemcpyAsync(stage, data + r0 * rb, (size_t)nr * rb, cudaMemcpyHostToDevice, be->stream);
+        SPYB_CUDA(be, cudaMalloc(&stage, (size_t)std::min(max_rows, n_rows) * rb + 64));
+        for (int64_t r0 = 0; r0 < n_rows; r0 += max_rows) {
+            const int64_t nr = std::min(max_rows, n_rows - r0);
+            cudaError_t e = cudaMemcpyAsync(stage, data + (row0 + r0) * rb, (size_t)nr * rb, cudaMemcpyHostToDevice, be->stream);
             if (e == cudaSuccess) { e = launch_prefill_retile(t->type, static_cast<const uint8_t *>(stage), rb, nr, nb, into->w, dst_row + r0, be->stream); }
             if (e == cudaSuccess) { e = cudaStreamSynchronize(be->stream); }
             if (e != cudaSuccess) { cudaFree(stage); be->set_error("GGUF: %s: upload failed: %s", name.c_str(), cudaGetErrorString(e)); return SPYB_FAIL; }
@@ -721,8 +740,10 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
     }
     // prompts run as GEMMs on the tensor cores when the model is unsharded, Q4_0 / Q8_0 throughout and its widths are
     // multiples of the kernel's 128-row tile (SPYB_PREFILL=0 keeps the mat-vec passes; the extra copy of the layer weights is then not made)
-    m->pf_ok = tp == 1 && (std::getenv("SPYB_PREFILL") == nullptr || std::atoi(std::getenv("SPYB_PREFILL")) != 0) &&
-               d % PF_ROWS == 0 && I.n_ff % PF_ROWS == 0 && d <= PF_MAX_K && I.n_ff <= PF_MAX_K && (!m->kq || (d % 256 == 0 && I.n_ff % 256 == 0));
+    // (a sharded model keeps its shard of Wq|Wk|Wv and of W_up|W_gate in that layout, W_o and W_down whole: the prompt path
+    // gathers the attention output and the FFN activation of all tokens with one NCCL all-gather each per layer)
+    m->pf_ok = (std::getenv("SPYB_PREFILL") == nullptr || std::atoi(std::getenv("SPYB_PREFILL")) != 0) &&
+               d <= PF_MAX_K && I.n_ff <= PF_MAX_K && (m->kq ? (tp == 1 && d % 256 == 0 && I.n_ff % 256 == 0) : (dl % 4 == 0 && fl % 4 == 0));
     if (const char *v = std::getenv("SPYB_PREFILL_CHUNK")) { const int n = std::atoi(v); if (n >= PF_TOK && n <= 4096) { m->pf_chunk = (n + TMAX - 1) / TMAX * TMAX; } }
     m->layers.resize(I.n_layer);
     for (int L = 0; L < I.n_layer; ++L) {
@@ -795,12 +816,13 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         if (dev_alloc(m, &ly.k_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS || dev_alloc(m, &ly.v_cache, (size_t)I.n_ctx * dl) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
         ly.k_base = ly.k_cache; ly.v_base = ly.v_cache;
         if (m->pf_ok) {
-            spyb_status ps = upload_pf(p + "attn_q.weight", d, d, &ly.pf_qkv, 0, 3 * (int64_t)d);
-            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_k.weight", d, d, &ly.pf_qkv, d, 3 * (int64_t)d); }
-            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_v.weight", d, d, &ly.pf_qkv, 2 * (int64_t)d, 3 * (int64_t)d); }
+            const int64_t q0 = (int64_t)r * dl, f0 = (int64_t)r * fl;   // this rank's heads and FFN rows
+            spyb_status ps = upload_pf(p + "attn_q.weight", d, d, &ly.pf_qkv, 0, 3 * (int64_t)dl, q0, dl);
+            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_k.weight", d, d, &ly.pf_qkv, dl, 3 * (int64_t)dl, q0, dl); }
+            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_v.weight", d, d, &ly.pf_qkv, 2 * (int64_t)dl, 3 * (int64_t)dl, q0, dl); }
             if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_output.weight", d, d, &ly.pf_wo, 0, d); }
-            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_up.weight", d, I.n_ff, &ly.pf_ug, 0, 2 * (int64_t)I.n_ff); }
-            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_gate.weight", d, I.n_ff, &ly.pf_ug, I.n_ff, 2 * (int64_t)I.n_ff); }
+            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_up.weight", d, I.n_ff, &ly.pf_ug, 0, 2 * (int64_t)fl, f0, fl); }
+            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_gate.weight", d, I.n_ff, &ly.pf_ug, fl, 2 * (int64_t)fl, f0, fl); }
             if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_down.weight", I.n_ff, d, &ly.pf_down, 0, d); }
             if (ps == SPYB_FAIL) { return fail(ps); }
             if (ps != SPYB_SUCCESS) { m->pf_ok = false; }   // a mix of types inside one stacked matrix: prompts stay on the mat-vec passes

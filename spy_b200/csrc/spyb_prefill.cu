@@ -235,7 +235,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
 #pragma unroll
             for (int t = 0; t < 8; ++t) {
                 const int token = tok_tile * PF_TOK + 8 * half + t;
-                if (token < g.T) {
+                if (token < g.T && (int64_t)row_tile * PF_M + row < g.n_rows) {   // (the last row tile may be partly padding)
                     const float r0 = __fadd_rn(acc[t][0], acc[t][4]), r1 = __fadd_rn(acc[t][1], acc[t][5]);
                     const float r2 = __fadd_rn(acc[t][2], acc[t][6]), r3 = __fadd_rn(acc[t][3], acc[t][7]);
                     const float v = __fadd_rn(__fadd_rn(r0, r2), __fadd_rn(r1, r3));
@@ -259,19 +259,25 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
 // groups of four squares formed in parallel, the running sum on one thread; Quantizator<FP32,Q8_0>, simd/vec_convert.h:178-261).
 // TOKT tokens per tile; YSUM: the blocks' integer sums follow the scales as floats (the K-quant kernels need them)
 template <bool NORM, int TOKT, bool YSUM>
-__global__ void __launch_bounds__(PF_QUANT_THREADS) prefill_quant_kernel(const float *x, int64_t x_stride, int K, const float *norm_w, float eps, uint8_t *yq) {
+__global__ void __launch_bounds__(PF_QUANT_THREADS) prefill_quant_kernel(const float *x, int64_t x_stride, int K, const float *norm_w, float eps, uint8_t *yq,
+                                                                         int part_len, int64_t part_stride) {
     constexpr int YQB = TOKT * 32 + TOKT * 4 * (YSUM ? 2 : 1);
     extern __shared__ __align__(16) float v3[];
     __shared__ float scale_s;
     const int tid = threadIdx.x, token = blockIdx.x;
     const int n4 = K >> 2, nb = K >> 5;
     const int npass = (n4 + PF_QUANT_THREADS - 1) / PF_QUANT_THREADS;
-    const float4 *x4 = reinterpret_cast<const float4 *>(x + (int64_t)token * x_stride);
+    // a row may lie in parts (the slices the ranks of a tensor-parallel group gathered): elements [i part_len, (i + 1) part_len)
+    // of token t at x + i part_stride + t x_stride; one part = the plain row
+    const float *xrow = x + (int64_t)token * x_stride;
     float4 xv[PF_QUANT_GROUPS];
 #pragma unroll
     for (int k = 0; k < PF_QUANT_GROUPS; ++k) {
         const int gi = tid + k * PF_QUANT_THREADS;
-        xv[k] = (k < npass && gi < n4) ? x4[gi] : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < npass && gi < n4) {
+            const int e = 4 * gi, part = e / part_len;
+            xv[k] = *reinterpret_cast<const float4 *>(xrow + (int64_t)part * part_stride + (e - part * part_len));
+        } else { xv[k] = make_float4(0.f, 0.f, 0.f, 0.f); }
     }
     if (NORM) {
         const float4 *w4 = reinterpret_cast<const float4 *>(norm_w);
@@ -401,14 +407,14 @@ cudaError_t launch_gemm_t(const PrefillGemm &g, cudaStream_t stream) {
     const size_t smem = PF_SMEM_BYTES;
     cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(prefill_gemm_kernel<WT>), smem);
     if (err != cudaSuccess) { return err; }
-    const dim3 grid((unsigned)((g.T + PF_TOK - 1) / PF_TOK), (unsigned)(g.n_rows / PF_M));
+    const dim3 grid((unsigned)((g.T + PF_TOK - 1) / PF_TOK), (unsigned)((g.n_rows + PF_M - 1) / PF_M));
     prefill_gemm_kernel<WT><<<grid, PF_THREADS, smem, stream>>>(g);
     return cudaGetLastError();
 }
 
 }  // namespace
 
-size_t prefill_weight_bytes(int type, int64_t n_rows, int nb) { return (size_t)(n_rows / PF_ROWS) * nb * ((type == 12 || type == 14) ? PF_KQ_WTILE : PF_WTILE); }
+size_t prefill_weight_bytes(int type, int64_t n_rows, int nb) { return (size_t)((n_rows + PF_ROWS - 1) / PF_ROWS) * nb * ((type == 12 || type == 14) ? PF_KQ_WTILE : PF_WTILE); }
 size_t prefill_act_bytes(int T, int nb) { return std::max((size_t)((T + PF_TOK - 1) / PF_TOK) * nb * PF_YQ_BYTES, (size_t)((T + PF_KQ_TOK - 1) / PF_KQ_TOK) * nb * PF_KQ_YQ_BYTES); }
 
 cudaError_t launch_prefill_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0, cudaStream_t stream) {
@@ -421,22 +427,25 @@ cudaError_t launch_prefill_retile(int type, const uint8_t *raw, int64_t row_stri
     return cudaGetLastError();
 }
 
-cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K, const float *norm_w, float eps, uint8_t *yq, cudaStream_t stream, bool kq_layout) {
+cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K, const float *norm_w, float eps, uint8_t *yq, cudaStream_t stream, bool kq_layout,
+                                 int part_len, int64_t part_stride) {
+    if (part_len <= 0) { part_len = K; part_stride = 0; }
+    if ((part_len & 3) || (part_stride & 3) || K % part_len != 0) { return cudaErrorInvalidValue; }
     if (T < 1 || K < 32 || (K & 31) || K > PF_MAX_K || (x_stride & 3) || ((uintptr_t)x & 15)) { return cudaErrorInvalidValue; }
     const size_t smem = norm_w != nullptr ? (size_t)K : 0;   // K / 4 floats
     if (kq_layout) {
-        if (norm_w != nullptr) { prefill_quant_kernel<true, PF_KQ_TOK, true><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq); }
-        else                   { prefill_quant_kernel<false, PF_KQ_TOK, true><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq); }
+        if (norm_w != nullptr) { prefill_quant_kernel<true, PF_KQ_TOK, true><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq, part_len, part_stride); }
+        else                   { prefill_quant_kernel<false, PF_KQ_TOK, true><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq, part_len, part_stride); }
     } else {
-        if (norm_w != nullptr) { prefill_quant_kernel<true, PF_TOK, false><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq); }
-        else                   { prefill_quant_kernel<false, PF_TOK, false><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq); }
+        if (norm_w != nullptr) { prefill_quant_kernel<true, PF_TOK, false><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq, part_len, part_stride); }
+        else                   { prefill_quant_kernel<false, PF_TOK, false><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq, part_len, part_stride); }
     }
     return cudaGetLastError();
 }
 
 cudaError_t launch_prefill_gemm(const PrefillGemm &g, cudaStream_t stream) {
     if (g.type == 12 || g.type == 14) { return launch_prefill_gemm_kq(g, stream); }
-    if (g.w == nullptr || g.yq == nullptr || g.out == nullptr || g.T < 1 || g.nb < 1 || g.n_rows < PF_ROWS || g.n_rows % PF_ROWS != 0) { return cudaErrorInvalidValue; }
+    if (g.w == nullptr || g.yq == nullptr || g.out == nullptr || g.T < 1 || g.nb < 1 || g.n_rows < 1) { return cudaErrorInvalidValue; }
     if (g.type == 2) { return launch_gemm_t<2>(g, stream); }
     if (g.type == 8) { return launch_gemm_t<8>(g, stream); }
     return cudaErrorInvalidValue;

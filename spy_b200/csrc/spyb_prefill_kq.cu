@@ -218,7 +218,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillG
 #pragma unroll
             for (int t = 0; t < 32; ++t) {
                 const int token = tok_tile * KQ_TOK + 32 * half + t;
-                if (token < g.T) {
+                if (token < g.T && (int64_t)row_tile * PF_M + row < g.n_rows) {
                     const int64_t i = (int64_t)token * g.out_stride + (int64_t)row_tile * PF_M + row;
                     g.out[i] = g.resid != nullptr ? __fadd_rn(tot[t], g.resid[i]) : tot[t];
                 }
@@ -278,7 +278,7 @@ template <int WT>
 cudaError_t launch_kq_t(const PrefillGemm &g, cudaStream_t stream) {
     cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(prefill_kq_gemm_kernel<WT>), KQ_SMEM_BYTES);
     if (err != cudaSuccess) { return err; }
-    const dim3 grid((unsigned)((g.T + KQ_TOK - 1) / KQ_TOK), (unsigned)(g.n_rows / PF_M));
+    const dim3 grid((unsigned)((g.T + KQ_TOK - 1) / KQ_TOK), (unsigned)((g.n_rows + PF_M - 1) / PF_M));
     prefill_kq_gemm_kernel<WT><<<grid, PF_THREADS, KQ_SMEM_BYTES, stream>>>(g);
     return cudaGetLastError();
 }
@@ -286,7 +286,7 @@ cudaError_t launch_kq_t(const PrefillGemm &g, cudaStream_t stream) {
 }  // namespace
 
 cudaError_t launch_prefill_gemm_kq(const PrefillGemm &g, cudaStream_t stream) {
-    if (g.w == nullptr || g.yq == nullptr || g.out == nullptr || g.T < 1 || g.nb < 8 || (g.nb & 7) || g.n_rows < PF_ROWS || g.n_rows % PF_ROWS != 0) { return cudaErrorInvalidValue; }
+    if (g.w == nullptr || g.yq == nullptr || g.out == nullptr || g.T < 1 || g.nb < 8 || (g.nb & 7) || g.n_rows < 1) { return cudaErrorInvalidValue; }
     if (g.type == 12) { return launch_kq_t<12>(g, stream); }
     if (g.type == 14) { return launch_kq_t<14>(g, stream); }
     return cudaErrorInvalidValue;

@@ -161,8 +161,9 @@ def test_prompt_on_the_tensor_cores(env, wtype, oracle, tmp_models, monkeypatch)
 
 
 def test_prompt_widths_the_gemm_tile_does_not_divide(be, oracle, tmp_models):
-    """n_ff = 448 is no multiple of the 128-row GEMM tile: the prompt stays on the mat-vec passes and is still exact."""
-    cfg = gguf_io.LlamaConfig(n_layer=2, d_model=256, n_head=2, n_ff=448, n_vocab=300, weight_std=0.05)
+    """n_ff = 416 is no multiple of the 128-row GEMM tile (the stacked up|gate matrix has 832 rows: the last tile is half
+    padding, and W_gate starts in the middle of a tile): the padded rows are neither computed into anything nor stored."""
+    cfg = gguf_io.LlamaConfig(n_layer=2, d_model=256, n_head=2, n_ff=416, n_vocab=300, weight_std=0.05)
     path = str(tmp_models / "odd_ff.gguf")
     gguf_io.make_llama_gguf(path, cfg, seed=59)
     prompt = np.random.default_rng(9).integers(3, cfg.n_vocab, size=20)

@@ -132,10 +132,10 @@ def test_matmul_small_shapes(be, oracle, qt, n, k, t):
 # MatMul of a prompt on the tensor cores (tcgen05): the same operator, the same bits
 @pytest.mark.parametrize("qt", [quants.Q4_0, quants.Q8_0])
 @pytest.mark.parametrize("n,k,t,norm", [(128, 32, 1, False), (128, 256, 16, False), (256, 1024, 37, True), (384, 96, 5, False), (128, 4096, 64, True),
-                                        (1024, 11008, 19, False)])
+                                        (1024, 11008, 19, False), (200, 512, 21, False), (4, 64, 3, False)])
 def test_prefill_matmul_matches_oracle(be, oracle, qt, n, k, t, norm):
-    """Block counts below, at and above the pipeline depths (1, 3, 8, 32, 128, 344 blocks), ragged token tiles, with and
-    without the RMSNorm in front; activations with a few outliers so that block scales differ widely."""
+    """Block counts below, at and above the pipeline depths (1, 3, 8, 32, 128, 344 blocks), ragged token tiles, row counts that
+    leave the last 128-row tile partly padding, with and without the RMSNorm in front; activations with a few outliers so that block scales differ widely."""
     rng = np.random.default_rng(n + k + t + qt)
     w = quants.quantize((rng.standard_normal((n, k)) * 0.02).astype(np.float32), qt)
     x = rng.standard_normal((t, k)).astype(np.float32)
@@ -191,9 +191,9 @@ def test_prefill_kernel_wait_runs_out_and_is_reported():
 
 def test_prefill_matmul_rejects_what_does_not_fit(be):
     w = np.zeros(100 * 18, dtype=np.uint8)
-    x = np.zeros((2, 32), dtype=np.float32)
+    x = np.zeros((2, 48), dtype=np.float32)
     with pytest.raises(B.SpybError) as e:
-        be.prefill_matmul(quants.Q4_0, w, 100, 32, x)          # rows not a multiple of 128
+        be.prefill_matmul(quants.Q4_0, w, 100, 48, x)          # k not a multiple of 32
     assert e.value.status == B.UNSUPPORTED
     with pytest.raises(B.SpybError) as e:
         be.prefill_matmul(quants.Q4_K, w, 128, 128, np.zeros((2, 128), dtype=np.float32))   # K-quant rows: k a multiple of 256

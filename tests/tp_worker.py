@@ -41,6 +41,10 @@ def main():
         dist.all_gather_object(handles, m.tp_export())
         m.tp_import(handles)
     ids, logits = m.generate(prompt, 12)
+    # a prompt long enough for the tensor-core GEMM path: every rank runs its heads and FFN rows for all tokens, the attention
+    # output and the FFN activation are all-gathered once per layer
+    long_prompt = np.random.default_rng(4).integers(3, cfg.n_vocab, size=41)
+    long_logits = m.eval(long_prompt, 0).copy()
     ok = True
     if rank == 0:
         b1 = B.B200Backend(local)
@@ -48,9 +52,10 @@ def main():
         ids1, logits1 = m1.generate(prompt, 12)
         err = float(np.abs(logits - logits1).max())
         same_bits = bool(np.array_equal(np.asarray(logits, dtype=np.float32).view(np.uint32), np.asarray(logits1, dtype=np.float32).view(np.uint32)))
-        ok = bool(np.array_equal(ids, ids1)) and same_bits
+        long_same = bool(np.array_equal(long_logits.view(np.uint32), m1.eval(long_prompt, 0).view(np.uint32)))
+        ok = bool(np.array_equal(ids, ids1)) and same_bits and long_same
         print(f"TP{world} vs TP1 ({'deep' if deep else 'small'} model): max|dlogit| = {err:.3e}, bits identical = {same_bits}, "
-              f"ids identical = {np.array_equal(ids, ids1)} -> {'OK' if ok else 'FAIL'}", flush=True)
+              f"ids identical = {np.array_equal(ids, ids1)}, 41-token prompt bits identical = {long_same} -> {'OK' if ok else 'FAIL'}", flush=True)
         m1.close(); b1.close()
     m.close(); be.close()
     flag = torch.tensor([0 if ok else 1])
