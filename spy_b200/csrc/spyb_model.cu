@@ -488,10 +488,11 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool bat
         g.error_flag = be->d_error_flag; g.wait_limit_ns = be->wait_limit_ns;
         return launch_prefill_gemm(g, s);
     };
-    // Tensor parallel: this rank's heads and FFN rows produce their slices of the attention output and of the FFN activation
-    // for all T tokens as one contiguous part [T][dl] / [T][fl]; one NCCL all-gather per vector puts the ranks' parts side
-    // by side ([tp][T][len]), and the quantizer in front of the replicated W_o / W_down reads a token's row across the parts.
-    // No f32 sum is split across ranks, as on the single-token path.
+    // Tensor parallel: every matrix is split by output rows - this rank's heads, FFN rows, and a slice of the rows of W_o and
+    // W_down - so each rank produces, for all T tokens, one contiguous part [T][len] of the attention output, the FFN
+    // activation and (twice) the residual stream; one NCCL all-gather per vector puts the ranks' parts side by side
+    // ([tp][T][len]) and the quantizer in front of the next matrix reads a token's row across the parts. Every dot product
+    // is computed whole by one rank: no f32 sum is split across ranks, as on the single-token path.
     auto gather = [&](float *parts, int64_t len) -> spyb_status {
         if (tp == 1) { return SPYB_SUCCESS; }
         if (m->nccl_comm == nullptr) { be->set_error("tensor-parallel model used before spyb_model_init_tp"); return SPYB_FAIL; }
@@ -501,9 +502,11 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool bat
         ++*launches;
         return SPYB_SUCCESS;
     };
+    const int dp = d / tp;                                  // W_o and W_down: this rank's dp output rows; the residual stream in parts [tp][T][dp]
     float *att_part = m->pf_att + (size_t)rank * T * dl, *act_part = m->pf_act + (size_t)rank * T * fl;   // (tp == 1: the whole buffers)
+    float *x_part = m->pf_x + (size_t)rank * T * dp;
     for (Layer &ly : m->layers) {
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, d, T, d, ly.attn_norm, m->info.rms_eps, m->pf_yq, s, m->kq));
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, dp, T, d, ly.attn_norm, m->info.rms_eps, m->pf_yq, s, m->kq, dp, (int64_t)T * dp));
         SPYB_CUDA(be, gemm(ly.pf_qkv, d, m->pf_qkv, 3 * (int64_t)dl, nullptr));
         if (m->kq) {   // one matrix per tensor: Wk and Wv fill the other two thirds of the QKV rows
             SPYB_CUDA(be, gemm(ly.pf_k, d, m->pf_qkv + dl, 3 * (int64_t)dl, nullptr));
@@ -529,14 +532,16 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool bat
         }
         if (gather(m->pf_att, dl) != SPYB_SUCCESS) { return SPYB_FAIL; }
         SPYB_CUDA(be, launch_prefill_quant(m->pf_att, dl, T, d, nullptr, 0.f, m->pf_yq, s, m->kq, dl, (int64_t)T * dl));
-        SPYB_CUDA(be, gemm(ly.pf_wo, d, m->pf_x, d, m->pf_x));
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, d, T, d, ly.ffn_norm, m->info.rms_eps, m->pf_yq, s, m->kq));
+        SPYB_CUDA(be, gemm(ly.pf_wo, d, x_part, dp, x_part));
+        if (gather(m->pf_x, dp) != SPYB_SUCCESS) { return SPYB_FAIL; }
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, dp, T, d, ly.ffn_norm, m->info.rms_eps, m->pf_yq, s, m->kq, dp, (int64_t)T * dp));
         SPYB_CUDA(be, gemm(ly.pf_ug, d, m->pf_ug, 2 * (int64_t)fl, nullptr));
         if (m->kq) { SPYB_CUDA(be, gemm(ly.pf_gate, d, m->pf_ug + fl, 2 * (int64_t)fl, nullptr)); ++*launches; }
         SPYB_CUDA(be, launch_prefill_silu_mul(m->pf_ug, T, fl, be->d_silu_table, act_part, s));
         if (gather(m->pf_act, fl) != SPYB_SUCCESS) { return SPYB_FAIL; }
         SPYB_CUDA(be, launch_prefill_quant(m->pf_act, fl, T, ff, nullptr, 0.f, m->pf_yq, s, m->kq, fl, (int64_t)T * fl));
-        SPYB_CUDA(be, gemm(ly.pf_down, ff, m->pf_x, d, m->pf_x));
+        SPYB_CUDA(be, gemm(ly.pf_down, ff, x_part, dp, x_part));
+        if (gather(m->pf_x, dp) != SPYB_SUCCESS) { return SPYB_FAIL; }
         *launches += 7;
     }
     return SPYB_SUCCESS;
@@ -740,10 +745,10 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
     }
     // prompts run as GEMMs on the tensor cores when the model is unsharded, Q4_0 / Q8_0 throughout and its widths are
     // multiples of the kernel's 128-row tile (SPYB_PREFILL=0 keeps the mat-vec passes; the extra copy of the layer weights is then not made)
-    // (a sharded model keeps its shard of Wq|Wk|Wv and of W_up|W_gate in that layout, W_o and W_down whole: the prompt path
-    // gathers the attention output and the FFN activation of all tokens with one NCCL all-gather each per layer)
+    // (a sharded model keeps its rows of every matrix in that layout - its heads, its FFN rows, its slice of the rows of W_o and
+    // W_down: the prompt path all-gathers the four vectors of a layer for all tokens of a chunk at once)
     m->pf_ok = (std::getenv("SPYB_PREFILL") == nullptr || std::atoi(std::getenv("SPYB_PREFILL")) != 0) &&
-               d <= PF_MAX_K && I.n_ff <= PF_MAX_K && (m->kq ? (tp == 1 && d % 256 == 0 && I.n_ff % 256 == 0) : (dl % 4 == 0 && fl % 4 == 0));
+               d <= PF_MAX_K && I.n_ff <= PF_MAX_K && (m->kq ? (tp == 1 && d % 256 == 0 && I.n_ff % 256 == 0) : (dl % 4 == 0 && fl % 4 == 0 && d % (4 * tp) == 0));
     if (const char *v = std::getenv("SPYB_PREFILL_CHUNK")) { const int n = std::atoi(v); if (n >= PF_TOK && n <= 4096) { m->pf_chunk = (n + TMAX - 1) / TMAX * TMAX; } }
     m->layers.resize(I.n_layer);
     for (int L = 0; L < I.n_layer; ++L) {
@@ -820,10 +825,11 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
             spyb_status ps = upload_pf(p + "attn_q.weight", d, d, &ly.pf_qkv, 0, 3 * (int64_t)dl, q0, dl);
             if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_k.weight", d, d, &ly.pf_qkv, dl, 3 * (int64_t)dl, q0, dl); }
             if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_v.weight", d, d, &ly.pf_qkv, 2 * (int64_t)dl, 3 * (int64_t)dl, q0, dl); }
-            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_output.weight", d, d, &ly.pf_wo, 0, d); }
+            const int64_t dp = d / tp, o0 = (int64_t)r * dp;            // and its slice of the output rows of W_o and W_down
+            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "attn_output.weight", d, d, &ly.pf_wo, 0, dp, o0, dp); }
             if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_up.weight", d, I.n_ff, &ly.pf_ug, 0, 2 * (int64_t)fl, f0, fl); }
             if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_gate.weight", d, I.n_ff, &ly.pf_ug, fl, 2 * (int64_t)fl, f0, fl); }
-            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_down.weight", I.n_ff, d, &ly.pf_down, 0, d); }
+            if (ps == SPYB_SUCCESS) { ps = upload_pf(p + "ffn_down.weight", I.n_ff, d, &ly.pf_down, 0, dp, o0, dp); }
             if (ps == SPYB_FAIL) { return fail(ps); }
             if (ps != SPYB_SUCCESS) { m->pf_ok = false; }   // a mix of types inside one stacked matrix: prompts stay on the mat-vec passes
         }
@@ -1008,10 +1014,27 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
             SPYB_CUDA(be, cudaMemcpyAsync(m->d_pos, m->h_pos_pinned, 12, cudaMemcpyHostToDevice, be->stream));
             SPYB_CUDA(be, cudaMemcpyAsync(m->pf_pos, m->h_pf_pos, (size_t)groups * 8, cudaMemcpyHostToDevice, be->stream));
             SPYB_CUDA(be, cudaMemcpyAsync(m->pf_tokens, m->h_pf_tokens, (size_t)T * 4, cudaMemcpyHostToDevice, be->stream));
-            SPYB_CUDA(be, launch_embed(m->pf_tokens, T, m->embd, m->embd_type, m->info.d_model, m->pf_x, be->stream)); ++launches;
+            // sharded: the residual stream of the chunk lives in tp parts [tp][T][d / tp] (rank i produces part i of every token and the
+            // parts are all-gathered in place); one part = the plain [T][d]
+            const int tp = m->info.tp_size, dmod = m->info.d_model, dp = dmod / tp;
+            if (tp == 1) { SPYB_CUDA(be, launch_embed(m->pf_tokens, T, m->embd, m->embd_type, dmod, m->pf_x, be->stream)); ++launches; }
+            else {
+                SPYB_CUDA(be, launch_embed(m->pf_tokens, T, m->embd, m->embd_type, dmod, m->pf_att, be->stream)); ++launches;
+                for (int i = 0; i < tp; ++i) {
+                    SPYB_CUDA(be, cudaMemcpy2DAsync(m->pf_x + (size_t)i * T * dp, (size_t)dp * 4, m->pf_att + (size_t)i * dp, (size_t)dmod * 4, (size_t)dp * 4, (size_t)T,
+                                                    cudaMemcpyDeviceToDevice, be->stream));
+                }
+            }
             if (run_prefill_layers(m, T, &launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
             if (t0 + T == n_tokens) {
-                if (run_head(m, 0, &launches, m->pf_x + (int64_t)(T - 1) * m->info.d_model) != SPYB_SUCCESS) { return SPYB_FAIL; }
+                const float *last_row = m->pf_x + (int64_t)(T - 1) * dmod;
+                if (tp > 1) {   // the last token's row from its parts
+                    for (int i = 0; i < tp; ++i) {
+                        SPYB_CUDA(be, cudaMemcpyAsync(m->x + (size_t)i * dp, m->pf_x + (size_t)i * T * dp + (size_t)(T - 1) * dp, (size_t)dp * 4, cudaMemcpyDeviceToDevice, be->stream));
+                    }
+                    last_row = m->x;
+                }
+                if (run_head(m, 0, &launches, last_row) != SPYB_SUCCESS) { return SPYB_FAIL; }
                 if (logits_host != nullptr) {
                     SPYB_CUDA(be, cudaMemcpyAsync(m->h_logits_pinned, m->logits, (size_t)m->info.n_vocab * 4, cudaMemcpyDeviceToHost, be->stream));
                 }
