@@ -454,6 +454,37 @@ int oracle_eval(const oracle_model *m, oracle_state *st, const int32_t *tokens, 
                 const float dd = h2f(dh);
                 for (int l = 0; l < 32; ++l) { x[i * d + b * 32 + l] = (float)(int8_t)row[b * 34 + 2 + l] * dd; }
             }
+        } else if (m->embd_type == T_Q4_K) {   /* no reference arithmetic: (d * sc) * q - dmin * m, every operation a separate f32 one */
+            const uint8_t *row = m->token_embd + (size_t)tokens[i] * (d / 256 * 144);
+            for (int64_t b = 0; b < d / 256; ++b) {
+                const uint8_t *s = row + b * 144;
+                uint16_t dh, mh; memcpy(&dh, s, 2); memcpy(&mh, s + 2, 2);
+                const float dd = h2f(dh), dmin = h2f(mh);
+                for (int j = 0; j < 8; ++j) {
+                    uint8_t sc, mn; scale_min_k4(j, s + 4, &sc, &mn);
+                    const float d1 = dd * (float)sc, m1 = dmin * (float)mn;
+                    for (int l = 0; l < 32; ++l) {
+                        const uint8_t qb = s[16 + 32 * (j / 2) + l];
+                        const float q = (float)((j & 1) ? (qb >> 4) : (qb & 0xF));
+                        const float prod = d1 * q;
+                        x[i * d + b * 256 + j * 32 + l] = prod - m1;
+                    }
+                }
+            }
+        } else if (m->embd_type == T_Q6_K) {   /* q * (d * sc) */
+            const uint8_t *row = m->token_embd + (size_t)tokens[i] * (d / 256 * 210);
+            for (int64_t b = 0; b < d / 256; ++b) {
+                const uint8_t *s = row + b * 210;
+                uint16_t dh; memcpy(&dh, s + 208, 2);
+                const float dd = h2f(dh);
+                for (int e = 0; e < 256; ++e) {
+                    const int hf = e >> 7, seg = (e >> 5) & 3, l = e & 31;
+                    const uint8_t lo = s[64 * hf + 32 * (seg & 1) + l], h = s[128 + 32 * hf + l];
+                    const int q = (((seg & 2) ? (lo >> 4) : (lo & 0xF)) | (((h >> (2 * seg)) & 3) << 4)) - 32;
+                    const float ds = dd * (float)(int8_t)s[192 + (e >> 4)];
+                    x[i * d + b * 256 + e] = (float)q * ds;
+                }
+            }
         } else { rc = 3; goto done; }
     }
 

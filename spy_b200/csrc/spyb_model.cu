@@ -701,7 +701,9 @@ spyb_status spyb_model_load_gguf(spyb_backend *be, const char *path, int32_t n_c
         if (!tensor("token_embd.weight", &t, &data)) { return fail(SPYB_FAIL); }
         I.n_vocab = (int)t->ne[1];
         m->embd_type = t->type;
-        if (t->type != SPYB_FP32 && t->type != SPYB_FP16 && t->type != SPYB_Q8_0 && t->type != SPYB_Q4_0) { be->set_error("token_embd type %d is not supported", t->type); return fail(SPYB_UNSUPPORTED); }
+        if (t->type != SPYB_FP32 && t->type != SPYB_FP16 && t->type != SPYB_Q8_0 && t->type != SPYB_Q4_0 && t->type != SPYB_Q4_K && t->type != SPYB_Q6_K) {
+            be->set_error("token_embd type %d is not supported", t->type); return fail(SPYB_UNSUPPORTED);
+        }
         const size_t bytes = (size_t)GgufFile::row_bytes(t->type, d) * t->ne[1];
         if (dev_alloc(m, &m->embd, bytes) != SPYB_SUCCESS) { return fail(SPYB_FAIL); }
         if (cudaMemcpy(m->embd, data, bytes, cudaMemcpyHostToDevice) != cudaSuccess) { be->set_error("embedding upload failed"); return fail(SPYB_FAIL); }

@@ -975,11 +975,37 @@ cudaError_t launch_copy_strided(const Strided &src, int src_type, const Strided 
     return launch_check();
 }
 
+// bytes of one table row of ne0 elements
+__host__ __device__ __forceinline__ int64_t table_row_bytes(int type, int64_t ne0) {
+    return type == 0 ? ne0 * 4 : type == 1 ? ne0 * 2 : type == 8 ? ne0 / 32 * 34 : type == 12 ? ne0 / 256 * 144 : type == 14 ? ne0 / 256 * 210 : ne0 / 32 * 18;
+}
 // embedding row -> f32: memcpy for F32, Q8_0 -> F32 as OperatorGetRowImpl::execute (view.cpp:33-81);
-// Q4_0 rows (which the CPU backend cannot gather) decode as (nibble - 8) * d.
+// Q4_0 rows (which the CPU backend cannot gather) decode as (nibble - 8) * d; K-quant rows (no reference arithmetic; the block
+// layouts of number_impl/k-quant.h) as (d * sc) * q - dmin * m (Q4_K) and q * (d * sc) (Q6_K), every operation a separate f32 one.
 __device__ __forceinline__ float embd_value(const uint8_t *row, int type, int64_t i) {
     if (type == 0) { return reinterpret_cast<const float *>(row)[i]; }
     if (type == 1) { return h2f(reinterpret_cast<const uint16_t *>(row)[i]); }
+    if (type == 12) {
+        const uint8_t *s = row + (i >> 8) * 144;
+        const int e = (int)(i & 255), j = e >> 5, l = e & 31;
+        const float d = h2f((uint16_t)(s[0] | (s[1] << 8))), dmin = h2f((uint16_t)(s[2] | (s[3] << 8)));
+        const uint8_t *sc12 = s + 4;
+        uint32_t sc, mn;
+        if (j < 4) { sc = sc12[j] & 63u; mn = sc12[j + 4] & 63u; }
+        else { sc = (sc12[j + 4] & 0xFu) | ((uint32_t)(sc12[j - 4] >> 6) << 4); mn = (uint32_t)(sc12[j + 4] >> 4) | ((uint32_t)(sc12[j] >> 6) << 4); }
+        const uint8_t qb = s[16 + 32 * (j >> 1) + l];
+        const int q = (j & 1) ? (qb >> 4) : (qb & 0xF);
+        return __fsub_rn(__fmul_rn(__fmul_rn(d, (float)sc), (float)q), __fmul_rn(dmin, (float)mn));
+    }
+    if (type == 14) {
+        const uint8_t *s = row + (i >> 8) * 210;
+        const int e = (int)(i & 255), hf = e >> 7, seg = (e >> 5) & 3, l = e & 31;
+        const uint8_t lo = s[64 * hf + 32 * (seg & 1) + l], h = s[128 + 32 * hf + l];
+        const int q = (((seg & 2) ? (lo >> 4) : (lo & 0xF)) | (((h >> (2 * seg)) & 3) << 4)) - 32;
+        const float d = h2f((uint16_t)(s[208] | (s[209] << 8)));
+        const int sc = (int)(int8_t)s[192 + (e >> 4)];
+        return __fmul_rn((float)q, __fmul_rn(d, (float)sc));
+    }
     const int64_t b = i >> 5; const int k = (int)(i & 31);
     if (type == 8) {
         const uint8_t *blk = row + b * 34;
@@ -996,14 +1022,13 @@ __global__ void getrow_kernel(const uint8_t *table, int type, int64_t row_bytes,
     for (int64_t i = threadIdx.x; i < ne0; i += blockDim.x) { out[r * ne0 + i] = embd_value(row, type, i); }
 }
 cudaError_t launch_getrow(const uint8_t *table, int table_type, int64_t row_bytes, int64_t ne0, const int32_t *ids, int64_t n_ids, float *out, cudaStream_t s) {
-    if (table_type != 0 && table_type != 1 && table_type != 2 && table_type != 8) { return cudaErrorNotSupported; }
+    if (table_type != 0 && table_type != 1 && table_type != 2 && table_type != 8 && table_type != 12 && table_type != 14) { return cudaErrorNotSupported; }
     if (n_ids == 0) { return cudaSuccess; }
     getrow_kernel<<<(unsigned)n_ids, 256, 0, s>>>(table, table_type, row_bytes, ne0, ids, out);
     return launch_check();
 }
 cudaError_t launch_embed(const int32_t *ids, int n_ids, const uint8_t *embd, int embd_type, int64_t d_model, float *x_out, cudaStream_t s) {
-    const int64_t rb = embd_type == 0 ? d_model * 4 : embd_type == 1 ? d_model * 2 : embd_type == 8 ? d_model / 32 * 34 : d_model / 32 * 18;
-    return launch_getrow(embd, embd_type, rb, d_model, ids, n_ids, x_out, s);
+    return launch_getrow(embd, embd_type, table_row_bytes(embd_type, d_model), d_model, ids, n_ids, x_out, s);
 }
 
 // MatMul with an F16 weight and f32 activations (the attention products when run op by op): activations
@@ -1087,8 +1112,7 @@ __global__ void __launch_bounds__(1024) argmax_embed_kernel(const float *logits,
     }
     __syncthreads();
     if (embd != nullptr) {
-        const int64_t rb = embd_type == 0 ? d_model * 4 : embd_type == 1 ? d_model * 2 : embd_type == 8 ? d_model / 32 * 34 : d_model / 32 * 18;
-        const uint8_t *row = embd + (int64_t)winner * rb;
+        const uint8_t *row = embd + (int64_t)winner * table_row_bytes(embd_type, d_model);
         for (int64_t i = tid; i < d_model; i += blockDim.x) { x_out[i] = embd_value(row, embd_type, i); }
     }
 }
@@ -1144,8 +1168,7 @@ __global__ void __launch_bounds__(1024) argmax_embed_batch_kernel(const float *l
     }
     __syncthreads();
     if (embd != nullptr && x_out != nullptr) {
-        const int64_t rb = embd_type == 0 ? d_model * 4 : embd_type == 1 ? d_model * 2 : embd_type == 8 ? d_model / 32 * 34 : d_model / 32 * 18;
-        const uint8_t *row = embd + (int64_t)winner * rb;
+        const uint8_t *row = embd + (int64_t)winner * table_row_bytes(embd_type, d_model);
         for (int64_t i = tid; i < d_model; i += blockDim.x) { x_out[(int64_t)c * x_stride + i] = embd_value(row, embd_type, i); }
     }
 }

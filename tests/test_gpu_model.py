@@ -229,6 +229,8 @@ def test_long_context_attention(be, oracle, tmp_models):
     ("q4k", dict(wtype=quants.Q4_K)),
     ("q4k_m", dict(wtype=quants.Q4_K, overrides={"attn_v": quants.Q6_K, "ffn_down": quants.Q6_K, "output": quants.Q6_K})),
     ("q6k_long_rows", dict(wtype=quants.Q6_K, n_ff=4608, overrides={"ffn_gate": quants.Q4_K, "ffn_down": quants.Q4_K})),   # 18 super-blocks per W_down row
+    ("q4k_embd", dict(wtype=quants.Q4_K, embd_type=quants.Q4_K, overrides={"output": quants.Q6_K})),   # token embeddings as K-quant rows, as stock files keep them
+    ("q6k_embd", dict(wtype=quants.Q4_K, embd_type=quants.Q6_K)),
 ])
 def test_k_quant_models_match_the_restatement(name, cfg, oracle, tmp_models):
     """Q4_K / Q6_K weights through the step plan (the Q4_K_M-style mix: Q6_K for attn_v, ffn_down and the output head).

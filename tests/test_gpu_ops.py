@@ -342,6 +342,18 @@ def test_getrow_q4_0_and_f16_tables(be):
     assert np.array_equal(bits(got), bits(th.astype(np.float32)[ids]))
 
 
+@pytest.mark.parametrize("qt", [quants.Q4_K, quants.Q6_K])
+def test_getrow_k_quant_tables(be, qt):
+    """Embedding tables in K-quant formats (stock Q4_K_M files keep token_embd that way): rows decode as (d * sc) * q - dmin * m
+    (Q4_K) and q * (d * sc) (Q6_K), one f32 operation at a time - the numpy decoder's order."""
+    rng = np.random.default_rng(19)
+    table = (rng.standard_normal((24, 512)) * 0.1).astype(np.float32)
+    ids = np.array([23, 0, 5, 5, 11], dtype=np.int32)
+    tq = quants.quantize(table, qt)
+    got = run(be, "GetRow", [(tq, qt, (512, 24), None, B.NODE_CONSTANT), (ids, B.INT32, (5,), None, B.NODE_IO)], (512, 5)).reshape(5, 512)
+    assert np.array_equal(bits(got), bits(quants.dequantize(tq, qt).reshape(24, 512)[ids]))
+
+
 def test_copy_into_strided_f16_cache_and_view(be, oracle):
     """KV append as the graph does it: View at a byte offset, Copy f32 -> f16 into a transposed destination."""
     rng = np.random.default_rng(8)
