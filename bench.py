@@ -375,6 +375,10 @@ def main():
             parity_tp = parity_record(ids_tp, logits_tp, ids_1, logits_1)
             parity_tp["against"] = "the same model unsharded on one GPU, same prompt and positions"
             parity_tp["warmup_ids_identical"] = bool(np.array_equal(w1, ids_warm) and int(np.argmax(f1)) == tok0)
+            # and the long prompt: the sharded GEMM path (NCCL all-gathers of whole chunks) against the unsharded one
+            pre_1 = m1.eval(pre_ids, 0)
+            prefill["parity_tp"] = {"bits_identical": bool(np.array_equal(pre_1.view(np.uint32), pre_logits.view(np.uint32))),
+                                    "max_abs_dlogit": float(np.abs(pre_1 - pre_logits).max()), "against": "the same model unsharded on one GPU, same prompt"}
             m1.close(); be1.close()
         barrier()
 
