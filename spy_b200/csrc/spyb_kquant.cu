@@ -30,7 +30,8 @@ namespace spyb {
 
 constexpr int KQ_THREADS = 512;
 constexpr int KQ_WARPS   = KQ_THREADS / WARP;
-constexpr int KQ_SB_WORDS = 65;   // words per super-block of activations in shared memory (64 + 1 against bank conflicts)
+constexpr int KQ_SB_WORDS = 68;   // words per super-block of activations in shared memory: 64 + 4, so that a block's eight words are two aligned
+                                  // 128-bit reads and the eight lanes of a quarter-warp (one super-block each) hit distinct banks
 
 struct KqPlanes { uint32_t *y; float *dx; int *ysum; };
 
@@ -106,11 +107,13 @@ __device__ __forceinline__ float kq_value_q4k(const uint8_t *wb, const uint32_t 
     for (int j = 0; j < 8; ++j) {          // sub-block j: bytes 32 * (j / 2) .. + 31 of qs, low nibbles when j is even
         const uint4 qa = q[2 * (j >> 1)], qb = q[2 * (j >> 1) + 1];
         const uint32_t w8[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+        const uint4 ya = *reinterpret_cast<const uint4 *>(ysb + j * 8), yb = *reinterpret_cast<const uint4 *>(ysb + j * 8 + 4);
+        const uint32_t y8[8] = {ya.x, ya.y, ya.z, ya.w, yb.x, yb.y, yb.z, yb.w};
         int isum = 0;
 #pragma unroll
         for (int w = 0; w < 8; ++w) {
             const uint32_t nib = (j & 1) ? (w8[w] >> 4) & 0x0f0f0f0fu : w8[w] & 0x0f0f0f0fu;
-            isum = __dp4a((int)nib, (int)ysb[j * 8 + w], isum);
+            isum = __dp4a((int)nib, (int)y8[w], isum);
         }
         float sc, mn; kq_scale_min(sw, j, sc, mn);
         acc = fmaf(__fmul_rn(__fmul_rn(dm.x, sc), dx[j]), (float)isum, acc);
@@ -138,12 +141,14 @@ __device__ __forceinline__ float kq_value_q6k(const uint8_t *wb, uint16_t d_half
         const int h = g >> 3, s = (g >> 1) & 3, l0 = 16 * (g & 1);
         const uint4 lv = ql[(64 * h + 32 * (s & 1) + l0) >> 4], hv = qh[(32 * h + l0) >> 4];
         const uint32_t lw[4] = {lv.x, lv.y, lv.z, lv.w}, hw[4] = {hv.x, hv.y, hv.z, hv.w};
+        const uint4 yv = *reinterpret_cast<const uint4 *>(ysb + (g >> 1) * 8 + 4 * (g & 1));
+        const uint32_t y4[4] = {yv.x, yv.y, yv.z, yv.w};
         int isum = 0, ys = 0;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const uint32_t lo = (s & 2) ? (lw[w] >> 4) & 0x0f0f0f0fu : lw[w] & 0x0f0f0f0fu;
             const uint32_t hi = ((hw[w] >> (2 * s)) & 0x03030303u) << 4;
-            const uint32_t y = ysb[(g >> 1) * 8 + 4 * (g & 1) + w];
+            const uint32_t y = y4[w];
             isum = __dp4a((int)(lo | hi), (int)y, isum);      // values 0..63
             ys   = __dp4a(0x01010101, (int)y, ys);
         }
