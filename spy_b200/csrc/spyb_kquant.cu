@@ -16,8 +16,8 @@
 // walk over the lanes' values. A warp owns a pair of rows (rows 2u, 2u+1 rotate together in RoPE; FFN up row i and gate
 // row i meet in the SiLU epilogue). HBM-bound: rows * K/256 * 144 (210) bytes per launch, read once, no re-tiling for
 // Q4_K; Q6_K rows are re-laid at upload so that every piece is 16-byte aligned (208-byte bodies, the fp16 scales of a
-// row together at its end). Activations: Q8_0 in shared memory, one 65-word stride per super-block so that lanes
-// working on different super-blocks hit different banks.
+// row together at its end). Activations: Q8_0 in shared memory, one 68-word stride per super-block so that a block's words
+// are aligned 128-bit reads and the lanes of a quarter-warp, working on different super-blocks, hit different banks.
 
 #include <algorithm>
 
