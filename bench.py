@@ -382,6 +382,35 @@ def main():
             m1.close(); be1.close()
         barrier()
 
+    # ---- a batch of independent sequences that share the weights (the batch > 1 cases of the configurations): sequence 0
+    # has the benchmark's prompt, so its ids can be compared with the single-sequence run; aggregate tokens/s over all sequences
+    n_batch = {1: 8, 4: 8, 5: 32}.get(args.config, 0)
+    batch_rec = None
+    if n_batch > 0 and not args.no_batch:
+        try:
+            n_cmp = min(16, room)
+            ref_ids, _ = model.decode(tok0, N_PROMPT, n_cmp)
+            model.set_sequences(n_batch)
+            rng_b = np.random.default_rng(PROMPT_SEED + 7)
+            firsts = []
+            for c in range(n_batch):
+                model.select_sequence(c)
+                pc = prompt if c == 0 else rng_b.integers(3, info.n_vocab, size=N_PROMPT).astype(np.int32)
+                firsts.append(int(np.argmax(model.eval(pc, 0))))
+            b_steps = min(32, room)
+            model.decode_batch(firsts, N_PROMPT, min(4, room))          # warm
+            b_ids, _ = model.decode_batch(firsts, N_PROMPT, b_steps)
+            batch_rec = {"sequences": n_batch, "steps": b_steps, "ms_per_step": model.last_ms / b_steps,
+                         "tokens_per_s": n_batch * b_steps / (model.last_ms / 1e3), "launches": int(model.last_launches),
+                         "sequence0_ids_match_single_sequence_run": bool(np.array_equal(b_ids[:n_cmp, 0], ref_ids[:n_cmp])),
+                         "note": "greedy decoding of the sequences in lockstep (spyb_model_decode_batch): per step the layer weights are streamed once per group of 4 sequences "
+                                 "through the mat-vec kernels (fewer than 16 sequences on one GPU), or once for all of them through the tcgen05 GEMM kernels (16 and more, "
+                                 "and every batch of a tensor-parallel model: each rank on its rows, NCCL all-gathers of the whole vectors); device time of rank 0"}
+            model.select_sequence(0)
+        except Exception as e:  # noqa: BLE001
+            batch_rec = {"error": str(e)[:300]}
+    barrier()
+
     # ---- dominant kernel alone, over every layer's weights ----------------------------------
     roof = None
     if rank == 0:
@@ -416,31 +445,8 @@ def main():
                         "device_ms_per_step": ev_ms / steps},
                 "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "prefill": prefill,
                 "ids_match_e2e": bool(np.array_equal(ids, np.array(e2e_ids)))}
-        # ---- a batch of independent sequences that share the weights (the batch > 1 cases of the configurations): sequence 0
-        # has the benchmark's prompt, so its ids can be compared with the single-sequence run; aggregate tokens/s over all sequences
-        n_batch = {1: 8, 4: 8, 5: 32}.get(args.config, 0)
-        if world == 1 and n_batch > 0 and not args.no_batch:
-            try:
-                n_cmp = min(16, room)
-                ref_ids, _ = model.decode(tok0, N_PROMPT, n_cmp)
-                model.set_sequences(n_batch)
-                rng_b = np.random.default_rng(PROMPT_SEED + 7)
-                firsts = []
-                for c in range(n_batch):
-                    model.select_sequence(c)
-                    pc = prompt if c == 0 else rng_b.integers(3, info.n_vocab, size=N_PROMPT).astype(np.int32)
-                    firsts.append(int(np.argmax(model.eval(pc, 0))))
-                b_steps = min(32, room)
-                model.decode_batch(firsts, N_PROMPT, min(4, room))          # warm
-                b_ids, _ = model.decode_batch(firsts, N_PROMPT, b_steps)
-                line["batch"] = {"sequences": n_batch, "steps": b_steps, "ms_per_step": model.last_ms / b_steps,
-                                 "tokens_per_s": n_batch * b_steps / (model.last_ms / 1e3), "launches": int(model.last_launches),
-                                 "sequence0_ids_match_single_sequence_run": bool(np.array_equal(b_ids[:n_cmp, 0], ref_ids[:n_cmp])),
-                                 "note": "greedy decoding of the sequences in lockstep (spyb_model_decode_batch): per step the layer weights are streamed once per group of 4 sequences "
-                                         "through the mat-vec kernels (fewer than 16 sequences), or once for all of them through the tcgen05 GEMM kernels (16 and more)"}
-                model.select_sequence(0)
-            except Exception as e:  # noqa: BLE001
-                line["batch"] = {"error": str(e)[:300]}
+        if batch_rec is not None:
+            line["batch"] = batch_rec
         if parity_tp is not None:
             line["parity_tp"] = parity_tp
         if not args.no_cpu_baseline and world == 1:

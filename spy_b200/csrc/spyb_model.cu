@@ -1237,7 +1237,8 @@ spyb_status spyb_model_set_sequences(spyb_model *m, int32_t n_seq) {
     if (m == nullptr) { return SPYB_FAIL; }
     spyb_backend *be = m->be;
     if (n_seq < 1 || n_seq > 64) { be->set_error("set_sequences: 1 to 64 sequences, got %d", n_seq); return SPYB_UNSUPPORTED; }
-    if (m->kq || m->info.tp_size != 1 || m->step_ok) { be->set_error("set_sequences: batches need an unsharded Q4_0 / Q8_0 model on the per-matrix kernels"); return SPYB_UNSUPPORTED; }
+    if (m->kq || m->step_ok) { be->set_error("set_sequences: batches need a Q4_0 / Q8_0 model on the per-matrix kernels"); return SPYB_UNSUPPORTED; }
+    if (m->info.tp_size != 1 && !m->pf_ok) { be->set_error("set_sequences: a sharded model runs batches on the tensor-core kernels, which this model was loaded without"); return SPYB_UNSUPPORTED; }
     cudaSetDevice(be->config.device_id);
     SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
     drop_graphs(m);
@@ -1287,15 +1288,28 @@ spyb_status spyb_model_decode_batch(spyb_model *m, const int32_t *first_tokens, 
     SPYB_CUDA(be, cudaStreamSynchronize(be->stream));   // (first_tokens may be pageable: it is consumed here)
     int64_t launches = 0;
     SPYB_CUDA(be, cudaEventRecord(m->ev0, be->stream));
-    const bool gemm = m->pf_ok && n_seq >= SPYB_PREFILL_MIN_TOKENS && n_seq <= m->pf_chunk;   // enough sequences to fill the tensor-core tiles
+    // enough sequences to fill the tensor-core tiles; a sharded model always takes that path (its all-gathers of whole vectors)
+    const int  tp   = m->info.tp_size, dp = d / tp;
+    const bool gemm = m->pf_ok && n_seq <= m->pf_chunk && (n_seq >= SPYB_PREFILL_MIN_TOKENS || tp > 1);
+    if (tp > 1 && !gemm) { be->set_error("decode_batch: a sharded model takes at most %d sequences", m->pf_chunk); return SPYB_UNSUPPORTED; }
     if (gemm && ensure_prefill_buffers(m) != SPYB_SUCCESS) { return SPYB_FAIL; }
     for (int step = 0; step < n_steps; ++step) {
         if (gemm) {   // the sequences of a step are the "tokens" of one GEMM pass; the head runs on groups of columns
-            SPYB_CUDA(be, launch_embed(m->batch_tokens, n_seq, m->embd, m->embd_type, d, m->pf_x, be->stream)); ++launches;
+            if (tp == 1) { SPYB_CUDA(be, launch_embed(m->batch_tokens, n_seq, m->embd, m->embd_type, d, m->pf_x, be->stream)); ++launches; }
+            else {        // the residual stream in tp parts [tp][n_seq][d / tp], as for a prompt
+                SPYB_CUDA(be, launch_embed(m->batch_tokens, n_seq, m->embd, m->embd_type, d, m->pf_att, be->stream)); ++launches;
+                for (int i = 0; i < tp; ++i) {
+                    SPYB_CUDA(be, cudaMemcpy2DAsync(m->pf_x + (size_t)i * n_seq * dp, (size_t)dp * 4, m->pf_att + (size_t)i * dp, (size_t)d * 4, (size_t)dp * 4, (size_t)n_seq,
+                                                    cudaMemcpyDeviceToDevice, be->stream));
+                }
+            }
             if (run_prefill_layers(m, n_seq, &launches, true) != SPYB_SUCCESS) { return SPYB_FAIL; }
             for (int g0 = 0; g0 < n_seq; g0 += group) {
                 const int T = std::min(group, n_seq - g0);
-                SPYB_CUDA(be, cudaMemcpyAsync(m->x, m->pf_x + (int64_t)g0 * d, (size_t)T * d * 4, cudaMemcpyDeviceToDevice, be->stream));
+                for (int i = 0; i < tp; ++i) {   // whole rows of the group's columns from their parts
+                    SPYB_CUDA(be, cudaMemcpy2DAsync(m->x + (size_t)i * dp, (size_t)d * 4, m->pf_x + (size_t)i * n_seq * dp + (size_t)g0 * dp, (size_t)dp * 4, (size_t)dp * 4, (size_t)T,
+                                                    cudaMemcpyDeviceToDevice, be->stream));
+                }
                 if (run_head_columns(m, T, m->logits_batch + (int64_t)g0 * V, &launches) != SPYB_SUCCESS) { return SPYB_FAIL; }
             }
         }

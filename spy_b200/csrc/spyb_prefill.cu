@@ -157,11 +157,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
         const int row = 32 * quad + lane;
         const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(64 * half);
         const uint32_t dw_addr = a_ring + PF_TILE + 2u * (uint32_t)row, dx_addr = y_ring + PF_TOK * 32 + 32u * (uint32_t)half;
-        float acc[8][8];
+        uint64_t acc[8][4];   // [token][pair]: accumulators 2 pair and 2 pair + 1 of the token, as one packed f32x2 value
 #pragma unroll
         for (int t = 0; t < 8; ++t) {
 #pragma unroll
-            for (int n = 0; n < 8; ++n) { acc[t][n] = 0.f; }
+            for (int n = 0; n < 4; ++n) { acc[t][n] = 0ull; }
         }
         for (int i = 0; i < PF_DBUF; ++i) {   // the offset pattern into this thread's part of every buffer
             tmem_st32_same(tbase + (uint32_t)(i * PF_N), MAGIC_I);
@@ -175,11 +175,14 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
         uint32_t ra[16], rb[16], pattern[16];
 #pragma unroll
         for (int i = 0; i < 16; ++i) { asm volatile("mov.b32 %0, %1;" : "=r"(pattern[i]) : "r"(MAGIC_I)); }   // (opaque to the compiler: 16 live registers)
-        auto fold2 = [&](const uint32_t *r, int t0, const float *sc) {   // two tokens: columns 8 t0 .. 8 t0 + 15
+        const uint64_t minus_magic = f2_pack(-MAGIC_F, -MAGIC_F);
+        auto fold2 = [&](const uint32_t *r, int t0, const uint64_t *sc) {   // two tokens: columns 8 t0 .. 8 t0 + 15
 #pragma unroll
             for (int t = 0; t < 2; ++t) {
 #pragma unroll
-                for (int n = 0; n < 8; ++n) { acc[t0 + t][n] = fmaf(sc[t0 + t], __fsub_rn(__uint_as_float(r[8 * t + n]), MAGIC_F), acc[t0 + t][n]); }
+                for (int n = 0; n < 4; ++n) {   // acc = fma(scale, pattern - 1.5 * 2^23, acc) on two accumulators at a time
+                    acc[t0 + t][n] = f2_fma(sc[t0 + t], f2_add(f2_pack_bits(r[8 * t + 2 * n], r[8 * t + 2 * n + 1]), minus_magic), acc[t0 + t][n]);
+                }
             }
         };
         bool ok = mbar_wait_bounded(d_full(0), 0u, limit);
@@ -199,8 +202,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
                 float dw = h2f((uint16_t)lds16(dw_q + (uint32_t)j * PF_WTILE));
                 if (WT == 2) { dw = __fmul_rn(dw, 0.0625f); }   // exact: undoes the factor 16 of the nibble trick
                 const float4 dxa = lds128f(dx_q + (uint32_t)j * PF_YQ_BYTES), dxb = lds128f(dx_q + (uint32_t)j * PF_YQ_BYTES + 16u);
-                const float sc[8] = {__fmul_rn(dw, dxa.x), __fmul_rn(dw, dxa.y), __fmul_rn(dw, dxa.z), __fmul_rn(dw, dxa.w),
-                                     __fmul_rn(dw, dxb.x), __fmul_rn(dw, dxb.y), __fmul_rn(dw, dxb.z), __fmul_rn(dw, dxb.w)};
+                const float s0 = __fmul_rn(dw, dxa.x), s1 = __fmul_rn(dw, dxa.y), s2 = __fmul_rn(dw, dxa.z), s3 = __fmul_rn(dw, dxa.w);
+                const float s4 = __fmul_rn(dw, dxb.x), s5 = __fmul_rn(dw, dxb.y), s6 = __fmul_rn(dw, dxb.z), s7 = __fmul_rn(dw, dxb.w);
+                const uint64_t sc[8] = {f2_pack(s0, s0), f2_pack(s1, s1), f2_pack(s2, s2), f2_pack(s3, s3),
+                                        f2_pack(s4, s4), f2_pack(s5, s5), f2_pack(s6, s6), f2_pack(s7, s7)};
                 tmem_ld_wait();                       // columns 0..31 of block b are in registers
                 fold2(ra, 0, sc);
                 tmem_ld16(taddr + 32u, ra);
@@ -236,8 +241,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
             for (int t = 0; t < 8; ++t) {
                 const int token = tok_tile * PF_TOK + 8 * half + t;
                 if (token < g.T && (int64_t)row_tile * PF_M + row < g.n_rows) {   // (the last row tile may be partly padding)
-                    const float r0 = __fadd_rn(acc[t][0], acc[t][4]), r1 = __fadd_rn(acc[t][1], acc[t][5]);
-                    const float r2 = __fadd_rn(acc[t][2], acc[t][6]), r3 = __fadd_rn(acc[t][3], acc[t][7]);
+                    float c[8];
+#pragma unroll
+                    for (int n = 0; n < 4; ++n) { f2_unpack(acc[t][n], c[2 * n], c[2 * n + 1]); }
+                    const float r0 = __fadd_rn(c[0], c[4]), r1 = __fadd_rn(c[1], c[5]);
+                    const float r2 = __fadd_rn(c[2], c[6]), r3 = __fadd_rn(c[3], c[7]);
                     const float v = __fadd_rn(__fadd_rn(r0, r2), __fadd_rn(r1, r3));
                     const int64_t i = (int64_t)token * g.out_stride + (int64_t)row_tile * PF_M + row;
                     g.out[i] = g.resid != nullptr ? __fadd_rn(v, g.resid[i]) : v;

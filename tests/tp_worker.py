@@ -45,6 +45,18 @@ def main():
     # output and the FFN activation are all-gathered once per layer
     long_prompt = np.random.default_rng(4).integers(3, cfg.n_vocab, size=41)
     long_logits = m.eval(long_prompt, 0).copy()
+    # batches of sequences on the sharded model (every step one pass of the GEMM path, the sequences as its tokens): 3 and 18
+    # sequences, each with its own 9-token prompt, decoded in lockstep
+    batches = {}
+    for nb in (3, 18):
+        m.set_sequences(nb)
+        prompts = [np.random.default_rng(100 + c).integers(3, cfg.n_vocab, size=9) for c in range(nb)]
+        firsts = []
+        for c in range(nb):
+            m.select_sequence(c)
+            firsts.append(int(np.argmax(m.eval(prompts[c], 0))))
+        b_ids, b_logits = m.decode_batch(firsts, 9, 5, want_logits=True)
+        batches[nb] = (prompts, firsts, b_ids.copy(), b_logits.copy())
     ok = True
     if rank == 0:
         b1 = B.B200Backend(local)
@@ -53,9 +65,15 @@ def main():
         err = float(np.abs(logits - logits1).max())
         same_bits = bool(np.array_equal(np.asarray(logits, dtype=np.float32).view(np.uint32), np.asarray(logits1, dtype=np.float32).view(np.uint32)))
         long_same = bool(np.array_equal(long_logits.view(np.uint32), m1.eval(long_prompt, 0).view(np.uint32)))
-        ok = bool(np.array_equal(ids, ids1)) and same_bits and long_same
+        batch_same = True
+        for nb, (prompts, firsts, b_ids, b_logits) in batches.items():
+            for c in range(nb):
+                i1, l1 = m1.generate(prompts[c], 6)
+                batch_same = batch_same and int(i1[0]) == firsts[c] and bool(np.array_equal(i1[1:], b_ids[:, c]))
+                batch_same = batch_same and bool(np.array_equal(l1[1:].view(np.uint32), b_logits[:, c].view(np.uint32)))
+        ok = bool(np.array_equal(ids, ids1)) and same_bits and long_same and batch_same
         print(f"TP{world} vs TP1 ({'deep' if deep else 'small'} model): max|dlogit| = {err:.3e}, bits identical = {same_bits}, "
-              f"ids identical = {np.array_equal(ids, ids1)}, 41-token prompt bits identical = {long_same} -> {'OK' if ok else 'FAIL'}", flush=True)
+              f"ids identical = {np.array_equal(ids, ids1)}, 41-token prompt bits identical = {long_same}, batches of 3 and 18 sequences bits identical = {batch_same} -> {'OK' if ok else 'FAIL'}", flush=True)
         m1.close(); b1.close()
     m.close(); be.close()
     flag = torch.tensor([0 if ok else 1])
