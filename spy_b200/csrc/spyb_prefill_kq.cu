@@ -11,7 +11,7 @@
 //
 // One MMA per 32-element block for a tile of 128 rows x 64 tokens: A = the block's integer weights as s8 (Q4_K: 0..15,
 // Q6_K: -32..31), B = 128 x 32 s8 whose rows 2 t and 2 t + 1 hold the first and the second 16 activation bytes of token t
-// at their place and zeros elsewhere, D[r][2 t + h] = the integer sum of half h of the block. Q6_K folds the two halves one
+// at their place and zeros elsewhere (the kernel orders the columns 4 (t / 2) + 2 h + t % 2), D[r][column of (t, h)] = the integer sum of half h of the block. Q6_K folds the two halves one
 // after the other with their own scales (they are two of its groups); Q4_K adds them first (exact: both are small integers).
 // The weight tile carries, per row, the two f32 products the restatement forms first (Q4_K: d * sc_j and dmin * m_j;
 // Q6_K: d * sc of the two groups), made at upload with the same f32 multiplication.
@@ -32,29 +32,39 @@ __device__ __forceinline__ float2 lds64f(uint32_t addr) {
     asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
     return v;
 }
-__device__ __forceinline__ float sum_f32(uint32_t bits) { return __fsub_rn(__uint_as_float(bits), MAGIC_F); }
+__device__ __forceinline__ uint64_t lds64u(uint32_t addr) {
+    uint64_t v;
+    asm volatile("ld.shared.u64 %0, [%1];" : "=l"(v) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void lds128_2x64(uint32_t addr, uint64_t &a, uint64_t &b) {
+    asm volatile("ld.shared.v2.u64 {%0,%1}, [%2];" : "=l"(a), "=l"(b) : "r"(addr));
+}
 
-// eight tokens (T0 .. T0 + 7 of a warp's 32) from one register set of 16 columns; `sc` = the row's two scale products of the
-// block, dx_s = the warp's 32 activation scales of the block in shared memory (the 32 block sums lie KQ_TOK * 4 bytes further)
+// eight tokens (T0 .. T0 + 7 of a warp's 32) from one register set of 16 columns, two tokens per packed f32x2 operation:
+// columns 4 u, 4 u + 1 hold the first-half sums of tokens T0 + 2 u and T0 + 2 u + 1, columns 4 u + 2, 4 u + 3 their second-half
+// sums. `scx`, `scy` = the row's two scale products of the block, each in both halves of a pair (Q4_K: scy negated);
+// dx_s = the warp's 32 activation scales of the block in shared memory (the 32 block sums lie KQ_TOK * 4 bytes further)
 template <int WT, int T0>
-__device__ __forceinline__ void kq_fold8(float (&acc)[32], const uint32_t (&r)[16], float2 sc, uint32_t dx_s) {
-    const float4 dxa = lds128f(dx_s + 4u * T0), dxb = lds128f(dx_s + 4u * T0 + 16u);
-    const float dx[8] = {dxa.x, dxa.y, dxa.z, dxa.w, dxb.x, dxb.y, dxb.z, dxb.w};
+__device__ __forceinline__ void kq_fold8(uint64_t (&acc)[16], const uint32_t (&r)[16], uint64_t scx, uint64_t scy, uint32_t dx_s, uint64_t minus_magic) {
+    uint64_t dx[4];
     if (WT == 14) {
+        lds128_2x64(dx_s + 4u * T0, dx[0], dx[1]);
+        lds128_2x64(dx_s + 4u * T0 + 16u, dx[2], dx[3]);
+    }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            acc[T0 + i] = fmaf(__fmul_rn(sc.x, dx[i]), sum_f32(r[2 * i]), acc[T0 + i]);
-            acc[T0 + i] = fmaf(__fmul_rn(sc.y, dx[i]), sum_f32(r[2 * i + 1]), acc[T0 + i]);
+    for (int u = 0; u < 4; ++u) {
+        const uint64_t p0 = f2_add(f2_pack_bits(r[4 * u], r[4 * u + 1]), minus_magic), p1 = f2_add(f2_pack_bits(r[4 * u + 2], r[4 * u + 3]), minus_magic);
+        uint64_t a = acc[T0 / 2 + u];
+        if (WT == 12) { dx[u] = lds64u(dx_s + 4u * T0 + 8u * u); }   // (Q4_K also reads the block sums: fewer values live at a time)
+        if (WT == 14) {
+            a = f2_fma(f2_mul(scx, dx[u]), p0, a);
+            a = f2_fma(f2_mul(scy, dx[u]), p1, a);
+        } else {
+            a = f2_fma(f2_mul(scx, dx[u]), f2_add(p0, p1), a);
+            a = f2_fma(f2_mul(scy, dx[u]), lds64u(dx_s + KQ_TOK * 4 + 4u * T0 + 8u * u), a);   // scy = -(dmin * m_j): the negation commutes with the rounding of the product
         }
-    } else {
-        const float4 ysa = lds128f(dx_s + KQ_TOK * 4 + 4u * T0), ysb = lds128f(dx_s + KQ_TOK * 4 + 4u * T0 + 16u);
-        const float ys[8] = {ysa.x, ysa.y, ysa.z, ysa.w, ysb.x, ysb.y, ysb.z, ysb.w};
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float p = __fadd_rn(sum_f32(r[2 * i]), sum_f32(r[2 * i + 1]));
-            acc[T0 + i] = fmaf(__fmul_rn(sc.x, dx[i]), p, acc[T0 + i]);
-            acc[T0 + i] = fmaf(-__fmul_rn(sc.y, dx[i]), ys[i], acc[T0 + i]);
-        }
+        acc[T0 / 2 + u] = a;
     }
 }
 
@@ -129,7 +139,8 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillG
             }
         }
     } else if (warp == PF_EPI_WARPS + 1) {
-        // ---- expander warp: word w of token tt -> row 2 tt + w / 4 of B, at its own place in the block
+        // ---- expander warp: word w of token tt -> row 4 (tt / 2) + 2 (w / 4) + tt % 2 of B (the same half of two neighbouring
+        // tokens in neighbouring columns of D, for the packed arithmetic of the epilogue), at its own place in the block
         for (int q = 0; q < n_batch; ++q) {
             bool ok = mbar_wait_relaxed(raw_full(q % NQ), (uint32_t)(q / NQ) & 1u, limit);
             ok = __all_sync(0xffffffffu, ok);
@@ -139,7 +150,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillG
                 const uint32_t ysrc_s = y_ring + (uint32_t)(s0 + j) * KQ_YQ, bdst = b_ring + (uint32_t)(s0 + j) * PF_TILE;
 #pragma unroll
                 for (int k = 0; k < KQ_TOK * 8 / 32; ++k) {
-                    const int i = lane + 32 * k, tt = i >> 3, w = i & 7, row = 2 * tt + (w >> 2);
+                    const int i = lane + 32 * k, tt = i >> 3, w = i & 7, row = 4 * (tt >> 1) + 2 * (w >> 2) + (tt & 1);
                     sts32(bdst + (uint32_t)(row >> 3) * 256u + (uint32_t)(w >> 2) * 128u + (uint32_t)(row & 7) * 16u + (uint32_t)(w & 3) * 4u, lds32(ysrc_s + (uint32_t)i * 4u));
                 }
             }
@@ -154,9 +165,10 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillG
         const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(64 * half);
         const uint32_t sc_addr = a_ring + PF_TILE + 8u * (uint32_t)row;
         const uint32_t dx_addr = y_ring + KQ_TOK * 32 + 128u * (uint32_t)half;        // this warp's 32 scales; the block sums lie KQ_TOK * 4 further
-        float acc[32], tot[32];
+        uint64_t acc[16], tot[16];   // packed pairs: tokens 2 u and 2 u + 1 of the warp's 32
 #pragma unroll
-        for (int t = 0; t < 32; ++t) { acc[t] = 0.f; tot[t] = 0.f; }
+        for (int t = 0; t < 16; ++t) { acc[t] = 0ull; tot[t] = 0ull; }
+        const uint64_t minus_magic = f2_pack(-MAGIC_F, -MAGIC_F);
         for (int i = 0; i < PF_DBUF; ++i) {
             tmem_st32_same(tbase + (uint32_t)(i * PF_NCOL), MAGIC_I);
             tmem_st32_same(tbase + (uint32_t)(i * PF_NCOL) + 32u, MAGIC_I);
@@ -180,16 +192,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillG
                 if (b >= nb || !ok) { break; }
                 const uint32_t taddr = tbase + (uint32_t)(j * PF_NCOL);
                 const float2 sc = lds64f(sc_q + (uint32_t)j * KQ_WT);
+                const uint64_t scx = f2_pack(sc.x, sc.x), scy = (WT == 12) ? f2_pack(-sc.y, -sc.y) : f2_pack(sc.y, sc.y);
                 const uint32_t dx_s = dx_q + (uint32_t)j * KQ_YQ;
                 tmem_ld_wait();                       // columns 0..31 of block b are in registers
-                kq_fold8<WT, 0>(acc, ra, sc, dx_s);
+                kq_fold8<WT, 0>(acc, ra, scx, scy, dx_s, minus_magic);
                 tmem_ld16(taddr + 32u, ra);
-                kq_fold8<WT, 8>(acc, rb, sc, dx_s);
+                kq_fold8<WT, 8>(acc, rb, scx, scy, dx_s, minus_magic);
                 tmem_ld16(taddr + 48u, rb);
                 tmem_ld_wait();                       // columns 32..63 too: the buffer has been read, put the offset pattern back
                 tmem_st32_same(taddr, MAGIC_I);
                 tmem_st32_same(taddr + 32u, MAGIC_I);
-                kq_fold8<WT, 16>(acc, ra, sc, dx_s);
+                kq_fold8<WT, 16>(acc, ra, scx, scy, dx_s, minus_magic);
                 const bool more = b + 1 < nb;
                 const uint32_t tnext = tbase + (uint32_t)(((j + 1) % PF_DBUF) * PF_NCOL);
                 if (more) {
@@ -197,11 +210,11 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillG
                     ok = __all_sync(0xffffffffu, ok);
                     if (ok) { tc_fence_after(); tmem_ld16(tnext, ra); }
                 }
-                kq_fold8<WT, 24>(acc, rb, sc, dx_s);
+                kq_fold8<WT, 24>(acc, rb, scx, scy, dx_s, minus_magic);
                 if (more && ok) { tmem_ld16(tnext + 16u, rb); }
                 if ((b & 7) == 7) {                   // a super-block ends: its value joins the row's sum
 #pragma unroll
-                    for (int t = 0; t < 32; ++t) { tot[t] = __fadd_rn(tot[t], acc[t]); acc[t] = 0.f; }
+                    for (int t = 0; t < 16; ++t) { tot[t] = f2_add(tot[t], acc[t]); acc[t] = 0ull; }
                 }
                 tmem_st_wait();
                 tc_fence_before();
@@ -218,9 +231,12 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillG
 #pragma unroll
             for (int t = 0; t < 32; ++t) {
                 const int token = tok_tile * KQ_TOK + 32 * half + t;
+                float lo, hi;
+                f2_unpack(tot[t >> 1], lo, hi);
+                const float v = (t & 1) ? hi : lo;
                 if (token < g.T && (int64_t)row_tile * PF_M + row < g.n_rows) {
                     const int64_t i = (int64_t)token * g.out_stride + (int64_t)row_tile * PF_M + row;
-                    g.out[i] = g.resid != nullptr ? __fadd_rn(tot[t], g.resid[i]) : tot[t];
+                    g.out[i] = g.resid != nullptr ? __fadd_rn(v, g.resid[i]) : v;
                 }
             }
         }
