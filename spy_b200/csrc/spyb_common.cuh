@@ -161,6 +161,41 @@ __device__ __forceinline__ float lane_sum_q8_0(uint32_t w, uint32_t y) {
     return __int_as_float(__dp4a((int)w, (int)y, (int)MAGIC_I)) - MAGIC_F;
 }
 
+// the same sums as bit patterns (of the float MAGIC_F + lane_sum), for callers that subtract MAGIC_F two at a time
+__device__ __forceinline__ uint32_t lane_bits16_q4_0(uint32_t w_x88, uint32_t mult, uint32_t y) {
+    return (uint32_t)__dp4a((int)((w_x88 * mult) & 0xf0f0f0f0u), (int)y, (int)MAGIC_I);
+}
+__device__ __forceinline__ uint32_t lane_bits_q8_0(uint32_t w, uint32_t y) { return (uint32_t)__dp4a((int)w, (int)y, (int)MAGIC_I); }
+
+// Two f32 operations per instruction (sm_100 packed f32x2): each half is the IEEE round-to-nearest operation of the
+// scalar instruction, so results are the bits of two fmaf / __fadd_rn calls at half the issue slots.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t f2_pack_bits(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t f2_mul(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 // hsum_float_8 (vec_util.h:74-81) over the 8 consecutive lanes that hold a0..a7:
 // ((a0+a4) + (a2+a6)) + ((a1+a5) + (a3+a7)). Every lane of the group ends with the same bits.
 __device__ __forceinline__ float hsum8_lanes(float v) {

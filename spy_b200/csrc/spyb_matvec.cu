@@ -565,12 +565,15 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
     const uint32_t row_s = ring_s + lrow * ROWB;
     const uint32_t col_y = (uint32_t)ng * 128, col_ds = (uint32_t)ng * 16;
 
-    float acc[TM][2 * NP];   // [pair][0] = accumulator j, [pair][1] = accumulator j + 4, j = part * NP + pair
+    // pair k of column t as one packed f32x2 value: low half = accumulator j, high half = accumulator j + 4, j = part * NP + k
+    // (both take the same scale in every step, so one packed subtraction and one packed FMA serve the two)
+    uint64_t acc2[TM][NP];
 #pragma unroll
     for (int t = 0; t < TM; ++t) {
 #pragma unroll
-        for (int a = 0; a < 2 * NP; ++a) { acc[t][a] = 0.f; }
+        for (int k = 0; k < NP; ++k) { acc2[t][k] = 0ull; }
     }
+    const uint64_t minus_magic = f2_pack(-MAGIC_F, -MAGIC_F);
 
     int64_t  cu = my_first; int crec = 0, slot = 0; uint32_t parity = 0;
     uint32_t ya = y_s, da = ds_s;
@@ -598,25 +601,26 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
                 for (int t = 0; t < TM; ++t) {
                     const float4 ds = lds128f(da + t * col_ds);
                     const float  s0 = __fmul_rn(f01.x, ds.x), s1 = __fmul_rn(f01.y, ds.y), s2 = __fmul_rn(f23.x, ds.z), s3 = __fmul_rn(f23.y, ds.w);
+                    const uint64_t S0 = f2_pack(s0, s0), S1 = f2_pack(s1, s1), S2 = f2_pack(s2, s2), S3 = f2_pack(s3, s3);
 #pragma unroll
                     for (int k = 0; k < NP; ++k) {
                         const int j = part * NP + k;
                         // accumulator j: Q4_0 high nibbles of word j (values 16 + 4j.. meet activation word 4 + j), Q8_0 word j;
                         // accumulator 4 + j: Q4_0 low nibbles of word j (activation word j), Q8_0 word 4 + j
                         const uint4 y0 = lds128(ya + t * col_y + ((WT == 8) ? j : 4 + j) * 16), y1 = lds128(ya + t * col_y + ((WT == 8) ? 4 + j : j) * 16);
-                        float a0 = acc[t][2 * k], a1 = acc[t][2 * k + 1];
+                        uint64_t a = acc2[t][k];
                         if (WT == 2) {
-                            a0 = fmaf(s0, lane_sum16_q4_0(w[k].x, 1u, y0.x), a0);  a1 = fmaf(s0, lane_sum16_q4_0(w[k].x, 16u, y1.x), a1);
-                            a0 = fmaf(s1, lane_sum16_q4_0(w[k].y, 1u, y0.y), a0);  a1 = fmaf(s1, lane_sum16_q4_0(w[k].y, 16u, y1.y), a1);
-                            a0 = fmaf(s2, lane_sum16_q4_0(w[k].z, 1u, y0.z), a0);  a1 = fmaf(s2, lane_sum16_q4_0(w[k].z, 16u, y1.z), a1);
-                            a0 = fmaf(s3, lane_sum16_q4_0(w[k].w, 1u, y0.w), a0);  a1 = fmaf(s3, lane_sum16_q4_0(w[k].w, 16u, y1.w), a1);
+                            a = f2_fma(S0, f2_add(f2_pack_bits(lane_bits16_q4_0(w[k].x, 1u, y0.x), lane_bits16_q4_0(w[k].x, 16u, y1.x)), minus_magic), a);
+                            a = f2_fma(S1, f2_add(f2_pack_bits(lane_bits16_q4_0(w[k].y, 1u, y0.y), lane_bits16_q4_0(w[k].y, 16u, y1.y)), minus_magic), a);
+                            a = f2_fma(S2, f2_add(f2_pack_bits(lane_bits16_q4_0(w[k].z, 1u, y0.z), lane_bits16_q4_0(w[k].z, 16u, y1.z)), minus_magic), a);
+                            a = f2_fma(S3, f2_add(f2_pack_bits(lane_bits16_q4_0(w[k].w, 1u, y0.w), lane_bits16_q4_0(w[k].w, 16u, y1.w)), minus_magic), a);
                         } else {
-                            a0 = fmaf(s0, lane_sum_q8_0(w[2 * k].x, y0.x), a0);  a1 = fmaf(s0, lane_sum_q8_0(w[2 * k + 1].x, y1.x), a1);
-                            a0 = fmaf(s1, lane_sum_q8_0(w[2 * k].y, y0.y), a0);  a1 = fmaf(s1, lane_sum_q8_0(w[2 * k + 1].y, y1.y), a1);
-                            a0 = fmaf(s2, lane_sum_q8_0(w[2 * k].z, y0.z), a0);  a1 = fmaf(s2, lane_sum_q8_0(w[2 * k + 1].z, y1.z), a1);
-                            a0 = fmaf(s3, lane_sum_q8_0(w[2 * k].w, y0.w), a0);  a1 = fmaf(s3, lane_sum_q8_0(w[2 * k + 1].w, y1.w), a1);
+                            a = f2_fma(S0, f2_add(f2_pack_bits(lane_bits_q8_0(w[2 * k].x, y0.x), lane_bits_q8_0(w[2 * k + 1].x, y1.x)), minus_magic), a);
+                            a = f2_fma(S1, f2_add(f2_pack_bits(lane_bits_q8_0(w[2 * k].y, y0.y), lane_bits_q8_0(w[2 * k + 1].y, y1.y)), minus_magic), a);
+                            a = f2_fma(S2, f2_add(f2_pack_bits(lane_bits_q8_0(w[2 * k].z, y0.z), lane_bits_q8_0(w[2 * k + 1].z, y1.z)), minus_magic), a);
+                            a = f2_fma(S3, f2_add(f2_pack_bits(lane_bits_q8_0(w[2 * k].w, y0.w), lane_bits_q8_0(w[2 * k + 1].w, y1.w)), minus_magic), a);
                         }
-                        acc[t][2 * k] = a0; acc[t][2 * k + 1] = a1;
+                        acc2[t][k] = a;
                     }
                 }
             }
@@ -630,20 +634,21 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_rows_kernel(const Matvec
             float h[TM];
 #pragma unroll
             for (int t = 0; t < TM; ++t) {
+                float acc[1][2 * NP];   // (indexed [0][..] below: this column's accumulators unpacked)
+#pragma unroll
+                for (int k = 0; k < NP; ++k) { f2_unpack(acc2[t][k], acc[0][2 * k], acc[0][2 * k + 1]); acc2[t][k] = 0ull; }
                 if (LPR == 1) {
-                    h[t] = __fadd_rn(__fadd_rn(__fadd_rn(acc[t][0], acc[t][1]), __fadd_rn(acc[t][4], acc[t][5])),
-                                     __fadd_rn(__fadd_rn(acc[t][2], acc[t][3]), __fadd_rn(acc[t][6], acc[t][7])));
+                    h[t] = __fadd_rn(__fadd_rn(__fadd_rn(acc[0][0], acc[0][1]), __fadd_rn(acc[0][4], acc[0][5])),
+                                     __fadd_rn(__fadd_rn(acc[0][2], acc[0][3]), __fadd_rn(acc[0][6], acc[0][7])));
                 } else if (LPR == 2) {   // part 0 holds p0, p1; part 1 holds p2, p3
-                    const float pa = __fadd_rn(acc[t][0], acc[t][1]), pb = __fadd_rn(acc[t][2], acc[t][3]);
+                    const float pa = __fadd_rn(acc[0][0], acc[0][1]), pb = __fadd_rn(acc[0][2], acc[0][3]);
                     const float qa = __fadd_rn(pa, __shfl_xor_sync(0xffffffffu, pa, 16)), qb = __fadd_rn(pb, __shfl_xor_sync(0xffffffffu, pb, 16));
                     h[t] = __fadd_rn(qa, qb);
                 } else {                 // part q holds p_q
-                    const float pa = __fadd_rn(acc[t][0], acc[t][1]);
+                    const float pa = __fadd_rn(acc[0][0], acc[0][1]);
                     const float qa = __fadd_rn(pa, __shfl_xor_sync(0xffffffffu, pa, 16));
                     h[t] = __fadd_rn(qa, __shfl_xor_sync(0xffffffffu, qa, 8));
                 }
-#pragma unroll
-                for (int a = 0; a < 2 * NP; ++a) { acc[t][a] = 0.f; }
             }
 #pragma unroll
             for (int t = 0; t < TM; ++t) {
