@@ -46,6 +46,9 @@ ARCH, WTYPE_NAME = "7b", "q4_0"
 #   5: 13B architecture, Q4_0, prompt of 128 ids, decode 128 (the configuration tensor parallelism is specified on)
 CONFIGS = {
     1: dict(arch="7b", wtype="q4_0", seed=1234, n_prompt=8, n_ctx=512, workload=WORKLOAD),
+    2: dict(arch="7b", wtype="q4_0", seed=99, n_prompt=0, n_ctx=0,
+            workload="MatMul operator sweep: Q4_0 / Q4_K / Q8_0 weights N(0, 0.02) x f32 activations N(0, 1), shapes 4096x4096, 11008x4096, "
+                     "4096x11008, 32000x4096 (rows x K), batch 1 / 4 / 16 (seed 99)"),
     3: dict(arch="7b", wtype="q4_k_m", seed=1236, n_prompt=512, n_ctx=1024,
             workload="llama2-7b-arch Q4_K_M-style (Q6_K for attn_v, ffn_down, output; Q4_K elsewhere) bs1, prompt 512 + decode, ctx 1024 (synthetic GGUF, seed 1236)"),
     4: dict(arch="7b", wtype="q8_0", seed=1237, n_prompt=3968, n_ctx=4096,
@@ -59,6 +62,59 @@ def select_config(n):
     global SEED, N_PROMPT, N_CTX, WORKLOAD, ARCH, WTYPE_NAME
     c = CONFIGS[n]
     SEED, N_PROMPT, N_CTX, WORKLOAD, ARCH, WTYPE_NAME = c["seed"], c["n_prompt"], c["n_ctx"], c["workload"], c["arch"], c["wtype"]
+
+
+def run_operator_sweep(args):
+    """--config 2: every (weight type, shape, batch) of the operator sweep through spyb_submit(MatMul) on device-resident
+    operands; device time from events on the backend's stream around back-to-back submits that walk over enough copies of
+    the weights to exceed the L2 cache. Algorithmic bytes = quantized weights + f32 activations in + f32 results out."""
+    import numpy as np
+    from spy_b200 import backend as B, quants
+    be = B.B200Backend(0)
+    peak, peak_kind = measured_peak()
+    rng = np.random.default_rng(99)
+    shapes = [(4096, 4096), (11008, 4096), (4096, 11008), (32000, 4096)]
+    types = [("q4_0", quants.Q4_0, 18 / 32), ("q4_k", quants.Q4_K, 144 / 256), ("q8_0", quants.Q8_0, 34 / 32)]
+    sampler = ClockSampler(0); sampler.start()
+    cases, launches = [], 0
+    for n, k in shapes:
+        wf = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+        for tname, qt, bpw in types:
+            w = quants.quantize(wf, qt)
+            w_bytes = int(n * k * bpw)
+            copies = max(2, -(-300_000_000 // w_bytes))
+            pws = [be.upload_constant(f"sweep_{tname}_{n}_{k}_{c}", w, qt, (k, n)) for c in range(copies)]
+            for t in (1, 4, 16):
+                x = rng.standard_normal((t, k)).astype(np.float32)
+                px = be.upload(x); po = be.alloc_memory(n * t * 4)
+                descs = []
+                for pw in pws:
+                    d = B.OpDesc(); d.op_type, d.num_input = B.OP["MatMul"], 2
+                    d.input[0] = B.make_tensor(pw, qt, (k, n), None, B.NODE_CONSTANT)
+                    d.input[1] = B.make_tensor(px, B.FP32, (k, t))
+                    d.output = B.make_tensor(po, B.FP32, (n, t))
+                    descs.append(d)
+                reps = max(args.steps, 2 * copies)
+                be.submit_timed(descs, max(args.warmup, copies))
+                ms = be.submit_timed(descs, reps)
+                us = ms * 1e3 / reps
+                alg = w_bytes + 4 * k * t + 4 * n * t
+                cases.append({"type": tname, "rows": n, "k": k, "batch": t, "us": us, "gbs": alg / us / 1e3, "frac": alg / us / 1e3 / peak, "bytes": alg, "weight_copies": copies})
+                launches += reps
+                be.dealloc_memory(px, x.nbytes); be.dealloc_memory(po, n * t * 4)
+    clocks = sampler.stop()
+    be.close()
+    geo = float(np.exp(np.mean([np.log(c["gbs"]) for c in cases])))
+    dom = max((c for c in cases if c["batch"] == 1), key=lambda c: c["gbs"])
+    line = {"metric": "MatMul operator sweep, geometric mean of achieved GB/s", "value": geo, "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": float(np.mean([c["us"] for c in cases])) / 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "int8 block dots, f32 accumulate", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "l2": "every case walks over copies of its weights that total 300 MB and more (L2: 126 MB)",
+                       "timing": "CUDA events on the backend's stream around back-to-back spyb_submit(MatMul) calls"},
+            "roofline": {"bound": "hbm", "kernel": f"MatMul {dom['type']} {dom['rows']}x{dom['k']} batch 1 (best single-column case)", "achieved": dom["gbs"], "peak": peak,
+                         "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": dom["frac"], "traffic": None},
+            "cpu_baseline": None, "e2e": None, "gpu_launches": launches, "clocks": clocks, "sweep": cases}
+    print(json.dumps(line))
 
 
 def model_path():
@@ -232,8 +288,14 @@ def main():
     select_config(args.config)
     if args.config != 1:
         args.no_cpu_baseline = True     # the CPU arm needs minutes to hours for these prompts; parity for them is in tests/
+    if args.impl == "reference" and args.config == 2:
+        print(json.dumps({"impl": "reference", "unavailable": "the operator sweep is timed on the GPU arm only; its parity against the CPU operators is in tests/test_gpu_ops.py"}))
+        return
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.config == 2:
+        run_operator_sweep(args)
         return
 
     import torch

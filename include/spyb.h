@@ -122,6 +122,10 @@ void *spyb_upload_constant(spyb_backend *backend, const char *name, const void *
 spyb_status spyb_submit(spyb_backend *backend, spyb_op_desc *desc, void (*callback)(void *), void *user);
 /* waits for everything submitted so far */
 spyb_status spyb_sync(spyb_backend *backend);
+/* measurement aid: submits descs[0], descs[1], ... round-robin `repeats` times (no callbacks; device-resident operands) between
+ * two events on the backend's stream and returns the device time of the whole sequence in milliseconds. Passing several
+ * descriptors whose operands together exceed the L2 cache gives cold-cache figures for a single operator. */
+spyb_status spyb_submit_timed(spyb_backend *backend, spyb_op_desc *descs, int32_t n_descs, int32_t repeats, float *ms_out);
 
 /* ---- staging of IO tensors, which the reference keeps in host vectors (model/src/llm/model/llama.cpp:259-263) */
 spyb_status spyb_memcpy_h2d(spyb_backend *backend, void *dst_device, const void *src_host, uint64_t bytes);

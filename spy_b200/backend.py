@@ -85,6 +85,7 @@ def lib():
         "spyb_is_support": (i32, [i32]),
         "spyb_upload_constant": (vp, [vp, C.c_char_p, vp, u64, i32, C.POINTER(i64)]),
         "spyb_submit": (i32, [vp, C.POINTER(OpDesc), vp, vp]),
+        "spyb_submit_timed": (i32, [vp, C.POINTER(OpDesc), i32, i32, C.POINTER(C.c_float)]),
         "spyb_sync": (i32, [vp]),
         "spyb_memcpy_h2d": (i32, [vp, vp, vp, u64]),
         "spyb_memcpy_d2h": (i32, [vp, vp, vp, u64]),
@@ -237,6 +238,13 @@ class B200Backend:
             cb = CALLBACK(lambda _user: callback())
             self._callbacks.append(cb)   # keep alive until it has fired
         self._check(self._l.spyb_submit(self.h, C.byref(desc), cb, None))
+
+    def submit_timed(self, descs, repeats: int) -> float:
+        """Device time in ms of `repeats` submits that walk round-robin over the descriptors (measurement aid)."""
+        arr = (OpDesc * len(descs))(*descs)
+        ms = C.c_float(0.0)
+        self._check(self._l.spyb_submit_timed(self.h, arr, len(descs), int(repeats), C.byref(ms)))
+        return float(ms.value)
 
     def set_wait_limit_ns(self, ns: int) -> None:
         self._check(self._l.spyb_set_wait_limit_ns(self.h, int(ns)))

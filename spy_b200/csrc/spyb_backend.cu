@@ -296,6 +296,7 @@ void *spyb_upload_constant(spyb_backend *be, const char *name, const void *host_
         }
     }
     be->constants[key] = raw;
+    be->const_types[raw] = number_type;
     return raw;
 }
 
@@ -531,15 +532,119 @@ void stage_release(spyb_backend *be, Staged *s) {
     s->dev = nullptr; s->temp = false;
 }
 
+// MatMul of 16 and more activation columns against an uploaded constant: the tcgen05 GEMM of the prompt path (same bits as
+// the mat-vec kernels). The matrix gets a second copy in that kernel's tile layout at first use, kept with the constant.
+// Returns SPYB_UNSUPPORTED without an error text when the operands do not qualify (the caller then takes the mat-vec route).
+spyb_status run_matmul_gemm(spyb_backend *be, const spyb_tensor &w, const spyb_tensor &x, void *out_dev) {
+    const int type = w.number_type;
+    const bool kq = type == SPYB_Q4_K || type == SPYB_Q6_K;
+    if (type != SPYB_Q4_0 && type != SPYB_Q8_0 && !kq) { return SPYB_UNSUPPORTED; }
+    const int64_t k = w.elements[0], n_rows = w.elements[1], T = x.elements[1] * x.elements[2] * x.elements[3];
+    if (T < SPYB_PREFILL_MIN_TOKENS || w.node_type != SPYB_NODE_CONSTANT || k != x.elements[0] || k < QK || k % QK != 0 || k > PF_MAX_K || (kq && k % 256 != 0) ||
+        n_rows < 1 || w.elements[2] != 1 || w.elements[3] != 1 || !tensor_contiguous(w) || !tensor_contiguous(x) ||
+        (reinterpret_cast<uintptr_t>(x.data) & 15) || (reinterpret_cast<uintptr_t>(out_dev) & 3)) {
+        return SPYB_UNSUPPORTED;
+    }
+    // Q4_0 / Q8_0: a GEMM CTA walks all of K for 128 rows x 16 columns, so few tiles leave most SMs idle and passes of four
+    // columns through the mat-vec kernel are faster (measured: 4096 rows x 16 columns slower, 11008 x 16 faster)
+    if (!kq && ((n_rows + PF_ROWS - 1) / PF_ROWS) * ((T + PF_TOK - 1) / PF_TOK) < 74) { return SPYB_UNSUPPORTED; }
+    static const bool off = [] { const char *e = std::getenv("SPYB_PREFILL"); return e != nullptr && e[0] == '0'; }();
+    if (off) { return SPYB_UNSUPPORTED; }
+    const int nb = (int)(k / QK);
+    uint8_t *tiles = nullptr;
+    {
+        std::lock_guard<std::mutex> g(be->const_mutex);
+        auto ct = be->const_types.find(w.data);
+        if (ct == be->const_types.end() || ct->second != type) { return SPYB_UNSUPPORTED; }   // not (or no longer) the constant that was uploaded
+        auto it = be->pf_tiles.find(w.data);
+        if (it != be->pf_tiles.end()) { tiles = it->second; }
+        else {
+            const int64_t rb = kq ? (k / 256) * (type == SPYB_Q4_K ? 144 : 210) : (int64_t)nb * (type == SPYB_Q4_0 ? 18 : 34);
+            const size_t wbytes = prefill_weight_bytes(type, n_rows, nb);
+            void *raw = nullptr;
+            SPYB_CUDA(be, cudaMalloc(&raw, wbytes));
+            be->owned.push_back(raw);
+            tiles = static_cast<uint8_t *>(raw);
+            SPYB_CUDA(be, cudaMemsetAsync(tiles, 0, wbytes, be->stream));   // (rows that pad the last tile stay zero)
+            SPYB_CUDA(be, launch_prefill_retile(type, static_cast<const uint8_t *>(w.data), rb, n_rows, nb, tiles, 0, be->stream));
+            be->pf_tiles[w.data] = tiles;
+        }
+    }
+    const int64_t chunk = 1024;
+    const size_t ybytes = prefill_act_bytes((int)std::min(chunk, T), nb);
+    void *yq = be->arena.alloc(ybytes);
+    if (yq == nullptr) { be->set_error("MatMul: out of device memory for the quantized activations"); return SPYB_FAIL; }
+    struct Release { spyb_backend *be; void *a; size_t n; ~Release() { be->arena.free(a, n); } } release{be, yq, ybytes};   // (stream-ordered reuse)
+    for (int64_t t0 = 0; t0 < T; t0 += chunk) {
+        const int Tc = (int)std::min(chunk, T - t0);
+        SPYB_CUDA(be, cudaMemsetAsync(yq, 0, prefill_act_bytes(Tc, nb), be->stream));
+        SPYB_CUDA(be, launch_prefill_quant(static_cast<const float *>(x.data) + t0 * k, k, Tc, (int)k, nullptr, 0.f, static_cast<uint8_t *>(yq), be->stream, kq));
+        PrefillGemm g;
+        g.w = tiles; g.type = type; g.n_rows = n_rows; g.nb = nb; g.yq = static_cast<uint8_t *>(yq); g.T = Tc;
+        g.out = static_cast<float *>(out_dev) + t0 * n_rows; g.out_stride = n_rows;
+        g.error_flag = be->d_error_flag; g.wait_limit_ns = be->wait_limit_ns;
+        SPYB_CUDA(be, launch_prefill_gemm(g, be->stream));
+    }
+    return SPYB_SUCCESS;
+}
+
+// MatMul of fewer than 16 columns against an uploaded Q4_K / Q6_K constant: the model path's K-quant mat-vec kernel, one column
+// per launch (activations quantized to Q8_0 first, the arithmetic of the restatement; the tensor-core route above gives the
+// same bits for 16 columns and more). Q6_K rows get a copy in that kernel's layout at first use.
+spyb_status run_matmul_kq_constant(spyb_backend *be, const spyb_tensor &w, const spyb_tensor &x, void *out_dev) {
+    const int type = w.number_type;
+    const int64_t k = w.elements[0], n_rows = w.elements[1], T = x.elements[1] * x.elements[2] * x.elements[3];
+    if (w.node_type != SPYB_NODE_CONSTANT || k != x.elements[0] || k % 256 != 0 || k > 256 * 32 * 4 || n_rows < 2 || (n_rows & 1) || w.elements[2] != 1 || w.elements[3] != 1 ||
+        !tensor_contiguous(w) || !tensor_contiguous(x) || (reinterpret_cast<uintptr_t>(x.data) & 15) || (reinterpret_cast<uintptr_t>(out_dev) & 3) ||
+        (reinterpret_cast<uintptr_t>(w.data) & 15)) {
+        return SPYB_UNSUPPORTED;
+    }
+    const uint8_t *rows = static_cast<const uint8_t *>(w.data);
+    {
+        std::lock_guard<std::mutex> g(be->const_mutex);
+        auto ct = be->const_types.find(w.data);
+        if (ct == be->const_types.end() || ct->second != type) { return SPYB_UNSUPPORTED; }
+        if (type == SPYB_Q6_K) {
+            auto it = be->kq_relaid.find(w.data);
+            if (it != be->kq_relaid.end()) { rows = it->second; }
+            else {
+                void *raw = nullptr;
+                SPYB_CUDA(be, cudaMalloc(&raw, (size_t)n_rows * kq_row_bytes(type, k) + 64));
+                be->owned.push_back(raw);
+                SPYB_CUDA(be, launch_kq_relayout_q6k(static_cast<const uint8_t *>(w.data), n_rows, k, static_cast<uint8_t *>(raw), be->stream));
+                be->kq_relaid[w.data] = static_cast<uint8_t *>(raw);
+                rows = static_cast<const uint8_t *>(raw);
+            }
+        }
+    }
+    for (int64_t t = 0; t < T; ++t) {
+        MatvecParams p;
+        p.A.type = SPYB_Q4_K; p.A.k = k; p.A.nb = (int)(k / QK); p.A.nbp = p.A.nb; p.A.n_rows = n_rows;   // (only the shape is used)
+        p.kq[0].w = rows; p.kq[0].type = type; p.kq[0].n_rows = n_rows; p.kq[0].row_bytes = kq_row_bytes(type, k); p.kq_n = 1;
+        p.T = 1; p.pro = PRO_QUANT; p.x = static_cast<const float *>(x.data) + t * k; p.x_stride = k;
+        p.epi = EPI_STORE; p.out = static_cast<float *>(out_dev) + t * n_rows; p.out_stride = n_rows;
+        SPYB_CUDA(be, launch_matvec_kq(p, be->launch_cfg(false)));
+    }
+    return SPYB_SUCCESS;
+}
+
 spyb_status run_matmul(spyb_backend *be, spyb_op_desc *d, void *out_dev) {
     const spyb_tensor &w = d->input[0], &x = d->input[1];
     if (x.number_type != SPYB_FP32) { be->set_error("MatMul: activations of type %d", x.number_type); return SPYB_UNSUPPORTED; }
+    {
+        const spyb_status st = run_matmul_gemm(be, w, x, out_dev);
+        if (st != SPYB_UNSUPPORTED) { return st; }
+    }
     if (w.number_type == SPYB_FP16) {
         SPYB_CUDA(be, launch_matmul_f16(to_strided(w, w.data), to_strided(x, x.data), to_strided(d->output, out_dev), be->stream));
         return SPYB_SUCCESS;
     }
     if (w.number_type == SPYB_Q4_K || w.number_type == SPYB_Q6_K) {
-        // layout-only types in the reference: decoded weights times f32 activations (tolerance-level parity)
+        {
+            const spyb_status st = run_matmul_kq_constant(be, w, x, out_dev);
+            if (st != SPYB_UNSUPPORTED) { return st; }
+        }
+        // operands that are not uploaded constants: decoded weights times f32 activations (tolerance-level parity)
         if (!tensor_contiguous(w) || !tensor_contiguous(x) || w.elements[2] != 1 || w.elements[3] != 1 || w.elements[0] % 256 != 0 || w.elements[0] != x.elements[0]) {
             be->set_error("MatMul: K-quant weights need contiguous 2-D operands with K a multiple of 256");
             return SPYB_UNSUPPORTED;
@@ -710,6 +815,25 @@ spyb_status spyb_submit(spyb_backend *be, spyb_op_desc *d, void (*callback)(void
         { std::lock_guard<std::mutex> g(be->cb_mutex); be->cb_queue.push_back(cb); }
         be->cb_cv.notify_one();
     }
+    return SPYB_SUCCESS;
+}
+
+spyb_status spyb_submit_timed(spyb_backend *be, spyb_op_desc *descs, int32_t n_descs, int32_t repeats, float *ms_out) {
+    if (be == nullptr || descs == nullptr || n_descs < 1 || repeats < 1 || ms_out == nullptr) { return SPYB_FAIL; }
+    cudaSetDevice(be->config.device_id);
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    SPYB_CUDA(be, cudaEventCreate(&e0));
+    SPYB_CUDA(be, cudaEventCreate(&e1));
+    spyb_status st = SPYB_SUCCESS;
+    cudaError_t err = cudaEventRecord(e0, be->stream);
+    for (int r = 0; r < repeats && st == SPYB_SUCCESS && err == cudaSuccess; ++r) { st = spyb_submit(be, &descs[r % n_descs], nullptr, nullptr); }
+    if (err == cudaSuccess) { err = cudaEventRecord(e1, be->stream); }
+    if (err == cudaSuccess) { err = cudaStreamSynchronize(be->stream); }
+    if (err == cudaSuccess && st == SPYB_SUCCESS) { err = cudaEventElapsedTime(ms_out, e0, e1); }
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    if (st != SPYB_SUCCESS) { return st; }
+    if (err != cudaSuccess) { be->set_error("submit_timed: %s", cudaGetErrorString(err)); return SPYB_FAIL; }
+    if (be->device_error()) { return SPYB_FAIL; }
     return SPYB_SUCCESS;
 }
 

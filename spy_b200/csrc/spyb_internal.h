@@ -74,6 +74,9 @@ struct spyb_backend {
     std::mutex                               const_mutex;
     std::unordered_map<std::string, void *>  constants;
     std::unordered_map<const void *, spyb::DevMatrix> retiled;
+    std::unordered_map<const void *, int>             const_types;   // raw pointer -> number type of every uploaded constant
+    std::unordered_map<const void *, uint8_t *>       kq_relaid;     // raw pointer of a Q6_K constant -> its rows in the K-quant mat-vec kernel's layout (made at first use)
+    std::unordered_map<const void *, uint8_t *>       pf_tiles;      // raw pointer -> the same matrix in the prompt GEMM's tile layout (made at first use)
     std::vector<void *>                      owned;   // cudaMalloc'd blocks to release at destroy
 
     // completion callbacks

@@ -223,6 +223,30 @@ def test_matmul_operator_sweep(be, oracle, qt, n, k, t):
     assert np.isfinite(got).all()
 
 
+@pytest.mark.parametrize("qt", [quants.Q4_0, quants.Q8_0, quants.Q4_K, quants.Q6_K])
+@pytest.mark.parametrize("n,k,t", [(132, 512, 1), (132, 512, 5), (200, 1024, 16), (260, 2816, 41), (1100, 512, 150)])
+def test_matmul_on_uploaded_constants_takes_the_model_kernels(be, oracle, qt, n, k, t):
+    """MatMul through spyb_submit against a constant from spyb_upload_constant: K-quant constants run the K-quant mat-vec
+    kernel column by column, and 16 columns and more run the tcgen05 GEMM against a tile copy made at first use (K-quants
+    always, Q4_0 / Q8_0 when rows x columns give the GEMM enough tiles: the last case). Either way the oracle's bits (for
+    K-quants: the restatement's)."""
+    rng = np.random.default_rng(n + k + t + qt)
+    w = quants.quantize((rng.standard_normal((n, k)) * 0.02).astype(np.float32), qt)
+    x = rng.standard_normal((t, k)).astype(np.float32)
+    pw = be.upload_constant(f"const_{qt}_{n}_{k}_{t}", w, qt, (k, n))
+    want = oracle.matmul(qt, w, k, n, x)
+    for _ in range(2):   # the second call finds the copies the first one made
+        d = B.OpDesc(); d.op_type, d.num_input = B.OP["MatMul"], 2
+        px = be.upload(x); po = be.alloc_memory(n * t * 4)
+        d.input[0] = B.make_tensor(pw, qt, (k, n), None, B.NODE_CONSTANT)
+        d.input[1] = B.make_tensor(px, B.FP32, (k, t))
+        d.output = B.make_tensor(po, B.FP32, (n, t))
+        be.submit(d); be.sync()
+        got = be.download(po, (t, n), np.float32)
+        be.dealloc_memory(px, x.nbytes); be.dealloc_memory(po, n * t * 4)
+        assert np.array_equal(bits(got), bits(want))
+
+
 def test_matmul_linearity_full_size(be):
     """Size-independent property at the 7B head shape: W(2x) == 2 W(x) exactly (power-of-two scaling commutes with Q8_0)."""
     rng = np.random.default_rng(5)
