@@ -588,8 +588,8 @@ spyb_status run_matmul_gemm(spyb_backend *be, const spyb_tensor &w, const spyb_t
     return SPYB_SUCCESS;
 }
 
-// MatMul of fewer than 16 columns against an uploaded Q4_K / Q6_K constant: the model path's K-quant mat-vec kernel, one column
-// per launch (activations quantized to Q8_0 first, the arithmetic of the restatement; the tensor-core route above gives the
+// MatMul of fewer than 16 columns against an uploaded Q4_K / Q6_K constant: the model path's K-quant mat-vec kernel, up to four
+// columns per launch (activations quantized to Q8_0 first, the arithmetic of the restatement; the tensor-core route above gives the
 // same bits for 16 columns and more). Q6_K rows get a copy in that kernel's layout at first use.
 spyb_status run_matmul_kq_constant(spyb_backend *be, const spyb_tensor &w, const spyb_tensor &x, void *out_dev) {
     const int type = w.number_type;
@@ -617,11 +617,11 @@ spyb_status run_matmul_kq_constant(spyb_backend *be, const spyb_tensor &w, const
             }
         }
     }
-    for (int64_t t = 0; t < T; ++t) {
+    for (int64_t t = 0; t < T; t += KQ_MAX_COLUMNS) {
         MatvecParams p;
         p.A.type = SPYB_Q4_K; p.A.k = k; p.A.nb = (int)(k / QK); p.A.nbp = p.A.nb; p.A.n_rows = n_rows;   // (only the shape is used)
         p.kq[0].w = rows; p.kq[0].type = type; p.kq[0].n_rows = n_rows; p.kq[0].row_bytes = kq_row_bytes(type, k); p.kq_n = 1;
-        p.T = 1; p.pro = PRO_QUANT; p.x = static_cast<const float *>(x.data) + t * k; p.x_stride = k;
+        p.T = (int)std::min<int64_t>(KQ_MAX_COLUMNS, T - t); p.pro = PRO_QUANT; p.x = static_cast<const float *>(x.data) + t * k; p.x_stride = k;
         p.epi = EPI_STORE; p.out = static_cast<float *>(out_dev) + t * n_rows; p.out_stride = n_rows;
         SPYB_CUDA(be, launch_matvec_kq(p, be->launch_cfg(false)));
     }

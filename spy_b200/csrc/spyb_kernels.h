@@ -187,6 +187,7 @@ int         smem_ledger_selftest();   // host-only check of SmemLedger, 0 = pass
 size_t      matvec_smem_bytes(int nb, int T);
 int         matvec_max_columns(int nb);   // most activation columns one launch can hold in shared memory for rows of nb blocks
 cudaError_t launch_matvec(const MatvecParams &p, const LaunchCfg &cfg);
+constexpr int KQ_MAX_COLUMNS = 4;                                             // activation columns of one pass of the K-quant mat-vec kernel
 cudaError_t launch_matvec_kq(const MatvecParams &p, const LaunchCfg &cfg);   // (launch_matvec forwards to it when p.kq_n > 0)
 int64_t     kq_row_bytes(int type, int64_t k);                             // bytes of one K-quant row in device memory
 cudaError_t launch_kq_relayout_q6k(const uint8_t *raw, int64_t n_rows, int64_t k, uint8_t *dst, cudaStream_t s);

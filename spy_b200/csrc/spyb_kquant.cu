@@ -33,15 +33,16 @@ constexpr int KQ_WARPS   = KQ_THREADS / WARP;
 constexpr int KQ_SB_WORDS = 68;   // words per super-block of activations in shared memory: 64 + 4, so that a block's eight words are two aligned
                                   // 128-bit reads and the eight lanes of a quarter-warp (one super-block each) hit distinct banks
 
-struct KqPlanes { uint32_t *y; float *dx; int *ysum; };
+// the planes of one activation column; column t of a pass lies t * col 32-bit words further (all three planes)
+struct KqPlanes { uint32_t *y; float *dx; int *ysum; int col; };
 
 // NormRMS + Mul(weight) (optional) + Quantizator<FP32,Q8_0> of one activation column into the K-quant planes; the
 // arithmetic is that of the Q4_0 / Q8_0 kernels' prologue (same device functions)
 template <bool NORM>
-__device__ __forceinline__ void kq_prologue(const MatvecParams &p, KqPlanes a, float *v3, float *scale_s) {
+__device__ __forceinline__ void kq_prologue(const MatvecParams &p, const float *x, KqPlanes a, float *v3, float *scale_s) {
     const int tid = threadIdx.x;
     const int n4  = (int)(p.A.k >> 2);
-    const float4 *x4 = reinterpret_cast<const float4 *>(p.x);
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
     float scale = 1.f;
     if (NORM) {
         for (int g = tid; g < n4; g += KQ_THREADS) {
@@ -93,37 +94,48 @@ __device__ __forceinline__ void kq_scale_min(const uint32_t (&sw)[3], int j, flo
     else { sc = (float)((byte(j + 4) & 0xFu) | ((byte(j - 4) >> 6) << 4)); mn = (float)((byte(j + 4) >> 4) | ((byte(j) >> 6) << 4)); }
 }
 
-// value of one Q4_K super-block: wb = its 144 bytes in global memory, ysb = its activations (8 blocks x 8 words) in shared
-// memory, dx / ysum = the 8 blocks' scales and integer sums
-__device__ __forceinline__ float kq_value_q4k(const uint8_t *wb, const uint32_t *ysb, const float *dx, const int *ysum) {
+// values of one Q4_K super-block for the nT <= TM activation columns of a pass: wb = its 144 bytes in global memory, sb = its
+// index (the activations of column t: 8 blocks x 8 words at a.y + t * a.col + sb * KQ_SB_WORDS, their scales and integer
+// sums at a.dx / a.ysum + t * a.col + 8 * sb). The weights are read and unpacked once for all columns.
+template <int TM>
+__device__ __forceinline__ void kq_values_q4k(const uint8_t *wb, const KqPlanes &a, int sb, int nT, float (&acc)[TM]) {
     const uint4 hd = ldg_nc(wb);
     uint4 q[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) { q[i] = ldg_nc(wb + 16 + 16 * i); }
     const float2 dm = __half22float2(*reinterpret_cast<const __half2 *>(&hd.x));   // d, dmin
     const uint32_t sw[3] = {hd.y, hd.z, hd.w};
-    float acc = 0.f;
+#pragma unroll
+    for (int t = 0; t < TM; ++t) { acc[t] = 0.f; }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {          // sub-block j: bytes 32 * (j / 2) .. + 31 of qs, low nibbles when j is even
         const uint4 qa = q[2 * (j >> 1)], qb = q[2 * (j >> 1) + 1];
         const uint32_t w8[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-        const uint4 ya = *reinterpret_cast<const uint4 *>(ysb + j * 8), yb = *reinterpret_cast<const uint4 *>(ysb + j * 8 + 4);
-        const uint32_t y8[8] = {ya.x, ya.y, ya.z, ya.w, yb.x, yb.y, yb.z, yb.w};
-        int isum = 0;
+        uint32_t nib[8];
 #pragma unroll
-        for (int w = 0; w < 8; ++w) {
-            const uint32_t nib = (j & 1) ? (w8[w] >> 4) & 0x0f0f0f0fu : w8[w] & 0x0f0f0f0fu;
-            isum = __dp4a((int)nib, (int)y8[w], isum);
-        }
+        for (int w = 0; w < 8; ++w) { nib[w] = (j & 1) ? (w8[w] >> 4) & 0x0f0f0f0fu : w8[w] & 0x0f0f0f0fu; }
         float sc, mn; kq_scale_min(sw, j, sc, mn);
-        acc = fmaf(__fmul_rn(__fmul_rn(dm.x, sc), dx[j]), (float)isum, acc);
-        acc = fmaf(-__fmul_rn(__fmul_rn(dm.y, mn), dx[j]), (float)ysum[j], acc);
+        const float dsc = __fmul_rn(dm.x, sc), dmn = __fmul_rn(dm.y, mn);
+#pragma unroll
+        for (int t = 0; t < TM; ++t) {
+            if (TM == 1 || t < nT) {
+                const uint32_t *ysb = a.y + t * a.col + sb * KQ_SB_WORDS;
+                const uint4 ya = *reinterpret_cast<const uint4 *>(ysb + j * 8), yb = *reinterpret_cast<const uint4 *>(ysb + j * 8 + 4);
+                const uint32_t y8[8] = {ya.x, ya.y, ya.z, ya.w, yb.x, yb.y, yb.z, yb.w};
+                int isum = 0;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) { isum = __dp4a((int)nib[w], (int)y8[w], isum); }
+                const float dxj = a.dx[t * a.col + 8 * sb + j];
+                acc[t] = fmaf(__fmul_rn(dsc, dxj), (float)isum, acc[t]);
+                acc[t] = fmaf(-__fmul_rn(dmn, dxj), (float)a.ysum[t * a.col + 8 * sb + j], acc[t]);
+            }
+        }
     }
-    return acc;
 }
 
-// value of one Q6_K super-block in the upload layout: wb = 208 bytes (ql 128, qh 64, 16 int8 scales), d = its fp16 scale
-__device__ __forceinline__ float kq_value_q6k(const uint8_t *wb, uint16_t d_half, const uint32_t *ysb, const float *dx) {
+// values of one Q6_K super-block in the upload layout: wb = 208 bytes (ql 128, qh 64, 16 int8 scales), d = its fp16 scale
+template <int TM>
+__device__ __forceinline__ void kq_values_q6k(const uint8_t *wb, uint16_t d_half, const KqPlanes &a, int sb, int nT, float (&acc)[TM]) {
     uint4 ql[8], qh[4];
 #pragma unroll
     for (int i = 0; i < 8; ++i) { ql[i] = ldg_nc(wb + 16 * i); }
@@ -132,31 +144,40 @@ __device__ __forceinline__ float kq_value_q6k(const uint8_t *wb, uint16_t d_half
     const uint4 scw = ldg_nc(wb + 192);
     const float d = h2f(d_half);
     const uint32_t scs[4] = {scw.x, scw.y, scw.z, scw.w};
-    float acc = 0.f;
+#pragma unroll
+    for (int t = 0; t < TM; ++t) { acc[t] = 0.f; }
 #pragma unroll
     for (int g = 0; g < 16; ++g) {
         // group g = values 16g .. 16g+15: half h of the super-block, segment s of 32 values, l = 16 * (g & 1) .. + 15
         //   s 0: ql[64h + l] low | qh[32h + l] bits 0-1     s 1: ql[64h + 32 + l] low  | bits 2-3
         //   s 2: ql[64h + l] high | bits 4-5                s 3: ql[64h + 32 + l] high | bits 6-7
-        const int h = g >> 3, s = (g >> 1) & 3, l0 = 16 * (g & 1);
-        const uint4 lv = ql[(64 * h + 32 * (s & 1) + l0) >> 4], hv = qh[(32 * h + l0) >> 4];
+        const int h = g >> 3, sg = (g >> 1) & 3, l0 = 16 * (g & 1);
+        const uint4 lv = ql[(64 * h + 32 * (sg & 1) + l0) >> 4], hv = qh[(32 * h + l0) >> 4];
         const uint32_t lw[4] = {lv.x, lv.y, lv.z, lv.w}, hw[4] = {hv.x, hv.y, hv.z, hv.w};
-        const uint4 yv = *reinterpret_cast<const uint4 *>(ysb + (g >> 1) * 8 + 4 * (g & 1));
-        const uint32_t y4[4] = {yv.x, yv.y, yv.z, yv.w};
-        int isum = 0, ys = 0;
+        uint32_t v6[4];                                          // the group's values 0..63, four per word
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const uint32_t lo = (s & 2) ? (lw[w] >> 4) & 0x0f0f0f0fu : lw[w] & 0x0f0f0f0fu;
-            const uint32_t hi = ((hw[w] >> (2 * s)) & 0x03030303u) << 4;
-            const uint32_t y = y4[w];
-            isum = __dp4a((int)(lo | hi), (int)y, isum);      // values 0..63
-            ys   = __dp4a(0x01010101, (int)y, ys);
+            const uint32_t lo = (sg & 2) ? (lw[w] >> 4) & 0x0f0f0f0fu : lw[w] & 0x0f0f0f0fu;
+            v6[w] = lo | (((hw[w] >> (2 * sg)) & 0x03030303u) << 4);
         }
-        isum -= 32 * ys;                                       // value = stored - 32
         const int sc = (int)(int8_t)((scs[g >> 2] >> (8 * (g & 3))) & 0xffu);
-        acc = fmaf(__fmul_rn(__fmul_rn(d, (float)sc), dx[g >> 1]), (float)isum, acc);
+        const float dsc = __fmul_rn(d, (float)sc);
+#pragma unroll
+        for (int t = 0; t < TM; ++t) {
+            if (TM == 1 || t < nT) {
+                const uint4 yv = *reinterpret_cast<const uint4 *>(a.y + t * a.col + sb * KQ_SB_WORDS + (g >> 1) * 8 + 4 * (g & 1));
+                const uint32_t y4[4] = {yv.x, yv.y, yv.z, yv.w};
+                int isum = 0, ys = 0;
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    isum = __dp4a((int)v6[w], (int)y4[w], isum);
+                    ys   = __dp4a(0x01010101, (int)y4[w], ys);
+                }
+                isum -= 32 * ys;                                 // value = stored - 32
+                acc[t] = fmaf(__fmul_rn(dsc, a.dx[t * a.col + 8 * sb + (g >> 1)]), (float)isum, acc[t]);
+            }
+        }
     }
-    return acc;
 }
 
 struct KqRow { const uint8_t *w; int type; };
@@ -169,85 +190,106 @@ __device__ __forceinline__ KqRow kq_row(const MatvecParams &p, int64_t row, int 
     return r;
 }
 
-// dot product of one row with the activation column, for the lanes [lane0, lane0 + G) of the warp; every lane of the
-// group returns the same value
-template <int G>
-__device__ __forceinline__ float kq_row_dot(const KqRow &r, int nsb, const KqPlanes &a, int l /* lane inside the group */, int lane0) {
+// dot products of one row with the nT <= TM activation columns of the pass, for the lanes [lane0, lane0 + G) of the warp;
+// every lane of the group ends with the same values
+template <int G, int TM>
+__device__ __forceinline__ void kq_row_dot(const KqRow &r, int nsb, const KqPlanes &a, int nT, int l /* lane inside the group */, int lane0, float (&total)[TM]) {
     constexpr int ROUNDS = 4;      // super-blocks per lane (K <= 256 * G * ROUNDS)
-    float part[ROUNDS];
+    float part[ROUNDS][TM];
 #pragma unroll
     for (int k = 0; k < ROUNDS; ++k) {
         const int sb = l + k * G;
-        part[k] = 0.f;
+#pragma unroll
+        for (int t = 0; t < TM; ++t) { part[k][t] = 0.f; }
         if (k * G < nsb && sb < nsb) {
-            if (r.type == 12) { part[k] = kq_value_q4k(r.w + (size_t)sb * 144, a.y + sb * KQ_SB_WORDS, a.dx + 8 * sb, a.ysum + 8 * sb); }
+            if (r.type == 12) { kq_values_q4k<TM>(r.w + (size_t)sb * 144, a, sb, nT, part[k]); }
             else {
                 const uint16_t dh = *reinterpret_cast<const uint16_t *>(r.w + (size_t)nsb * 208 + 2 * sb);
-                part[k] = kq_value_q6k(r.w + (size_t)sb * 208, dh, a.y + sb * KQ_SB_WORDS, a.dx + 8 * sb);
+                kq_values_q6k<TM>(r.w + (size_t)sb * 208, dh, a, sb, nT, part[k]);
             }
         }
     }
-    float total = 0.f;             // the super-blocks' values in order
 #pragma unroll
-    for (int k = 0; k < ROUNDS; ++k) {
-        if (k * G >= nsb) { break; }
-        for (int i = 0; i < G; ++i) {
-            const float v = __shfl_sync(0xffffffffu, part[k], lane0 + i);
-            if (i + k * G < nsb) { total = __fadd_rn(total, v); }
+    for (int t = 0; t < TM; ++t) {
+        float sum = 0.f;             // the super-blocks' values in order
+        if (TM == 1 || t < nT) {
+#pragma unroll
+            for (int k = 0; k < ROUNDS; ++k) {
+                if (k * G >= nsb) { break; }
+                for (int i = 0; i < G; ++i) {
+                    const float v = __shfl_sync(0xffffffffu, part[k][t], lane0 + i);
+                    if (i + k * G < nsb) { sum = __fadd_rn(sum, v); }
+                }
+            }
         }
+        total[t] = sum;
     }
-    return total;
 }
 
+template <int TM>
 __global__ void __launch_bounds__(KQ_THREADS, 1) matvec_kq_kernel(const MatvecParams p) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ float scale_s;
     const int nb = p.A.nb, nsb = nb >> 3;
+    const int nT = (TM == 1) ? 1 : p.T;
     KqPlanes a;
+    a.col  = nsb * KQ_SB_WORDS + 2 * nb;
     a.y    = reinterpret_cast<uint32_t *>(smem_raw);
     a.dx   = reinterpret_cast<float *>(a.y + (size_t)nsb * KQ_SB_WORDS);
     a.ysum = reinterpret_cast<int *>(a.dx + nb);
     pdl_launch_dependents();
     pdl_wait();
     tp_wait(p.tp, p.error_flag);
-    {
-        float *v3 = reinterpret_cast<float *>(smem_raw);   // nb * 8 floats = the size of the y plane (nb * 32 bytes): aliases it
-        if (p.pro == PRO_NORM_QUANT) { kq_prologue<true>(p, a, v3, &scale_s); } else { kq_prologue<false>(p, a, v3, &scale_s); }
+#pragma unroll 1
+    for (int t = 0; t < nT; ++t) {
+        KqPlanes c = a;
+        c.y += t * a.col; c.dx += t * a.col; c.ysum += t * a.col;
+        float *v3 = reinterpret_cast<float *>(c.y);   // nb * 8 floats = the size of the y plane (nb * 32 bytes): aliases it
+        const float *x = p.x + (int64_t)t * p.x_stride;
+        if (p.pro == PRO_NORM_QUANT) { kq_prologue<true>(p, x, c, v3, &scale_s); } else { kq_prologue<false>(p, x, c, v3, &scale_s); }
+        __syncthreads();
     }
-    __syncthreads();
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t n_units = p.pair_mode ? p.kq[0].n_rows : (p.A.n_rows >> 1);
     for (int64_t u = (int64_t)blockIdx.x * KQ_WARPS + warp; u < n_units; u += (int64_t)gridDim.x * KQ_WARPS) {
         const int64_t row_a = p.pair_mode ? u : 2 * u, row_b = p.pair_mode ? u : 2 * u + 1;
-        float va, vb;
+        float va[TM], vb[TM];
         if (nsb <= 16) {            // both rows at once, a half-warp each
             const int half = lane >> 4;
             const KqRow r = kq_row(p, half ? row_b : row_a, half);
-            const float v = kq_row_dot<16>(r, nsb, a, lane & 15, lane & 16);
-            va = __shfl_sync(0xffffffffu, v, 0); vb = __shfl_sync(0xffffffffu, v, 16);
+            float v[TM];
+            kq_row_dot<16, TM>(r, nsb, a, nT, lane & 15, lane & 16, v);
+#pragma unroll
+            for (int t = 0; t < TM; ++t) { va[t] = __shfl_sync(0xffffffffu, v[t], 0); vb[t] = __shfl_sync(0xffffffffu, v[t], 16); }
         } else {
-            va = kq_row_dot<32>(kq_row(p, row_a, 0), nsb, a, lane, 0);
-            vb = kq_row_dot<32>(kq_row(p, row_b, 1), nsb, a, lane, 0);
+            kq_row_dot<32, TM>(kq_row(p, row_a, 0), nsb, a, nT, lane, 0, va);
+            kq_row_dot<32, TM>(kq_row(p, row_b, 1), nsb, a, nT, lane, 0, vb);
         }
-        if (p.epi == EPI_SILU_MUL) { matvec_epilogue_silu(p, u, 0, va, vb, lane == 0); }
-        else {
-            matvec_epilogue(p, row_a, 0, va, vb, lane == 0);
-            matvec_epilogue(p, row_b, 0, vb, va, lane == 0);
+#pragma unroll
+        for (int t = 0; t < TM; ++t) {
+            const bool store = lane == 0 && t < nT;
+            if (p.epi == EPI_SILU_MUL) { matvec_epilogue_silu(p, u, t, va[t], vb[t], store); }
+            else {
+                matvec_epilogue(p, row_a, t, va[t], vb[t], store);
+                matvec_epilogue(p, row_b, t, vb[t], va[t], store);
+            }
         }
     }
-    tp_publish(p.tp, 1);
+    tp_publish(p.tp, p.T);
 }
 
 cudaError_t launch_matvec_kq(const MatvecParams &p, const LaunchCfg &cfg) {
-    if (p.T != 1 || p.kq_n < 1 || p.kq_n > 3 || p.A.k % 256 != 0 || p.A.k > 256 * 32 * 4 || p.A.nb != (int)(p.A.k / QK)) { return cudaErrorInvalidValue; }
+    if (p.T < 1 || p.T > KQ_MAX_COLUMNS || p.kq_n < 1 || p.kq_n > 3 || p.A.k % 256 != 0 || p.A.k > 256 * 32 * 4 || p.A.nb != (int)(p.A.k / QK)) { return cudaErrorInvalidValue; }
     if (p.pair_mode ? (p.kq_n != 2 || p.kq[0].n_rows != p.kq[1].n_rows || p.epi != EPI_SILU_MUL) : (p.epi == EPI_SILU_MUL || (p.A.n_rows & 1))) { return cudaErrorInvalidValue; }
     for (int i = 0; i < p.kq_n; ++i) {
         if ((p.kq[i].type != 12 && p.kq[i].type != 14) || p.kq[i].w == nullptr || (p.kq[i].n_rows & 1) || (reinterpret_cast<uintptr_t>(p.kq[i].w) & 15) || (p.kq[i].row_bytes & 15)) { return cudaErrorInvalidValue; }
     }
     const int nsb = (int)(p.A.k / 256);
-    const size_t smem = (size_t)nsb * KQ_SB_WORDS * 4 + (size_t)p.A.nb * 8 + 16;
-    cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(matvec_kq_kernel), smem);
+    const int    TM   = p.T == 1 ? 1 : KQ_MAX_COLUMNS;
+    const size_t smem = (size_t)TM * ((size_t)nsb * KQ_SB_WORDS * 4 + (size_t)p.A.nb * 8) + 16;
+    void (*kernel)(const MatvecParams) = p.T == 1 ? matvec_kq_kernel<1> : matvec_kq_kernel<KQ_MAX_COLUMNS>;
+    cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(kernel), smem);
     if (err != cudaSuccess) { return err; }
     MatvecParams q = p;
     if (q.error_flag == nullptr) { q.error_flag = cfg.error_flag; }
@@ -259,7 +301,7 @@ cudaError_t launch_matvec_kq(const MatvecParams &p, const LaunchCfg &cfg) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr; lc.numAttrs = cfg.pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&lc, matvec_kq_kernel, q);
+    return cudaLaunchKernelEx(&lc, kernel, q);
 }
 
 // upload-time re-layout of Q6_K rows: [sb][ql 128 | qh 64 | scales 16 | d 2] (210 bytes each) ->

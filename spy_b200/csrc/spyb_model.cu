@@ -1051,7 +1051,7 @@ spyb_status spyb_model_eval(spyb_model *m, const int32_t *tokens, int32_t n_toke
         return SPYB_SUCCESS;
     }
     SPYB_CUDA(be, cudaEventRecord(m->ev0, be->stream));
-    const int tmax = m->kq ? 1 : std::min(8, std::min(matvec_max_columns(m->info.d_model / 32), matvec_max_columns(m->info.n_ff / 32)));   // (the K-quant kernel takes one column)
+    const int tmax = m->kq ? KQ_MAX_COLUMNS : std::min(8, std::min(matvec_max_columns(m->info.d_model / 32), matvec_max_columns(m->info.n_ff / 32)));
     for (int t0 = 0; t0 < n_tokens; t0 += tmax) {
         const int T = std::min(tmax, n_tokens - t0);
         SPYB_CUDA(be, cudaStreamSynchronize(be->stream));   // pinned staging words are reused per pass
@@ -1237,7 +1237,7 @@ spyb_status spyb_model_set_sequences(spyb_model *m, int32_t n_seq) {
     if (m == nullptr) { return SPYB_FAIL; }
     spyb_backend *be = m->be;
     if (n_seq < 1 || n_seq > 64) { be->set_error("set_sequences: 1 to 64 sequences, got %d", n_seq); return SPYB_UNSUPPORTED; }
-    if (m->kq || m->step_ok) { be->set_error("set_sequences: batches need a Q4_0 / Q8_0 model on the per-matrix kernels"); return SPYB_UNSUPPORTED; }
+    if (m->step_ok) { be->set_error("set_sequences: batches need the model on the per-matrix kernels"); return SPYB_UNSUPPORTED; }
     if (m->info.tp_size != 1 && !m->pf_ok) { be->set_error("set_sequences: a sharded model runs batches on the tensor-core kernels, which this model was loaded without"); return SPYB_UNSUPPORTED; }
     cudaSetDevice(be->config.device_id);
     SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
@@ -1279,7 +1279,7 @@ spyb_status spyb_model_decode_batch(spyb_model *m, const int32_t *first_tokens, 
         m->batch_ids_cap = need;
     }
     const int V = m->info.n_vocab, d = m->info.d_model;
-    const int group = std::min(TMAX, std::min(matvec_max_columns(d / 32), matvec_max_columns(m->info.n_ff / 32)));   // columns per pass through the layers
+    const int group = m->kq ? KQ_MAX_COLUMNS : std::min(TMAX, std::min(matvec_max_columns(d / 32), matvec_max_columns(m->info.n_ff / 32)));   // columns per pass through the layers
     SPYB_CUDA(be, cudaStreamSynchronize(be->stream));
     m->h_pos_pinned[0] = n_past; m->h_pos_pinned[1] = 0; m->h_pos_pinned[2] = ++m->epoch;
     m->epoch += n_steps - 1;

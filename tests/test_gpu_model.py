@@ -174,15 +174,17 @@ def test_prompt_widths_the_gemm_tile_does_not_divide(be, oracle, tmp_models):
     m.close()
 
 
-@pytest.mark.parametrize("n_seq,n_ctx", [(3, 64), (8, 64), (6, 1100), (20, 64), (17, 1100)])
-def test_batch_of_sequences_equals_single_sequence_runs(n_seq, n_ctx, oracle, tmp_models):
+@pytest.mark.parametrize("n_seq,n_ctx,kq", [(3, 64, False), (8, 64, False), (6, 1100, False), (20, 64, False), (17, 1100, False),
+                                            (3, 64, True), (6, 64, True), (18, 64, True)])
+def test_batch_of_sequences_equals_single_sequence_runs(n_seq, n_ctx, kq, oracle, tmp_models):
     """Independent sequences that share the weights and advance in lockstep: every sequence must give the ids and the
     logits of a run on its own (the batch > 1 configurations are replicas of the single-sequence reference). Prompts of
     one length, different contents; 3 sequences = one group of activation columns, 8 and 6 = two groups; 16 and more go
     through the tensor-core GEMM kernels as the tokens of one pass; a context above 1024 positions takes the three-kernel
-    attention."""
-    cfg = gguf_io.LlamaConfig(n_layer=2, d_model=256, n_head=2, n_ff=512, n_vocab=400, weight_std=0.06)
-    path = str(tmp_models / "batch.gguf")
+    attention. kq: the Q4_K_M-style mix (groups of four columns through the K-quant mat-vec kernel, or the K-quant GEMM)."""
+    cfg = gguf_io.LlamaConfig(n_layer=2, d_model=256, n_head=2, n_ff=512, n_vocab=400, weight_std=0.06,
+                              **(dict(wtype=quants.Q4_K, overrides={"attn_v": quants.Q6_K, "ffn_down": quants.Q6_K, "output": quants.Q6_K}) if kq else {}))
+    path = str(tmp_models / ("batch_kq.gguf" if kq else "batch.gguf"))
     if not os.path.exists(path):
         gguf_io.make_llama_gguf(path, cfg, seed=61)
     rng = np.random.default_rng(n_seq)

@@ -227,7 +227,7 @@ def test_matmul_operator_sweep(be, oracle, qt, n, k, t):
 @pytest.mark.parametrize("n,k,t", [(132, 512, 1), (132, 512, 5), (200, 1024, 16), (260, 2816, 41), (1100, 512, 150)])
 def test_matmul_on_uploaded_constants_takes_the_model_kernels(be, oracle, qt, n, k, t):
     """MatMul through spyb_submit against a constant from spyb_upload_constant: K-quant constants run the K-quant mat-vec
-    kernel column by column, and 16 columns and more run the tcgen05 GEMM against a tile copy made at first use (K-quants
+    kernel in passes of four columns, and 16 columns and more run the tcgen05 GEMM against a tile copy made at first use (K-quants
     always, Q4_0 / Q8_0 when rows x columns give the GEMM enough tiles: the last case). Either way the oracle's bits (for
     K-quants: the restatement's)."""
     rng = np.random.default_rng(n + k + t + qt)
