@@ -437,7 +437,7 @@ spyb_status spyb_prefill_matmul(spyb_backend *be, int32_t weight_type, const voi
     if (err == cudaSuccess) { err = cudaMemcpyAsync(x, x_host, (size_t)T * k * 4, cudaMemcpyHostToDevice, be->stream); }
     if (err == cudaSuccess && nw != nullptr) { err = cudaMemcpyAsync(nw, norm_w_host, (size_t)k * 4, cudaMemcpyHostToDevice, be->stream); }
     if (err == cudaSuccess) { err = launch_prefill_retile(weight_type, raw, rb, n_rows, nb, w, 0, be->stream); }
-    if (err == cudaSuccess) { err = launch_prefill_quant(x, k, T, (int)k, nw, eps, yq, be->stream, kq); }
+    if (err == cudaSuccess) { err = launch_prefill_quant(x, k, T, (int)k, nw, eps, yq, be->stream, weight_type); }
     if (err == cudaSuccess) {
         PrefillGemm g;
         g.w = w; g.type = weight_type; g.n_rows = n_rows; g.nb = nb; g.yq = yq; g.T = T; g.out = out; g.out_stride = n_rows;
@@ -578,7 +578,7 @@ spyb_status run_matmul_gemm(spyb_backend *be, const spyb_tensor &w, const spyb_t
     for (int64_t t0 = 0; t0 < T; t0 += chunk) {
         const int Tc = (int)std::min(chunk, T - t0);
         SPYB_CUDA(be, cudaMemsetAsync(yq, 0, prefill_act_bytes(Tc, nb), be->stream));
-        SPYB_CUDA(be, launch_prefill_quant(static_cast<const float *>(x.data) + t0 * k, k, Tc, (int)k, nullptr, 0.f, static_cast<uint8_t *>(yq), be->stream, kq));
+        SPYB_CUDA(be, launch_prefill_quant(static_cast<const float *>(x.data) + t0 * k, k, Tc, (int)k, nullptr, 0.f, static_cast<uint8_t *>(yq), be->stream, type));
         PrefillGemm g;
         g.w = tiles; g.type = type; g.n_rows = n_rows; g.nb = nb; g.yq = static_cast<uint8_t *>(yq); g.T = Tc;
         g.out = static_cast<float *>(out_dev) + t0 * n_rows; g.out_stride = n_rows;

@@ -110,7 +110,8 @@ struct MatvecParams {
 // Prompt evaluation as a GEMM on the tcgen05 tensor cores (spyb_prefill.cu). Weights in tiles of PF_ROWS rows x 1 block,
 // activations as compact Q8_0 blocks grouped by (tile of PF_TOK tokens, block).
 constexpr int PF_ROWS = 128, PF_TOK = 16;
-constexpr int PF_YQ_BYTES = PF_TOK * 32 + PF_TOK * 4;
+constexpr int PF_YQ_BYTES = PF_TOK * 32 + PF_TOK * 4;           // Q8_0 weights: 16 x 32 s8, 16 f32 scales
+constexpr int PF_YQ_BYTES_F8 = 2 * PF_TOK * 32 + PF_TOK * 4;    // Q4_0 weights: the activation bytes split into two e4m3 planes (16 x 32 each), 16 f32 scales
 constexpr int PF_KQ_TOK = 64;                                   // K-quant kernels: 64 tokens per tile, two columns of D per token
 constexpr int PF_KQ_YQ_BYTES = PF_KQ_TOK * 32 + PF_KQ_TOK * 8;   // 64 x 32 s8, 64 f32 scales, 64 f32 block sums
 constexpr int PF_KQ_WTILE = 128 * 32 + 128 * 8;                 // the s8 A operand of a 32-element block, then two f32 scale products per row
@@ -120,7 +121,7 @@ struct PrefillGemm {
     int            type = 0;          // 2 = Q4_0, 8 = Q8_0, 12 = Q4_K, 14 = Q6_K
     int64_t        n_rows = 0;        // (the last tile of PF_ROWS rows may be partly padding: zero weights, rows not stored)
     int            nb = 0;            // blocks per row
-    const uint8_t *yq = nullptr;      // [ceil(T / PF_TOK)][nb][PF_YQ_BYTES] (launch_prefill_quant)
+    const uint8_t *yq = nullptr;      // [ceil(T / PF_TOK)][nb][PF_YQ_BYTES or PF_YQ_BYTES_F8] (launch_prefill_quant for this weight type)
     int            T = 0;
     float         *out = nullptr;     // [T][out_stride]
     int64_t        out_stride = 0;
@@ -133,8 +134,10 @@ struct PrefillGemm {
 size_t      prefill_weight_bytes(int type, int64_t n_rows, int nb);
 size_t      prefill_act_bytes(int T, int nb);
 cudaError_t launch_prefill_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0, cudaStream_t stream);
-cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K, const float *norm_w, float eps, uint8_t *yq, cudaStream_t stream, bool kq_layout = false,
-                                 int part_len = 0, int64_t part_stride = 0);   // part_len > 0: a row lies in K / part_len parts, part_stride floats apart
+// weight_type: the type of the matrix the activations will meet (2, 8, 12 or 14): it decides their layout;
+// part_len > 0: a row lies in K / part_len parts, part_stride floats apart
+cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K, const float *norm_w, float eps, uint8_t *yq, cudaStream_t stream, int weight_type,
+                                 int part_len = 0, int64_t part_stride = 0);
 cudaError_t launch_prefill_gemm_kq(const PrefillGemm &g, cudaStream_t stream);   // type 12 = Q4_K, 14 = Q6_K (spyb_prefill_kq.cu)
 cudaError_t launch_prefill_retile_kq(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0, cudaStream_t stream);
 cudaError_t launch_prefill_gemm(const PrefillGemm &g, cudaStream_t stream);

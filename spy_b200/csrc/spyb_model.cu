@@ -506,7 +506,7 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool bat
     float *att_part = m->pf_att + (size_t)rank * T * dl, *act_part = m->pf_act + (size_t)rank * T * fl;   // (tp == 1: the whole buffers)
     float *x_part = m->pf_x + (size_t)rank * T * dp;
     for (Layer &ly : m->layers) {
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, dp, T, d, ly.attn_norm, m->info.rms_eps, m->pf_yq, s, m->kq, dp, (int64_t)T * dp));
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, dp, T, d, ly.attn_norm, m->info.rms_eps, m->pf_yq, s, ly.pf_qkv.type, dp, (int64_t)T * dp));
         SPYB_CUDA(be, gemm(ly.pf_qkv, d, m->pf_qkv, 3 * (int64_t)dl, nullptr));
         if (m->kq) {   // one matrix per tensor: Wk and Wv fill the other two thirds of the QKV rows
             SPYB_CUDA(be, gemm(ly.pf_k, d, m->pf_qkv + dl, 3 * (int64_t)dl, nullptr));
@@ -531,15 +531,15 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool bat
             }
         }
         if (gather(m->pf_att, dl) != SPYB_SUCCESS) { return SPYB_FAIL; }
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_att, dl, T, d, nullptr, 0.f, m->pf_yq, s, m->kq, dl, (int64_t)T * dl));
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_att, dl, T, d, nullptr, 0.f, m->pf_yq, s, ly.pf_wo.type, dl, (int64_t)T * dl));
         SPYB_CUDA(be, gemm(ly.pf_wo, d, x_part, dp, x_part));
         if (gather(m->pf_x, dp) != SPYB_SUCCESS) { return SPYB_FAIL; }
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, dp, T, d, ly.ffn_norm, m->info.rms_eps, m->pf_yq, s, m->kq, dp, (int64_t)T * dp));
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, dp, T, d, ly.ffn_norm, m->info.rms_eps, m->pf_yq, s, ly.pf_ug.type, dp, (int64_t)T * dp));
         SPYB_CUDA(be, gemm(ly.pf_ug, d, m->pf_ug, 2 * (int64_t)fl, nullptr));
         if (m->kq) { SPYB_CUDA(be, gemm(ly.pf_gate, d, m->pf_ug + fl, 2 * (int64_t)fl, nullptr)); ++*launches; }
         SPYB_CUDA(be, launch_prefill_silu_mul(m->pf_ug, T, fl, be->d_silu_table, act_part, s));
         if (gather(m->pf_act, fl) != SPYB_SUCCESS) { return SPYB_FAIL; }
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_act, fl, T, ff, nullptr, 0.f, m->pf_yq, s, m->kq, fl, (int64_t)T * fl));
+        SPYB_CUDA(be, launch_prefill_quant(m->pf_act, fl, T, ff, nullptr, 0.f, m->pf_yq, s, ly.pf_down.type, fl, (int64_t)T * fl));
         SPYB_CUDA(be, gemm(ly.pf_down, ff, x_part, dp, x_part));
         if (gather(m->pf_x, dp) != SPYB_SUCCESS) { return SPYB_FAIL; }
         *launches += 7;

@@ -50,26 +50,37 @@ constexpr int PF_QUANT_GROUPS  = PF_MAX_K / (4 * PF_QUANT_THREADS);   // float4 
 //   A ring  [PF_STAGES][4352]   weight tiles (s8 operand + 128 fp16 scales), written by cp.async.bulk
 //   Y ring  [PF_STAGES][576]    compact activations (16 tokens x 32 s8, 16 f32 scales), written by cp.async.bulk
 //   B ring  [PF_STAGES][4096]   expanded activations, written by the expander warp
+template <int WT> struct PfGeom {
+    static constexpr bool F8      = WT == 2;                               // Q4_0: e4m3 operands, f32 accumulators, two MMAs per block
+    static constexpr int  YQ      = F8 ? PF_YQ_BYTES_F8 : PF_YQ_BYTES;     // a block's compact activations
+    static constexpr int  BT      = F8 ? 2 * PF_TILE : PF_TILE;            // a block's B operand(s)
+    static constexpr int  MMA_W   = F8 ? PF_MMA_WARPS_F8 : PF_MMA_WARPS;
+    static constexpr int  THREADS = F8 ? PF_THREADS_F8 : PF_THREADS;
+    static constexpr size_t SMEM  = (size_t)PF_STAGES * (PF_WTILE + YQ + BT) + 8 * (3 * PF_RING + 2 * PF_DBUF) + 16;
+};
+
 template <int WT>
-__global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm g) {
+__global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(PrefillGemm g) {
     constexpr int NS = PF_STAGES, NQ = PF_RING;
+    constexpr bool F8 = PfGeom<WT>::F8;
+    constexpr int YQ = PfGeom<WT>::YQ, BT = PfGeom<WT>::BT, MMA_W = PfGeom<WT>::MMA_W, THREADS = PfGeom<WT>::THREADS;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
-    const uint32_t a_ring = sbase, y_ring = a_ring + NS * PF_WTILE, b_ring = y_ring + NS * PF_YQ_BYTES;
-    const uint32_t bars  = b_ring + NS * PF_TILE;
+    const uint32_t a_ring = sbase, y_ring = a_ring + NS * PF_WTILE, b_ring = y_ring + NS * YQ;
+    const uint32_t bars  = b_ring + NS * BT;
     auto raw_full = [&](int q) { return bars + 8u * q; };                        // the batch's weights and activations have landed
     auto ops_full = [&](int q) { return bars + 8u * (NQ + q); };                 // the batch's B operands are written and fenced
     auto st_free  = [&](int q) { return bars + 8u * (2 * NQ + q); };             // the batch's stages may be refilled (one arrival per epilogue warp)
     auto d_full   = [&](int i) { return bars + 8u * (3 * NQ + i); };             // the MMA into buffer i has completed
     auto d_free   = [&](int i) { return bars + 8u * (3 * NQ + PF_DBUF + i); };   // buffer i holds the offset pattern again (one arrival per epilogue warp)
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (size_t)NS * (PF_WTILE + PF_YQ_BYTES + PF_TILE) + 8 * (3 * NQ + 2 * PF_DBUF));
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (size_t)NS * (PF_WTILE + YQ + BT) + 8 * (3 * NQ + 2 * PF_DBUF));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nb = g.nb, n_batch = (nb + PF_BATCH - 1) / PF_BATCH;
     const uint64_t limit = g.wait_limit_ns;
     const int row_tile = blockIdx.y, tok_tile = blockIdx.x;   // CTAs that run together share a weight tile: it crosses HBM once
     const uint8_t *wsrc = g.w + ((int64_t)row_tile * nb) * PF_WTILE;
-    const uint8_t *ysrc = g.yq + ((int64_t)tok_tile * nb) * PF_YQ_BYTES;
+    const uint8_t *ysrc = g.yq + ((int64_t)tok_tile * nb) * YQ;
 
     if (tid == 0) {
         for (int q = 0; q < NQ; ++q) { mbar_init(raw_full(q), 1); mbar_init(ops_full(q), 1); mbar_init(st_free(q), PF_EPI_WARPS); }
@@ -77,7 +88,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
         mbar_init_fence();
     }
     // the B tiles are zero except where the expansion writes, and it writes the same places for every block
-    for (int i = tid; i < NS * (PF_TILE / 16); i += PF_THREADS) { sts128(b_ring + (uint32_t)i * 16u, make_uint4(0u, 0u, 0u, 0u)); }
+    for (int i = tid; i < NS * (BT / 16); i += THREADS) { sts128(b_ring + (uint32_t)i * 16u, make_uint4(0u, 0u, 0u, 0u)); }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(PF_DBUF * PF_N) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -93,7 +104,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
         // that holds the offset pattern; MMAs into different buffers do not depend on one another
         if (lane == 0) {
             int last = -1;
-            for (int b = warp - (PF_EPI_WARPS + 2); b < nb; b += PF_MMA_WARPS) {
+            for (int b = warp - (PF_EPI_WARPS + 2); b < nb; b += MMA_W) {
                 const int s = b % NS, q = b / PF_BATCH, buf = b % PF_DBUF;
                 PF_STAMP(2, b, 0);
                 if (!mbar_wait_relaxed(ops_full(q % NQ), (uint32_t)(q / NQ) & 1u, limit)) { pf_report(g.error_flag, 5); break; }
@@ -101,7 +112,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
                 if (!mbar_wait_relaxed(d_free(buf), (uint32_t)(b / PF_DBUF) & 1u, limit)) { pf_report(g.error_flag, 5); break; }
                 PF_STAMP(2, b, 2);
                 tc_fence_after();
-                mma_s8_ss(tmem + (uint32_t)(buf * PF_N), operand_desc(a_ring + (uint32_t)s * PF_WTILE), operand_desc(b_ring + (uint32_t)s * PF_TILE));
+                if (F8) {   // the two e4m3 halves of the activation bytes, one after the other onto the same accumulators
+                    const uint64_t a_desc = operand_desc(a_ring + (uint32_t)s * PF_WTILE);
+                    mma_f8_ss(tmem + (uint32_t)(buf * PF_N), a_desc, operand_desc(b_ring + (uint32_t)s * BT), 0u);
+                    mma_f8_ss(tmem + (uint32_t)(buf * PF_N), a_desc, operand_desc(b_ring + (uint32_t)s * BT + PF_TILE), 1u);
+                } else {
+                    mma_s8_ss(tmem + (uint32_t)(buf * PF_N), operand_desc(a_ring + (uint32_t)s * PF_WTILE), operand_desc(b_ring + (uint32_t)s * BT));
+                }
                 mma_commit(d_full(buf));
                 PF_STAMP(2, b, 3);
                 last = b;
@@ -118,9 +135,9 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
                 if (q >= NQ && !mbar_wait_relaxed(st_free(q % NQ), (uint32_t)((q / NQ) - 1) & 1u, limit)) { pf_report(g.error_flag, 4); break; }
                 const int b0 = q * PF_BATCH, n = min(PF_BATCH, nb - b0), s0 = b0 % NS;
                 PF_STAMP(0, b0, 0);
-                mbar_expect_tx(raw_full(q % NQ), (uint32_t)(n * (PF_WTILE + PF_YQ_BYTES)));
+                mbar_expect_tx(raw_full(q % NQ), (uint32_t)(n * (PF_WTILE + YQ)));
                 bulk_copy_g2s(a_ring + (uint32_t)s0 * PF_WTILE, wsrc + (int64_t)b0 * PF_WTILE, (uint32_t)(n * PF_WTILE), raw_full(q % NQ));
-                bulk_copy_g2s(y_ring + (uint32_t)s0 * PF_YQ_BYTES, ysrc + (int64_t)b0 * PF_YQ_BYTES, (uint32_t)(n * PF_YQ_BYTES), raw_full(q % NQ));
+                bulk_copy_g2s(y_ring + (uint32_t)s0 * YQ, ysrc + (int64_t)b0 * YQ, (uint32_t)(n * YQ), raw_full(q % NQ));
                 issued = q + 1;
             }
             // no copy of this CTA is in flight when it leaves
@@ -138,11 +155,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
             const int b0 = q * PF_BATCH, n = min(PF_BATCH, nb - b0), s0 = b0 % NS;
             if (lane == 0) { PF_STAMP(1, b0, 0); }
             for (int j = 0; j < n; ++j) {
-                const uint32_t ysrc_s = y_ring + (uint32_t)(s0 + j) * PF_YQ_BYTES, bdst = b_ring + (uint32_t)(s0 + j) * PF_TILE;
+                const uint32_t ysrc_s = y_ring + (uint32_t)(s0 + j) * YQ, bdst = b_ring + (uint32_t)(s0 + j) * BT;
+                constexpr int NW = (F8 ? 2 : 1) * PF_TOK * 8 / 32;   // words per lane (e4m3 form: the second plane of words goes to the second B operand)
+                uint32_t v[NW];
 #pragma unroll
-                for (int k = 0; k < PF_TOK * 8 / 32; ++k) {
-                    const int i = lane + 32 * k, tt = i >> 3, w = i & 7;
-                    sts32(bdst + (uint32_t)tt * 256u + (uint32_t)(w >> 2) * 128u + (uint32_t)w * 16u + (uint32_t)(w & 3) * 4u, lds32(ysrc_s + (uint32_t)i * 4u));
+                for (int k = 0; k < NW; ++k) { v[k] = lds32(ysrc_s + (uint32_t)(lane + 32 * k) * 4u); }   // all loads in flight before the first store
+#pragma unroll
+                for (int k = 0; k < NW; ++k) {
+                    const int i = lane + 32 * k, plane = i >> 7, tt = (i >> 3) & (PF_TOK - 1), w = i & 7;
+                    sts32(bdst + (uint32_t)plane * PF_TILE + (uint32_t)tt * 256u + (uint32_t)(w >> 2) * 128u + (uint32_t)w * 16u + (uint32_t)(w & 3) * 4u, v[k]);
                 }
             }
             fence_async_smem();
@@ -156,79 +177,133 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
         const int quad = warp & 3, half = warp >> 2;
         const int row = 32 * quad + lane;
         const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(64 * half);
-        const uint32_t dw_addr = a_ring + PF_TILE + 2u * (uint32_t)row, dx_addr = y_ring + PF_TOK * 32 + 32u * (uint32_t)half;
+        const uint32_t dw_addr = a_ring + PF_TILE + 2u * (uint32_t)row, dx_addr = y_ring + (F8 ? 2 : 1) * PF_TOK * 32 + 32u * (uint32_t)half;
         uint64_t acc[8][4];   // [token][pair]: accumulators 2 pair and 2 pair + 1 of the token, as one packed f32x2 value
 #pragma unroll
         for (int t = 0; t < 8; ++t) {
 #pragma unroll
             for (int n = 0; n < 4; ++n) { acc[t][n] = 0ull; }
         }
-        for (int i = 0; i < PF_DBUF; ++i) {   // the offset pattern into this thread's part of every buffer
-            tmem_st32_same(tbase + (uint32_t)(i * PF_N), MAGIC_I);
-            tmem_st32_same(tbase + (uint32_t)(i * PF_N) + 32u, MAGIC_I);
-        }
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) { for (int i = 0; i < PF_DBUF; ++i) { mbar_arrive(d_free(i)); } }
-
-        uint32_t ra[16], rb[16], pattern[16];
+        bool ok = true;
+        if constexpr (F8) {
+            // ---- e4m3 operands: D is f32 and holds (float)lane_sum itself, so a lane sum costs half a packed FMA and the buffer is
+            // free for the next MMA as soon as it has been read
+            if (lane == 0) { for (int i = 0; i < PF_DBUF; ++i) { mbar_arrive(d_free(i)); } }
+            uint32_t ra[16], rb[16];
+            auto fold2 = [&](const uint32_t *r, int t0, const uint64_t *sc) {   // two tokens: columns 8 t0 .. 8 t0 + 15
 #pragma unroll
-        for (int i = 0; i < 16; ++i) { asm volatile("mov.b32 %0, %1;" : "=r"(pattern[i]) : "r"(MAGIC_I)); }   // (opaque to the compiler: 16 live registers)
-        const uint64_t minus_magic = f2_pack(-MAGIC_F, -MAGIC_F);
-        auto fold2 = [&](const uint32_t *r, int t0, const uint64_t *sc) {   // two tokens: columns 8 t0 .. 8 t0 + 15
+                for (int t = 0; t < 2; ++t) {
 #pragma unroll
-            for (int t = 0; t < 2; ++t) {
+                    for (int n = 0; n < 4; ++n) { acc[t0 + t][n] = f2_fma(sc[t0 + t], f2_pack_bits(r[8 * t + 2 * n], r[8 * t + 2 * n + 1]), acc[t0 + t][n]); }
+                }
+            };
+            ok = mbar_wait_bounded(d_full(0), 0u, limit);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) { tc_fence_after(); tmem_ld16(tbase, ra); tmem_ld16(tbase + 16u, rb); }
+            static_assert(PF_BATCH == PF_DBUF, "the unrolled epilogue pairs block j of a batch with accumulator buffer j");
+            for (int q = 0; q < n_batch && ok; ++q) {
+                const uint32_t ring_q = (uint32_t)(q % NQ) * PF_BATCH;
+                const uint32_t dw_q = dw_addr + ring_q * PF_WTILE, dx_q = dx_addr + ring_q * YQ;
 #pragma unroll
-                for (int n = 0; n < 4; ++n) {   // acc = fma(scale, pattern - 1.5 * 2^23, acc) on two accumulators at a time
-                    acc[t0 + t][n] = f2_fma(sc[t0 + t], f2_add(f2_pack_bits(r[8 * t + 2 * n], r[8 * t + 2 * n + 1]), minus_magic), acc[t0 + t][n]);
+                for (int j = 0; j < PF_BATCH; ++j) {
+                    const int b = q * PF_BATCH + j;
+                    if (b >= nb || !ok) { break; }
+                    const uint32_t taddr = tbase + (uint32_t)(j * PF_N);
+                    const float dw = h2f((uint16_t)lds16(dw_q + (uint32_t)j * PF_WTILE));
+                    const float4 dxa = lds128f(dx_q + (uint32_t)j * YQ), dxb = lds128f(dx_q + (uint32_t)j * YQ + 16u);
+                    const float s0 = __fmul_rn(dw, dxa.x), s1 = __fmul_rn(dw, dxa.y), s2 = __fmul_rn(dw, dxa.z), s3 = __fmul_rn(dw, dxa.w);
+                    const float s4 = __fmul_rn(dw, dxb.x), s5 = __fmul_rn(dw, dxb.y), s6 = __fmul_rn(dw, dxb.z), s7 = __fmul_rn(dw, dxb.w);
+                    const uint64_t sc[8] = {f2_pack(s0, s0), f2_pack(s1, s1), f2_pack(s2, s2), f2_pack(s3, s3),
+                                            f2_pack(s4, s4), f2_pack(s5, s5), f2_pack(s6, s6), f2_pack(s7, s7)};
+                    tmem_ld_wait();                       // columns 0..31 of block b are in registers
+                    fold2(ra, 0, sc);
+                    tmem_ld16(taddr + 32u, ra);
+                    fold2(rb, 2, sc);
+                    tmem_ld16(taddr + 48u, rb);
+                    tmem_ld_wait();                       // columns 32..63 too: the buffer has been read
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) { mbar_arrive(d_free(j)); }
+                    fold2(ra, 4, sc);
+                    const bool more = b + 1 < nb;
+                    const uint32_t tnext = tbase + (uint32_t)(((j + 1) % PF_DBUF) * PF_N);
+                    if (more) {                           // the next block's first columns arrive while the last two tokens are folded
+                        ok = mbar_wait_bounded(d_full((j + 1) % PF_DBUF), (uint32_t)(q + (j + 1) / PF_DBUF) & 1u, limit);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (ok) { tc_fence_after(); tmem_ld16(tnext, ra); }
+                    }
+                    fold2(rb, 6, sc);
+                    if (more && ok) { tmem_ld16(tnext + 16u, rb); }
+                    if (lane == 0 && (j == PF_BATCH - 1 || b == nb - 1)) { mbar_arrive(st_free(q % NQ)); }   // the batch's scales have been read
                 }
             }
-        };
-        bool ok = mbar_wait_bounded(d_full(0), 0u, limit);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) { tc_fence_after(); tmem_ld16(tbase, ra); tmem_ld16(tbase + 16u, rb); }
-        // a batch per outer iteration: block j of a batch uses accumulator buffer j and stage 4 (q % PF_RING) + j, so that inside the
-        // unrolled body every address is a constant offset and every phase parity a bit of q
-        static_assert(PF_BATCH == PF_DBUF, "the unrolled epilogue pairs block j of a batch with accumulator buffer j");
-        for (int q = 0; q < n_batch && ok; ++q) {
-            const uint32_t ring_q = (uint32_t)(q % NQ) * PF_BATCH;
-            const uint32_t dw_q = dw_addr + ring_q * PF_WTILE, dx_q = dx_addr + ring_q * PF_YQ_BYTES;
-#pragma unroll
-            for (int j = 0; j < PF_BATCH; ++j) {
-                const int b = q * PF_BATCH + j;
-                if (b >= nb || !ok) { break; }
-                const uint32_t taddr = tbase + (uint32_t)(j * PF_N);
-                float dw = h2f((uint16_t)lds16(dw_q + (uint32_t)j * PF_WTILE));
-                if (WT == 2) { dw = __fmul_rn(dw, 0.0625f); }   // exact: undoes the factor 16 of the nibble trick
-                const float4 dxa = lds128f(dx_q + (uint32_t)j * PF_YQ_BYTES), dxb = lds128f(dx_q + (uint32_t)j * PF_YQ_BYTES + 16u);
-                const float s0 = __fmul_rn(dw, dxa.x), s1 = __fmul_rn(dw, dxa.y), s2 = __fmul_rn(dw, dxa.z), s3 = __fmul_rn(dw, dxa.w);
-                const float s4 = __fmul_rn(dw, dxb.x), s5 = __fmul_rn(dw, dxb.y), s6 = __fmul_rn(dw, dxb.z), s7 = __fmul_rn(dw, dxb.w);
-                const uint64_t sc[8] = {f2_pack(s0, s0), f2_pack(s1, s1), f2_pack(s2, s2), f2_pack(s3, s3),
-                                        f2_pack(s4, s4), f2_pack(s5, s5), f2_pack(s6, s6), f2_pack(s7, s7)};
-                tmem_ld_wait();                       // columns 0..31 of block b are in registers
-                fold2(ra, 0, sc);
-                tmem_ld16(taddr + 32u, ra);
-                fold2(rb, 2, sc);
-                tmem_ld16(taddr + 48u, rb);
-                tmem_ld_wait();                       // columns 32..63 too: the buffer has been read, put the offset pattern back
-                tmem_st16(taddr, pattern); tmem_st16(taddr + 16u, pattern); tmem_st16(taddr + 32u, pattern); tmem_st16(taddr + 48u, pattern);
-                fold2(ra, 4, sc);
-                const bool more = b + 1 < nb;
-                const uint32_t tnext = tbase + (uint32_t)(((j + 1) % PF_DBUF) * PF_N);
-                if (more) {                           // the next block's first columns arrive while the last two tokens are folded
-                    ok = mbar_wait_bounded(d_full((j + 1) % PF_DBUF), (uint32_t)(q + (j + 1) / PF_DBUF) & 1u, limit);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (ok) { tc_fence_after(); tmem_ld16(tnext, ra); }
+        } else {
+            for (int i = 0; i < PF_DBUF; ++i) {   // the offset pattern into this thread's part of every buffer
+                tmem_st32_same(tbase + (uint32_t)(i * PF_N), MAGIC_I);
+                tmem_st32_same(tbase + (uint32_t)(i * PF_N) + 32u, MAGIC_I);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) { for (int i = 0; i < PF_DBUF; ++i) { mbar_arrive(d_free(i)); } }
+
+            uint32_t ra[16], rb[16], pattern[16];
+    #pragma unroll
+            for (int i = 0; i < 16; ++i) { asm volatile("mov.b32 %0, %1;" : "=r"(pattern[i]) : "r"(MAGIC_I)); }   // (opaque to the compiler: 16 live registers)
+            const uint64_t minus_magic = f2_pack(-MAGIC_F, -MAGIC_F);
+            auto fold2 = [&](const uint32_t *r, int t0, const uint64_t *sc) {   // two tokens: columns 8 t0 .. 8 t0 + 15
+    #pragma unroll
+                for (int t = 0; t < 2; ++t) {
+    #pragma unroll
+                    for (int n = 0; n < 4; ++n) {   // acc = fma(scale, pattern - 1.5 * 2^23, acc) on two accumulators at a time
+                        acc[t0 + t][n] = f2_fma(sc[t0 + t], f2_add(f2_pack_bits(r[8 * t + 2 * n], r[8 * t + 2 * n + 1]), minus_magic), acc[t0 + t][n]);
+                    }
                 }
-                fold2(rb, 6, sc);
-                if (more && ok) { tmem_ld16(tnext + 16u, rb); }
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    mbar_arrive(d_free(j));
-                    if (j == PF_BATCH - 1 || b == nb - 1) { mbar_arrive(st_free(q % NQ)); }   // the batch's scales have been read
+            };
+            ok = mbar_wait_bounded(d_full(0), 0u, limit);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) { tc_fence_after(); tmem_ld16(tbase, ra); tmem_ld16(tbase + 16u, rb); }
+            // a batch per outer iteration: block j of a batch uses accumulator buffer j and stage 4 (q % PF_RING) + j, so that inside the
+            // unrolled body every address is a constant offset and every phase parity a bit of q
+            static_assert(PF_BATCH == PF_DBUF, "the unrolled epilogue pairs block j of a batch with accumulator buffer j");
+            for (int q = 0; q < n_batch && ok; ++q) {
+                const uint32_t ring_q = (uint32_t)(q % NQ) * PF_BATCH;
+                const uint32_t dw_q = dw_addr + ring_q * PF_WTILE, dx_q = dx_addr + ring_q * YQ;
+    #pragma unroll
+                for (int j = 0; j < PF_BATCH; ++j) {
+                    const int b = q * PF_BATCH + j;
+                    if (b >= nb || !ok) { break; }
+                    const uint32_t taddr = tbase + (uint32_t)(j * PF_N);
+                    const float dw = h2f((uint16_t)lds16(dw_q + (uint32_t)j * PF_WTILE));
+                    const float4 dxa = lds128f(dx_q + (uint32_t)j * YQ), dxb = lds128f(dx_q + (uint32_t)j * YQ + 16u);
+                    const float s0 = __fmul_rn(dw, dxa.x), s1 = __fmul_rn(dw, dxa.y), s2 = __fmul_rn(dw, dxa.z), s3 = __fmul_rn(dw, dxa.w);
+                    const float s4 = __fmul_rn(dw, dxb.x), s5 = __fmul_rn(dw, dxb.y), s6 = __fmul_rn(dw, dxb.z), s7 = __fmul_rn(dw, dxb.w);
+                    const uint64_t sc[8] = {f2_pack(s0, s0), f2_pack(s1, s1), f2_pack(s2, s2), f2_pack(s3, s3),
+                                            f2_pack(s4, s4), f2_pack(s5, s5), f2_pack(s6, s6), f2_pack(s7, s7)};
+                    tmem_ld_wait();                       // columns 0..31 of block b are in registers
+                    fold2(ra, 0, sc);
+                    tmem_ld16(taddr + 32u, ra);
+                    fold2(rb, 2, sc);
+                    tmem_ld16(taddr + 48u, rb);
+                    tmem_ld_wait();                       // columns 32..63 too: the buffer has been read, put the offset pattern back
+                    tmem_st16(taddr, pattern); tmem_st16(taddr + 16u, pattern); tmem_st16(taddr + 32u, pattern); tmem_st16(taddr + 48u, pattern);
+                    fold2(ra, 4, sc);
+                    const bool more = b + 1 < nb;
+                    const uint32_t tnext = tbase + (uint32_t)(((j + 1) % PF_DBUF) * PF_N);
+                    if (more) {                           // the next block's first columns arrive while the last two tokens are folded
+                        ok = mbar_wait_bounded(d_full((j + 1) % PF_DBUF), (uint32_t)(q + (j + 1) / PF_DBUF) & 1u, limit);
+                        ok = __all_sync(0xffffffffu, ok);
+                        if (ok) { tc_fence_after(); tmem_ld16(tnext, ra); }
+                    }
+                    fold2(rb, 6, sc);
+                    if (more && ok) { tmem_ld16(tnext + 16u, rb); }
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        mbar_arrive(d_free(j));
+                        if (j == PF_BATCH - 1 || b == nb - 1) { mbar_arrive(st_free(q % NQ)); }   // the batch's scales have been read
+                    }
                 }
             }
         }
@@ -265,11 +340,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_gemm_kernel(PrefillGemm
 // activations of T tokens -> compact Q8_0 blocks grouped by (token tile, block): [T/16][nb][16 x 32 s8 | 16 f32 scales].
 // One CTA per token; RMSNorm and the quantizer as in the mat-vec prologue (NormRMS, backend/host/operator/non-linear.cpp:194-223:
 // groups of four squares formed in parallel, the running sum on one thread; Quantizator<FP32,Q8_0>, simd/vec_convert.h:178-261).
-// TOKT tokens per tile; YSUM: the blocks' integer sums follow the scales as floats (the K-quant kernels need them)
-template <bool NORM, int TOKT, bool YSUM>
+// TOKT tokens per tile; YSUM: the blocks' integer sums follow the scales as floats (the K-quant kernels need them); F8: every
+// activation byte as two e4m3 values (a plane of TOKT x 32 codes each: the multiple of 16 and the rest) for the Q4_0 kernel
+template <bool NORM, int TOKT, bool YSUM, bool F8>
 __global__ void __launch_bounds__(PF_QUANT_THREADS) prefill_quant_kernel(const float *x, int64_t x_stride, int K, const float *norm_w, float eps, uint8_t *yq,
                                                                          int part_len, int64_t part_stride) {
-    constexpr int YQB = TOKT * 32 + TOKT * 4 * (YSUM ? 2 : 1);
+    constexpr int YQB = (F8 ? 2 : 1) * TOKT * 32 + TOKT * 4 * (YSUM ? 2 : 1);
+    constexpr int SCALES = (F8 ? 2 : 1) * TOKT * 32;   // offset of the scales inside a block's record
     extern __shared__ __align__(16) float v3[];
     __shared__ float scale_s;
     const int tid = threadIdx.x, token = blockIdx.x;
@@ -335,19 +412,26 @@ __global__ void __launch_bounds__(PF_QUANT_THREADS) prefill_quant_kernel(const f
             if (gi < n4) {
                 const int b = gi >> 3, w = gi & 7;
                 uint8_t *blk = tile + (int64_t)b * YQB;
-                reinterpret_cast<uint32_t *>(blk + tt * 32)[w] = q;
+                if (F8) {
+                    uint32_t hi, lo;
+                    e4m3_split4(q, hi, lo);
+                    reinterpret_cast<uint32_t *>(blk + tt * 32)[w] = hi;
+                    reinterpret_cast<uint32_t *>(blk + TOKT * 32 + tt * 32)[w] = lo;
+                } else {
+                    reinterpret_cast<uint32_t *>(blk + tt * 32)[w] = q;
+                }
                 if (w == 0) {
-                    reinterpret_cast<float *>(blk + TOKT * 32)[tt] = h2f(dh);
-                    if (YSUM) { reinterpret_cast<float *>(blk + TOKT * 32 + TOKT * 4)[tt] = (float)sum; }
+                    reinterpret_cast<float *>(blk + SCALES)[tt] = h2f(dh);
+                    if (YSUM) { reinterpret_cast<float *>(blk + SCALES + TOKT * 4)[tt] = (float)sum; }
                 }
             }
         }
     }
 }
 
-// upload-time re-layout: raw 18-byte / 34-byte blocks of rows [0, n_rows) -> tiles of 128 rows x 1 block: the s8 A operand
-// (core matrices of 8 rows x 16 bytes; Q4_0: element k < 16 is 16 * (low nibble of byte k - 8), element 16 + k the same of
-// the high nibble - the factor 16 is undone in the scale, exactly) followed by the 128 fp16 block scales
+// upload-time re-layout: raw 18-byte / 34-byte blocks of rows [0, n_rows) -> tiles of 128 rows x 1 block: the A operand
+// (core matrices of 8 rows x 16 bytes; Q8_0: the s8 values; Q4_0: element k < 16 is the e4m3 code of (low nibble of byte k - 8),
+// element 16 + k the same of the high nibble) followed by the 128 fp16 block scales
 template <int WT>
 __global__ void prefill_retile_kernel(const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0) {
     const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -363,9 +447,15 @@ __global__ void prefill_retile_kernel(const uint8_t *raw, int64_t row_stride, in
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
         if (WT == 2) {
-            const uint32_t v = (uint32_t)(src[2 + 4 * k] | (src[3 + 4 * k] << 8) | (src[4 + 4 * k] << 16) | ((uint32_t)src[5 + 4 * k] << 24)) ^ 0x88888888u;
-            lo[k] = (v << 4) & 0xf0f0f0f0u;
-            hi[k] = v & 0xf0f0f0f0u;
+            uint32_t l = 0u, h = 0u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int byte = src[2 + 4 * k + i];
+                l |= e4m3_of_signed((byte & 15) - 8) << (8 * i);
+                h |= e4m3_of_signed((byte >> 4) - 8) << (8 * i);
+            }
+            lo[k] = l;
+            hi[k] = h;
         } else {
             lo[k] = (uint32_t)(src[2 + 4 * k] | (src[3 + 4 * k] << 8) | (src[4 + 4 * k] << 16) | ((uint32_t)src[5 + 4 * k] << 24));
             hi[k] = (uint32_t)(src[18 + 4 * k] | (src[19 + 4 * k] << 8) | (src[20 + 4 * k] << 16) | ((uint32_t)src[21 + 4 * k] << 24));
@@ -408,22 +498,22 @@ __global__ void prefill_silu_mul_kernel(const float *upgate, int T, int F, const
     act[i] = __fmul_rn(up, silu_table[f2h(gate)]);
 }
 
-constexpr size_t PF_SMEM_BYTES = (size_t)PF_STAGES * (PF_WTILE + PF_YQ_BYTES + PF_TILE) + 8 * (3 * PF_RING + 2 * PF_DBUF) + 16;
-
 template <int WT>
 cudaError_t launch_gemm_t(const PrefillGemm &g, cudaStream_t stream) {
-    const size_t smem = PF_SMEM_BYTES;
+    const size_t smem = PfGeom<WT>::SMEM;
     cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(prefill_gemm_kernel<WT>), smem);
     if (err != cudaSuccess) { return err; }
     const dim3 grid((unsigned)((g.T + PF_TOK - 1) / PF_TOK), (unsigned)((g.n_rows + PF_M - 1) / PF_M));
-    prefill_gemm_kernel<WT><<<grid, PF_THREADS, smem, stream>>>(g);
+    prefill_gemm_kernel<WT><<<grid, PfGeom<WT>::THREADS, smem, stream>>>(g);
     return cudaGetLastError();
 }
 
 }  // namespace
 
 size_t prefill_weight_bytes(int type, int64_t n_rows, int nb) { return (size_t)((n_rows + PF_ROWS - 1) / PF_ROWS) * nb * ((type == 12 || type == 14) ? PF_KQ_WTILE : PF_WTILE); }
-size_t prefill_act_bytes(int T, int nb) { return std::max((size_t)((T + PF_TOK - 1) / PF_TOK) * nb * PF_YQ_BYTES, (size_t)((T + PF_KQ_TOK - 1) / PF_KQ_TOK) * nb * PF_KQ_YQ_BYTES); }
+size_t prefill_act_bytes(int T, int nb) {   // (the largest of the layouts)
+    return std::max((size_t)((T + PF_TOK - 1) / PF_TOK) * nb * std::max(PF_YQ_BYTES, PF_YQ_BYTES_F8), (size_t)((T + PF_KQ_TOK - 1) / PF_KQ_TOK) * nb * PF_KQ_YQ_BYTES);
+}
 
 cudaError_t launch_prefill_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0, cudaStream_t stream) {
     if (type == 12 || type == 14) { return launch_prefill_retile_kq(type, raw, row_stride, n_rows, nb, base, dst_row0, stream); }
@@ -435,18 +525,23 @@ cudaError_t launch_prefill_retile(int type, const uint8_t *raw, int64_t row_stri
     return cudaGetLastError();
 }
 
-cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K, const float *norm_w, float eps, uint8_t *yq, cudaStream_t stream, bool kq_layout,
+cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K, const float *norm_w, float eps, uint8_t *yq, cudaStream_t stream, int weight_type,
                                  int part_len, int64_t part_stride) {
+    if (weight_type != 2 && weight_type != 8 && weight_type != 12 && weight_type != 14) { return cudaErrorInvalidValue; }
+    const bool kq_layout = weight_type == 12 || weight_type == 14;
     if (part_len <= 0) { part_len = K; part_stride = 0; }
     if ((part_len & 3) || (part_stride & 3) || K % part_len != 0) { return cudaErrorInvalidValue; }
     if (T < 1 || K < 32 || (K & 31) || K > PF_MAX_K || (x_stride & 3) || ((uintptr_t)x & 15)) { return cudaErrorInvalidValue; }
     const size_t smem = norm_w != nullptr ? (size_t)K : 0;   // K / 4 floats
     if (kq_layout) {
-        if (norm_w != nullptr) { prefill_quant_kernel<true, PF_KQ_TOK, true><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq, part_len, part_stride); }
-        else                   { prefill_quant_kernel<false, PF_KQ_TOK, true><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq, part_len, part_stride); }
+        if (norm_w != nullptr) { prefill_quant_kernel<true, PF_KQ_TOK, true, false><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq, part_len, part_stride); }
+        else                   { prefill_quant_kernel<false, PF_KQ_TOK, true, false><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq, part_len, part_stride); }
+    } else if (weight_type == 2) {
+        if (norm_w != nullptr) { prefill_quant_kernel<true, PF_TOK, false, true><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq, part_len, part_stride); }
+        else                   { prefill_quant_kernel<false, PF_TOK, false, true><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq, part_len, part_stride); }
     } else {
-        if (norm_w != nullptr) { prefill_quant_kernel<true, PF_TOK, false><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq, part_len, part_stride); }
-        else                   { prefill_quant_kernel<false, PF_TOK, false><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq, part_len, part_stride); }
+        if (norm_w != nullptr) { prefill_quant_kernel<true, PF_TOK, false, false><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq, part_len, part_stride); }
+        else                   { prefill_quant_kernel<false, PF_TOK, false, false><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq, part_len, part_stride); }
     }
     return cudaGetLastError();
 }

@@ -148,10 +148,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillG
             const int b0 = q * PF_BATCH, n = min(PF_BATCH, nb - b0), s0 = b0 % NS;
             for (int j = 0; j < n; ++j) {
                 const uint32_t ysrc_s = y_ring + (uint32_t)(s0 + j) * KQ_YQ, bdst = b_ring + (uint32_t)(s0 + j) * PF_TILE;
+                uint32_t v[KQ_TOK * 8 / 32];
+#pragma unroll
+                for (int k = 0; k < KQ_TOK * 8 / 32; ++k) { v[k] = lds32(ysrc_s + (uint32_t)(lane + 32 * k) * 4u); }   // all loads in flight before the first store
 #pragma unroll
                 for (int k = 0; k < KQ_TOK * 8 / 32; ++k) {
                     const int i = lane + 32 * k, tt = i >> 3, w = i & 7, row = 4 * (tt >> 1) + 2 * (w >> 2) + (tt & 1);
-                    sts32(bdst + (uint32_t)(row >> 3) * 256u + (uint32_t)(w >> 2) * 128u + (uint32_t)(row & 7) * 16u + (uint32_t)(w & 3) * 4u, lds32(ysrc_s + (uint32_t)i * 4u));
+                    sts32(bdst + (uint32_t)(row >> 3) * 256u + (uint32_t)(w >> 2) * 128u + (uint32_t)(row & 7) * 16u + (uint32_t)(w & 3) * 4u, v[k]);
                 }
             }
             fence_async_smem();

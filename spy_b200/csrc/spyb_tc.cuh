@@ -17,6 +17,8 @@ constexpr int PF_RING        = 4;                  // batches in the shared-memo
 constexpr int PF_STAGES      = PF_RING * PF_BATCH; // blocks in the rings
 constexpr int PF_MMA_WARPS   = 2;                  // warps whose first thread issues the MMAs of every PF_MMA_WARPS-th block
 constexpr int PF_THREADS     = (PF_EPI_WARPS + 2 + PF_MMA_WARPS) * 32;   // + the copy warp and the expander warp
+constexpr int PF_MMA_WARPS_F8 = 4;                 // the e4m3 form issues two MMAs per block: four issuing threads
+constexpr int PF_THREADS_F8  = (PF_EPI_WARPS + 2 + PF_MMA_WARPS_F8) * 32;
 constexpr int PF_DBUF        = 4;                  // accumulator buffers in tensor memory, PF_NCOL columns each (512 columns = all of it)
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
@@ -54,6 +56,15 @@ __device__ __forceinline__ void mma_s8_ss(uint32_t d_tmem, uint64_t a_desc, uint
                  "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
                  ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(PF_IDESC), "r"(accumulate), "r"(zero) : "memory");
 }
+// e4m3 operands (kind::f8f6f4), f32 accumulators: D (+)= A B^T. Small integers are exact in e4m3 (|v| <= 16, and multiples of 16
+// up to 128), their products and the sums of a block's few products are exact in f32, so D holds (float)(integer sum) itself.
+constexpr uint32_t PF_IDESC_F8 = (1u << 4) | ((uint32_t)(PF_NCOL >> 3) << 17) | ((uint32_t)(PF_M >> 4) << 24);
+__device__ __forceinline__ void mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    const uint32_t zero = 0;
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(PF_IDESC_F8), "r"(accumulate), "r"(zero) : "memory");
+}
 __device__ __forceinline__ void mma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -78,6 +89,27 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t *v) {
                    "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]) : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// e4m3 code of the integer v, 0 <= v <= 15 (exact: three mantissa bits cover 8..15), and of a signed value in [-15, 15]
+__host__ __device__ __forceinline__ uint32_t e4m3_of_small(uint32_t v) {
+    if (v == 0) { return 0u; }
+    const int e = v >= 8 ? 3 : v >= 4 ? 2 : v >= 2 ? 1 : 0;
+    return ((uint32_t)(e + 7) << 3) | ((v << (3 - e)) & 7u);
+}
+__host__ __device__ __forceinline__ uint32_t e4m3_of_signed(int v) { return v < 0 ? (0x80u | e4m3_of_small((uint32_t)-v)) : e4m3_of_small((uint32_t)v); }
+// a Q8_0 activation byte y in [-127, 127] as two e4m3 values: y = hi + lo with lo = y mod 16 in [0, 15] and hi = y - lo a
+// multiple of 16 in [-128, 112] (the code of |hi| / 16 with the exponent raised by four)
+__device__ __forceinline__ void e4m3_split4(uint32_t q, uint32_t &hi, uint32_t &lo) {
+    hi = 0u; lo = 0u;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int y = (int)(int8_t)((q >> (8 * i)) & 0xffu);
+        const int yl = y & 15, yh = (y - yl) >> 4;   // yh in [-8, 7]
+        const uint32_t ch = yh == 0 ? 0u : (e4m3_of_signed(yh) + 0x20u);
+        hi |= ch << (8 * i);
+        lo |= e4m3_of_small((uint32_t)yl) << (8 * i);
+    }
+}
 
 // feeder roles (copy, expansion, MMA issue) run ahead of the epilogue: their waits back off instead of competing with the
 // epilogue warps for issue slots
