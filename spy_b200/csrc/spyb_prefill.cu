@@ -5,17 +5,24 @@
 // per 32-element block the eight integer "lane sums" (4 products each) are converted to f32 and folded into eight f32
 // accumulators with acc = fma(d_w * d_x, lane_sum, acc), block after block, and the eight accumulators meet in the
 // hsum_float_8 tree at the end of the row. Only the integer lane sums are a contraction; everything after them is
-// order-bound f32 work. So one MMA computes the lane sums of one block for a tile of 128 rows x 16 tokens:
+// order-bound f32 work. So the tensor core computes the lane sums of one block for a tile of 128 rows x 16 tokens:
 //
-//   A (128 x 32, s8)  = the block's weights of 128 rows (Q4_0: 16 * (nibble - 8), the factor 16 goes into the scale)
-//   B (128 x 32, s8)  = for token t and accumulator n the row 8 t + n holds the four activation bytes of accumulator n
-//                       at their place in the block and zeros elsewhere (block-diagonal per token)
-//   D (128 x 128, s32, tensor memory) = A B^T: D[r][8 t + n] = lane sum n of (row r, token t) of this block
+//   A (128 x 32)  = the block's weights of 128 rows
+//   B (128 x 32)  = for token t and accumulator n the row 8 t + n holds the four activation bytes of accumulator n
+//                   at their place in the block and zeros elsewhere (block-diagonal per token)
+//   D (128 x 128, tensor memory) = A B^T: D[r][8 t + n] = lane sum n of (row r, token t) of this block
 //
-// with accumulate = 0 for every block, four D buffers in flight. The eight epilogue warps read D back with tcgen05.ld
-// (lane = row, 64 columns = 8 tokens per thread), convert, and run the CPU's FMA chains in block order on 64 f32
-// accumulators per thread. Operands reach shared memory by cp.async.bulk (weights in a 128-row x 1-block tile layout
-// made at upload, activations as compact Q8_0 blocks); the epilogue warps also expand them into the canonical K-major
+// in one of two forms, four D buffers in flight:
+//   Q8_0 weights: s8 operands, s32 accumulators (kind::i8). The buffers are preset with the s32 pattern of 1.5 * 2^23 and the
+//     MMA accumulates onto it, so that what the epilogue reads back is the bit pattern of the float 1.5 * 2^23 + lane_sum and
+//     one exact subtraction gives (float)lane_sum (|lane_sum| < 2^22); the epilogue writes the pattern back after reading.
+//   Q4_0 weights: e4m3 operands, f32 accumulators (kind::f8f6f4). nibble - 8 is exact in e4m3, and an activation byte y is
+//     the sum of two e4m3 values, y - (y mod 16) and y mod 16: two MMAs per block (accumulate = 0, then 1) onto the same
+//     buffer. Every product and the sum of a lane's four products are small integers, exact in f32, so D holds
+//     (float)lane_sum itself: no conversion, no preset, and the buffer is free for the next MMA as soon as it has been read.
+// The epilogue warps read D back with tcgen05.ld (lane = row) and run the CPU's FMA chains in block order on f32 accumulators
+// held as packed f32x2 pairs. Operands reach shared memory by cp.async.bulk (weights in a 128-row x 1-block tile layout
+// made at upload, activations as compact blocks); an expander warp writes the activations into the canonical K-major
 // no-swizzle operand layout (core matrices of 8 rows x 16 bytes) ahead of the MMA. Every wait is bounded.
 #include "spyb_tc.cuh"
 
@@ -27,33 +34,33 @@ namespace {
 
 constexpr int PF_N           = 8 * PF_TOK;         // 8 accumulator columns per token
 static_assert(PF_N == PF_NCOL, "16 tokens x 8 accumulators fill the MMA's columns");
-constexpr int PF_WTILE       = PF_TILE + 256;      // a weight tile in HBM: the s8 A operand of 128 rows x 32, then 128 fp16 block scales
+constexpr int PF_WTILE       = PF_TILE + 256;      // a weight tile in HBM: the A operand of 128 rows x 32 (s8 or e4m3), then 128 fp16 block scales
 constexpr int PF_QUANT_THREADS = 512;
 constexpr int PF_QUANT_GROUPS  = PF_MAX_K / (4 * PF_QUANT_THREADS);   // float4 groups per thread
 
 // ---------------------------------------------------------------------------------------------
 // the GEMM. grid = (token tiles, row tiles); one CTA per SM (it takes all 512 tensor-memory columns).
 //
-// Warps 0-15  epilogue: row = 32 (warp % 4) + lane, tokens 4 (warp / 4) .. + 3 of the tile; four warps per scheduler and loads
-//             requested a half block ahead hide the latency of tensor memory behind the f32 chains
-// warp 16     one thread streams batches of PF_BATCH blocks with cp.async.bulk: two copies per batch (the weight tiles, which
-//             arrive as A operands, and the compact activations) - issuing a bulk copy costs its thread hundreds of cycles
-// warp 17     expands the compact activations of a batch into the B operands
-// warps 18-19 one thread each issues the MMAs of alternate blocks (an MMA and its commit hold the issuing thread for
-//             ~450 cycles; threads of different warps issue in parallel)
-//
-// The accumulator buffers hold the s32 pattern of 1.5 * 2^23 in every element and the MMA accumulates onto it, so what
-// the epilogue reads back is the bit pattern of the float 1.5 * 2^23 + lane_sum: one exact subtraction gives
-// (float)lane_sum without an integer conversion (|lane_sum| < 2^22). The epilogue writes the pattern back after reading.
+// Q8_0 form (12 warps, 168 registers): warps 0-7 epilogue - row = 32 (warp % 4) + lane, tokens 8 (warp / 4) .. + 7 of the tile,
+//             read back 16 columns at a time into two alternating register sets
+// Q4_0 form (20 warps, 96 registers): warps 0-15 epilogue - row = 32 (warp % 4) + lane, tokens 4 (warp / 4) .. + 3; four warps
+//             per scheduler hide the latency of tensor memory behind one another's f32 chains
+// then        one warp whose first thread streams batches of PF_BATCH blocks with cp.async.bulk: two copies per batch (the
+//             weight tiles, which arrive as A operands, and the compact activations) - issuing a bulk copy costs its thread
+//             hundreds of cycles
+//             one warp that expands the compact activations of a batch into the B operands
+//             two warps whose first thread issues the MMAs of alternate blocks (MMA and commit hold the issuing thread for
+//             hundreds of cycles; threads of different warps issue in parallel)
 //
 // Shared memory: rings of PF_STAGES blocks (PF_RING batches), one ring per kind so that a batch is one contiguous run:
-//   A ring  [PF_STAGES][4352]   weight tiles (s8 operand + 128 fp16 scales), written by cp.async.bulk
-//   Y ring  [PF_STAGES][576]    compact activations (16 tokens x 32 s8, 16 f32 scales), written by cp.async.bulk
-//   B ring  [PF_STAGES][4096]   expanded activations, written by the expander warp
+//   A ring  [PF_STAGES][4352]          weight tiles (A operand + 128 fp16 scales), written by cp.async.bulk
+//   Y ring  [PF_STAGES][576 | 1088]    compact activations (16 tokens x 32 bytes, or two e4m3 planes of them; 16 f32 scales)
+//   B ring  [PF_STAGES][4096 | 8192]   expanded activations (one or two B operands), written by the expander warp
 template <int WT> struct PfGeom {
     static constexpr bool F8      = WT == 2;                               // Q4_0: e4m3 operands, f32 accumulators, two MMAs per block
     static constexpr int  YQ      = F8 ? PF_YQ_BYTES_F8 : PF_YQ_BYTES;     // a block's compact activations
     static constexpr int  BT      = F8 ? 2 * PF_TILE : PF_TILE;            // a block's B operand(s)
+    static constexpr int  EPI_W   = F8 ? PF_EPI_WARPS_F8 : PF_EPI_WARPS;
     static constexpr int  MMA_W   = F8 ? PF_MMA_WARPS_F8 : PF_MMA_WARPS;
     static constexpr int  THREADS = F8 ? PF_THREADS_F8 : PF_THREADS;
     static constexpr size_t SMEM  = (size_t)PF_STAGES * (PF_WTILE + YQ + BT) + 8 * (3 * PF_RING + 2 * PF_DBUF) + 16;
@@ -63,7 +70,7 @@ template <int WT>
 __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(PrefillGemm g) {
     constexpr int NS = PF_STAGES, NQ = PF_RING;
     constexpr bool F8 = PfGeom<WT>::F8;
-    constexpr int YQ = PfGeom<WT>::YQ, BT = PfGeom<WT>::BT, MMA_W = PfGeom<WT>::MMA_W, THREADS = PfGeom<WT>::THREADS;
+    constexpr int YQ = PfGeom<WT>::YQ, BT = PfGeom<WT>::BT, EPI_W = PfGeom<WT>::EPI_W, MMA_W = PfGeom<WT>::MMA_W, THREADS = PfGeom<WT>::THREADS;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const uint32_t a_ring = sbase, y_ring = a_ring + NS * PF_WTILE, b_ring = y_ring + NS * YQ;
@@ -83,8 +90,8 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
     const uint8_t *ysrc = g.yq + ((int64_t)tok_tile * nb) * YQ;
 
     if (tid == 0) {
-        for (int q = 0; q < NQ; ++q) { mbar_init(raw_full(q), 1); mbar_init(ops_full(q), 1); mbar_init(st_free(q), PF_EPI_WARPS); }
-        for (int i = 0; i < PF_DBUF; ++i) { mbar_init(d_full(i), 1); mbar_init(d_free(i), PF_EPI_WARPS); }
+        for (int q = 0; q < NQ; ++q) { mbar_init(raw_full(q), 1); mbar_init(ops_full(q), 1); mbar_init(st_free(q), EPI_W); }
+        for (int i = 0; i < PF_DBUF; ++i) { mbar_init(d_full(i), 1); mbar_init(d_free(i), EPI_W); }
         mbar_init_fence();
     }
     // the B tiles are zero except where the expansion writes, and it writes the same places for every block
@@ -99,12 +106,12 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
 
-    if (warp >= PF_EPI_WARPS + 2) {
+    if (warp >= EPI_W + 2) {
         // ---- MMA warps: the first thread of warp m issues the 128 x 128 x 32 MMA of blocks m, m + PF_MMA_WARPS, ... onto a buffer
         // that holds the offset pattern; MMAs into different buffers do not depend on one another
         if (lane == 0) {
             int last = -1;
-            for (int b = warp - (PF_EPI_WARPS + 2); b < nb; b += MMA_W) {
+            for (int b = warp - (EPI_W + 2); b < nb; b += MMA_W) {
                 const int s = b % NS, q = b / PF_BATCH, buf = b % PF_DBUF;
                 PF_STAMP(2, b, 0);
                 if (!mbar_wait_relaxed(ops_full(q % NQ), (uint32_t)(q / NQ) & 1u, limit)) { pf_report(g.error_flag, 5); break; }
@@ -126,7 +133,7 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
             // every MMA has completed (it reads shared memory and writes tensor memory) before the CTA leaves
             if (last >= 0 && !mbar_wait_relaxed(d_full(last % PF_DBUF), (uint32_t)(last / PF_DBUF) & 1u, limit)) { pf_report(g.error_flag, 5); }
         }
-    } else if (warp == PF_EPI_WARPS) {
+    } else if (warp == EPI_W) {
         // ---- copy warp: one thread requests batch after batch
         if (lane == 0) {
             int issued = 0;
@@ -145,7 +152,7 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
                 if (!mbar_wait_relaxed(raw_full(q % NQ), (uint32_t)(q / NQ) & 1u, limit)) { pf_report(g.error_flag, 4); break; }
             }
         }
-    } else if (warp == PF_EPI_WARPS + 1) {
+    } else if (warp == EPI_W + 1) {
         // ---- expander warp: word w of token tt of the compact activations -> row 8 tt + w of B, at its own place in the
         // block (the rest of B stays zero); one proxy fence per batch makes the writes visible to the tensor core
         for (int q = 0; q < n_batch; ++q) {
@@ -174,27 +181,31 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
         // ---- epilogue warps: row = 32 (warp % 4) + lane, tokens 8 (warp / 4) .. + 7 of the tile = 64 columns of D, read back 16
         // columns (two tokens) at a time into two alternating register sets: a set is requested again as soon as its values
         // have been folded, so that the tensor-memory loads overlap the f32 chains of the other set
-        const int quad = warp & 3, half = warp >> 2;
+        const int quad = warp & 3;
         const int row = 32 * quad + lane;
-        const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(64 * half);
-        const uint32_t dw_addr = a_ring + PF_TILE + 2u * (uint32_t)row, dx_addr = y_ring + (F8 ? 2 : 1) * PF_TOK * 32 + 32u * (uint32_t)half;
-        uint64_t acc[8][4];   // [token][pair]: accumulators 2 pair and 2 pair + 1 of the token, as one packed f32x2 value
-#pragma unroll
-        for (int t = 0; t < 8; ++t) {
-#pragma unroll
-            for (int n = 0; n < 4; ++n) { acc[t][n] = 0ull; }
-        }
+        const uint32_t dw_addr = a_ring + PF_TILE + 2u * (uint32_t)row;
         bool ok = true;
         if constexpr (F8) {
-            // ---- e4m3 operands: D is f32 and holds (float)lane_sum itself, so a lane sum costs half a packed FMA and the buffer is
-            // free for the next MMA as soon as it has been read
+            // ---- e4m3 operands: D is f32 and holds (float)lane_sum itself, so a lane sum costs half a packed FMA. Sixteen warps:
+            // warp = (row quadrant, quarter of the columns = tokens 4 part .. + 3), both halves of its 32 columns requested
+            // together, so the buffer is free for the next MMA as soon as they have arrived.
+            const int part = warp >> 2;
+            const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(32 * part);
+            const uint32_t dx_addr = y_ring + 2 * PF_TOK * 32 + 16u * (uint32_t)part;
+            uint64_t acc[4][4];   // [token][pair]: accumulators 2 pair and 2 pair + 1 of the token, as one packed f32x2 value
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+#pragma unroll
+                for (int n = 0; n < 4; ++n) { acc[t][n] = 0ull; }
+            }
             if (lane == 0) { for (int i = 0; i < PF_DBUF; ++i) { mbar_arrive(d_free(i)); } }
             uint32_t ra[16], rb[16];
-            auto fold2 = [&](const uint32_t *r, int t0, const uint64_t *sc) {   // two tokens: columns 8 t0 .. 8 t0 + 15
+            auto fold2 = [&](const uint32_t *r, int t0, float sa, float sb) {   // two tokens: columns 8 t0 .. 8 t0 + 15 of the warp's 32
+                const uint64_t sc[2] = {f2_pack(sa, sa), f2_pack(sb, sb)};
 #pragma unroll
                 for (int t = 0; t < 2; ++t) {
 #pragma unroll
-                    for (int n = 0; n < 4; ++n) { acc[t0 + t][n] = f2_fma(sc[t0 + t], f2_pack_bits(r[8 * t + 2 * n], r[8 * t + 2 * n + 1]), acc[t0 + t][n]); }
+                    for (int n = 0; n < 4; ++n) { acc[t0 + t][n] = f2_fma(sc[t], f2_pack_bits(r[8 * t + 2 * n], r[8 * t + 2 * n + 1]), acc[t0 + t][n]); }
                 }
             };
             ok = mbar_wait_bounded(d_full(0), 0u, limit);
@@ -208,36 +219,53 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
                 for (int j = 0; j < PF_BATCH; ++j) {
                     const int b = q * PF_BATCH + j;
                     if (b >= nb || !ok) { break; }
-                    const uint32_t taddr = tbase + (uint32_t)(j * PF_N);
                     const float dw = h2f((uint16_t)lds16(dw_q + (uint32_t)j * PF_WTILE));
-                    const float4 dxa = lds128f(dx_q + (uint32_t)j * YQ), dxb = lds128f(dx_q + (uint32_t)j * YQ + 16u);
-                    const float s0 = __fmul_rn(dw, dxa.x), s1 = __fmul_rn(dw, dxa.y), s2 = __fmul_rn(dw, dxa.z), s3 = __fmul_rn(dw, dxa.w);
-                    const float s4 = __fmul_rn(dw, dxb.x), s5 = __fmul_rn(dw, dxb.y), s6 = __fmul_rn(dw, dxb.z), s7 = __fmul_rn(dw, dxb.w);
-                    const uint64_t sc[8] = {f2_pack(s0, s0), f2_pack(s1, s1), f2_pack(s2, s2), f2_pack(s3, s3),
-                                            f2_pack(s4, s4), f2_pack(s5, s5), f2_pack(s6, s6), f2_pack(s7, s7)};
-                    tmem_ld_wait();                       // columns 0..31 of block b are in registers
-                    fold2(ra, 0, sc);
-                    tmem_ld16(taddr + 32u, ra);
-                    fold2(rb, 2, sc);
-                    tmem_ld16(taddr + 48u, rb);
-                    tmem_ld_wait();                       // columns 32..63 too: the buffer has been read
+                    const float4 dx = lds128f(dx_q + (uint32_t)j * YQ);
+                    tmem_ld_wait();                       // the warp's 32 columns of block b are in registers: the buffer has been read
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) { mbar_arrive(d_free(j)); }
-                    fold2(ra, 4, sc);
+                    fold2(ra, 0, __fmul_rn(dw, dx.x), __fmul_rn(dw, dx.y));
                     const bool more = b + 1 < nb;
                     const uint32_t tnext = tbase + (uint32_t)(((j + 1) % PF_DBUF) * PF_N);
-                    if (more) {                           // the next block's first columns arrive while the last two tokens are folded
+                    if (more) {                           // the next block's columns arrive while the last two tokens are folded
                         ok = mbar_wait_bounded(d_full((j + 1) % PF_DBUF), (uint32_t)(q + (j + 1) / PF_DBUF) & 1u, limit);
                         ok = __all_sync(0xffffffffu, ok);
                         if (ok) { tc_fence_after(); tmem_ld16(tnext, ra); }
                     }
-                    fold2(rb, 6, sc);
+                    fold2(rb, 2, __fmul_rn(dw, dx.z), __fmul_rn(dw, dx.w));
                     if (more && ok) { tmem_ld16(tnext + 16u, rb); }
                     if (lane == 0 && (j == PF_BATCH - 1 || b == nb - 1)) { mbar_arrive(st_free(q % NQ)); }   // the batch's scales have been read
                 }
             }
+            tmem_ld_wait();
+            if (!ok) { if (lane == 0) { pf_report(g.error_flag, 6); } }
+            else {
+#pragma unroll
+                for (int t = 0; t < 4; ++t) {   // hsum_float_8 (vec_util.h:74-81): column n < 4 is accumulator 4 + n (low nibbles); the tree is (c0 + c4) + (c2 + c6) and (c1 + c5) + (c3 + c7)
+                    const int token = tok_tile * PF_TOK + 4 * part + t;
+                    if (token < g.T && (int64_t)row_tile * PF_M + row < g.n_rows) {   // (the last row tile may be partly padding)
+                        float c[8];
+#pragma unroll
+                        for (int n = 0; n < 4; ++n) { f2_unpack(acc[t][n], c[2 * n], c[2 * n + 1]); }
+                        const float r0 = __fadd_rn(c[0], c[4]), r1 = __fadd_rn(c[1], c[5]);
+                        const float r2 = __fadd_rn(c[2], c[6]), r3 = __fadd_rn(c[3], c[7]);
+                        const float v = __fadd_rn(__fadd_rn(r0, r2), __fadd_rn(r1, r3));
+                        const int64_t i = (int64_t)token * g.out_stride + (int64_t)row_tile * PF_M + row;
+                        g.out[i] = g.resid != nullptr ? __fadd_rn(v, g.resid[i]) : v;
+                    }
+                }
+            }
         } else {
+            const int half = warp >> 2;
+            const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(64 * half);
+            const uint32_t dx_addr = y_ring + PF_TOK * 32 + 32u * (uint32_t)half;
+            uint64_t acc[8][4];   // [token][pair]: accumulators 2 pair and 2 pair + 1 of the token, as one packed f32x2 value
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+#pragma unroll
+                for (int n = 0; n < 4; ++n) { acc[t][n] = 0ull; }
+            }
             for (int i = 0; i < PF_DBUF; ++i) {   // the offset pattern into this thread's part of every buffer
                 tmem_st32_same(tbase + (uint32_t)(i * PF_N), MAGIC_I);
                 tmem_st32_same(tbase + (uint32_t)(i * PF_N) + 32u, MAGIC_I);
@@ -248,13 +276,13 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
             if (lane == 0) { for (int i = 0; i < PF_DBUF; ++i) { mbar_arrive(d_free(i)); } }
 
             uint32_t ra[16], rb[16], pattern[16];
-    #pragma unroll
+#pragma unroll
             for (int i = 0; i < 16; ++i) { asm volatile("mov.b32 %0, %1;" : "=r"(pattern[i]) : "r"(MAGIC_I)); }   // (opaque to the compiler: 16 live registers)
             const uint64_t minus_magic = f2_pack(-MAGIC_F, -MAGIC_F);
             auto fold2 = [&](const uint32_t *r, int t0, const uint64_t *sc) {   // two tokens: columns 8 t0 .. 8 t0 + 15
-    #pragma unroll
+#pragma unroll
                 for (int t = 0; t < 2; ++t) {
-    #pragma unroll
+#pragma unroll
                     for (int n = 0; n < 4; ++n) {   // acc = fma(scale, pattern - 1.5 * 2^23, acc) on two accumulators at a time
                         acc[t0 + t][n] = f2_fma(sc[t0 + t], f2_add(f2_pack_bits(r[8 * t + 2 * n], r[8 * t + 2 * n + 1]), minus_magic), acc[t0 + t][n]);
                     }
@@ -269,7 +297,7 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
             for (int q = 0; q < n_batch && ok; ++q) {
                 const uint32_t ring_q = (uint32_t)(q % NQ) * PF_BATCH;
                 const uint32_t dw_q = dw_addr + ring_q * PF_WTILE, dx_q = dx_addr + ring_q * YQ;
-    #pragma unroll
+#pragma unroll
                 for (int j = 0; j < PF_BATCH; ++j) {
                     const int b = q * PF_BATCH + j;
                     if (b >= nb || !ok) { break; }
@@ -306,24 +334,24 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
                     }
                 }
             }
-        }
-        tmem_ld_wait();
-        if (!ok) { if (lane == 0) { pf_report(g.error_flag, 6); } }
-        else {
-            // hsum_float_8 (vec_util.h:74-81): column n < 4 is accumulator 4 + n for Q4_0 (low nibbles) and accumulator n for Q8_0;
-            // either way the tree is (c0 + c4) + (c2 + c6) and (c1 + c5) + (c3 + c7)
+            tmem_ld_wait();
+            if (!ok) { if (lane == 0) { pf_report(g.error_flag, 6); } }
+            else {
+                // hsum_float_8 (vec_util.h:74-81): column n < 4 is accumulator 4 + n for Q4_0 (low nibbles) and accumulator n for Q8_0;
+                // either way the tree is (c0 + c4) + (c2 + c6) and (c1 + c5) + (c3 + c7)
 #pragma unroll
-            for (int t = 0; t < 8; ++t) {
-                const int token = tok_tile * PF_TOK + 8 * half + t;
-                if (token < g.T && (int64_t)row_tile * PF_M + row < g.n_rows) {   // (the last row tile may be partly padding)
-                    float c[8];
+                for (int t = 0; t < 8; ++t) {
+                    const int token = tok_tile * PF_TOK + 8 * half + t;
+                    if (token < g.T && (int64_t)row_tile * PF_M + row < g.n_rows) {   // (the last row tile may be partly padding)
+                        float c[8];
 #pragma unroll
-                    for (int n = 0; n < 4; ++n) { f2_unpack(acc[t][n], c[2 * n], c[2 * n + 1]); }
-                    const float r0 = __fadd_rn(c[0], c[4]), r1 = __fadd_rn(c[1], c[5]);
-                    const float r2 = __fadd_rn(c[2], c[6]), r3 = __fadd_rn(c[3], c[7]);
-                    const float v = __fadd_rn(__fadd_rn(r0, r2), __fadd_rn(r1, r3));
-                    const int64_t i = (int64_t)token * g.out_stride + (int64_t)row_tile * PF_M + row;
-                    g.out[i] = g.resid != nullptr ? __fadd_rn(v, g.resid[i]) : v;
+                        for (int n = 0; n < 4; ++n) { f2_unpack(acc[t][n], c[2 * n], c[2 * n + 1]); }
+                        const float r0 = __fadd_rn(c[0], c[4]), r1 = __fadd_rn(c[1], c[5]);
+                        const float r2 = __fadd_rn(c[2], c[6]), r3 = __fadd_rn(c[3], c[7]);
+                        const float v = __fadd_rn(__fadd_rn(r0, r2), __fadd_rn(r1, r3));
+                        const int64_t i = (int64_t)token * g.out_stride + (int64_t)row_tile * PF_M + row;
+                        g.out[i] = g.resid != nullptr ? __fadd_rn(v, g.resid[i]) : v;
+                    }
                 }
             }
         }

@@ -17,8 +17,9 @@ constexpr int PF_RING        = 4;                  // batches in the shared-memo
 constexpr int PF_STAGES      = PF_RING * PF_BATCH; // blocks in the rings
 constexpr int PF_MMA_WARPS   = 2;                  // warps whose first thread issues the MMAs of every PF_MMA_WARPS-th block
 constexpr int PF_THREADS     = (PF_EPI_WARPS + 2 + PF_MMA_WARPS) * 32;   // + the copy warp and the expander warp
-constexpr int PF_MMA_WARPS_F8 = 4;                 // the e4m3 form issues two MMAs per block: four issuing threads
-constexpr int PF_THREADS_F8  = (PF_EPI_WARPS + 2 + PF_MMA_WARPS_F8) * 32;
+constexpr int PF_EPI_WARPS_F8 = 16;                // the e4m3 form: (row quadrant) x (quarter of the columns); its epilogue needs under 96 registers
+constexpr int PF_MMA_WARPS_F8 = 2;                 // two MMAs and a commit per block hold the issuing thread ~240 cycles
+constexpr int PF_THREADS_F8  = (PF_EPI_WARPS_F8 + 2 + PF_MMA_WARPS_F8) * 32;
 constexpr int PF_DBUF        = 4;                  // accumulator buffers in tensor memory, PF_NCOL columns each (512 columns = all of it)
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
