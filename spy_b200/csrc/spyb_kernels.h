@@ -113,7 +113,8 @@ constexpr int PF_ROWS = 128, PF_TOK = 16;
 constexpr int PF_YQ_BYTES = PF_TOK * 32 + PF_TOK * 4;           // Q8_0 weights: 16 x 32 s8, 16 f32 scales
 constexpr int PF_YQ_BYTES_F8 = 2 * PF_TOK * 32 + PF_TOK * 4;    // Q4_0 weights: the activation bytes split into two e4m3 planes (16 x 32 each), 16 f32 scales
 constexpr int PF_KQ_TOK = 64;                                   // K-quant kernels: 64 tokens per tile, two columns of D per token
-constexpr int PF_KQ_YQ_BYTES = PF_KQ_TOK * 32 + PF_KQ_TOK * 8;   // 64 x 32 s8, 64 f32 scales, 64 f32 block sums
+constexpr int PF_KQ_YQ_BYTES = PF_KQ_TOK * 32 + PF_KQ_TOK * 8;   // Q6_K weights: 64 x 32 s8, 64 f32 scales, 64 f32 block sums
+constexpr int PF_KQ_YQ_BYTES_F8 = 2 * PF_KQ_TOK * 32 + PF_KQ_TOK * 8;   // Q4_K weights: two e4m3 planes of 64 x 32, scales, block sums
 constexpr int PF_KQ_WTILE = 128 * 32 + 128 * 8;                 // the s8 A operand of a 32-element block, then two f32 scale products per row
 constexpr int PF_MAX_K = 14336;   // widest activation row the quantizer kernel holds in registers
 struct PrefillGemm {

@@ -482,7 +482,20 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool bat
     const LaunchCfg cfg = be->launch_cfg(false);
     const int d = m->info.d_model, ff = m->info.n_ff, dl = m->dl, fl = m->fl, hd = m->info.head_dim;
     const int tp = m->info.tp_size, rank = m->info.tp_rank;
+    // the quantized activations are laid out for the type of the matrix they meet (s8 or e4m3 planes, tiles of 16 or 64 tokens):
+    // quant() makes them for the first matrix of a group, gemm() makes them again when a later matrix of the group wants another form
+    struct { const float *x; int part_len; const float *norm_w; int K; int64_t part_stride; int type; } yq_src = {};
+    auto layout_of = [](int type) { return type == SPYB_Q4_0 ? 2 : type == SPYB_Q4_K ? 3 : type == SPYB_Q6_K ? 1 : 0; };
+    auto quant = [&](const float *x, int part_len, int K, const float *norm_w, int type, int64_t part_stride) {
+        yq_src = {x, part_len, norm_w, K, part_stride, type};
+        return launch_prefill_quant(x, part_len, T, K, norm_w, norm_w != nullptr ? m->info.rms_eps : 0.f, m->pf_yq, s, type, part_len, part_stride);
+    };
     auto gemm = [&](const PfMat &W, int K, float *out, int64_t out_stride, const float *resid) {
+        if (layout_of(W.type) != layout_of(yq_src.type)) {
+            cudaError_t e = quant(yq_src.x, yq_src.part_len, yq_src.K, yq_src.norm_w, W.type, yq_src.part_stride);
+            if (e != cudaSuccess) { return e; }
+            ++*launches;
+        }
         PrefillGemm g;
         g.w = W.w; g.type = W.type; g.n_rows = W.n_rows; g.nb = K / 32; g.yq = m->pf_yq; g.T = T; g.out = out; g.out_stride = out_stride; g.resid = resid;
         g.error_flag = be->d_error_flag; g.wait_limit_ns = be->wait_limit_ns;
@@ -506,7 +519,7 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool bat
     float *att_part = m->pf_att + (size_t)rank * T * dl, *act_part = m->pf_act + (size_t)rank * T * fl;   // (tp == 1: the whole buffers)
     float *x_part = m->pf_x + (size_t)rank * T * dp;
     for (Layer &ly : m->layers) {
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, dp, T, d, ly.attn_norm, m->info.rms_eps, m->pf_yq, s, ly.pf_qkv.type, dp, (int64_t)T * dp));
+        SPYB_CUDA(be, quant(m->pf_x, dp, d, ly.attn_norm, ly.pf_qkv.type, (int64_t)T * dp));
         SPYB_CUDA(be, gemm(ly.pf_qkv, d, m->pf_qkv, 3 * (int64_t)dl, nullptr));
         if (m->kq) {   // one matrix per tensor: Wk and Wv fill the other two thirds of the QKV rows
             SPYB_CUDA(be, gemm(ly.pf_k, d, m->pf_qkv + dl, 3 * (int64_t)dl, nullptr));
@@ -531,15 +544,15 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool bat
             }
         }
         if (gather(m->pf_att, dl) != SPYB_SUCCESS) { return SPYB_FAIL; }
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_att, dl, T, d, nullptr, 0.f, m->pf_yq, s, ly.pf_wo.type, dl, (int64_t)T * dl));
+        SPYB_CUDA(be, quant(m->pf_att, dl, d, nullptr, ly.pf_wo.type, (int64_t)T * dl));
         SPYB_CUDA(be, gemm(ly.pf_wo, d, x_part, dp, x_part));
         if (gather(m->pf_x, dp) != SPYB_SUCCESS) { return SPYB_FAIL; }
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_x, dp, T, d, ly.ffn_norm, m->info.rms_eps, m->pf_yq, s, ly.pf_ug.type, dp, (int64_t)T * dp));
+        SPYB_CUDA(be, quant(m->pf_x, dp, d, ly.ffn_norm, ly.pf_ug.type, (int64_t)T * dp));
         SPYB_CUDA(be, gemm(ly.pf_ug, d, m->pf_ug, 2 * (int64_t)fl, nullptr));
         if (m->kq) { SPYB_CUDA(be, gemm(ly.pf_gate, d, m->pf_ug + fl, 2 * (int64_t)fl, nullptr)); ++*launches; }
         SPYB_CUDA(be, launch_prefill_silu_mul(m->pf_ug, T, fl, be->d_silu_table, act_part, s));
         if (gather(m->pf_act, fl) != SPYB_SUCCESS) { return SPYB_FAIL; }
-        SPYB_CUDA(be, launch_prefill_quant(m->pf_act, fl, T, ff, nullptr, 0.f, m->pf_yq, s, ly.pf_down.type, fl, (int64_t)T * fl));
+        SPYB_CUDA(be, quant(m->pf_act, fl, ff, nullptr, ly.pf_down.type, (int64_t)T * fl));
         SPYB_CUDA(be, gemm(ly.pf_down, ff, x_part, dp, x_part));
         if (gather(m->pf_x, dp) != SPYB_SUCCESS) { return SPYB_FAIL; }
         *launches += 7;

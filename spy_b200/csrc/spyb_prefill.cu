@@ -540,7 +540,8 @@ cudaError_t launch_gemm_t(const PrefillGemm &g, cudaStream_t stream) {
 
 size_t prefill_weight_bytes(int type, int64_t n_rows, int nb) { return (size_t)((n_rows + PF_ROWS - 1) / PF_ROWS) * nb * ((type == 12 || type == 14) ? PF_KQ_WTILE : PF_WTILE); }
 size_t prefill_act_bytes(int T, int nb) {   // (the largest of the layouts)
-    return std::max((size_t)((T + PF_TOK - 1) / PF_TOK) * nb * std::max(PF_YQ_BYTES, PF_YQ_BYTES_F8), (size_t)((T + PF_KQ_TOK - 1) / PF_KQ_TOK) * nb * PF_KQ_YQ_BYTES);
+    return std::max((size_t)((T + PF_TOK - 1) / PF_TOK) * nb * std::max(PF_YQ_BYTES, PF_YQ_BYTES_F8),
+                    (size_t)((T + PF_KQ_TOK - 1) / PF_KQ_TOK) * nb * std::max(PF_KQ_YQ_BYTES, PF_KQ_YQ_BYTES_F8));
 }
 
 cudaError_t launch_prefill_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0, cudaStream_t stream) {
@@ -561,7 +562,10 @@ cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K,
     if ((part_len & 3) || (part_stride & 3) || K % part_len != 0) { return cudaErrorInvalidValue; }
     if (T < 1 || K < 32 || (K & 31) || K > PF_MAX_K || (x_stride & 3) || ((uintptr_t)x & 15)) { return cudaErrorInvalidValue; }
     const size_t smem = norm_w != nullptr ? (size_t)K : 0;   // K / 4 floats
-    if (kq_layout) {
+    if (weight_type == 12) {
+        if (norm_w != nullptr) { prefill_quant_kernel<true, PF_KQ_TOK, true, true><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq, part_len, part_stride); }
+        else                   { prefill_quant_kernel<false, PF_KQ_TOK, true, true><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq, part_len, part_stride); }
+    } else if (kq_layout) {
         if (norm_w != nullptr) { prefill_quant_kernel<true, PF_KQ_TOK, true, false><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq, part_len, part_stride); }
         else                   { prefill_quant_kernel<false, PF_KQ_TOK, true, false><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq, part_len, part_stride); }
     } else if (weight_type == 2) {

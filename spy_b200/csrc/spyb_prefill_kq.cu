@@ -9,8 +9,8 @@
 //   Q6_K:  acc = 0; for the 16 groups g of 16 values:    acc = fma((d * sc_g) * dx_(g/2), (float)sum(q * y), acc)
 // the row's result being the super-blocks' values added in order.
 //
-// One MMA per 32-element block for a tile of 128 rows x 64 tokens: A = the block's integer weights as s8 (Q4_K: 0..15,
-// Q6_K: -32..31), B = 128 x 32 s8 whose rows 2 t and 2 t + 1 hold the first and the second 16 activation bytes of token t
+// One MMA (Q6_K, s8 operands) or two (Q4_K, e4m3 operands: see KqGeom) per 32-element block for a tile of 128 rows x 64 tokens:
+// A = the block's integer weights (Q4_K: 0..15, Q6_K: -32..31), B = 128 x 32 s8 whose rows 2 t and 2 t + 1 hold the first and the second 16 activation bytes of token t
 // at their place and zeros elsewhere (the kernel orders the columns 4 (t / 2) + 2 h + t % 2), D[r][column of (t, h)] = the integer sum of half h of the block. Q6_K folds the two halves one
 // after the other with their own scales (they are two of its groups); Q4_K adds them first (exact: both are small integers).
 // The weight tile carries, per row, the two f32 products the restatement forms first (Q4_K: d * sc_j and dmin * m_j;
@@ -23,9 +23,19 @@ namespace spyb {
 
 namespace {
 
-constexpr int KQ_TOK = PF_KQ_TOK, KQ_YQ = PF_KQ_YQ_BYTES, KQ_WT = PF_KQ_WTILE;
+constexpr int KQ_TOK = PF_KQ_TOK, KQ_WT = PF_KQ_WTILE;
 static_assert(2 * KQ_TOK == PF_NCOL, "64 tokens x 2 halves fill the MMA's columns");
-constexpr size_t KQ_SMEM_BYTES = (size_t)PF_STAGES * (KQ_WT + KQ_YQ + PF_TILE) + 8 * (3 * PF_RING + 2 * PF_DBUF) + 16;
+// Q4_K takes the e4m3 form of spyb_prefill.cu (its values 0..15 are exact in e4m3; the activation bytes as two e4m3 planes, two
+// MMAs per block, f32 accumulators that hold (float)sum itself: no offset pattern, no subtraction); its larger activation
+// records and B operands leave room for rings of three batches. Q6_K (-32..31 does not fit e4m3) keeps the s8 form.
+template <int WT> struct KqGeom {
+    static constexpr bool F8 = WT == 12;
+    static constexpr int  YQ = F8 ? PF_KQ_YQ_BYTES_F8 : PF_KQ_YQ_BYTES;
+    static constexpr int  BT = F8 ? 2 * PF_TILE : PF_TILE;
+    static constexpr int  NQ = F8 ? 3 : PF_RING;            // batches in the rings
+    static constexpr int  NS = NQ * PF_BATCH;               // blocks in the rings
+    static constexpr size_t SMEM = (size_t)NS * (KQ_WT + YQ + BT) + 8 * (3 * NQ + 2 * PF_DBUF) + 16;
+};
 
 __device__ __forceinline__ float2 lds64f(uint32_t addr) {
     float2 v;
@@ -47,6 +57,7 @@ __device__ __forceinline__ void lds128_2x64(uint32_t addr, uint64_t &a, uint64_t
 // dx_s = the warp's 32 activation scales of the block in shared memory (the 32 block sums lie KQ_TOK * 4 bytes further)
 template <int WT, int T0>
 __device__ __forceinline__ void kq_fold8(uint64_t (&acc)[16], const uint32_t (&r)[16], uint64_t scx, uint64_t scy, uint32_t dx_s, uint64_t minus_magic) {
+    constexpr bool F8 = KqGeom<WT>::F8;   // the columns already hold floats
     uint64_t dx[4];
     if (WT == 14) {
         lds128_2x64(dx_s + 4u * T0, dx[0], dx[1]);
@@ -54,7 +65,8 @@ __device__ __forceinline__ void kq_fold8(uint64_t (&acc)[16], const uint32_t (&r
     }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-        const uint64_t p0 = f2_add(f2_pack_bits(r[4 * u], r[4 * u + 1]), minus_magic), p1 = f2_add(f2_pack_bits(r[4 * u + 2], r[4 * u + 3]), minus_magic);
+        const uint64_t b0 = f2_pack_bits(r[4 * u], r[4 * u + 1]), b1 = f2_pack_bits(r[4 * u + 2], r[4 * u + 3]);
+        const uint64_t p0 = F8 ? b0 : f2_add(b0, minus_magic), p1 = F8 ? b1 : f2_add(b1, minus_magic);
         uint64_t a = acc[T0 / 2 + u];
         if (WT == 12) { dx[u] = lds64u(dx_s + 4u * T0 + 8u * u); }   // (Q4_K also reads the block sums: fewer values live at a time)
         if (WT == 14) {
@@ -72,17 +84,18 @@ __device__ __forceinline__ void kq_fold8(uint64_t (&acc)[16], const uint32_t (&r
 // of the tile), warp 8 copies, warp 9 expands the activations, warps 10-11 issue the MMAs - as in prefill_gemm_kernel.
 template <int WT>   // 12 = Q4_K, 14 = Q6_K
 __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillGemm g) {
-    constexpr int NS = PF_STAGES, NQ = PF_RING;
+    constexpr bool F8 = KqGeom<WT>::F8;
+    constexpr int NS = KqGeom<WT>::NS, NQ = KqGeom<WT>::NQ, KQ_YQ = KqGeom<WT>::YQ, BT = KqGeom<WT>::BT;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
     const uint32_t a_ring = sbase, y_ring = a_ring + NS * KQ_WT, b_ring = y_ring + NS * KQ_YQ;
-    const uint32_t bars  = b_ring + NS * PF_TILE;
+    const uint32_t bars  = b_ring + NS * BT;
     auto raw_full = [&](int q) { return bars + 8u * q; };
     auto ops_full = [&](int q) { return bars + 8u * (NQ + q); };
     auto st_free  = [&](int q) { return bars + 8u * (2 * NQ + q); };
     auto d_full   = [&](int i) { return bars + 8u * (3 * NQ + i); };
     auto d_free   = [&](int i) { return bars + 8u * (3 * NQ + PF_DBUF + i); };
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (size_t)NS * (KQ_WT + KQ_YQ + PF_TILE) + 8 * (3 * NQ + 2 * PF_DBUF));
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (size_t)NS * (KQ_WT + KQ_YQ + BT) + 8 * (3 * NQ + 2 * PF_DBUF));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nb = g.nb, n_batch = (nb + PF_BATCH - 1) / PF_BATCH;
@@ -96,7 +109,7 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillG
         for (int i = 0; i < PF_DBUF; ++i) { mbar_init(d_full(i), 1); mbar_init(d_free(i), PF_EPI_WARPS); }
         mbar_init_fence();
     }
-    for (int i = tid; i < NS * (PF_TILE / 16); i += PF_THREADS) { sts128(b_ring + (uint32_t)i * 16u, make_uint4(0u, 0u, 0u, 0u)); }
+    for (int i = tid; i < NS * (BT / 16); i += PF_THREADS) { sts128(b_ring + (uint32_t)i * 16u, make_uint4(0u, 0u, 0u, 0u)); }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(PF_DBUF * PF_NCOL) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -116,7 +129,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillG
                 if (!mbar_wait_relaxed(ops_full(q % NQ), (uint32_t)(q / NQ) & 1u, limit)) { pf_report(g.error_flag, 5); break; }
                 if (!mbar_wait_relaxed(d_free(buf), (uint32_t)(b / PF_DBUF) & 1u, limit)) { pf_report(g.error_flag, 5); break; }
                 tc_fence_after();
-                mma_s8_ss(tmem + (uint32_t)(buf * PF_NCOL), operand_desc(a_ring + (uint32_t)s * KQ_WT), operand_desc(b_ring + (uint32_t)s * PF_TILE));
+                if (F8) {
+                    const uint64_t a_desc = operand_desc(a_ring + (uint32_t)s * KQ_WT);
+                    mma_f8_ss(tmem + (uint32_t)(buf * PF_NCOL), a_desc, operand_desc(b_ring + (uint32_t)s * BT), 0u);
+                    mma_f8_ss(tmem + (uint32_t)(buf * PF_NCOL), a_desc, operand_desc(b_ring + (uint32_t)s * BT + PF_TILE), 1u);
+                } else {
+                    mma_s8_ss(tmem + (uint32_t)(buf * PF_NCOL), operand_desc(a_ring + (uint32_t)s * KQ_WT), operand_desc(b_ring + (uint32_t)s * BT));
+                }
                 mma_commit(d_full(buf));
                 last = b;
             }
@@ -147,14 +166,17 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillG
             if (!ok) { if (lane == 0) { pf_report(g.error_flag, 4); } break; }
             const int b0 = q * PF_BATCH, n = min(PF_BATCH, nb - b0), s0 = b0 % NS;
             for (int j = 0; j < n; ++j) {
-                const uint32_t ysrc_s = y_ring + (uint32_t)(s0 + j) * KQ_YQ, bdst = b_ring + (uint32_t)(s0 + j) * PF_TILE;
-                uint32_t v[KQ_TOK * 8 / 32];
+                const uint32_t ysrc_s = y_ring + (uint32_t)(s0 + j) * KQ_YQ, bdst = b_ring + (uint32_t)(s0 + j) * BT;
 #pragma unroll
-                for (int k = 0; k < KQ_TOK * 8 / 32; ++k) { v[k] = lds32(ysrc_s + (uint32_t)(lane + 32 * k) * 4u); }   // all loads in flight before the first store
+                for (int plane = 0; plane < (F8 ? 2 : 1); ++plane) {   // (e4m3 form: the second plane of words goes to the second B operand)
+                    uint32_t v[KQ_TOK * 8 / 32];
 #pragma unroll
-                for (int k = 0; k < KQ_TOK * 8 / 32; ++k) {
-                    const int i = lane + 32 * k, tt = i >> 3, w = i & 7, row = 4 * (tt >> 1) + 2 * (w >> 2) + (tt & 1);
-                    sts32(bdst + (uint32_t)(row >> 3) * 256u + (uint32_t)(w >> 2) * 128u + (uint32_t)(row & 7) * 16u + (uint32_t)(w & 3) * 4u, v[k]);
+                    for (int k = 0; k < KQ_TOK * 8 / 32; ++k) { v[k] = lds32(ysrc_s + (uint32_t)(plane * KQ_TOK * 8 + lane + 32 * k) * 4u); }   // all loads in flight before the first store
+#pragma unroll
+                    for (int k = 0; k < KQ_TOK * 8 / 32; ++k) {
+                        const int i = lane + 32 * k, tt = i >> 3, w = i & 7, row = 4 * (tt >> 1) + 2 * (w >> 2) + (tt & 1);
+                        sts32(bdst + (uint32_t)plane * PF_TILE + (uint32_t)(row >> 3) * 256u + (uint32_t)(w >> 2) * 128u + (uint32_t)(row & 7) * 16u + (uint32_t)(w & 3) * 4u, v[k]);
+                    }
                 }
             }
             fence_async_smem();
@@ -167,17 +189,19 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillG
         const int row = 32 * quad + lane;
         const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(64 * half);
         const uint32_t sc_addr = a_ring + PF_TILE + 8u * (uint32_t)row;
-        const uint32_t dx_addr = y_ring + KQ_TOK * 32 + 128u * (uint32_t)half;        // this warp's 32 scales; the block sums lie KQ_TOK * 4 further
+        const uint32_t dx_addr = y_ring + (F8 ? 2 : 1) * KQ_TOK * 32 + 128u * (uint32_t)half;   // this warp's 32 scales; the block sums lie KQ_TOK * 4 further
         uint64_t acc[16], tot[16];   // packed pairs: tokens 2 u and 2 u + 1 of the warp's 32
 #pragma unroll
         for (int t = 0; t < 16; ++t) { acc[t] = 0ull; tot[t] = 0ull; }
         const uint64_t minus_magic = f2_pack(-MAGIC_F, -MAGIC_F);
-        for (int i = 0; i < PF_DBUF; ++i) {
-            tmem_st32_same(tbase + (uint32_t)(i * PF_NCOL), MAGIC_I);
-            tmem_st32_same(tbase + (uint32_t)(i * PF_NCOL) + 32u, MAGIC_I);
+        if (!F8) {   // the offset pattern into this thread's part of every buffer
+            for (int i = 0; i < PF_DBUF; ++i) {
+                tmem_st32_same(tbase + (uint32_t)(i * PF_NCOL), MAGIC_I);
+                tmem_st32_same(tbase + (uint32_t)(i * PF_NCOL) + 32u, MAGIC_I);
+            }
+            tmem_st_wait();
+            tc_fence_before();
         }
-        tmem_st_wait();
-        tc_fence_before();
         __syncwarp();
         if (lane == 0) { for (int i = 0; i < PF_DBUF; ++i) { mbar_arrive(d_free(i)); } }
 
@@ -202,9 +226,15 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillG
                 tmem_ld16(taddr + 32u, ra);
                 kq_fold8<WT, 8>(acc, rb, scx, scy, dx_s, minus_magic);
                 tmem_ld16(taddr + 48u, rb);
-                tmem_ld_wait();                       // columns 32..63 too: the buffer has been read, put the offset pattern back
-                tmem_st32_same(taddr, MAGIC_I);
-                tmem_st32_same(taddr + 32u, MAGIC_I);
+                tmem_ld_wait();                       // columns 32..63 too: the buffer has been read
+                if (F8) {                             // free for the next MMA at once
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) { mbar_arrive(d_free(j)); }
+                } else {                              // put the offset pattern back
+                    tmem_st32_same(taddr, MAGIC_I);
+                    tmem_st32_same(taddr + 32u, MAGIC_I);
+                }
                 kq_fold8<WT, 16>(acc, ra, scx, scy, dx_s, minus_magic);
                 const bool more = b + 1 < nb;
                 const uint32_t tnext = tbase + (uint32_t)(((j + 1) % PF_DBUF) * PF_NCOL);
@@ -219,11 +249,13 @@ __global__ void __launch_bounds__(PF_THREADS, 1) prefill_kq_gemm_kernel(PrefillG
 #pragma unroll
                     for (int t = 0; t < 16; ++t) { tot[t] = f2_add(tot[t], acc[t]); acc[t] = 0ull; }
                 }
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
+                if (!F8) {
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                }
                 if (lane == 0) {
-                    mbar_arrive(d_free(j));
+                    if (!F8) { mbar_arrive(d_free(j)); }
                     if (j == PF_BATCH - 1 || b == nb - 1) { mbar_arrive(st_free(q % NQ)); }
                 }
             }
@@ -276,7 +308,7 @@ __global__ void prefill_kq_retile_kernel(const uint8_t *raw, int64_t row_stride,
         else { sc = (sc12[j + 4] & 0xFu) | ((sc12[j - 4] >> 6) << 4); mn = (uint32_t)(sc12[j + 4] >> 4) | ((uint32_t)(sc12[j] >> 6) << 4); }
         scales[0] = __fmul_rn(d, (float)sc);
         scales[1] = __fmul_rn(dmin, (float)mn);
-        for (int l = 0; l < 32; ++l) { *tile_elem(tile, r, l) = (int8_t)((j & 1) ? (qs[l] >> 4) : (qs[l] & 0xF)); }
+        for (int l = 0; l < 32; ++l) { *tile_elem(tile, r, l) = (int8_t)e4m3_of_small((uint32_t)((j & 1) ? (qs[l] >> 4) : (qs[l] & 0xF))); }   // (the e4m3 code of 0..15)
     } else {
         const uint8_t *s = raw + lrow * row_stride + (int64_t)sb * 210;
         const uint8_t *ql = s, *qh = s + 128;
@@ -295,6 +327,7 @@ __global__ void prefill_kq_retile_kernel(const uint8_t *raw, int64_t row_stride,
 
 template <int WT>
 cudaError_t launch_kq_t(const PrefillGemm &g, cudaStream_t stream) {
+    constexpr size_t KQ_SMEM_BYTES = KqGeom<WT>::SMEM;
     cudaError_t err = allow_dynamic_smem(reinterpret_cast<const void *>(prefill_kq_gemm_kernel<WT>), KQ_SMEM_BYTES);
     if (err != cudaSuccess) { return err; }
     const dim3 grid((unsigned)((g.T + KQ_TOK - 1) / KQ_TOK), (unsigned)((g.n_rows + PF_M - 1) / PF_M));
