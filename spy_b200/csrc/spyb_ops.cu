@@ -514,6 +514,45 @@ __global__ void __launch_bounds__(ATT_PV_WARPS * WARP) attn_pv_tiled_kernel(cons
         for (int ee = 0; ee < ATT_EE; ++ee) { acc[tt][ee] = 0.f; }
     }
     int j0 = 0;
+    if (nt == ATT_TT) {
+        // positions every token of the tile sees, in chunks of four 32-position steps: no masks to test, and the V^T values of
+        // the next chunk are requested before the products of this one, so that their latency hides behind 128 FMAs per thread
+        constexpr int CH = 4;
+        const int full_end = (min(n_main, vis0) / (32 * CH)) * (32 * CH);
+        __half vh[CH][ATT_EE];
+        if (full_end > 0) {
+#pragma unroll
+            for (int s = 0; s < CH; ++s) {
+#pragma unroll
+                for (int ee = 0; ee < ATT_EE; ++ee) { vh[s][ee] = vrow[(int64_t)ee * p.n_ctx + 32 * s + lane]; }
+            }
+        }
+        for (; j0 < full_end; j0 += 32 * CH) {
+            float v[CH][ATT_EE];
+#pragma unroll
+            for (int s = 0; s < CH; ++s) {
+#pragma unroll
+                for (int ee = 0; ee < ATT_EE; ++ee) { v[s][ee] = __half2float(vh[s][ee]); }
+            }
+            if (j0 + 32 * CH < full_end) {
+#pragma unroll
+                for (int s = 0; s < CH; ++s) {
+#pragma unroll
+                    for (int ee = 0; ee < ATT_EE; ++ee) { vh[s][ee] = vrow[(int64_t)ee * p.n_ctx + j0 + 32 * (CH + s) + lane]; }
+                }
+            }
+#pragma unroll
+            for (int tt = 0; tt < ATT_TT; ++tt) {
+                const float *pr = att_smem + (size_t)tt * n_pad + j0 + lane;
+#pragma unroll
+                for (int s = 0; s < CH; ++s) {
+                    const float pv = pr[32 * s];
+#pragma unroll
+                    for (int ee = 0; ee < ATT_EE; ++ee) { acc[tt][ee] = fmaf(v[s][ee], pv, acc[tt][ee]); }
+                }
+            }
+        }
+    }
     for (; j0 + 2 * 32 <= n_main && j0 + 2 * 32 <= vis_last; j0 += 2 * 32) {   // two steps' loads in flight per element
         float v[2][ATT_EE];
 #pragma unroll
@@ -536,7 +575,7 @@ __global__ void __launch_bounds__(ATT_PV_WARPS * WARP) attn_pv_tiled_kernel(cons
             }
         }
     }
-    for (; j0 < n_main; j0 += 32) {
+    for (; j0 < n_main && j0 < vis_last; j0 += 32) {   // (steps behind the tile's last visible position add nothing)
         const int j = j0 + lane;
         float v[ATT_EE];
 #pragma unroll
@@ -550,24 +589,37 @@ __global__ void __launch_bounds__(ATT_PV_WARPS * WARP) attn_pv_tiled_kernel(cons
             }
         }
     }
-    float vt[ATT_EE];
-#pragma unroll
-    for (int ee = 0; ee < ATT_EE; ++ee) { vt[ee] = (n_main + lane < vis_last) ? __half2float(vrow[(int64_t)ee * p.n_ctx + n_main + lane]) : 0.f; }
+    // The vector parts: reduce_f16dot_lanes leaves every lane with the sum; lane 4 tt + ee keeps that of (token tt, element ee).
+    static_assert(ATT_TT * ATT_EE == WARP, "one lane per (token, element) of the warp's outputs");
+    const int my_tt = lane >> 2, my_ee = lane & 3;
+    float vec = 0.f;
 #pragma unroll
     for (int tt = 0; tt < ATT_TT; ++tt) {
-        if (tt >= nt) { break; }
 #pragma unroll
         for (int ee = 0; ee < ATT_EE; ++ee) {
             const float a = reduce_f16dot_lanes(acc[tt][ee]);
-            float tail = 0.f;                         // positions n_main .. n_tot-1 (at most 32): scalar chain
-#pragma unroll 1
-            for (int i = 0; i < 32; ++i) {
-                const float v = __shfl_sync(0xffffffffu, vt[ee], i);
-                if (n_main + i < vis0 + tt) { tail = fmaf(v, att_smem[(size_t)tt * n_pad + n_main + i], tail); }
-            }
-            if (lane == 0) { p.out[(int64_t)(t0 + tt) * (p.out_stride ? p.out_stride : p.dl) + (int64_t)h * ATT_HD + e0 + ee] = __fadd_rn(tail, a); }
+            if (lane == tt * ATT_EE + ee) { vec = a; }
         }
     }
+    // The scalar tails (positions n_main .. n_tot - 1, at most 32, one FMA chain per output): each lane runs the chain of its own
+    // (token, element) instead of all lanes running all 32 chains; the V^T value of position n_main + i sits in lane i
+    float vt[ATT_EE];
+#pragma unroll
+    for (int ee = 0; ee < ATT_EE; ++ee) { vt[ee] = (n_main + lane < vis_last) ? __half2float(vrow[(int64_t)ee * p.n_ctx + n_main + lane]) : 0.f; }
+    float tail = 0.f;
+    const float *pr_mine = att_smem + (size_t)my_tt * n_pad + n_main;
+    const int n_tail = min(32, vis0 + my_tt - n_main);        // positions of the tail this lane's token sees (<= 0: none)
+#pragma unroll 4
+    for (int i = 0; i < 32; ++i) {
+        float v = 0.f;
+#pragma unroll
+        for (int ee = 0; ee < ATT_EE; ++ee) {
+            const float w = __shfl_sync(0xffffffffu, vt[ee], i);
+            if (my_ee == ee) { v = w; }
+        }
+        if (i < n_tail) { tail = fmaf(v, pr_mine[i], tail); }
+    }
+    if (my_tt < nt) { p.out[(int64_t)(t0 + my_tt) * (p.out_stride ? p.out_stride : p.dl) + (int64_t)h * ATT_HD + e0 + my_ee] = __fadd_rn(tail, vec); }
 }
 
 static cudaError_t launch_with_pdl(const void *kernel, dim3 grid, dim3 block, size_t smem, const AttnParams &p, const LaunchCfg &cfg) {
