@@ -147,6 +147,7 @@ cudaError_t launch_prefill_qkv_post(const float *qkv, int T, int dl, int hd, con
 cudaError_t launch_prefill_silu_mul(const float *upgate, int T, int F, const float *silu_table, float *act, cudaStream_t stream);
 
 struct AttnParams {
+    int           force_long = 0;     // take the three-kernel path (scratch needed) also at short contexts
     const __half *q = nullptr;        // [T][dl], already rounded to fp16
     const __half *k_cache = nullptr;  // [n_ctx][dl]
     const __half *v_cache = nullptr;  // [dl][n_ctx]

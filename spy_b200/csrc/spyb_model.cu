@@ -171,6 +171,7 @@ struct spyb_model {
     int             embd_type = 0;
     float2         *rope_table = nullptr;
     // activations for up to 8 tokens per pass
+    float  *pf_att_scratch = nullptr;   // score rows of a group of prompt tokens at contexts the single-kernel attention serves (the prompt path tiles tokens there too)
     float  *x = nullptr, *att = nullptr, *act = nullptr, *logits = nullptr, *scratch = nullptr, *att_scratch = nullptr;   // att [T][d_model] and act [T][n_ff] are the gathered vectors (inside tp_local)
     __half *q = nullptr;
     int    *d_pos = nullptr;
@@ -465,6 +466,13 @@ spyb_status ensure_prefill_buffers(spyb_model *m) {
               dev_alloc(m, &m->pf_yq, prefill_act_bytes((int)C, nb_max)) == SPYB_SUCCESS && dev_alloc(m, &m->pf_tokens, C) == SPYB_SUCCESS &&
               dev_alloc(m, &m->pf_pos, 2 * (C / TMAX + 1)) == SPYB_SUCCESS;   // (sized for the smallest group)
     if (!ok) { return SPYB_FAIL; }
+    // prompts share K rows and V^T rows among tiles of eight tokens at every context length (SPYB_PF_ATT_TILED=0: contexts up to
+    // 1024 positions keep one CTA per head and token, as single-token steps do)
+    const char *tiled_env = std::getenv("SPYB_PF_ATT_TILED");
+    if (m->att_scratch == nullptr && (tiled_env == nullptr || std::atoi(tiled_env) != 0)) {
+        const size_t n_pad = ((size_t)m->info.n_ctx + 3) & ~(size_t)3;
+        if (dev_alloc(m, &m->pf_att_scratch, (size_t)m->att_group * (dl / m->info.head_dim) * n_pad) != SPYB_SUCCESS) { return SPYB_FAIL; }
+    }
     if (cudaMallocHost(reinterpret_cast<void **>(&m->h_pf_tokens), C * 4) != cudaSuccess ||
         cudaMallocHost(reinterpret_cast<void **>(&m->h_pf_pos), 2 * (C / TMAX + 1) * 4) != cudaSuccess) { be->set_error("pinned host allocation failed"); return SPYB_FAIL; }
     m->pf_buffers = true;
@@ -532,11 +540,12 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool bat
         AttnParams a;
         a.k_cache = kc; a.v_cache = vc; a.out_stride = dl; a.exp_table = be->d_exp_table; a.seq_stride = batch ? m->seq_stride : 0;
         a.n_head = dl / hd; a.hd = hd; a.dl = dl; a.n_ctx = m->info.n_ctx; a.scale = 1.0f / std::sqrt((float)hd); a.error_flag = be->d_error_flag;
-        if (m->att_scratch == nullptr) {   // short contexts: one CTA per (head, token)
+        float *att_rows = m->att_scratch != nullptr ? m->att_scratch : (batch ? nullptr : m->pf_att_scratch);
+        if (att_rows == nullptr) {   // short contexts: one CTA per (head, token)
             a.q = m->pf_q; a.out = att_part; a.pos_base = m->d_pos; a.T = T;
             SPYB_CUDA(be, launch_attention(a, cfg)); ++*launches;
         } else {                           // long contexts: the chip-wide kernels on groups of tokens that fit the score scratch
-            a.scratch = m->att_scratch;
+            a.scratch = att_rows; a.force_long = 1;
             for (int t0 = 0; t0 < T; t0 += m->att_group) {
                 a.q = m->pf_q + (int64_t)t0 * dl; a.out = att_part + (int64_t)t0 * dl; a.pos_base = batch ? m->d_pos : m->pf_pos + 2 * (t0 / m->att_group); a.T = std::min(m->att_group, T - t0);
                 if (batch) { a.k_cache = kc + (int64_t)t0 * m->seq_stride; a.v_cache = vc + (int64_t)t0 * m->seq_stride; }

@@ -641,7 +641,7 @@ size_t attention_scratch_floats(int n_ctx, int n_head, int T) {   // 0: the sing
 cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
     if (p.hd != ATT_HD || p.T < 1 || p.n_ctx < 1 || (p.n_ctx & 3) || (p.dl & 7)) { return cudaErrorInvalidValue; }
     const size_t n_pad = ((size_t)p.n_ctx + 3) & ~(size_t)3;
-    if (p.n_ctx > ATT_LONG_MIN && p.scratch != nullptr) {
+    if ((p.n_ctx > ATT_LONG_MIN || p.force_long) && p.scratch != nullptr) {
         const bool tiled = p.T >= ATT_TT && p.tp.counter == nullptr && !cfg.pdl && p.seq_stride == 0;   // a prompt: tokens share the K rows and the V^T rows
         cudaError_t err = tiled
             ? launch_with_pdl(reinterpret_cast<const void *>(attn_scores_tiled_kernel), dim3((unsigned)((p.n_ctx + 255) / 256), p.n_head, (unsigned)((p.T + ATT_TT - 1) / ATT_TT)), dim3(256), 0, p, cfg)
