@@ -493,7 +493,7 @@ spyb_status run_prefill_layers(spyb_model *m, int T, int64_t *launches, bool bat
     // the quantized activations are laid out for the type of the matrix they meet (s8 or e4m3 planes, tiles of 16 or 64 tokens):
     // quant() makes them for the first matrix of a group, gemm() makes them again when a later matrix of the group wants another form
     struct { const float *x; int part_len; const float *norm_w; int K; int64_t part_stride; int type; } yq_src = {};
-    auto layout_of = [](int type) { return type == SPYB_Q4_0 ? 2 : type == SPYB_Q4_K ? 3 : type == SPYB_Q6_K ? 1 : 0; };
+    auto layout_of = [](int type) { return type == SPYB_Q4_K ? 3 : type == SPYB_Q6_K ? 1 : 2; };   // (Q4_0 and Q8_0 share one)
     auto quant = [&](const float *x, int part_len, int K, const float *norm_w, int type, int64_t part_stride) {
         yq_src = {x, part_len, norm_w, K, part_stride, type};
         return launch_prefill_quant(x, part_len, T, K, norm_w, norm_w != nullptr ? m->info.rms_eps : 0.f, m->pf_yq, s, type, part_len, part_stride);

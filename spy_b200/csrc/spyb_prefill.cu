@@ -34,7 +34,6 @@ namespace {
 
 constexpr int PF_N           = 8 * PF_TOK;         // 8 accumulator columns per token
 static_assert(PF_N == PF_NCOL, "16 tokens x 8 accumulators fill the MMA's columns");
-constexpr int PF_WTILE       = PF_TILE + 256;      // a weight tile in HBM: the A operand of 128 rows x 32 (s8 or e4m3), then 128 fp16 block scales
 constexpr int PF_QUANT_THREADS = 512;
 constexpr int PF_QUANT_GROUPS  = PF_MAX_K / (4 * PF_QUANT_THREADS);   // float4 groups per thread
 
@@ -57,19 +56,21 @@ constexpr int PF_QUANT_GROUPS  = PF_MAX_K / (4 * PF_QUANT_THREADS);   // float4 
 //   Y ring  [PF_STAGES][576 | 1088]    compact activations (16 tokens x 32 bytes, or two e4m3 planes of them; 16 f32 scales)
 //   B ring  [PF_STAGES][4096 | 8192]   expanded activations (one or two B operands), written by the expander warp
 template <int WT> struct PfGeom {
-    static constexpr bool F8      = WT == 2;                               // Q4_0: e4m3 operands, f32 accumulators, two MMAs per block
-    static constexpr int  YQ      = F8 ? PF_YQ_BYTES_F8 : PF_YQ_BYTES;     // a block's compact activations
-    static constexpr int  BT      = F8 ? 2 * PF_TILE : PF_TILE;            // a block's B operand(s)
-    static constexpr int  EPI_W   = F8 ? PF_EPI_WARPS_F8 : PF_EPI_WARPS;
-    static constexpr int  MMA_W   = F8 ? PF_MMA_WARPS_F8 : PF_MMA_WARPS;
-    static constexpr int  THREADS = F8 ? PF_THREADS_F8 : PF_THREADS;
-    static constexpr size_t SMEM  = (size_t)PF_STAGES * (PF_WTILE + YQ + BT) + 8 * (3 * PF_RING + 2 * PF_DBUF) + 16;
+    static constexpr int  NA      = WT == 8 ? 2 : 1;                       // A operands per block: Q8_0 weights are split like the activations
+    static constexpr int  WTILE   = NA * PF_TILE + 256;                    // a weight tile in HBM: the A operand(s) of 128 rows x 32 e4m3 codes, then 128 fp16 block scales
+    static constexpr int  YQ      = PF_YQ_BYTES_F8;                        // a block's compact activations
+    static constexpr int  BT      = 2 * PF_TILE;                           // a block's two B operands
+    static constexpr int  NQ      = WT == 8 ? 3 : PF_RING;                 // batches in the rings (what fits the shared memory)
+    static constexpr int  NS      = NQ * PF_BATCH;                         // blocks in the rings
+    static constexpr int  EPI_W   = PF_EPI_WARPS_F8;
+    static constexpr int  MMA_W   = PF_MMA_WARPS_F8;
+    static constexpr int  THREADS = PF_THREADS_F8;
+    static constexpr size_t SMEM  = (size_t)NS * (WTILE + YQ + BT) + 8 * (3 * NQ + 2 * PF_DBUF) + 16;
 };
 
 template <int WT>
 __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(PrefillGemm g) {
-    constexpr int NS = PF_STAGES, NQ = PF_RING;
-    constexpr bool F8 = PfGeom<WT>::F8;
+    constexpr int NS = PfGeom<WT>::NS, NQ = PfGeom<WT>::NQ, NA = PfGeom<WT>::NA, PF_WTILE = PfGeom<WT>::WTILE;
     constexpr int YQ = PfGeom<WT>::YQ, BT = PfGeom<WT>::BT, EPI_W = PfGeom<WT>::EPI_W, MMA_W = PfGeom<WT>::MMA_W, THREADS = PfGeom<WT>::THREADS;
     extern __shared__ __align__(128) uint8_t smem[];
     const uint32_t sbase = smem_u32(smem);
@@ -119,12 +120,14 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
                 if (!mbar_wait_relaxed(d_free(buf), (uint32_t)(b / PF_DBUF) & 1u, limit)) { pf_report(g.error_flag, 5); break; }
                 PF_STAMP(2, b, 2);
                 tc_fence_after();
-                if (F8) {   // the two e4m3 halves of the activation bytes, one after the other onto the same accumulators
-                    const uint64_t a_desc = operand_desc(a_ring + (uint32_t)s * PF_WTILE);
-                    mma_f8_ss(tmem + (uint32_t)(buf * PF_N), a_desc, operand_desc(b_ring + (uint32_t)s * BT), 0u);
-                    mma_f8_ss(tmem + (uint32_t)(buf * PF_N), a_desc, operand_desc(b_ring + (uint32_t)s * BT + PF_TILE), 1u);
-                } else {
-                    mma_s8_ss(tmem + (uint32_t)(buf * PF_N), operand_desc(a_ring + (uint32_t)s * PF_WTILE), operand_desc(b_ring + (uint32_t)s * BT));
+                // the e4m3 parts of the activation bytes (and of Q8_0 weights), one product after the other onto the same accumulators
+                const uint32_t d_tmem = tmem + (uint32_t)(buf * PF_N);
+                const uint64_t b_hi = operand_desc(b_ring + (uint32_t)s * BT), b_lo = operand_desc(b_ring + (uint32_t)s * BT + PF_TILE);
+#pragma unroll
+                for (int a = 0; a < NA; ++a) {
+                    const uint64_t a_desc = operand_desc(a_ring + (uint32_t)s * PF_WTILE + (uint32_t)a * PF_TILE);
+                    mma_f8_ss(d_tmem, a_desc, b_hi, a == 0 ? 0u : 1u);
+                    mma_f8_ss(d_tmem, a_desc, b_lo, 1u);
                 }
                 mma_commit(d_full(buf));
                 PF_STAMP(2, b, 3);
@@ -163,7 +166,7 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
             if (lane == 0) { PF_STAMP(1, b0, 0); }
             for (int j = 0; j < n; ++j) {
                 const uint32_t ysrc_s = y_ring + (uint32_t)(s0 + j) * YQ, bdst = b_ring + (uint32_t)(s0 + j) * BT;
-                constexpr int NW = (F8 ? 2 : 1) * PF_TOK * 8 / 32;   // words per lane (e4m3 form: the second plane of words goes to the second B operand)
+                constexpr int NW = 2 * PF_TOK * 8 / 32;   // words per lane (the second plane of words goes to the second B operand)
                 uint32_t v[NW];
 #pragma unroll
                 for (int k = 0; k < NW; ++k) { v[k] = lds32(ysrc_s + (uint32_t)(lane + 32 * k) * 4u); }   // all loads in flight before the first store
@@ -183,9 +186,9 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
         // have been folded, so that the tensor-memory loads overlap the f32 chains of the other set
         const int quad = warp & 3;
         const int row = 32 * quad + lane;
-        const uint32_t dw_addr = a_ring + PF_TILE + 2u * (uint32_t)row;
+        const uint32_t dw_addr = a_ring + NA * PF_TILE + 2u * (uint32_t)row;
         bool ok = true;
-        if constexpr (F8) {
+        {
             // ---- e4m3 operands: D is f32 and holds (float)lane_sum itself, so a lane sum costs half a packed FMA. Sixteen warps:
             // warp = (row quadrant, quarter of the columns = tokens 4 part .. + 3), both halves of its 32 columns requested
             // together, so the buffer is free for the next MMA as soon as they have arrived.
@@ -242,106 +245,8 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
             if (!ok) { if (lane == 0) { pf_report(g.error_flag, 6); } }
             else {
 #pragma unroll
-                for (int t = 0; t < 4; ++t) {   // hsum_float_8 (vec_util.h:74-81): column n < 4 is accumulator 4 + n (low nibbles); the tree is (c0 + c4) + (c2 + c6) and (c1 + c5) + (c3 + c7)
+                for (int t = 0; t < 4; ++t) {   // hsum_float_8 (vec_util.h:74-81): column n < 4 is accumulator 4 + n for Q4_0 (low nibbles) and accumulator n for Q8_0; either way the tree is (c0 + c4) + (c2 + c6) and (c1 + c5) + (c3 + c7)
                     const int token = tok_tile * PF_TOK + 4 * part + t;
-                    if (token < g.T && (int64_t)row_tile * PF_M + row < g.n_rows) {   // (the last row tile may be partly padding)
-                        float c[8];
-#pragma unroll
-                        for (int n = 0; n < 4; ++n) { f2_unpack(acc[t][n], c[2 * n], c[2 * n + 1]); }
-                        const float r0 = __fadd_rn(c[0], c[4]), r1 = __fadd_rn(c[1], c[5]);
-                        const float r2 = __fadd_rn(c[2], c[6]), r3 = __fadd_rn(c[3], c[7]);
-                        const float v = __fadd_rn(__fadd_rn(r0, r2), __fadd_rn(r1, r3));
-                        const int64_t i = (int64_t)token * g.out_stride + (int64_t)row_tile * PF_M + row;
-                        g.out[i] = g.resid != nullptr ? __fadd_rn(v, g.resid[i]) : v;
-                    }
-                }
-            }
-        } else {
-            const int half = warp >> 2;
-            const uint32_t tbase = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(64 * half);
-            const uint32_t dx_addr = y_ring + PF_TOK * 32 + 32u * (uint32_t)half;
-            uint64_t acc[8][4];   // [token][pair]: accumulators 2 pair and 2 pair + 1 of the token, as one packed f32x2 value
-#pragma unroll
-            for (int t = 0; t < 8; ++t) {
-#pragma unroll
-                for (int n = 0; n < 4; ++n) { acc[t][n] = 0ull; }
-            }
-            for (int i = 0; i < PF_DBUF; ++i) {   // the offset pattern into this thread's part of every buffer
-                tmem_st32_same(tbase + (uint32_t)(i * PF_N), MAGIC_I);
-                tmem_st32_same(tbase + (uint32_t)(i * PF_N) + 32u, MAGIC_I);
-            }
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) { for (int i = 0; i < PF_DBUF; ++i) { mbar_arrive(d_free(i)); } }
-
-            uint32_t ra[16], rb[16], pattern[16];
-#pragma unroll
-            for (int i = 0; i < 16; ++i) { asm volatile("mov.b32 %0, %1;" : "=r"(pattern[i]) : "r"(MAGIC_I)); }   // (opaque to the compiler: 16 live registers)
-            const uint64_t minus_magic = f2_pack(-MAGIC_F, -MAGIC_F);
-            auto fold2 = [&](const uint32_t *r, int t0, const uint64_t *sc) {   // two tokens: columns 8 t0 .. 8 t0 + 15
-#pragma unroll
-                for (int t = 0; t < 2; ++t) {
-#pragma unroll
-                    for (int n = 0; n < 4; ++n) {   // acc = fma(scale, pattern - 1.5 * 2^23, acc) on two accumulators at a time
-                        acc[t0 + t][n] = f2_fma(sc[t0 + t], f2_add(f2_pack_bits(r[8 * t + 2 * n], r[8 * t + 2 * n + 1]), minus_magic), acc[t0 + t][n]);
-                    }
-                }
-            };
-            ok = mbar_wait_bounded(d_full(0), 0u, limit);
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) { tc_fence_after(); tmem_ld16(tbase, ra); tmem_ld16(tbase + 16u, rb); }
-            // a batch per outer iteration: block j of a batch uses accumulator buffer j and stage 4 (q % PF_RING) + j, so that inside the
-            // unrolled body every address is a constant offset and every phase parity a bit of q
-            static_assert(PF_BATCH == PF_DBUF, "the unrolled epilogue pairs block j of a batch with accumulator buffer j");
-            for (int q = 0; q < n_batch && ok; ++q) {
-                const uint32_t ring_q = (uint32_t)(q % NQ) * PF_BATCH;
-                const uint32_t dw_q = dw_addr + ring_q * PF_WTILE, dx_q = dx_addr + ring_q * YQ;
-#pragma unroll
-                for (int j = 0; j < PF_BATCH; ++j) {
-                    const int b = q * PF_BATCH + j;
-                    if (b >= nb || !ok) { break; }
-                    const uint32_t taddr = tbase + (uint32_t)(j * PF_N);
-                    const float dw = h2f((uint16_t)lds16(dw_q + (uint32_t)j * PF_WTILE));
-                    const float4 dxa = lds128f(dx_q + (uint32_t)j * YQ), dxb = lds128f(dx_q + (uint32_t)j * YQ + 16u);
-                    const float s0 = __fmul_rn(dw, dxa.x), s1 = __fmul_rn(dw, dxa.y), s2 = __fmul_rn(dw, dxa.z), s3 = __fmul_rn(dw, dxa.w);
-                    const float s4 = __fmul_rn(dw, dxb.x), s5 = __fmul_rn(dw, dxb.y), s6 = __fmul_rn(dw, dxb.z), s7 = __fmul_rn(dw, dxb.w);
-                    const uint64_t sc[8] = {f2_pack(s0, s0), f2_pack(s1, s1), f2_pack(s2, s2), f2_pack(s3, s3),
-                                            f2_pack(s4, s4), f2_pack(s5, s5), f2_pack(s6, s6), f2_pack(s7, s7)};
-                    tmem_ld_wait();                       // columns 0..31 of block b are in registers
-                    fold2(ra, 0, sc);
-                    tmem_ld16(taddr + 32u, ra);
-                    fold2(rb, 2, sc);
-                    tmem_ld16(taddr + 48u, rb);
-                    tmem_ld_wait();                       // columns 32..63 too: the buffer has been read, put the offset pattern back
-                    tmem_st16(taddr, pattern); tmem_st16(taddr + 16u, pattern); tmem_st16(taddr + 32u, pattern); tmem_st16(taddr + 48u, pattern);
-                    fold2(ra, 4, sc);
-                    const bool more = b + 1 < nb;
-                    const uint32_t tnext = tbase + (uint32_t)(((j + 1) % PF_DBUF) * PF_N);
-                    if (more) {                           // the next block's first columns arrive while the last two tokens are folded
-                        ok = mbar_wait_bounded(d_full((j + 1) % PF_DBUF), (uint32_t)(q + (j + 1) / PF_DBUF) & 1u, limit);
-                        ok = __all_sync(0xffffffffu, ok);
-                        if (ok) { tc_fence_after(); tmem_ld16(tnext, ra); }
-                    }
-                    fold2(rb, 6, sc);
-                    if (more && ok) { tmem_ld16(tnext + 16u, rb); }
-                    tmem_st_wait();
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        mbar_arrive(d_free(j));
-                        if (j == PF_BATCH - 1 || b == nb - 1) { mbar_arrive(st_free(q % NQ)); }   // the batch's scales have been read
-                    }
-                }
-            }
-            tmem_ld_wait();
-            if (!ok) { if (lane == 0) { pf_report(g.error_flag, 6); } }
-            else {
-                // hsum_float_8 (vec_util.h:74-81): column n < 4 is accumulator 4 + n for Q4_0 (low nibbles) and accumulator n for Q8_0;
-                // either way the tree is (c0 + c4) + (c2 + c6) and (c1 + c5) + (c3 + c7)
-#pragma unroll
-                for (int t = 0; t < 8; ++t) {
-                    const int token = tok_tile * PF_TOK + 8 * half + t;
                     if (token < g.T && (int64_t)row_tile * PF_M + row < g.n_rows) {   // (the last row tile may be partly padding)
                         float c[8];
 #pragma unroll
@@ -469,8 +374,8 @@ __global__ void prefill_retile_kernel(const uint8_t *raw, int64_t row_stride, in
     const uint8_t *src = raw + lrow * row_stride + (int64_t)b * (WT == 2 ? 18 : 34);
     const int64_t row = dst_row0 + lrow;
     const int     r = (int)(row % PF_M);
-    uint8_t *tile = base + ((row / PF_M) * nb + b) * (int64_t)PF_WTILE;
-    reinterpret_cast<uint16_t *>(tile + PF_TILE)[r] = (uint16_t)(src[0] | (src[1] << 8));
+    uint8_t *tile = base + ((row / PF_M) * nb + b) * (int64_t)PfGeom<WT>::WTILE;
+    reinterpret_cast<uint16_t *>(tile + PfGeom<WT>::NA * PF_TILE)[r] = (uint16_t)(src[0] | (src[1] << 8));
     uint32_t *lo = reinterpret_cast<uint32_t *>(tile + (r >> 3) * 256 + (r & 7) * 16), *hi = lo + 32;   // elements 0..15 and 16..31
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -484,9 +389,11 @@ __global__ void prefill_retile_kernel(const uint8_t *raw, int64_t row_stride, in
             }
             lo[k] = l;
             hi[k] = h;
-        } else {
-            lo[k] = (uint32_t)(src[2 + 4 * k] | (src[3 + 4 * k] << 8) | (src[4 + 4 * k] << 16) | ((uint32_t)src[5 + 4 * k] << 24));
-            hi[k] = (uint32_t)(src[18 + 4 * k] | (src[19 + 4 * k] << 8) | (src[20 + 4 * k] << 16) | ((uint32_t)src[21 + 4 * k] << 24));
+        } else {   // Q8_0: every s8 weight as two e4m3 values, the multiple of 16 in the first operand tile and the rest in the second
+            const uint32_t w_lo = (uint32_t)(src[2 + 4 * k] | (src[3 + 4 * k] << 8) | (src[4 + 4 * k] << 16) | ((uint32_t)src[5 + 4 * k] << 24));
+            const uint32_t w_hi = (uint32_t)(src[18 + 4 * k] | (src[19 + 4 * k] << 8) | (src[20 + 4 * k] << 16) | ((uint32_t)src[21 + 4 * k] << 24));
+            e4m3_split4(w_lo, lo[k], lo[k + PF_TILE / 4]);
+            e4m3_split4(w_hi, hi[k], hi[k + PF_TILE / 4]);
         }
     }
 }
@@ -538,7 +445,10 @@ cudaError_t launch_gemm_t(const PrefillGemm &g, cudaStream_t stream) {
 
 }  // namespace
 
-size_t prefill_weight_bytes(int type, int64_t n_rows, int nb) { return (size_t)((n_rows + PF_ROWS - 1) / PF_ROWS) * nb * ((type == 12 || type == 14) ? PF_KQ_WTILE : PF_WTILE); }
+size_t prefill_weight_bytes(int type, int64_t n_rows, int nb) {
+    const size_t tile = (type == 12 || type == 14) ? (size_t)PF_KQ_WTILE : type == 8 ? (size_t)PfGeom<8>::WTILE : (size_t)PfGeom<2>::WTILE;
+    return (size_t)((n_rows + PF_ROWS - 1) / PF_ROWS) * nb * tile;
+}
 size_t prefill_act_bytes(int T, int nb) {   // (the largest of the layouts)
     return std::max((size_t)((T + PF_TOK - 1) / PF_TOK) * nb * std::max(PF_YQ_BYTES, PF_YQ_BYTES_F8),
                     (size_t)((T + PF_KQ_TOK - 1) / PF_KQ_TOK) * nb * std::max(PF_KQ_YQ_BYTES, PF_KQ_YQ_BYTES_F8));
@@ -568,12 +478,9 @@ cudaError_t launch_prefill_quant(const float *x, int64_t x_stride, int T, int K,
     } else if (kq_layout) {
         if (norm_w != nullptr) { prefill_quant_kernel<true, PF_KQ_TOK, true, false><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq, part_len, part_stride); }
         else                   { prefill_quant_kernel<false, PF_KQ_TOK, true, false><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq, part_len, part_stride); }
-    } else if (weight_type == 2) {
+    } else {   // Q4_0 and Q8_0 weights: tiles of 16 tokens, the two e4m3 planes
         if (norm_w != nullptr) { prefill_quant_kernel<true, PF_TOK, false, true><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq, part_len, part_stride); }
         else                   { prefill_quant_kernel<false, PF_TOK, false, true><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq, part_len, part_stride); }
-    } else {
-        if (norm_w != nullptr) { prefill_quant_kernel<true, PF_TOK, false, false><<<T, PF_QUANT_THREADS, smem, stream>>>(x, x_stride, K, norm_w, eps, yq, part_len, part_stride); }
-        else                   { prefill_quant_kernel<false, PF_TOK, false, false><<<T, PF_QUANT_THREADS, 0, stream>>>(x, x_stride, K, nullptr, 0.f, yq, part_len, part_stride); }
     }
     return cudaGetLastError();
 }
