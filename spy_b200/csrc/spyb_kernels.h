@@ -110,8 +110,8 @@ struct MatvecParams {
 // Prompt evaluation as a GEMM on the tcgen05 tensor cores (spyb_prefill.cu). Weights in tiles of PF_ROWS rows x 1 block,
 // activations as compact Q8_0 blocks grouped by (tile of PF_TOK tokens, block).
 constexpr int PF_ROWS = 128, PF_TOK = 16;
-constexpr int PF_YQ_BYTES = PF_TOK * 32 + PF_TOK * 4;           // Q8_0 weights: 16 x 32 s8, 16 f32 scales
-constexpr int PF_YQ_BYTES_F8 = 2 * PF_TOK * 32 + PF_TOK * 4;    // Q4_0 weights: the activation bytes split into two e4m3 planes (16 x 32 each), 16 f32 scales
+constexpr int PF_YQ_BYTES = PF_TOK * 32 + PF_TOK * 4;           // the s8 form (16 x 32 s8, 16 f32 scales; no Q4_0 / Q8_0 kernel uses it any more)
+constexpr int PF_YQ_BYTES_F8 = 2 * PF_TOK * 32 + PF_TOK * 4;    // Q4_0 / Q8_0 weights: the activation bytes split into two e4m3 planes (16 x 32 each), 16 f32 scales
 constexpr int PF_KQ_TOK = 64;                                   // K-quant kernels: 64 tokens per tile, two columns of D per token
 constexpr int PF_KQ_YQ_BYTES = PF_KQ_TOK * 32 + PF_KQ_TOK * 8;   // Q6_K weights: 64 x 32 s8, 64 f32 scales, 64 f32 block sums
 constexpr int PF_KQ_YQ_BYTES_F8 = 2 * PF_KQ_TOK * 32 + PF_KQ_TOK * 8;   // Q4_K weights: two e4m3 planes of 64 x 32, scales, block sums

@@ -12,14 +12,12 @@
 //                   at their place in the block and zeros elsewhere (block-diagonal per token)
 //   D (128 x 128, tensor memory) = A B^T: D[r][8 t + n] = lane sum n of (row r, token t) of this block
 //
-// in one of two forms, four D buffers in flight:
-//   Q8_0 weights: s8 operands, s32 accumulators (kind::i8). The buffers are preset with the s32 pattern of 1.5 * 2^23 and the
-//     MMA accumulates onto it, so that what the epilogue reads back is the bit pattern of the float 1.5 * 2^23 + lane_sum and
-//     one exact subtraction gives (float)lane_sum (|lane_sum| < 2^22); the epilogue writes the pattern back after reading.
-//   Q4_0 weights: e4m3 operands, f32 accumulators (kind::f8f6f4). nibble - 8 is exact in e4m3, and an activation byte y is
-//     the sum of two e4m3 values, y - (y mod 16) and y mod 16: two MMAs per block (accumulate = 0, then 1) onto the same
-//     buffer. Every product and the sum of a lane's four products are small integers, exact in f32, so D holds
-//     (float)lane_sum itself: no conversion, no preset, and the buffer is free for the next MMA as soon as it has been read.
+// with e4m3 operands and f32 accumulators (tcgen05.mma kind::f8f6f4), four D buffers in flight. Small integers are exact in
+// e4m3: a Q4_0 weight nibble - 8 directly; an 8-bit value y (an activation byte, a Q8_0 weight) as the sum of two e4m3 values,
+// y - (y mod 16) and y mod 16. So a block takes two MMAs (Q4_0) or four (Q8_0: weights split as well) onto the same buffer,
+// the first with accumulate = 0. Every product and every sum of a lane's four products are integers below 2^17, exact in
+// f32, so D holds (float)lane_sum itself: no conversion, no preset, and a buffer is free for the next MMA as soon as it has
+// been read. (The K-quant kernel of spyb_prefill_kq.cu keeps an s8 / s32 form for Q6_K, whose values do not fit.)
 // The epilogue warps read D back with tcgen05.ld (lane = row) and run the CPU's FMA chains in block order on f32 accumulators
 // held as packed f32x2 pairs. Operands reach shared memory by cp.async.bulk (weights in a 128-row x 1-block tile layout
 // made at upload, activations as compact blocks); an expander warp writes the activations into the canonical K-major
@@ -40,21 +38,19 @@ constexpr int PF_QUANT_GROUPS  = PF_MAX_K / (4 * PF_QUANT_THREADS);   // float4 
 // ---------------------------------------------------------------------------------------------
 // the GEMM. grid = (token tiles, row tiles); one CTA per SM (it takes all 512 tensor-memory columns).
 //
-// Q8_0 form (12 warps, 168 registers): warps 0-7 epilogue - row = 32 (warp % 4) + lane, tokens 8 (warp / 4) .. + 7 of the tile,
-//             read back 16 columns at a time into two alternating register sets
-// Q4_0 form (20 warps, 96 registers): warps 0-15 epilogue - row = 32 (warp % 4) + lane, tokens 4 (warp / 4) .. + 3; four warps
-//             per scheduler hide the latency of tensor memory behind one another's f32 chains
-// then        one warp whose first thread streams batches of PF_BATCH blocks with cp.async.bulk: two copies per batch (the
-//             weight tiles, which arrive as A operands, and the compact activations) - issuing a bulk copy costs its thread
-//             hundreds of cycles
-//             one warp that expands the compact activations of a batch into the B operands
-//             two warps whose first thread issues the MMAs of alternate blocks (MMA and commit hold the issuing thread for
-//             hundreds of cycles; threads of different warps issue in parallel)
+// 20 warps (96 registers):
+// warps 0-15  epilogue - row = 32 (warp % 4) + lane, tokens 4 (warp / 4) .. + 3 of the tile; four warps per scheduler hide the
+//             latency of tensor memory behind one another's f32 chains
+// warp 16     its first thread streams batches of PF_BATCH blocks with cp.async.bulk: two copies per batch (the weight tiles,
+//             which arrive as A operands, and the compact activations) - issuing a bulk copy costs its thread hundreds of cycles
+// warp 17     expands the compact activations of a batch into the B operands
+// warps 18-19 their first threads issue the MMAs of alternate blocks (MMAs and commit hold the issuing thread for hundreds
+//             of cycles; threads of different warps issue in parallel)
 //
-// Shared memory: rings of PF_STAGES blocks (PF_RING batches), one ring per kind so that a batch is one contiguous run:
-//   A ring  [PF_STAGES][4352]          weight tiles (A operand + 128 fp16 scales), written by cp.async.bulk
-//   Y ring  [PF_STAGES][576 | 1088]    compact activations (16 tokens x 32 bytes, or two e4m3 planes of them; 16 f32 scales)
-//   B ring  [PF_STAGES][4096 | 8192]   expanded activations (one or two B operands), written by the expander warp
+// Shared memory: rings of NS blocks (NQ batches), one ring per kind so that a batch is one contiguous run:
+//   A ring  [NS][4352 | 8448]   weight tiles (one or two A operands + 128 fp16 scales), written by cp.async.bulk
+//   Y ring  [NS][1088]          compact activations (two e4m3 planes of 16 tokens x 32 codes; 16 f32 scales)
+//   B ring  [NS][8192]          expanded activations (two B operands), written by the expander warp
 template <int WT> struct PfGeom {
     static constexpr int  NA      = WT == 8 ? 2 : 1;                       // A operands per block: Q8_0 weights are split like the activations
     static constexpr int  WTILE   = NA * PF_TILE + 256;                    // a weight tile in HBM: the A operand(s) of 128 rows x 32 e4m3 codes, then 128 fp16 block scales
@@ -108,7 +104,7 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
     const uint32_t tmem = *tmem_slot;
 
     if (warp >= EPI_W + 2) {
-        // ---- MMA warps: the first thread of warp m issues the 128 x 128 x 32 MMA of blocks m, m + PF_MMA_WARPS, ... onto a buffer
+        // ---- MMA warps: the first thread of warp m issues the 128 x 128 x 32 MMAs of blocks m, m + MMA_W, ... onto a buffer
         // that holds the offset pattern; MMAs into different buffers do not depend on one another
         if (lane == 0) {
             int last = -1;
