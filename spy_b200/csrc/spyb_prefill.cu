@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
     auto ops_full = [&](int q) { return bars + 8u * (NQ + q); };                 // the batch's B operands are written and fenced
     auto st_free  = [&](int q) { return bars + 8u * (2 * NQ + q); };             // the batch's stages may be refilled (one arrival per epilogue warp)
     auto d_full   = [&](int i) { return bars + 8u * (3 * NQ + i); };             // the MMA into buffer i has completed
-    auto d_free   = [&](int i) { return bars + 8u * (3 * NQ + PF_DBUF + i); };   // buffer i holds the offset pattern again (one arrival per epilogue warp)
+    auto d_free   = [&](int i) { return bars + 8u * (3 * NQ + PF_DBUF + i); };   // buffer i has been read (one arrival per epilogue warp)
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + (size_t)NS * (PF_WTILE + YQ + BT) + 8 * (3 * NQ + 2 * PF_DBUF));
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -105,7 +105,7 @@ __global__ void __launch_bounds__(PfGeom<WT>::THREADS, 1) prefill_gemm_kernel(Pr
 
     if (warp >= EPI_W + 2) {
         // ---- MMA warps: the first thread of warp m issues the 128 x 128 x 32 MMAs of blocks m, m + MMA_W, ... onto a buffer
-        // that holds the offset pattern; MMAs into different buffers do not depend on one another
+        // the epilogue has read; MMAs into different buffers do not depend on one another
         if (lane == 0) {
             int last = -1;
             for (int b = warp - (EPI_W + 2); b < nb; b += MMA_W) {
