@@ -95,8 +95,9 @@ void        spyb_destroy(spyb_backend *backend);
  * spy_assert/std::terminate error path (util/include/util/log/logger.h:96-150) */
 const char *spyb_last_error(const spyb_backend *backend);
 
-/* Host-only self-check of the library's book-keeping (per-device shared-memory limits of the kernels); needs no GPU.
- * 0 = passed. No reference counterpart. */
+/* Host-only self-check of the library's book-keeping (per-device shared-memory limits of the kernels) and of the e4m3 codes
+ * the prompt GEMM feeds the tensor cores (every code decodes to its integer, every 8-bit value is the sum of its two
+ * parts); needs no GPU. 0 = passed. No reference counterpart. */
 int32_t spyb_selftest_host(void);
 
 /* ---- Backend::get_max/avail_memory_capacity (backend.h:46-51) */

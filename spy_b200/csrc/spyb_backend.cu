@@ -161,7 +161,10 @@ using namespace spyb;
 
 extern "C" {
 
-int32_t spyb_selftest_host(void) { return smem_ledger_selftest(); }
+int32_t spyb_selftest_host(void) {
+    const int a = smem_ledger_selftest();
+    return a != 0 ? a : prefill_e4m3_selftest();
+}
 
 spyb_status spyb_create(const spyb_config *config, spyb_backend **out) {
     if (config == nullptr || out == nullptr) { return SPYB_FAIL; }

@@ -132,6 +132,7 @@ struct PrefillGemm {
     long long     *stamps = nullptr;  // profiling aid: clock stamps of CTA (0, 0), [8 roles][512 blocks][4]
     int            selftest_skip_batch = -1;   // failure-path check: the copy thread leaves this batch out, so the waits for it run out
 };
+int         prefill_e4m3_selftest();   // host-only: 0 when the e4m3 codes of the prompt GEMM decode to the integers they stand for
 size_t      prefill_weight_bytes(int type, int64_t n_rows, int nb);
 size_t      prefill_act_bytes(int T, int nb);
 cudaError_t launch_prefill_retile(int type, const uint8_t *raw, int64_t row_stride, int64_t n_rows, int nb, uint8_t *base, int64_t dst_row0, cudaStream_t stream);

@@ -441,6 +441,24 @@ cudaError_t launch_gemm_t(const PrefillGemm &g, cudaStream_t stream) {
 
 }  // namespace
 
+// host-only check of the e4m3 codes the exactness of the prompt GEMM rests on (no device needed): 0 when every code decodes
+// to the integer it stands for and every 8-bit value is the sum of its two parts
+int prefill_e4m3_selftest() {
+    auto decode = [](uint32_t c) {   // e4m3: sign, 4 exponent bits (bias 7), 3 mantissa bits; exponent 0 = subnormal
+        const int e = (int)((c >> 3) & 15u), m = (int)(c & 7u);
+        const double v = e == 0 ? m / 8.0 / 64.0 : (1.0 + m / 8.0) * (double)(1 << e) / 128.0;
+        return (c & 0x80u) ? -v : v;
+    };
+    for (int v = 0; v <= 15; ++v) { if (decode(e4m3_of_small((uint32_t)v)) != (double)v) { return 100 + v; } }
+    for (int v = -15; v <= 15; ++v) { if (decode(e4m3_of_signed(v)) != (double)v) { return 200 + v + 15; } }
+    for (int y = -128; y <= 127; ++y) {   // the split of e4m3_split4, one byte at a time
+        const int yl = y & 15, yh = (y - yl) >> 4;
+        const uint32_t ch = yh == 0 ? 0u : (e4m3_of_signed(yh) + 0x20u), cl = e4m3_of_small((uint32_t)yl);
+        if (decode(ch) != 16.0 * yh || decode(cl) != (double)yl || 16 * yh + yl != y || (ch & 0x7fu) > 0x7eu) { return 1000 + y + 128; }
+    }
+    return 0;
+}
+
 size_t prefill_weight_bytes(int type, int64_t n_rows, int nb) {
     const size_t tile = (type == 12 || type == 14) ? (size_t)PF_KQ_WTILE : type == 8 ? (size_t)PfGeom<8>::WTILE : (size_t)PfGeom<2>::WTILE;
     return (size_t)((n_rows + PF_ROWS - 1) / PF_ROWS) * nb * tile;
