@@ -163,6 +163,29 @@ def test_prefill_matmul_k_quants_match_the_restatement(be, oracle, qt, n, k, t, 
     assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
+@pytest.mark.parametrize("qt", [quants.Q4_0, quants.Q8_0])
+def test_prefill_matmul_extreme_bytes(be, oracle, qt):
+    """Weight blocks written byte by byte over the whole range (Q8_0: -128 and 127 included, Q4_0: nibbles 0 and 15) against
+    activations whose blocks quantize to +-127 and to zeros: the tensor-core operands split every 8-bit value into two e4m3
+    values, and every split must add up."""
+    rng = np.random.default_rng(77 + qt)
+    n, k, t = 136, 512, 21
+    nb = k // 32
+    bb = 18 if qt == quants.Q4_0 else 34
+    raw = rng.integers(0, 256, size=(n, nb, bb), dtype=np.uint8)
+    raw[:, :, 0:2] = rng.uniform(0.001, 0.05, size=(n, nb)).astype(np.float16).view(np.uint8).reshape(n, nb, 2)   # fp16 scales
+    raw[0, :, 2:] = 0x80 if qt == quants.Q8_0 else 0x00          # a row of -128 / of nibble 0 (value -8)
+    raw[1, :, 2:] = 0x7F if qt == quants.Q8_0 else 0xFF          # a row of 127 / of nibble 15 (value 7)
+    w = np.ascontiguousarray(raw.reshape(n, nb * bb))
+    x = rng.standard_normal((t, k)).astype(np.float32)
+    x[0] = np.where(rng.random(k) < 0.5, 1.0, -1.0)              # every byte +-127
+    x[1] = 0.0                                                   # every byte 0, scales 0
+    x[2, ::2] = 0.0
+    got = be.prefill_matmul(qt, w, n, k, x)
+    want = oracle.matmul(qt, w, k, n, x)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
 def test_prefill_matmul_full_size_rows_sample(be, oracle):
     """The 7B FFN-down shape with a 512-token prompt: a row and token sample against the oracle, bit for bit."""
     n, k, t = 4096, 11008, 512
