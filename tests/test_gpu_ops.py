@@ -227,7 +227,7 @@ def test_prefill_matmul_rejects_what_does_not_fit(be):
 @pytest.mark.parametrize("n,k", SHAPES)
 @pytest.mark.parametrize("t", [1, 4, 16])
 def test_matmul_operator_sweep(be, oracle, qt, n, k, t):
-    """BASELINE operator sweep: weights N(0, 0.02), activations N(0, 1); the oracle checks a row sample."""
+    """The operator sweep of the benchmark configurations: weights N(0, 0.02), activations N(0, 1); the oracle checks a row sample."""
     rng = np.random.default_rng(99)
     w = quants.quantize((rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)), qt)
     x = rng.standard_normal((t, k)).astype(np.float32)
