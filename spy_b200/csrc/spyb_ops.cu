@@ -391,6 +391,8 @@ __global__ void __launch_bounds__(ATT_SM_THREADS) attn_softmax_kernel(const Attn
     __shared__ float red[ATT_SM_THREADS / WARP];
     __shared__ float bcast;
     const int h = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nthr = blockDim.x;   // 1024 for single steps (one CTA per head: latency), 256 for prompts (many CTAs: more of them per SM, so that
+                                   // one CTA's serial sum overlaps the parallel phases of the others)
     pdl_launch_dependents();
     pdl_wait();
     const bool batch = p.seq_stride != 0;
@@ -401,7 +403,7 @@ __global__ void __launch_bounds__(ATT_SM_THREADS) attn_softmax_kernel(const Attn
     float *row = p.scratch + ((int64_t)t * p.n_head + h) * n_pad;
     // masked softmax: (score + mask) * scale, subtract the maximum, table exp, std::reduce, multiply by 1/sum
     float m = -CUDART_INF_F;
-    for (int j = tid; j < n_vis; j += ATT_SM_THREADS) {
+    for (int j = tid; j < n_vis; j += nthr) {
         const float v = __fmul_rn(__fadd_rn(row[j], 0.0f), p.scale);
         sc[j] = v;
         m = fmaxf(m, v);
@@ -411,11 +413,11 @@ __global__ void __launch_bounds__(ATT_SM_THREADS) attn_softmax_kernel(const Attn
     __syncthreads();
     m = red[0];
 #pragma unroll
-    for (int w = 1; w < ATT_SM_THREADS / WARP; ++w) { m = fmaxf(m, red[w]); }
+    for (int w = 1; w < ATT_SM_THREADS / WARP; ++w) { if (w < (nthr >> 5)) { m = fmaxf(m, red[w]); } }
     const int n_tot4 = (n_tot + 3) & ~3;
-    for (int j = tid; j < n_tot4; j += ATT_SM_THREADS) { sc[j] = (j < n_vis) ? p.exp_table[f2h(__fsub_rn(sc[j], m))] : 0.f; }
+    for (int j = tid; j < n_tot4; j += nthr) { sc[j] = (j < n_vis) ? p.exp_table[f2h(__fsub_rn(sc[j], m))] : 0.f; }
     __syncthreads();
-    for (int g = tid; g < (n_tot >> 2); g += ATT_SM_THREADS) {
+    for (int g = tid; g < (n_tot >> 2); g += nthr) {
         const float4 v = reinterpret_cast<const float4 *>(sc)[g];
         gs[g] = __fadd_rn(__fadd_rn(v.x, v.y), __fadd_rn(v.z, v.w));
     }
@@ -435,7 +437,7 @@ __global__ void __launch_bounds__(ATT_SM_THREADS) attn_softmax_kernel(const Attn
     __syncthreads();
     const float inv = bcast;
     // probabilities, rounded to fp16 as the PV MatMul does with its f32 operand
-    for (int j = tid; j < n_vis; j += ATT_SM_THREADS) { row[j] = __half2float(__float2half_rn(__fmul_rn(sc[j], inv))); }
+    for (int j = tid; j < n_vis; j += nthr) { row[j] = __half2float(__float2half_rn(__fmul_rn(sc[j], inv))); }
 }
 
 constexpr int ATT_PV_WARPS = 16;
@@ -651,7 +653,7 @@ cudaError_t launch_attention(const AttnParams &p, const LaunchCfg &cfg) {
         if (sm_smem > 200 * 1024) { return cudaErrorInvalidValue; }
         err = allow_dynamic_smem(reinterpret_cast<const void *>(attn_softmax_kernel), sm_smem);
         if (err != cudaSuccess) { return err; }
-        err = launch_with_pdl(reinterpret_cast<const void *>(attn_softmax_kernel), dim3(p.n_head, p.T), dim3(ATT_SM_THREADS), sm_smem, p, cfg);
+        err = launch_with_pdl(reinterpret_cast<const void *>(attn_softmax_kernel), dim3(p.n_head, p.T), dim3(tiled ? 256 : ATT_SM_THREADS), sm_smem, p, cfg);
         if (err != cudaSuccess) { return err; }
         if (tiled && (size_t)ATT_TT * n_pad * sizeof(float) + 16 <= 200 * 1024) {
             const size_t tsm = (size_t)ATT_TT * n_pad * sizeof(float) + 16;
