@@ -299,22 +299,33 @@ constexpr int ATT_LONG_MIN = 1024;
 // Dot<FP16,FP16>(K row, Q) with the K row in registers (16 x 8 fp16) and Q as 128 floats in shared memory: 4 x 8
 // accumulators over elements 0..95, the reduction tree, the scalar chain over elements 96..127, tail + simd
 __device__ __forceinline__ float score_dot(const uint4 (&kv)[16], const float4 *q4) {
-    float acc[4][8];
+    // the 4 x 8 accumulators as 4 x 4 packed f32x2 pairs (elements 2 p, 2 p + 1 of an accumulator step): one fma.rn.f32x2 is two
+    // of the scalar FMAs, bit for bit
+    uint64_t acc2[4][4];
 #pragma unroll
     for (int a = 0; a < 4; ++a) {
 #pragma unroll
-        for (int e = 0; e < 8; ++e) { acc[a][e] = 0.f; }
+        for (int e = 0; e < 4; ++e) { acc2[a][e] = 0ull; }
     }
 #pragma unroll
     for (int step = 0; step < 3; ++step) {       // elements 0..95: accumulator a takes elements 32 * step + 8a .. + 7
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
-            float kf[8]; unpack8(kv[4 * step + a], kf);
+            const uint4 kw = kv[4 * step + a];
+            const float2 k0 = __half22float2(*reinterpret_cast<const __half2 *>(&kw.x)), k1 = __half22float2(*reinterpret_cast<const __half2 *>(&kw.y));
+            const float2 k2 = __half22float2(*reinterpret_cast<const __half2 *>(&kw.z)), k3 = __half22float2(*reinterpret_cast<const __half2 *>(&kw.w));
             const float4 qa = q4[(4 * step + a) * 2], qb = q4[(4 * step + a) * 2 + 1];
-            const float  qv[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
-#pragma unroll
-            for (int e = 0; e < 8; ++e) { acc[a][e] = fmaf(kf[e], qv[e], acc[a][e]); }
+            acc2[a][0] = f2_fma(f2_pack(k0.x, k0.y), f2_pack(qa.x, qa.y), acc2[a][0]);
+            acc2[a][1] = f2_fma(f2_pack(k1.x, k1.y), f2_pack(qa.z, qa.w), acc2[a][1]);
+            acc2[a][2] = f2_fma(f2_pack(k2.x, k2.y), f2_pack(qb.x, qb.y), acc2[a][2]);
+            acc2[a][3] = f2_fma(f2_pack(k3.x, k3.y), f2_pack(qb.z, qb.w), acc2[a][3]);
         }
+    }
+    float acc[4][8];
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) { f2_unpack(acc2[a][e], acc[a][2 * e], acc[a][2 * e + 1]); }
     }
     float u[4];
 #pragma unroll
