@@ -208,6 +208,13 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
+def bf16_peak_tflops():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p)).get("bf16_tflops", 1590.0))
+    return 1590.0
+
+
 N_PARITY = 32   # generated tokens of the parity record: the 8-token prompt, then 32 greedy tokens
 
 
@@ -374,8 +381,14 @@ def main():
     t_pre = torch.tensor([model.last_ms], dtype=torch.float64)
     if dist is not None:
         dist.all_reduce(t_pre, op=dist.ReduceOp.MAX)
+    layer_weights = int(info.n_layer) * (4 * int(info.d_model) ** 2 + 3 * int(info.d_model) * int(info.n_ff))   # elements of the layers' matrices (all ranks together)
+    pre_tflops = 2.0 * layer_weights * n_pre / (float(t_pre[0]) / 1e3) / 1e12
     prefill = {"tokens": int(n_pre), "ms": float(t_pre[0]), "tokens_per_s": float(n_pre / (float(t_pre[0]) / 1e3)),
                "launches": int(model.last_launches),
+               "tflops": pre_tflops, "frac_of_bf16_peak": pre_tflops / (bf16_peak_tflops() * world),
+               "tflops_note": "algorithmic: 2 x layer weights x tokens / time, against the measured dense bf16 peak of the GPUs used; the tensor cores issue 8 x "
+                              "that (one MMA column per accumulator of a token: block-diagonal B operand), times 2 (Q4_0) or 4 (Q8_0) for the e4m3 split of "
+                              "8-bit values, and the f32 chains after them set the time",
                "note": "one spyb_model_eval over the prompt (device time, CUDA events): chunks of up to 512 tokens through the tcgen05 GEMM kernel when the "
                        "widths fit its tiles (sharded models: each rank its heads and FFN rows, one NCCL all-gather of the attention output and of the FFN activation per layer)"}
     barrier()
