@@ -123,10 +123,14 @@ void *spyb_upload_constant(spyb_backend *backend, const char *name, const void *
 spyb_status spyb_submit(spyb_backend *backend, spyb_op_desc *desc, void (*callback)(void *), void *user);
 /* waits for everything submitted so far */
 spyb_status spyb_sync(spyb_backend *backend);
+/* (Entry points that exist for measurement only - timed submits, single-kernel timing, kernel time stamps - are left out of a
+ * library built with -DSPYB_NO_MEASUREMENT_AIDS.) */
+#ifndef SPYB_NO_MEASUREMENT_AIDS
 /* measurement aid: submits descs[0], descs[1], ... round-robin `repeats` times (no callbacks; device-resident operands) between
  * two events on the backend's stream and returns the device time of the whole sequence in milliseconds. Passing several
  * descriptors whose operands together exceed the L2 cache gives cold-cache figures for a single operator. */
 spyb_status spyb_submit_timed(spyb_backend *backend, spyb_op_desc *descs, int32_t n_descs, int32_t repeats, float *ms_out);
+#endif
 
 /* ---- staging of IO tensors, which the reference keeps in host vectors (model/src/llm/model/llama.cpp:259-263) */
 spyb_status spyb_memcpy_h2d(spyb_backend *backend, void *dst_device, const void *src_host, uint64_t bytes);
@@ -281,6 +285,7 @@ spyb_status spyb_model_decode_batch(spyb_model *model, const int32_t *first_toke
  * measured with CUDA events on the backend's stream; number of kernels that call launched */
 float   spyb_model_last_ms(const spyb_model *model);
 int64_t spyb_model_last_launches(const spyb_model *model);
+#ifndef SPYB_NO_MEASUREMENT_AIDS
 /* Measurement aid: launches one kind of mat-vec kernel of the plan alone, `sweeps` times over every layer's
  * weights back to back (kind 0 = Wq|Wk|Wv, 1 = attention output, 2 = FFN up+gate, 3 = FFN down, 4 = output head),
  * and returns the average device time per launch in milliseconds (CUDA events on the backend's stream);
@@ -288,6 +293,7 @@ int64_t spyb_model_last_launches(const spyb_model *model);
  * the KV cache below position n_ctx-1 and the residual stream are left untouched. No reference counterpart
  * (the reference times whole steps only, util/include/util/timer.h:51-80). */
 float spyb_model_bench_kernel(spyb_model *model, int32_t kind, int32_t sweeps, uint64_t *bytes_per_launch);
+#endif
 /* Parity tap: copies one activation buffer of the last pass (up to 8 token columns) to the host:
  * which 0 = Q after RoPE as fp16 [T][d_local], 1 = attention output f32 [T][d_local], 2 = residual stream f32 [T][d_model],
  * 3 = up*silu(gate) f32 [T][ff_local], 4 = logits f32 [n_vocab]; the layer buffers hold the LAST layer's values.
@@ -297,6 +303,7 @@ spyb_status spyb_model_read_activation(spyb_model *model, int32_t which, void *h
  * (d_model/32 * 34 bytes, reference layout) to host */
 spyb_status spyb_model_tap_xq(spyb_model *model, void *blocks_host);
 
+#ifndef SPYB_NO_MEASUREMENT_AIDS
 /* Profiling aid without a reference counterpart. When the model was loaded with SPYB_TIMELINE=1 in the
  * environment, every kernel of the step plan records eight device-clock stamps (ns): CTA 0 started,
  * its predecessor finished, its activations quantized, last CTA finished, then the latest CTA's start,
@@ -308,6 +315,7 @@ int32_t spyb_model_read_timeline(spyb_model *model, uint64_t *stamps_host, int32
  * every check point of the step - kernel entry, then per layer: barrier passed / activations quantized / mat-vec done for
  * Wq|Wk|Wv, attention begun / done, and the same triples for Wo, up|gate and down, finally the head. Returns the number of pairs. */
 int32_t spyb_model_read_step_timeline(spyb_model *model, uint64_t *stamps_host, int32_t max_points);
+#endif
 
 #ifdef __cplusplus
 }

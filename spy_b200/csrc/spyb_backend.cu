@@ -821,6 +821,7 @@ spyb_status spyb_submit(spyb_backend *be, spyb_op_desc *d, void (*callback)(void
     return SPYB_SUCCESS;
 }
 
+#ifndef SPYB_NO_MEASUREMENT_AIDS
 spyb_status spyb_submit_timed(spyb_backend *be, spyb_op_desc *descs, int32_t n_descs, int32_t repeats, float *ms_out) {
     if (be == nullptr || descs == nullptr || n_descs < 1 || repeats < 1 || ms_out == nullptr) { return SPYB_FAIL; }
     cudaSetDevice(be->config.device_id);
@@ -839,5 +840,6 @@ spyb_status spyb_submit_timed(spyb_backend *be, spyb_op_desc *descs, int32_t n_d
     if (be->device_error()) { return SPYB_FAIL; }
     return SPYB_SUCCESS;
 }
+#endif
 
 }  // extern "C"

@@ -372,6 +372,7 @@ void set_weights(const spyb_model *m, const Layer *ly, int kind, MatvecParams &p
     default: p.A = m->head; break;
     }
 }
+#ifndef SPYB_NO_MEASUREMENT_AIDS
 uint64_t weights_bytes(const MatvecParams &p) {
     if (p.kq_n > 0) {
         uint64_t b = 0;
@@ -380,6 +381,7 @@ uint64_t weights_bytes(const MatvecParams &p) {
     }
     return p.A.bytes() + (p.pair_mode ? p.B.bytes() : 0);
 }
+#endif
 
 // the five fused kernels of every layer for T tokens whose first position is *d_pos.
 // Tensor parallel: Wq|Wk|Wv, attention and FFN up|gate work on this rank's heads / FFN columns; their outputs are
@@ -1157,6 +1159,7 @@ spyb_status spyb_model_decode(spyb_model *m, int32_t first_token, int32_t n_past
     return SPYB_SUCCESS;
 }
 
+#ifndef SPYB_NO_MEASUREMENT_AIDS
 float spyb_model_bench_kernel(spyb_model *m, int32_t kind, int32_t sweeps, uint64_t *bytes_per_launch) {
     if (m == nullptr || kind < 0 || kind > 4 || sweeps < 1) { return -1.f; }
     spyb_backend *be = m->be;
@@ -1211,6 +1214,7 @@ float spyb_model_bench_kernel(spyb_model *m, int32_t kind, int32_t sweeps, uint6
     }
     return n ? total_ms / (float)n : -1.f;
 }
+#endif
 
 spyb_status spyb_tp_layer_shard(int32_t d_model, int32_t n_head, int32_t n_ff, int32_t tp_size, int32_t tp_rank, int64_t out[4]) {
     if (out == nullptr || tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size || d_model <= 0 || n_head <= 0 || n_ff <= 0 || d_model % n_head != 0) { return SPYB_FAIL; }
@@ -1376,6 +1380,7 @@ spyb_status spyb_model_read_activation(spyb_model *m, int32_t which, void *host,
     return SPYB_SUCCESS;
 }
 
+#ifndef SPYB_NO_MEASUREMENT_AIDS
 int32_t spyb_model_read_timeline(spyb_model *m, uint64_t *stamps_host, int32_t max_kernels) {
     if (m == nullptr || m->d_stamps == nullptr || stamps_host == nullptr) { return 0; }
     const int n = std::min<int>(max_kernels, 5 * (int)m->layers.size() + 1);
@@ -1389,6 +1394,7 @@ int32_t spyb_model_read_step_timeline(spyb_model *m, uint64_t *stamps_host, int3
     if (cudaMemcpy(stamps_host, m->d_step_stamps, (size_t)n * 2 * sizeof(uint64_t), cudaMemcpyDeviceToHost) != cudaSuccess) { return 0; }
     return n;
 }
+#endif
 
 spyb_status spyb_model_tap_xq(spyb_model *m, void *blocks_host) {
     if (m == nullptr || blocks_host == nullptr) { return SPYB_FAIL; }
