@@ -202,3 +202,27 @@ def dequantize(raw: np.ndarray, number_type: int) -> np.ndarray:
     if number_type == FP16:
         return np.ascontiguousarray(raw).view(np.float16).astype(np.float32)
     return DEQUANTIZE[number_type](raw)
+
+
+# ---------------------------------------------------------------------------------------------
+# e4m3 codes of small integers, as the prompt GEMM feeds them to the tensor cores (spyb_prefill.cu: a Q4_0 weight nibble - 8
+# directly; an 8-bit value y as the two codes of y - y mod 16 and y mod 16). Kept here for tools that want to read or build
+# the kernel's operand tiles on the host, and checked against an independent e4m3 decoder in the tests.
+def e4m3_of_small(v: int) -> int:
+    """Code of the integer 0 <= v <= 15 (exact: three mantissa bits cover 8..15)."""
+    if v == 0:
+        return 0
+    e = v.bit_length() - 1
+    return ((e + 7) << 3) | ((v << (3 - e)) & 7)
+
+
+def e4m3_of_signed(v: int) -> int:
+    return (0x80 | e4m3_of_small(-v)) if v < 0 else e4m3_of_small(v)
+
+
+def e4m3_split(y: int) -> tuple[int, int]:
+    """(code of y - y mod 16, code of y mod 16) for -128 <= y <= 127."""
+    yl = y & 15
+    yh = (y - yl) >> 4
+    return (0 if yh == 0 else e4m3_of_signed(yh) + 0x20), e4m3_of_small(yl)
+
