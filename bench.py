@@ -497,7 +497,7 @@ def main():
         roof = {"bound": "hbm", "kernel": "matvec_rows_kernel<Q4_0, 1 column, 2 lanes per row> (fused FFN up|gate, RMSNorm+Q8_0 prologue, SiLU-mul epilogue)",
                 "achieved": dom["gbs"], "peak": peak,
                 "peak_kind": f"of {peak_kind} ({'MEASURED_PEAKS.json copy bandwidth' if peak_kind == 'measured' else 'fallback 6650 GB/s'})",
-                "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": 50838016 if (dom["bytes"] == 50724864 and WTYPE_NAME == "q4_0") else None,
+                "unit": "GB/s", "frac": dom["gbs"] / peak, "traffic": 50836224 if (dom["bytes"] == 50724864 and WTYPE_NAME == "q4_0") else None,
                 "traffic_source": "ncu capture of this kernel on this matrix, summarised in profiles/matvec_rows_q4_0_ffn_up_gate_7b.md (not re-measured by this run)" if dom["bytes"] == 50724864 else None,
                 "timing": "CUDA events on the launching stream around 320 back-to-back launches (10 sweeps over the 32 layers' matrices, 1.6 GB per sweep)",
                 "bytes_per_launch": dom["bytes"], "us_per_launch": dom["us"], "kernels": kb}
